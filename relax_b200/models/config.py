@@ -1,0 +1,121 @@
+"""Model shape descriptions and the named presets used by recipes and benchmarks.
+
+The fields follow the MODEL_ARGS of the reference's ``scripts/models/*.sh``
+(e.g. scripts/models/qwen3-8B.sh:4-18, scripts/models/qwen3-30B-A3B.sh:40-50).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field, asdict, replace
+from typing import Optional
+
+
+@dataclass
+class VisionConfig:
+    num_layers: int = 32
+    hidden_size: int = 1280
+    num_heads: int = 16
+    ffn_hidden_size: int = 3420
+    patch_size: int = 14
+    spatial_merge_size: int = 2
+    in_channels: int = 3
+    temporal_patch_size: int = 2
+    out_hidden_size: int = 3584
+
+
+@dataclass
+class ModelConfig:
+    name: str = "tiny"
+    num_layers: int = 2
+    hidden_size: int = 256
+    num_attention_heads: int = 4
+    num_query_groups: int = 2
+    head_dim: int = 64
+    ffn_hidden_size: int = 688
+    vocab_size: int = 1024
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    qk_layernorm: bool = True
+    qkv_bias: bool = False
+    tie_word_embeddings: bool = False
+    # MoE
+    num_experts: int = 0
+    moe_top_k: int = 0
+    moe_ffn_hidden_size: int = 0
+    moe_router_norm_topk_prob: bool = True
+    moe_aux_loss_coef: float = 0.0
+    moe_layer_freq: int = 1
+    # multimodal
+    vision: Optional[VisionConfig] = None
+    mrope_section: Optional[tuple] = None  # (t, h, w) halves of head_dim/2
+    image_token_id: int = -1
+    # value / classification head
+    value_head: bool = False
+    dtype: str = "bf16"
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_query_groups * self.head_dim
+
+    def num_parameters(self) -> int:
+        h, L = self.hidden_size, self.num_layers
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        if self.qk_layernorm:
+            attn += 2 * self.head_dim
+        if self.is_moe:
+            mlp = self.num_experts * 3 * h * self.moe_ffn_hidden_size + h * self.num_experts
+        else:
+            mlp = 3 * h * self.ffn_hidden_size
+        per_layer = attn + mlp + 2 * h
+        emb = self.vocab_size * h
+        out = 0 if self.tie_word_embeddings else self.vocab_size * h
+        return L * per_layer + emb + out + h
+
+    def to_dict(self):
+        return asdict(self)
+
+
+PRESETS: dict[str, ModelConfig] = {}
+
+
+def _reg(c: ModelConfig):
+    PRESETS[c.name] = c
+    return c
+
+
+# BASELINE config 0 ("tiny Qwen-style decoder")
+_reg(ModelConfig(name="tiny", num_layers=2, hidden_size=256, num_attention_heads=4, num_query_groups=2,
+                 head_dim=64, ffn_hidden_size=688, vocab_size=1024, dtype="fp32"))
+_reg(ModelConfig(name="tiny-moe", num_layers=2, hidden_size=256, num_attention_heads=4, num_query_groups=2,
+                 head_dim=64, ffn_hidden_size=688, vocab_size=1024, num_experts=8, moe_top_k=2,
+                 moe_ffn_hidden_size=128, dtype="fp32"))
+_reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
+_reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=9728, vocab_size=151936, tie_word_embeddings=True))
+_reg(ModelConfig(name="qwen3-8b", num_layers=36, hidden_size=4096, num_attention_heads=32, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=12288, vocab_size=151936))
+_reg(ModelConfig(name="qwen3-32b", num_layers=64, hidden_size=5120, num_attention_heads=64, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=25600, vocab_size=151936))
+_reg(ModelConfig(name="qwen3-30b-a3b", num_layers=48, hidden_size=2048, num_attention_heads=32, num_query_groups=4,
+                 head_dim=128, ffn_hidden_size=6144, vocab_size=151936, num_experts=128, moe_top_k=8,
+                 moe_ffn_hidden_size=768))
+_reg(ModelConfig(name="qwen2.5-vl-7b", num_layers=28, hidden_size=3584, num_attention_heads=28, num_query_groups=4,
+                 head_dim=128, ffn_hidden_size=18944, vocab_size=152064, qk_layernorm=False, qkv_bias=True,
+                 vision=VisionConfig(), mrope_section=(16, 24, 24), image_token_id=151655))
+_reg(ModelConfig(name="llama3-8b", num_layers=32, hidden_size=4096, num_attention_heads=32, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=14336, vocab_size=128256, qk_layernorm=False, rope_theta=5e5,
+                 rms_norm_eps=1e-5))
+
+
+def get_config(name: str, **overrides) -> ModelConfig:
+    if name not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
+    return replace(PRESETS[name], **overrides)

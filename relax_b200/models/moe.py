@@ -1,0 +1,172 @@
+"""Mixture-of-experts MLP with expert parallelism.
+
+Softmax router in fp32, top-k, token permutation, all-to-all dispatch to the
+ranks that own the experts, grouped SwiGLU expert GEMMs, all-to-all combine and
+weighted un-permutation - the pipeline the reference configures through
+Megatron (scripts/models/qwen3-30B-A3B.sh:40-50: alltoall dispatcher, grouped
+GEMM, permute fusion).  This file is the unfused statement over
+``torch.distributed``; on CUDA the dispatch+permute+grouped-GEMM and
+GEMM+unpermute+combine pairs are fused kernels (:mod:`relax_b200.ops.fused_comm`).
+
+Routing replay (relax/utils/training/routing_replay.py:17-106): when a
+:class:`RoutingReplay` is active the top-k indices recorded by an earlier
+forward (rollout or old-policy) replace the router's own choice, while the
+gate weights are still computed from the current router logits.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..parallel.state import ParallelState
+
+
+class RoutingReplay:
+    """Process-wide record/replay switch for MoE top-k decisions."""
+
+    mode: Optional[str] = None  # None | "record" | "replay"
+    store: dict = {}
+    cursor: dict = {}
+
+    @classmethod
+    def begin_record(cls):
+        cls.mode, cls.store = "record", {}
+
+    @classmethod
+    def begin_replay(cls, store: Optional[dict] = None):
+        cls.mode = "replay"
+        if store is not None:
+            cls.store = store
+        cls.cursor = {k: 0 for k in cls.store}
+
+    @classmethod
+    def end(cls):
+        cls.mode = None
+
+    @classmethod
+    def route(cls, layer_idx: int, idx: torch.Tensor) -> torch.Tensor:
+        if cls.mode == "record":
+            cls.store.setdefault(layer_idx, []).append(idx.detach().clone())
+            return idx
+        if cls.mode == "replay":
+            c = cls.cursor.get(layer_idx, 0)
+            rec = cls.store[layer_idx][c]
+            cls.cursor[layer_idx] = c + 1
+            if rec.shape != idx.shape:
+                raise ValueError(f"routing replay shape mismatch at layer {layer_idx}: {rec.shape} vs {idx.shape}")
+            return rec.to(idx.device)
+        return idx
+
+
+class _AllToAll(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, out_splits, in_splits, group):
+        ctx.group, ctx.out_splits, ctx.in_splits = group, out_splits, in_splits
+        out = x.new_empty((sum(out_splits),) + tuple(x.shape[1:]))
+        dist.all_to_all_single(out, x.contiguous(), out_splits, in_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx = dy.new_empty((sum(ctx.in_splits),) + tuple(dy.shape[1:]))
+        dist.all_to_all_single(dx, dy.contiguous(), ctx.in_splits, ctx.out_splits, group=ctx.group)
+        return dx, None, None, None
+
+
+def grouped_swiglu_mlp(x, tokens_per_expert, w1, w2):
+    """x ``[N, H]`` sorted by expert; w1 ``[E, 2F, H]``, w2 ``[E, H, F]``."""
+    if x.is_cuda:
+        from ..ops import cuda as _c
+
+        if hasattr(_c, "grouped_swiglu_mlp") and not ops._force_ref():
+            return _c.grouped_swiglu_mlp(x, tokens_per_expert, w1, w2)
+    outs, s = [], 0
+    for e, n in enumerate(tokens_per_expert):
+        if n == 0:
+            continue
+        xe = x[s:s + n]
+        a = ops.swiglu(ops.linear(xe, w1[e]))
+        outs.append(ops.linear(a, w2[e]))
+        s += n
+    if not outs:
+        return x.new_zeros(0, w2.shape[1]) + 0.0 * (w1.sum() + w2.sum())
+    return torch.cat(outs, 0)
+
+
+class MoEMLP(nn.Module):
+    def __init__(self, cfg, ps: ParallelState, dtype, device, gen, layer_idx: int):
+        super().__init__()
+        self.cfg, self.ps, self.layer_idx = cfg, ps, layer_idx
+        E, F, H = cfg.num_experts, cfg.moe_ffn_hidden_size, cfg.hidden_size
+        ep = ps.ep.size
+        assert E % ep == 0
+        self.e_local = E // ep
+        self.e_start = ps.ep.rank * self.e_local
+        self.router = nn.Module()
+        self.router.weight = nn.Parameter(gen.draw(f"layers.{layer_idx}.router", (E, H), 0.02).to(dtype))
+        w1 = gen.draw(f"layers.{layer_idx}.experts.fc1", (E, 2 * F, H), 0.02)
+        w2 = gen.draw(f"layers.{layer_idx}.experts.fc2", (E, H, F), 0.02 / math.sqrt(2 * cfg.num_layers))
+        self.experts = nn.Module()
+        self.experts.linear_fc1 = nn.Module()
+        self.experts.linear_fc2 = nn.Module()
+        sl = slice(self.e_start, self.e_start + self.e_local)
+        self.experts.linear_fc1.weight = nn.Parameter(w1[sl].to(dtype).contiguous())
+        self.experts.linear_fc2.weight = nn.Parameter(w2[sl].to(dtype).contiguous())
+        self.last_aux = None
+
+    def forward(self, x):
+        """x ``[T_local, H]`` (the sequence-parallel shard: MoE runs with TP=1 for
+        experts, tokens stay sharded)."""
+        cfg, ps = self.cfg, self.ps
+        T, H = x.shape
+        k, E = cfg.moe_top_k, cfg.num_experts
+        logits = torch.nn.functional.linear(x.float(), self.router.weight.float())
+        w, idx, probs = ops.topk_router(logits, k, cfg.moe_router_norm_topk_prob)
+        replay_idx = RoutingReplay.route(self.layer_idx, idx)
+        if replay_idx is not idx:
+            idx = replay_idx
+            w = probs.gather(-1, idx)
+            if cfg.moe_router_norm_topk_prob:
+                w = w / w.sum(-1, keepdim=True)
+        if cfg.moe_aux_loss_coef > 0 and self.training:
+            f = torch.zeros(E, device=x.device).index_add_(0, idx.reshape(-1), torch.ones(T * k, device=x.device))
+            self.last_aux = cfg.moe_aux_loss_coef * E * ((f / (T * k)) * probs.mean(0)).sum()
+
+        flat_e = idx.reshape(-1)                      # [T*k]
+        order = torch.argsort(flat_e, stable=True)    # permutation: sorted by expert
+        src_tok = order // k
+        xp = x[src_tok]                               # permuted copies [T*k, H]
+        counts = torch.bincount(flat_e, minlength=E)  # tokens per (global) expert
+
+        if ps.ep.size > 1:
+            ep = ps.ep.size
+            send_counts = counts.view(ep, self.e_local)
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts.contiguous(), group=ps.ep.group)
+            in_splits = send_counts.sum(1).tolist()
+            out_splits = recv_counts.sum(1).tolist()
+            xr = _AllToAll.apply(xp, out_splits, in_splits, ps.ep.group)
+            # received rows are ordered (src rank, local expert); regroup by local expert
+            rc = recv_counts.reshape(-1)
+            seg_expert = torch.arange(self.e_local, device=x.device).repeat(ep)
+            row_expert = torch.repeat_interleave(seg_expert, rc)
+            reorder = torch.argsort(row_expert, stable=True)
+            xe = xr[reorder]
+            tpe = recv_counts.sum(0).tolist()
+            ye = grouped_swiglu_mlp(xe, tpe, self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
+            inv = torch.empty_like(reorder)
+            inv[reorder] = torch.arange(reorder.numel(), device=x.device)
+            yr = ye[inv]
+            yp = _AllToAll.apply(yr, in_splits, out_splits, ps.ep.group)
+        else:
+            yp = grouped_swiglu_mlp(xp, counts.tolist(), self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
+
+        wf = w.reshape(-1)[order].to(yp.dtype)
+        out = torch.zeros(T, H, dtype=yp.dtype, device=x.device)
+        out = out.index_add(0, src_tok, yp * wf[:, None])
+        return out.to(x.dtype)

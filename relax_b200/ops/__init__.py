@@ -1,0 +1,108 @@
+"""Operator entry points.
+
+CUDA tensors go to the hand-written sm_100a kernels in the in-tree extension
+(:mod:`relax_b200.ops.cuda`); CPU tensors go to the PyTorch statements in
+:mod:`relax_b200.ops.reference`.  There is no silent fallback on a GPU: if the
+extension is missing, a CUDA call raises.  ``RELAX_B200_FORCE_REFERENCE=1``
+routes CUDA tensors through the PyTorch/library path on purpose - that is the
+"unfused NCCL + cuBLAS" baseline arm used for A/B timing.
+"""
+from __future__ import annotations
+
+import os
+
+from . import reference as ref
+
+
+def _force_ref() -> bool:
+    return os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") == "1"
+
+
+def _use_cuda(t) -> bool:
+    return t.is_cuda and not _force_ref()
+
+
+def _cuda():
+    from . import cuda as _c
+
+    return _c
+
+
+def rmsnorm(x, w, eps=1e-6):
+    return _cuda().rmsnorm(x, w, eps) if _use_cuda(x) else ref.rmsnorm(x, w, eps)
+
+
+def add_rmsnorm(x, residual, w, eps=1e-6):
+    return _cuda().add_rmsnorm(x, residual, w, eps) if _use_cuda(x) else ref.add_rmsnorm(x, residual, w, eps)
+
+
+def swiglu(gate_up):
+    return _cuda().swiglu(gate_up) if _use_cuda(gate_up) else ref.swiglu(gate_up)
+
+
+def linear(x, w, bias=None):
+    return _cuda().linear(x, w, bias) if _use_cuda(x) else ref.linear(x, w, bias)
+
+
+def rope_cos_sin(positions, head_dim, theta, mrope_section=None):
+    return ref.rope_cos_sin(positions, head_dim, theta, mrope_section)
+
+
+def apply_rope(x, cos, sin):
+    return _cuda().apply_rope(x, cos, sin) if _use_cuda(x) else ref.apply_rope(x, cos, sin)
+
+
+def attention_varlen(q, k, v, cu_seqlens, causal=True, scale=None, cu_seqlens_k=None, max_seqlen=None):
+    if _use_cuda(q):
+        return _cuda().attention_varlen(q, k, v, cu_seqlens, causal, scale, cu_seqlens_k, max_seqlen)
+    return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, cu_seqlens_k)
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale=None):
+    if _use_cuda(q):
+        return _cuda().paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
+    return ref.paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
+
+
+def sample(logits, temperature, top_k, top_p, uniform):
+    if _use_cuda(logits):
+        return _cuda().sample(logits, temperature, top_k, top_p, uniform)
+    return ref.sample(logits, temperature, top_k, top_p, uniform)
+
+
+def topk_router(logits, top_k, norm_topk_prob=True):
+    if _use_cuda(logits):
+        return _cuda().topk_router(logits, top_k, norm_topk_prob)
+    return ref.topk_router(logits, top_k, norm_topk_prob)
+
+
+def fused_lm_head_logprob(hidden, weight, targets, tp_group=None, vocab_start=0, with_entropy=True,
+                          temperature=1.0, chunk_size=4096):
+    """LM-head GEMM fused with online-softmax log-prob / entropy; ``[T, V]`` is never stored."""
+    if _use_cuda(hidden):
+        return _cuda().fused_lm_head_logprob(hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature)
+    from ..algo.logprob import chunked_log_probs_and_entropy
+
+    return chunked_log_probs_and_entropy(hidden, weight, targets, tp_group, vocab_start, with_entropy,
+                                         temperature, chunk_size)
+
+
+def fake_int4_quant(x, block_m, block_n, sym=True):
+    if _use_cuda(x):
+        return _cuda().fake_int4_quant(x, block_m, block_n, sym)
+    return ref.fake_int4_quant(x, block_m, block_n, sym)
+
+
+def blockwise_cast_to_fp8(w, block=128, ue8m0=False):
+    if _use_cuda(w):
+        return _cuda().blockwise_cast_to_fp8(w, block, ue8m0)
+    return ref.blockwise_cast_to_fp8(w, block, ue8m0)
+
+
+def blockwise_dequant_fp8(q, scale_inv, block=128, dtype=None):
+    import torch
+
+    dtype = dtype or torch.bfloat16
+    if _use_cuda(q):
+        return _cuda().blockwise_dequant_fp8(q, scale_inv, block, dtype)
+    return ref.blockwise_dequant_fp8(q, scale_inv, block, dtype)

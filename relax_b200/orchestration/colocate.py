@@ -1,0 +1,196 @@
+"""Colocated (synchronous, time-shared GPUs) RL loop in SPMD form.
+
+Every process owns one GPU and plays two roles in turn: a rank of a rollout
+engine, then a rank of the trainer - the reference's ``--colocate`` mode with
+``max_staleness=0`` (one colocated step: relax/components/rollout.py:403-523 +
+relax/backends/megatron/actor.py:724-842).  Per step:
+
+1. ``generate``: the rank's engine samples ``n_samples_per_prompt`` responses
+   for its share of the prompt batch (group prefix sharing, log-probs returned);
+2. rewards + group normalisation; rows are published to the data plane under
+   partition ``train_{rollout_id}``;
+3. rollout memory is released by tag, trainer state is onloaded;
+4. the trainer consumes its rows (task ``actor``): reference / old log-probs,
+   advantages, optimizer steps;
+5. trainer -> rollout weight sync (block-copy plan), version bump.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..data import transfer_queue as tq
+from ..data.convert import convert_samples_to_train_data, custom_meta_rows
+from ..models.config import ModelConfig, get_config
+from ..parallel.state import GroupInfo, ParallelDims, init_parallel_state, single_process_state
+from ..rewards import get_reward_spec
+from ..rollout.data_source import RolloutDataSource, SyntheticPromptDataset
+from ..rollout.engine import RolloutEngine, SamplingParams
+from ..train.actor import TrainActor, TrainConfig
+from ..types import Sample, SampleStatus
+from ..utils.timer import Timer
+from ..weight_sync.plan import TrainerLayout
+from ..weight_sync.sync import WeightSync
+
+
+@dataclass
+class ColocateConfig:
+    model: ModelConfig = field(default_factory=lambda: get_config("tiny"))
+    train: TrainConfig = field(default_factory=TrainConfig)
+    trainer_tp: int = 1
+    trainer_cp: int = 1
+    rollout_tp: int = 1
+    rollout_batch_size: int = 8          # prompts per rollout step (global)
+    prompt_len: int = 64
+    max_response_len: int = 64
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    rm_type: str = "parity"
+    eos_token_id: Optional[int] = None
+    kv_blocks: int = 512
+    kv_block_size: int = 16
+    max_running: int = 256
+    seed: int = 0
+    rollout_seed: int = 42
+    offload_train: bool = False
+    offload_rollout: bool = True
+    num_prompts: int = 1 << 14
+
+
+class ColocatedGRPO:
+    def __init__(self, cfg: ColocateConfig, device="cpu"):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        ttp, tcp = cfg.trainer_tp, cfg.trainer_cp
+        dp = self.world // (ttp * tcp)
+        if self.world > 1:
+            self.ps = init_parallel_state(ParallelDims(tp=ttp, cp=tcp, dp=dp))
+        else:
+            self.ps = single_process_state()
+        # rollout engines: consecutive blocks of rollout_tp ranks
+        rtp = cfg.rollout_tp
+        self.num_engines = self.world // rtp
+        self.engine_id = self.rank // rtp
+        eng_group = None
+        eng_ranks = tuple(range(self.engine_id * rtp, (self.engine_id + 1) * rtp))
+        if rtp > 1:
+            for e in range(self.num_engines):
+                rr = list(range(e * rtp, (e + 1) * rtp))
+                g = dist.new_group(rr)
+                if e == self.engine_id:
+                    eng_group = g
+        self.rollout_tp_group = GroupInfo(eng_group, eng_ranks, self.rank % rtp)
+
+        need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
+        cfg.train.n_samples_per_prompt = cfg.train.n_samples_per_prompt
+        self.actor = TrainActor(cfg.model, cfg.train, self.ps, device=device, seed=cfg.seed, with_reference=need_ref)
+        self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
+                                    num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
+                                    max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
+                                    eos_token_id=cfg.eos_token_id)
+        # the trainer replica that feeds my engine is the one I belong to (colocated)
+        my_dp = self.ps.dp.rank
+        tr_ranks = [r for r in self.ps.tp.ranks]
+        self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
+        self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks
+        if not self._aligned and not (ttp == 1 or rtp == 1 or ttp == rtp):
+            raise NotImplementedError("colocated sync needs trainer TP group == rollout engine ranks, or TP 1 on one side")
+        self.queue = tq.init({"capacity_partitions": 2})
+        ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
+        self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt)
+        self.reward_fn = get_reward_spec(cfg.rm_type).fn
+        self.timer = Timer()
+        self.rollout_id = 0
+        self.sync_weights()
+
+    # ------------------------------------------------------------------ weight sync
+    def sync_weights(self) -> float:
+        params = dict(self.actor.named_local_params())
+        ms = self.sync.update_weights(params, self.engine.weights, self.engine, version=self.actor.weight_version)
+        return ms
+
+    # ------------------------------------------------------------------ rollout
+    def generate(self, rollout_id: int) -> list[Sample]:
+        cfg = self.cfg
+        groups_all = self.data_source.get_samples(cfg.rollout_batch_size)
+        per = cfg.rollout_batch_size // self.num_engines
+        mine = groups_all[self.engine_id * per:(self.engine_id + 1) * per]
+        sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
+                            max_new_tokens=cfg.max_response_len)
+        flat = [s for g in mine for s in g]
+        res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
+        for s, r in zip(flat, res):
+            s.tokens = list(r.prompt) + list(r.output)
+            s.response_length = len(r.output)
+            s.rollout_log_probs = list(r.logprobs)
+            s.weight_versions = sorted(set(r.weight_versions))
+            s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
+            s.reward = self.reward_fn(s)
+        return flat
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> dict:
+        cfg, rid = self.cfg, self.rollout_id
+        t_all = time.perf_counter()
+        with self.timer.span("rollout"):
+            if cfg.offload_rollout:
+                self.engine.resume_memory_occupation(("kv_cache",))
+            samples = self.generate(rid)
+            if cfg.offload_rollout:
+                self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
+        with self.timer.span("data"):
+            batch = convert_samples_to_train_data(
+                samples, advantage_estimator=cfg.train.advantage_estimator,
+                n_samples_per_prompt=cfg.train.n_samples_per_prompt,
+                rewards_normalization=cfg.train.rewards_normalization,
+                grpo_std_normalization=cfg.train.grpo_std_normalization)
+            # ranks of one engine hold identical rows; only the rows of replicas that
+            # differ from mine have to travel
+            batch = self._exchange(batch)
+            part = tq.partition_name(rid)
+            self.queue.put(batch, part, custom_meta=custom_meta_rows(batch), is_last=True)
+            meta = self.queue.get_meta(list(batch.keys()), None, part, "actor")
+            data = self.queue.get_data(meta)
+        with self.timer.span("train"):
+            if cfg.offload_train:
+                self.actor.wake_up()
+            m = self.actor.train(rid, data)
+            self.actor.after_train()
+            if cfg.offload_train:
+                self.actor.sleep()
+        self.queue.clear_partition(part)
+        with self.timer.span("weight_sync"):
+            sync_ms = self.sync_weights()
+        n_resp = sum(batch["response_lengths"])
+        n_tok = sum(batch["total_lengths"])
+        m.update(weight_sync_ms=sync_ms, response_tokens_local=n_resp, total_tokens_local=n_tok,
+                 raw_reward_mean=float(sum(batch["raw_reward"]) / max(1, len(batch["raw_reward"]))),
+                 step_time=time.perf_counter() - t_all)
+        m.update(self.timer.log_dict())
+        self.rollout_id += 1
+        return m
+
+    def _exchange(self, batch: dict) -> dict:
+        """Give every trainer replica the rows it trains on.  When engines and
+        trainer replicas coincide nothing moves; otherwise rows are gathered
+        and re-split evenly over data-parallel replicas."""
+        if self.world == 1 or (self._aligned and not self.cfg.train.balance_data):
+            return batch
+        # one contributor per engine (its tp rank 0)
+        contrib = batch if self.rollout_tp_group.rank == 0 else None
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, contrib)
+        merged: dict = {}
+        for b in gathered:
+            if b is None:
+                continue
+            for k, v in b.items():
+                merged.setdefault(k, []).extend(v)
+        return self.actor.split_for_dp(merged)

@@ -1,0 +1,356 @@
+"""In-house rollout (inference) engine: paged KV cache, continuous batching,
+group prefix sharing, sampling with log-prob return, abort / partial rollout,
+weight-version tagging and tagged memory release.
+
+It fills the place the reference gives to an external inference server
+(relax/backends/sglang/sglang_engine.py:339-1450; request fields used by
+relax/engine/rollout/sglang_rollout.py:299-493: ``input_ids``, sampling
+params, ``return_logprob``).  One engine spans a tensor-parallel group of
+rollout ranks; all ranks of the group run the same scheduler deterministically
+(same requests, same random draws), so no control messages cross ranks inside
+the decode loop - only the collectives inside the model.
+"""
+from __future__ import annotations
+
+import math
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..parallel.state import GroupInfo
+from .weights import RolloutWeights
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = -1
+    max_new_tokens: int = 1024
+    stop_token_ids: tuple = ()
+    ignore_eos: bool = False
+    no_stop_trim: bool = False
+
+
+@dataclass
+class Request:
+    rid: int
+    prompt: list
+    params: SamplingParams
+    group_key: Optional[int] = None
+    output: list = field(default_factory=list)
+    logprobs: list = field(default_factory=list)
+    blocks: list = field(default_factory=list)
+    status: str = "waiting"        # waiting | running | finished | aborted
+    finish_reason: Optional[str] = None
+    weight_versions: list = field(default_factory=list)
+    cached_tokens: int = 0
+    t_arrive: float = 0.0
+    t_first: float = 0.0
+    t_done: float = 0.0
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+class BlockManager:
+    """Reference-counted fixed-size KV blocks."""
+
+    def __init__(self, num_blocks: int, block_size: int):
+        self.num_blocks, self.block_size = num_blocks, block_size
+        self.free = deque(range(num_blocks))
+        self.ref = [0] * num_blocks
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise RuntimeError("KV cache exhausted")
+        b = self.free.popleft()
+        self.ref[b] = 1
+        return b
+
+    def share(self, b: int) -> int:
+        self.ref[b] += 1
+        return b
+
+    def release(self, blocks: Sequence[int]):
+        for b in blocks:
+            self.ref[b] -= 1
+            if self.ref[b] == 0:
+                self.free.append(b)
+            elif self.ref[b] < 0:
+                raise RuntimeError(f"block {b} released twice")
+
+    def blocks_for(self, ntokens: int) -> int:
+        return (ntokens + self.block_size - 1) // self.block_size
+
+
+class RolloutEngine:
+    def __init__(self, cfg: ModelConfig, tp: Optional[GroupInfo] = None, device="cpu", dtype=None,
+                 num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
+                 max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
+                 use_cuda_graph: bool = True):
+        self.cfg = cfg
+        self.tp = tp or GroupInfo(None, (0,), 0)
+        self.device = torch.device(device)
+        self.dtype = dtype or {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
+        self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype)
+        self.block_size = block_size
+        self.bm = BlockManager(num_kv_blocks, block_size)
+        self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
+        self.eos = eos_token_id
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.finished: list[Request] = []
+        self._next_rid = 0
+        self.paused = False
+        self.weight_version = 0
+        self.gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.kv = None
+        self._alloc_kv()
+        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        self._graphs = {}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0}
+
+    # ------------------------------------------------------------------ memory
+    def _alloc_kv(self):
+        c = self.cfg
+        hkv = c.num_query_groups // self.tp.size
+        self.kv = torch.zeros(c.num_layers, 2, self.bm.num_blocks, self.block_size, hkv, c.head_dim,
+                              dtype=self.dtype, device=self.device)
+
+    def release_memory_occupation(self, tags: Sequence[str] = ("kv_cache", "cuda_graph")):
+        """Free device memory by tag (``weights`` / ``kv_cache`` / ``cuda_graph``)
+        while the trainer uses the GPU (relax/distributed/ray/rollout.py:1201-1233)."""
+        if self.running or self.waiting:
+            raise RuntimeError("cannot release memory with requests in flight; abort or drain first")
+        if "cuda_graph" in tags:
+            self._graphs = {}
+        if "kv_cache" in tags:
+            self.kv = None
+        if "weights" in tags:
+            self.weights.release()
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def resume_memory_occupation(self, tags: Sequence[str] = ("kv_cache",)):
+        if "weights" in tags:
+            self.weights.resume()
+        if "kv_cache" in tags and self.kv is None:
+            self._alloc_kv()
+
+    def flush_cache(self):
+        if self.running:
+            raise RuntimeError("flush_cache with running requests")
+        self.bm = BlockManager(self.bm.num_blocks, self.block_size)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: Sequence[int], params: SamplingParams, group_key: Optional[int] = None,
+                    resume_output: Optional[Sequence[int]] = None, resume_logprobs: Optional[Sequence[float]] = None) -> int:
+        r = Request(self._next_rid, list(prompt), params, group_key, t_arrive=time.perf_counter())
+        if resume_output:
+            # partial rollout: earlier tokens become part of the context, generation continues
+            r.output = list(resume_output)
+            r.logprobs = list(resume_logprobs or [0.0] * len(r.output))
+        self._next_rid += 1
+        self.waiting.append(r)
+        return r.rid
+
+    def pause_generation(self):
+        self.paused = True
+
+    def continue_generation(self):
+        self.paused = False
+
+    def abort_all(self) -> list[Request]:
+        """Stop every request; running ones are returned with their partial output."""
+        out = []
+        for r in self.running:
+            self.bm.release(r.blocks)
+            r.blocks = []
+            r.status, r.finish_reason = "aborted", "abort"
+            out.append(r)
+        for r in self.waiting:
+            r.status, r.finish_reason = "aborted", "abort"
+            out.append(r)
+        self.running, self.waiting = [], deque()
+        return out
+
+    @property
+    def has_work(self) -> bool:
+        return bool(self.running or self.waiting)
+
+    # ------------------------------------------------------------------ scheduling
+    def _admit(self) -> list[Request]:
+        """Move waiting requests to running while KV blocks (reserved for their
+        whole maximum length) and the prefill token budget allow."""
+        admitted, budget = [], self.max_prefill_tokens
+        leaders: dict = {}
+        while self.waiting and len(self.running) + len(admitted) < self.max_running:
+            r = self.waiting[0]
+            ctx = r.num_tokens
+            need_total = self.bm.blocks_for(len(r.prompt) + r.params.max_new_tokens)
+            lead = leaders.get(r.group_key) if (r.group_key is not None and not r.output) else None
+            shared_full = (len(r.prompt) - 1) // self.block_size if lead is not None else 0
+            need = need_total - shared_full
+            reserved = sum(getattr(x, "_reserve", 0) for x in self.running) + sum(getattr(x, "_reserve", 0) for x in admitted)
+            if need > self.bm.num_free - reserved:
+                break
+            if lead is None and ctx > budget and admitted:
+                break
+            self.waiting.popleft()
+            r._lead = lead
+            if lead is None:
+                budget -= ctx
+                if r.group_key is not None and not r.output:
+                    leaders[r.group_key] = r
+                nb = self.bm.blocks_for(ctx)
+                r.blocks = [self.bm.alloc() for _ in range(nb)]
+            else:
+                # share the leader's full prompt blocks; own the tail block (copied after prefill)
+                r.blocks = [self.bm.share(b) for b in lead.blocks[:shared_full]]
+                r.blocks += [self.bm.alloc() for _ in range(self.bm.blocks_for(ctx) - shared_full)]
+                r.cached_tokens = shared_full * self.block_size
+            r._reserve = need_total - len(r.blocks)
+            r.status = "running"
+            admitted.append(r)
+        return admitted
+
+    def _slots(self, r: Request, start: int, end: int) -> list:
+        bs = self.block_size
+        return [r.blocks[p // bs] * bs + p % bs for p in range(start, end)]
+
+    # ------------------------------------------------------------------ step
+    @torch.no_grad()
+    def step(self) -> list[Request]:
+        """One scheduler iteration: admit + prefill new requests, else one decode
+        step for all running requests.  Returns requests that finished."""
+        if self.paused:
+            return []
+        self.stats["steps"] += 1
+        new = self._admit()
+        if new:
+            self._prefill(new)
+            self.running.extend(new)
+        elif self.running:
+            self._decode()
+        done = [r for r in self.running if r.status == "finished"]
+        if done:
+            self.running = [r for r in self.running if r.status != "finished"]
+            for r in done:
+                self.bm.release(r.blocks)
+                r.blocks = []
+                r._reserve = 0
+                r.t_done = time.perf_counter()
+        return done
+
+    def _prefill(self, reqs: list[Request]):
+        leaders = [r for r in reqs if r._lead is None]
+        toks, pos, cu, slots, last_rows = [], [], [0], [], []
+        for r in leaders:
+            ctx = r.prompt + r.output
+            toks += ctx
+            pos += list(range(len(ctx)))
+            slots += self._slots(r, 0, len(ctx))
+            cu.append(cu[-1] + len(ctx))
+            last_rows.append(cu[-1] - 1)
+        dev = self.device
+        if leaders:
+            t = torch.tensor(toks, dtype=torch.int64, device=dev)
+            logits = self.weights.forward_prefill(
+                t, torch.tensor(pos, dtype=torch.int64, device=dev),
+                torch.tensor(cu, dtype=torch.int32, device=dev),
+                torch.tensor(slots, dtype=torch.int64, device=dev), self.kv,
+                torch.tensor(last_rows, dtype=torch.int64, device=dev), self.tp, max_seqlen=max(b - a for a, b in zip(cu, cu[1:])))
+            self.stats["prefill_tokens"] += len(toks)
+        row_of = {id(r): i for i, r in enumerate(leaders)}
+        # followers copy the leader's partially filled tail block and reuse its last-token logits
+        rows = []
+        bs = self.block_size
+        for r in reqs:
+            lead = r._lead
+            if lead is not None:
+                n_shared = (len(r.prompt) - 1) // bs
+                for j in range(n_shared, len(lead.blocks)):
+                    if j < len(r.blocks):
+                        self.kv[:, :, r.blocks[j]] = self.kv[:, :, lead.blocks[j]]
+                self.stats["cached_tokens"] += len(r.prompt)
+                rows.append(row_of[id(lead)])
+            else:
+                rows.append(row_of[id(r)])
+        sel = logits[torch.tensor(rows, device=dev)] if len(rows) != len(leaders) or rows != list(range(len(leaders))) else logits
+        self._sample_and_append(reqs, sel)
+        now = time.perf_counter()
+        for r in reqs:
+            r.t_first = now
+
+    def _decode(self):
+        reqs = self.running
+        dev = self.device
+        bs = self.block_size
+        # the newest token of each request is fed; its K/V goes to position num_tokens-1
+        for r in reqs:
+            p = r.num_tokens - 1
+            if p // bs >= len(r.blocks):
+                r.blocks.append(self.bm.alloc())
+                r._reserve = max(0, r._reserve - 1)
+        B = len(reqs)
+        maxb = max(len(r.blocks) for r in reqs)
+        bt = torch.zeros(B, maxb, dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            bt[i, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
+        tok = torch.tensor([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], dtype=torch.int64, device=dev)
+        pos = torch.tensor([r.num_tokens - 1 for r in reqs], dtype=torch.int64, device=dev)
+        ctx = torch.tensor([r.num_tokens for r in reqs], dtype=torch.int32, device=dev)
+        slots = torch.tensor([self._slots(r, r.num_tokens - 1, r.num_tokens)[0] for r in reqs], dtype=torch.int64, device=dev)
+        logits = self.weights.forward_decode(tok, pos, bt.to(dev), ctx, slots, self.kv, self.tp)
+        self.stats["decode_tokens"] += B
+        self._sample_and_append(reqs, logits)
+
+    def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):
+        dev = self.device
+        B = len(reqs)
+        v = self.cfg.vocab_size
+        logits = logits[:, :v]
+        temp = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
+        topk = torch.tensor([r.params.top_k for r in reqs], dtype=torch.int64, device=dev)
+        topp = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
+        u = torch.rand(B, generator=self.gen).to(dev)
+        tok, lp = ops.sample(logits, temp, topk, topp, u)
+        tok_l, lp_l = tok.tolist(), lp.tolist()
+        for r, t, l in zip(reqs, tok_l, lp_l):
+            r.output.append(t)
+            r.logprobs.append(l)
+            r.weight_versions.append(self.weight_version)
+            stop = (not r.params.ignore_eos) and ((self.eos is not None and t == self.eos) or t in r.params.stop_token_ids)
+            if stop:
+                r.status, r.finish_reason = "finished", "stop"
+            elif len(r.output) >= r.params.max_new_tokens:
+                r.status, r.finish_reason = "finished", "length"
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],
+                 group_keys: Optional[Sequence[int]] = None) -> list[Request]:
+        """Blocking generation of a batch; results in the order of ``prompts``."""
+        ids = []
+        for i, p in enumerate(prompts):
+            sp = params if isinstance(params, SamplingParams) else params[i]
+            ids.append(self.add_request(p, sp, group_keys[i] if group_keys is not None else None))
+        res = {}
+        while self.has_work:
+            for r in self.step():
+                res[r.rid] = r
+        return [res[i] for i in ids]
+
+    def update_weight_version(self, v: int):
+        self.weight_version = v

@@ -1,0 +1,187 @@
+"""Parameter buffers and model forward of the rollout engine.
+
+Layout ("rollout layout", one TP shard per rank, all in ONE flat buffer so the
+weight-sync kernel writes into a single registered region):
+
+* ``layers.{i}.qkv``      ``[(nq + 2 nkv) * hd, H]`` rows ordered ``[q heads | k heads | v heads]``
+* ``layers.{i}.o``        ``[H, nq * hd]``
+* ``layers.{i}.gate_up``  ``[2 F, H]`` rows ``[gate | up]``
+* ``layers.{i}.down``     ``[H, F]``
+* ``layers.{i}.input_norm / post_norm / q_norm / k_norm``
+* ``embed [V_l, H]``, ``lm_head [V_l, H]`` (aliases ``embed`` when tied), ``final_norm``
+* MoE layers: ``router [E, H]``, ``experts_gate_up [E_l, 2F, H]``, ``experts_down [E_l, H, F]``
+
+The HF/serving order of q|k|v differs from the trainer's per-group interleave;
+the permutation is applied by the weight-sync path
+(:mod:`relax_b200.weight_sync`).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.config import ModelConfig
+from ..parallel.state import GroupInfo
+
+
+def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
+    hd, H = cfg.head_dim, cfg.hidden_size
+    nq, nkv = cfg.num_attention_heads // tp, cfg.num_query_groups // tp
+    v_pad = (cfg.vocab_size + tp - 1) // tp * tp
+    shapes = {"embed": (v_pad // tp, H)}
+    for i in range(cfg.num_layers):
+        p = f"layers.{i}."
+        shapes[p + "input_norm"] = (H,)
+        shapes[p + "qkv"] = ((nq + 2 * nkv) * hd, H)
+        if cfg.qkv_bias:
+            shapes[p + "qkv_bias"] = ((nq + 2 * nkv) * hd,)
+        if cfg.qk_layernorm:
+            shapes[p + "q_norm"] = (hd,)
+            shapes[p + "k_norm"] = (hd,)
+        shapes[p + "o"] = (H, nq * hd)
+        shapes[p + "post_norm"] = (H,)
+        if cfg.is_moe and i % cfg.moe_layer_freq == 0:
+            el = cfg.num_experts // ep
+            shapes[p + "router"] = (cfg.num_experts, H)
+            shapes[p + "experts_gate_up"] = (el, 2 * cfg.moe_ffn_hidden_size, H)
+            shapes[p + "experts_down"] = (el, H, cfg.moe_ffn_hidden_size)
+        else:
+            F = cfg.ffn_hidden_size // tp
+            shapes[p + "gate_up"] = (2 * F, H)
+            shapes[p + "down"] = (H, F)
+    shapes["final_norm"] = (H,)
+    if not cfg.tie_word_embeddings:
+        shapes["lm_head"] = (v_pad // tp, H)
+    return shapes
+
+
+class RolloutWeights:
+    def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0):
+        self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
+        self.ep_size, self.ep_rank = ep_size, ep_rank
+        self.device, self.dtype = torch.device(device), dtype
+        self.shapes = rollout_param_shapes(cfg, tp_size, ep_size)
+        self.offsets, n = {}, 0
+        for k, s in self.shapes.items():
+            self.offsets[k] = n
+            n += (math.prod(s) + 127) // 128 * 128
+        self.numel = n
+        self.flat = None
+        self.p: dict[str, torch.Tensor] = {}
+        self.resume()
+        self.v_local = self.shapes["embed"][0]
+        self.vocab_start = tp_rank * self.v_local
+
+    def resume(self):
+        if self.flat is not None:
+            return
+        self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        self.p = {k: self.flat[o:o + math.prod(self.shapes[k])].view(self.shapes[k]) for k, o in self.offsets.items()}
+        if self.cfg.tie_word_embeddings:
+            self.p["lm_head"] = self.p["embed"]
+
+    def release(self):
+        self.flat, self.p = None, {}
+
+    # ------------------------------------------------------------------ model pieces
+    def _embed(self, tokens, tp: GroupInfo):
+        w = self.p["embed"]
+        if tp.size == 1:
+            return w[tokens]
+        loc = tokens - self.vocab_start
+        ok = (loc >= 0) & (loc < self.v_local)
+        e = w[torch.where(ok, loc, torch.zeros_like(loc))] * ok[:, None].to(w.dtype)
+        dist.all_reduce(e, group=tp.group)
+        return e
+
+    def _allreduce(self, x, tp: GroupInfo):
+        if tp.size > 1:
+            dist.all_reduce(x, group=tp.group)
+        return x
+
+    def _logits(self, h, tp: GroupInfo):
+        z = ops.linear(h, self.p["lm_head"]).float()
+        if tp.size > 1:
+            out = torch.empty(tp.size, z.shape[0], z.shape[1], dtype=z.dtype, device=z.device)
+            dist.all_gather_into_tensor(out, z.contiguous(), group=tp.group)
+            z = out.permute(1, 0, 2).reshape(z.shape[0], -1)
+        return z
+
+    def _mlp(self, i, x, tp):
+        p, cfg = self.p, self.cfg
+        pre = f"layers.{i}."
+        if pre + "router" in p:
+            logits = torch.nn.functional.linear(x.float(), p[pre + "router"].float())
+            w, idx, _ = ops.topk_router(logits, cfg.moe_top_k, cfg.moe_router_norm_topk_prob)
+            out = torch.zeros_like(x, dtype=torch.float32)
+            el = p[pre + "experts_gate_up"].shape[0]
+            e0 = self.ep_rank * el
+            for e in range(el):
+                m = (idx == e0 + e)
+                rows = m.any(-1).nonzero()[:, 0]
+                if rows.numel() == 0:
+                    continue
+                a = ops.swiglu(ops.linear(x[rows], p[pre + "experts_gate_up"][e]))
+                y = ops.linear(a, p[pre + "experts_down"][e]).float()
+                out.index_add_(0, rows, y * (w * m)[rows].sum(-1, keepdim=True))
+            return out.to(x.dtype), self.ep_size > 1
+        a = ops.swiglu(ops.linear(x, p[pre + "gate_up"]))
+        return ops.linear(a, p[pre + "down"]), tp.size > 1
+
+    def _layer(self, i, h, cos, sin, attn, tp):
+        cfg, p = self.cfg, self.p
+        pre = f"layers.{i}."
+        hd = cfg.head_dim
+        nq, nkv = cfg.num_attention_heads // self.tp_size, cfg.num_query_groups // self.tp_size
+        x = ops.rmsnorm(h, p[pre + "input_norm"], cfg.rms_norm_eps)
+        qkv = ops.linear(x, p[pre + "qkv"], p.get(pre + "qkv_bias"))
+        T = qkv.shape[0]
+        q = qkv[:, : nq * hd].reshape(T, nq, hd)
+        k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+        v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+        if cfg.qk_layernorm:
+            q = ops.rmsnorm(q, p[pre + "q_norm"], cfg.rms_norm_eps)
+            k = ops.rmsnorm(k, p[pre + "k_norm"], cfg.rms_norm_eps)
+        q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+        o = attn(i, q, k, v).reshape(T, nq * hd)
+        a = self._allreduce(ops.linear(o, p[pre + "o"]), tp)
+        x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
+        m, need_ar = self._mlp(i, x, tp)
+        if need_ar:
+            m = self._allreduce(m, tp)
+        return h + m
+
+    def _run(self, tokens, positions, attn, tp):
+        cfg = self.cfg
+        h = self._embed(tokens, tp)
+        cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        for i in range(cfg.num_layers):
+            h = self._layer(i, h, cos, sin, attn, tp)
+        return ops.rmsnorm(h, self.p["final_norm"], cfg.rms_norm_eps)
+
+    # ------------------------------------------------------------------ entry points
+    def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
+        def attn(i, q, k, v):
+            kc = kv[i, 0].view(-1, k.shape[1], k.shape[2])
+            vc = kv[i, 1].view(-1, v.shape[1], v.shape[2])
+            kc[slots] = k
+            vc[slots] = v
+            return ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=True, max_seqlen=max_seqlen)
+
+        h = self._run(tokens, positions, attn, tp)
+        return self._logits(h[last_rows], tp)
+
+    def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
+        def attn(i, q, k, v):
+            kc = kv[i, 0].view(-1, k.shape[1], k.shape[2])
+            vc = kv[i, 1].view(-1, v.shape[1], v.shape[2])
+            kc[slots] = k
+            vc[slots] = v
+            return ops.paged_decode_attention(q, kv[i, 0], kv[i, 1], block_tables, context_lens)
+
+        h = self._run(tokens, positions, attn, tp)
+        return self._logits(h, tp)

@@ -1,0 +1,344 @@
+"""Policy trainer rank (``actor`` / ``actor_fwd`` / ``reference`` / ``critic`` roles).
+
+One :class:`TrainActor` lives in each trainer process.  It owns the model
+shard, the distributed optimizer and tagged weight snapshots (``actor``,
+``ref``, ``old_actor``, ``teacher``), and exposes the operations the reference's
+trainer actor offers (relax/backends/megatron/actor.py:177: ``train``,
+``compute_log_prob``, ``update_weights``, ``save_model``, ``sleep`` / ``wake_up``).
+
+A training call follows relax/backends/megatron/actor.py:890-1096:
+reference log-probs -> old-policy log-probs -> advantages -> optimizer steps.
+"""
+from __future__ import annotations
+
+import math
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..algo import loss as L
+from ..algo.ppo_utils import Segments, post_process_rewards
+from ..data.packing import pack_samples
+from ..data.seqlen_balancing import balanced_microbatches, karmarkar_karp
+from ..models.config import ModelConfig
+from ..models.transformer import GPTModel
+from ..parallel.state import ParallelState, single_process_state
+from ..utils.timer import Timer
+from .optimizer import DistributedOptimizer, OptimizerConfig
+
+
+@dataclass
+class TrainConfig:
+    advantage_estimator: str = "grpo"
+    global_batch_size: int = 32            # samples per optimizer step (all DP ranks together)
+    max_tokens_per_gpu: int = 8192         # dynamic micro-batch token cap
+    use_dynamic_batch_size: bool = True
+    micro_batch_size: int = 1
+    rollout_temperature: float = 1.0
+    n_samples_per_prompt: int = 8
+    kl_coef: float = 0.0                   # reward shaping (ppo / reinforce++)
+    gamma: float = 1.0
+    lambd: float = 1.0
+    normalize_advantages: bool = False
+    rewards_normalization: bool = True
+    grpo_std_normalization: bool = True
+    balance_data: bool = False
+    recompute: bool = False
+    pad_multiple: int = 128
+    use_rollout_logprobs: bool = False
+    keep_old_actor: bool = False
+    compute_entropy: bool = True
+    loss: L.LossConfig = field(default_factory=L.LossConfig)
+    optim: OptimizerConfig = field(default_factory=OptimizerConfig)
+
+
+class TrainActor:
+    def __init__(self, model_cfg: ModelConfig, cfg: TrainConfig, ps: Optional[ParallelState] = None,
+                 device="cpu", seed: int = 0, role: str = "actor", with_optimizer: bool = True,
+                 with_reference: bool = False):
+        self.mcfg, self.cfg, self.role = model_cfg, cfg, role
+        self.ps = ps or single_process_state()
+        self.device = torch.device(device)
+        self.model = GPTModel(model_cfg, self.ps, device=device, seed=seed, recompute=cfg.recompute)
+        self.optimizer = DistributedOptimizer(self.model, self.ps, cfg.optim) if with_optimizer else None
+        self.timer = Timer()
+        self.weight_version = 0
+        self.snapshots: dict[str, torch.Tensor] = {}
+        self._active_tag = "actor"
+        if self.optimizer is None:
+            self._flatten_params()
+        if with_reference:
+            self.backup("ref")
+
+    # ------------------------------------------------------------------ tagged weights
+    def _flatten_params(self):
+        ps_ = [p for p in self.model.parameters()]
+        n = sum((p.numel() + 15) // 16 * 16 for p in ps_)
+        buf = torch.zeros(n, dtype=ps_[0].dtype, device=ps_[0].device)
+        o = 0
+        self._flat_offsets = []
+        for p in ps_:
+            v = buf[o:o + p.numel()].view_as(p)
+            v.copy_(p.data)
+            p.data = v
+            self._flat_offsets.append(o)
+            o += (p.numel() + 15) // 16 * 16
+        self._flat = buf
+
+    @property
+    def param_buf(self) -> torch.Tensor:
+        return self.optimizer.param_buf if self.optimizer is not None else self._flat
+
+    def _bound_params(self):
+        if self.optimizer is not None:
+            return list(zip(self.optimizer.params, self.optimizer.offsets))
+        return list(zip(self.model.parameters(), self._flat_offsets))
+
+    def backup(self, tag: str, to_host: bool = False):
+        """Snapshot the active weights under ``tag`` (device copy, or pinned host
+        copy like relax/utils/training/tensor_backper.py:48-80)."""
+        src = self.param_buf
+        if to_host:
+            dst = self.snapshots.get(tag)
+            if dst is None or dst.is_cuda or dst.shape != src.shape:
+                dst = torch.empty(src.shape, dtype=src.dtype, pin_memory=src.is_cuda)
+            dst.copy_(src, non_blocking=True)
+        else:
+            dst = src.clone()
+        self.snapshots[tag] = dst
+
+    def switch_model(self, tag: str):
+        """Make the weights stored under ``tag`` the ones the model computes
+        with.  Device snapshots are bound by re-pointing the parameter views (no
+        copy); host snapshots are copied into a staging buffer first."""
+        if tag == self._active_tag:
+            return
+        if tag == "actor":
+            buf = self.param_buf
+        else:
+            buf = self.snapshots[tag]
+            if not buf.is_cuda and self.device.type == "cuda":
+                stage = getattr(self, "_stage", None)
+                if stage is None:
+                    stage = self._stage = torch.empty_like(self.param_buf)
+                stage.copy_(buf, non_blocking=True)
+                buf = stage
+        for p, o in self._bound_params():
+            p.data = buf[o:o + p.numel()].view_as(p)
+        self._active_tag = tag
+
+    # ------------------------------------------------------------------ forward
+    def _pack(self, tokens: Sequence, response_lengths: Sequence[int]):
+        mult = self.ps.tp.size * (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
+        return pack_samples(tokens, response_lengths, pad_multiple=max(1, mult), device=self.device)
+
+    def _forward_logp(self, pb, with_entropy: bool):
+        h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+        hr = h.index_select(0, pb.logit_rows)
+        return self.model.log_probs(hr, pb.targets, self.cfg.rollout_temperature, with_entropy)
+
+    def _microbatches(self, lengths: Sequence[int], for_train: bool = True) -> list[list[int]]:
+        cfg = self.cfg
+        n = len(lengths)
+        if n == 0:
+            mbs = []
+        elif cfg.use_dynamic_batch_size:
+            mbs = balanced_microbatches(list(lengths), cfg.max_tokens_per_gpu)
+        else:
+            mbs = [list(range(s, min(n, s + cfg.micro_batch_size))) for s in range(0, n, cfg.micro_batch_size)]
+        # every data-parallel replica must run the same number of micro-batches
+        # (collectives inside the model); short ranks append dummy ones
+        cnt = torch.tensor([len(mbs)], device=self.device)
+        if self.ps.dp_cp.size > 1:
+            dist.all_reduce(cnt, op=dist.ReduceOp.MAX, group=self.ps.dp_cp.group)
+        while len(mbs) < int(cnt):
+            mbs.append([])
+        return mbs
+
+    @torch.no_grad()
+    def compute_log_prob(self, batch: dict, tag: str = "actor", with_entropy: bool = False) -> dict:
+        """Forward-only pass; returns per-sample lists ``log_probs`` (and ``entropy``)."""
+        self.switch_model(tag)
+        toks, rl = batch["tokens"], batch["response_lengths"]
+        mbs = self._microbatches([len(t) for t in toks])
+        out_lp = [None] * len(toks)
+        out_en = [None] * len(toks)
+        for mb in mbs:
+            if not mb:
+                self._dummy_forward()
+                continue
+            pb = self._pack([toks[i] for i in mb], [rl[i] for i in mb])
+            lp, en = self._forward_logp(pb, with_entropy)
+            for i, a, b in zip(mb, torch.split(lp, pb.response_lengths), torch.split(en, pb.response_lengths)):
+                out_lp[i], out_en[i] = a, b
+        self.switch_model("actor")
+        res = {"log_probs": out_lp}
+        if with_entropy:
+            res["entropy"] = out_en
+        return res
+
+    def _dummy_forward(self, backward: bool = False):
+        pb = self._pack([[0, 0]], [1])
+        if backward:
+            lp, en = self._forward_logp(pb, False)
+            (lp.sum() * 0.0).backward()
+        else:
+            with torch.no_grad():
+                self._forward_logp(pb, False)
+
+    # ------------------------------------------------------------------ data-parallel split
+    def split_for_dp(self, batch: dict) -> dict:
+        """Keep this replica's share of a batch that every rank holds in full.
+        ``balance_data`` equalises token totals (Karmarkar-Karp), else contiguous."""
+        dp, r = self.ps.dp.size, self.ps.dp.rank
+        n = len(batch["tokens"])
+        if dp == 1:
+            return batch
+        if self.cfg.balance_data and n % dp == 0:
+            idx = karmarkar_karp([len(t) for t in batch["tokens"]], dp, equal_size=True)[r]
+        else:
+            per = n // dp
+            idx = list(range(r * per, (r + 1) * per))
+        return {k: ([v[i] for i in idx] if isinstance(v, list) and len(v) == n else v) for k, v in batch.items()}
+
+    # ------------------------------------------------------------------ training
+    def train(self, rollout_id: int, batch: dict) -> dict:
+        """One rollout's worth of optimizer steps on this replica's samples
+        (``batch`` already split for data parallelism).  Returns reduced metrics."""
+        cfg, dev = self.cfg, self.device
+        t0 = time.perf_counter()
+        n = len(batch["tokens"])
+        resp = [int(r) for r in batch["response_lengths"]]
+        masks = [torch.as_tensor(m, dtype=torch.float32, device=dev) for m in batch["loss_masks"]]
+
+        with self.timer.span("ref_log_probs"):
+            if "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
+                batch["ref_log_probs"] = self.compute_log_prob(batch, "ref")["log_probs"]
+        with self.timer.span("old_log_probs"):
+            if cfg.use_rollout_logprobs and batch.get("rollout_log_probs") is not None:
+                batch["log_probs"] = [torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch["rollout_log_probs"]]
+            elif not cfg.loss.true_on_policy:
+                tag = "old_actor" if (cfg.keep_old_actor and "old_actor" in self.snapshots) else "actor"
+                batch["log_probs"] = self.compute_log_prob(batch, tag)["log_probs"]
+
+        seg_all = Segments.from_lengths(resp, device=dev)
+        mask_all = torch.cat(masks) if masks else torch.zeros(0, device=dev)
+        rewards = torch.as_tensor(batch["rewards"], dtype=torch.float32, device=dev)
+        cat = lambda k: torch.cat([torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch[k]]) \
+            if batch.get(k) is not None and len(batch[k]) else None
+        adv, ret = L.compute_advantages_and_returns(
+            cfg.advantage_estimator, rewards, seg_all, mask_all,
+            log_probs=cat("log_probs"), ref_log_probs=cat("ref_log_probs"), values=cat("values"),
+            kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type, gamma=cfg.gamma, lambd=cfg.lambd,
+            normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group,
+        )
+        batch["advantages"] = seg_all.split(adv)
+        batch["returns"] = seg_all.split(ret)
+
+        dp = self.ps.dp.size
+        per_step = max(1, cfg.global_batch_size // dp)
+        steps = max(1, math.ceil(n / per_step)) if n else 1
+        nsteps = torch.tensor([steps], device=dev)
+        if self.ps.dp_cp.size > 1:
+            dist.all_reduce(nsteps, op=dist.ReduceOp.MAX, group=self.ps.dp_cp.group)
+        agg: dict[str, torch.Tensor] = {}
+        last_norm = 0.0
+        for s in range(int(nsteps)):
+            idx = list(range(s * per_step, min(n, (s + 1) * per_step)))
+            with self.timer.span("train_step"):
+                m, last_norm = self._train_step(batch, idx)
+            for k, v in m.items():
+                agg[k] = agg.get(k, 0) + v / int(nsteps)
+        out = {k: float(v) for k, v in agg.items()}
+        out["grad_norm"] = last_norm
+        out["train_time"] = time.perf_counter() - t0
+        return out
+
+    def _loss_batch(self, batch, idx, pb) -> L.LossBatch:
+        dev = self.device
+        f = lambda key: torch.cat([torch.as_tensor(batch[key][i], dtype=torch.float32, device=dev) for i in idx]) \
+            if batch.get(key) is not None else None
+        seg = Segments.from_lengths(pb.response_lengths, device=dev)
+        denoms = None
+        if batch.get("sample_index_mask_sums") is not None:
+            denoms = torch.as_tensor([batch["sample_index_mask_sums"][i] for i in idx], dtype=torch.float32, device=dev)
+        return L.LossBatch(seg=seg, loss_mask=f("loss_masks"), advantages=f("advantages"),
+                           old_log_probs=f("log_probs"), ref_log_probs=f("ref_log_probs"),
+                           rollout_log_probs=f("rollout_log_probs"), returns=f("returns"), values=f("values"),
+                           sample_denoms=denoms)
+
+    def _train_step(self, batch, idx):
+        cfg, ps = self.cfg, self.ps
+        opt = self.optimizer
+        self.switch_model("actor")
+        opt.zero_grad()
+        lens = [len(batch["tokens"][i]) for i in idx]
+        mbs = self._microbatches(lens)
+        dp_cp = ps.dp_cp.size
+        metrics: dict[str, torch.Tensor] = {}
+        ntok = torch.zeros(1, device=self.device)
+        for mb in mbs:
+            if not mb:
+                self._dummy_forward(backward=True)
+                continue
+            ids = [idx[j] for j in mb]
+            pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
+            lp, en = self._forward_logp(pb, cfg.compute_entropy)
+            lb = self._loss_batch(batch, ids, pb)
+            if self.role == "critic":
+                raise NotImplementedError
+            loss, m = L.policy_loss(lp, en, lb, cfg.loss)
+            ntok += lb.loss_mask.sum()
+            if cfg.loss.calculate_per_token_loss:
+                scaled = loss
+            else:
+                scaled = loss * (dp_cp / cfg.global_batch_size)
+            scaled.backward()
+            for k, v in m.items():
+                metrics[k] = metrics.get(k, 0) + v.detach().float()
+        gscale = 1.0
+        if cfg.loss.calculate_per_token_loss:
+            tot = ntok.clone()
+            if dp_cp > 1:
+                dist.all_reduce(tot, group=ps.dp_cp.group)
+            gscale = dp_cp / float(tot.clamp_min(1))
+        norm, skipped = opt.step(grad_scale=gscale)
+        # metrics: sum over samples -> mean over the global batch
+        keys = sorted(metrics)
+        if keys:
+            vec = torch.stack([metrics[k] for k in keys])
+        else:
+            vec = torch.zeros(0, device=self.device)
+        if cfg.loss.calculate_per_token_loss:
+            denom = ntok.clone()
+        else:
+            denom = torch.tensor([float(len(idx))], device=self.device)
+        pack = torch.cat([vec, denom])
+        if dp_cp > 1:
+            # every replica must contribute the same keys; keys depend only on the config
+            dist.all_reduce(pack, group=ps.dp_cp.group)
+        d = pack[-1].clamp_min(1)
+        out = {k: pack[i] / d for i, k in enumerate(keys)}
+        return out, norm
+
+    # ------------------------------------------------------------------ misc
+    def after_train(self):
+        self.weight_version += 1
+        if self.cfg.keep_old_actor:
+            self.backup("old_actor")
+
+    def named_local_params(self):
+        """(megatron-style name, tensor) for every local parameter, actor weights."""
+        self.switch_model("actor")
+        return list(self.model.named_parameters())
+
+    def sleep(self):
+        if self.optimizer is not None:
+            self.optimizer.offload_state()
+
+    def wake_up(self):
+        if self.optimizer is not None:
+            self.optimizer.onload_state()

@@ -1,0 +1,282 @@
+"""Distributed optimizer (ZeRO-1) on flat buffers.
+
+All parameters of a rank are views into ONE contiguous low-precision buffer and
+their gradients accumulate into ONE contiguous gradient buffer.  After the
+backward passes of a step the gradient buffer is reduce-scattered over the
+data-parallel group; every rank runs Adam on its contiguous shard (fp32 state)
+and the updated shard is all-gathered back into the parameter buffer - the
+behaviour of the reference's always-on distributed optimizer
+(relax/backends/megatron/arguments.py:266-289, model.py:282-354,968-1312).
+
+Memory layout choice for 180 GB parts: the fp32 master weight of a bf16
+parameter is stored as the bf16 value plus a signed 16-bit remainder
+(``fp32_bits == (bf16_bits << 16) + int16``), which reconstructs the fp32
+master exactly while saving two bytes per parameter compared with a separate
+fp32 copy.  Ten bytes of optimizer state per parameter, spread over dp ranks.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Iterable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.state import ParallelState
+
+
+@dataclass
+class OptimizerConfig:
+    lr: float = 1e-6
+    min_lr: float = 0.0
+    weight_decay: float = 0.0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_eps: float = 1e-8
+    clip_grad: float = 1.0
+    lr_decay_style: str = "constant"   # constant | linear | cosine
+    lr_warmup_iters: int = 0
+    lr_decay_iters: Optional[int] = None
+    grad_dtype: str = "fp32"           # fp32 | param (accumulate in the parameter dtype)
+    split_master: bool = True          # bf16 + int16 remainder instead of an fp32 copy
+
+
+def lr_at(cfg: OptimizerConfig, it: int) -> float:
+    """Learning rate of optimizer step ``it`` (0-based): linear warm-up then the
+    chosen decay (relax/backends/megatron/model.py:220-265)."""
+    if cfg.lr_warmup_iters > 0 and it < cfg.lr_warmup_iters:
+        return cfg.lr * (it + 1) / cfg.lr_warmup_iters
+    if cfg.lr_decay_style == "constant" or not cfg.lr_decay_iters:
+        return cfg.lr
+    t = min(1.0, (it - cfg.lr_warmup_iters) / max(1, cfg.lr_decay_iters - cfg.lr_warmup_iters))
+    if cfg.lr_decay_style == "linear":
+        c = 1.0 - t
+    elif cfg.lr_decay_style == "cosine":
+        c = 0.5 * (1.0 + math.cos(math.pi * t))
+    else:
+        raise ValueError(cfg.lr_decay_style)
+    return cfg.min_lr + (cfg.lr - cfg.min_lr) * c
+
+
+def _split_fp32(x32: torch.Tensor, out_dtype):
+    """fp32 -> (low-precision value rounded to nearest, int16 remainder) with
+    exact reconstruction for bf16."""
+    hi = x32.to(out_dtype)
+    hi_bits = hi.view(torch.int16).to(torch.int32) << 16
+    rem = (x32.view(torch.int32) - hi_bits).to(torch.int16)
+    return hi, rem
+
+
+def _join_fp32(hi: torch.Tensor, rem: torch.Tensor):
+    bits = (hi.view(torch.int16).to(torch.int32) << 16) + rem.to(torch.int32)
+    return bits.view(torch.float32)
+
+
+class DistributedOptimizer:
+    ALIGN = 256  # elements; keeps every shard 512-byte aligned
+
+    def __init__(self, model: torch.nn.Module, ps: ParallelState, cfg: OptimizerConfig):
+        self.model, self.ps, self.cfg = model, ps, cfg
+        params = [p for p in model.parameters() if p.requires_grad]
+        self.frozen = [p for p in model.parameters() if not p.requires_grad]
+        # replicated-over-TP parameters first: one small all-reduce covers their gradients
+        def is_rep(p):
+            return getattr(p, "tp_replicated", False)
+        self.params = [p for p in params if is_rep(p)] + [p for p in params if not is_rep(p)]
+        self.pdtype = self.params[0].dtype
+        dev = self.params[0].device
+        dp = ps.dp_cp.size
+        offs, n = [], 0
+        for p in self.params:
+            if p.dtype != self.pdtype:
+                raise ValueError("all trainable parameters must share one dtype (router weights are kept in "
+                                 "fp32 by a separate small optimizer group)")
+            offs.append(n)
+            n += (p.numel() + 15) // 16 * 16
+        self.rep_elems = 0
+        for p, o in zip(self.params, offs):
+            if is_rep(p):
+                self.rep_elems = o + p.numel()
+        chunk = self.ALIGN * dp
+        self.total = (n + chunk - 1) // chunk * chunk
+        self.shard = self.total // dp
+        self.offsets = offs
+        self.param_buf = torch.zeros(self.total, dtype=self.pdtype, device=dev)
+        gdt = torch.float32 if cfg.grad_dtype == "fp32" else self.pdtype
+        self.grad_buf = torch.zeros(self.total, dtype=gdt, device=dev)
+        for p, o in zip(self.params, offs):
+            v = self.param_buf[o:o + p.numel()].view_as(p)
+            v.copy_(p.data)
+            p.data = v
+            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+            if gdt == self.pdtype:
+                p.grad = p.main_grad
+            else:
+                p.register_post_accumulate_grad_hook(self._make_hook(p))
+        r = ps.dp_cp.rank
+        self.lo, self.hi = r * self.shard, (r + 1) * self.shard
+        my = self.param_buf[self.lo:self.hi]
+        self.split_master = cfg.split_master and self.pdtype == torch.bfloat16
+        if self.split_master:
+            self.master_rem = torch.zeros(self.shard, dtype=torch.int16, device=dev)
+            self.master = None
+        else:
+            self.master = my.float().clone()
+        self.exp_avg = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(self.shard, dtype=torch.float32, device=dev)
+        self.step_count = 0
+        self.grad_shard = None
+        self.last_grad_norm = 0.0
+
+    @staticmethod
+    def _make_hook(p):
+        def hook(param):
+            if param.grad is not None:
+                param.main_grad.add_(param.grad)
+                param.grad = None
+        return hook
+
+    # ------------------------------------------------------------------ step pieces
+    def zero_grad(self):
+        self.grad_buf.zero_()
+        if self.grad_buf.dtype == self.pdtype:
+            for p in self.params:
+                p.grad = p.main_grad
+
+    def _reduce_grads(self):
+        ps = self.ps
+        if ps.tp.size > 1 and self.rep_elems > 0:
+            dist.all_reduce(self.grad_buf[: self.rep_elems], group=ps.tp.group)
+        g = ps.dp_cp
+        if g.size > 1:
+            out = torch.empty(self.shard, dtype=self.grad_buf.dtype, device=self.grad_buf.device)
+            dist.reduce_scatter_tensor(out, self.grad_buf, op=dist.ReduceOp.SUM, group=g.group)
+            out.div_(g.size)
+            return out
+        return self.grad_buf[self.lo:self.hi]
+
+    def _global_grad_norm(self, gshard: torch.Tensor) -> torch.Tensor:
+        ps = self.ps
+        # replicated parameters appear on every TP rank: count them once
+        lo, hi = self.lo, self.hi
+        sq = gshard.float().pow(2)
+        tot = sq.sum()
+        if ps.tp.size > 1 and ps.tp.rank != 0 and self.rep_elems > lo:
+            tot = tot - sq[: max(0, min(hi, self.rep_elems) - lo)].sum()
+        if ps.dp_cp.size > 1:
+            dist.all_reduce(tot, group=ps.dp_cp.group)
+        if ps.tp.size > 1:
+            dist.all_reduce(tot, group=ps.tp.group)
+        if ps.pp.size > 1:
+            dist.all_reduce(tot, group=ps.pp.group)
+        return tot.sqrt()
+
+    def step(self, lr: Optional[float] = None, grad_scale: float = 1.0):
+        """Reduce gradients, clip, Adam on my shard, all-gather parameters.
+        Returns ``(grad_norm, skipped)``; a non-finite norm skips the update."""
+        cfg = self.cfg
+        gshard = self._reduce_grads()
+        norm = self._global_grad_norm(gshard) * grad_scale
+        self.last_grad_norm = float(norm)
+        if not math.isfinite(self.last_grad_norm):
+            return self.last_grad_norm, True
+        clip = 1.0
+        if cfg.clip_grad > 0 and self.last_grad_norm > cfg.clip_grad:
+            clip = cfg.clip_grad / (self.last_grad_norm + 1e-6)
+        self.step_count += 1
+        lr = lr if lr is not None else lr_at(cfg, self.step_count - 1)
+        self._adam_shard(gshard, lr, grad_scale * clip)
+        g = self.ps.dp_cp
+        if g.size > 1:
+            dist.all_gather_into_tensor(self.param_buf, self.param_buf[self.lo:self.hi].clone(), group=g.group)
+        return self.last_grad_norm, False
+
+    def _adam_shard(self, gshard, lr, scale):
+        cfg = self.cfg
+        pshard = self.param_buf[self.lo:self.hi]
+        if gshard.is_cuda:
+            from ..ops import cuda as C
+
+            if C.available():
+                C.fused_adam(pshard, self.master_rem if self.split_master else self.master, gshard,
+                             self.exp_avg, self.exp_avg_sq, self.step_count, lr, cfg.adam_beta1, cfg.adam_beta2,
+                             cfg.adam_eps, cfg.weight_decay, scale, self.split_master)
+                return
+        from ..ops.reference import adam_step
+
+        p32 = _join_fp32(pshard, self.master_rem) if self.split_master else self.master
+        p32 = adam_step(p32.clone() if self.split_master else p32, gshard, self.exp_avg, self.exp_avg_sq,
+                        self.step_count, lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps, cfg.weight_decay, scale)
+        if self.split_master:
+            hi, rem = _split_fp32(p32, self.pdtype)
+            pshard.copy_(hi)
+            self.master_rem.copy_(rem)
+        else:
+            pshard.copy_(p32.to(self.pdtype))
+
+    # ------------------------------------------------------------------ state
+    def master_shard_fp32(self) -> torch.Tensor:
+        return _join_fp32(self.param_buf[self.lo:self.hi], self.master_rem) if self.split_master else self.master
+
+    def state_dict(self) -> dict:
+        return {"step": self.step_count, "master": self.master_shard_fp32().cpu(), "exp_avg": self.exp_avg.cpu(),
+                "exp_avg_sq": self.exp_avg_sq.cpu(), "shard": (self.lo, self.hi), "total": self.total}
+
+    def load_state_dict(self, sd: dict):
+        self.step_count = int(sd["step"])
+        m = sd["master"].to(self.exp_avg.device)
+        if self.split_master:
+            hi, rem = _split_fp32(m, self.pdtype)
+            self.param_buf[self.lo:self.hi].copy_(hi)
+            self.master_rem.copy_(rem)
+        else:
+            self.master.copy_(m)
+            self.param_buf[self.lo:self.hi].copy_(m.to(self.pdtype))
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        g = self.ps.dp_cp
+        if g.size > 1:
+            dist.all_gather_into_tensor(self.param_buf, self.param_buf[self.lo:self.hi].clone(), group=g.group)
+
+    def reload_master_from_params(self):
+        """After parameters were overwritten in place (checkpoint load, weight
+        switch) rebuild the master copy of my shard from them."""
+        if self.split_master:
+            self.master_rem.zero_()
+        else:
+            self.master.copy_(self.param_buf[self.lo:self.hi].float())
+
+    # ------------------------------------------------------------------ offload (colocate sleep / wake_up)
+    def offload_state(self):
+        """Move optimizer state to pinned host memory and release the gradient
+        buffer (relax/backends/megatron/weight_update/train_offload.py:135-346)."""
+        self._host = {}
+        for name in ("exp_avg", "exp_avg_sq", "master", "master_rem"):
+            t = getattr(self, name, None)
+            if t is None or not t.is_cuda:
+                continue
+            h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+            h.copy_(t, non_blocking=True)
+            self._host[name] = h
+        if self.grad_buf.is_cuda:
+            torch.cuda.current_stream().synchronize()
+            for name in self._host:
+                setattr(self, name, None)
+            self._grad_meta = (self.grad_buf.shape, self.grad_buf.dtype, self.grad_buf.device)
+            self.grad_buf = None
+            for p in self.params:
+                p.main_grad = None
+                p.grad = None
+
+    def onload_state(self):
+        host = getattr(self, "_host", None)
+        if not host:
+            return
+        shape, dtype, dev = self._grad_meta
+        for name, h in host.items():
+            setattr(self, name, h.to(dev, non_blocking=True))
+        self.grad_buf = torch.zeros(shape, dtype=dtype, device=dev)
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+        self._host = None

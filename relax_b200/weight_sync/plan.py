@@ -1,0 +1,168 @@
+"""Copy plan for trainer -> rollout weight synchronisation.
+
+The trainer holds Megatron-layout shards (per-group interleaved QKV, ``[gate;
+up]`` per TP shard, TP/PP/EP sharding of the trainer); the rollout engine holds
+serving-layout shards (``[q | k | v]``, its own TP/EP).  Instead of gathering
+full tensors, converting names/shapes and broadcasting them (the reference's
+path: relax/backends/megatron/weight_update/common.py:20-126,
+weight_conversion/qwen2.py, update_weight_from_distributed.py:351-376), this
+module computes, once, a table of 2-D block copies
+
+    (src rank, src tensor, row0, col0)  ->  (dst rank, dst tensor, row0, col0), rows x cols
+
+that moves every element exactly once from a trainer shard straight into the
+rollout parameter buffer.  The table is consumed by the CUDA weight-sync kernel
+(peer stores over NVLink, optional cast/quantise) and by the CPU executor in
+:mod:`relax_b200.weight_sync.sync`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterable
+
+from ..models.config import ModelConfig
+
+
+@dataclass(frozen=True)
+class BlockCopy:
+    src_rank: int      # trainer-local rank index (tp + tp_size * (ep...)) see TrainerLayout.rank_of
+    src_name: str      # trainer parameter name
+    src_row: int
+    src_col: int
+    dst_rank: int      # rollout-engine-local rank (tp rank or ep rank)
+    dst_name: str      # rollout parameter name
+    dst_row: int
+    dst_col: int
+    rows: int
+    cols: int
+    src_batch: int = 0   # leading index for stacked expert tensors
+    dst_batch: int = 0
+
+
+@dataclass(frozen=True)
+class TrainerLayout:
+    tp: int = 1
+    pp: int = 1
+    ep: int = 1
+
+    def layer_owner_pp(self, cfg: ModelConfig, layer: int) -> int:
+        return layer // (cfg.num_layers // self.pp)
+
+
+def _intersect(a0, a1, b0, b1):
+    lo, hi = max(a0, b0), min(a1, b1)
+    return (lo, hi) if lo < hi else None
+
+
+def _row_sharded(canon_rows: int, src_parts: int, dst_parts: int):
+    """Yield (src_part, src_off, dst_part, dst_off, n) for a dimension split evenly both ways."""
+    s, d = canon_rows // src_parts, canon_rows // dst_parts
+    for sp in range(src_parts):
+        for dp in range(dst_parts):
+            it = _intersect(sp * s, (sp + 1) * s, dp * d, (dp + 1) * d)
+            if it:
+                yield sp, it[0] - sp * s, dp, it[0] - dp * d, it[1] - it[0]
+
+
+def trainer_param_name(layer_local: int, kind: str) -> str:
+    base = f"decoder.layers.{layer_local}."
+    return {
+        "qkv": base + "self_attention.linear_qkv.weight",
+        "qkv_bias": base + "self_attention.linear_qkv.bias",
+        "input_norm": base + "self_attention.linear_qkv.layer_norm_weight",
+        "q_norm": base + "self_attention.q_layernorm.weight",
+        "k_norm": base + "self_attention.k_layernorm.weight",
+        "o": base + "self_attention.linear_proj.weight",
+        "post_norm": base + "mlp.linear_fc1.layer_norm_weight",
+        "post_norm_moe": base + "pre_mlp_layernorm.weight",
+        "fc1": base + "mlp.linear_fc1.weight",
+        "fc2": base + "mlp.linear_fc2.weight",
+        "router": base + "mlp.router.weight",
+        "experts_fc1": base + "mlp.experts.linear_fc1.weight",
+        "experts_fc2": base + "mlp.experts.linear_fc2.weight",
+    }[kind]
+
+
+def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 1) -> list[BlockCopy]:
+    """All block copies for one rollout engine, sourced from ONE trainer
+    data-parallel replica.  ``src_rank`` is the trainer TP rank for dense
+    tensors and the EP rank for expert tensors (``src_batch`` = local expert);
+    the pipeline stage that owns a layer is implied by the layer index."""
+    H, hd = cfg.hidden_size, cfg.head_dim
+    ng, qpg = cfg.num_query_groups, cfg.num_attention_heads // cfg.num_query_groups
+    plan: list[BlockCopy] = []
+    per_stage = cfg.num_layers // src.pp
+    add = plan.append
+
+    def rep(src_name, dst_name, n):
+        for r in range(dst_tp):
+            add(BlockCopy(r % src.tp, src_name, 0, 0, r, dst_name, 0, 0, 1, n))
+
+    # vocabulary-sharded tensors
+    v_src = (cfg.vocab_size + src.tp - 1) // src.tp * src.tp
+    v_dst = (cfg.vocab_size + dst_tp - 1) // dst_tp * dst_tp
+    names = [("embedding.word_embeddings.weight", "embed")]
+    if not cfg.tie_word_embeddings:
+        names.append(("output_layer.weight", "lm_head"))
+    for sname, dname in names:
+        s, d = v_src // src.tp, v_dst // dst_tp
+        for sp in range(src.tp):
+            for dp in range(dst_tp):
+                it = _intersect(sp * s, min((sp + 1) * s, cfg.vocab_size), dp * d, min((dp + 1) * d, cfg.vocab_size))
+                if it:
+                    add(BlockCopy(sp, sname, it[0] - sp * s, 0, dp, dname, it[0] - dp * d, 0, it[1] - it[0], H))
+    rep("decoder.final_layernorm.weight", "final_norm", H)
+
+    ng_s, ng_d = ng // src.tp, ng // dst_tp
+    grp_rows = (qpg + 2) * hd
+    for layer in range(cfg.num_layers):
+        ll = layer % per_stage
+        p = f"layers.{layer}."
+        rep(trainer_param_name(ll, "input_norm"), p + "input_norm", H)
+        if cfg.qk_layernorm:
+            rep(trainer_param_name(ll, "q_norm"), p + "q_norm", hd)
+            rep(trainer_param_name(ll, "k_norm"), p + "k_norm", hd)
+        # QKV: per global group g, three row blocks
+        nq_d, nkv_d = cfg.num_attention_heads // dst_tp, ng_d
+        for g in range(ng):
+            st, sg = g // ng_s, g % ng_s
+            dt, dg = g // ng_d, g % ng_d
+            sbase = sg * grp_rows
+            blocks = (
+                (sbase, dg * qpg * hd, qpg * hd),                      # q heads of the group
+                (sbase + qpg * hd, nq_d * hd + dg * hd, hd),           # k
+                (sbase + (qpg + 1) * hd, (nq_d + nkv_d) * hd + dg * hd, hd),  # v
+            )
+            for srow, drow, n in blocks:
+                add(BlockCopy(st, trainer_param_name(ll, "qkv"), srow, 0, dt, p + "qkv", drow, 0, n, H))
+                if cfg.qkv_bias:
+                    add(BlockCopy(st, trainer_param_name(ll, "qkv_bias"), 0, srow, dt, p + "qkv_bias", 0, drow, 1, n))
+        # o_proj: column sharded
+        for sp, so, dp, do, n in _row_sharded(cfg.q_size, src.tp, dst_tp):
+            add(BlockCopy(sp, trainer_param_name(ll, "o"), 0, so, dp, p + "o", 0, do, H, n))
+        is_moe = cfg.is_moe and layer % cfg.moe_layer_freq == 0
+        if is_moe:
+            rep(trainer_param_name(ll, "post_norm_moe"), p + "post_norm", H)
+            for r in range(dst_tp):
+                add(BlockCopy(r % src.tp, trainer_param_name(ll, "router"), 0, 0, r, p + "router", 0, 0, cfg.num_experts, H))
+            F = cfg.moe_ffn_hidden_size
+            el_s, el_d = cfg.num_experts // src.ep, cfg.num_experts // dst_ep
+            for e in range(cfg.num_experts):
+                add(BlockCopy(e // el_s, trainer_param_name(ll, "experts_fc1"), 0, 0, e // el_d, p + "experts_gate_up",
+                              0, 0, 2 * F, H, src_batch=e % el_s, dst_batch=e % el_d))
+                add(BlockCopy(e // el_s, trainer_param_name(ll, "experts_fc2"), 0, 0, e // el_d, p + "experts_down",
+                              0, 0, H, F, src_batch=e % el_s, dst_batch=e % el_d))
+        else:
+            rep(trainer_param_name(ll, "post_norm"), p + "post_norm", H)
+            F = cfg.ffn_hidden_size
+            Fs, Fd = F // src.tp, F // dst_tp
+            for sp, so, dp, do, n in _row_sharded(F, src.tp, dst_tp):
+                add(BlockCopy(sp, trainer_param_name(ll, "fc1"), so, 0, dp, p + "gate_up", do, 0, n, H))          # gate
+                add(BlockCopy(sp, trainer_param_name(ll, "fc1"), Fs + so, 0, dp, p + "gate_up", Fd + do, 0, n, H))  # up
+            for sp, so, dp, do, n in _row_sharded(F, src.tp, dst_tp):
+                add(BlockCopy(sp, trainer_param_name(ll, "fc2"), 0, so, dp, p + "down", 0, do, H, n))
+    return plan
+
+
+def plan_bytes(plan: Iterable[BlockCopy], itemsize: int = 2) -> int:
+    return sum(b.rows * b.cols for b in plan) * itemsize
