@@ -276,8 +276,27 @@ class GPTModel(nn.Module):
         v_real = min(self.v_local, max(0, self.cfg.vocab_size - self.vocab_start))
         if v_real < self.v_local:
             w = w[:v_real]
-        hidden = TP.copy_to_tp(hidden, self.ps.tp)
+        # sequence parallel: ``hidden`` came out of an all-gather whose backward is a
+        # reduce-scatter, which already sums the partial (per vocab shard) gradients
+        if not self.sequence_parallel:
+            hidden = TP.copy_to_tp(hidden, self.ps.tp)
         return ops.fused_lm_head_logprob(hidden, w, targets, self.ps.tp.group, self.vocab_start, with_entropy, temperature)
 
     def values(self, hidden):
+        """Scalar value per row (critic).  The head is replicated over TP, so
+        under sequence parallelism each rank's (identical) gradient is scaled by
+        1/tp before the reduce-scatter sums them."""
+        if self.sequence_parallel:
+            hidden = _ScaleGrad.apply(hidden, 1.0 / self.ps.tp.size)
         return ops.linear(hidden, self.value_head.weight)[:, 0].float()
+
+
+class _ScaleGrad(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, s):
+        ctx.s = s
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g * ctx.s, None

@@ -106,9 +106,9 @@ class RolloutWeights:
     def _logits(self, h, tp: GroupInfo):
         z = ops.linear(h, self.p["lm_head"]).float()
         if tp.size > 1:
-            out = torch.empty(tp.size, z.shape[0], z.shape[1], dtype=z.dtype, device=z.device)
+            out = torch.empty(tp.size * z.shape[0], z.shape[1], dtype=z.dtype, device=z.device)
             dist.all_gather_into_tensor(out, z.contiguous(), group=tp.group)
-            z = out.permute(1, 0, 2).reshape(z.shape[0], -1)
+            z = out.view(tp.size, z.shape[0], z.shape[1]).permute(1, 0, 2).reshape(z.shape[0], -1)
         return z
 
     def _mlp(self, i, x, tp):

@@ -1,0 +1,97 @@
+import torch
+
+from relax_b200.models.config import get_config
+from relax_b200.rollout.engine import BlockManager, RolloutEngine, SamplingParams
+from relax_b200.train.actor import TrainActor, TrainConfig
+from relax_b200.weight_sync.plan import TrainerLayout
+from relax_b200.weight_sync.sync import WeightSync
+
+
+def _pair(kv_blocks=256, **kw):
+    cfg = get_config("tiny")
+    actor = TrainActor(cfg, TrainConfig(), seed=0, with_optimizer=False)
+    eng = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=kv_blocks, block_size=8, **kw)
+    WeightSync(cfg, TrainerLayout(), 1, [0], [0]).update_weights(dict(actor.named_local_params()), eng.weights, eng, 1)
+    return cfg, actor, eng
+
+
+def test_block_manager_refcounts():
+    bm = BlockManager(4, 8)
+    a, b = bm.alloc(), bm.alloc()
+    bm.share(a)
+    bm.release([a])
+    assert bm.num_free == 2
+    bm.release([a, b])
+    assert bm.num_free == 4 and bm.blocks_for(17) == 3
+
+
+def test_rollout_logprobs_match_trainer_forward():
+    cfg, actor, eng = _pair()
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (5, 11, 8)]
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=9))
+    assert eng.weight_version == 1
+    batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [len(r.output) for r in res]}
+    lp = actor.compute_log_prob(batch)["log_probs"]
+    for r, l in zip(res, lp):
+        assert len(r.output) == 9 and r.finish_reason == "length"
+        assert torch.allclose(torch.tensor(r.logprobs), l, atol=1e-4)
+    assert eng.bm.num_free == eng.bm.num_blocks       # every block returned
+
+
+def test_group_prefix_sharing_equals_independent_prefill():
+    cfg, actor, eng = _pair()
+    prompt = list(range(3, 22))                        # 19 tokens: 2 full blocks + partial tail
+    sp = SamplingParams(max_new_tokens=6)
+    shared = eng.generate([prompt] * 4, sp, group_keys=[0] * 4)
+    assert eng.stats["prefill_tokens"] == len(prompt)  # one prefill for the whole group
+    # log-probs of every member agree with a fresh trainer forward (KV sharing is exact)
+    batch = {"tokens": [r.prompt + r.output for r in shared], "response_lengths": [6] * 4}
+    for r, l in zip(shared, actor.compute_log_prob(batch)["log_probs"]):
+        assert torch.allclose(torch.tensor(r.logprobs), l, atol=1e-4)
+    assert len({tuple(r.output) for r in shared}) > 1  # members sample independently
+    assert eng.bm.num_free == eng.bm.num_blocks
+
+
+def test_continuous_batching_under_kv_pressure_and_eos():
+    cfg, actor, eng = _pair(kv_blocks=12, max_running=8)   # 96 KV slots: at most ~3 requests of 8+20 tokens
+    eng.eos = 7
+    prompts = [[i + 1] * 8 for i in range(6)]
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=20))
+    assert len(res) == 6 and all(r.status == "finished" for r in res)
+    for r in res:
+        assert r.finish_reason in ("stop", "length")
+        if r.finish_reason == "stop":
+            assert r.output[-1] == 7
+    assert eng.bm.num_free == 12
+
+
+def test_abort_returns_partial_and_resume_continues():
+    cfg, actor, eng = _pair()
+    rid = eng.add_request([1, 2, 3, 4], SamplingParams(max_new_tokens=10))
+    for _ in range(4):
+        eng.step()
+    part = eng.abort_all()
+    assert len(part) == 1 and part[0].status == "aborted" and 0 < len(part[0].output) < 10
+    assert eng.bm.num_free == eng.bm.num_blocks
+    got = len(part[0].output)
+    eng.add_request(part[0].prompt, SamplingParams(max_new_tokens=10), resume_output=part[0].output,
+                    resume_logprobs=part[0].logprobs)
+    done = []
+    while eng.has_work:
+        done += eng.step()
+    assert len(done[0].output) == 10 and done[0].output[:got] == part[0].output
+
+
+def test_pause_and_memory_release():
+    cfg, actor, eng = _pair()
+    eng.add_request([1, 2, 3], SamplingParams(max_new_tokens=2))
+    eng.pause_generation()
+    assert eng.step() == [] and eng.has_work
+    eng.continue_generation()
+    while eng.has_work:
+        eng.step()
+    eng.release_memory_occupation(("kv_cache", "weights"))
+    assert eng.kv is None and eng.weights.flat is None
+    eng.resume_memory_occupation(("kv_cache", "weights"))
+    assert eng.kv is not None and eng.weights.flat is not None
