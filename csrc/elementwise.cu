@@ -1,0 +1,602 @@
+// Memory-bound fused kernels: RMSNorm (+residual) fwd/bwd, RoPE fwd/bwd, SwiGLU
+// fwd/bwd, fused Adam with split fp32 master, int4 fake-quant, block fp8 cast /
+// dequant, table-driven block copy (weight sync), KV-cache scatter.
+// All use 128-bit accesses and grid-stride loops sized to the SM count.
+#include "common.cuh"
+#include "host_utils.h"
+#include <cuda_fp8.h>
+
+namespace rb {
+
+template <typename T> struct Cvt;
+template <> struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to(__nv_bfloat16 v) { return __bfloat162float(v); }
+  static __device__ __forceinline__ __nv_bfloat16 from(float v) { return __float2bfloat16(v); }
+};
+template <> struct Cvt<__half> {
+  static __device__ __forceinline__ float to(__half v) { return __half2float(v); }
+  static __device__ __forceinline__ __half from(float v) { return __float2half(v); }
+};
+template <> struct Cvt<float> {
+  static __device__ __forceinline__ float to(float v) { return v; }
+  static __device__ __forceinline__ float from(float v) { return v; }
+};
+
+template <typename T> struct Vec { static constexpr int N = 16 / sizeof(T); T v[N]; };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float* out) {
+  constexpr int N = 16 / sizeof(T);
+  Vec<T> v = *reinterpret_cast<const Vec<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < N; ++i) out[i] = Cvt<T>::to(v.v[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float* in) {
+  constexpr int N = 16 / sizeof(T);
+  Vec<T> v;
+#pragma unroll
+  for (int i = 0; i < N; ++i) v.v[i] = Cvt<T>::from(in[i]);
+  *reinterpret_cast<Vec<T>*>(p) = v;
+}
+
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v, float* smem, int row_in_block, int t) {
+  if constexpr (TPR == 32) {
+    return warp_sum(v);
+  } else {
+    v = warp_sum(v);
+    constexpr int W = TPR / 32;
+    if ((t & 31) == 0) smem[row_in_block * W + (t >> 5)] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < W; ++i) s += smem[row_in_block * W + i];
+    __syncthreads();
+    return s;
+  }
+}
+
+// ----------------------------------------------------------------------------- RMSNorm forward (+ residual add)
+// y = rmsnorm(x [+ res]) * w ; optionally writes the sum r = x + res (new residual stream).
+template <typename T, int TPR, bool ADD>
+__global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                                   T* __restrict__ y, T* __restrict__ r_out, int rows, int cols, float eps) {
+  constexpr int N = 16 / sizeof(T);
+  constexpr int RPB = 256 / TPR;
+  __shared__ float red[RPB * (TPR / 32) + 1];
+  const int t = threadIdx.x % TPR;
+  const int rib = threadIdx.x / TPR;
+  for (int row0 = blockIdx.x * RPB; row0 < rows; row0 += gridDim.x * RPB) {
+    const int row = row0 + rib;
+    const bool live = row < rows;
+    const size_t base = static_cast<size_t>(live ? row : 0) * cols;
+    float ss = 0.f;
+    if (live) {
+      for (int c = t * N; c < cols; c += TPR * N) {
+        float a[N];
+        load_vec(x + base + c, a);
+        if constexpr (ADD) {
+          float b[N];
+          load_vec(res + base + c, b);
+#pragma unroll
+          for (int i = 0; i < N; ++i) a[i] = Cvt<T>::to(Cvt<T>::from(a[i] + b[i]));
+          store_vec(r_out + base + c, a);
+        }
+#pragma unroll
+        for (int i = 0; i < N; ++i) ss += a[i] * a[i];
+      }
+    }
+    ss = group_sum<TPR>(ss, red, rib, t);
+    const float rstd = rsqrtf(ss / cols + eps);
+    if (live) {
+      const T* src = ADD ? r_out : x;
+      for (int c = t * N; c < cols; c += TPR * N) {
+        float a[N], g[N];
+        load_vec(src + base + c, a);
+        load_vec(w + c, g);
+#pragma unroll
+        for (int i = 0; i < N; ++i) a[i] = a[i] * rstd * g[i];
+        store_vec(y + base + c, a);
+      }
+    }
+  }
+}
+
+// Backward: dx = rstd * (g - x * rstd^2 * mean(g*x)) with g = dy*w ; dw partials per block.
+template <typename T, int TPR>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
+                                   T* __restrict__ dx, float* __restrict__ dw_partial, int rows, int cols, float eps) {
+  constexpr int N = 16 / sizeof(T);
+  constexpr int RPB = 256 / TPR;
+  __shared__ float red[RPB * (TPR / 32) + 1];
+  extern __shared__ float dw_acc[];  // [cols]
+  const int t = threadIdx.x % TPR;
+  const int rib = threadIdx.x / TPR;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_acc[c] = 0.f;
+  __syncthreads();
+  for (int row0 = blockIdx.x * RPB; row0 < rows; row0 += gridDim.x * RPB) {
+    const int row = row0 + rib;
+    const bool live = row < rows;
+    const size_t base = static_cast<size_t>(live ? row : 0) * cols;
+    float ss = 0.f, dot = 0.f;
+    if (live) {
+      for (int c = t * N; c < cols; c += TPR * N) {
+        float a[N], g[N], d[N];
+        load_vec(x + base + c, a);
+        load_vec(w + c, g);
+        load_vec(dy + base + c, d);
+#pragma unroll
+        for (int i = 0; i < N; ++i) { ss += a[i] * a[i]; dot += a[i] * g[i] * d[i]; }
+      }
+    }
+    ss = group_sum<TPR>(ss, red, rib, t);
+    dot = group_sum<TPR>(dot, red, rib, t);
+    const float rstd = rsqrtf(ss / cols + eps);
+    const float coef = rstd * rstd * dot / cols;
+    if (live) {
+      for (int c = t * N; c < cols; c += TPR * N) {
+        float a[N], g[N], d[N], o[N];
+        load_vec(x + base + c, a);
+        load_vec(w + c, g);
+        load_vec(dy + base + c, d);
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          o[i] = rstd * (g[i] * d[i] - a[i] * coef);
+          atomicAdd(&dw_acc[c + i], d[i] * a[i] * rstd);
+        }
+        store_vec(dx + base + c, o);
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * cols + c] = dw_acc[c];
+}
+
+template <typename T>
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out, int nparts, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float s = 0.f;
+  for (int p = 0; p < nparts; ++p) s += partial[static_cast<size_t>(p) * cols + c];
+  out[c] = Cvt<T>::from(s);
+}
+
+// ----------------------------------------------------------------------------- RoPE (rotate-half), x[T][H][D], cos/sin[T][D/2] fp32
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const float* __restrict__ cos_t,
+                            const float* __restrict__ sin_t, long long total_pairs, int H, int D, float sin_sign) {
+  constexpr int N = 16 / sizeof(T);
+  const int half = D / 2;
+  const long long nvec = total_pairs / N;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const long long pair = v * N;
+    const int j = static_cast<int>(pair % half);
+    const long long th = pair / half;  // token*H + head
+    const long long tok = th / H;
+    const size_t base = static_cast<size_t>(th) * D;
+    float a[N], b[N], oa[N], ob[N];
+    load_vec(x + base + j, a);
+    load_vec(x + base + half + j, b);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float c = cos_t[tok * half + j + i], s = sin_sign * sin_t[tok * half + j + i];
+      oa[i] = a[i] * c - b[i] * s;
+      ob[i] = b[i] * c + a[i] * s;
+    }
+    store_vec(y + base + j, oa);
+    store_vec(y + base + half + j, ob);
+  }
+}
+
+// ----------------------------------------------------------------------------- SwiGLU, in[T][2F] = [gate | up]
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int F) {
+  constexpr int N = 16 / sizeof(T);
+  const long long nvec = rows * F / N;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const long long e = v * N;
+    const long long r = e / F;
+    const int c = static_cast<int>(e % F);
+    float g[N], u[N], o[N];
+    load_vec(in + r * 2 * F + c, g);
+    load_vec(in + r * 2 * F + F + c, u);
+#pragma unroll
+    for (int i = 0; i < N; ++i) o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+    store_vec(out + e, o);
+  }
+}
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ in, const T* __restrict__ dout, T* __restrict__ din,
+                                  long long rows, int F) {
+  constexpr int N = 16 / sizeof(T);
+  const long long nvec = rows * F / N;
+  for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const long long e = v * N;
+    const long long r = e / F;
+    const int c = static_cast<int>(e % F);
+    float g[N], u[N], d[N], dg[N], du[N];
+    load_vec(in + r * 2 * F + c, g);
+    load_vec(in + r * 2 * F + F + c, u);
+    load_vec(dout + e, d);
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float s = 1.f / (1.f + __expf(-g[i]));
+      const float silu = g[i] * s;
+      du[i] = d[i] * silu;
+      dg[i] = d[i] * u[i] * (s + silu * (1.f - s));
+    }
+    store_vec(din + r * 2 * F + c, dg);
+    store_vec(din + r * 2 * F + F + c, du);
+  }
+}
+
+// ----------------------------------------------------------------------------- fused AdamW on a flat shard
+// SPLIT: the fp32 master is (bf16 param << 16) + int16 remainder; else `master` is fp32.
+template <typename G, bool SPLIT>
+__global__ void adam_kernel(__nv_bfloat16* __restrict__ p, void* __restrict__ master, const G* __restrict__ g,
+                            float* __restrict__ m, float* __restrict__ v, long long n, float lr, float b1, float b2,
+                            float eps, float wd, float gscale, float bc1, float bc2) {
+  for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < n; i += (long long)gridDim.x * blockDim.x * 4) {
+    float gv[4], mv[4], vv[4], w[4];
+    if constexpr (sizeof(G) == 4) {
+      float4 t = *reinterpret_cast<const float4*>(g + i);
+      gv[0] = t.x; gv[1] = t.y; gv[2] = t.z; gv[3] = t.w;
+    } else {
+      uint2 t = *reinterpret_cast<const uint2*>(g + i);
+      const __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&t.x), b = *reinterpret_cast<__nv_bfloat162*>(&t.y);
+      gv[0] = __low2float(a); gv[1] = __high2float(a); gv[2] = __low2float(b); gv[3] = __high2float(b);
+    }
+    float4 m4 = *reinterpret_cast<float4*>(m + i), v4 = *reinterpret_cast<float4*>(v + i);
+    mv[0] = m4.x; mv[1] = m4.y; mv[2] = m4.z; mv[3] = m4.w;
+    vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+    uint2 praw = *reinterpret_cast<uint2*>(p + i);
+    const uint16_t* ph = reinterpret_cast<const uint16_t*>(&praw);
+    if constexpr (SPLIT) {
+      uint2 rraw = *reinterpret_cast<uint2*>(reinterpret_cast<int16_t*>(master) + i);
+      const int16_t* rh = reinterpret_cast<const int16_t*>(&rraw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) w[k] = __int_as_float((static_cast<int>(static_cast<int16_t>(ph[k])) << 16) + static_cast<int>(rh[k]));
+    } else {
+      float4 t = *reinterpret_cast<float4*>(reinterpret_cast<float*>(master) + i);
+      w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+    }
+    uint16_t hi[4];
+    int16_t rem[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gg = gv[k] * gscale;
+      mv[k] = b1 * mv[k] + (1.f - b1) * gg;
+      vv[k] = b2 * vv[k] + (1.f - b2) * gg * gg;
+      const float denom = sqrtf(vv[k] / bc2) + eps;
+      w[k] = w[k] * (1.f - lr * wd) - lr * (mv[k] / bc1) / denom;
+      const __nv_bfloat16 h = __float2bfloat16_rn(w[k]);
+      hi[k] = *reinterpret_cast<const uint16_t*>(&h);
+      rem[k] = static_cast<int16_t>(__float_as_int(w[k]) - (static_cast<int>(static_cast<int16_t>(hi[k])) << 16));
+    }
+    *reinterpret_cast<float4*>(m + i) = make_float4(mv[0], mv[1], mv[2], mv[3]);
+    *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    *reinterpret_cast<uint2*>(p + i) = *reinterpret_cast<uint2*>(hi);
+    if constexpr (SPLIT) {
+      *reinterpret_cast<uint2*>(reinterpret_cast<int16_t*>(master) + i) = *reinterpret_cast<uint2*>(rem);
+    } else {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(master) + i) = make_float4(w[0], w[1], w[2], w[3]);
+    }
+  }
+}
+
+// sum of squares of a flat buffer -> one float (atomic)
+template <typename G>
+__global__ void sumsq_kernel(const G* __restrict__ g, long long n, float* __restrict__ out) {
+  float s = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float x = Cvt<G>::to(g[i]);
+    s += x * x;
+  }
+  s = warp_sum(s);
+  __shared__ float sm[8];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 8) {
+    s = sm[threadIdx.x];
+    s += __shfl_xor_sync(0xff, s, 4); s += __shfl_xor_sync(0xff, s, 2); s += __shfl_xor_sync(0xff, s, 1);
+    if (threadIdx.x == 0) atomicAdd(out, s);
+  }
+}
+
+// ----------------------------------------------------------------------------- table-driven 2-D block copy
+struct CopyDesc {
+  const void* src;
+  void* dst;
+  int rows, cols;       // elements
+  int src_ld, dst_ld;   // elements
+};
+// One CTA walks whole descriptors in chunks; descriptors with 16-byte aligned rows use 128-bit
+// accesses.  `dst` may be a peer GPU's memory (NVLink store) - only stores cross the link.
+template <typename T>
+__global__ void copy_table_kernel(const CopyDesc* __restrict__ table, int n_desc, const int* __restrict__ chunk_start,
+                                  int total_chunks, int chunk_rows) {
+  constexpr int N = 16 / sizeof(T);
+  for (int ch = blockIdx.x; ch < total_chunks; ch += gridDim.x) {
+    // binary search: descriptor that owns chunk ch
+    int lo = 0, hi = n_desc - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (chunk_start[mid] <= ch) lo = mid; else hi = mid - 1;
+    }
+    const CopyDesc d = table[lo];
+    const int r0 = (ch - chunk_start[lo]) * chunk_rows;
+    const int r1 = min(d.rows, r0 + chunk_rows);
+    const T* s = reinterpret_cast<const T*>(d.src);
+    T* o = reinterpret_cast<T*>(d.dst);
+    const bool vec = (d.cols % N == 0) && (d.src_ld % N == 0) && (d.dst_ld % N == 0) &&
+                     (reinterpret_cast<uintptr_t>(s) % 16 == 0) && (reinterpret_cast<uintptr_t>(o) % 16 == 0);
+    if (vec) {
+      const int vpr = d.cols / N;
+      const long long total = static_cast<long long>(r1 - r0) * vpr;
+      for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+        const int r = r0 + static_cast<int>(i / vpr), c = static_cast<int>(i % vpr) * N;
+        *reinterpret_cast<uint4*>(o + static_cast<size_t>(r) * d.dst_ld + c) =
+            *reinterpret_cast<const uint4*>(s + static_cast<size_t>(r) * d.src_ld + c);
+      }
+    } else {
+      const long long total = static_cast<long long>(r1 - r0) * d.cols;
+      for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+        const int r = r0 + static_cast<int>(i / d.cols), c = static_cast<int>(i % d.cols);
+        o[static_cast<size_t>(r) * d.dst_ld + c] = s[static_cast<size_t>(r) * d.src_ld + c];
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- KV-cache scatter: cache[slot][h][d] = k[t][h][d]
+template <typename T>
+__global__ void kv_scatter_kernel(const T* __restrict__ k, const T* __restrict__ v, T* __restrict__ kc, T* __restrict__ vc,
+                                  const long long* __restrict__ slots, int tokens, int row_elems, long long k_stride,
+                                  long long v_stride) {
+  constexpr int N = 16 / sizeof(T);
+  const int vpr = row_elems / N;
+  const long long total = static_cast<long long>(tokens) * vpr;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = static_cast<int>(i / vpr), c = static_cast<int>(i % vpr) * N;
+    const long long slot = slots[t];
+    if (slot < 0) continue;
+    *reinterpret_cast<uint4*>(kc + slot * row_elems + c) = *reinterpret_cast<const uint4*>(k + t * k_stride + c);
+    *reinterpret_cast<uint4*>(vc + slot * row_elems + c) = *reinterpret_cast<const uint4*>(v + t * v_stride + c);
+  }
+}
+
+// ----------------------------------------------------------------------------- int4 fake quant (groups of block_m x block_n)
+template <typename T>
+__global__ void int4_fake_quant_kernel(const T* __restrict__ x, T* __restrict__ out, T* __restrict__ scale_out,
+                                       T* __restrict__ zero_out, int M, int N, int bm, int bn, int sym) {
+  // one warp per group
+  const int gn = (N + bn - 1) / bn, gm = (M + bm - 1) / bm;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long g = blockIdx.x * (long long)warps_per_block + (threadIdx.x >> 5); g < (long long)gm * gn;
+       g += (long long)gridDim.x * warps_per_block) {
+    const int gi = static_cast<int>(g / gn), gj = static_cast<int>(g % gn);
+    const int r0 = gi * bm, c0 = gj * bn;
+    const int rows = min(bm, M - r0), cols = min(bn, N - c0);
+    const int n = rows * cols;
+    float mx = -INFINITY, mn = INFINITY;
+    for (int i = lane; i < n; i += 32) {
+      const float v = Cvt<T>::to(x[static_cast<size_t>(r0 + i / cols) * N + c0 + i % cols]);
+      mx = fmaxf(mx, v); mn = fminf(mn, v);
+    }
+    mx = warp_max(mx); mn = -warp_max(-mn);
+    float scale, zero = 0.f;
+    if (sym) {
+      scale = fmaxf(fmaxf(fabsf(mx), fabsf(mn)) / 7.f, 1e-5f);
+    } else {
+      scale = fmaxf((mx - mn) / 15.f, 1e-5f);
+      zero = fminf(fmaxf(rintf(-mn / scale), 0.f), 15.f);
+    }
+    for (int i = lane; i < n; i += 32) {
+      const size_t idx = static_cast<size_t>(r0 + i / cols) * N + c0 + i % cols;
+      const float v = Cvt<T>::to(x[idx]);
+      float q, dq;
+      if (sym) { q = fminf(fmaxf(rintf(v / scale), -8.f), 7.f); dq = q * scale; }
+      else { q = fminf(fmaxf(rintf(v / scale) + zero, 0.f), 15.f); dq = (q - zero) * scale; }
+      out[idx] = Cvt<T>::from(dq);
+    }
+    if (lane == 0) { scale_out[g] = Cvt<T>::from(scale); zero_out[g] = Cvt<T>::from(zero); }
+  }
+}
+
+// ----------------------------------------------------------------------------- block-scaled fp8 (e4m3) cast / dequant
+template <typename T>
+__global__ void fp8_block_cast_kernel(const T* __restrict__ w, __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale,
+                                      int M, int N, int block, int ue8m0) {
+  // one CTA per block x block tile
+  const int gn = (N + block - 1) / block;
+  const int r0 = (blockIdx.x / gn) * block, c0 = (blockIdx.x % gn) * block;
+  const int rows = min(block, M - r0), cols = min(block, N - c0);
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < rows * cols; i += blockDim.x)
+    amax = fmaxf(amax, fabsf(Cvt<T>::to(w[static_cast<size_t>(r0 + i / cols) * N + c0 + i % cols])));
+  amax = warp_max(amax);
+  __shared__ float sm[32];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) amax = fmaxf(amax, sm[i]);
+  float s = fmaxf(amax, 1e-12f) / 448.f;
+  if (ue8m0) s = exp2f(ceilf(log2f(s)));
+  for (int i = threadIdx.x; i < rows * cols; i += blockDim.x) {
+    const size_t idx = static_cast<size_t>(r0 + i / cols) * N + c0 + i % cols;
+    const float v = fminf(fmaxf(Cvt<T>::to(w[idx]) / s, -448.f), 448.f);
+    q[idx] = __nv_fp8_e4m3(v);
+  }
+  if (threadIdx.x == 0) scale[blockIdx.x] = s;
+}
+template <typename T>
+__global__ void fp8_block_dequant_kernel(const __nv_fp8_e4m3* __restrict__ q, const float* __restrict__ scale,
+                                         T* __restrict__ out, int M, int N, int block) {
+  const int gn = (N + block - 1) / block;
+  const long long total = static_cast<long long>(M) * N;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = static_cast<int>(i / N), c = static_cast<int>(i % N);
+    out[i] = Cvt<T>::from(static_cast<float>(q[i]) * scale[(r / block) * gn + c / block]);
+  }
+}
+
+static inline int grid_for(long long work_items, int threads) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  return static_cast<int>(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+#define RB_DISPATCH(dtype, ...)                                       \
+  switch (dtype) {                                                    \
+    case 0: { using T = __nv_bfloat16; __VA_ARGS__; break; }          \
+    case 1: { using T = __half; __VA_ARGS__; break; }                 \
+    case 2: { using T = float; __VA_ARGS__; break; }                  \
+    default: return -1;                                               \
+  }
+
+extern "C" int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* r_out, int rows, int cols,
+                              float eps, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if (cols % (16 / esz)) return -2;
+  const bool small = cols <= 512;
+  const int rpb = small ? 8 : 1;
+  const int grid = grid_for((rows + rpb - 1) / rpb, 1);
+  RB_DISPATCH(dtype, {
+    const T *xx = (const T*)x, *rr = (const T*)res, *ww = (const T*)w;
+    T *yy = (T*)y, *ro = (T*)r_out;
+    if (res) {
+      if (small) rmsnorm_fwd_kernel<T, 32, true><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+      else rmsnorm_fwd_kernel<T, 256, true><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+    } else {
+      if (small) rmsnorm_fwd_kernel<T, 32, false><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+      else rmsnorm_fwd_kernel<T, 256, false><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+    }
+  });
+  return (int)cudaGetLastError();
+}
+
+// scratch: fp32 [rb_rmsnorm_bwd_parts(rows, cols)][cols]
+extern "C" int rb_rmsnorm_bwd_parts(int rows, int cols) {
+  const int rpb = cols <= 512 ? 8 : 1;
+  long long b = (rows + rpb - 1) / rpb;
+  const long long cap = (long long)num_sms() * 2;
+  return (int)(b < 1 ? 1 : (b > cap ? cap : b));
+}
+extern "C" int rb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void* dx, void* dw, float* scratch, int rows,
+                              int cols, float eps, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if (cols % (16 / esz)) return -2;
+  const bool small = cols <= 512;
+  const int grid = rb_rmsnorm_bwd_parts(rows, cols);
+  const size_t shm = (size_t)cols * 4;
+  RB_DISPATCH(dtype, {
+    if (small) rmsnorm_bwd_kernel<T, 32><<<grid, 256, shm, st>>>((const T*)x, (const T*)w, (const T*)dy, (T*)dx, scratch, rows, cols, eps);
+    else rmsnorm_bwd_kernel<T, 256><<<grid, 256, shm, st>>>((const T*)x, (const T*)w, (const T*)dy, (T*)dx, scratch, rows, cols, eps);
+    reduce_partials_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(scratch, (T*)dw, grid, cols);
+  });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_rope(const void* x, void* y, const float* cos_t, const float* sin_t, long long tokens, int H, int D,
+                       int backward, int dtype, cudaStream_t st) {
+  const long long pairs = tokens * H * (D / 2);
+  if (pairs == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if ((D / 2) % (16 / esz)) return -2;
+  const int grid = grid_for(pairs / (16 / esz), 256);
+  RB_DISPATCH(dtype, { rope_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, cos_t, sin_t, pairs, H, D, backward ? -1.f : 1.f); });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_swiglu_fwd(const void* in, void* out, long long rows, int F, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if (F % (16 / esz)) return -2;
+  const int grid = grid_for(rows * F / (16 / esz), 256);
+  RB_DISPATCH(dtype, { swiglu_fwd_kernel<T><<<grid, 256, 0, st>>>((const T*)in, (T*)out, rows, F); });
+  return (int)cudaGetLastError();
+}
+extern "C" int rb_swiglu_bwd(const void* in, const void* dout, void* din, long long rows, int F, int dtype, cudaStream_t st) {
+  if (rows == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if (F % (16 / esz)) return -2;
+  const int grid = grid_for(rows * F / (16 / esz), 256);
+  RB_DISPATCH(dtype, { swiglu_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)in, (const T*)dout, (T*)din, rows, F); });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_adam(void* p, void* master, const void* g, float* m, float* v, long long n, int step, float lr, float b1,
+                       float b2, float eps, float wd, float gscale, int split, int grad_fp32, cudaStream_t st) {
+  if (n == 0) return 0;
+  if (n % 4) return -2;
+  const float bc1 = 1.f - powf(b1, (float)step), bc2 = 1.f - powf(b2, (float)step);
+  const int grid = grid_for(n / 4, 256);
+  __nv_bfloat16* pp = (__nv_bfloat16*)p;
+  if (grad_fp32) {
+    if (split) adam_kernel<float, true><<<grid, 256, 0, st>>>(pp, master, (const float*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
+    else adam_kernel<float, false><<<grid, 256, 0, st>>>(pp, master, (const float*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
+  } else {
+    if (split) adam_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(pp, master, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
+    else adam_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(pp, master, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_sumsq(const void* g, long long n, float* out, int dtype, cudaStream_t st) {
+  if (n == 0) return 0;
+  const int grid = grid_for(n, 256 * 8);
+  RB_DISPATCH(dtype, { sumsq_kernel<T><<<grid, 256, 0, st>>>((const T*)g, n, out); });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_copy_table(const void* table, int n_desc, const int* chunk_start, int total_chunks, int chunk_rows,
+                             int elem_size, cudaStream_t st) {
+  if (total_chunks == 0) return 0;
+  const int grid = total_chunks < num_sms() * 4 ? total_chunks : num_sms() * 4;
+  if (elem_size == 2) copy_table_kernel<uint16_t><<<grid, 256, 0, st>>>((const CopyDesc*)table, n_desc, chunk_start, total_chunks, chunk_rows);
+  else if (elem_size == 4) copy_table_kernel<uint32_t><<<grid, 256, 0, st>>>((const CopyDesc*)table, n_desc, chunk_start, total_chunks, chunk_rows);
+  else return -1;
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_kv_scatter(const void* k, const void* v, void* kc, void* vc, const long long* slots, int tokens,
+                             int row_elems, long long k_stride, long long v_stride, int dtype, cudaStream_t st) {
+  if (tokens == 0) return 0;
+  const int esz = dtype == 2 ? 4 : 2;
+  if (row_elems % (16 / esz) || k_stride % (16 / esz) || v_stride % (16 / esz)) return -2;
+  const int grid = grid_for((long long)tokens * row_elems / (16 / esz), 256);
+  RB_DISPATCH(dtype, { kv_scatter_kernel<T><<<grid, 256, 0, st>>>((const T*)k, (const T*)v, (T*)kc, (T*)vc, slots, tokens, row_elems, k_stride, v_stride); });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_int4_fake_quant(const void* x, void* out, void* scale, void* zero, int M, int N, int bm, int bn, int sym,
+                                  int dtype, cudaStream_t st) {
+  const long long groups = (long long)((M + bm - 1) / bm) * ((N + bn - 1) / bn);
+  if (groups == 0) return 0;
+  const int grid = grid_for(groups, 8);
+  RB_DISPATCH(dtype, { int4_fake_quant_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)out, (T*)scale, (T*)zero, M, N, bm, bn, sym); });
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_fp8_block_cast(const void* w, void* q, float* scale, int M, int N, int block, int ue8m0, int dtype,
+                                 cudaStream_t st) {
+  const int blocks = ((M + block - 1) / block) * ((N + block - 1) / block);
+  if (blocks == 0) return 0;
+  RB_DISPATCH(dtype, { fp8_block_cast_kernel<T><<<blocks, 256, 0, st>>>((const T*)w, (__nv_fp8_e4m3*)q, scale, M, N, block, ue8m0); });
+  return (int)cudaGetLastError();
+}
+extern "C" int rb_fp8_block_dequant(const void* q, const float* scale, void* out, int M, int N, int block, int dtype,
+                                    cudaStream_t st) {
+  if ((long long)M * N == 0) return 0;
+  const int grid = grid_for((long long)M * N, 256);
+  RB_DISPATCH(dtype, { fp8_block_dequant_kernel<T><<<grid, 256, 0, st>>>((const __nv_fp8_e4m3*)q, scale, (T*)out, M, N, block); });
+  return (int)cudaGetLastError();
+}

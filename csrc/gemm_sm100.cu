@@ -1,0 +1,341 @@
+// Persistent warp-specialised GEMM for sm_100a: TMA -> shared memory ring ->
+// tcgen05.mma (accumulators in TMEM, double buffered) -> epilogue warps.
+//
+//   C[M,N] (+)= A_op[M,K] * B_op[N,K]^T        bf16/fp16 in, fp32 accumulate
+//
+// Operand storage (all row-major in global memory):
+//   A K-major : A[M][K]  (lda >= K)        A MN-major : A[K][M]  (lda >= M)   ("transposed A")
+//   B K-major : B[N][K]  (ldb >= K)        B MN-major : B[K][N]  (ldb >= N)
+// which covers y = x W^T (K,K), dx = dy W (K,MN) and dW = dy^T x (MN,MN) without
+// materialising a transpose.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (TMEM -> registers -> global).  One CTA per SM, static
+// round-robin tile schedule with grouped ordering for L2 reuse.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace rb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  int ldc;
+  int tiles_m, tiles_n;
+  int out_fp32, accumulate;
+  int a_mn, b_mn;
+  uint32_t lbo_a, sbo_a, lbo_b, sbo_b;  // MN-major descriptor strides (bytes)
+  void* C;
+  const void* bias;  // optional [N], same dtype as inputs
+  int* err;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = kStages * kStageBytes;
+  static constexpr int kTotal = kBarOffset + 256 + 1024;  // barriers + alignment slack
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  constexpr int GM = 8;
+  const int per_group = GM * tiles_n;
+  const int group = t / per_group;
+  const int first_m = group * GM;
+  const int gm = min(tiles_m - first_m, GM);
+  const int r = t - group * per_group;
+  tm = first_m + (r % gm);
+  tn = r / gm;
+}
+
+template <int BN, bool BF16>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + S::kBarOffset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tfull_bar = empty_bar + kStages;   // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_iters = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<kTmemCols>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
+          uint8_t* sa = smem + s * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[s], S::kStageBytes);
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tma_a, &full_bar[s], k * BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d(sa + c * (BK * 128), &tma_a, &full_bar[s], m0 + c * 64, k * BK);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tma_b, &full_bar[s], k * BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < (BN + 63) / 64; ++c) tma_load_2d(sb + c * (BK * 128), &tma_b, &full_bar[s], n0 + c * 64, k * BK);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(BM, BN, BF16, p.a_mn != 0, p.b_mn != 0);
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.err)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int k = 0; k < k_iters; ++k) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
+          const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            // K-major: 16 elements = 32 bytes inside the 128-byte swizzle row.
+            // MN-major: 16 k-rows of 128 bytes.
+            const uint64_t da = p.a_mn ? make_smem_desc(sa + kk * 2048, p.lbo_a, p.sbo_a, kSwizzle128B)
+                                       : make_smem_desc(sa + kk * 32, 16, 1024, kSwizzle128B);
+            const uint64_t db = p.b_mn ? make_smem_desc(sb + kk * 2048, p.lbo_b, p.sbo_b, kSwizzle128B)
+                                       : make_smem_desc(sb + kk * 32, 16, 1024, kSwizzle128B);
+            umma_f16(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == kStages) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int lane_grp = warp & 3;  // TMEM lanes [32*lane_grp, +32) are visible to this warp
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      const int row = tm * BM + lane_grp * 32 + lane;
+      const int n0 = tn * BN;
+      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.err)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(lane_grp * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_wait_ld();
+        const int col = n0 + c * 32;
+        if (row < p.M && col < p.N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (p.bias) {
+            if constexpr (BF16) {
+              const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) if (col + i < p.N) v[i] += __bfloat162float(b[i]);
+            } else {
+              const __half* b = reinterpret_cast<const __half*>(p.bias) + col;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) if (col + i < p.N) v[i] += __half2float(b[i]);
+            }
+          }
+          const size_t off = static_cast<size_t>(row) * p.ldc + col;
+          const bool full = (col + 32 <= p.N);
+          if (p.out_fp32) {
+            float* out = reinterpret_cast<float*>(p.C) + off;
+            if (full && (p.ldc % 4 == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (p.accumulate) {
+                  const float4 old = reinterpret_cast<float4*>(out)[i];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                reinterpret_cast<float4*>(out)[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < p.N; ++i) out[i] = p.accumulate ? out[i] + v[i] : v[i];
+            }
+          } else {
+            uint16_t* out = reinterpret_cast<uint16_t*>(p.C) + off;
+            if (full && (p.ldc % 8 == 0) && !p.accumulate) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                if constexpr (BF16) {
+                  o.x = pack_bf16(v[8 * i], v[8 * i + 1]);
+                  o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+                  o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+                  o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+                } else {
+                  __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]), h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+                  __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]), h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                  o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                  o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                }
+                reinterpret_cast<uint4*>(out)[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col + i < p.N; ++i) {
+                float x = v[i];
+                if constexpr (BF16) {
+                  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + i;
+                  if (p.accumulate) x += __bfloat162float(*o);
+                  *o = __float2bfloat16(x);
+                } else {
+                  __half* o = reinterpret_cast<__half*>(out) + i;
+                  if (p.accumulate) x += __half2float(*o);
+                  *o = __float2half(x);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1;
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  if (*abort_flag) __nanosleep(50000);  // let any bulk copy still in flight land before shared memory is released
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<kTmemCols>(tmem_base);
+  }
+}
+
+// ----------------------------------------------------------------------------- host side
+
+static int make_operand_map(CUtensorMap* map, const void* ptr, bool mn_major, int rows_op, int K, int ld, int box_rows) {
+  // rows_op = M (for A) or N (for B).  K-major storage: [rows_op][K] -> dims {K, rows_op}, box {64, box_rows}.
+  // MN-major storage: [K][rows_op] -> dims {rows_op, K}, box {64, 64}.
+  if (!mn_major) return encode_tma_2d_bf16(map, ptr, K, rows_op, ld, BK, box_rows);
+  return encode_tma_2d_bf16(map, ptr, rows_op, K, ld, 64, BK);
+}
+
+template <int BN, bool BF16>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+  using S = GemmSmem<BN>;
+  static bool attr_set = false;
+  auto kern = gemm_kernel<BN, BF16>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  p.tiles_m = (p.M + BM - 1) / BM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < num_sms() ? tiles : num_sms();
+  kern<<<grid, GEMM_THREADS, S::kTotal, stream>>>(ta, tb, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace rb
+
+extern "C" int rb_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                       int ldc, int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int is_fp16,
+                       int force_bn, int lbo_a, int sbo_a, int lbo_b, int sbo_b, int* err_flag, cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
+  int bn = force_bn;
+  if (bn == 0) {
+    // fill the machine: shrink the N tile while the tile count is below the SM count
+    const int tm = (M + BM - 1) / BM;
+    bn = 256;
+    while (bn > 64 && tm * ((N + bn - 1) / bn) < num_sms()) bn >>= 1;
+    if (!b_mn_major && bn == 64 && tm * ((N + 63) / 64) < num_sms() / 2) bn = 32;
+  }
+  if (b_mn_major && bn < 64) bn = 64;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  p.a_mn = a_mn_major; p.b_mn = b_mn_major;
+  // MN-major canonical layout (128-byte swizzle): 64-element chunks along M/N are
+  // BK*128 bytes apart (one TMA box each), 8-row k groups are 1024 bytes apart.
+  p.lbo_a = lbo_a ? lbo_a : BK * 128; p.sbo_a = sbo_a ? sbo_a : 1024;
+  p.lbo_b = lbo_b ? lbo_b : BK * 128; p.sbo_b = sbo_b ? sbo_b : 1024;
+  p.C = C; p.bias = bias; p.err = err_flag;
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, A, a_mn_major, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, B, b_mn_major, N, K, ldb, bn);
+  if (rc) return rc;
+#define RB_LAUNCH(BN_)                                                              \
+  return is_fp16 ? launch<BN_, false>(ta, tb, p, stream) : launch<BN_, true>(ta, tb, p, stream);
+  switch (bn) {
+    case 256: RB_LAUNCH(256)
+    case 128: RB_LAUNCH(128)
+    case 64: RB_LAUNCH(64)
+    case 32: RB_LAUNCH(32)
+    default: return -3;
+  }
+#undef RB_LAUNCH
+}

@@ -1,0 +1,403 @@
+"""Autograd wrappers around the in-tree sm_100a extension (``relax_b200/_C.so``).
+
+Importing this module on a machine with a GPU but without the built extension
+raises: CUDA tensors never fall back to library kernels silently.
+"""
+from __future__ import annotations
+
+import importlib.util
+import math
+import os
+from typing import Optional
+
+import torch
+
+_SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+_C = None
+_ERR: dict = {}
+_MN_OK: Optional[bool] = None
+
+
+def _load():
+    global _C
+    if _C is not None:
+        return _C
+    if not os.path.exists(_SO):
+        raise RuntimeError(f"{_SO} is missing: build it with `python __graft_entry__.py` (nvcc, sm_100a)")
+    spec = importlib.util.spec_from_file_location("relax_b200._C", _SO)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    _C = mod
+    return mod
+
+
+def available() -> bool:
+    if not torch.cuda.is_available():
+        return False
+    _load()
+    return True
+
+
+def err_flag(device=None) -> torch.Tensor:
+    dev = torch.device(device if device is not None else torch.cuda.current_device())
+    if dev.type != "cuda":
+        dev = torch.device("cuda", torch.cuda.current_device())
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _ERR:
+        _ERR[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+    return _ERR[idx]
+
+
+def check_error_flag(device=None):
+    """Raise if any kernel recorded an error status (e.g. a bounded wait that ran out)."""
+    f = err_flag(device)
+    v = int(f.item())
+    if v != 0:
+        f.zero_()
+        raise RuntimeError(f"sm_100a kernel reported error status {v} (1 = barrier wait timed out, 3 = peer wait timed out)")
+
+
+# --------------------------------------------------------------------------- GEMM
+
+
+def gemm_raw(a, b, out, M, N, K, lda, ldb, ldc, a_mn=False, b_mn=False, accumulate=False, bias=None, force_bn=0,
+             lbo_a=0, sbo_a=0, lbo_b=0, sbo_b=0):
+    _load().gemm(a, b, out, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, force_bn, lbo_a, sbo_a, lbo_b, sbo_b,
+                 err_flag(a.device))
+    return out
+
+
+def _rowmajor_2d(t):
+    """Return (tensor, ld) such that the tensor is a row-major matrix with 16-byte aligned pitch."""
+    if t.stride(-1) != 1 or t.stride(0) % 8 or t.stride(0) < t.shape[1] or t.data_ptr() % 16:
+        t = t.contiguous()
+        if t.shape[1] % 8:
+            raise ValueError(f"GEMM operand inner dimension {t.shape[1]} must be a multiple of 8")
+    return t, t.stride(0)
+
+
+def mn_major_ok() -> bool:
+    """One-time numerical self-check of the MN-major (transposed operand) tensor-core path
+    against the K-major path on explicitly transposed copies."""
+    global _MN_OK
+    if _MN_OK is None:
+        if os.environ.get("RELAX_B200_DISABLE_MN_MAJOR", "0") == "1":
+            _MN_OK = False
+            return False
+        g = torch.Generator(device="cuda").manual_seed(1)
+        M, N, K = 256, 192, 320
+        at = torch.randn(K, M, device="cuda", generator=g).bfloat16()   # A stored transposed
+        bt = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+        ref = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        gemm_raw(at.t().contiguous(), bt.t().contiguous(), ref, M, N, K, K, K, N)
+        out = torch.empty_like(ref)
+        gemm_raw(at, bt, out, M, N, K, M, N, N, a_mn=True, b_mn=True)
+        _MN_OK = bool(torch.allclose(out.float(), ref.float(), atol=1e-2, rtol=1e-2))
+    return _MN_OK
+
+
+def matmul_nt(x, w, bias=None, out_dtype=None, out=None, accumulate=False):
+    """x[M,K] @ w[N,K]^T."""
+    x, lda = _rowmajor_2d(x)
+    w, ldb = _rowmajor_2d(w)
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
+    return gemm_raw(x, w, out, M, N, K, lda, ldb, out.stride(0), bias=bias, accumulate=accumulate)
+
+
+def matmul_nn(a, b, out=None, out_dtype=None):
+    """a[M,K] @ b[K,N]  (b row-major: the MN-major B operand)."""
+    a, lda = _rowmajor_2d(a)
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if mn_major_ok() and N % 8 == 0:
+        b, ldb = _rowmajor_2d(b)
+        return gemm_raw(a, b, out, M, N, K, lda, ldb, out.stride(0), b_mn=True)
+    bt = b.t().contiguous()
+    return gemm_raw(a, bt, out, M, N, K, lda, bt.stride(0), out.stride(0))
+
+
+def matmul_tn(a, b, out=None, out_dtype=None, accumulate=False):
+    """a[K,M]^T @ b[K,N] -> [M,N]  (both operands MN-major: weight gradients)."""
+    K, M = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or a.dtype, device=a.device)
+    if mn_major_ok() and M % 8 == 0 and N % 8 == 0:
+        a, lda = _rowmajor_2d(a)
+        b, ldb = _rowmajor_2d(b)
+        return gemm_raw(a, b, out, M, N, K, lda, ldb, out.stride(0), a_mn=True, b_mn=True, accumulate=accumulate)
+    at, bt = a.t().contiguous(), b.t().contiguous()
+    return gemm_raw(at, bt, out, M, N, K, at.stride(0), bt.stride(0), out.stride(0), accumulate=accumulate)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = bias is not None
+        return matmul_nt(x, w, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = matmul_nn(dy, w) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = matmul_tn(dy, x)
+        db = dy.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db
+
+
+def linear(x, w, bias=None):
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("the sm_100a GEMM takes bf16/fp16 inputs")
+    if w.dim() != 2:
+        raise ValueError("weight must be 2-D")
+    if not w.is_contiguous() and w.t().is_contiguous():
+        # y = x @ (w^T stored row-major)  ->  NN product
+        y = _LinearNN.apply(x2, w.t())
+    else:
+        y = _Linear.apply(x2, w, bias)
+        bias = None
+    if bias is not None:
+        y = y + bias
+    return y.reshape(*shp[:-1], y.shape[-1])
+
+
+class _LinearNN(torch.autograd.Function):
+    """y = x @ b with b[K,N] row-major (used when the caller passes ``w.t()``)."""
+
+    @staticmethod
+    def forward(ctx, x, b):
+        ctx.save_for_backward(x, b)
+        return matmul_nn(x, b)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, b = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = matmul_nt(dy, b) if ctx.needs_input_grad[0] else None
+        db = matmul_tn(x, dy) if ctx.needs_input_grad[1] else None
+        return dx, db
+
+
+# --------------------------------------------------------------------------- norms / elementwise
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps):
+        x = x.contiguous()
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        y = torch.empty_like(x)
+        _load().rmsnorm_fwd(x, None, w, y, None, rows, cols, eps)
+        ctx.save_for_backward(x, w)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.empty_like(w)
+        C = _load()
+        scratch = torch.empty(C.rmsnorm_bwd_parts(rows, cols) * cols, dtype=torch.float32, device=x.device)
+        C.rmsnorm_bwd(x, w, dy, dx, dw, scratch, rows, cols, ctx.eps)
+        return dx, dw, None
+
+
+def rmsnorm(x, w, eps=1e-6):
+    return _RMSNorm.apply(x, w, eps)
+
+
+class _AddRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, eps):
+        x, res = x.contiguous(), res.contiguous()
+        cols = x.shape[-1]
+        rows = x.numel() // cols
+        y, r = torch.empty_like(x), torch.empty_like(x)
+        _load().rmsnorm_fwd(x, res, w, y, r, rows, cols, eps)
+        ctx.save_for_backward(r, w)
+        ctx.eps = eps
+        return y, r
+
+    @staticmethod
+    def backward(ctx, dy, dr):
+        r, w = ctx.saved_tensors
+        cols = r.shape[-1]
+        rows = r.numel() // cols
+        dx = torch.empty_like(r)
+        dw = torch.empty_like(w)
+        C = _load()
+        scratch = torch.empty(C.rmsnorm_bwd_parts(rows, cols) * cols, dtype=torch.float32, device=r.device)
+        C.rmsnorm_bwd(r, w, dy.contiguous(), dx, dw, scratch, rows, cols, ctx.eps)
+        if dr is not None:
+            dx = dx + dr
+        return dx, dx, dw, None
+
+
+def add_rmsnorm(x, res, w, eps=1e-6):
+    return _AddRMSNorm.apply(x, res, w, eps)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        x = x.contiguous()
+        T, H, D = x.shape
+        y = torch.empty_like(x)
+        cos, sin = cos.contiguous(), sin.contiguous()
+        _load().rope(x, y, cos, sin, T, H, D, False)
+        ctx.save_for_backward(cos, sin)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        dy = dy.contiguous()
+        T, H, D = dy.shape
+        dx = torch.empty_like(dy)
+        _load().rope(dy, dx, cos, sin, T, H, D, True)
+        return dx, None, None
+
+
+def apply_rope(x, cos, sin):
+    return _Rope.apply(x, cos.float(), sin.float())
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu = gu.contiguous()
+        F = gu.shape[-1] // 2
+        rows = gu.numel() // (2 * F)
+        out = torch.empty(*gu.shape[:-1], F, dtype=gu.dtype, device=gu.device)
+        _load().swiglu_fwd(gu, out, rows, F)
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        F = gu.shape[-1] // 2
+        rows = gu.numel() // (2 * F)
+        din = torch.empty_like(gu)
+        _load().swiglu_bwd(gu, dout.contiguous(), din, rows, F)
+        return din
+
+
+def swiglu(gate_up):
+    return _SwiGLU.apply(gate_up)
+
+
+# --------------------------------------------------------------------------- optimizer / misc
+
+
+def fused_adam(pshard, master, gshard, exp_avg, exp_avg_sq, step, lr, b1, b2, eps, wd, gscale, split):
+    _load().adam(pshard, master, gshard, exp_avg, exp_avg_sq, step, lr, b1, b2, eps, wd, gscale, split)
+
+
+def sumsq(x) -> torch.Tensor:
+    out = torch.zeros(1, dtype=torch.float32, device=x.device)
+    _load().sumsq(x.contiguous().view(-1), out)
+    return out
+
+
+def kv_scatter(k, v, k_cache, v_cache, slots):
+    """k/v ``[T, H, D]`` (possibly strided views of a fused qkv buffer) -> cache rows ``slots[T]``."""
+    T = k.shape[0]
+    row = k.shape[1] * k.shape[2]
+    if k.stride(2) != 1 or k.stride(1) != k.shape[2]:
+        k = k.contiguous()
+    if v.stride(2) != 1 or v.stride(1) != v.shape[2]:
+        v = v.contiguous()
+    _load().kv_scatter(k, v, k_cache, v_cache, slots, T, row, k.stride(0), v.stride(0))
+
+
+def fake_int4_quant(x, block_m, block_n, sym=True):
+    x = x.contiguous()
+    M, N = x.shape
+    gm, gn = (M + block_m - 1) // block_m, (N + block_n - 1) // block_n
+    out = torch.empty_like(x)
+    scale = torch.empty(gm, gn, dtype=x.dtype, device=x.device)
+    zero = torch.empty(gm, gn, dtype=x.dtype, device=x.device)
+    _load().int4_fake_quant(x, out, scale, zero, block_m, block_n, sym)
+    return out, scale, zero
+
+
+def blockwise_cast_to_fp8(w, block=128, ue8m0=False):
+    w = w.contiguous()
+    M, N = w.shape
+    q = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=w.device)
+    scale = torch.empty((M + block - 1) // block, (N + block - 1) // block, dtype=torch.float32, device=w.device)
+    _load().fp8_block_cast(w, q, scale, block, ue8m0)
+    return q, scale
+
+
+def blockwise_dequant_fp8(q, scale_inv, block=128, dtype=torch.bfloat16):
+    out = torch.empty(q.shape, dtype=dtype, device=q.device)
+    _load().fp8_block_dequant(q.contiguous(), scale_inv.contiguous(), out, block)
+    return out
+
+
+# --------------------------------------------------------------------------- weight-sync copy table
+
+
+class CopyTable:
+    def __init__(self, table, chunk_start, n_desc, total_chunks, chunk_rows, elem_size, keepalive):
+        self.table, self.chunk_start = table, chunk_start
+        self.n_desc, self.total_chunks, self.chunk_rows, self.elem_size = n_desc, total_chunks, chunk_rows, elem_size
+        self.keepalive = keepalive
+
+
+def build_copy_table_raw(entries, device, elem_size: int, chunk_bytes: int = 1 << 18) -> CopyTable:
+    """entries: (src_ptr, dst_ptr, rows, cols, src_ld, dst_ld) in elements.  Large blocks are
+    split into chunks of about ``chunk_bytes`` so the copy spreads over all SMs."""
+    import struct
+
+    raw = bytearray()
+    starts, total = [], 0
+    chunk_rows_list = []
+    # one global chunk_rows keeps the kernel simple: rows per chunk chosen from the widest block
+    max_cols = max((e[3] for e in entries), default=1)
+    chunk_rows = max(1, chunk_bytes // max(1, max_cols * elem_size))
+    for (s, d, rows, cols, sld, dld) in entries:
+        raw += struct.pack("<QQiiii", s, d, rows, cols, sld, dld)
+        starts.append(total)
+        total += (rows + chunk_rows - 1) // chunk_rows
+    table = torch.frombuffer(bytes(raw), dtype=torch.uint8).to(device)
+    cs = torch.tensor(starts, dtype=torch.int32, device=device)
+    return CopyTable(table, cs, len(entries), total, chunk_rows, elem_size, None)
+
+
+def build_copy_table(blocks, trainer_params: dict, rollout_weights) -> CopyTable:
+    entries = []
+    es = next(iter(trainer_params.values())).element_size()
+    for b in blocks:
+        src = trainer_params[b.src_name]
+        dst = rollout_weights.p[b.dst_name]
+        s2 = src[b.src_batch] if src.dim() == 3 else (src.view(1, -1) if src.dim() == 1 else src)
+        d2 = dst[b.dst_batch] if dst.dim() == 3 else (dst.view(1, -1) if dst.dim() == 1 else dst)
+        sp = s2.data_ptr() + (b.src_row * s2.stride(0) + b.src_col) * es
+        dp = d2.data_ptr() + (b.dst_row * d2.stride(0) + b.dst_col) * es
+        entries.append((sp, dp, b.rows, b.cols, s2.stride(0), d2.stride(0)))
+    t = build_copy_table_raw(entries, rollout_weights.device, es)
+    t.keepalive = (trainer_params, rollout_weights)
+    return t
+
+
+def run_copy_table(t: CopyTable):
+    _load().copy_table(t.table, t.n_desc, t.chunk_start, t.total_chunks, t.chunk_rows, t.elem_size)
