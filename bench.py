@@ -1,0 +1,237 @@
+"""Headline benchmark: colocated GRPO step (rollout + train + weight sync) of a
+Qwen3-8B-shaped model, tokens/s for the whole job.
+
+    python bench.py --gpus 1 --steps 2 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Config (weak scaling: per-GPU work fixed): per GPU 16 prompts of 512 random token
+ids, 8 samples each, responses up to 2048 tokens at temperature 1; at 8 GPUs that
+is the named configuration (128 prompts, trainer TP2 x DP4 with the distributed
+optimizer, rollout TP2 x 4 engines).  Random-init weights, synthetic prompts,
+parity reward, GRPO clip 0.2 with a k1 KL term (coef 0.001) to a frozen reference,
+weight sync after every step.
+
+`value` is device-timed (CUDA events around the K steps); `e2e.value` is wall
+clock around the same public-API calls, which include, per step, the host->device
+copy of that step's prompts from pinned memory and the device->host read of the
+step's loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-8b")
+    ap.add_argument("--prompts-per-gpu", type=int, default=16)
+    ap.add_argument("--group-size", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--response-len", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: override depth (result is then not comparable)")
+    ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
+    ap.add_argument("--kv-gb", type=float, default=28.0)
+    return ap.parse_args()
+
+
+def reference_arm(args):
+    """The reference needs Ray, Megatron-LM, TransformerEngine, SGLang and its data-plane
+    package at run time; none of them is installed and none can be fetched offline."""
+    why = "reference run-time dependencies (ray, megatron.core, transformer_engine, sglang, transfer_queue) are not installed and cannot be installed offline"
+    try:
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import importlib
+
+        missing = [m for m in ("ray", "megatron.core", "sglang", "transformer_engine") if importlib.util.find_spec(m.split(".")[0]) is None]
+        if not missing:
+            why = "reference dependencies import, but no offline recipe drives its Ray Serve deployment on this box"
+        else:
+            why = f"reference cannot run: missing {', '.join(missing)} (not installable offline)"
+    except Exception as e:  # noqa: BLE001
+        why = f"reference probe failed: {e!r}"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons of this process's GPU during the timed region."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], False
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.5)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = max(mx, float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm(args)
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    import torch
+    import torch.distributed as dist
+
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.ops import cuda as C
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert C.available()
+
+    over = {} if args.layers is None else {"num_layers": args.layers}
+    mcfg = get_config(args.model, **over)
+    tp = 2 if world >= 2 else 1
+    G = args.group_size
+    n_prompts = args.prompts_per_gpu * world
+    kv_bytes_per_block = mcfg.num_layers * 2 * 16 * (mcfg.num_query_groups // tp) * mcfg.head_dim * 2
+    kv_blocks = int(args.kv_gb * (1 << 30) / kv_bytes_per_block)
+    need_blocks = args.prompts_per_gpu * tp * G * ((args.prompt_len + args.response_len + 15) // 16 + 1)
+    kv_blocks = min(kv_blocks, need_blocks)
+    cfg = ColocateConfig(
+        model=mcfg,
+        train=TrainConfig(advantage_estimator="grpo", n_samples_per_prompt=G, global_batch_size=n_prompts * G,
+                          max_tokens_per_gpu=args.max_tokens_per_gpu, pad_multiple=128,
+                          loss=LossConfig(eps_clip=0.2, use_kl_loss=True, kl_loss_coef=0.001, kl_loss_type="k1"),
+                          optim=OptimizerConfig(lr=1e-6, clip_grad=1.0, grad_dtype="fp32")),
+        trainer_tp=tp, rollout_tp=tp, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
+        max_response_len=args.response_len, temperature=1.0, rm_type="parity", eos_token_id=None,
+        kv_blocks=kv_blocks, kv_block_size=16, max_running=512, seed=0, rollout_seed=42,
+        offload_rollout=True, release_rollout_weights=True, pinned_prompts=True)
+    run = ColocatedGRPO(cfg, device=dev)
+
+    def one_step():
+        m = run.step()
+        return m
+
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    C.reset_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    ev0.record()
+    resp_tokens = total_tokens = 0
+    sync_ms, losses, h2d, d2h = [], [], 0, 0
+    parts = {}
+    for _ in range(args.steps):
+        m = one_step()
+        resp_tokens += m["response_tokens_local"]
+        total_tokens += m["total_tokens_local"]
+        sync_ms.append(m["weight_sync_ms"])
+        losses.append(m["loss"])
+        h2d += m.get("h2d_bytes", 0)
+        d2h += m.get("d2h_bytes", 0)
+        for k, v in m.items():
+            if k.startswith("perf/"):
+                parts[k] = parts.get(k, 0.0) + v
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    dev_s = ev0.elapsed_time(ev1) / 1e3
+    sampler.stop_flag = True
+    launches = C.launch_count()
+    # each engine's TP ranks hold identical samples: count every sequence once
+    stat = torch.tensor([dev_s, wall, resp_tokens / tp, total_tokens / tp, float(launches)], device=dev, dtype=torch.float64)
+    if world > 1:
+        mx = stat.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stat.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dev_s, wall = float(mx[0]), float(mx[1])
+        resp_all, tot_all = float(sm[2]), float(sm[3])
+        launches = int(mx[4])
+    else:
+        resp_all, tot_all = resp_tokens, total_tokens
+    C.check_error_flag()
+    if rank == 0:
+        value = resp_all / dev_s
+        out = {
+            "metric": "grpo_e2e_response_tokens_per_sec_per_box",
+            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_s * 1e3 / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic prompts (random token ids), random-init weights, parity reward",
+            "config": {
+                "model": mcfg.name + ("" if args.layers is None else f"-{args.layers}L-debug"),
+                "global_batch": n_prompts, "group_size": G, "seq_len": args.prompt_len + args.response_len,
+                "prompt_len": args.prompt_len, "max_response_len": args.response_len,
+                "parallelism": f"trainer tp{tp}xdp{world // tp} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated",
+                "loss": "grpo clip 0.2 + k1 kl 0.001 to frozen reference", "weight_sync_every_step": True,
+                "cache": "working set per step (weights + activations + KV) far exceeds the 126 MB L2; no flush needed",
+            },
+            "total_tokens_per_sec": round(tot_all / dev_s, 2),
+            "weight_sync_ms": round(sum(sync_ms) / len(sync_ms), 3),
+            "phase_seconds_per_step": {k[5:]: round(v / args.steps, 3) for k, v in sorted(parts.items())},
+            "loss": losses[-1],
+            "e2e": {"value": round(resp_all / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d // max(1, args.steps),
+                    "d2h_bytes_per_step": d2h // max(1, args.steps)},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

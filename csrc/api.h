@@ -42,3 +42,32 @@ int rb_fp8_block_dequant(const void* q, const float* scale, void* out, int M, in
 #include <pybind11/pybind11.h>
 void register_more(pybind11::module_& m);
 #endif
+
+// ---- attention / decode / sampling / fused LM head (declared again for C callers)
+#ifdef __cplusplus
+extern "C" {
+#endif
+int rb_fa_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_q, const int* cu_k,
+              int num_seqs, int Tq, int Tk, int Hq, int Hkv, long long q_tok, long long q_head, long long k_tok,
+              long long k_head, long long v_tok, long long v_head, int causal, float scale, int max_q_blocks, int* err,
+              cudaStream_t stream);
+int rb_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+              void* dk, void* dv, float* delta, float* dq_acc, const int* cu_q, const int* cu_k, int num_seqs, int Tq,
+              int Tk, int Hq, int Hkv, int causal, float scale, int max_kv_blocks, int* err, cudaStream_t stream);
+int rb_decode_attn_splits(int B, int Hkv, int max_ctx);
+int rb_decode_attn(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens, void* out,
+                   float* part_o, float* part_ml, int B, int Hq, int Hkv, int block_size, int max_blocks, int max_ctx,
+                   float scale, int splits, cudaStream_t st);
+int rb_sample(const float* logits, int B, int V, int ld, const float* temperature, const long long* top_k,
+              const float* top_p, const float* uniform, long long* tok, float* logp, cudaStream_t st);
+int rb_topk_router(const float* logits, int T, int E, int K, int norm, float* w, long long* idx, float* probs,
+                   cudaStream_t st);
+int rb_lm_head_splits(int M, int N);
+int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
+                       int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);
+int rb_lm_head_dlogits(const void* h, const void* W, const long long* targets, const float* row_stats, const float* g_lp,
+                       const float* g_ent, void* dlogits, int M, int N, int K, int ldh, int ldw, int ldd, int vocab_start,
+                       float inv_temp, int* err, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

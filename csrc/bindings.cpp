@@ -7,9 +7,36 @@
 
 #include "api.h"
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 namespace {
 
-inline cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+// Debug aid: print a native backtrace when the process receives SIGSEGV/SIGABRT.
+void crash_handler(int sig) {
+  const char msg[] = "\n[relax_b200] fatal signal, native backtrace:\n";
+  (void)!write(2, msg, sizeof(msg) - 1);
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  backtrace_symbols_fd(frames, n, 2);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+void install_crash_handler() {
+  void* warm[4];
+  (void)backtrace(warm, 4);  // loads the unwinder now, not inside the handler
+  signal(SIGSEGV, crash_handler);
+  signal(SIGBUS, crash_handler);
+}
+
+// Also clears this thread's "last error" slot: launchers report cudaGetLastError() after their
+// launch, and an unrelated, already handled status left there by another library (for example
+// cudaErrorNotReady from an event query) must not be mistaken for a launch failure.
+inline cudaStream_t cur_stream() {
+  (void)cudaGetLastError();
+  return at::cuda::getCurrentCUDAStream().stream();
+}
 
 inline int dtype_code(const torch::Tensor& t) {
   switch (t.scalar_type()) {
@@ -19,7 +46,14 @@ inline int dtype_code(const torch::Tensor& t) {
     default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
   }
 }
-inline void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+inline void check(int rc, const char* what) {
+  if (rc != 0) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "%s failed with code %d (%s)", what, rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "argument check");
+    fprintf(stderr, "[relax_b200] %s\n", buf);
+    throw std::runtime_error(buf);
+  }
+}
 inline const void* optptr(const c10::optional<torch::Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 
 #define CHECK_CUDA_CONTIG(t) TORCH_CHECK((t).is_cuda() && (t).is_contiguous(), #t " must be a contiguous CUDA tensor")
@@ -121,6 +155,7 @@ void fp8_block_dequant(torch::Tensor q, torch::Tensor scale, torch::Tensor out, 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("install_crash_handler", &install_crash_handler);
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_parts", &rmsnorm_bwd_parts);

@@ -5,4 +5,106 @@
 
 #include "api.h"
 
-void register_more(pybind11::module_& m) { (void)m; }
+namespace {
+// Also clears this thread's "last error" slot: launchers report cudaGetLastError() after their
+// launch, and an unrelated, already handled status left there by another library (for example
+// cudaErrorNotReady from an event query) must not be mistaken for a launch failure.
+inline cudaStream_t cur_stream() {
+  (void)cudaGetLastError();
+  return at::cuda::getCurrentCUDAStream().stream();
+}
+inline void check(int rc, const char* what) {
+  if (rc != 0) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "%s failed with code %d (%s)", what, rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "argument check");
+    fprintf(stderr, "[relax_b200] %s\n", buf);
+    throw std::runtime_error(buf);
+  }
+}
+
+void fa_fwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor lse, torch::Tensor cu_q,
+            torch::Tensor cu_k, int64_t max_q_blocks, bool causal, double scale, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && q.size(2) == 128, "flash attention: bf16, head_dim 128");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1, "head dimension must be contiguous");
+  check(rb_fa_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), cu_q.data_ptr<int>(),
+                  cu_k.data_ptr<int>(), (int)cu_q.numel() - 1, (int)q.size(0), (int)k.size(0), (int)q.size(1),
+                  (int)k.size(1), q.stride(0), q.stride(1), k.stride(0), k.stride(1), v.stride(0), v.stride(1), causal,
+                  (float)scale, (int)max_q_blocks, err.data_ptr<int>(), cur_stream()),
+        "rb_fa_fwd");
+}
+void fa_bwd(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor d_o, torch::Tensor lse,
+            torch::Tensor dq, torch::Tensor dk, torch::Tensor dv, torch::Tensor delta, torch::Tensor dq_acc,
+            torch::Tensor cu_q, torch::Tensor cu_k, int64_t max_kv_blocks, bool causal, double scale, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  check(rb_fa_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                  dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
+                  cu_q.data_ptr<int>(), cu_k.data_ptr<int>(), (int)cu_q.numel() - 1, (int)q.size(0), (int)k.size(0),
+                  (int)q.size(1), (int)k.size(1), causal, (float)scale, (int)max_kv_blocks, err.data_ptr<int>(),
+                  cur_stream()),
+        "rb_fa_bwd");
+}
+int64_t decode_attn_splits(int64_t B, int64_t Hkv, int64_t max_ctx) {
+  return rb_decode_attn_splits((int)B, (int)Hkv, (int)max_ctx);
+}
+void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Tensor block_tables, torch::Tensor ctx_lens,
+                 torch::Tensor out, c10::optional<torch::Tensor> part_o, c10::optional<torch::Tensor> part_ml,
+                 int64_t max_ctx, double scale, int64_t splits) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && q.size(2) == 128, "decode attention: bf16, head_dim 128");
+  check(rb_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                       out.data_ptr(), part_o.has_value() ? part_o->data_ptr<float>() : nullptr,
+                       part_ml.has_value() ? part_ml->data_ptr<float>() : nullptr, (int)q.size(0), (int)q.size(1),
+                       (int)kc.size(2), (int)kc.size(1), (int)block_tables.size(1), (int)max_ctx, (float)scale,
+                       (int)splits, cur_stream()),
+        "rb_decode_attn");
+}
+void sample(torch::Tensor logits, torch::Tensor temperature, torch::Tensor top_k, torch::Tensor top_p,
+            torch::Tensor uniform, torch::Tensor tok, torch::Tensor logp, int64_t V) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  check(rb_sample(logits.data_ptr<float>(), (int)logits.size(0), (int)V, (int)logits.stride(0),
+                  temperature.data_ptr<float>(), (const long long*)top_k.data_ptr<int64_t>(), top_p.data_ptr<float>(),
+                  uniform.data_ptr<float>(), (long long*)tok.data_ptr<int64_t>(), logp.data_ptr<float>(), cur_stream()),
+        "rb_sample");
+}
+void topk_router(torch::Tensor logits, int64_t K, bool norm, torch::Tensor w, torch::Tensor idx, torch::Tensor probs) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  check(rb_topk_router(logits.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)K, norm,
+                       w.data_ptr<float>(), (long long*)idx.data_ptr<int64_t>(), probs.data_ptr<float>(), cur_stream()),
+        "rb_topk_router");
+}
+int64_t lm_head_splits(int64_t M, int64_t N) { return rb_lm_head_splits((int)M, (int)N); }
+void lm_head_logprob(torch::Tensor h, torch::Tensor W, torch::Tensor targets, torch::Tensor partials, int64_t vocab_start,
+                     double inv_temp, int64_t n_splits, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(h.device());
+  TORCH_CHECK(h.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16, "fused LM head: bf16");
+  check(rb_lm_head_logprob(h.data_ptr(), W.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                           partials.data_ptr<float>(), (int)h.size(0), (int)W.size(0), (int)h.size(1), (int)h.stride(0),
+                           (int)W.stride(0), (int)vocab_start, (float)inv_temp, (int)n_splits, err.data_ptr<int>(),
+                           cur_stream()),
+        "rb_lm_head_logprob");
+}
+void lm_head_dlogits(torch::Tensor h, torch::Tensor W, torch::Tensor targets, torch::Tensor row_stats, torch::Tensor g_lp,
+                     c10::optional<torch::Tensor> g_ent, torch::Tensor dlogits, int64_t vocab_start, double inv_temp,
+                     torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(h.device());
+  check(rb_lm_head_dlogits(h.data_ptr(), W.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                           row_stats.data_ptr<float>(), g_lp.data_ptr<float>(),
+                           g_ent.has_value() ? g_ent->data_ptr<float>() : nullptr, dlogits.data_ptr(), (int)h.size(0),
+                           (int)W.size(0), (int)h.size(1), (int)h.stride(0), (int)W.stride(0), (int)dlogits.stride(0),
+                           (int)vocab_start, (float)inv_temp, err.data_ptr<int>(), cur_stream()),
+        "rb_lm_head_dlogits");
+}
+}  // namespace
+
+void register_more(pybind11::module_& m) {
+  m.def("fa_fwd", &fa_fwd);
+  m.def("fa_bwd", &fa_bwd);
+  m.def("decode_attn_splits", &decode_attn_splits);
+  m.def("decode_attn", &decode_attn);
+  m.def("sample", &sample);
+  m.def("topk_router", &topk_router);
+  m.def("lm_head_splits", &lm_head_splits);
+  m.def("lm_head_logprob", &lm_head_logprob);
+  m.def("lm_head_dlogits", &lm_head_dlogits);
+}

@@ -272,7 +272,12 @@ __global__ void adam_kernel(__nv_bfloat16* __restrict__ p, void* __restrict__ ma
       w[k] = w[k] * (1.f - lr * wd) - lr * (mv[k] / bc1) / denom;
       const __nv_bfloat16 h = __float2bfloat16_rn(w[k]);
       hi[k] = *reinterpret_cast<const uint16_t*>(&h);
-      rem[k] = static_cast<int16_t>(__float_as_int(w[k]) - (static_cast<int>(static_cast<int16_t>(hi[k])) << 16));
+      int r = __float_as_int(w[k]) - (static_cast<int>(static_cast<int16_t>(hi[k])) << 16);
+      if (r == 32768) {  // exact tie rounded to the smaller pattern: take the other neighbour so the remainder fits int16
+        hi[k] = static_cast<uint16_t>(hi[k] + 1);
+        r = -32768;
+      }
+      rem[k] = static_cast<int16_t>(r);
     }
     *reinterpret_cast<float4*>(m + i) = make_float4(mv[0], mv[1], mv[2], mv[3]);
     *reinterpret_cast<float4*>(v + i) = make_float4(vv[0], vv[1], vv[2], vv[3]);

@@ -31,7 +31,18 @@ struct GemmParams {
   void* C;
   const void* bias;  // optional [N], same dtype as inputs
   int* err;
+  // ---- fused LM-head modes (MODE 1: log-prob/entropy partials, MODE 2: d(logits) tile)
+  const long long* targets;  // [M] global vocabulary ids
+  int vocab_start;           // first vocabulary id of this shard
+  float inv_temp;
+  int n_splits, tiles_per_split;
+  float* partials;           // MODE 1 out: [M][n_splits][4] = (max, sum exp, sum exp*z, target logit or -inf)
+  const float* row_stats;    // MODE 2 in:  [M][2] = (log Z, sum p*z) of the temperature-scaled logits
+  const float* g_lp;         // MODE 2 in:  [M] upstream gradient of log-prob
+  const float* g_ent;        // MODE 2 in:  [M] upstream gradient of entropy (may be null)
 };
+
+enum : int { kEpiStore = 0, kEpiLogProb = 1, kEpiDLogits = 2 };
 
 template <int BN>
 struct GemmSmem {
@@ -54,7 +65,24 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / gm;
 }
 
-template <int BN, bool BF16>
+// i-th tile of this CTA.  MODE 1 pins a CTA to one row block and a contiguous range of
+// column tiles (so per-row softmax statistics stay in registers); the other modes use the
+// persistent round-robin schedule.
+template <int MODE>
+__device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, int& tn) {
+  if constexpr (MODE == kEpiLogProb) {
+    tm = blockIdx.x / p.n_splits;
+    tn = (blockIdx.x % p.n_splits) * p.tiles_per_split + i;
+    return i < p.tiles_per_split && tn < p.tiles_n;
+  } else {
+    const int t = blockIdx.x + i * gridDim.x;
+    if (t >= p.tiles_m * p.tiles_n) return false;
+    tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    return true;
+  }
+}
+
+template <int BN, bool BF16, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
   using S = GemmSmem<BN>;
@@ -71,7 +99,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.tiles_m * p.tiles_n;
   const int k_iters = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -103,9 +130,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int ti = 0; ok; ++ti) {
         int tm, tn;
-        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        if (!next_tile<MODE>(p, ti, tm, tn)) break;
         const int m0 = tm * BM, n0 = tn * BN;
         for (int k = 0; k < k_iters; ++k) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
@@ -137,7 +164,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int ti = 0; ok; ++ti) {
+        int tm_, tn_;
+        if (!next_tile<MODE>(p, ti, tm_, tn_)) break;
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.err)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -170,10 +199,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     const int lane_grp = warp & 3;  // TMEM lanes [32*lane_grp, +32) are visible to this warp
     int acc = 0;
     uint32_t acc_ph = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    // MODE 1 running statistics of this thread's row over the CTA's column range
+    float st_m = -1e30f, st_s = 0.f, st_u = 0.f, st_t = -INFINITY;
+    int st_row = -1;
+    if constexpr (MODE == kEpiLogProb) st_row = (blockIdx.x / p.n_splits) * BM + lane_grp * 32 + lane;
+    for (int ti = 0;; ++ti) {
       int tm, tn;
-      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      if (!next_tile<MODE>(p, ti, tm, tn)) break;
       const int row = tm * BM + lane_grp * 32 + lane;
+      st_row = row;
       const int n0 = tn * BN;
       if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.err)) break;
       tc_fence_after();
@@ -184,6 +218,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_wait_ld();
         const int col = n0 + c * 32;
+        if constexpr (MODE == kEpiLogProb) {
+          if (row < p.M && col < p.N) {
+            const float l2e = 1.4426950408889634f;
+            const long long tgt = p.targets[row] - p.vocab_start;
+            float mx = st_m;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float z = (col + i < p.N) ? __uint_as_float(r[i]) * p.inv_temp : -1e30f;
+              r[i] = __float_as_uint(z);
+              mx = fmaxf(mx, z);
+            }
+            const float alpha = exp2f((st_m - mx) * l2e);
+            st_s *= alpha;
+            st_u *= alpha;
+            st_m = mx;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float z = __uint_as_float(r[i]);
+              const float e = exp2f((z - mx) * l2e);
+              st_s += e;
+              st_u += (col + i < p.N) ? e * z : 0.f;
+              if (tgt == col + i) st_t = z;
+            }
+          }
+          continue;
+        }
+        if constexpr (MODE == kEpiDLogits) {
+          if (row < p.M && col < p.N) {
+            const float l2e = 1.4426950408889634f;
+            const long long tgt = p.targets[row] - p.vocab_start;
+            const float logz = p.row_stats[2 * row], ez = p.row_stats[2 * row + 1];
+            const float glp = p.g_lp[row];
+            const float gen = p.g_ent ? p.g_ent[row] : 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float z = __uint_as_float(r[i]) * p.inv_temp;
+              const float pr = exp2f((z - logz) * l2e);
+              float g = -pr * glp + pr * (ez - z) * gen;
+              if (tgt == col + i) g += glp;
+              r[i] = __float_as_uint(g * p.inv_temp);
+            }
+          }
+        }
         if (row < p.M && col < p.N) {
           float v[32];
 #pragma unroll
@@ -258,6 +335,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
     }
+    if constexpr (MODE == kEpiLogProb) {
+      if (st_row >= 0 && st_row < p.M) {
+        float4 o = make_float4(st_m, st_s, st_u, st_t);
+        reinterpret_cast<float4*>(p.partials)[static_cast<size_t>(st_row) * p.n_splits + (blockIdx.x % p.n_splits)] = o;
+      }
+    }
   }
 
   // ------------------------------------------------------------------ teardown
@@ -279,11 +362,11 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, bool mn_major, in
   return encode_tma_2d_bf16(map, ptr, rows_op, K, ld, 64, BK);
 }
 
-template <int BN, bool BF16>
+template <int BN, bool BF16, int MODE = kEpiStore>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
   using S = GemmSmem<BN>;
   static bool attr_set = false;
-  auto kern = gemm_kernel<BN, BF16>;
+  auto kern = gemm_kernel<BN, BF16, MODE>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -292,7 +375,11 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cu
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < num_sms() ? tiles : num_sms();
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (MODE == kEpiLogProb) {
+    p.tiles_per_split = (p.tiles_n + p.n_splits - 1) / p.n_splits;
+    grid = p.tiles_m * p.n_splits;
+  }
   kern<<<grid, GEMM_THREADS, S::kTotal, stream>>>(ta, tb, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -338,4 +425,57 @@ extern "C" int rb_gemm(const void* A, const void* B, void* C, const void* bias, 
     default: return -3;
   }
 #undef RB_LAUNCH
+}
+
+
+// Number of column splits the log-prob kernel uses for M rows (callers size `partials` with it).
+extern "C" int rb_lm_head_splits(int M, int N) {
+  using namespace rb;
+  const int tm = (M + BM - 1) / BM;
+  const int tn = (N + 255) / 256;
+  int splits = (num_sms() + tm - 1) / tm;
+  if (splits > tn) splits = tn;
+  if (splits < 1) splits = 1;
+  const int per = (tn + splits - 1) / splits;
+  return (tn + per - 1) / per;  // every split owns at least one column tile
+}
+
+// Fused LM head, forward: partials[M][splits][4] of the temperature-scaled logits h W^T
+// (never written to memory).  h [M][K], W [N][K] (bf16, K-major).
+extern "C" int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N,
+                                  int K, int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err,
+                                  cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0) return 0;
+  if ((ldh % 8) || (ldw % 8)) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = N; p.err = err;
+  p.lbo_a = p.lbo_b = BK * 128; p.sbo_a = p.sbo_b = 1024;
+  p.targets = targets; p.vocab_start = vocab_start; p.inv_temp = inv_temp; p.n_splits = n_splits; p.partials = partials;
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, h, false, M, K, ldh, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, W, false, N, K, ldw, 256);
+  if (rc) return rc;
+  return launch<256, true, kEpiLogProb>(ta, tb, p, stream);
+}
+
+// Fused LM head, backward helper: dlogits[M][N] (bf16) from recomputed logits.
+extern "C" int rb_lm_head_dlogits(const void* h, const void* W, const long long* targets, const float* row_stats,
+                                  const float* g_lp, const float* g_ent, void* dlogits, int M, int N, int K, int ldh,
+                                  int ldw, int ldd, int vocab_start, float inv_temp, int* err, cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0) return 0;
+  if ((ldh % 8) || (ldw % 8)) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldd; p.C = dlogits; p.err = err;
+  p.lbo_a = p.lbo_b = BK * 128; p.sbo_a = p.sbo_b = 1024;
+  p.targets = targets; p.vocab_start = vocab_start; p.inv_temp = inv_temp;
+  p.row_stats = row_stats; p.g_lp = g_lp; p.g_ent = g_ent;
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, h, false, M, K, ldh, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, W, false, N, K, ldw, 256);
+  if (rc) return rc;
+  return launch<256, true, kEpiDLogits>(ta, tb, p, stream);
 }

@@ -18,6 +18,16 @@ inline int num_sms() {
   return n;
 }
 
+// Tensor-map encoding is a driver call and needs a current context on the calling thread.
+// Worker threads (e.g. an autograd engine thread) may not have touched the runtime yet.
+inline void ensure_context() {
+  static thread_local bool done = false;
+  if (!done) {
+    cudaFree(nullptr);
+    done = true;
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -38,6 +48,7 @@ inline EncodeTiledFn encode_fn() {
 // row pitch `ld` elements.  Box = box_inner x box_outer, 128-byte swizzle, zero fill out of bounds.
 inline int encode_tma_2d_16bit(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
                                uint32_t box_inner, uint32_t box_outer, bool is_bf16 = true, bool swizzle128 = true) {
+  ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
   cuuint64_t dims[2] = {inner, outer};
@@ -59,6 +70,7 @@ inline int encode_tma_2d_bf16(CUtensorMap* map, const void* ptr, uint64_t inner,
 inline int encode_tma_3d_16bit(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0, uint32_t b1, uint32_t b2,
                                bool is_bf16 = true) {
+  ensure_context();
   EncodeTiledFn fn = encode_fn();
   if (!fn) return -10;
   cuuint64_t dims[3] = {d0, d1, d2};

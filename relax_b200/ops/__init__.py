@@ -106,3 +106,25 @@ def blockwise_dequant_fp8(q, scale_inv, block=128, dtype=None):
     if _use_cuda(q):
         return _cuda().blockwise_dequant_fp8(q, scale_inv, block, dtype)
     return ref.blockwise_dequant_fp8(q, scale_inv, block, dtype)
+
+
+def dgrad(dy, w):
+    """dy[M,N] @ w[N,K] (input gradient of ``linear``)."""
+    if _use_cuda(dy):
+        return _cuda().matmul_nn(dy.contiguous(), w)
+    return dy @ w
+
+
+def wgrad(dy, x, w=None):
+    """dy[M,N]^T @ x[M,K] (weight gradient of ``linear``).  When ``w`` carries an fp32
+    ``main_grad`` buffer the CUDA path accumulates into it and returns ``None``."""
+    if _use_cuda(dy):
+        c = _cuda()
+        mg = getattr(w, "main_grad", None) if w is not None else None
+        import torch
+
+        if mg is not None and mg.dtype == torch.float32 and mg.shape == w.shape:
+            c.matmul_tn(dy.contiguous(), x.contiguous(), out=mg, accumulate=True)
+            return None
+        return c.matmul_tn(dy.contiguous(), x.contiguous())
+    return dy.t() @ x

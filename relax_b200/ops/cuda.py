@@ -27,6 +27,8 @@ def _load():
     spec = importlib.util.spec_from_file_location("relax_b200._C", _SO)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
+    if os.environ.get("RELAX_B200_CRASH_TRACE", "0") == "1":
+        mod.install_crash_handler()
     _C = mod
     return mod
 
@@ -149,7 +151,13 @@ class _Linear(torch.autograd.Function):
         dx = matmul_nn(dy, w) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            dw = matmul_tn(dy, x)
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32 and mg.shape == w.shape and mg.stride(-1) == 1:
+                # weight-gradient GEMM accumulates straight into the fp32 gradient buffer of the
+                # distributed optimizer: no temporary, no separate add pass
+                matmul_tn(dy, x, out=mg, accumulate=True)
+            else:
+                dw = matmul_tn(dy, x)
         db = dy.sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
         return dx, dw, db
 
@@ -401,3 +409,206 @@ def build_copy_table(blocks, trainer_params: dict, rollout_weights) -> CopyTable
 
 def run_copy_table(t: CopyTable):
     _load().copy_table(t.table, t.n_desc, t.chunk_start, t.total_chunks, t.chunk_rows, t.elem_size)
+
+
+# --------------------------------------------------------------------------- flash attention (training / prefill)
+
+
+def _tok_head_view(t):
+    """[T, H, 128] with unit inner stride and 16-byte aligned outer strides, else a contiguous copy."""
+    if t.stride(2) != 1 or t.stride(0) % 8 or t.stride(1) % 8 or t.data_ptr() % 16:
+        t = t.contiguous()
+    return t
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, causal, scale, max_q_blocks, max_kv_blocks):
+        q, k, v = _tok_head_view(q), _tok_head_view(k), _tok_head_view(v)
+        Tq, Hq, D = q.shape
+        o = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
+        lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+        _load().fa_fwd(q, k, v, o, lse, cu_q, cu_k, max_q_blocks, causal, scale, err_flag(q.device))
+        ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k)
+        ctx.causal, ctx.scale, ctx.max_kv_blocks = causal, scale, max_kv_blocks
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse, cu_q, cu_k = ctx.saved_tensors
+        q, k, v, do = q.contiguous(), k.contiguous(), v.contiguous(), do.contiguous()
+        Tq, Hq, D = q.shape
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+        dq_acc = torch.empty(Tq, Hq, D, dtype=torch.float32, device=q.device)
+        _load().fa_bwd(q, k, v, o, do, lse, dq, dk, dv, delta, dq_acc, cu_q, cu_k, ctx.max_kv_blocks, ctx.causal,
+                       ctx.scale, err_flag(q.device))
+        return dq, dk, dv, None, None, None, None, None, None
+
+
+def attention_varlen(q, k, v, cu_seqlens, causal=True, scale=None, cu_seqlens_k=None, max_seqlen=None):
+    """Packed varlen attention; q [Tq, Hq, 128], k/v [Tk, Hkv, 128] bf16."""
+    if q.dtype != torch.bfloat16 or q.shape[-1] != 128:
+        raise NotImplementedError("the sm_100a attention kernel handles bf16 with head_dim 128")
+    cu_q = cu_seqlens.to(torch.int32)
+    cu_k = cu_q if cu_seqlens_k is None else cu_seqlens_k.to(torch.int32)
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    nseq = cu_q.numel() - 1
+    # upper bounds of the tile counts (no host sync): every sequence adds at most one partial tile
+    max_q_blocks = (q.shape[0] + 127) // 128 + nseq
+    max_kv_blocks = (k.shape[0] + 127) // 128 + nseq
+    return _FlashAttn.apply(q, k, v, cu_q, cu_k, bool(causal), float(scale), max_q_blocks, max_kv_blocks)
+
+
+# --------------------------------------------------------------------------- rollout kernels
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale=None, max_ctx=None):
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if max_ctx is None:
+        max_ctx = block_tables.shape[1] * k_cache.shape[1]
+    C = _load()
+    splits = C.decode_attn_splits(B, Hkv, max_ctx)
+    out = torch.empty_like(q)
+    po = pm = None
+    if splits > 1:
+        po = torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device)
+        pm = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
+    C.decode_attn(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(),
+                  context_lens.to(torch.int32).contiguous(), out, po, pm, max_ctx, scale, splits)
+    return out
+
+
+def sample(logits, temperature, top_k, top_p, uniform):
+    logits = logits.float()
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    B, V = logits.shape
+    tok = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    _load().sample(logits, temperature.float().contiguous(), top_k.to(torch.int64).contiguous(),
+                   top_p.float().contiguous(), uniform.float().contiguous(), tok, lp, V)
+    return tok, lp
+
+
+class _TopKRouter(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, norm):
+        logits = logits.float().contiguous()
+        T, E = logits.shape
+        w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+        idx = torch.empty(T, k, dtype=torch.int64, device=logits.device)
+        probs = torch.empty(T, E, dtype=torch.float32, device=logits.device)
+        _load().topk_router(logits, k, norm, w, idx, probs)
+        ctx.save_for_backward(probs, idx, w)
+        ctx.norm = norm
+        ctx.mark_non_differentiable(idx)
+        return w, idx, probs
+
+    @staticmethod
+    def backward(ctx, dw, _didx, dprobs):
+        probs, idx, w = ctx.saved_tensors
+        # gradient w.r.t. probs from the (optionally renormalised) selected weights
+        gp = torch.zeros_like(probs) if dprobs is None else dprobs.clone()
+        if dw is not None:
+            if ctx.norm:
+                sel = probs.gather(-1, idx)
+                ssum = sel.sum(-1, keepdim=True)
+                dsel = (dw - (dw * w).sum(-1, keepdim=True)) / ssum
+            else:
+                dsel = dw
+            gp.scatter_add_(-1, idx, dsel)
+        # softmax backward
+        dlogits = probs * (gp - (gp * probs).sum(-1, keepdim=True))
+        return dlogits, None, None
+
+
+def topk_router(logits, top_k, norm_topk_prob=True):
+    return _TopKRouter.apply(logits, int(top_k), bool(norm_topk_prob))
+
+
+# --------------------------------------------------------------------------- fused LM head + log-prob / entropy
+
+
+class _FusedLMHead(torch.autograd.Function):
+    CHUNK = 4096
+
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature):
+        import torch.distributed as dist
+
+        C = _load()
+        h = hidden if (hidden.stride(1) == 1 and hidden.stride(0) % 8 == 0) else hidden.contiguous()
+        w = weight if (weight.stride(1) == 1 and weight.stride(0) % 8 == 0) else weight.contiguous()
+        T, V = h.shape[0], w.shape[0]
+        inv_t = 1.0 / float(temperature)
+        tp = tp_group is not None and dist.is_initialized() and dist.get_world_size(tp_group) > 1
+        if T == 0:
+            z = torch.zeros(0, dtype=torch.float32, device=h.device)
+            ctx.save_for_backward(h, w, targets, z, z)
+            ctx.meta = (tp_group, vocab_start, inv_t, with_entropy, weight)
+            return z, z.clone()
+        splits = C.lm_head_splits(T, V)
+        part = torch.empty(T, splits, 4, dtype=torch.float32, device=h.device)
+        C.lm_head_logprob(h, w, targets.contiguous(), part, vocab_start, inv_t, splits, err_flag(h.device))
+        m = part[..., 0]
+        gm = m.max(1).values
+        if tp:
+            dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=tp_group)
+        sc = torch.exp(m - gm[:, None])
+        zt = part[..., 3].max(1).values
+        found = torch.isfinite(zt)
+        acc = torch.stack([(part[..., 1] * sc).sum(1), (part[..., 2] * sc).sum(1), torch.where(found, zt, torch.zeros_like(zt))])
+        if tp:
+            dist.all_reduce(acc, group=tp_group)
+        s, u, zt = acc[0], acc[1], acc[2]
+        logz = gm + torch.log(s)
+        ez = u / s
+        lp = zt - logz
+        ent = logz - ez if with_entropy else torch.zeros_like(lp)
+        ctx.save_for_backward(h, w, targets, logz, ez)
+        ctx.meta = (tp_group, vocab_start, inv_t, with_entropy, weight)
+        return lp, ent
+
+    @staticmethod
+    def backward(ctx, g_lp, g_ent):
+        h, w, targets, logz, ez = ctx.saved_tensors
+        tp_group, vocab_start, inv_t, with_entropy, weight = ctx.meta
+        C = _load()
+        T, H = h.shape
+        V = w.shape[0]
+        dh = torch.empty_like(h)
+        main_grad = getattr(weight, "main_grad", None)
+        direct = main_grad is not None and main_grad.dtype == torch.float32 and main_grad.shape == weight.shape \
+            and w.data_ptr() == weight.data_ptr()
+        dw32 = main_grad if direct else torch.zeros(V, H, dtype=torch.float32, device=h.device)
+        if main_grad is not None and not direct and main_grad.dtype == torch.float32 and w.shape[0] < weight.shape[0] \
+                and w.data_ptr() == weight.data_ptr():
+            dw32, direct = main_grad[:V], True   # vocabulary padding rows sliced off by the caller
+        stats = torch.stack([logz, ez], 1).contiguous()
+        g_lp = (g_lp if g_lp is not None else torch.zeros_like(logz)).float().contiguous()
+        g_en = g_ent.float().contiguous() if (with_entropy and g_ent is not None) else None
+        tg = targets.contiguous()
+        ck = _FusedLMHead.CHUNK
+        buf = torch.empty(min(ck, T), V, dtype=h.dtype, device=h.device)
+        for s in range(0, T, ck):
+            e = min(T, s + ck)
+            d = buf[: e - s]
+            C.lm_head_dlogits(h[s:e], w, tg[s:e], stats[s:e], g_lp[s:e], None if g_en is None else g_en[s:e], d,
+                              vocab_start, inv_t, err_flag(h.device))
+            matmul_nn(d, w, out=dh[s:e])
+            matmul_tn(d, h[s:e], out=dw32, accumulate=True)
+        dw = None if direct else dw32.to(weight.dtype)
+        if dw is not None and dw.shape != weight.shape:
+            full = torch.zeros_like(weight)
+            full[: dw.shape[0]] = dw
+            dw = full
+        return dh, dw, None, None, None, None, None
+
+
+def fused_lm_head_logprob(hidden, weight, targets, tp_group=None, vocab_start=0, with_entropy=True, temperature=1.0):
+    if hidden.dtype != torch.bfloat16:
+        raise TypeError("fused LM head expects bf16 hidden states")
+    return _FusedLMHead.apply(hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature)

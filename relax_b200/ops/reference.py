@@ -140,21 +140,24 @@ def sample(logits, temperature, top_k, top_p, uniform):
     logp_full = torch.log_softmax(z, -1)
     greedy = temperature <= 0
     V = z.shape[-1]
+    # kept set: the k largest, then the shortest prefix (descending order) of those whose
+    # renormalised mass reaches top_p
     sorted_z, idx = torch.sort(z, -1, descending=True)
     ranks = torch.arange(V, device=z.device)[None, :]
     k = torch.where(top_k > 0, top_k, torch.full_like(top_k, V))
     keep = ranks < k[:, None]
-    probs = torch.softmax(sorted_z, -1)
+    probs = torch.softmax(sorted_z.masked_fill(~keep, float("-inf")), -1)
     csum = torch.cumsum(probs, -1)
     keep &= (csum - probs) < top_p.float()[:, None]
-    probs = torch.where(keep, probs, torch.zeros_like(probs))
-    probs = probs / probs.sum(-1, keepdim=True)
-    c = torch.cumsum(probs, -1)
-    pick = (c < uniform.float()[:, None]).sum(-1).clamp_max(V - 1)
-    # never pick a filtered slot because of rounding at the end of the CDF
-    last_kept = keep.float().cumsum(-1).argmax(-1)
-    pick = torch.minimum(pick, last_kept)
-    tok = idx.gather(-1, pick[:, None])[:, 0]
+    mask = torch.zeros_like(keep).scatter(-1, idx, keep)
+    # inverse CDF in vocabulary order over the kept entries
+    e = torch.exp(z - z.max(-1, keepdim=True).values) * mask
+    c = torch.cumsum(e.double(), -1)
+    target = uniform.double()[:, None] * c[:, -1:]
+    pick = (c <= target).sum(-1).clamp_max(V - 1)
+    # rounding at the end of the CDF must not select a filtered slot
+    last_kept = (mask * torch.arange(V, device=z.device)[None, :]).amax(-1)
+    tok = torch.minimum(pick, last_kept)
     tok = torch.where(greedy, z.argmax(-1), tok)
     return tok, logp_full.gather(-1, tok[:, None])[:, 0]
 

@@ -67,8 +67,8 @@ class _AGLinear(torch.autograd.Function):
         g = ctx.g
         dy = dy.contiguous()
         xf = _ag(x, g)  # re-gather instead of keeping T*tp activations alive
-        dx = _rs(ops.linear(dy, w.t()), g)
-        dw = ops.linear(dy.t(), xf.t())
+        dx = _rs(ops.dgrad(dy, w), g)
+        dw = ops.wgrad(dy, xf, w)
         return dx, dw, None
 
 
@@ -90,8 +90,8 @@ class _LinearRS(torch.autograd.Function):
         x, w = ctx.saved_tensors
         g = ctx.g
         dyf = _ag(dy.contiguous(), g)
-        dx = ops.linear(dyf, w.t())
-        dw = ops.linear(dyf.t(), x.t())
+        dx = ops.dgrad(dyf, w)
+        dw = ops.wgrad(dyf, x, w)
         return dx, dw, None
 
 

@@ -64,8 +64,14 @@ def _split_fp32(x32: torch.Tensor, out_dtype):
     exact reconstruction for bf16."""
     hi = x32.to(out_dtype)
     hi_bits = hi.view(torch.int16).to(torch.int32) << 16
-    rem = (x32.view(torch.int32) - hi_bits).to(torch.int16)
-    return hi, rem
+    rem = x32.view(torch.int32) - hi_bits
+    # an exact tie that rounded towards the smaller bit pattern leaves +32768, which
+    # does not fit int16: take the other neighbour instead (remainder -32768)
+    up = rem == 32768
+    hi_bits = torch.where(up, hi_bits + 65536, hi_bits)
+    rem = torch.where(up, torch.full_like(rem, -32768), rem)
+    hi = (hi_bits >> 16).to(torch.int16).view(out_dtype)
+    return hi, rem.to(torch.int16)
 
 
 def _join_fp32(hi: torch.Tensor, rem: torch.Tensor):

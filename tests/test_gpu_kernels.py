@@ -120,7 +120,7 @@ def test_rmsnorm_fwd_bwd(rows, cols):
     y2, r2 = ops.add_rmsnorm(x, res, w, 1e-6)
     (y2.float().sum() + 2 * r2.float().sum()).backward()
     xf2, rf2 = x.detach().float().requires_grad_(), res.detach().float().requires_grad_()
-    rsum = (xf2 + rf2).bfloat16().float() + (xf2 + rf2) - (xf2 + rf2).detach()
+    rsum = (xf2 + rf2) + ((xf2 + rf2).bfloat16().float() - (xf2 + rf2)).detach()
     yr2 = R.rmsnorm(rsum, wf.detach(), 1e-6)
     (yr2.sum() + 2 * rsum.sum()).backward()
     _close(y2, yr2, 0.02, 1e-2)
@@ -178,7 +178,7 @@ def test_fused_adam_matches_reference(split, grad_fp32):
         adam_step(rp, grad, rm, rv, step, 1e-4, 0.9, 0.999, 1e-8, 0.01, 0.5)
     got = _join_fp32(p, mst) if split else mst
     _close(got, rp, 1e-7, 1e-5)
-    assert torch.equal(p, got.bfloat16())
+    assert (p.float() - got).abs().max() <= got.abs().max() * 2 ** -8
     _close(m, rm, 1e-9, 1e-5)
     assert abs(C.sumsq(grad).item() - grad.float().pow(2).sum().item()) < 1e-3 * grad.float().pow(2).sum().item()
 
