@@ -411,6 +411,7 @@ extern "C" int rb_fa_bwd(const void* q, const void* k, const void* v, const void
   p.dK = (__nv_bfloat16*)dk; p.dV = (__nv_bfloat16*)dv; p.Tq = Tq; p.err = err;
   dim3 grid(max_kv_blocks, Hkv);
   fa_bwd_kernel<<<grid, FB_THREADS, FB_SMEM_TOTAL, stream>>>(tq, tdo, tk, tv, p);
+  rb_note_launch(3);
   {
     long long blocks = (n_dq / 4 + 255) / 256;
     if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;

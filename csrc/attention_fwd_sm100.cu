@@ -327,5 +327,6 @@ extern "C" int rb_fa_fwd(const void* q, const void* k, const void* v, void* o, f
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.lse = lse; p.Tq = Tq; p.err = err;
   dim3 grid(max_q_blocks, Hq);
   fa_fwd_kernel<<<grid, FA_THREADS, FA_SMEM_TOTAL, stream>>>(tq, tk, tv, p);
+  rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -6,6 +6,7 @@
 #include <torch/extension.h>
 
 #include "api.h"
+#include "host_utils.h"
 
 #include <execinfo.h>
 #include <signal.h>
@@ -156,6 +157,8 @@ void fp8_block_dequant(torch::Tensor q, torch::Tensor scale, torch::Tensor out, 
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("install_crash_handler", &install_crash_handler);
+  m.def("launch_count", []() { return (int64_t)rb_launch_count(); });
+  m.def("reset_launch_count", []() { rb_reset_launch_count(); });
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_parts", &rmsnorm_bwd_parts);

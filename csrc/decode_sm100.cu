@@ -382,6 +382,7 @@ extern "C" int rb_decode_attn(const void* q, const void* kc, const void* vc, con
   }
 #undef RB_DA
   if (splits > 1) decode_attn_combine_kernel<<<B * Hq, DA_D, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -389,6 +390,7 @@ extern "C" int rb_sample(const float* logits, int B, int V, int ld, const float*
                          const float* top_p, const float* uniform, long long* tok, float* logp, cudaStream_t st) {
   if (B == 0) return 0;
   sample_kernel<<<B, SM_THREADS, 0, st>>>(logits, V, ld, temperature, top_k, top_p, uniform, tok, logp);
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -399,5 +401,6 @@ extern "C" int rb_topk_router(const float* logits, int T, int E, int K, int norm
   int blocks = (T + 7) / 8;
   if (blocks > num_sms() * 8) blocks = num_sms() * 8;
   topk_router_kernel<<<blocks, 256, 0, st>>>(logits, E, K, norm, w, idx, probs, T);
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }

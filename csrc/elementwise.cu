@@ -457,6 +457,12 @@ static inline int grid_for(long long work_items, int threads) {
 
 using namespace rb;
 
+#include <atomic>
+static std::atomic<long long> g_launches{0};
+extern "C" void rb_note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+extern "C" long long rb_launch_count() { return g_launches.load(std::memory_order_relaxed); }
+extern "C" void rb_reset_launch_count() { g_launches.store(0, std::memory_order_relaxed); }
+
 #define RB_DISPATCH(dtype, ...)                                       \
   switch (dtype) {                                                    \
     case 0: { using T = __nv_bfloat16; __VA_ARGS__; break; }          \
@@ -484,6 +490,7 @@ extern "C" int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
       else rmsnorm_fwd_kernel<T, 256, false><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
     }
   });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -507,6 +514,7 @@ extern "C" int rb_rmsnorm_bwd(const void* x, const void* w, const void* dy, void
     else rmsnorm_bwd_kernel<T, 256><<<grid, 256, shm, st>>>((const T*)x, (const T*)w, (const T*)dy, (T*)dx, scratch, rows, cols, eps);
     reduce_partials_kernel<T><<<(cols + 255) / 256, 256, 0, st>>>(scratch, (T*)dw, grid, cols);
   });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -518,6 +526,7 @@ extern "C" int rb_rope(const void* x, void* y, const float* cos_t, const float* 
   if ((D / 2) % (16 / esz)) return -2;
   const int grid = grid_for(pairs / (16 / esz), 256);
   RB_DISPATCH(dtype, { rope_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)y, cos_t, sin_t, pairs, H, D, backward ? -1.f : 1.f); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -527,6 +536,7 @@ extern "C" int rb_swiglu_fwd(const void* in, void* out, long long rows, int F, i
   if (F % (16 / esz)) return -2;
   const int grid = grid_for(rows * F / (16 / esz), 256);
   RB_DISPATCH(dtype, { swiglu_fwd_kernel<T><<<grid, 256, 0, st>>>((const T*)in, (T*)out, rows, F); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 extern "C" int rb_swiglu_bwd(const void* in, const void* dout, void* din, long long rows, int F, int dtype, cudaStream_t st) {
@@ -535,6 +545,7 @@ extern "C" int rb_swiglu_bwd(const void* in, const void* dout, void* din, long l
   if (F % (16 / esz)) return -2;
   const int grid = grid_for(rows * F / (16 / esz), 256);
   RB_DISPATCH(dtype, { swiglu_bwd_kernel<T><<<grid, 256, 0, st>>>((const T*)in, (const T*)dout, (T*)din, rows, F); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -552,6 +563,7 @@ extern "C" int rb_adam(void* p, void* master, const void* g, float* m, float* v,
     if (split) adam_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(pp, master, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
     else adam_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(pp, master, (const __nv_bfloat16*)g, m, v, n, lr, b1, b2, eps, wd, gscale, bc1, bc2);
   }
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -559,6 +571,7 @@ extern "C" int rb_sumsq(const void* g, long long n, float* out, int dtype, cudaS
   if (n == 0) return 0;
   const int grid = grid_for(n, 256 * 8);
   RB_DISPATCH(dtype, { sumsq_kernel<T><<<grid, 256, 0, st>>>((const T*)g, n, out); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -569,6 +582,7 @@ extern "C" int rb_copy_table(const void* table, int n_desc, const int* chunk_sta
   if (elem_size == 2) copy_table_kernel<uint16_t><<<grid, 256, 0, st>>>((const CopyDesc*)table, n_desc, chunk_start, total_chunks, chunk_rows);
   else if (elem_size == 4) copy_table_kernel<uint32_t><<<grid, 256, 0, st>>>((const CopyDesc*)table, n_desc, chunk_start, total_chunks, chunk_rows);
   else return -1;
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -579,6 +593,7 @@ extern "C" int rb_kv_scatter(const void* k, const void* v, void* kc, void* vc, c
   if (row_elems % (16 / esz) || k_stride % (16 / esz) || v_stride % (16 / esz)) return -2;
   const int grid = grid_for((long long)tokens * row_elems / (16 / esz), 256);
   RB_DISPATCH(dtype, { kv_scatter_kernel<T><<<grid, 256, 0, st>>>((const T*)k, (const T*)v, (T*)kc, (T*)vc, slots, tokens, row_elems, k_stride, v_stride); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -588,6 +603,7 @@ extern "C" int rb_int4_fake_quant(const void* x, void* out, void* scale, void* z
   if (groups == 0) return 0;
   const int grid = grid_for(groups, 8);
   RB_DISPATCH(dtype, { int4_fake_quant_kernel<T><<<grid, 256, 0, st>>>((const T*)x, (T*)out, (T*)scale, (T*)zero, M, N, bm, bn, sym); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 
@@ -596,6 +612,7 @@ extern "C" int rb_fp8_block_cast(const void* w, void* q, float* scale, int M, in
   const int blocks = ((M + block - 1) / block) * ((N + block - 1) / block);
   if (blocks == 0) return 0;
   RB_DISPATCH(dtype, { fp8_block_cast_kernel<T><<<blocks, 256, 0, st>>>((const T*)w, (__nv_fp8_e4m3*)q, scale, M, N, block, ue8m0); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }
 extern "C" int rb_fp8_block_dequant(const void* q, const float* scale, void* out, int M, int N, int block, int dtype,
@@ -603,5 +620,6 @@ extern "C" int rb_fp8_block_dequant(const void* q, const float* scale, void* out
   if ((long long)M * N == 0) return 0;
   const int grid = grid_for((long long)M * N, 256);
   RB_DISPATCH(dtype, { fp8_block_dequant_kernel<T><<<grid, 256, 0, st>>>((const __nv_fp8_e4m3*)q, scale, (T*)out, M, N, block); });
+  rb_note_launch(1);
   return (int)cudaGetLastError();
 }

@@ -381,6 +381,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cu
     grid = p.tiles_m * p.n_splits;
   }
   kern<<<grid, GEMM_THREADS, S::kTotal, stream>>>(ta, tb, p);
+  rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -5,6 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+extern "C" void rb_note_launch(int n);
+extern "C" long long rb_launch_count();
+extern "C" void rb_reset_launch_count();
+
 namespace rb {
 
 inline int num_sms() {

@@ -108,6 +108,17 @@ def blockwise_dequant_fp8(q, scale_inv, block=128, dtype=None):
     return ref.blockwise_dequant_fp8(q, scale_inv, block, dtype)
 
 
+def kv_cache_write(k, v, k_cache, v_cache, slots):
+    """Scatter new K/V rows ``[T, Hkv, D]`` into a paged cache ``[blocks, block_size, Hkv, D]``
+    at flat slot indices ``slots[T]`` (``block * block_size + offset``)."""
+    if _use_cuda(k):
+        return _cuda().kv_scatter(k, v, k_cache, v_cache, slots)
+    kc = k_cache.view(-1, k.shape[1], k.shape[2])
+    vc = v_cache.view(-1, v.shape[1], v.shape[2])
+    kc[slots] = k
+    vc[slots] = v
+
+
 def dgrad(dy, w):
     """dy[M,N] @ w[N,K] (input gradient of ``linear``)."""
     if _use_cuda(dy):

@@ -612,3 +612,12 @@ def fused_lm_head_logprob(hidden, weight, targets, tp_group=None, vocab_start=0,
     if hidden.dtype != torch.bfloat16:
         raise TypeError("fused LM head expects bf16 hidden states")
     return _FusedLMHead.apply(hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature)
+
+
+def launch_count() -> int:
+    """Number of kernels of this extension launched since the last reset (all threads)."""
+    return int(_load().launch_count())
+
+
+def reset_launch_count():
+    _load().reset_launch_count()

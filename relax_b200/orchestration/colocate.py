@@ -59,6 +59,10 @@ class ColocateConfig:
     rollout_seed: int = 42
     offload_train: bool = False
     offload_rollout: bool = True
+    # also free the rollout parameter buffer and the trainer's gradient buffer while the other
+    # role runs (they are rewritten by the weight sync / zeroed before backward anyway)
+    release_rollout_weights: bool = False
+    pinned_prompts: bool = False
     num_prompts: int = 1 << 14
 
 
@@ -91,6 +95,10 @@ class ColocatedGRPO:
         need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
         cfg.train.n_samples_per_prompt = cfg.train.n_samples_per_prompt
         self.actor = TrainActor(cfg.model, cfg.train, self.ps, device=device, seed=cfg.seed, with_reference=need_ref)
+        if cfg.release_rollout_weights and self.actor.optimizer is not None:
+            self.actor.optimizer.release_grads()   # before the engine allocates its weights and KV cache
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
         self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
                                     num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
                                     max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
@@ -159,17 +167,25 @@ class ColocatedGRPO:
             meta = self.queue.get_meta(list(batch.keys()), None, part, "actor")
             data = self.queue.get_data(meta)
         with self.timer.span("train"):
+            if cfg.release_rollout_weights:
+                self.engine.release_memory_occupation(("weights",))
+                self.actor.optimizer.allocate_grads()
             if cfg.offload_train:
                 self.actor.wake_up()
             m = self.actor.train(rid, data)
             self.actor.after_train()
             if cfg.offload_train:
                 self.actor.sleep()
+            if cfg.release_rollout_weights:
+                self.actor.optimizer.release_grads()
+                self.engine.resume_memory_occupation(("weights",))
         self.queue.clear_partition(part)
         with self.timer.span("weight_sync"):
             sync_ms = self.sync_weights()
         n_resp = sum(batch["response_lengths"])
         n_tok = sum(batch["total_lengths"])
+        st = self.engine.stats
+        m.update(h2d_bytes=st.pop("h2d_bytes", 0), d2h_bytes=st.pop("d2h_bytes", 0) + 8 * len(m))
         m.update(weight_sync_ms=sync_ms, response_tokens_local=n_resp, total_tokens_local=n_tok,
                  raw_reward_mean=float(sum(batch["raw_reward"]) / max(1, len(batch["raw_reward"]))),
                  step_time=time.perf_counter() - t_all)

@@ -254,6 +254,36 @@ class RolloutEngine:
                 r.t_done = time.perf_counter()
         return done
 
+    def _stage(self, arrays):
+        """Host lists -> device tensors through ONE pinned staging buffer and ONE
+        asynchronous host-to-device copy.  ``arrays`` is a list of ``(list, dtype)``."""
+        if self.device.type != "cuda":
+            return [torch.tensor(a, dtype=dt) for a, dt in arrays]
+        cpu = [torch.tensor(a, dtype=dt) for a, dt in arrays]
+        offs, n = [], 0
+        for t in cpu:
+            offs.append(n)
+            n += (t.numel() * t.element_size() + 15) // 16 * 16
+        if getattr(self, "_pin", None) is None or self._pin.numel() < n:
+            cap = max(n * 2, 1 << 16)
+            self._pin = torch.empty(cap, dtype=torch.uint8, pin_memory=True)
+            self._dev_stage = [torch.empty(cap, dtype=torch.uint8, device=self.device) for _ in range(2)]
+            self._stage_flip = 0
+        self._stage_flip ^= 1
+        dbuf = self._dev_stage[self._stage_flip]
+        for t, o in zip(cpu, offs):
+            nb = t.numel() * t.element_size()
+            if nb:
+                self._pin[o:o + nb].copy_(t.view(-1).view(torch.uint8))
+        if n:
+            dbuf[:n].copy_(self._pin[:n], non_blocking=True)
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + n
+        out = []
+        for t, o in zip(cpu, offs):
+            nb = t.numel() * t.element_size()
+            out.append(dbuf[o:o + nb].view(t.dtype).view(t.shape))
+        return out
+
     def _prefill(self, reqs: list[Request]):
         leaders = [r for r in reqs if r._lead is None]
         toks, pos, cu, slots, last_rows = [], [], [0], [], []
@@ -266,12 +296,10 @@ class RolloutEngine:
             last_rows.append(cu[-1] - 1)
         dev = self.device
         if leaders:
-            t = torch.tensor(toks, dtype=torch.int64, device=dev)
-            logits = self.weights.forward_prefill(
-                t, torch.tensor(pos, dtype=torch.int64, device=dev),
-                torch.tensor(cu, dtype=torch.int32, device=dev),
-                torch.tensor(slots, dtype=torch.int64, device=dev), self.kv,
-                torch.tensor(last_rows, dtype=torch.int64, device=dev), self.tp, max_seqlen=max(b - a for a, b in zip(cu, cu[1:])))
+            t, pos_t, cu_t, slots_t, last_t = self._stage([(toks, torch.int64), (pos, torch.int64), (cu, torch.int32),
+                                                           (slots, torch.int64), (last_rows, torch.int64)])
+            logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
+                                                  max_seqlen=max(b - a for a, b in zip(cu, cu[1:])))
             self.stats["prefill_tokens"] += len(toks)
         row_of = {id(r): i for i, r in enumerate(leaders)}
         # followers copy the leader's partially filled tail block and reuse its last-token logits
@@ -288,7 +316,7 @@ class RolloutEngine:
                 rows.append(row_of[id(lead)])
             else:
                 rows.append(row_of[id(r)])
-        sel = logits[torch.tensor(rows, device=dev)] if len(rows) != len(leaders) or rows != list(range(len(leaders))) else logits
+        sel = logits[torch.tensor(rows, device=dev)] if rows != list(range(len(leaders))) else logits
         self._sample_and_append(reqs, sel)
         now = time.perf_counter()
         for r in reqs:
@@ -306,14 +334,15 @@ class RolloutEngine:
                 r._reserve = max(0, r._reserve - 1)
         B = len(reqs)
         maxb = max(len(r.blocks) for r in reqs)
-        bt = torch.zeros(B, maxb, dtype=torch.int32)
-        for i, r in enumerate(reqs):
-            bt[i, :len(r.blocks)] = torch.tensor(r.blocks, dtype=torch.int32)
-        tok = torch.tensor([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], dtype=torch.int64, device=dev)
-        pos = torch.tensor([r.num_tokens - 1 for r in reqs], dtype=torch.int64, device=dev)
-        ctx = torch.tensor([r.num_tokens for r in reqs], dtype=torch.int32, device=dev)
-        slots = torch.tensor([self._slots(r, r.num_tokens - 1, r.num_tokens)[0] for r in reqs], dtype=torch.int64, device=dev)
-        logits = self.weights.forward_decode(tok, pos, bt.to(dev), ctx, slots, self.kv, self.tp)
+        maxb = (maxb + 7) // 8 * 8
+        bt_rows = [r.blocks + [0] * (maxb - len(r.blocks)) for r in reqs]
+        tok, pos, ctx, slots, bt = self._stage([
+            ([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], torch.int64),
+            ([r.num_tokens - 1 for r in reqs], torch.int64),
+            ([r.num_tokens for r in reqs], torch.int32),
+            ([r.blocks[(r.num_tokens - 1) // bs] * bs + (r.num_tokens - 1) % bs for r in reqs], torch.int64),
+            (bt_rows, torch.int32)])
+        logits = self.weights.forward_decode(tok, pos, bt, ctx, slots, self.kv, self.tp)
         self.stats["decode_tokens"] += B
         self._sample_and_append(reqs, logits)
 
@@ -322,12 +351,14 @@ class RolloutEngine:
         B = len(reqs)
         v = self.cfg.vocab_size
         logits = logits[:, :v]
-        temp = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32, device=dev)
-        topk = torch.tensor([r.params.top_k for r in reqs], dtype=torch.int64, device=dev)
-        topp = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32, device=dev)
-        u = torch.rand(B, generator=self.gen).to(dev)
+        u = torch.rand(B, generator=self.gen)
+        temp, topk, topp, u = self._stage([([r.params.temperature for r in reqs], torch.float32),
+                                           ([r.params.top_k for r in reqs], torch.int64),
+                                           ([r.params.top_p for r in reqs], torch.float32),
+                                           (u.tolist(), torch.float32)])
         tok, lp = ops.sample(logits, temp, topk, topp, u)
         tok_l, lp_l = tok.tolist(), lp.tolist()
+        self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + B * 12
         for r, t, l in zip(reqs, tok_l, lp_l):
             r.output.append(t)
             r.logprobs.append(l)

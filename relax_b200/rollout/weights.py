@@ -166,10 +166,7 @@ class RolloutWeights:
     # ------------------------------------------------------------------ entry points
     def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
         def attn(i, q, k, v):
-            kc = kv[i, 0].view(-1, k.shape[1], k.shape[2])
-            vc = kv[i, 1].view(-1, v.shape[1], v.shape[2])
-            kc[slots] = k
-            vc[slots] = v
+            ops.kv_cache_write(k, v, kv[i, 0], kv[i, 1], slots)
             return ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=True, max_seqlen=max_seqlen)
 
         h = self._run(tokens, positions, attn, tp)
@@ -177,10 +174,7 @@ class RolloutWeights:
 
     def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
         def attn(i, q, k, v):
-            kc = kv[i, 0].view(-1, k.shape[1], k.shape[2])
-            vc = kv[i, 1].view(-1, v.shape[1], v.shape[2])
-            kc[slots] = k
-            vc[slots] = v
+            ops.kv_cache_write(k, v, kv[i, 0], kv[i, 1], slots)
             return ops.paged_decode_attention(q, kv[i, 0], kv[i, 1], block_tables, context_lens)
 
         h = self._run(tokens, positions, attn, tp)

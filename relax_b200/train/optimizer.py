@@ -253,6 +253,26 @@ class DistributedOptimizer:
         else:
             self.master.copy_(self.param_buf[self.lo:self.hi].float())
 
+    def release_grads(self):
+        """Drop the gradient buffer (it is zeroed at the start of every step anyway)."""
+        if self.grad_buf is None:
+            return
+        self._grad_meta = (self.grad_buf.shape, self.grad_buf.dtype, self.grad_buf.device)
+        self.grad_buf = None
+        for p in self.params:
+            p.main_grad = None
+            p.grad = None
+
+    def allocate_grads(self):
+        if self.grad_buf is not None:
+            return
+        shape, dtype, dev = self._grad_meta
+        self.grad_buf = torch.zeros(shape, dtype=dtype, device=dev)
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+            if dtype == self.pdtype:
+                p.grad = p.main_grad
+
     # ------------------------------------------------------------------ offload (colocate sleep / wake_up)
     def offload_state(self):
         """Move optimizer state to pinned host memory and release the gradient
