@@ -386,7 +386,7 @@ def build_copy_table_raw(entries, device, elem_size: int, chunk_bytes: int = 1 <
         raw += struct.pack("<QQiiii", s, d, rows, cols, sld, dld)
         starts.append(total)
         total += (rows + chunk_rows - 1) // chunk_rows
-    table = torch.frombuffer(bytes(raw), dtype=torch.uint8).to(device)
+    table = torch.frombuffer(raw, dtype=torch.uint8).to(device)
     cs = torch.tensor(starts, dtype=torch.int32, device=device)
     return CopyTable(table, cs, len(entries), total, chunk_rows, elem_size, None)
 

@@ -102,6 +102,7 @@ class ColocatedGRPO:
         self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
                                     num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
                                     max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
+                                    max_model_len=cfg.prompt_len + cfg.max_response_len,
                                     eos_token_id=cfg.eos_token_id)
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank

@@ -99,7 +99,7 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, tp: Optional[GroupInfo] = None, device="cpu", dtype=None,
                  num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
-                 use_cuda_graph: bool = True):
+                 use_cuda_graph: bool = True, max_model_len: int = 4096):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
@@ -119,7 +119,11 @@ class RolloutEngine:
         self.kv = None
         self._alloc_kv()
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        self.max_model_len = max_model_len
         self._graphs = {}
+        self._graph_pool = None
+        # padding rows of a graph bucket read/write this block; it is never handed to a request
+        self._scratch_block = self.bm.alloc() if self.use_cuda_graph else 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0}
 
     # ------------------------------------------------------------------ memory
@@ -136,6 +140,7 @@ class RolloutEngine:
             raise RuntimeError("cannot release memory with requests in flight; abort or drain first")
         if "cuda_graph" in tags:
             self._graphs = {}
+            self._graph_pool = None
         if "kv_cache" in tags:
             self.kv = None
         if "weights" in tags:
@@ -153,6 +158,8 @@ class RolloutEngine:
         if self.running:
             raise RuntimeError("flush_cache with running requests")
         self.bm = BlockManager(self.bm.num_blocks, self.block_size)
+        if self.use_cuda_graph:
+            self._scratch_block = self.bm.alloc()
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: SamplingParams, group_key: Optional[int] = None,
@@ -323,6 +330,8 @@ class RolloutEngine:
             r.t_first = now
 
     def _decode(self):
+        if self.use_cuda_graph and self._decode_graph():
+            return
         reqs = self.running
         dev = self.device
         bs = self.block_size
@@ -346,6 +355,110 @@ class RolloutEngine:
         self.stats["decode_tokens"] += B
         self._sample_and_append(reqs, logits)
 
+    # ------------------------------------------------------------------ CUDA-graph decode
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+
+    def _graph_state(self, bucket: int):
+        """Static input/output buffers and the captured graph of one batch-size bucket.
+        All inputs of a step live in ONE device buffer refreshed by ONE async H2D copy."""
+        st = self._graphs.get(bucket)
+        if st is not None:
+            return st
+        dev, bs = self.device, self.block_size
+        maxb = (self.bm.blocks_for(self._max_model_len()) + 7) // 8 * 8
+        i64, i32, f32 = torch.int64, torch.int32, torch.float32
+        fields = [("tok", i64, (bucket,)), ("pos", i64, (bucket,)), ("slots", i64, (bucket,)), ("topk", i64, (bucket,)),
+                  ("ctx", i32, (bucket,)), ("bt", i32, (bucket, maxb)), ("temp", f32, (bucket,)), ("topp", f32, (bucket,)),
+                  ("u", f32, (bucket,))]
+        offs, n = {}, 0
+        for name, dt, shp in fields:
+            offs[name] = n
+            n += (math.prod(shp) * torch.empty(0, dtype=dt).element_size() + 15) // 16 * 16
+        host = torch.zeros(n, dtype=torch.uint8, pin_memory=True)
+        devb = torch.zeros(n, dtype=torch.uint8, device=dev)
+
+        def views(buf):
+            out = {}
+            for name, dt, shp in fields:
+                nb = math.prod(shp) * torch.empty(0, dtype=dt).element_size()
+                out[name] = buf[offs[name]:offs[name] + nb].view(dt).view(shp)
+            return out
+
+        st = {"host": host, "dev": devb, "h": views(host), "d": views(devb), "nbytes": n, "maxb": maxb}
+        # neutral padding rows: context of one token held in the scratch block
+        h = st["h"]
+        h["ctx"].fill_(1)
+        h["bt"].fill_(self._scratch_block)
+        h["slots"].fill_(self._scratch_block * bs)
+        h["temp"].fill_(1.0)
+        h["topp"].fill_(1.0)
+        h["topk"].fill_(-1)
+        h["u"].fill_(0.5)
+        devb.copy_(host)
+        d = st["d"]
+
+        def run():
+            logits = self.weights.forward_decode(d["tok"], d["pos"], d["bt"], d["ctx"], d["slots"], self.kv, self.tp)
+            return ops.sample(logits[:, :self.cfg.vocab_size], d["temp"], d["topk"], d["topp"], d["u"])
+
+        run()                                   # eager warm-up (lazy initialisation, communicator set-up)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self._graph_pool):
+            st["out_tok"], st["out_lp"] = run()
+        if self._graph_pool is None:
+            self._graph_pool = g.pool()
+        st["graph"] = g
+        self._graphs[bucket] = st
+        return st
+
+    def _max_model_len(self) -> int:
+        return getattr(self, "max_model_len", 0) or 4096
+
+    def _decode_graph(self):
+        reqs = self.running
+        bs = self.block_size
+        for r in reqs:
+            p = r.num_tokens - 1
+            if p // bs >= len(r.blocks):
+                r.blocks.append(self.bm.alloc())
+                r._reserve = max(0, r._reserve - 1)
+        B = len(reqs)
+        bucket = next((b for b in self.GRAPH_BUCKETS if b >= B), None)
+        if bucket is None or max(r.num_tokens for r in reqs) > self._max_model_len():
+            return False
+        st = self._graph_state(bucket)
+        h = st["h"]
+        h["tok"][:B] = torch.tensor([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], dtype=torch.int64)
+        h["pos"][:B] = torch.tensor([r.num_tokens - 1 for r in reqs], dtype=torch.int64)
+        h["ctx"][:B] = torch.tensor([r.num_tokens for r in reqs], dtype=torch.int32)
+        h["slots"][:B] = torch.tensor([r.blocks[(r.num_tokens - 1) // bs] * bs + (r.num_tokens - 1) % bs for r in reqs],
+                                      dtype=torch.int64)
+        maxb = st["maxb"]
+        h["bt"][:B] = torch.tensor([r.blocks + [self._scratch_block] * (maxb - len(r.blocks)) for r in reqs], dtype=torch.int32)
+        h["temp"][:B] = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32)
+        h["topk"][:B] = torch.tensor([r.params.top_k for r in reqs], dtype=torch.int64)
+        h["topp"][:B] = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32)
+        h["u"][:B] = torch.rand(B, generator=self.gen)
+        if B < bucket and st.get("last_B", 0) > B:   # rows that held real requests last time become padding again
+            lb = st["last_B"]
+            h["ctx"][B:lb] = 1
+            h["bt"][B:lb] = self._scratch_block
+            h["slots"][B:lb] = self._scratch_block * bs
+            h["temp"][B:lb] = 1.0
+            h["topk"][B:lb] = -1
+            h["topp"][B:lb] = 1.0
+        st["last_B"] = B
+        st["dev"].copy_(st["host"], non_blocking=True)
+        st["graph"].replay()
+        tok_l, lp_l = st["out_tok"][:B].tolist(), st["out_lp"][:B].tolist()
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + st["nbytes"]
+        self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + B * 12
+        self.stats["decode_tokens"] += B
+        self.stats["graph_replays"] = self.stats.get("graph_replays", 0) + 1
+        self._append_tokens(reqs, tok_l, lp_l)
+        return True
+
     def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):
         dev = self.device
         B = len(reqs)
@@ -359,6 +472,9 @@ class RolloutEngine:
         tok, lp = ops.sample(logits, temp, topk, topp, u)
         tok_l, lp_l = tok.tolist(), lp.tolist()
         self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + B * 12
+        self._append_tokens(reqs, tok_l, lp_l)
+
+    def _append_tokens(self, reqs, tok_l, lp_l):
         for r, t, l in zip(reqs, tok_l, lp_l):
             r.output.append(t)
             r.logprobs.append(l)

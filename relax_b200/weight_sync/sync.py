@@ -118,8 +118,11 @@ class WeightSync:
             from ..ops import cuda as C
 
             if C.available():
-                if self._device_table is None:
+                # the table holds raw addresses: rebuild it whenever either side was re-allocated
+                key = (rw.flat.data_ptr(), tuple(trainer_params[b.src_name].data_ptr() for b in blocks[:4]))
+                if self._device_table is None or getattr(self, "_table_key", None) != key:
                     self._device_table = C.build_copy_table(blocks, trainer_params, rw)
+                    self._table_key = key
                 C.run_copy_table(self._device_table)
                 return
         for b in blocks:

@@ -1,0 +1,78 @@
+"""Rollout engine and colocated GRPO loop on a GPU (bf16, sm_100a kernels)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg():
+    from relax_b200.models.config import get_config
+
+    return get_config("qwen3-0.6b", num_layers=2, vocab_size=4096, tie_word_embeddings=False)
+
+
+def _pair(use_graph, kv_blocks=256):
+    from relax_b200.rollout.engine import RolloutEngine
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.weight_sync.plan import TrainerLayout
+    from relax_b200.weight_sync.sync import WeightSync
+
+    cfg = _cfg()
+    actor = TrainActor(cfg, TrainConfig(pad_multiple=128), device="cuda", seed=0, with_optimizer=False)
+    eng = RolloutEngine(cfg, device="cuda", dtype=torch.bfloat16, num_kv_blocks=kv_blocks, block_size=16,
+                        use_cuda_graph=use_graph, max_model_len=256)
+    WeightSync(cfg, TrainerLayout(), 1, [0], [0]).update_weights(dict(actor.named_local_params()), eng.weights, eng, 1)
+    return cfg, actor, eng
+
+
+def test_engine_logprobs_match_trainer_and_graph_equals_eager():
+    from relax_b200.ops import cuda as C
+    from relax_b200.rollout.engine import SamplingParams
+
+    outs = {}
+    for use_graph in (False, True):
+        cfg, actor, eng = _pair(use_graph)
+        g = torch.Generator().manual_seed(0)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 40, 17, 33, 64)]
+        res = eng.generate(prompts + [prompts[1]] * 3, SamplingParams(max_new_tokens=24), group_keys=[0, 1, 2, 3, 4, 1, 1, 1])
+        outs[use_graph] = res
+        if use_graph:
+            assert eng.stats.get("graph_replays", 0) >= 20
+        batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [len(r.output) for r in res]}
+        lp = actor.compute_log_prob(batch)["log_probs"]
+        for r, l in zip(res, lp):
+            d = (torch.tensor(r.logprobs, device="cuda") - l).abs()
+            assert d.mean() < 0.03 and d.max() < 0.25, (d.mean().item(), d.max().item())
+        C.check_error_flag()
+    for a, b in zip(outs[False], outs[True]):
+        assert a.output == b.output
+        assert max(abs(x - y) for x, y in zip(a.logprobs, b.logprobs)) < 1e-4
+
+
+def test_colocated_grpo_two_steps_on_gpu():
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.ops import cuda as C
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    cfg = ColocateConfig(
+        model=_cfg(),
+        train=TrainConfig(n_samples_per_prompt=4, global_batch_size=16, max_tokens_per_gpu=1024, pad_multiple=128,
+                          loss=LossConfig(use_kl_loss=True, kl_loss_coef=0.001), optim=OptimizerConfig(lr=1e-5)),
+        rollout_batch_size=4, prompt_len=32, max_response_len=32, eos_token_id=7, kv_blocks=128,
+        release_rollout_weights=True)
+    run = ColocatedGRPO(cfg, device="cuda")
+    C.reset_launch_count()
+    for _ in range(2):
+        m = run.step()
+        assert math.isfinite(m["loss"]) and math.isfinite(m["grad_norm"]) and m["grad_norm"] > 0
+        assert m["train_rollout_logprob_abs_diff"] < 0.05
+        assert m["weight_sync_ms"] >= 0
+    assert C.launch_count() > 100
+    # rollout weights equal the trainer's after the sync (bit exact block copies)
+    p = dict(run.actor.named_local_params())
+    assert torch.equal(run.engine.weights.p["layers.1.o"], p["decoder.layers.1.self_attention.linear_proj.weight"])
+    C.check_error_flag()
