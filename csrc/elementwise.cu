@@ -623,3 +623,43 @@ extern "C" int rb_fp8_block_dequant(const void* q, const float* scale, void* out
   rb_note_launch(1);
   return (int)cudaGetLastError();
 }
+
+// ----------------------------------------------------------------------------- allocation-free RMSNorm backward
+#include "no_alloc.h"
+#include <cstdio>
+
+// Scratch of rb_rmsnorm_bwd_static.  In host code this name is only a handle for the
+// runtime; the address the kernels use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_rmsnorm_scratch[RB_NOALLOC_RMSNORM_SCRATCH_FLOATS];
+
+extern "C" int rb_rmsnorm_bwd_static(const void* x, const void* w, const void* dy, void* dx, void* dw, int rows, int cols,
+                                     float eps, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (cols <= 0 || cols > RB_NOALLOC_RMSNORM_MAX_COLS ||
+      static_cast<long long>(rb_rmsnorm_bwd_parts(rows, cols)) * cols > RB_NOALLOC_RMSNORM_SCRATCH_FLOATS) {
+    fprintf(stderr,
+            "[relax_b200] rb_rmsnorm_bwd_static: rows=%d cols=%d needs %lld scratch floats; the built-in buffer holds %d "
+            "(cols <= %d). Use rb_rmsnorm_bwd with your own scratch for larger problems.\n",
+            rows, cols, static_cast<long long>(rb_rmsnorm_bwd_parts(rows, cols)) * cols,
+            RB_NOALLOC_RMSNORM_SCRATCH_FLOATS, RB_NOALLOC_RMSNORM_MAX_COLS);
+    return RB_ERR_NOALLOC_TOO_LARGE;
+  }
+  // one address per device, resolved on first use with that device current
+  constexpr int kMaxDevices = 64;
+  static float* scratch_of_device[kMaxDevices] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return RB_ERR_NOALLOC_SETUP;
+  float* scratch = scratch_of_device[dev];
+  if (scratch == nullptr) {
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), g_noalloc_rmsnorm_scratch);
+    if (e != cudaSuccess || scratch == nullptr) {
+      fprintf(stderr, "[relax_b200] rb_rmsnorm_bwd_static: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return e != cudaSuccess ? static_cast<int>(e) : RB_ERR_NOALLOC_SETUP;
+    }
+    scratch_of_device[dev] = scratch;
+  }
+  return rb_rmsnorm_bwd(x, w, dy, dx, dw, scratch, rows, cols, eps, dtype, stream);
+}
