@@ -40,9 +40,13 @@ def _ar(x, g: GroupInfo):
     return x
 
 
-def _fused_enabled(x) -> bool:
-    return x.is_cuda and os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") != "1" and \
-        os.environ.get("RELAX_B200_FUSED_TP", "1") == "1"
+def _fused_enabled(x, g=None) -> bool:
+    if not (x.is_cuda and os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") != "1" and
+            os.environ.get("RELAX_B200_FUSED_TP", "1") == "1"):
+        return False
+    from ..ops import fused_comm
+
+    return g is not None and fused_comm.enabled_for(g)
 
 
 class _AGLinear(torch.autograd.Function):
@@ -51,7 +55,7 @@ class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, g):
         ctx.g = g
-        if g.size > 1 and _fused_enabled(x):
+        if g.size > 1 and _fused_enabled(x, g):
             from ..ops import fused_comm
 
             y, xf = fused_comm.ag_gemm(x, w, g)
@@ -79,7 +83,7 @@ class _LinearRS(torch.autograd.Function):
     def forward(ctx, x, w, g):
         ctx.g = g
         ctx.save_for_backward(x, w)
-        if g.size > 1 and _fused_enabled(x):
+        if g.size > 1 and _fused_enabled(x, g):
             from ..ops import fused_comm
 
             return fused_comm.gemm_rs(x, w, g)
