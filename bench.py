@@ -44,7 +44,7 @@ def parse():
     ap.add_argument("--response-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="debug only: override depth (result is then not comparable)")
     ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
-    ap.add_argument("--kv-gb", type=float, default=28.0)
+    ap.add_argument("--kv-gb", type=float, default=None)
     return ap.parse_args()
 
 
@@ -137,13 +137,15 @@ def main():
     G = args.group_size
     n_prompts = args.prompts_per_gpu * world
     kv_bytes_per_block = mcfg.num_layers * 2 * 16 * (mcfg.num_query_groups // tp) * mcfg.head_dim * 2
-    kv_blocks = int(args.kv_gb * (1 << 30) / kv_bytes_per_block)
+    ref_on_host = world == 1   # one GPU holds the whole model: park the frozen reference in pinned host memory
+    kv_gb = args.kv_gb if args.kv_gb is not None else (52.0 if world == 1 else 40.0)
+    kv_blocks = int(kv_gb * (1 << 30) / kv_bytes_per_block)
     need_blocks = args.prompts_per_gpu * tp * G * ((args.prompt_len + args.response_len + 15) // 16 + 1)
     kv_blocks = min(kv_blocks, need_blocks)
     cfg = ColocateConfig(
         model=mcfg,
         train=TrainConfig(advantage_estimator="grpo", n_samples_per_prompt=G, global_batch_size=n_prompts * G,
-                          max_tokens_per_gpu=args.max_tokens_per_gpu, pad_multiple=128,
+                          max_tokens_per_gpu=args.max_tokens_per_gpu, pad_multiple=128, ref_on_host=ref_on_host,
                           loss=LossConfig(eps_clip=0.2, use_kl_loss=True, kl_loss_coef=0.001, kl_loss_type="k1"),
                           optim=OptimizerConfig(lr=1e-6, clip_grad=1.0, grad_dtype="fp32")),
         trainer_tp=tp, rollout_tp=tp, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,

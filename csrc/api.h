@@ -58,10 +58,20 @@ int rb_decode_attn_splits(int B, int Hkv, int max_ctx);
 int rb_decode_attn(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens, void* out,
                    float* part_o, float* part_ml, int B, int Hq, int Hkv, int block_size, int max_blocks, int max_ctx,
                    float scale, int splits, cudaStream_t st);
+int rb_decode_attn_v1(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens, void* out,
+                      float* part_o, float* part_ml, int B, int Hq, int Hkv, int block_size, int max_blocks, int max_ctx,
+                      float scale, int splits, cudaStream_t st);
+int rb_decode_attn_tc(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens, void* out,
+                      float* part_o, float* part_ml, int B, int Hq, int Hkv, int num_blocks, int block_size, int max_blocks,
+                      int max_ctx, float scale, int splits, int* err, cudaStream_t st);
 int rb_sample(const float* logits, int B, int V, int ld, const float* temperature, const long long* top_k,
               const float* top_p, const float* uniform, long long* tok, float* logp, cudaStream_t st);
 int rb_topk_router(const float* logits, int T, int E, int K, int norm, float* w, long long* idx, float* probs,
                    cudaStream_t st);
+int rb_gemm_splitk_plan(int M, int N, int K, int* bn_out);
+int rb_gemm_splitk(const void* A, const void* B, void* C, const void* bias, const void* residual, float* workspace, int M,
+                   int N, int K, int lda, int ldb, int ldc, int splits, int bn, int is_fp16, int* err_flag,
+                   cudaStream_t stream);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

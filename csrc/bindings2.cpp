@@ -49,10 +49,20 @@ int64_t decode_attn_splits(int64_t B, int64_t Hkv, int64_t max_ctx) {
 }
 void decode_attn(torch::Tensor q, torch::Tensor kc, torch::Tensor vc, torch::Tensor block_tables, torch::Tensor ctx_lens,
                  torch::Tensor out, c10::optional<torch::Tensor> part_o, c10::optional<torch::Tensor> part_ml,
-                 int64_t max_ctx, double scale, int64_t splits) {
+                 int64_t max_ctx, double scale, int64_t splits, int64_t version, torch::Tensor err) {
   const c10::cuda::CUDAGuard guard(q.device());
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && q.size(2) == 128, "decode attention: bf16, head_dim 128");
-  check(rb_decode_attn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+  if (version == 3) {
+    check(rb_decode_attn_tc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
+                            out.data_ptr(), part_o.has_value() ? part_o->data_ptr<float>() : nullptr,
+                            part_ml.has_value() ? part_ml->data_ptr<float>() : nullptr, (int)q.size(0), (int)q.size(1),
+                            (int)kc.size(2), (int)kc.size(0), (int)kc.size(1), (int)block_tables.size(1), (int)max_ctx,
+                            (float)scale, (int)splits, err.data_ptr<int>(), cur_stream()),
+          "rb_decode_attn_tc");
+    return;
+  }
+  auto fn = version == 1 ? rb_decode_attn_v1 : rb_decode_attn;
+  check(fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), block_tables.data_ptr<int>(), ctx_lens.data_ptr<int>(),
                        out.data_ptr(), part_o.has_value() ? part_o->data_ptr<float>() : nullptr,
                        part_ml.has_value() ? part_ml->data_ptr<float>() : nullptr, (int)q.size(0), (int)q.size(1),
                        (int)kc.size(2), (int)kc.size(1), (int)block_tables.size(1), (int)max_ctx, (float)scale,
@@ -72,6 +82,21 @@ void topk_router(torch::Tensor logits, int64_t K, bool norm, torch::Tensor w, to
   check(rb_topk_router(logits.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)K, norm,
                        w.data_ptr<float>(), (long long*)idx.data_ptr<int64_t>(), probs.data_ptr<float>(), cur_stream()),
         "rb_topk_router");
+}
+std::tuple<int64_t, int64_t> gemm_splitk_plan(int64_t M, int64_t N, int64_t K) {
+  int bn = 0;
+  const int s = rb_gemm_splitk_plan((int)M, (int)N, (int)K, &bn);
+  return {s, bn};
+}
+void gemm_splitk(torch::Tensor A, torch::Tensor B, torch::Tensor C, c10::optional<torch::Tensor> bias,
+                 c10::optional<torch::Tensor> residual, torch::Tensor workspace, int64_t splits, int64_t bn,
+                 torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  check(rb_gemm_splitk(A.data_ptr(), B.data_ptr(), C.data_ptr(), bias.has_value() ? bias->data_ptr() : nullptr,
+                       residual.has_value() ? residual->data_ptr() : nullptr, workspace.data_ptr<float>(), (int)A.size(0),
+                       (int)B.size(0), (int)A.size(1), (int)A.stride(0), (int)B.stride(0), (int)C.stride(0), (int)splits,
+                       (int)bn, A.scalar_type() == at::kHalf, err.data_ptr<int>(), cur_stream()),
+        "rb_gemm_splitk");
 }
 int64_t lm_head_splits(int64_t M, int64_t N) { return rb_lm_head_splits((int)M, (int)N); }
 void lm_head_logprob(torch::Tensor h, torch::Tensor W, torch::Tensor targets, torch::Tensor partials, int64_t vocab_start,
@@ -104,6 +129,8 @@ void register_more(pybind11::module_& m) {
   m.def("decode_attn", &decode_attn);
   m.def("sample", &sample);
   m.def("topk_router", &topk_router);
+  m.def("gemm_splitk_plan", &gemm_splitk_plan);
+  m.def("gemm_splitk", &gemm_splitk);
   m.def("lm_head_splits", &lm_head_splits);
   m.def("lm_head_logprob", &lm_head_logprob);
   m.def("lm_head_dlogits", &lm_head_dlogits);

@@ -358,7 +358,7 @@ extern "C" int rb_decode_attn_splits(int B, int Hkv, int max_ctx) {
 }
 
 // scratch (only when splits > 1): part_o fp32 [B*Hq*splits*128], part_ml fp32 [B*Hq*splits*2]
-extern "C" int rb_decode_attn(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens,
+extern "C" int rb_decode_attn_v1(const void* q, const void* kc, const void* vc, const int* block_tables, const int* ctx_lens,
                               void* out, float* part_o, float* part_ml, int B, int Hq, int Hkv, int block_size,
                               int max_blocks, int max_ctx, float scale, int splits, cudaStream_t st) {
   if (B == 0) return 0;

@@ -14,6 +14,7 @@
 // round-robin tile schedule with grouped ordering for L2 reuse.
 #include "common.cuh"
 #include "host_utils.h"
+#include <type_traits>
 
 namespace rb {
 
@@ -27,6 +28,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int out_fp32, accumulate;
   int a_mn, b_mn;
+  int k_splits, k_iters_per_split;  // split-K: partial sums go to fp32 workspace slices C + split*M*ldc
   uint32_t lbo_a, sbo_a, lbo_b, sbo_b;  // MN-major descriptor strides (bytes)
   void* C;
   const void* bias;  // optional [N], same dtype as inputs
@@ -69,14 +71,17 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 // column tiles (so per-row softmax statistics stay in registers); the other modes use the
 // persistent round-robin schedule.
 template <int MODE>
-__device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, int& tn) {
+__device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, int& tn, int& split) {
+  split = 0;
   if constexpr (MODE == kEpiLogProb) {
     tm = blockIdx.x / p.n_splits;
     tn = (blockIdx.x % p.n_splits) * p.tiles_per_split + i;
     return i < p.tiles_per_split && tn < p.tiles_n;
   } else {
-    const int t = blockIdx.x + i * gridDim.x;
-    if (t >= p.tiles_m * p.tiles_n) return false;
+    int t = blockIdx.x + i * gridDim.x;
+    if (t >= p.tiles_m * p.tiles_n * p.k_splits) return false;
+    split = t % p.k_splits;
+    t /= p.k_splits;
     tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
     return true;
   }
@@ -99,7 +104,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int k_iters = (p.K + BK - 1) / BK;
+  const int k_iters_total = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -131,10 +136,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       uint32_t ph = 0;
       bool ok = true;
       for (int ti = 0; ok; ++ti) {
-        int tm, tn;
-        if (!next_tile<MODE>(p, ti, tm, tn)) break;
+        int tm, tn, split;
+        if (!next_tile<MODE>(p, ti, tm, tn, split)) break;
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int k = 0; k < k_iters; ++k) {
+        const int k_lo = split * p.k_iters_per_split, k_hi = min(k_iters_total, k_lo + p.k_iters_per_split);
+        for (int k = k_lo; k < k_hi; ++k) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
           uint8_t* sa = smem + s * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
@@ -165,12 +171,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       uint32_t acc_ph = 0;
       bool ok = true;
       for (int ti = 0; ok; ++ti) {
-        int tm_, tn_;
-        if (!next_tile<MODE>(p, ti, tm_, tn_)) break;
+        int tm_, tn_, split;
+        if (!next_tile<MODE>(p, ti, tm_, tn_, split)) break;
+        const int k_lo = split * p.k_iters_per_split, k_hi = min(k_iters_total, k_lo + p.k_iters_per_split);
         if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.err)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int k = 0; k < k_iters; ++k) {
+        for (int k = k_lo; k < k_hi; ++k) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
@@ -183,7 +190,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                                        : make_smem_desc(sa + kk * 32, 16, 1024, kSwizzle128B);
             const uint64_t db = p.b_mn ? make_smem_desc(sb + kk * 2048, p.lbo_b, p.sbo_b, kSwizzle128B)
                                        : make_smem_desc(sb + kk * 32, 16, 1024, kSwizzle128B);
-            umma_f16(d_tmem, da, db, idesc, (k > 0 || kk > 0) ? 1u : 0u);
+            umma_f16(d_tmem, da, db, idesc, (k > k_lo || kk > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == kStages) { s = 0; ph ^= 1; }
@@ -204,8 +211,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     int st_row = -1;
     if constexpr (MODE == kEpiLogProb) st_row = (blockIdx.x / p.n_splits) * BM + lane_grp * 32 + lane;
     for (int ti = 0;; ++ti) {
-      int tm, tn;
-      if (!next_tile<MODE>(p, ti, tm, tn)) break;
+      int tm, tn, split;
+      if (!next_tile<MODE>(p, ti, tm, tn, split)) break;
       const int row = tm * BM + lane_grp * 32 + lane;
       st_row = row;
       const int n0 = tn * BN;
@@ -276,7 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               for (int i = 0; i < 32; ++i) if (col + i < p.N) v[i] += __half2float(b[i]);
             }
           }
-          const size_t off = static_cast<size_t>(row) * p.ldc + col;
+          const size_t off = static_cast<size_t>(split) * p.M * p.ldc + static_cast<size_t>(row) * p.ldc + col;
           const bool full = (col + 32 <= p.N);
           if (p.out_fp32) {
             float* out = reinterpret_cast<float*>(p.C) + off;
@@ -374,9 +381,15 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cu
   }
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  const int tiles = p.tiles_m * p.tiles_n;
+  if (p.k_splits < 1) p.k_splits = 1;
+  {
+    const int kit = (p.K + BK - 1) / BK;
+    p.k_iters_per_split = (kit + p.k_splits - 1) / p.k_splits;
+  }
+  const int tiles = p.tiles_m * p.tiles_n * p.k_splits;
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (MODE == kEpiLogProb) {
+    p.k_splits = 1;
     p.tiles_per_split = (p.tiles_n + p.n_splits - 1) / p.n_splits;
     grid = p.tiles_m * p.n_splits;
   }
@@ -479,4 +492,84 @@ extern "C" int rb_lm_head_dlogits(const void* h, const void* W, const long long*
   rc = make_operand_map(&tb, W, false, N, K, ldw, 256);
   if (rc) return rc;
   return launch<256, true, kEpiDLogits>(ta, tb, p, stream);
+}
+
+
+namespace rb {
+// out[m][n] = sum_s ws[s][m][n] (+ bias[n]) (+ residual[m][n]); 8 columns per thread
+template <bool BF16>
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, const void* __restrict__ bias,
+                                     const void* __restrict__ residual, int M, int N, int splits, int ldo) {
+  const long long total = static_cast<long long>(M) * (N / 4);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int m = static_cast<int>(i / (N / 4)), n = static_cast<int>(i % (N / 4)) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + (static_cast<size_t>(s) * M + m) * N + n);
+      a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
+    using T = typename std::conditional<BF16, __nv_bfloat16, __half>::type;
+    auto tof = [](T v) { if constexpr (BF16) return __bfloat162float(v); else return __half2float(v); };
+    if (bias) { const T* b = reinterpret_cast<const T*>(bias) + n; a.x += tof(b[0]); a.y += tof(b[1]); a.z += tof(b[2]); a.w += tof(b[3]); }
+    if (residual) {
+      const T* r = reinterpret_cast<const T*>(residual) + static_cast<size_t>(m) * ldo + n;
+      a.x += tof(r[0]); a.y += tof(r[1]); a.z += tof(r[2]); a.w += tof(r[3]);
+    }
+    T* o = reinterpret_cast<T*>(out) + static_cast<size_t>(m) * ldo + n;
+    if constexpr (BF16) {
+      uint2 pk; pk.x = pack_bf16(a.x, a.y); pk.y = pack_bf16(a.z, a.w);
+      *reinterpret_cast<uint2*>(o) = pk;
+    } else {
+      o[0] = __float2half(a.x); o[1] = __float2half(a.y); o[2] = __float2half(a.z); o[3] = __float2half(a.w);
+    }
+  }
+}
+}  // namespace rb
+
+// Split-K plan for skinny problems (decode): returns the number of K splits (1 = do not split) and the N tile.
+extern "C" int rb_gemm_splitk_plan(int M, int N, int K, int* bn_out) {
+  using namespace rb;
+  const int tm = (M + BM - 1) / BM;
+  int bn = 128;
+  if (N % 128 && N % 64 == 0) bn = 64;
+  const int tiles = tm * ((N + bn - 1) / bn);
+  const int kit = (K + BK - 1) / BK;
+  int splits = 1;
+  if (tiles < num_sms()) {
+    splits = num_sms() / tiles;
+    if (splits > kit / 8) splits = kit / 8;   // at least 8 k-iterations (512 elements) per split
+    if (splits < 1) splits = 1;
+    if (splits > 16) splits = 16;
+  }
+  *bn_out = bn;
+  return splits;
+}
+
+// C[M,N] = A[M,K] * B[N,K]^T through split-K: workspace fp32 [splits][M][N] supplied by the caller.
+extern "C" int rb_gemm_splitk(const void* A, const void* B, void* C, const void* bias, const void* residual, float* workspace,
+                              int M, int N, int K, int lda, int ldb, int ldc, int splits, int bn, int is_fp16, int* err_flag,
+                              cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (N % 4) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = N;
+  p.out_fp32 = 1; p.accumulate = 0;
+  p.lbo_a = p.lbo_b = BK * 128; p.sbo_a = p.sbo_b = 1024;
+  p.C = workspace; p.err = err_flag; p.k_splits = splits;
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, A, false, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, B, false, N, K, ldb, bn);
+  if (rc) return rc;
+  if (bn == 128) rc = is_fp16 ? launch<128, false>(ta, tb, p, stream) : launch<128, true>(ta, tb, p, stream);
+  else if (bn == 64) rc = is_fp16 ? launch<64, false>(ta, tb, p, stream) : launch<64, true>(ta, tb, p, stream);
+  else return -3;
+  if (rc) return rc;
+  long long blocks = (static_cast<long long>(M) * (N / 4) + 255) / 256;
+  if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
+  if (is_fp16) splitk_reduce_kernel<false><<<(int)blocks, 256, 0, stream>>>(workspace, C, bias, residual, M, N, splits, ldc);
+  else splitk_reduce_kernel<true><<<(int)blocks, 256, 0, stream>>>(workspace, C, bias, residual, M, N, splits, ldc);
+  rb_note_launch(1);
+  return static_cast<int>(cudaGetLastError());
 }

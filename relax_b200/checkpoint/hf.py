@@ -1,0 +1,227 @@
+"""Megatron-layout <-> Hugging Face name/shape conversion and safetensors IO.
+
+Per family the reference keeps one converter (relax/backends/megatron/
+weight_conversion/{qwen2,qwen3moe,llama,glm4,...}.py, dispatched by model name in
+``__init__.py:24-93``): fused QKV is split by query group, ``linear_fc1`` is cut into
+gate/up, norms fused into the following linear get their own HF names, experts are
+numbered globally.  Here one table-driven converter covers the dense Qwen2/Qwen3/
+Llama layouts and the Qwen3-MoE layout, in both directions, on FULL (unsharded)
+tensors; sharded export gathers through :mod:`relax_b200.checkpoint.dist_ckpt`.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Iterable, Iterator, Optional
+
+import torch
+
+from ..models.config import ModelConfig
+
+_LAYER = re.compile(r"decoder\.layers\.(\d+)\.(.+)")
+
+
+def strip_prefix(name: str) -> str:
+    while name.startswith("module."):
+        name = name[len("module."):]
+    return name
+
+
+def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
+    """One Megatron tensor -> list of ``(hf_name, tensor)``."""
+    name = strip_prefix(name)
+    H, hd = cfg.hidden_size, cfg.head_dim
+    ng, qpg = cfg.num_query_groups, cfg.num_attention_heads // cfg.num_query_groups
+    if name == "embedding.word_embeddings.weight":
+        return [("model.embed_tokens.weight", p[: cfg.vocab_size])]
+    if name == "output_layer.weight":
+        return [("lm_head.weight", p[: cfg.vocab_size])]
+    if name == "decoder.final_layernorm.weight":
+        return [("model.norm.weight", p)]
+    if name == "value_head.weight":
+        return [("score.weight", p)]
+    m = _LAYER.match(name)
+    if not m:
+        raise ValueError(f"unknown parameter name {name!r}")
+    i, rest = m.groups()
+    pre = f"model.layers.{i}."
+    if rest == "self_attention.linear_qkv.weight":
+        x = p.view(ng, qpg + 2, hd, H)
+        return [(pre + "self_attn.q_proj.weight", x[:, :qpg].reshape(-1, H)),
+                (pre + "self_attn.k_proj.weight", x[:, qpg].reshape(-1, H)),
+                (pre + "self_attn.v_proj.weight", x[:, qpg + 1].reshape(-1, H))]
+    if rest == "self_attention.linear_qkv.bias":
+        x = p.view(ng, qpg + 2, hd)
+        return [(pre + "self_attn.q_proj.bias", x[:, :qpg].reshape(-1)), (pre + "self_attn.k_proj.bias", x[:, qpg].reshape(-1)),
+                (pre + "self_attn.v_proj.bias", x[:, qpg + 1].reshape(-1))]
+    simple = {
+        "self_attention.linear_proj.weight": "self_attn.o_proj.weight",
+        "self_attention.linear_qkv.layer_norm_weight": "input_layernorm.weight",
+        "self_attention.q_layernorm.weight": "self_attn.q_norm.weight",
+        "self_attention.k_layernorm.weight": "self_attn.k_norm.weight",
+        "mlp.linear_fc1.layer_norm_weight": "post_attention_layernorm.weight",
+        "pre_mlp_layernorm.weight": "post_attention_layernorm.weight",
+        "mlp.linear_fc2.weight": "mlp.down_proj.weight",
+        "mlp.router.weight": "mlp.gate.weight",
+    }
+    if rest in simple:
+        return [(pre + simple[rest], p)]
+    if rest == "mlp.linear_fc1.weight":
+        g, u = p.chunk(2, 0)
+        return [(pre + "mlp.gate_proj.weight", g), (pre + "mlp.up_proj.weight", u)]
+    if rest == "mlp.experts.linear_fc1.weight":      # stacked [E, 2F, H]
+        out = []
+        for e in range(p.shape[0]):
+            g, u = p[e].chunk(2, 0)
+            out += [(pre + f"mlp.experts.{e}.gate_proj.weight", g), (pre + f"mlp.experts.{e}.up_proj.weight", u)]
+        return out
+    if rest == "mlp.experts.linear_fc2.weight":
+        return [(pre + f"mlp.experts.{e}.down_proj.weight", p[e]) for e in range(p.shape[0])]
+    raise ValueError(f"unknown layer parameter {rest!r}")
+
+
+def convert_state_to_hf(cfg: ModelConfig, state: dict) -> dict:
+    out = {}
+    for k, v in state.items():
+        for hk, hv in megatron_to_hf(cfg, k, v):
+            out[hk] = hv.contiguous()
+    if cfg.tie_word_embeddings:
+        out.pop("lm_head.weight", None)
+    return out
+
+
+def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
+    """Full HF state dict -> full Megatron-layout state dict (inverse of :func:`convert_state_to_hf`)."""
+    H, hd = cfg.hidden_size, cfg.head_dim
+    ng, qpg = cfg.num_query_groups, cfg.num_attention_heads // cfg.num_query_groups
+    out = {"embedding.word_embeddings.weight": hf["model.embed_tokens.weight"],
+           "decoder.final_layernorm.weight": hf["model.norm.weight"]}
+    if not cfg.tie_word_embeddings:
+        out["output_layer.weight"] = hf.get("lm_head.weight", hf["model.embed_tokens.weight"])
+    for i in range(cfg.num_layers):
+        pre, b = f"model.layers.{i}.", f"decoder.layers.{i}."
+        q = hf[pre + "self_attn.q_proj.weight"].view(ng, qpg, hd, H)
+        k = hf[pre + "self_attn.k_proj.weight"].view(ng, 1, hd, H)
+        v = hf[pre + "self_attn.v_proj.weight"].view(ng, 1, hd, H)
+        out[b + "self_attention.linear_qkv.weight"] = torch.cat([q, k, v], 1).reshape(-1, H)
+        if cfg.qkv_bias:
+            qb = hf[pre + "self_attn.q_proj.bias"].view(ng, qpg, hd)
+            kb = hf[pre + "self_attn.k_proj.bias"].view(ng, 1, hd)
+            vb = hf[pre + "self_attn.v_proj.bias"].view(ng, 1, hd)
+            out[b + "self_attention.linear_qkv.bias"] = torch.cat([qb, kb, vb], 1).reshape(-1)
+        out[b + "self_attention.linear_proj.weight"] = hf[pre + "self_attn.o_proj.weight"]
+        out[b + "self_attention.linear_qkv.layer_norm_weight"] = hf[pre + "input_layernorm.weight"]
+        if cfg.qk_layernorm:
+            out[b + "self_attention.q_layernorm.weight"] = hf[pre + "self_attn.q_norm.weight"]
+            out[b + "self_attention.k_layernorm.weight"] = hf[pre + "self_attn.k_norm.weight"]
+        if cfg.is_moe and i % cfg.moe_layer_freq == 0:
+            out[b + "pre_mlp_layernorm.weight"] = hf[pre + "post_attention_layernorm.weight"]
+            out[b + "mlp.router.weight"] = hf[pre + "mlp.gate.weight"]
+            out[b + "mlp.experts.linear_fc1.weight"] = torch.stack(
+                [torch.cat([hf[pre + f"mlp.experts.{e}.gate_proj.weight"], hf[pre + f"mlp.experts.{e}.up_proj.weight"]], 0)
+                 for e in range(cfg.num_experts)])
+            out[b + "mlp.experts.linear_fc2.weight"] = torch.stack(
+                [hf[pre + f"mlp.experts.{e}.down_proj.weight"] for e in range(cfg.num_experts)])
+        else:
+            out[b + "mlp.linear_fc1.layer_norm_weight"] = hf[pre + "post_attention_layernorm.weight"]
+            out[b + "mlp.linear_fc1.weight"] = torch.cat([hf[pre + "mlp.gate_proj.weight"], hf[pre + "mlp.up_proj.weight"]], 0)
+            out[b + "mlp.linear_fc2.weight"] = hf[pre + "mlp.down_proj.weight"]
+    return out
+
+
+def hf_config_dict(cfg: ModelConfig) -> dict:
+    arch = "Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_layernorm else "Qwen2ForCausalLM")
+    d = {"architectures": [arch], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
+         "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_query_groups,
+         "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn_hidden_size, "vocab_size": cfg.vocab_size,
+         "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta, "tie_word_embeddings": cfg.tie_word_embeddings,
+         "torch_dtype": "bfloat16", "hidden_act": "silu"}
+    if cfg.is_moe:
+        d.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.moe_top_k, moe_intermediate_size=cfg.moe_ffn_hidden_size,
+                 norm_topk_prob=cfg.moe_router_norm_topk_prob)
+    return d
+
+
+# ----------------------------------------------------------------------------- safetensors, sharded by size
+
+
+def save_hf_checkpoint(directory: str, cfg: ModelConfig, hf_state: dict, max_shard_bytes: int = 5 << 30,
+                       quantize_fp8: bool = False, fp8_block: int = 128, post_hook=None):
+    """Write ``model-0000x-of-0000y.safetensors`` + index + ``config.json``.  With
+    ``quantize_fp8`` every 2-D projection weight is stored as e4m3 with a
+    ``weight_scale_inv`` tensor (block ``fp8_block``), the layout of the reference's
+    streaming fp8 writer (relax/backends/megatron/model.py:1609-1653)."""
+    from safetensors.torch import save_file
+
+    from .. import ops
+
+    os.makedirs(directory, exist_ok=True)
+    items = []
+    for k, v in hf_state.items():
+        v = v.detach()
+        if quantize_fp8 and v.dim() == 2 and "proj" in k and k.endswith(".weight"):
+            q, s = ops.blockwise_cast_to_fp8(v, fp8_block)
+            items.append((k, q.cpu()))
+            items.append((k + "_scale_inv", s.cpu()))
+        else:
+            items.append((k, v.cpu().contiguous()))
+    shards, cur, cur_bytes = [], {}, 0
+    for k, v in items:
+        nb = v.numel() * v.element_size()
+        if cur and cur_bytes + nb > max_shard_bytes:
+            shards.append(cur)
+            cur, cur_bytes = {}, 0
+        cur[k] = v
+        cur_bytes += nb
+    if cur:
+        shards.append(cur)
+    weight_map, total = {}, 0
+    for i, sh in enumerate(shards):
+        fn = f"model-{i + 1:05d}-of-{len(shards):05d}.safetensors" if len(shards) > 1 else "model.safetensors"
+        save_file(sh, os.path.join(directory, fn), metadata={"format": "pt"})
+        for k, v in sh.items():
+            weight_map[k] = fn
+            total += v.numel() * v.element_size()
+    with open(os.path.join(directory, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=1)
+    c = hf_config_dict(cfg)
+    if quantize_fp8:
+        c["quantization_config"] = {"quant_method": "fp8", "fmt": "e4m3", "weight_block_size": [fp8_block, fp8_block],
+                                    "activation_scheme": "dynamic"}
+    with open(os.path.join(directory, "config.json"), "w") as f:
+        json.dump(c, f, indent=1)
+    if post_hook is not None:
+        post_hook(directory)
+
+
+def load_hf_checkpoint(directory: str, dequantize: bool = True, dtype=None) -> dict:
+    from safetensors import safe_open
+
+    from .. import ops
+
+    files = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files in {directory}")
+    out = {}
+    for fn in files:
+        with safe_open(os.path.join(directory, fn), framework="pt") as f:
+            for k in f.keys():
+                out[k] = f.get_tensor(k)
+    if dequantize:
+        for k in [k for k in out if k.endswith("_scale_inv")]:
+            base = k[: -len("_scale_inv")]
+            s = out.pop(k)
+            block = 128
+            cfgp = os.path.join(directory, "config.json")
+            if os.path.exists(cfgp):
+                block = json.load(open(cfgp)).get("quantization_config", {}).get("weight_block_size", [128])[0]
+            out[base] = ops.blockwise_dequant_fp8(out[base], s, block, dtype or torch.bfloat16)
+    if dtype is not None:
+        out = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in out.items()}
+    return out
+
+
+def is_hf_checkpoint(path: str) -> bool:
+    return os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")) and \
+        any(f.endswith(".safetensors") for f in os.listdir(path))

@@ -169,7 +169,11 @@ def linear(x, w, bias=None):
         raise TypeError("the sm_100a GEMM takes bf16/fp16 inputs")
     if w.dim() != 2:
         raise ValueError("weight must be 2-D")
-    if not w.is_contiguous() and w.t().is_contiguous():
+    if x2.shape[0] <= 128 and not (torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad)) \
+            and w.is_contiguous() and w.shape[0] % 64 == 0:
+        y = matmul_nt_skinny(x2, w, bias)
+        bias = None
+    elif not w.is_contiguous() and w.t().is_contiguous():
         # y = x @ (w^T stored row-major)  ->  NN product
         y = _LinearNN.apply(x2, w.t())
     else:
@@ -178,6 +182,24 @@ def linear(x, w, bias=None):
     if bias is not None:
         y = y + bias
     return y.reshape(*shp[:-1], y.shape[-1])
+
+
+def matmul_nt_skinny(x, w, bias=None, residual=None):
+    """x[M<=128, K] @ w[N, K]^T for decode: when the N tiles alone cannot fill the SMs the
+    reduction dimension is split across CTAs (fp32 partials in a workspace, one small reduce
+    kernel that also adds bias / residual)."""
+    x, _ = _rowmajor_2d(x)
+    M, K = x.shape
+    N = w.shape[0]
+    C = _load()
+    splits, bn = C.gemm_splitk_plan(M, N, K)
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if splits <= 1:
+        gemm_raw(x, w, out, M, N, K, x.stride(0), w.stride(0), N, bias=bias)
+        return out if residual is None else out + residual
+    ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+    C.gemm_splitk(x, w, out, bias, residual, ws, splits, bn, err_flag(x.device))
+    return out
 
 
 class _LinearNN(torch.autograd.Function):
@@ -463,21 +485,30 @@ def attention_varlen(q, k, v, cu_seqlens, causal=True, scale=None, cu_seqlens_k=
 # --------------------------------------------------------------------------- rollout kernels
 
 
-def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale=None, max_ctx=None):
+def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale=None, max_ctx=None, splits=None,
+                           version=None):
     B, Hq, D = q.shape
     Hkv = k_cache.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if max_ctx is None:
         max_ctx = block_tables.shape[1] * k_cache.shape[1]
     C = _load()
-    splits = C.decode_attn_splits(B, Hkv, max_ctx)
+    if splits is None:
+        splits = int(os.environ.get("RELAX_B200_DECODE_SPLITS", "0")) or C.decode_attn_splits(B, Hkv, max_ctx)
+        if B * Hkv >= 148:
+            splits = 1   # enough CTAs already; splitting only adds the combine pass
+    if version is None:
+        version = int(os.environ.get("RELAX_B200_DECODE_ATTN_VERSION", "3"))
+    if version == 3 and k_cache.shape[1] != 16:
+        version = 1   # the tensor-core kernel gathers 16-token pages
     out = torch.empty_like(q)
     po = pm = None
     if splits > 1:
         po = torch.empty(B * Hq * splits * D, dtype=torch.float32, device=q.device)
         pm = torch.empty(B * Hq * splits * 2, dtype=torch.float32, device=q.device)
     C.decode_attn(q.contiguous(), k_cache, v_cache, block_tables.to(torch.int32).contiguous(),
-                  context_lens.to(torch.int32).contiguous(), out, po, pm, max_ctx, scale, splits)
+                  context_lens.to(torch.int32).contiguous(), out, po, pm, max_ctx, scale, splits, version,
+                  err_flag(q.device))
     return out
 
 

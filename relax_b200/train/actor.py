@@ -51,6 +51,7 @@ class TrainConfig:
     use_rollout_logprobs: bool = False
     keep_old_actor: bool = False
     compute_entropy: bool = True
+    ref_on_host: bool = False           # keep the frozen reference weights in pinned host memory
     loss: L.LossConfig = field(default_factory=L.LossConfig)
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
 
@@ -71,7 +72,9 @@ class TrainActor:
         if self.optimizer is None:
             self._flatten_params()
         if with_reference:
-            self.backup("ref")
+            self.backup("ref", to_host=cfg.ref_on_host)
+            if cfg.ref_on_host and self.device.type == "cuda":
+                torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ tagged weights
     def _flatten_params(self):
@@ -118,6 +121,7 @@ class TrainActor:
             return
         if tag == "actor":
             buf = self.param_buf
+            self._stage = None      # staging copy of a host snapshot is only needed while it is bound
         else:
             buf = self.snapshots[tag]
             if not buf.is_cuda and self.device.type == "cuda":
