@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: override depth (result is then not comparable)")
     ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
     ap.add_argument("--kv-gb", type=float, default=None)
+    ap.add_argument("--no-fused-tp", action="store_true",
+                    help="A/B: use the NCCL statements instead of the fused GEMM+collective kernels (TP>1 only)")
     return ap.parse_args()
 
 
@@ -151,7 +153,8 @@ def main():
         trainer_tp=tp, rollout_tp=tp, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
         max_response_len=args.response_len, temperature=1.0, rm_type="parity", eos_token_id=None,
         kv_blocks=kv_blocks, kv_block_size=16, max_running=512, seed=0, rollout_seed=42,
-        offload_rollout=True, release_rollout_weights=True, pinned_prompts=True)
+        offload_rollout=True, release_rollout_weights=True, pinned_prompts=True,
+        fused_tp=not args.no_fused_tp)
     run = ColocatedGRPO(cfg, device=dev)
 
     def one_step():

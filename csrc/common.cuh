@@ -240,4 +240,39 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// ----------------------------------------------------------------------------- cross-GPU signalling
+// Counters that other GPUs bump through NVLink peer mappings.  A producer writes its payload with
+// plain stores, fences at system scope and then adds to the consumer's counter; the consumer polls
+// with acquire loads.  Every wait is bounded by wall time (the nanosecond global timer): when the
+// limit passes the caller records an error and leaves, so a missing peer cannot hang the GPU.
+__device__ __forceinline__ void sys_red_add(unsigned* addr, unsigned v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned sys_ld_acquire(const unsigned* addr) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits until (int)(*addr - target) >= 0.  Returns false after `limit_ns`.
+__device__ __forceinline__ bool sys_wait_ge(const unsigned* addr, unsigned target, unsigned long long limit_ns) {
+  if (static_cast<int>(sys_ld_acquire(addr) - target) >= 0) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (static_cast<int>(sys_ld_acquire(addr) - target) >= 0) return true;
+      __nanosleep(40);
+    }
+    if (global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 }  // namespace rb

@@ -48,10 +48,6 @@ struct DecodeTcParams {
   int* err;
 };
 
-__device__ __forceinline__ void named_bar_sync(int id, int n) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory");
-}
-
 __global__ void __launch_bounds__(DT_THREADS, 1)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                       const DecodeTcParams p) {

@@ -1,0 +1,60 @@
+// Bindings of the kernels that fuse a GEMM with its tensor-parallel collective over NVLink peer memory.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "api.h"
+
+namespace {
+inline cudaStream_t cur_stream() {
+  (void)cudaGetLastError();
+  return at::cuda::getCurrentCUDAStream().stream();
+}
+inline void check(int rc, const char* what) {
+  if (rc != 0) {
+    char buf[160];
+    snprintf(buf, sizeof(buf), "%s failed with code %d (%s)", what, rc, rc > 0 ? cudaGetErrorString((cudaError_t)rc) : "argument check");
+    throw std::runtime_error(buf);
+  }
+}
+
+std::tuple<int64_t, int64_t> gemm_ar_plan(int64_t M, int64_t N, int64_t K) {
+  int bn = 0;
+  const int s = rb_gemm_ar_plan((int)M, (int)N, (int)K, &bn);
+  return {s, bn};
+}
+
+// x [M,K] bf16, w [N,K] bf16 (this rank's K shard).  ws_ptrs / sig_ptrs: device addresses of every rank's
+// workspace / counters as mapped in this process.  Writes out_h (and out_x when norm_w is given).
+void gemm_ar_rmsnorm(torch::Tensor x, torch::Tensor w, std::vector<int64_t> ws_ptrs, std::vector<int64_t> sig_ptrs,
+                     int64_t tp_rank, torch::Tensor state, c10::optional<torch::Tensor> residual,
+                     c10::optional<torch::Tensor> norm_w, torch::Tensor out_h, c10::optional<torch::Tensor> out_x, double eps,
+                     int64_t splits, int64_t bn, bool reduce_scatter, bool w_is_kn, int64_t wait_ns, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: bf16");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out_h.is_contiguous(), "gemm_ar_rmsnorm: contiguous rows");
+  // w_is_kn: w is stored [K][N] (the dgrad form dy @ W); otherwise [N][K]
+  const int N = (int)(w_is_kn ? w.size(1) : w.size(0));
+  TORCH_CHECK(norm_w.has_value() == out_x.has_value(), "norm_w and out_x go together");
+  const int tp = (int)ws_ptrs.size();
+  TORCH_CHECK(tp >= 1 && tp <= 8 && sig_ptrs.size() == ws_ptrs.size());
+  float* ws[8];
+  unsigned* sg[8];
+  for (int r = 0; r < tp; ++r) {
+    ws[r] = reinterpret_cast<float*>(ws_ptrs[r]);
+    sg[r] = reinterpret_cast<unsigned*>(sig_ptrs[r]);
+  }
+  check(rb_gemm_ar_rmsnorm(x.data_ptr(), w.data_ptr(), (int)x.size(0), N, (int)x.size(1), (int)x.stride(0),
+                           (int)w.stride(0), tp, (int)tp_rank, ws, sg, state.data_ptr<int>(),
+                           residual.has_value() ? residual->data_ptr() : nullptr,
+                           norm_w.has_value() ? norm_w->data_ptr() : nullptr, out_h.data_ptr(),
+                           out_x.has_value() ? out_x->data_ptr() : nullptr, (float)eps, (int)splits, (int)bn,
+                           reduce_scatter ? 1 : 0, w_is_kn ? 1 : 0, (unsigned long long)wait_ns, err.data_ptr<int>(), cur_stream()),
+        "rb_gemm_ar_rmsnorm");
+}
+}  // namespace
+
+void register_fused(pybind11::module_& m) {
+  m.def("gemm_ar_plan", &gemm_ar_plan);
+  m.def("gemm_ar_rmsnorm", &gemm_ar_rmsnorm);
+}

@@ -42,9 +42,26 @@ struct GemmParams {
   const float* row_stats;    // MODE 2 in:  [M][2] = (log Z, sum p*z) of the temperature-scaled logits
   const float* g_lp;         // MODE 2 in:  [M] upstream gradient of log-prob
   const float* g_ent;        // MODE 2 in:  [M] upstream gradient of entropy (may be null)
+  // ---- MODE 3: row-parallel GEMM fused with its tensor-parallel all-reduce, the residual add and RMSNorm.
+  // Every rank stores its fp32 partial tiles straight into slot (parity, rank, k split) of EVERY
+  // rank's workspace through NVLink peer pointers, bumps a counter on every rank, waits (bounded)
+  // until all tiles of all ranks have landed in its own workspace and then reduces its own copy.
+  // Reduce-scatter form (rs != 0): row block r of the product belongs to rank r only, so a partial row
+  // goes to its owner alone and every rank reduces rows_out = M / tp rows; tiles are visited starting
+  // with the next rank's rows so that the transfers overlap the rest of the GEMM.
+  int tp, tp_rank, rs, rows_out, tm_rot;
+  float* peer_ws[8];         // workspace of rank r as mapped here: [2][tp][k_splits][rows_out][N] fp32
+  unsigned* peer_sig[8];     // arrival counters of rank r as mapped here: [2], one per parity
+  int* pr_state;             // local: [0] call sequence, [1..2] counter base per parity, [3] CTAs finished
+  const void* residual;      // [M][N] bf16 (may be null)
+  const void* norm_w;        // [N] bf16 (may be null: no norm output)
+  void* out_h;               // [M][N] bf16: residual + sum over ranks
+  void* out_x;               // [M][N] bf16: rmsnorm(out_h) * norm_w
+  float eps;
+  unsigned long long wait_ns;  // limit of the wait for the peers
 };
 
-enum : int { kEpiStore = 0, kEpiLogProb = 1, kEpiDLogits = 2 };
+enum : int { kEpiStore = 0, kEpiLogProb = 1, kEpiDLogits = 2, kEpiPeerReduce = 3 };
 
 template <int BN>
 struct GemmSmem {
@@ -83,6 +100,10 @@ __device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, i
     split = t % p.k_splits;
     t /= p.k_splits;
     tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+    if constexpr (MODE == kEpiPeerReduce) {
+      tm += p.tm_rot;
+      if (tm >= p.tiles_m) tm -= p.tiles_m;
+    }
     return true;
   }
 }
@@ -210,6 +231,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     float st_m = -1e30f, st_s = 0.f, st_u = 0.f, st_t = -INFINITY;
     int st_row = -1;
     if constexpr (MODE == kEpiLogProb) st_row = (blockIdx.x / p.n_splits) * BM + lane_grp * 32 + lane;
+    int pr_parity = 0;
+    if constexpr (MODE == kEpiPeerReduce) pr_parity = p.pr_state[0] & 1;
     for (int ti = 0;; ++ti) {
       int tm, tn, split;
       if (!next_tile<MODE>(p, ti, tm, tn, split)) break;
@@ -267,6 +290,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               r[i] = __float_as_uint(g * p.inv_temp);
             }
           }
+        }
+        if constexpr (MODE == kEpiPeerReduce) {
+          // fp32 partial tile -> slot (parity, my rank, k split) of EVERY rank's symmetric workspace
+          if (row < p.M && col + 32 <= p.N) {
+            const size_t slot = (static_cast<size_t>(pr_parity) * p.tp + p.tp_rank) * p.k_splits + split;
+            const int owner = p.rs ? row / p.rows_out : 0;
+            const int lrow = p.rs ? row - owner * p.rows_out : row;
+            const int r_hi = p.rs ? owner + 1 : p.tp;
+            const size_t off = (slot * p.rows_out + lrow) * p.N + col;
+#pragma unroll 1
+            for (int rk = owner; rk < r_hi; ++rk) {
+              float4* dst = reinterpret_cast<float4*>(p.peer_ws[rk] + off);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                                     __uint_as_float(r[4 * i + 3]));
+            }
+          }
+          continue;
         }
         if (row < p.M && col < p.N) {
           float v[32];
@@ -341,6 +383,87 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1;
+    }
+    if constexpr (MODE == kEpiPeerReduce) {
+      // ---- publish: this CTA's partial tiles are on their way to every rank
+      const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+      __threadfence_system();
+      named_bar_sync(1, 128);
+      if (et < p.tp && !*abort_flag) sys_red_add(p.peer_sig[et] + pr_parity, 1u);
+      // ---- wait until every CTA of every rank has published into THIS rank's workspace
+      const unsigned target = static_cast<unsigned>(p.pr_state[1 + pr_parity]) + static_cast<unsigned>(p.tp) * gridDim.x;
+      if (et == 0) {
+        if (!sys_wait_ge(p.peer_sig[p.tp_rank] + pr_parity, target, p.wait_ns)) {
+          *abort_flag = 1;
+          atomicExch(p.err, 3);
+        }
+      }
+      named_bar_sync(1, 128);
+      if (!*abort_flag) {
+        __threadfence_system();  // order the reads below after the acquire seen by thread 0
+        float* red = reinterpret_cast<float*>(smem);  // pipeline stages are idle by now (all tiles consumed)
+        const int slots = p.tp * p.k_splits;
+        const float* ws = p.peer_ws[p.tp_rank] + static_cast<size_t>(pr_parity) * slots * p.rows_out * p.N;
+        const size_t slot_stride = static_cast<size_t>(p.rows_out) * p.N;
+        for (int row = blockIdx.x; row < p.rows_out; row += gridDim.x) {
+          const size_t base = static_cast<size_t>(row) * p.N;
+          __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(p.out_h) + base;
+          float ss = 0.f;
+          for (int c = et * 4; c < p.N; c += 512) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < slots; ++s) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + s * slot_stride + base + c));
+              a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+            }
+            if (p.residual) {
+              const uint2 rr = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.residual) + base + c);
+              const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+              const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+              a.x += __low2float(r0); a.y += __high2float(r0); a.z += __low2float(r1); a.w += __high2float(r1);
+            }
+            uint2 pk;
+            pk.x = pack_bf16(a.x, a.y);
+            pk.y = pack_bf16(a.z, a.w);
+            *reinterpret_cast<uint2*>(oh + c) = pk;
+            const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&pk.x);
+            const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(&pk.y);
+            const float h0 = __low2float(q0), h1 = __high2float(q0), h2 = __low2float(q1), h3 = __high2float(q1);
+            ss += h0 * h0 + h1 * h1 + h2 * h2 + h3 * h3;
+          }
+          if (p.norm_w) {
+            ss = warp_sum(ss);
+            if (lane == 0) red[warp - 2] = ss;
+            named_bar_sync(1, 128);
+            const float rstd = rsqrtf((red[0] + red[1] + red[2] + red[3]) / p.N + p.eps);
+            named_bar_sync(1, 128);
+            __nv_bfloat16* ox = reinterpret_cast<__nv_bfloat16*>(p.out_x) + base;
+            const __nv_bfloat16* w = reinterpret_cast<const __nv_bfloat16*>(p.norm_w);
+            for (int c = et * 4; c < p.N; c += 512) {
+              const uint2 hh = *reinterpret_cast<const uint2*>(oh + c);  // this thread's own stores
+              const uint2 ww = *reinterpret_cast<const uint2*>(w + c);
+              const __nv_bfloat162 h0 = *reinterpret_cast<const __nv_bfloat162*>(&hh.x);
+              const __nv_bfloat162 h1 = *reinterpret_cast<const __nv_bfloat162*>(&hh.y);
+              const __nv_bfloat162 w0 = *reinterpret_cast<const __nv_bfloat162*>(&ww.x);
+              const __nv_bfloat162 w1 = *reinterpret_cast<const __nv_bfloat162*>(&ww.y);
+              uint2 pk;
+              pk.x = pack_bf16(__low2float(h0) * rstd * __low2float(w0), __high2float(h0) * rstd * __high2float(w0));
+              pk.y = pack_bf16(__low2float(h1) * rstd * __low2float(w1), __high2float(h1) * rstd * __high2float(w1));
+              *reinterpret_cast<uint2*>(ox + c) = pk;
+            }
+          }
+        }
+      }
+      // ---- the last CTA of this rank to finish advances the call state for the next launch
+      named_bar_sync(1, 128);
+      if (et == 0) {
+        __threadfence();
+        if (atomicAdd(p.pr_state + 3, 1) == static_cast<int>(gridDim.x) - 1) {
+          p.pr_state[3] = 0;
+          p.pr_state[1 + pr_parity] = static_cast<int>(target);
+          p.pr_state[0] = p.pr_state[0] + 1;
+          __threadfence();
+        }
+      }
     }
     if constexpr (MODE == kEpiLogProb) {
       if (st_row >= 0 && st_row < p.M) {
@@ -572,4 +695,63 @@ extern "C" int rb_gemm_splitk(const void* A, const void* B, void* C, const void*
   else splitk_reduce_kernel<true><<<(int)blocks, 256, 0, stream>>>(workspace, C, bias, residual, M, N, splits, ldc);
   rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
+}
+
+// ----------------------------------------------------------------------------- GEMM + all-reduce + residual + RMSNorm
+// Plan of the fused row-parallel GEMM (decode: M <= a few hundred rows): N tile and K splits.  Every rank
+// calls it with the same shapes and so gets the same plan (the workspace slot layout depends on it).
+extern "C" int rb_gemm_ar_plan(int M, int N, int K, int* bn_out) {
+  using namespace rb;
+  const int tm = (M + BM - 1) / BM;
+  const int bn = (N % 64 == 0) ? 64 : 32;
+  const int tiles = tm * (N / bn);
+  const int kit = (K + BK - 1) / BK;
+  int splits = num_sms() / (tiles > 0 ? tiles : 1);
+  if (splits > kit / 8) splits = kit / 8;
+  if (splits > 4) splits = 4;
+  if (splits < 1) splits = 1;
+  *bn_out = bn;
+  return splits;
+}
+
+// out_h = residual + sum_r A_r B_r^T ; out_x = rmsnorm(out_h) * norm_w, with the sum over the `tp` ranks done
+// inside the kernel over peer memory.  A [M][K] and B [N][K] are this rank's K shards (bf16, K-major).
+// peer_ws / peer_sig: host arrays of `tp` device pointers (rank r's workspace / counters as mapped in this
+// process).  The workspace holds 2*tp*splits*rows_out*N floats (rows_out = M, or M/tp when reduce_scatter).
+// reduce_scatter: rank r keeps rows [r*M/tp, (r+1)*M/tp) only; out_h is then [M/tp][N].  state: 4 ints of this rank, zero at set-up.
+extern "C" int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int tp, int tp_rank,
+                                  float* const* peer_ws, unsigned* const* peer_sig, int* state, const void* residual,
+                                  const void* norm_w, void* out_h, void* out_x, float eps, int splits, int bn,
+                                  int reduce_scatter, int b_mn_major, unsigned long long wait_ns, int* err_flag,
+                                  cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tp < 1 || tp > 8 || tp_rank < 0 || tp_rank >= tp) return -4;
+  if (reduce_scatter && (M % tp)) return -5;
+  if (b_mn_major && bn < 64) return -3;
+  if ((lda % 8) || (ldb % 8) || (N % 32) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16)) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = N;
+  p.lbo_a = p.lbo_b = BK * 128; p.sbo_a = p.sbo_b = 1024;
+  p.err = err_flag; p.k_splits = splits;
+  p.tp = tp; p.tp_rank = tp_rank;
+  p.rs = reduce_scatter; p.rows_out = reduce_scatter ? M / tp : M; p.b_mn = b_mn_major;
+  if (reduce_scatter) {
+    // start with the rows of rank+1, finish with this rank's own rows
+    const int tiles_m = (M + BM - 1) / BM;
+    p.tm_rot = static_cast<int>((static_cast<long long>((tp_rank + 1) % tp) * p.rows_out) / BM) % tiles_m;
+  }
+  for (int r = 0; r < tp; ++r) { p.peer_ws[r] = peer_ws[r]; p.peer_sig[r] = peer_sig[r]; }
+  p.pr_state = state; p.residual = residual; p.norm_w = norm_w; p.out_h = out_h; p.out_x = out_x; p.eps = eps;
+  p.wait_ns = wait_ns;
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, A, false, M, K, lda, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, B, b_mn_major != 0, N, K, ldb, bn);
+  if (rc) return rc;
+  if (bn == 256) return launch<256, true, kEpiPeerReduce>(ta, tb, p, stream);
+  if (bn == 128) return launch<128, true, kEpiPeerReduce>(ta, tb, p, stream);
+  if (bn == 64) return launch<64, true, kEpiPeerReduce>(ta, tb, p, stream);
+  if (bn == 32) return launch<32, true, kEpiPeerReduce>(ta, tb, p, stream);
+  return -3;
 }

@@ -63,6 +63,10 @@ class ColocateConfig:
     # role runs (they are rewritten by the weight sync / zeroed before backward anyway)
     release_rollout_weights: bool = False
     pinned_prompts: bool = False
+    # fuse tensor-parallel GEMMs with their collectives over NVLink peer memory (needs all ranks of a
+    # TP group on one node); the symmetric workspace is allocated once per TP group
+    fused_tp: bool = True
+    fused_workspace_mb: int = 512
     num_prompts: int = 1 << 14
 
 
@@ -91,6 +95,16 @@ class ColocatedGRPO:
                 if e == self.engine_id:
                     eng_group = g
         self.rollout_tp_group = GroupInfo(eng_group, eng_ranks, self.rank % rtp)
+        self.fused_comms = []
+        if cfg.fused_tp and self.device.type == "cuda":
+            from ..ops import fused_comm
+            from ..parallel.symm_mem import attach_group
+
+            for g in (self.rollout_tp_group, self.ps.tp):
+                if g.size > 1 and fused_comm.comm_of(g) is None:
+                    c = attach_group(g, self.device, cfg.fused_workspace_mb)
+                    if c is not None:
+                        self.fused_comms.append(c)
 
         need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
         cfg.train.n_samples_per_prompt = cfg.train.n_samples_per_prompt

@@ -40,13 +40,28 @@ def _ar(x, g: GroupInfo):
     return x
 
 
-def _fused_enabled(x, g=None) -> bool:
+def _fused_enabled(x, g=None, op: str = "") -> bool:
+    """Whether ``op`` runs as one fused kernel for group ``g``: CUDA tensors, a symmetric-memory
+    communicator attached to the group that implements the operator, and not switched off."""
     if not (x.is_cuda and os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") != "1" and
             os.environ.get("RELAX_B200_FUSED_TP", "1") == "1"):
         return False
     from ..ops import fused_comm
 
-    return g is not None and fused_comm.enabled_for(g)
+    comm = fused_comm.comm_of(g) if g is not None else None
+    return comm is not None and comm.supports(op)
+
+
+def _rs_of_product(x, w, g: GroupInfo, w_is_kn: bool):
+    """reduce_scatter(x @ w.T) (or x @ w when ``w_is_kn``): fused over peer memory when available."""
+    if g.size > 1 and _fused_enabled(x, g, "gemm_rs") and x.shape[0] % (g.size * 128) == 0:
+        from ..ops import fused_comm
+
+        comm = fused_comm.comm_of(g)
+        n = w.shape[1] if w_is_kn else w.shape[0]
+        if comm.fits_rs(x.shape[0], n):
+            return comm.gemm_rs(x.contiguous(), w, w_is_kn)
+    return _rs(ops.dgrad(x, w) if w_is_kn else ops.linear(x, w), g)
 
 
 class _AGLinear(torch.autograd.Function):
@@ -55,7 +70,7 @@ class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, g):
         ctx.g = g
-        if g.size > 1 and _fused_enabled(x, g):
+        if g.size > 1 and _fused_enabled(x, g, "ag_gemm"):
             from ..ops import fused_comm
 
             y, xf = fused_comm.ag_gemm(x, w, g)
@@ -71,7 +86,7 @@ class _AGLinear(torch.autograd.Function):
         g = ctx.g
         dy = dy.contiguous()
         xf = _ag(x, g)  # re-gather instead of keeping T*tp activations alive
-        dx = _rs(ops.dgrad(dy, w), g)
+        dx = _rs_of_product(dy, w, g, True)
         dw = ops.wgrad(dy, xf, w)
         return dx, dw, None
 
@@ -83,11 +98,7 @@ class _LinearRS(torch.autograd.Function):
     def forward(ctx, x, w, g):
         ctx.g = g
         ctx.save_for_backward(x, w)
-        if g.size > 1 and _fused_enabled(x, g):
-            from ..ops import fused_comm
-
-            return fused_comm.gemm_rs(x, w, g)
-        return _rs(ops.linear(x, w), g)
+        return _rs_of_product(x, w, g, False)
 
     @staticmethod
     def backward(ctx, dy):

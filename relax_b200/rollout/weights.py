@@ -132,12 +132,26 @@ class RolloutWeights:
         a = ops.swiglu(ops.linear(x, p[pre + "gate_up"]))
         return ops.linear(a, p[pre + "down"]), tp.size > 1
 
-    def _layer(self, i, h, cos, sin, attn, tp):
+    def _fused(self, tp: GroupInfo, rows: int, n: int):
+        """The symmetric-memory communicator of ``tp`` when the fused GEMM + all-reduce + residual +
+        RMSNorm kernel can take a call of this size, else None (NCCL statement)."""
+        if tp.size <= 1:
+            return None
+        from ..ops import fused_comm
+
+        comm = fused_comm.comm_of(tp)
+        if comm is None or not comm.supports("gemm_ar_add_rmsnorm") or not comm.fits(rows, n):
+            return None
+        return comm
+
+    def _layer(self, i, h, x, cos, sin, attn, tp, next_norm):
+        """One decoder layer.  ``h`` is the residual stream, ``x`` its normed copy (input of the attention
+        block); returns the new ``(h, x)`` where ``x`` is already normed with ``next_norm`` (the next layer's
+        input norm or the final norm), so every residual add is fused with the norm that follows it."""
         cfg, p = self.cfg, self.p
         pre = f"layers.{i}."
         hd = cfg.head_dim
         nq, nkv = cfg.num_attention_heads // self.tp_size, cfg.num_query_groups // self.tp_size
-        x = ops.rmsnorm(h, p[pre + "input_norm"], cfg.rms_norm_eps)
         qkv = ops.linear(x, p[pre + "qkv"], p.get(pre + "qkv_bias"))
         T = qkv.shape[0]
         q = qkv[:, : nq * hd].reshape(T, nq, hd)
@@ -148,20 +162,30 @@ class RolloutWeights:
             k = ops.rmsnorm(k, p[pre + "k_norm"], cfg.rms_norm_eps)
         q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
         o = attn(i, q, k, v).reshape(T, nq * hd)
-        a = self._allreduce(ops.linear(o, p[pre + "o"]), tp)
-        x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
+        comm = self._fused(tp, T, cfg.hidden_size)
+        if comm is not None:
+            h, x = comm.gemm_ar_add_rmsnorm(o, p[pre + "o"], h, p[pre + "post_norm"], cfg.rms_norm_eps)
+        else:
+            a = self._allreduce(ops.linear(o, p[pre + "o"]), tp)
+            x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
+        if comm is not None and (pre + "router") not in p:
+            a = ops.swiglu(ops.linear(x, p[pre + "gate_up"]))
+            return comm.gemm_ar_add_rmsnorm(a, p[pre + "down"], h, next_norm, cfg.rms_norm_eps)
         m, need_ar = self._mlp(i, x, tp)
         if need_ar:
             m = self._allreduce(m, tp)
-        return h + m
+        x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
+        return h, x
 
     def _run(self, tokens, positions, attn, tp):
-        cfg = self.cfg
+        cfg, p = self.cfg, self.p
         h = self._embed(tokens, tp)
         cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        x = ops.rmsnorm(h, p["layers.0.input_norm"], cfg.rms_norm_eps)
         for i in range(cfg.num_layers):
-            h = self._layer(i, h, cos, sin, attn, tp)
-        return ops.rmsnorm(h, self.p["final_norm"], cfg.rms_norm_eps)
+            nxt = p[f"layers.{i + 1}.input_norm"] if i + 1 < cfg.num_layers else p["final_norm"]
+            h, x = self._layer(i, h, x, cos, sin, attn, tp, nxt)
+        return x
 
     # ------------------------------------------------------------------ entry points
     def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):

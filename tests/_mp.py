@@ -1,4 +1,4 @@
-"""Spawn helper: run ``fn(rank, world, *args)`` in ``world`` gloo processes."""
+"""Spawn helper: run ``fn(rank, world, *args)`` in ``world`` processes (gloo on CPU, or NCCL with one GPU each)."""
 import os
 import socket
 import traceback
@@ -16,12 +16,16 @@ def _free_port():
     return p
 
 
-def _entry(rank, world, port, fn, args, q):
+def _entry(rank, world, port, fn, args, q, backend="gloo"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.set_num_threads(1)
     try:
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
         out = fn(rank, world, *args)
         q.put((rank, "ok", out))
     except Exception:  # noqa: BLE001
@@ -31,11 +35,11 @@ def _entry(rank, world, port, fn, args, q):
             dist.destroy_process_group()
 
 
-def run_distributed(fn, world, *args, timeout=300):
+def run_distributed(fn, world, *args, timeout=300, backend="gloo"):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, backend)) for r in range(world)]
     for p in procs:
         p.start()
     res = {}

@@ -1,0 +1,148 @@
+"""Fused GEMM + collective kernels over NVLink peer memory (2 GPUs), against an fp32 statement of the
+same math, and the bounded wait of the peer protocol (1 GPU, a counter that nothing bumps)."""
+import os
+
+import pytest
+import torch
+
+from tests._mp import run_distributed
+
+pytestmark = pytest.mark.gpu
+
+
+def _two_gpus():
+    return torch.cuda.is_available() and torch.cuda.device_count() >= 2
+
+
+def _group(world):
+    import torch.distributed as dist
+    from relax_b200.parallel.state import GroupInfo
+
+    return GroupInfo(group=dist.group.WORLD, ranks=tuple(range(world)), rank=dist.get_rank())
+
+
+def _inputs(step, rank_of, M, N, K, dev):
+    g = torch.Generator(device="cpu").manual_seed(1000 * step + rank_of)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+    return x, w
+
+
+def _ar_worker(rank, world, shapes, graph):
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.symm_mem import SymmComm
+
+    dev = torch.device("cuda", rank)
+    comm = SymmComm(_group(world), dev, workspace_mb=64)
+    worst = 0.0
+    step = 0
+    for (M, N, K) in shapes:
+        for rep in range(3):
+            step += 1
+            g = torch.Generator(device="cpu").manual_seed(7 + step)
+            res = torch.randn(M, N, generator=g).to(torch.bfloat16).to(dev)
+            nw = (1 + 0.1 * torch.randn(N, generator=g)).to(torch.bfloat16).to(dev)
+            x, w = _inputs(step, rank, M, N, K, dev)
+            h, y = comm.gemm_ar_add_rmsnorm(x, w, res, nw, 1e-6)
+            ref = res.float()
+            for r in range(world):
+                xr, wr = _inputs(step, r, M, N, K, dev)
+                ref = ref + xr.float() @ wr.float().t()
+            ref_h = ref.to(torch.bfloat16).float()
+            ref_y = ref_h * torch.rsqrt(ref_h.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+            C.check_error_flag(dev)
+            worst = max(worst, (h.float() - ref_h).abs().max().item(), (y.float() - ref_y).abs().max().item())
+    if graph:
+        M, N, K = shapes[0]
+        x, w = _inputs(99, rank, M, N, K, dev)
+        res = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        s = torch.cuda.Stream(dev)
+        with torch.cuda.stream(s):
+            comm.gemm_ar_add_rmsnorm(x, w, res, None, 0.0)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=s):
+                h1, _ = comm.gemm_ar_add_rmsnorm(x, w, res, None, 0.0)
+                h2, _ = comm.gemm_ar_add_rmsnorm(h1[:, :K].contiguous(), w, res, None, 0.0)
+            for _ in range(5):
+                gr.replay()
+        torch.cuda.synchronize(dev)
+        C.check_error_flag(dev)
+        ref = sum((_inputs(99, r, M, N, K, dev)[0].float() @ _inputs(99, r, M, N, K, dev)[1].float().t()) for r in range(world))
+        worst = max(worst, (h1.float() - ref.to(torch.bfloat16).float()).abs().max().item())
+    torch.cuda.synchronize(dev)
+    comm.close()
+    return worst
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_gemm_allreduce_residual_rmsnorm_two_ranks():
+    shapes = [(80, 1024, 512), (16, 4096, 2048), (200, 512, 1536), (1024, 1024, 256)]
+    worst = run_distributed(_ar_worker, 2, shapes, True, backend="nccl", timeout=600)
+    assert max(worst) < 0.08, worst
+
+
+def _rs_worker(rank, world, shapes):
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.symm_mem import SymmComm
+
+    dev = torch.device("cuda", rank)
+    comm = SymmComm(_group(world), dev, workspace_mb=64)
+    worst = 0.0
+    step = 100
+    for (M, N, K, kn) in shapes:
+        for rep in range(2):
+            step += 1
+            x, w = _inputs(step, rank, M, N, K, dev)
+            wk = w.t().contiguous() if kn else w
+            y = comm.gemm_rs(x, wk, w_is_kn=kn)
+            ref = 0
+            for r in range(world):
+                xr, wr = _inputs(step, r, M, N, K, dev)
+                ref = ref + xr.float() @ wr.float().t()
+            rows = M // world
+            ref = ref[rank * rows:(rank + 1) * rows]
+            C.check_error_flag(dev)
+            worst = max(worst, (y.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item()))
+    torch.cuda.synchronize(dev)
+    comm.close()
+    return worst
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_gemm_reduce_scatter_two_ranks():
+    shapes = [(512, 1024, 512, False), (2048, 512, 1024, False), (1024, 768, 512, True)]
+    worst = run_distributed(_rs_worker, 2, shapes, backend="nccl", timeout=600)
+    assert max(worst) < 0.02, worst
+
+
+def test_peer_wait_runs_out_and_reports():
+    """A claimed second rank that never launches: the wait for its arrivals expires, the kernel sets the error
+    flag and returns, and the context stays usable."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from relax_b200.ops import cuda as C
+
+    dev = torch.device("cuda", 0)
+    _C = C._load()
+    ws0 = _C.symm_alloc(8 << 20, 0)
+    ws1 = _C.symm_alloc(8 << 20, 0)
+    sg0 = _C.symm_alloc(1024, 0)
+    sg1 = _C.symm_alloc(1024, 0)
+    try:
+        M, N, K = 32, 256, 256
+        x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+        w = torch.randn(N, K, device=dev).to(torch.bfloat16)
+        state = torch.zeros(8, dtype=torch.int32, device=dev)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        err = C.err_flag(dev)
+        _C.gemm_ar_rmsnorm(x, w, [ws0, ws1], [sg0, sg1], 0, state, None, None, out, None, 0.0, 1, 64, False, False,
+                           200_000_000, err)
+        torch.cuda.synchronize(dev)
+        assert int(err.item()) == 3
+        err.zero_()
+        # the context still works
+        y = C.matmul_nt(x, w)
+        torch.testing.assert_close(y.float(), x.float() @ w.float().t(), atol=0.5, rtol=0.05)
+    finally:
+        for p in (ws0, ws1, sg0, sg1):
+            _C.symm_free(p, 0)
