@@ -76,8 +76,11 @@ int rb_gemm_ar_plan(int M, int N, int K, int* bn_out);
 int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int tp, int tp_rank,
                        float* const* peer_ws, unsigned* const* peer_sig, int* state, const void* residual,
                        const void* norm_w, void* out_h, void* out_x, float eps, int splits, int bn,
-                       int reduce_scatter, int b_mn_major, unsigned long long wait_ns, int* err_flag,
-                       cudaStream_t stream);
+                       int reduce_scatter, int b_mn_major, unsigned long long wait_ns, unsigned long long* timeline,
+                       int* err_flag, cudaStream_t stream);
+int rb_ag_gemm(const void* x_shard, const void* B, void* C, int M, int N, int K, int ldb, int ldc, int tp, int tp_rank,
+               void* const* peer_ag, unsigned* const* peer_sig, int* state, int bn, unsigned long long wait_ns,
+               int* err_flag, cudaStream_t stream);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

@@ -29,7 +29,8 @@ std::tuple<int64_t, int64_t> gemm_ar_plan(int64_t M, int64_t N, int64_t K) {
 void gemm_ar_rmsnorm(torch::Tensor x, torch::Tensor w, std::vector<int64_t> ws_ptrs, std::vector<int64_t> sig_ptrs,
                      int64_t tp_rank, torch::Tensor state, c10::optional<torch::Tensor> residual,
                      c10::optional<torch::Tensor> norm_w, torch::Tensor out_h, c10::optional<torch::Tensor> out_x, double eps,
-                     int64_t splits, int64_t bn, bool reduce_scatter, bool w_is_kn, int64_t wait_ns, torch::Tensor err) {
+                     int64_t splits, int64_t bn, bool reduce_scatter, bool w_is_kn, int64_t wait_ns, torch::Tensor err,
+                     c10::optional<torch::Tensor> timeline) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "gemm_ar_rmsnorm: bf16");
   TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out_h.is_contiguous(), "gemm_ar_rmsnorm: contiguous rows");
@@ -49,12 +50,40 @@ void gemm_ar_rmsnorm(torch::Tensor x, torch::Tensor w, std::vector<int64_t> ws_p
                            residual.has_value() ? residual->data_ptr() : nullptr,
                            norm_w.has_value() ? norm_w->data_ptr() : nullptr, out_h.data_ptr(),
                            out_x.has_value() ? out_x->data_ptr() : nullptr, (float)eps, (int)splits, (int)bn,
-                           reduce_scatter ? 1 : 0, w_is_kn ? 1 : 0, (unsigned long long)wait_ns, err.data_ptr<int>(), cur_stream()),
+                           reduce_scatter ? 1 : 0, w_is_kn ? 1 : 0, (unsigned long long)wait_ns,
+                           timeline.has_value() ? reinterpret_cast<unsigned long long*>(timeline->data_ptr<int64_t>()) : nullptr,
+                           err.data_ptr<int>(), cur_stream()),
         "rb_gemm_ar_rmsnorm");
+}
+
+// x_shard [M/tp, K] bf16 contiguous, w [N, K] bf16; y [M, N].  ag_ptrs: every rank's gathered buffer ([2][M][K]).
+void ag_gemm(torch::Tensor x_shard, torch::Tensor w, torch::Tensor y, std::vector<int64_t> ag_ptrs,
+             std::vector<int64_t> sig_ptrs, int64_t tp_rank, torch::Tensor state, int64_t bn, int64_t wait_ns,
+             torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(x_shard.device());
+  TORCH_CHECK(x_shard.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16, "ag_gemm: bf16");
+  TORCH_CHECK(x_shard.is_contiguous() && w.stride(1) == 1 && y.stride(1) == 1, "ag_gemm: contiguous rows");
+  const int tp = (int)ag_ptrs.size();
+  TORCH_CHECK(tp >= 1 && tp <= 8 && sig_ptrs.size() == ag_ptrs.size() && state.numel() >= 12);
+  void* ag[8];
+  unsigned* sg[8];
+  for (int r = 0; r < tp; ++r) {
+    ag[r] = reinterpret_cast<void*>(ag_ptrs[r]);
+    sg[r] = reinterpret_cast<unsigned*>(sig_ptrs[r]);
+  }
+  check(rb_ag_gemm(x_shard.data_ptr(), w.data_ptr(), y.data_ptr(), (int)x_shard.size(0) * tp, (int)w.size(0),
+                   (int)x_shard.size(1), (int)w.stride(0), (int)y.stride(0), tp, (int)tp_rank, ag, sg,
+                   state.data_ptr<int>(), (int)bn, (unsigned long long)wait_ns, err.data_ptr<int>(), cur_stream()),
+        "rb_ag_gemm");
 }
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
   m.def("gemm_ar_plan", &gemm_ar_plan);
-  m.def("gemm_ar_rmsnorm", &gemm_ar_rmsnorm);
+  m.def("ag_gemm", &ag_gemm);
+  m.def("gemm_ar_rmsnorm", &gemm_ar_rmsnorm, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("ws_ptrs"),
+        pybind11::arg("sig_ptrs"), pybind11::arg("tp_rank"), pybind11::arg("state"), pybind11::arg("residual"),
+        pybind11::arg("norm_w"), pybind11::arg("out_h"), pybind11::arg("out_x"), pybind11::arg("eps"),
+        pybind11::arg("splits"), pybind11::arg("bn"), pybind11::arg("reduce_scatter"), pybind11::arg("w_is_kn"),
+        pybind11::arg("wait_ns"), pybind11::arg("err"), pybind11::arg("timeline") = c10::optional<torch::Tensor>());
 }

@@ -21,6 +21,8 @@ namespace rb {
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int GEMM_THREADS = 192;
+constexpr int kStagePitch = 36;                          // floats per staged row (32 + 4: conflict-free float4 access)
+constexpr int kStageBytes4 = 4 * 32 * kStagePitch * 4;   // per-warp 32x32 fp32 staging of the peer-reduce epilogue
 
 struct GemmParams {
   int M, N, K;
@@ -59,9 +61,16 @@ struct GemmParams {
   void* out_x;               // [M][N] bf16: rmsnorm(out_h) * norm_w
   float eps;
   unsigned long long wait_ns;  // limit of the wait for the peers
+  // ---- MODE 4: all-gather of the A row shards fused into the GEMM.  The epilogue warps first push this rank's
+  // shard into every peer's gathered buffer (double buffered by call parity) and signal; the TMA producer
+  // starts with this rank's own rows and waits (bounded) for a peer's arrival count before its rows.
+  void* peer_ag[8];          // gathered buffer of rank r as mapped here: [2][M][K] bf16
+  const void* ag_src;        // this rank's shard [M/tp][K], contiguous
+  int ag_rows;               // M / tp
+  unsigned long long* timeline;  // optional [grid][8] global-timer stamps of the phases (profiling aid)
 };
 
-enum : int { kEpiStore = 0, kEpiLogProb = 1, kEpiDLogits = 2, kEpiPeerReduce = 3 };
+enum : int { kEpiStore = 0, kEpiLogProb = 1, kEpiDLogits = 2, kEpiPeerReduce = 3, kEpiAllGather = 4 };
 
 template <int BN>
 struct GemmSmem {
@@ -100,7 +109,7 @@ __device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, i
     split = t % p.k_splits;
     t /= p.k_splits;
     tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
-    if constexpr (MODE == kEpiPeerReduce) {
+    if constexpr (MODE == kEpiPeerReduce || MODE == kEpiAllGather) {
       tm += p.tm_rot;
       if (tm >= p.tiles_m) tm -= p.tiles_m;
     }
@@ -110,7 +119,8 @@ __device__ __forceinline__ bool next_tile(const GemmParams& p, int i, int& tm, i
 
 template <int BN, bool BF16, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+            const __grid_constant__ CUtensorMap tma_g, const GemmParams p) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   constexpr int kTmemCols = (2 * BN <= 32) ? 32 : 2 * BN;
@@ -156,17 +166,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+      // MODE 4 state: parity of this call, arrival target, sources already seen complete
+      int ag_parity = 0;
+      unsigned ag_target = 0, ag_ready = 0;
+      if constexpr (MODE == kEpiAllGather) {
+        tma_prefetch_desc(&tma_g);
+        ag_parity = p.pr_state[8] & 1;
+        ag_target = static_cast<unsigned>(p.pr_state[9 + ag_parity]) + gridDim.x;
+        ag_ready = 1u << p.tp_rank;
+      }
       for (int ti = 0; ok; ++ti) {
         int tm, tn, split;
         if (!next_tile<MODE>(p, ti, tm, tn, split)) break;
         const int m0 = tm * BM, n0 = tn * BN;
+        int ag_src_rank = 0;
+        if constexpr (MODE == kEpiAllGather) {
+          ag_src_rank = m0 / p.ag_rows;
+          if (!((ag_ready >> ag_src_rank) & 1u)) {
+            if (!sys_wait_ge(p.peer_sig[p.tp_rank] + 16 + ag_parity * 8 + ag_src_rank, ag_target, p.wait_ns)) {
+              *abort_flag = 1;
+              atomicExch(p.err, 3);
+              break;
+            }
+            fence_proxy_async_global();
+            ag_ready |= 1u << ag_src_rank;
+          }
+        }
         const int k_lo = split * p.k_iters_per_split, k_hi = min(k_iters_total, k_lo + p.k_iters_per_split);
         for (int k = k_lo; k < k_hi; ++k) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
           uint8_t* sa = smem + s * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
           mbar_expect_tx(&full_bar[s], S::kStageBytes);
-          if (!p.a_mn) {
+          if constexpr (MODE == kEpiAllGather) {
+            if (ag_src_rank == p.tp_rank) tma_load_2d(sa, &tma_a, &full_bar[s], k * BK, m0 - p.tp_rank * p.ag_rows);
+            else tma_load_2d(sa, &tma_g, &full_bar[s], k * BK, ag_parity * p.M + m0);
+          } else if (!p.a_mn) {
             tma_load_2d(sa, &tma_a, &full_bar[s], k * BK, m0);
           } else {
 #pragma unroll
@@ -232,7 +267,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     int st_row = -1;
     if constexpr (MODE == kEpiLogProb) st_row = (blockIdx.x / p.n_splits) * BM + lane_grp * 32 + lane;
     int pr_parity = 0;
-    if constexpr (MODE == kEpiPeerReduce) pr_parity = p.pr_state[0] & 1;
+    if constexpr (MODE == kEpiPeerReduce) {
+      pr_parity = p.pr_state[0] & 1;
+      if (p.timeline && threadIdx.x == 64) p.timeline[blockIdx.x * 8 + 0] = global_timer_ns();
+    }
+    if constexpr (MODE == kEpiAllGather) {
+      // ---- push this rank's shard to the peers while the first tiles (own rows) are being computed
+      const int et = threadIdx.x - 64;
+      const int parity = p.pr_state[8] & 1;
+      const long long total = static_cast<long long>(p.ag_rows) * p.K / 8;  // 16-byte vectors
+      const long long per = (total + gridDim.x - 1) / gridDim.x;
+      const long long lo = per * blockIdx.x, hi = (lo + per < total) ? lo + per : total;
+      const uint4* src = reinterpret_cast<const uint4*>(p.ag_src);
+      const long long dst_off = (static_cast<long long>(parity) * p.M + static_cast<long long>(p.tp_rank) * p.ag_rows) * p.K / 8;
+      for (int rk = 1; rk < p.tp; ++rk) {
+        const int dst_rank = (p.tp_rank + rk) % p.tp;
+        uint4* dst = reinterpret_cast<uint4*>(p.peer_ag[dst_rank]) + dst_off;
+        long long i = lo + et;
+        for (; i + 3 * 128 < hi; i += 4 * 128) {
+          const uint4 v0 = __ldg(src + i), v1 = __ldg(src + i + 128), v2 = __ldg(src + i + 256), v3 = __ldg(src + i + 384);
+          dst[i] = v0; dst[i + 128] = v1; dst[i + 256] = v2; dst[i + 384] = v3;
+        }
+        for (; i < hi; i += 128) dst[i] = __ldg(src + i);
+      }
+      named_bar_sync(1, 128);
+      if (et < p.tp && et != p.tp_rank) sys_red_add(p.peer_sig[et] + 16 + parity * 8 + p.tp_rank, 1u);
+    }
     for (int ti = 0;; ++ti) {
       int tm, tn, split;
       if (!next_tile<MODE>(p, ti, tm, tn, split)) break;
@@ -293,21 +353,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         if constexpr (MODE == kEpiPeerReduce) {
           // fp32 partial tile -> slot (parity, my rank, k split) of EVERY rank's symmetric workspace
-          if (row < p.M && col + 32 <= p.N) {
-            const size_t slot = (static_cast<size_t>(pr_parity) * p.tp + p.tp_rank) * p.k_splits + split;
-            const int owner = p.rs ? row / p.rows_out : 0;
-            const int lrow = p.rs ? row - owner * p.rows_out : row;
-            const int r_hi = p.rs ? owner + 1 : p.tp;
-            const size_t off = (slot * p.rows_out + lrow) * p.N + col;
-#pragma unroll 1
-            for (int rk = owner; rk < r_hi; ++rk) {
-              float4* dst = reinterpret_cast<float4*>(p.peer_ws[rk] + off);
+          // Transpose the warp's 32x32 fp32 block through shared memory so that every store instruction
+          // writes whole 128-byte rows (4 rows x 8 lanes x 16 bytes): peer stores over NVLink need full lines.
+          float* stg = reinterpret_cast<float*>(smem + S::kBarOffset + 256) + (warp - 2) * (32 * kStagePitch);
 #pragma unroll
-              for (int i = 0; i < 8; ++i)
-                dst[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
-                                     __uint_as_float(r[4 * i + 3]));
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(stg + lane * kStagePitch + 4 * i) =
+                make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]), __uint_as_float(r[4 * i + 2]),
+                            __uint_as_float(r[4 * i + 3]));
+          __syncwarp();
+          if (col + 32 <= p.N) {
+            const size_t slot = (static_cast<size_t>(pr_parity) * p.tp + p.tp_rank) * p.k_splits + split;
+            const int row0 = tm * BM + lane_grp * 32;
+            const int sub = lane >> 3, c4 = (lane & 7) * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int rr = j * 4 + sub;
+              const int grow = row0 + rr;
+              if (grow < p.M) {
+                const float4 val = *reinterpret_cast<const float4*>(stg + rr * kStagePitch + c4);
+                const int owner = p.rs ? grow / p.rows_out : 0;
+                const int lrow = p.rs ? grow - owner * p.rows_out : grow;
+                const int r_hi = p.rs ? owner + 1 : p.tp;
+                const size_t off = (slot * p.rows_out + lrow) * p.N + col + c4;
+                for (int rk = owner; rk < r_hi; ++rk) *reinterpret_cast<float4*>(p.peer_ws[rk] + off) = val;
+              }
             }
           }
+          __syncwarp();
           continue;
         }
         if (row < p.M && col < p.N) {
@@ -387,9 +460,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     if constexpr (MODE == kEpiPeerReduce) {
       // ---- publish: this CTA's partial tiles are on their way to every rank
       const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
-      __threadfence_system();
+      unsigned long long* tl = (p.timeline && et == 0) ? p.timeline + blockIdx.x * 8 : nullptr;
+      if (tl) tl[1] = global_timer_ns();
+      // All stores of the 128 epilogue threads are ordered before the barrier; the signalling threads
+      // (one per destination, in parallel) then release at system scope, which is cumulative over them.
       named_bar_sync(1, 128);
+      if (tl) tl[2] = global_timer_ns();
       if (et < p.tp && !*abort_flag) sys_red_add(p.peer_sig[et] + pr_parity, 1u);
+      if (tl) tl[3] = global_timer_ns();
       // ---- wait until every CTA of every rank has published into THIS rank's workspace
       const unsigned target = static_cast<unsigned>(p.pr_state[1 + pr_parity]) + static_cast<unsigned>(p.tp) * gridDim.x;
       if (et == 0) {
@@ -399,6 +477,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
       }
       named_bar_sync(1, 128);
+      if (tl) tl[4] = global_timer_ns();
       if (!*abort_flag) {
         __threadfence_system();  // order the reads below after the acquire seen by thread 0
         float* red = reinterpret_cast<float*>(smem);  // pipeline stages are idle by now (all tiles consumed)
@@ -409,26 +488,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           const size_t base = static_cast<size_t>(row) * p.N;
           __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(p.out_h) + base;
           float ss = 0.f;
-          for (int c = et * 4; c < p.N; c += 512) {
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          // 8 column chunks per pass so that 8 independent 16-byte loads are in flight per slot
+          for (int c0 = et * 4; c0 < p.N; c0 += 512 * 8) {
+            float4 a[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 2
             for (int s = 0; s < slots; ++s) {
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(ws + s * slot_stride + base + c));
-              a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+              float4 v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int c = c0 + j * 512;
+                v[j] = (c < p.N) ? __ldcg(reinterpret_cast<const float4*>(ws + s * slot_stride + base + c))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { a[j].x += v[j].x; a[j].y += v[j].y; a[j].z += v[j].z; a[j].w += v[j].w; }
             }
-            if (p.residual) {
-              const uint2 rr = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.residual) + base + c);
-              const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
-              const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
-              a.x += __low2float(r0); a.y += __high2float(r0); a.z += __low2float(r1); a.w += __high2float(r1);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = c0 + j * 512;
+              if (c >= p.N) continue;
+              if (p.residual) {
+                const uint2 rr = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.residual) + base + c);
+                const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&rr.x);
+                const __nv_bfloat162 r1 = *reinterpret_cast<const __nv_bfloat162*>(&rr.y);
+                a[j].x += __low2float(r0); a[j].y += __high2float(r0); a[j].z += __low2float(r1); a[j].w += __high2float(r1);
+              }
+              uint2 pk;
+              pk.x = pack_bf16(a[j].x, a[j].y);
+              pk.y = pack_bf16(a[j].z, a[j].w);
+              *reinterpret_cast<uint2*>(oh + c) = pk;
+              const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&pk.x);
+              const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(&pk.y);
+              const float h0 = __low2float(q0), h1 = __high2float(q0), h2 = __low2float(q1), h3 = __high2float(q1);
+              ss += h0 * h0 + h1 * h1 + h2 * h2 + h3 * h3;
             }
-            uint2 pk;
-            pk.x = pack_bf16(a.x, a.y);
-            pk.y = pack_bf16(a.z, a.w);
-            *reinterpret_cast<uint2*>(oh + c) = pk;
-            const __nv_bfloat162 q0 = *reinterpret_cast<const __nv_bfloat162*>(&pk.x);
-            const __nv_bfloat162 q1 = *reinterpret_cast<const __nv_bfloat162*>(&pk.y);
-            const float h0 = __low2float(q0), h1 = __high2float(q0), h2 = __low2float(q1), h3 = __high2float(q1);
-            ss += h0 * h0 + h1 * h1 + h2 * h2 + h3 * h3;
           }
           if (p.norm_w) {
             ss = warp_sum(ss);
@@ -455,12 +550,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       }
       // ---- the last CTA of this rank to finish advances the call state for the next launch
       named_bar_sync(1, 128);
+      if (tl) tl[5] = global_timer_ns();
       if (et == 0) {
         __threadfence();
         if (atomicAdd(p.pr_state + 3, 1) == static_cast<int>(gridDim.x) - 1) {
           p.pr_state[3] = 0;
           p.pr_state[1 + pr_parity] = static_cast<int>(target);
           p.pr_state[0] = p.pr_state[0] + 1;
+          __threadfence();
+        }
+      }
+    }
+    if constexpr (MODE == kEpiAllGather) {
+      // the last CTA of this rank to finish advances the call state for the next launch
+      named_bar_sync(1, 128);
+      if (threadIdx.x == 64) {
+        __threadfence();
+        if (atomicAdd(p.pr_state + 11, 1) == static_cast<int>(gridDim.x) - 1) {
+          const int parity = p.pr_state[8] & 1;
+          p.pr_state[11] = 0;
+          p.pr_state[9 + parity] += static_cast<int>(gridDim.x);
+          p.pr_state[8] = p.pr_state[8] + 1;
           __threadfence();
         }
       }
@@ -493,12 +603,14 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, bool mn_major, in
 }
 
 template <int BN, bool BF16, int MODE = kEpiStore>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream,
+                  const CUtensorMap* tg = nullptr) {
   using S = GemmSmem<BN>;
   static bool attr_set = false;
+  constexpr int kSmem = S::kTotal + (MODE == kEpiPeerReduce ? kStageBytes4 : 0);
   auto kern = gemm_kernel<BN, BF16, MODE>;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
@@ -516,7 +628,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cu
     p.tiles_per_split = (p.tiles_n + p.n_splits - 1) / p.n_splits;
     grid = p.tiles_m * p.n_splits;
   }
-  kern<<<grid, GEMM_THREADS, S::kTotal, stream>>>(ta, tb, p);
+  kern<<<grid, GEMM_THREADS, kSmem, stream>>>(ta, tb, tg ? *tg : ta, p);
   rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -722,8 +834,8 @@ extern "C" int rb_gemm_ar_plan(int M, int N, int K, int* bn_out) {
 extern "C" int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int tp, int tp_rank,
                                   float* const* peer_ws, unsigned* const* peer_sig, int* state, const void* residual,
                                   const void* norm_w, void* out_h, void* out_x, float eps, int splits, int bn,
-                                  int reduce_scatter, int b_mn_major, unsigned long long wait_ns, int* err_flag,
-                                  cudaStream_t stream) {
+                                  int reduce_scatter, int b_mn_major, unsigned long long wait_ns,
+                                  unsigned long long* timeline, int* err_flag, cudaStream_t stream) {
   using namespace rb;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (tp < 1 || tp > 8 || tp_rank < 0 || tp_rank >= tp) return -4;
@@ -743,7 +855,7 @@ extern "C" int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, in
   }
   for (int r = 0; r < tp; ++r) { p.peer_ws[r] = peer_ws[r]; p.peer_sig[r] = peer_sig[r]; }
   p.pr_state = state; p.residual = residual; p.norm_w = norm_w; p.out_h = out_h; p.out_x = out_x; p.eps = eps;
-  p.wait_ns = wait_ns;
+  p.wait_ns = wait_ns; p.timeline = timeline;
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, A, false, M, K, lda, BM);
   if (rc) return rc;
@@ -753,5 +865,39 @@ extern "C" int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, in
   if (bn == 128) return launch<128, true, kEpiPeerReduce>(ta, tb, p, stream);
   if (bn == 64) return launch<64, true, kEpiPeerReduce>(ta, tb, p, stream);
   if (bn == 32) return launch<32, true, kEpiPeerReduce>(ta, tb, p, stream);
+  return -3;
+}
+
+// ----------------------------------------------------------------------------- all-gather + GEMM
+// y[M][N] = all_gather_rows(x_shard)[M][K] * W[N][K]^T with the gather done by the kernel itself: peers' shards
+// arrive in `peer_ag[tp_rank]` (this rank's gathered buffer, [2][M][K] bf16, double buffered by call parity)
+// while the tiles of this rank's own rows are computed straight from `x_shard`.  M = tp * rows of a shard, and
+// a shard must hold a multiple of 128 rows.  state: ints [8..11] of the same array the reduce kernels use;
+// peer_sig: counters [16..31] of every rank's signal pad.
+extern "C" int rb_ag_gemm(const void* x_shard, const void* B, void* C, int M, int N, int K, int ldb, int ldc, int tp,
+                          int tp_rank, void* const* peer_ag, unsigned* const* peer_sig, int* state, int bn,
+                          unsigned long long wait_ns, int* err_flag, cudaStream_t stream) {
+  using namespace rb;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tp < 1 || tp > 8 || tp_rank < 0 || tp_rank >= tp) return -4;
+  if ((M % tp) || ((M / tp) % BM) || (K % 8) || (ldb % 8)) return -2;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
+  p.lbo_a = p.lbo_b = BK * 128; p.sbo_a = p.sbo_b = 1024;
+  p.err = err_flag; p.k_splits = 1;
+  p.tp = tp; p.tp_rank = tp_rank; p.ag_rows = M / tp; p.ag_src = x_shard;
+  for (int r = 0; r < tp; ++r) { p.peer_ag[r] = peer_ag[r]; p.peer_sig[r] = peer_sig[r]; }
+  p.pr_state = state; p.wait_ns = wait_ns;
+  p.tm_rot = tp_rank * (p.ag_rows / BM);  // own rows first
+  CUtensorMap ta, tb, tg;
+  int rc = make_operand_map(&ta, x_shard, false, p.ag_rows, K, K, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tg, peer_ag[tp_rank], false, 2 * M, K, K, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, B, false, N, K, ldb, bn);
+  if (rc) return rc;
+  if (bn == 256) return launch<256, true, kEpiAllGather>(ta, tb, p, stream, &tg);
+  if (bn == 128) return launch<128, true, kEpiAllGather>(ta, tb, p, stream, &tg);
+  if (bn == 64) return launch<64, true, kEpiAllGather>(ta, tb, p, stream, &tg);
   return -3;
 }

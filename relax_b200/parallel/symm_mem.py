@@ -90,27 +90,35 @@ class SymmComm:
     """Symmetric workspace + arrival counters of one tensor-parallel group and the fused operators
     that use them.  ``workspace_mb`` bounds the largest call (see :func:`workspace_bytes`)."""
 
-    def __init__(self, g: GroupInfo, device: torch.device, workspace_mb: int = 256, wait_ms: Optional[int] = None):
+    def __init__(self, g: GroupInfo, device: torch.device, workspace_mb: int = 256, wait_ms: Optional[int] = None,
+                 gather_mb: Optional[int] = None):
         assert g.size <= 8, "peer tables hold 8 ranks (one NVLink domain)"
         self.g, self.device = g, device
         self.ws = SymmBuffer(workspace_mb << 20, g, device)
         self.sig = SymmBuffer(_SIG_BYTES, g, device)
-        self.state = torch.zeros(8, dtype=torch.int32, device=device)
+        # gathered-activation buffer of the fused all-gather + GEMM ([2][T][K] bf16)
+        self.ag = SymmBuffer((gather_mb if gather_mb is not None else workspace_mb // 2) << 20, g, device)
+        self.state = torch.zeros(16, dtype=torch.int32, device=device)
         if wait_ms is None:
             wait_ms = int(os.environ.get("RELAX_B200_PEER_WAIT_MS", "5000"))
         self.wait_ns = int(wait_ms) * 1_000_000
         self.calls = 0
+        self.timeline = None   # set to an int64 [148, 8] tensor to record per-CTA phase stamps of the next calls
         torch.cuda.synchronize(device)
         dist.barrier(group=g.group)
 
     # -- capability switches (callers fall back to the NCCL statement when False)
     def supports(self, op: str) -> bool:
-        return op in ("gemm_ar_add_rmsnorm", "gemm_rs")
+        return op in ("gemm_ar_add_rmsnorm", "gemm_rs", "ag_gemm")
+
+    def fits_ag(self, shard_rows: int, k: int) -> bool:
+        return (shard_rows % 128 == 0 and k % 8 == 0 and
+                2 * shard_rows * self.g.size * k * 2 <= self.ag.nbytes)
 
     def fits(self, rows: int, n: int, splits: int = 4) -> bool:
         """Whether an all-reduce-form call with ``rows`` x ``n`` outputs fits the workspace."""
         if rows > 512:
-            splits = 1
+            return False   # large all-reduces move less data as reduce-scatter + all-gather: leave them to NCCL
         return workspace_bytes(self.g.size, splits, rows, n) <= self.ws.nbytes and n % 32 == 0
 
     def fits_rs(self, rows: int, n: int) -> bool:
@@ -146,7 +154,8 @@ class SymmComm:
         if x.stride(1) != 1 or (x.stride(0) % 8):
             x = x.contiguous()
         _C().gemm_ar_rmsnorm(x, w, self.ws.ptrs, self.sig.ptrs, self.g.rank, self.state, residual, norm_w, out_h, out_x,
-                             float(eps), splits, bn, reduce_scatter, w_is_kn, self.wait_ns, _cuda.err_flag(x.device))
+                             float(eps), splits, bn, reduce_scatter, w_is_kn, self.wait_ns, _cuda.err_flag(x.device),
+                             self.timeline)
         self.calls += 1
         return out_h, out_x
 
@@ -159,9 +168,27 @@ class SymmComm:
         """``reduce_scatter(x @ w.T)`` over rows: returns this rank's ``[T/tp, N]`` block."""
         return self._launch(x, w, None, None, 0.0, True, w_is_kn)[0]
 
+    def ag_gemm(self, x_shard, w):
+        """``all_gather(x_shard, dim=0) @ w.T`` with the gather inside the GEMM kernel: the tiles of this rank's
+        own rows are computed while the peers' shards arrive over NVLink.  Returns ``(y, None)``."""
+        from ..ops import cuda as _cuda
+
+        Ts, K = x_shard.shape
+        N = w.shape[0]
+        M = Ts * self.g.size
+        bn = 256 if N % 256 == 0 else (128 if N % 128 == 0 else 64)
+        while bn > 64 and (M // 128) * (N // bn) < 148:
+            bn //= 2
+        y = torch.empty(M, N, dtype=x_shard.dtype, device=x_shard.device)
+        _C().ag_gemm(x_shard.contiguous(), w, y, self.ag.ptrs, self.sig.ptrs, self.g.rank, self.state, bn, self.wait_ns,
+                     _cuda.err_flag(x_shard.device))
+        self.calls += 1
+        return y, None
+
     def close(self):
         self.ws.close()
         self.sig.close()
+        self.ag.close()
 
 
 def attach_group(g: GroupInfo, device: torch.device, workspace_mb: int = 256) -> Optional[SymmComm]:

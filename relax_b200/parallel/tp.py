@@ -70,10 +70,15 @@ class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, g):
         ctx.g = g
+        comm = None
         if g.size > 1 and _fused_enabled(x, g, "ag_gemm"):
             from ..ops import fused_comm
 
-            y, xf = fused_comm.ag_gemm(x, w, g)
+            comm = fused_comm.comm_of(g)
+            if not (comm.fits_ag(x.shape[0], x.shape[1]) and w.shape[0] % 64 == 0 and w.stride(1) == 1):
+                comm = None
+        if comm is not None:
+            y, _ = comm.ag_gemm(x, w)
         else:
             xf = _ag(x, g)
             y = ops.linear(xf, w)

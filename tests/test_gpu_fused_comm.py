@@ -115,6 +115,36 @@ def test_gemm_reduce_scatter_two_ranks():
     assert max(worst) < 0.02, worst
 
 
+def _ag_worker(rank, world, shapes):
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.symm_mem import SymmComm
+
+    dev = torch.device("cuda", rank)
+    comm = SymmComm(_group(world), dev, workspace_mb=64)
+    worst = 0.0
+    step = 200
+    for (Ts, N, K) in shapes:
+        for rep in range(3):
+            step += 1
+            x, _ = _inputs(step, rank, Ts, 8, K, dev)
+            _, w = _inputs(step, 77, 8, N, K, dev)   # same weight shard on both ranks: checks rows only
+            y, _ = comm.ag_gemm(x, w)
+            xs = [_inputs(step, r, Ts, 8, K, dev)[0] for r in range(world)]
+            ref = torch.cat(xs).float() @ w.float().t()
+            C.check_error_flag(dev)
+            worst = max(worst, (y.float() - ref).abs().max().item() / max(1.0, ref.abs().max().item()))
+    torch.cuda.synchronize(dev)
+    comm.close()
+    return worst
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_allgather_gemm_two_ranks():
+    shapes = [(128, 256, 256), (512, 1024, 512), (1280, 768, 1024)]
+    worst = run_distributed(_ag_worker, 2, shapes, backend="nccl", timeout=600)
+    assert max(worst) < 0.02, worst
+
+
 def test_peer_wait_runs_out_and_reports():
     """A claimed second rank that never launches: the wait for its arrivals expires, the kernel sets the error
     flag and returns, and the context stays usable."""
