@@ -182,6 +182,7 @@ def main():
         total_tokens += m["total_tokens_local"]
         sync_ms.append(m["weight_sync_ms"])
         losses.append(m["loss"])
+        lp_diff = next((float(v) for k, v in m.items() if k.endswith("train_rollout_logprob_abs_diff")), None)
         h2d += m.get("h2d_bytes", 0)
         d2h += m.get("d2h_bytes", 0)
         for k, v in m.items():
@@ -226,7 +227,7 @@ def main():
             "total_tokens_per_sec": round(tot_all / dev_s, 2),
             "weight_sync_ms": round(sum(sync_ms) / len(sync_ms), 3),
             "phase_seconds_per_step": {k[5:]: round(v / args.steps, 3) for k, v in sorted(parts.items())},
-            "loss": losses[-1],
+            "loss": losses[-1], "train_rollout_logprob_abs_diff": lp_diff,
             "e2e": {"value": round(resp_all / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d // max(1, args.steps),
                     "d2h_bytes_per_step": d2h // max(1, args.steps)},
             "gpu_launches": launches,
