@@ -12,7 +12,10 @@
 // dV/dK accumulate in TMEM over the whole walk and are written once (no atomics:
 // the CTA visits every query head of its KV head).  dQ^T tiles are added to an
 // fp32 accumulation buffer with coalesced red.global (lane = d), converted to
-// bf16 by a second small kernel.  TMEM (512 columns): S^T x2, dP^T x2, dV, dK;
+// bf16 by a second small kernel.  The softmax / dS work is split by query columns over two
+// warpgroups (columns 0-31 and 32-63 of every tile); the producer warp stages the 64 lse and delta
+// values of a query block in shared memory (pre-scaled, +inf / 0 beyond the sequence end) so the
+// inner loop has no global loads.  TMEM (512 columns): S^T x2, dP^T x2, dV, dK;
 // dQ^T of step i reuses the S^T buffer of step i.
 #include "common.cuh"
 #include "host_utils.h"
@@ -22,7 +25,7 @@ namespace rb {
 constexpr int FB_D = 128;
 constexpr int FB_BKV = 128;
 constexpr int FB_BQ = 64;
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;  // 2 softmax warpgroups (warps 0-7), TMA producer (8), MMA issuer (9)
 constexpr int FB_KV_BYTES = FB_BKV * FB_D * 2;  // 32 KB
 constexpr int FB_Q_BYTES = FB_BQ * FB_D * 2;    // 16 KB
 constexpr int FB_PT_BYTES = FB_BKV * FB_BQ * 2; // 16 KB
@@ -33,7 +36,8 @@ constexpr int FB_SMEM_DO = FB_SMEM_Q + 2 * FB_Q_BYTES;      // 2 stages
 constexpr int FB_SMEM_PT = FB_SMEM_DO + 2 * FB_Q_BYTES;
 constexpr int FB_SMEM_DS = FB_SMEM_PT + FB_PT_BYTES;
 constexpr int FB_SMEM_BAR = FB_SMEM_DS + FB_PT_BYTES;
-constexpr int FB_SMEM_TOTAL = FB_SMEM_BAR + 256;
+constexpr int FB_SMEM_LD = FB_SMEM_BAR + 256;      // 2 stages x (64 lse*log2e + 64 delta) floats
+constexpr int FB_SMEM_TOTAL = FB_SMEM_LD + 2 * 128 * 4;
 constexpr int FB_T_ST = 0;     // two buffers of 64 columns
 constexpr int FB_T_DP = 128;   // two buffers of 64 columns
 constexpr int FB_T_DV = 256;
@@ -112,13 +116,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
       mbar_init(&qfull[s], 1);
       mbar_init(&qempty[s], 1);
       mbar_init(&bar_sdp[s], 1);
-      mbar_init(&bar_dqfree[s], 128);
+      mbar_init(&bar_dqfree[s], 256);
     }
-    mbar_init(bar_pds, 128);
+    mbar_init(bar_pds, 256);
     mbar_init(bar_mma2, 1);
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc<512>(tmem_slot);
     tmem_relinquish();
   }
@@ -127,29 +131,48 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 4) {
-    // ================================================================ TMA producer
-    if (lane == 0 && n_it > 0) {
-      mbar_expect_tx(kvfull, 2 * FB_KV_BYTES);
-      tma_load_3d(smem + FB_SMEM_K, &tma_k, kvfull, 0, kv_head, k_begin + kv0);
-      tma_load_3d(smem + FB_SMEM_K + FB_KV_BYTES / 2, &tma_k, kvfull, 64, kv_head, k_begin + kv0);
-      tma_load_3d(smem + FB_SMEM_V, &tma_v, kvfull, 0, kv_head, k_begin + kv0);
-      tma_load_3d(smem + FB_SMEM_V + FB_KV_BYTES / 2, &tma_v, kvfull, 64, kv_head, k_begin + kv0);
+  if (warp == 8) {
+    // ================================================================ TMA producer + lse/delta staging (whole warp)
+    if (n_it > 0) {
+      if (lane == 0) {
+        mbar_expect_tx(kvfull, 2 * FB_KV_BYTES);
+        tma_load_3d(smem + FB_SMEM_K, &tma_k, kvfull, 0, kv_head, k_begin + kv0);
+        tma_load_3d(smem + FB_SMEM_K + FB_KV_BYTES / 2, &tma_k, kvfull, 64, kv_head, k_begin + kv0);
+        tma_load_3d(smem + FB_SMEM_V, &tma_v, kvfull, 0, kv_head, k_begin + kv0);
+        tma_load_3d(smem + FB_SMEM_V + FB_KV_BYTES / 2, &tma_v, kvfull, 64, kv_head, k_begin + kv0);
+      }
+      const float log2e = 1.4426950408889634f;
       for (int it = 0; it < n_it; ++it) {
         const int s = it & 1;
-        if (!mbar_wait(&qempty[s], (static_cast<uint32_t>(it >> 1) & 1) ^ 1, abort_flag, p.err)) break;
+        int okw = 1;
+        if (lane == 0) okw = mbar_wait(&qempty[s], (static_cast<uint32_t>(it >> 1) & 1) ^ 1, abort_flag, p.err) ? 1 : 0;
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) break;
         const int head = kv_head * G + it / n_i;
-        const int row = q_begin + (i_start + it % n_i) * FB_BQ;
-        uint8_t* sq = smem + FB_SMEM_Q + s * FB_Q_BYTES;
-        uint8_t* sd = smem + FB_SMEM_DO + s * FB_Q_BYTES;
-        mbar_expect_tx(&qfull[s], 2 * FB_Q_BYTES);
-        tma_load_3d(sq, &tma_q, &qfull[s], 0, head, row);
-        tma_load_3d(sq + FB_Q_BYTES / 2, &tma_q, &qfull[s], 64, head, row);
-        tma_load_3d(sd, &tma_do, &qfull[s], 0, head, row);
-        tma_load_3d(sd + FB_Q_BYTES / 2, &tma_do, &qfull[s], 64, head, row);
+        const int q0 = (i_start + it % n_i) * FB_BQ;
+        const int row = q_begin + q0;
+        float* ld = reinterpret_cast<float*>(smem + FB_SMEM_LD) + s * 128;
+        const size_t hb = static_cast<size_t>(head) * p.Tq + row;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int qi = lane + 32 * j;
+          const bool in = q0 + qi < len_q;
+          ld[qi] = in ? __ldg(p.lse + hb + qi) * log2e : INFINITY;
+          ld[64 + qi] = in ? __ldg(p.delta + hb + qi) : 0.f;
+        }
+        __syncwarp();
+        if (lane == 0) {
+          uint8_t* sq = smem + FB_SMEM_Q + s * FB_Q_BYTES;
+          uint8_t* sd = smem + FB_SMEM_DO + s * FB_Q_BYTES;
+          mbar_expect_tx(&qfull[s], 2 * FB_Q_BYTES);
+          tma_load_3d(sq, &tma_q, &qfull[s], 0, head, row);
+          tma_load_3d(sq + FB_Q_BYTES / 2, &tma_q, &qfull[s], 64, head, row);
+          tma_load_3d(sd, &tma_do, &qfull[s], 0, head, row);
+          tma_load_3d(sd + FB_Q_BYTES / 2, &tma_do, &qfull[s], 64, head, row);
+        }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ================================================================ MMA issuer
     if (lane == 0 && n_it > 0) {
       const uint32_t id_sdp = make_idesc_f16(128, FB_BQ, true, false, false);  // K-major x K-major
@@ -216,32 +239,34 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
       }
     }
   } else {
-    // ================================================================ softmax / dS / epilogue (warps 0..3)
-    const int r = warp * 32 + lane;  // kv row of the tile (S^T, dP^T, dV, dK) or d index (dQ^T)
+    // ================================================================ softmax / dS / epilogue (warps 0..7)
+    const int wg = warp >> 2;                  // warpgroup: query columns [32*wg, 32*wg+32) of every tile
+    const int r = (warp & 3) * 32 + lane;      // kv row of the tile (S^T, dP^T, dV, dK) or d index (dQ^T)
+    const int cb = wg * 32;
     const int kv_row = kv0 + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    const float log2e = 1.4426950408889634f;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint8_t* spt = smem + FB_SMEM_PT + r * 128;
     uint8_t* sds = smem + FB_SMEM_DS + r * 128;
     bool ok = true;
 
     auto drain_dq = [&](int it) {
-      // dQ^T of step `it`: lane = d, 64 columns = query rows
+      // dQ^T of step `it`: lane = d, this warpgroup's 32 columns = query rows
       const int s = it & 1;
       const int head = kv_head * G + it / n_i;
-      const int q0 = (i_start + it % n_i) * FB_BQ;
+      const int q0 = (i_start + it % n_i) * FB_BQ + cb;
       tc_fence_after();
       float* base = p.dq_acc + (static_cast<size_t>(q_begin + q0) * p.Hq + head) * FB_D + r;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_base + FB_T_ST + s * 64 + lane_addr + c * 32, v);
-        tmem_wait_ld();
+      const size_t qstride = static_cast<size_t>(p.Hq) * FB_D;
+      uint32_t v[32];
+      tmem_ld_32x32b_x32(tmem_base + FB_T_ST + s * 64 + lane_addr + cb, v);
+      tmem_wait_ld();
+      if (q0 + 32 <= len_q) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int q = q0 + c * 32 + i;
-          if (q < len_q) atomicAdd(base + static_cast<size_t>(c * 32 + i) * p.Hq * FB_D, __uint_as_float(v[i]));
-        }
+        for (int i = 0; i < 32; ++i) atomicAdd(base + i * qstride, __uint_as_float(v[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (q0 + i < len_q) atomicAdd(base + i * qstride, __uint_as_float(v[i]));
       }
       tc_fence_before();
       mbar_arrive(&bar_dqfree[s]);
@@ -249,35 +274,51 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
 
     for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
-      const int head = kv_head * G + it / n_i;
       const int q0 = (i_start + it % n_i) * FB_BQ;
       if (!mbar_wait(&bar_sdp[s], static_cast<uint32_t>(it >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
+      // the staged lse/delta were written before this stage's barrier was armed; it has completed long ago
+      if (!mbar_wait(&qfull[s], static_cast<uint32_t>(it >> 1) & 1, abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      const float* lse = p.lse + static_cast<size_t>(head) * p.Tq + q_begin + q0;
-      const float* dl = p.delta + static_cast<size_t>(head) * p.Tq + q_begin + q0;
-      uint32_t pk_p[32], pk_ds[32];
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_base + FB_T_ST + s * 64 + lane_addr + c * 32, sv);
-        tmem_ld_32x32b_x32(tmem_base + FB_T_DP + s * 64 + lane_addr + c * 32, dv);
-        tmem_wait_ld();
+      const float4* l4 = reinterpret_cast<const float4*>(smem + FB_SMEM_LD) + s * 32 + wg * 8;
+      const float4* d4 = l4 + 16;
+      uint32_t pk_p[16], pk_ds[16];
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32b_x32(tmem_base + FB_T_ST + s * 64 + lane_addr + cb, sv);
+      tmem_ld_32x32b_x32(tmem_base + FB_T_DP + s * 64 + lane_addr + cb, dv);
+      tmem_wait_ld();
+      const bool full = (kv0 + FB_BKV - 1 < len_k) && (!p.causal || (kv0 + FB_BKV - 1 <= q0 + offset));
+      if (full) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 l = l4[i], d = d4[i];
+          const float p0 = exp2f(fmaf(__uint_as_float(sv[4 * i]), p.scale_log2, -l.x));
+          const float p1 = exp2f(fmaf(__uint_as_float(sv[4 * i + 1]), p.scale_log2, -l.y));
+          const float p2 = exp2f(fmaf(__uint_as_float(sv[4 * i + 2]), p.scale_log2, -l.z));
+          const float p3 = exp2f(fmaf(__uint_as_float(sv[4 * i + 3]), p.scale_log2, -l.w));
+          pk_p[2 * i] = pack_bf16(p0, p1);
+          pk_p[2 * i + 1] = pack_bf16(p2, p3);
+          pk_ds[2 * i] = pack_bf16(p0 * (__uint_as_float(dv[4 * i]) - d.x) * p.scale,
+                                   p1 * (__uint_as_float(dv[4 * i + 1]) - d.y) * p.scale);
+          pk_ds[2 * i + 1] = pack_bf16(p2 * (__uint_as_float(dv[4 * i + 2]) - d.z) * p.scale,
+                                       p3 * (__uint_as_float(dv[4 * i + 3]) - d.w) * p.scale);
+        }
+      } else {
+        const float* lf = reinterpret_cast<const float*>(l4);
+        const float* df = reinterpret_cast<const float*>(d4);
+        const int qlim = p.causal ? kv_row - offset : -(1 << 30);  // valid iff q >= qlim (and the kv row exists)
+        const bool row_ok = kv_row < len_k;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float pv[2], ds[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int q = q0 + c * 32 + i + u;
-            bool valid = (q < len_q) && (kv_row < len_k);
-            if (p.causal) valid = valid && (kv_row <= q + offset);
-            const float l2 = valid ? __ldg(lse + c * 32 + i + u) * log2e : 0.f;
-            const float dd = valid ? __ldg(dl + c * 32 + i + u) : 0.f;
-            const float pr = valid ? exp2f(__uint_as_float(sv[i + u]) * p.scale_log2 - l2) : 0.f;
+            const bool valid = row_ok && (q0 + cb + i + u >= qlim);
+            const float pr = valid ? exp2f(fmaf(__uint_as_float(sv[i + u]), p.scale_log2, -lf[i + u])) : 0.f;
             pv[u] = pr;
-            ds[u] = pr * (__uint_as_float(dv[i + u]) - dd) * p.scale;
+            ds[u] = pr * (__uint_as_float(dv[i + u]) - df[i + u]) * p.scale;
           }
-          pk_p[c * 16 + i / 2] = pack_bf16(pv[0], pv[1]);
-          pk_ds[c * 16 + i / 2] = pack_bf16(ds[0], ds[1]);
+          pk_p[i / 2] = pack_bf16(pv[0], pv[1]);
+          pk_ds[i / 2] = pack_bf16(ds[0], ds[1]);
         }
       }
       tc_fence_before();
@@ -285,10 +326,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
         if (!mbar_wait(bar_mma2, static_cast<uint32_t>(it - 1) & 1, abort_flag, p.err)) { ok = false; break; }
       }
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
-        const int off = (c8 ^ (r & 7)) << 4;
-        *reinterpret_cast<uint4*>(spt + off) = make_uint4(pk_p[c8 * 4], pk_p[c8 * 4 + 1], pk_p[c8 * 4 + 2], pk_p[c8 * 4 + 3]);
-        *reinterpret_cast<uint4*>(sds + off) = make_uint4(pk_ds[c8 * 4], pk_ds[c8 * 4 + 1], pk_ds[c8 * 4 + 2], pk_ds[c8 * 4 + 3]);
+      for (int j = 0; j < 4; ++j) {
+        const int off = ((wg * 4 + j) ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(spt + off) = make_uint4(pk_p[j * 4], pk_p[j * 4 + 1], pk_p[j * 4 + 2], pk_p[j * 4 + 3]);
+        *reinterpret_cast<uint4*>(sds + off) = make_uint4(pk_ds[j * 4], pk_ds[j * 4 + 1], pk_ds[j * 4 + 2], pk_ds[j * 4 + 3]);
       }
       fence_proxy_async();
       mbar_arrive(bar_pds);
@@ -299,7 +340,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
       if (ok) drain_dq(n_it - 1);
     }
     tc_fence_after();
-    // ---- dK / dV: row r of the tile
+    // ---- dK / dV: row r of the tile, this warpgroup's half of the head dimension
     const bool live = ok && (kv_row < len_k);
     __nv_bfloat16* outk = p.dK + (static_cast<size_t>(k_begin + kv_row) * p.Hkv + kv_head) * FB_D;
     __nv_bfloat16* outv = p.dV + (static_cast<size_t>(k_begin + kv_row) * p.Hkv + kv_head) * FB_D;
@@ -308,7 +349,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
       __nv_bfloat16* out = which ? outk : outv;
       const uint32_t tcol = which ? FB_T_DK : FB_T_DV;
 #pragma unroll 1
-      for (int c = 0; c < FB_D / 32; ++c) {
+      for (int c = 2 * wg; c < 2 * wg + 2; ++c) {
         uint32_t o[32];
         if (n_it > 0) {
           tmem_ld_32x32b_x32(tmem_base + tcol + lane_addr + c * 32, o);
@@ -335,7 +376,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__
   if (*abort_flag) __nanosleep(50000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc<512>(tmem_base);
   }
