@@ -81,6 +81,10 @@ int rb_gemm_ar_rmsnorm(const void* A, const void* B, int M, int N, int K, int ld
 int rb_ag_gemm(const void* x_shard, const void* B, void* C, int M, int N, int K, int ldb, int ldc, int tp, int tp_rank,
                void* const* peer_ag, unsigned* const* peer_sig, int* state, int bn, unsigned long long wait_ns,
                int* err_flag, cudaStream_t stream);
+int rb_qkv_post(const void* qkv, int ld, const void* qw, const void* kw, const float* cos_t, const float* sin_t, void* q_out,
+                void* k_out, void* v_out, void* k_cache, void* v_cache, const long long* slots, int T, int nq, int nkv,
+                float eps, cudaStream_t st);
+int rb_splitk_swiglu(const float* ws, void* out, int M, int F, int splits, cudaStream_t st);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

@@ -76,11 +76,52 @@ void ag_gemm(torch::Tensor x_shard, torch::Tensor w, torch::Tensor y, std::vecto
                    state.data_ptr<int>(), (int)bn, (unsigned long long)wait_ns, err.data_ptr<int>(), cur_stream()),
         "rb_ag_gemm");
 }
+
+// Fused QKV post-processing (see qkv_post_sm100.cu).  k_out / v_out / cache / slots are optional.
+void qkv_post(torch::Tensor qkv, c10::optional<torch::Tensor> qw, c10::optional<torch::Tensor> kw, torch::Tensor cos_t,
+              torch::Tensor sin_t, torch::Tensor q_out, c10::optional<torch::Tensor> k_out,
+              c10::optional<torch::Tensor> v_out, c10::optional<torch::Tensor> k_cache,
+              c10::optional<torch::Tensor> v_cache, c10::optional<torch::Tensor> slots, int64_t nq, int64_t nkv, double eps) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.scalar_type() == at::kBFloat16 && qkv.stride(1) == 1 && qkv.size(1) == (nq + 2 * nkv) * 128,
+              "qkv_post: bf16 [T, (nq + 2 nkv) * 128]");
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(1) == 64);
+  TORCH_CHECK(q_out.is_contiguous() && (!k_out.has_value() || k_out->is_contiguous()) &&
+              (!v_out.has_value() || v_out->is_contiguous()));
+  TORCH_CHECK(slots.has_value() == k_cache.has_value() && slots.has_value() == v_cache.has_value());
+  if (k_cache.has_value()) TORCH_CHECK(k_cache->is_contiguous() && v_cache->is_contiguous() && k_cache->size(2) == nkv);
+  auto ptr = [](c10::optional<torch::Tensor>& t) -> void* { return t.has_value() ? t->data_ptr() : nullptr; };
+  check(rb_qkv_post(qkv.data_ptr(), (int)qkv.stride(0), ptr(qw), ptr(kw), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(),
+                    q_out.data_ptr(), ptr(k_out), ptr(v_out), ptr(k_cache), ptr(v_cache),
+                    slots.has_value() ? (const long long*)slots->data_ptr<int64_t>() : nullptr, (int)qkv.size(0), (int)nq,
+                    (int)nkv, (float)eps, cur_stream()),
+        "rb_qkv_post");
+}
+
+// Split-K partial sums of x @ w^T into ws ([splits][M][N] fp32); no reduction.
+void gemm_splitk_partial(torch::Tensor A, torch::Tensor B, torch::Tensor workspace, int64_t splits, int64_t bn,
+                         torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  check(rb_gemm_splitk(A.data_ptr(), B.data_ptr(), nullptr, nullptr, nullptr, workspace.data_ptr<float>(), (int)A.size(0),
+                       (int)B.size(0), (int)A.size(1), (int)A.stride(0), (int)B.stride(0), (int)B.size(0), (int)splits, (int)bn,
+                       A.scalar_type() == at::kHalf, err.data_ptr<int>(), cur_stream()),
+        "rb_gemm_splitk");
+}
+void splitk_swiglu(torch::Tensor workspace, torch::Tensor out, int64_t splits) {
+  const c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous());
+  check(rb_splitk_swiglu(workspace.data_ptr<float>(), out.data_ptr(), (int)out.size(0), (int)out.size(1), (int)splits,
+                         cur_stream()),
+        "rb_splitk_swiglu");
+}
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
   m.def("gemm_ar_plan", &gemm_ar_plan);
   m.def("ag_gemm", &ag_gemm);
+  m.def("qkv_post", &qkv_post);
+  m.def("gemm_splitk_partial", &gemm_splitk_partial);
+  m.def("splitk_swiglu", &splitk_swiglu);
   m.def("gemm_ar_rmsnorm", &gemm_ar_rmsnorm, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("ws_ptrs"),
         pybind11::arg("sig_ptrs"), pybind11::arg("tp_rank"), pybind11::arg("state"), pybind11::arg("residual"),
         pybind11::arg("norm_w"), pybind11::arg("out_h"), pybind11::arg("out_x"), pybind11::arg("eps"),

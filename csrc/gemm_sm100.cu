@@ -801,6 +801,7 @@ extern "C" int rb_gemm_splitk(const void* A, const void* B, void* C, const void*
   else if (bn == 64) rc = is_fp16 ? launch<64, false>(ta, tb, p, stream) : launch<64, true>(ta, tb, p, stream);
   else return -3;
   if (rc) return rc;
+  if (C == nullptr) return 0;  // partial sums only: the caller runs its own fused reduction
   long long blocks = (static_cast<long long>(M) * (N / 4) + 255) / 256;
   if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
   if (is_fp16) splitk_reduce_kernel<false><<<(int)blocks, 256, 0, stream>>>(workspace, C, bias, residual, M, N, splits, ldc);

@@ -9,6 +9,8 @@ routes CUDA tensors through the PyTorch/library path on purpose - that is the
 """
 from __future__ import annotations
 
+import torch
+
 import os
 
 from . import reference as ref
@@ -117,6 +119,34 @@ def kv_cache_write(k, v, k_cache, v_cache, slots):
     vc = v_cache.view(-1, v.shape[1], v.shape[2])
     kc[slots] = k
     vc[slots] = v
+
+
+def qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache=None, v_cache=None, slots=None, dense_kv=True):
+    """Inference-side glue after the fused QKV projection: optional per-head RMSNorm of q and k, rotary
+    embedding, and the write of the new K/V rows into the paged cache.  One kernel on CUDA (bf16,
+    head_dim 128); the statement below elsewhere.  Returns ``(q, k, v)`` with ``k``/``v`` None when
+    ``dense_kv`` is False (decode: attention reads the cache)."""
+    hd = qkv.shape[1] // (nq + 2 * nkv)
+    if (_use_cuda(qkv) and hd == 128 and qkv.dtype == torch.bfloat16 and not torch.is_grad_enabled()
+            and cos.shape[-1] == 64):
+        return _cuda().qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache, v_cache, slots, dense_kv)
+    T = qkv.shape[0]
+    q = qkv[:, : nq * hd].reshape(T, nq, hd)
+    k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
+    v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
+    if q_norm_w is not None:
+        q, k = rmsnorm(q, q_norm_w, eps), rmsnorm(k, k_norm_w, eps)
+    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    if slots is not None:
+        kv_cache_write(k, v, k_cache, v_cache, slots)
+    return (q, k, v.contiguous()) if dense_kv else (q, None, None)
+
+
+def linear_swiglu(x, w):
+    """``swiglu(x @ w.T)`` with ``w`` = [gate; up]; fused split-K reduction + activation for decode shapes."""
+    if _use_cuda(x) and x.shape[0] <= 128 and not torch.is_grad_enabled() and x.dim() == 2:
+        return _cuda().linear_swiglu_skinny(x, w)
+    return swiglu(linear(x, w))
 
 
 def dgrad(dy, w):

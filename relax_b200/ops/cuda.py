@@ -202,6 +202,35 @@ def matmul_nt_skinny(x, w, bias=None, residual=None):
     return out
 
 
+def linear_swiglu_skinny(x, w):
+    """``swiglu(x @ w.T)`` for decode (``w`` = [gate; up] rows): split-K partial sums, then ONE kernel that
+    reduces them and applies the activation, instead of reduce + swiglu."""
+    x, _ = _rowmajor_2d(x)
+    M, K = x.shape
+    N = w.shape[0]
+    C = _load()
+    splits, bn = C.gemm_splitk_plan(M, N, K)
+    if splits <= 1 or x.dtype != torch.bfloat16 or (N // 2) % 4:
+        return swiglu(linear(x, w))
+    ws = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+    C.gemm_splitk_partial(x, w, ws, splits, bn, err_flag(x.device))
+    out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
+    C.splitk_swiglu(ws, out, splits)
+    return out
+
+
+def qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache=None, v_cache=None, slots=None, dense_kv=True):
+    """Per-head q/k RMSNorm (optional) + rotary embedding + KV-cache write in one launch.
+    Returns ``(q, k, v)`` as ``[T, heads, 128]``; ``k``/``v`` are None unless ``dense_kv``."""
+    T = qkv.shape[0]
+    q = torch.empty(T, nq, 128, dtype=qkv.dtype, device=qkv.device)
+    k = torch.empty(T, nkv, 128, dtype=qkv.dtype, device=qkv.device) if dense_kv else None
+    v = torch.empty(T, nkv, 128, dtype=qkv.dtype, device=qkv.device) if dense_kv else None
+    _load().qkv_post(qkv, q_norm_w, k_norm_w, cos.contiguous(), sin.contiguous(), q, k, v, k_cache, v_cache, slots, nq, nkv,
+                     float(eps))
+    return q, k, v
+
+
 class _LinearNN(torch.autograd.Function):
     """y = x @ b with b[K,N] row-major (used when the caller passes ``w.t()``)."""
 

@@ -101,7 +101,7 @@ class ColocatedGRPO:
             from ..parallel.symm_mem import attach_group
 
             for g in (self.rollout_tp_group, self.ps.tp):
-                if g.size > 1 and fused_comm.comm_of(g) is None:
+                if fused_comm.comm_of(g) is None:
                     c = attach_group(g, self.device, cfg.fused_workspace_mb)
                     if c is not None:
                         self.fused_comms.append(c)

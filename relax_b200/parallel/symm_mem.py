@@ -86,6 +86,19 @@ def workspace_bytes(tp: int, splits: int, rows_out: int, n: int) -> int:
     return 2 * tp * splits * rows_out * n * 4
 
 
+class _LocalBuffer:
+    """Stand-in for :class:`SymmBuffer` when the group has one rank: a plain device tensor."""
+
+    def __init__(self, nbytes: int, device: torch.device):
+        self.nbytes = int(nbytes)
+        self.t = torch.zeros(self.nbytes // 4, dtype=torch.int32, device=device)
+        self.ptrs = [self.t.data_ptr()]
+
+    def close(self):
+        self.t = None
+        self.ptrs = []
+
+
 class SymmComm:
     """Symmetric workspace + arrival counters of one tensor-parallel group and the fused operators
     that use them.  ``workspace_mb`` bounds the largest call (see :func:`workspace_bytes`)."""
@@ -94,10 +107,16 @@ class SymmComm:
                  gather_mb: Optional[int] = None):
         assert g.size <= 8, "peer tables hold 8 ranks (one NVLink domain)"
         self.g, self.device = g, device
-        self.ws = SymmBuffer(workspace_mb << 20, g, device)
-        self.sig = SymmBuffer(_SIG_BYTES, g, device)
-        # gathered-activation buffer of the fused all-gather + GEMM ([2][T][K] bf16)
-        self.ag = SymmBuffer((gather_mb if gather_mb is not None else workspace_mb // 2) << 20, g, device)
+        if g.size == 1:
+            # one rank: the same kernels fuse split-K GEMM + reduction + residual + RMSNorm into one launch
+            self.ws = _LocalBuffer(workspace_mb << 20, device)
+            self.sig = _LocalBuffer(_SIG_BYTES, device)
+            self.ag = _LocalBuffer(16, device)
+        else:
+            self.ws = SymmBuffer(workspace_mb << 20, g, device)
+            self.sig = SymmBuffer(_SIG_BYTES, g, device)
+            # gathered-activation buffer of the fused all-gather + GEMM ([2][T][K] bf16)
+            self.ag = SymmBuffer((gather_mb if gather_mb is not None else workspace_mb // 2) << 20, g, device)
         self.state = torch.zeros(16, dtype=torch.int32, device=device)
         if wait_ms is None:
             wait_ms = int(os.environ.get("RELAX_B200_PEER_WAIT_MS", "5000"))
@@ -105,10 +124,13 @@ class SymmComm:
         self.calls = 0
         self.timeline = None   # set to an int64 [148, 8] tensor to record per-CTA phase stamps of the next calls
         torch.cuda.synchronize(device)
-        dist.barrier(group=g.group)
+        if g.size > 1:
+            dist.barrier(group=g.group)
 
     # -- capability switches (callers fall back to the NCCL statement when False)
     def supports(self, op: str) -> bool:
+        if self.g.size == 1:
+            return op == "gemm_ar_add_rmsnorm"
         return op in ("gemm_ar_add_rmsnorm", "gemm_rs", "ag_gemm")
 
     def fits_ag(self, shard_rows: int, k: int) -> bool:
@@ -196,8 +218,12 @@ def attach_group(g: GroupInfo, device: torch.device, workspace_mb: int = 256) ->
     with peer access; returns None (callers keep the NCCL statements) otherwise."""
     from ..ops import fused_comm
 
-    if g.size <= 1 or device.type != "cuda" or os.environ.get("RELAX_B200_FUSED_TP", "1") != "1":
+    if device.type != "cuda" or os.environ.get("RELAX_B200_FUSED_TP", "1") != "1":
         return None
+    if g.size == 1:
+        comm = SymmComm(g, device, min(workspace_mb, 128))
+        fused_comm.attach(g, comm)
+        return comm
     C = _C()
     dev = device.index if device.index is not None else torch.cuda.current_device()
     # every rank of the group must sit on this host, on a device of its own, with peer access

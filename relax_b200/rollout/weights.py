@@ -129,14 +129,12 @@ class RolloutWeights:
                 y = ops.linear(a, p[pre + "experts_down"][e]).float()
                 out.index_add_(0, rows, y * (w * m)[rows].sum(-1, keepdim=True))
             return out.to(x.dtype), self.ep_size > 1
-        a = ops.swiglu(ops.linear(x, p[pre + "gate_up"]))
+        a = ops.linear_swiglu(x, p[pre + "gate_up"])
         return ops.linear(a, p[pre + "down"]), tp.size > 1
 
     def _fused(self, tp: GroupInfo, rows: int, n: int):
         """The symmetric-memory communicator of ``tp`` when the fused GEMM + all-reduce + residual +
         RMSNorm kernel can take a call of this size, else None (NCCL statement)."""
-        if tp.size <= 1:
-            return None
         from ..ops import fused_comm
 
         comm = fused_comm.comm_of(tp)
@@ -144,7 +142,7 @@ class RolloutWeights:
             return None
         return comm
 
-    def _layer(self, i, h, x, cos, sin, attn, tp, next_norm):
+    def _layer(self, i, h, x, cos, sin, attn, tp, next_norm, cache):
         """One decoder layer.  ``h`` is the residual stream, ``x`` its normed copy (input of the attention
         block); returns the new ``(h, x)`` where ``x`` is already normed with ``next_norm`` (the next layer's
         input norm or the final norm), so every residual add is fused with the norm that follows it."""
@@ -154,13 +152,10 @@ class RolloutWeights:
         nq, nkv = cfg.num_attention_heads // self.tp_size, cfg.num_query_groups // self.tp_size
         qkv = ops.linear(x, p[pre + "qkv"], p.get(pre + "qkv_bias"))
         T = qkv.shape[0]
-        q = qkv[:, : nq * hd].reshape(T, nq, hd)
-        k = qkv[:, nq * hd:(nq + nkv) * hd].reshape(T, nkv, hd)
-        v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
-        if cfg.qk_layernorm:
-            q = ops.rmsnorm(q, p[pre + "q_norm"], cfg.rms_norm_eps)
-            k = ops.rmsnorm(k, p[pre + "k_norm"], cfg.rms_norm_eps)
-        q, k = ops.apply_rope(q, cos, sin), ops.apply_rope(k, cos, sin)
+        kc, vc, slots, dense = cache
+        q, k, v = ops.qkv_post(qkv, nq, nkv, p.get(pre + "q_norm") if cfg.qk_layernorm else None,
+                               p.get(pre + "k_norm") if cfg.qk_layernorm else None, cos, sin, cfg.rms_norm_eps,
+                               kc[i], vc[i], slots, dense)
         o = attn(i, q, k, v).reshape(T, nq * hd)
         comm = self._fused(tp, T, cfg.hidden_size)
         if comm is not None:
@@ -169,7 +164,7 @@ class RolloutWeights:
             a = self._allreduce(ops.linear(o, p[pre + "o"]), tp)
             x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
         if comm is not None and (pre + "router") not in p:
-            a = ops.swiglu(ops.linear(x, p[pre + "gate_up"]))
+            a = ops.linear_swiglu(x, p[pre + "gate_up"])
             return comm.gemm_ar_add_rmsnorm(a, p[pre + "down"], h, next_norm, cfg.rms_norm_eps)
         m, need_ar = self._mlp(i, x, tp)
         if need_ar:
@@ -177,29 +172,27 @@ class RolloutWeights:
         x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
         return h, x
 
-    def _run(self, tokens, positions, attn, tp):
+    def _run(self, tokens, positions, attn, tp, cache):
         cfg, p = self.cfg, self.p
         h = self._embed(tokens, tp)
         cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
         x = ops.rmsnorm(h, p["layers.0.input_norm"], cfg.rms_norm_eps)
         for i in range(cfg.num_layers):
             nxt = p[f"layers.{i + 1}.input_norm"] if i + 1 < cfg.num_layers else p["final_norm"]
-            h, x = self._layer(i, h, x, cos, sin, attn, tp, nxt)
+            h, x = self._layer(i, h, x, cos, sin, attn, tp, nxt, cache)
         return x
 
     # ------------------------------------------------------------------ entry points
     def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
         def attn(i, q, k, v):
-            ops.kv_cache_write(k, v, kv[i, 0], kv[i, 1], slots)
-            return ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=True, max_seqlen=max_seqlen)
+            return ops.attention_varlen(q, k, v, cu_seqlens, causal=True, max_seqlen=max_seqlen)
 
-        h = self._run(tokens, positions, attn, tp)
+        h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True))
         return self._logits(h[last_rows], tp)
 
     def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
         def attn(i, q, k, v):
-            ops.kv_cache_write(k, v, kv[i, 0], kv[i, 1], slots)
             return ops.paged_decode_attention(q, kv[i, 0], kv[i, 1], block_tables, context_lens)
 
-        h = self._run(tokens, positions, attn, tp)
+        h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, False))
         return self._logits(h, tp)
