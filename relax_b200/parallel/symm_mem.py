@@ -137,7 +137,7 @@ class SymmComm:
         return (shard_rows % 128 == 0 and k % 8 == 0 and
                 2 * shard_rows * self.g.size * k * 2 <= self.ag.nbytes)
 
-    def fits(self, rows: int, n: int, splits: int = 4) -> bool:
+    def fits(self, rows: int, n: int, splits: int = 8) -> bool:
         """Whether an all-reduce-form call with ``rows`` x ``n`` outputs fits the workspace."""
         if rows > 512:
             return False   # large all-reduces move less data as reduce-scatter + all-gather: leave them to NCCL
@@ -154,7 +154,13 @@ class SymmComm:
             while bn > 64 and tm * (N // bn) < 148:
                 bn //= 2
             return 1, bn
-        splits, bn = _C().gemm_ar_plan(M, N, K)
+        if self.g.size == 1 and os.environ.get("RELAX_B200_LOCAL_PLAN", "splitk") == "splitk":
+            # nothing crosses NVLink: take the split-K plan of the plain skinny GEMM (wider N tiles re-read
+            # the activation tile from L2 half as often)
+            splits, bn = _C().gemm_splitk_plan(M, N, K)
+            splits = min(splits, 8)
+        else:
+            splits, bn = _C().gemm_ar_plan(M, N, K)
         if w_is_kn and bn < 64:
             bn = 64
         return splits, bn
@@ -221,6 +227,11 @@ def attach_group(g: GroupInfo, device: torch.device, workspace_mb: int = 256) ->
     if device.type != "cuda" or os.environ.get("RELAX_B200_FUSED_TP", "1") != "1":
         return None
     if g.size == 1:
+        # One rank: the single-launch split-K GEMM + reduce + residual + RMSNorm measured 10-12 us slower per
+        # call than the three separate launches inside a CUDA graph (the in-kernel release/wait/reduce tail
+        # costs more than two kernel boundaries), so it is opt-in.
+        if os.environ.get("RELAX_B200_FUSED_LOCAL", "0") != "1":
+            return None
         comm = SymmComm(g, device, min(workspace_mb, 128))
         fused_comm.attach(g, comm)
         return comm
