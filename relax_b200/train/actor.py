@@ -144,6 +144,26 @@ class TrainActor:
         hr = h.index_select(0, pb.logit_rows)
         return self.model.log_probs(hr, pb.targets, self.cfg.rollout_temperature, with_entropy)
 
+    def _forward_values(self, pb):
+        """Critic: one scalar per response position (the hidden state that predicts token t+1 also carries V(s_t))."""
+        h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+        return self.model.values(h.index_select(0, pb.logit_rows))
+
+    @torch.no_grad()
+    def compute_values(self, batch: dict) -> dict:
+        """Forward-only critic pass (relax/backends/megatron/loss.py get_values :466-529): per-sample value lists."""
+        toks, rl = batch["tokens"], batch["response_lengths"]
+        out = [None] * len(toks)
+        for mb in self._microbatches([len(t) for t in toks]):
+            if not mb:
+                self._dummy_forward()
+                continue
+            pb = self._pack([toks[i] for i in mb], [rl[i] for i in mb])
+            v = self._forward_values(pb)
+            for i, a in zip(mb, torch.split(v, pb.response_lengths)):
+                out[i] = a
+        return {"values": out}
+
     def _microbatches(self, lengths: Sequence[int], for_train: bool = True) -> list[list[int]]:
         cfg = self.cfg
         n = len(lengths)
@@ -187,6 +207,9 @@ class TrainActor:
     def _dummy_forward(self, backward: bool = False):
         pb = self._pack([[0, 0]], [1])
         if backward:
+            if self.role == "critic":
+                (self._forward_values(pb).sum() * 0.0).backward()
+                return
             lp, en = self._forward_logp(pb, False)
             (lp.sum() * 0.0).backward()
         else:
@@ -290,11 +313,15 @@ class TrainActor:
                 continue
             ids = [idx[j] for j in mb]
             pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
-            lp, en = self._forward_logp(pb, cfg.compute_entropy)
             lb = self._loss_batch(batch, ids, pb)
             if self.role == "critic":
-                raise NotImplementedError
-            loss, m = L.policy_loss(lp, en, lb, cfg.loss)
+                loss, m = L.value_loss(self._forward_values(pb), lb, cfg.loss)
+            elif self.role == "sft":
+                lp, _ = self._forward_logp(pb, False)
+                loss, m = L.sft_loss(lp, lb, cfg.loss)
+            else:
+                lp, en = self._forward_logp(pb, cfg.compute_entropy)
+                loss, m = L.policy_loss(lp, en, lb, cfg.loss)
             ntok += lb.loss_mask.sum()
             if cfg.loss.calculate_per_token_loss:
                 scaled = loss
@@ -327,6 +354,51 @@ class TrainActor:
         d = pack[-1].clamp_min(1)
         out = {k: pack[i] / d for i, k in enumerate(keys)}
         return out, norm
+
+    def train_critic(self, rollout_id: int, batch: dict) -> dict:
+        """PPO critic update (relax/backends/megatron/actor.py train_critic :844-888): ``batch`` carries the
+        rollout-time ``values`` and the GAE ``returns`` computed with them; clipped value loss."""
+        assert self.role == "critic"
+        return self._optimizer_steps(batch)
+
+    def train_sft(self, batch: dict) -> dict:
+        """Supervised step(s): next-token cross entropy over the positions with ``loss_masks`` 1
+        (relax/backends/megatron/loss.py sft_loss_function :1247-1298).  ``tokens`` are prompt+response,
+        ``response_lengths`` the trained suffix of each sample."""
+        assert self.role == "sft"
+        return self._optimizer_steps(batch)
+
+    def _optimizer_steps(self, batch: dict) -> dict:
+        cfg, dev = self.cfg, self.device
+        n = len(batch["tokens"])
+        per_step = max(1, cfg.global_batch_size // self.ps.dp.size)
+        nsteps = torch.tensor([max(1, math.ceil(n / per_step)) if n else 1], device=dev)
+        if self.ps.dp_cp.size > 1:
+            dist.all_reduce(nsteps, op=dist.ReduceOp.MAX, group=self.ps.dp_cp.group)
+        agg: dict = {}
+        norm = 0.0
+        for s_ in range(int(nsteps)):
+            idx = list(range(s_ * per_step, min(n, (s_ + 1) * per_step)))
+            m, norm = self._train_step(batch, idx)
+            for k, v in m.items():
+                agg[k] = agg.get(k, 0) + v / int(nsteps)
+        out = {k: float(v) for k, v in agg.items()}
+        out["grad_norm"] = norm
+        return out
+
+    @torch.no_grad()
+    def evaluate_ppl(self, batch: dict) -> dict:
+        """Token-level negative log-likelihood and perplexity over the masked positions (SFT eval)."""
+        lps = self.compute_log_prob(batch)["log_probs"]
+        tot = torch.zeros(2, device=self.device, dtype=torch.float64)
+        for lp, m in zip(lps, batch["loss_masks"]):
+            m = torch.as_tensor(m, dtype=torch.float32, device=self.device)
+            tot[0] += -(lp.float() * m).sum()
+            tot[1] += m.sum()
+        if self.ps.dp_cp.size > 1:
+            dist.all_reduce(tot, group=self.ps.dp_cp.group)
+        nll = float(tot[0] / tot[1].clamp_min(1))
+        return {"eval/nll": nll, "eval/ppl": math.exp(min(nll, 50.0)), "eval/tokens": float(tot[1])}
 
     # ------------------------------------------------------------------ misc
     def after_train(self):
