@@ -49,6 +49,12 @@ class ParamInit:
         return w.normal_(0.0, std, generator=g)
 
 
+def _lora():
+    from ..train import lora
+
+    return lora
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: ModelConfig, ps: ParallelState, dtype, device, gen, layer_idx: int):
         super().__init__()
@@ -88,6 +94,8 @@ class Attention(nn.Module):
     def forward(self, x_normed, cos, sin, cu_seqlens, attn_fn=None, max_seqlen=None):
         cfg = self.cfg
         qkv = TP.ag_linear(x_normed, self.linear_qkv.weight, self.ps.tp)
+        if hasattr(self.linear_qkv, "lora_A"):
+            qkv = qkv + _lora().lora_delta(self.linear_qkv, x_normed, self.ps.tp, True)
         if cfg.qkv_bias:
             qkv = qkv + self.linear_qkv.bias
         q, k, v = self.split_qkv(qkv)
@@ -101,7 +109,10 @@ class Attention(nn.Module):
         else:
             o = ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=True, max_seqlen=max_seqlen)
         o = o.reshape(o.shape[0], -1)
-        return TP.linear_rs(o, self.linear_proj.weight, self.ps.tp)
+        y = TP.linear_rs(o, self.linear_proj.weight, self.ps.tp)
+        if hasattr(self.linear_proj, "lora_A"):
+            y = y + _lora().lora_delta(self.linear_proj, o, self.ps.tp, False)
+        return y
 
 
 class MLP(nn.Module):
@@ -124,8 +135,13 @@ class MLP(nn.Module):
 
     def forward(self, x_normed):
         gu = TP.ag_linear(x_normed, self.linear_fc1.weight, self.ps.tp)
+        if hasattr(self.linear_fc1, "lora_A"):
+            gu = gu + _lora().lora_delta(self.linear_fc1, x_normed, self.ps.tp, True)
         a = ops.swiglu(gu)
-        return TP.linear_rs(a, self.linear_fc2.weight, self.ps.tp)
+        y = TP.linear_rs(a, self.linear_fc2.weight, self.ps.tp)
+        if hasattr(self.linear_fc2, "lora_A"):
+            y = y + _lora().lora_delta(self.linear_fc2, a, self.ps.tp, False)
+        return y
 
 
 class TransformerLayer(nn.Module):

@@ -52,6 +52,7 @@ class TrainConfig:
     keep_old_actor: bool = False
     compute_entropy: bool = True
     ref_on_host: bool = False           # keep the frozen reference weights in pinned host memory
+    lora: Optional[object] = None       # a train.lora.LoRAConfig: train adapters only
     loss: L.LossConfig = field(default_factory=L.LossConfig)
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
 
@@ -64,6 +65,10 @@ class TrainActor:
         self.ps = ps or single_process_state()
         self.device = torch.device(device)
         self.model = GPTModel(model_cfg, self.ps, device=device, seed=seed, recompute=cfg.recompute)
+        if cfg.lora is not None:
+            from .lora import apply_lora
+
+            apply_lora(self.model, cfg.lora)
         self.optimizer = DistributedOptimizer(self.model, self.ps, cfg.optim) if with_optimizer else None
         self.timer = Timer()
         self.weight_version = 0
@@ -409,6 +414,10 @@ class TrainActor:
     def named_local_params(self):
         """(megatron-style name, tensor) for every local parameter, actor weights."""
         self.switch_model("actor")
+        if self.cfg.lora is not None:
+            from .lora import merged_named_params
+
+            return merged_named_params(self.model)   # merged-weights sync: the engine sees a plain model
         return list(self.model.named_parameters())
 
     def sleep(self):

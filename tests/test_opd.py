@@ -1,0 +1,71 @@
+"""On-policy distillation divergences against brute-force statements."""
+import math
+
+import pytest
+import torch
+
+from relax_b200.algo import opd
+
+
+def _dists(R=5, V=11, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    s = torch.log_softmax(torch.randn(R, V, generator=g), -1)
+    t = torch.log_softmax(torch.randn(R, V, generator=g) * 1.5, -1)
+    return s, t
+
+
+def test_sampled_token_estimators():
+    s, t = _dists()
+    ids = torch.tensor([0, 3, 5, 7, 10])
+    sl, tl = s[torch.arange(5), ids], t[torch.arange(5), ids]
+    assert torch.allclose(opd.token_kl(sl, tl, "reverse_kl"), sl - tl)
+    r = sl - tl
+    assert torch.allclose(opd.token_kl(sl, tl, "low_var_kl"), torch.exp(-r) - 1 + r)
+    with pytest.raises(ValueError):
+        opd.token_kl(sl, tl, "jsd")
+    c = opd.token_kl(torch.tensor([-50.0]), torch.tensor([-1.0]), "reverse_kl", log_prob_min_clamp=-10.0)
+    assert float(c) == -9.0
+
+
+def test_full_support_topk_equals_exact_divergences():
+    s, t = _dists()
+    rev = (s.exp() * (s - t)).sum(-1)
+    fwd = (t.exp() * (t - s)).sum(-1)
+    for mode in ("tail", "norm", "trunc"):
+        assert torch.allclose(opd.token_kl(s, t, "reverse_kl", norm_mode=mode), rev, atol=1e-5)
+        assert torch.allclose(opd.token_kl(s, t, "forward_kl", norm_mode=mode), fwd, atol=1e-5)
+    a = 0.3
+    m = torch.log((1 - a) * s.exp() + a * t.exp())
+    jsd = (1 - a) * (s.exp() * (s - m)).sum(-1) + a * (t.exp() * (t - m)).sum(-1)
+    assert torch.allclose(opd.token_kl(s, t, "jsd", alpha=a, norm_mode="trunc"), jsd, atol=1e-5)
+
+
+def test_tail_bin_and_union_mask():
+    s, t = _dists(V=16)
+    ids_s, ids_t = s.topk(4, -1).indices, t.topk(4, -1).indices
+    ids, lens = opd.union_ids(ids_s, ids_t)
+    assert ids.shape[0] == 5 and int(lens.min()) >= 4 and int(lens.max()) <= 8
+    for r in range(5):
+        assert set(ids[r, :lens[r]].tolist()) == set(ids_s[r].tolist()) | set(ids_t[r].tolist())
+    sk, tk = s.gather(-1, ids), t.gather(-1, ids)
+    got = opd.per_token_signal("union", student_topk_lp=sk, teacher_topk_lp=tk, k_lengths=lens, kl_type="reverse_kl",
+                               norm_mode="tail")
+    for r in range(5):
+        k = int(lens[r])
+        ps, pt = sk[r, :k].exp(), tk[r, :k].exp()
+        want = (ps * (sk[r, :k] - tk[r, :k])).sum() + (1 - ps.sum()) * (torch.log(1 - ps.sum()) - torch.log(1 - pt.sum()))
+        assert abs(float(got[r]) - float(want)) < 1e-5
+        assert float(got[r]) >= -1e-6   # a KL between two proper distributions (K ids + tail)
+
+
+def test_advantage_shaping_and_loss():
+    adv = [torch.zeros(3), torch.ones(2)]
+    sig = [torch.tensor([0.5, 3.0, -1.0]), torch.tensor([0.1, 0.2])]
+    out = opd.apply_to_advantages(adv, sig, coef=2.0, per_token_clip=1.0)
+    assert torch.allclose(out[0], torch.tensor([-1.0, -2.0, 2.0])) and torch.allclose(out[1], torch.tensor([0.8, 0.6]))
+    assert opd.apply_to_advantages(adv, sig, coef=0.0) is adv
+    x = torch.tensor([1.0, 2.0, 3.0, 4.0, 5.0], requires_grad=True)
+    loss = opd.opd_loss(x, [torch.tensor([1.0, 0.0, 1.0]), torch.tensor([1.0, 1.0])], [3, 2], coef=0.5)
+    assert abs(float(loss) - 0.5 * (1 + 3 + 4 + 5) / 4) < 1e-6
+    loss.backward()
+    assert torch.allclose(x.grad, torch.tensor([0.125, 0.0, 0.125, 0.125, 0.125]))
