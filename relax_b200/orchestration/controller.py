@@ -1,0 +1,202 @@
+"""Controller: turns parsed flags into a running job.
+
+It picks the execution mode (colocated synchronous RL, fully-async / hybrid role pipeline, SFT),
+builds the model / trainer / rollout engine / data plane for it, resolves the start step from a
+checkpoint, runs the training loop with periodic save / eval / metrics reporting, watches role
+health, and shuts down gracefully on SIGTERM/SIGINT (finish the step in flight, save, exit).
+The reference's controller does the same over Ray Serve deployments (relax/core/controller.py:
+``__init__`` :147-212, ``training_loop`` :801-928, ``shutdown`` :930-959); here the roles are
+objects of one process per GPU, wired by ``torch.distributed``.
+"""
+from __future__ import annotations
+
+import os
+import signal
+import time
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..checkpoint import dist_ckpt
+from ..config.arguments import model_config_from_args, train_config_from_args
+from ..metrics.flops import B200_BF16_DENSE_TFLOPS, mfu, train_step_flops
+from ..metrics.service import MetricsClient, MetricsService
+from ..utils.profiler import TrainProfiler, memory_stats
+
+
+def _get(a, name, default=None):
+    v = getattr(a, name, None)
+    return default if v is None else v
+
+
+class Controller:
+    def __init__(self, args, metrics: Optional[MetricsService] = None, device: Optional[str] = None):
+        self.args = args
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        if device is None:
+            device = f"cuda:{int(os.environ.get('LOCAL_RANK', 0))}" if torch.cuda.is_available() else "cpu"
+        self.device = device
+        self.metrics = MetricsClient(service=metrics or MetricsService())
+        self.model_cfg = model_config_from_args(args)
+        self.train_cfg = train_config_from_args(args)
+        if getattr(args, "lora_rank", 0):
+            from ..train.lora import LoRAConfig
+
+            self.train_cfg.lora = LoRAConfig(rank=args.lora_rank, alpha=2.0 * args.lora_rank)
+        self.mode = self._pick_mode()
+        self._stop = False
+        self.profiler = TrainProfiler(_get(args, "profile_dir", args.save and os.path.join(args.save, "profile")),
+                                      _get(args, "profile_step_start", -1), _get(args, "profile_step_end", -1), self.rank)
+        self.start_rollout_id = dist_ckpt.resolve_start_rollout_id(args.load, args.start_rollout_id)
+        self.runner = self._build_runner()
+        self._maybe_resume()
+
+    # ------------------------------------------------------------------ mode
+    def _pick_mode(self) -> str:
+        a = self.args
+        if getattr(a, "loss_type", "policy_loss") == "sft_loss":
+            return "sft"
+        if getattr(a, "fully_async", False) or getattr(a, "hybrid", False):
+            return "async"
+        return "colocate"
+
+    def _build_runner(self):
+        a = self.args
+        if self.mode == "colocate":
+            from .colocate import ColocatedGRPO, ColocateConfig
+
+            plen = _get(a, "rollout_max_prompt_len", 512)
+            ctx = _get(a, "rollout_max_context_len", plen + a.rollout_max_response_len)
+            page = _get(a, "sglang_page_size", 16)
+            cfg = ColocateConfig(
+                model=self.model_cfg, train=self.train_cfg, trainer_tp=a.tensor_model_parallel_size,
+                trainer_cp=a.context_parallel_size, rollout_tp=_get(a, "rollout_num_gpus_per_engine", 1),
+                rollout_batch_size=a.rollout_batch_size, prompt_len=plen,
+                max_response_len=a.rollout_max_response_len, temperature=a.rollout_temperature,
+                top_p=_get(a, "rollout_top_p", 1.0), top_k=_get(a, "rollout_top_k", -1), rm_type=a.rm_type or "parity",
+                kv_blocks=_get(a, "kv_blocks", max(64, a.rollout_batch_size * a.n_samples_per_prompt * (ctx // 16 + 2))),
+                kv_block_size=page if page > 1 else 16,
+                max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
+                offload_rollout=a.offload_rollout, offload_train=a.offload_train)
+            return ColocatedGRPO(cfg, device=self.device)
+        if self.mode == "sft":
+            from ..train.actor import TrainActor
+            from ..parallel.state import ParallelDims, init_parallel_state, single_process_state
+
+            ps = (init_parallel_state(ParallelDims(tp=a.tensor_model_parallel_size, cp=a.context_parallel_size,
+                                                   dp=self.world // (a.tensor_model_parallel_size * a.context_parallel_size)))
+                  if self.world > 1 else single_process_state())
+            return _SFTRunner(TrainActor(self.model_cfg, self.train_cfg, ps, device=self.device, seed=a.seed, role="sft"), a)
+        from .async_runner import build_async_runner
+
+        return build_async_runner(self.args, self.model_cfg, self.train_cfg, self.device, self.start_rollout_id)
+
+    # ------------------------------------------------------------------ checkpoints
+    def _actor(self):
+        return getattr(self.runner, "actor", None)
+
+    def _maybe_resume(self):
+        a, actor = self.args, self._actor()
+        if not a.load or actor is None or not os.path.isdir(a.load):
+            return
+        if dist_ckpt.read_latest_iteration(a.load) is None:
+            return
+        dist_ckpt.load_checkpoint(a.load, self.model_cfg, actor.ps, actor.model, None if _get(a, "no_load_optim", False) else actor.optimizer)
+        if hasattr(self.runner, "sync_weights"):
+            self.runner.sync_weights()
+        if hasattr(self.runner, "rollout_id"):
+            self.runner.rollout_id = self.start_rollout_id
+
+    def save(self, rollout_id: int):
+        a, actor = self.args, self._actor()
+        if not a.save or actor is None:
+            return
+        dist_ckpt.save_checkpoint(a.save, rollout_id, self.model_cfg, actor.ps, actor.model,
+                                  None if _get(a, "no_save_optim", False) else actor.optimizer)
+        if self.rank == 0:
+            dist_ckpt.rotate_checkpoints(a.save, getattr(a, "max_checkpoints_to_keep", None))
+
+    # ------------------------------------------------------------------ loop
+    def _install_signal_handlers(self):
+        def handler(signum, frame):
+            self._stop = True
+
+        for s in (signal.SIGTERM, signal.SIGINT):
+            try:
+                signal.signal(s, handler)
+            except ValueError:   # not the main thread (tests)
+                pass
+
+    def training_loop(self) -> list:
+        a = self.args
+        self._install_signal_handlers()
+        history = []
+        if self.mode == "async":
+            out = self.runner.run()
+            for rid, m in out:
+                self.metrics.log_metrics_batch(rid, {k: float(v) for k, v in m.items() if isinstance(v, (int, float))})
+                self.metrics.report_step(rid)
+            if out:
+                self.save(max(r for r, _ in out))
+            return out
+        rid = self.start_rollout_id
+        while rid < a.num_rollout and not self._stop:
+            t0 = time.perf_counter()
+            m = self.runner.step()
+            dt = time.perf_counter() - t0
+            rec = {k: float(v) for k, v in m.items() if isinstance(v, (int, float))}
+            rec["perf/step_time"] = dt
+            if "total_tokens_local" in m and getattr(a, "profile_with_flops", True):
+                n = max(1, int(m["total_tokens_local"]))
+                seq = _get(a, "rollout_max_prompt_len", 512) + a.rollout_max_response_len if self.mode == "colocate" else n
+                lens = [seq] * max(1, n // max(1, seq))
+                fl = train_step_flops(self.model_cfg, lens, forward_only_passes=2)
+                rec["perf/train_mfu"] = mfu(fl, max(m.get("perf/train_time", dt), 1e-9), 1, B200_BF16_DENSE_TFLOPS)
+            rec.update(memory_stats(self.device) if str(self.device).startswith("cuda") else {})
+            self.metrics.log_metrics_batch(rid, rec)
+            self.metrics.report_step(rid)
+            self.profiler.step()
+            history.append(rec)
+            rid += 1
+            if a.save and a.save_interval and rid % a.save_interval == 0:
+                self.save(rid - 1)   # a checkpoint is named after the last rollout it contains
+        if self._stop and a.save and rid > self.start_rollout_id:
+            self.save(rid - 1)   # interrupted: keep what was learned
+        self.profiler.close()
+        return history
+
+    def shutdown(self):
+        svc = self.metrics.service
+        if svc is not None:
+            svc.close()
+        if hasattr(self.runner, "close"):
+            self.runner.close()
+
+
+class _SFTRunner:
+    """One ``step()`` = one global batch of the streaming SFT dataset."""
+
+    def __init__(self, actor, args):
+        from ..data.sft import StreamingSFTDataset, pack_batches
+
+        self.actor = actor
+        files = [p for p in str(args.prompt_data).split(",") if p]
+        tok = _byte_tokenizer(actor.mcfg.vocab_size)
+        ds = StreamingSFTDataset(files, tok, actor.ps.dp.rank, actor.ps.dp.size,
+                                 max_len=_get(args, "rollout_max_context_len", 4096), epochs=None)
+        per_rank = max(1, actor.cfg.global_batch_size // actor.ps.dp.size)
+        self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
+        self.dataset = ds
+
+    def step(self) -> dict:
+        b = next(self.batches)
+        m = self.actor.train_sft(b)
+        m["total_tokens_local"] = sum(len(t) for t in b["tokens"])
+        return m
+
+
+def _byte_tokenizer(vocab: int):
+    """Fallback tokenizer when no HF tokenizer directory is given: UTF-8 bytes offset past the special ids."""
+    return lambda s: [3 + (b % max(1, vocab - 3)) for b in s.encode("utf-8")]

@@ -1,0 +1,38 @@
+"""The train entrypoint end to end on CPU with the tiny model: colocated RL with save/resume, async mode, SFT."""
+import json
+import os
+
+from relax_b200.checkpoint import dist_ckpt
+from relax_b200.entrypoints.train import main
+
+COMMON = ["--model-name", "tiny", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+          "--rollout-max-prompt-len", "8", "--rollout-max-response-len", "8", "--lr", "1e-4", "--max-tokens-per-gpu", "256"]
+
+
+def test_colocated_run_saves_and_resumes(tmp_path):
+    save = str(tmp_path / "ckpt")
+    assert main(COMMON + ["--num-rollout", "2", "--save", save, "--save-interval", "1", "--colocate"]) == 0
+    assert dist_ckpt.read_latest_iteration(save) == 1
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert [l["step"] for l in lines] == [0, 1] and "perf/step_time" in lines[0]
+    # resume: starts at step 2, runs one more
+    assert main(COMMON + ["--num-rollout", "3", "--save", save, "--load", save, "--save-interval", "1", "--colocate"]) == 0
+    assert dist_ckpt.read_latest_iteration(save) == 2
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert [l["step"] for l in lines] == [0, 1, 2]
+
+
+def test_fully_async_run(tmp_path):
+    assert main(COMMON + ["--num-rollout", "3", "--fully-async", "--max-staleness", "1"]) == 0
+
+
+def test_sft_run(tmp_path):
+    data = tmp_path / "sft.jsonl"
+    with open(data, "w") as f:
+        for i in range(16):
+            f.write(json.dumps({"prompt": f"say {i}", "response": f"number {i}"}) + "\n")
+    save = str(tmp_path / "sft_ckpt")
+    assert main(["--model-name", "tiny", "--loss-type", "sft_loss", "--prompt-data", str(data), "--num-rollout", "3",
+                 "--global-batch-size", "4", "--lr", "1e-3", "--max-tokens-per-gpu", "512", "--save", save]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert len(lines) == 3 and lines[-1]["loss"] < lines[0]["loss"]
