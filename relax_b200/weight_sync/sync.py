@@ -47,8 +47,10 @@ class WeightSync:
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int,
                  trainer_ranks: Sequence[int], rollout_ranks: Sequence[int], rollout_ep: int = 1,
-                 group=None):
+                 group=None, post_hook=None):
         self.cfg = cfg
+        # ``post_hook(name, tensor) -> tensor`` runs on every rollout tensor after the copy (quantisation round trip)
+        self.post_hook = post_hook
         self.plan = build_plan(cfg, trainer_layout, rollout_tp, rollout_ep)
         self.trainer_ranks, self.rollout_ranks = list(trainer_ranks), list(rollout_ranks)
         self.me = dist.get_rank() if dist.is_initialized() else 0
@@ -103,6 +105,12 @@ class WeightSync:
                 d = _view2d(rollout_weights.p[b.dst_name], b.dst_batch)[b.dst_row:b.dst_row + b.rows, b.dst_col:b.dst_col + b.cols]
                 d.copy_(buf[o:o + b.rows * b.cols].view(b.rows, b.cols))
                 o += b.rows * b.cols
+        if self.post_hook is not None and rollout_weights is not None:
+            with torch.no_grad():
+                for n, t in rollout_weights.p.items():
+                    q = self.post_hook(n, t)
+                    if q is not t:
+                        t.copy_(q)
         if engine is not None:
             if version is not None:
                 engine.update_weight_version(version)

@@ -1,0 +1,83 @@
+"""Filters + dynamic sampling, env registry, reloadable process groups, quantised weight-sync hook."""
+import pytest
+import torch
+
+from relax_b200.rollout.filters import FilterOutput, check_reward_nonzero_std, dynamic_sampling, load_filter
+from relax_b200.types import Sample
+from relax_b200.utils import env as E
+from relax_b200.weight_sync import quant as Q
+from tests._mp import run_distributed
+
+
+def _group(rewards, gi=0):
+    return [Sample(group_index=gi, index=i, tokens=[1, 2], response_length=1, reward=r) for i, r in enumerate(rewards)]
+
+
+def test_nonzero_std_filter_and_oversampling():
+    assert check_reward_nonzero_std(_group([0, 1, 0])).keep
+    out = check_reward_nonzero_std(_group([1, 1, 1]))
+    assert not out.keep and out.reason.startswith("zero_std")
+    calls = []
+    pool = iter([_group([1, 1]), _group([0, 1]), _group([0, 0]), _group([1, 0]), _group([0, 1]), _group([1, 0])])
+
+    def gen(n):
+        calls.append(n)
+        return [next(pool) for _ in range(n)]
+
+    back = []
+    kept, stats = dynamic_sampling(gen, 3, over_sampling_batch_size=3, group_filter=check_reward_nonzero_std, give_back=back.extend)
+    assert len(kept) == 3 and calls == [3, 3] and stats["dropped_groups"] == 2 and len(back) == 1
+    assert stats["drop/zero_std_1.0"] == 1 and stats["drop/zero_std_0.0"] == 1
+    with pytest.raises(RuntimeError):
+        dynamic_sampling(lambda n: [_group([1, 1]) for _ in range(n)], 1, group_filter=check_reward_nonzero_std, max_rounds=3)
+    assert load_filter("relax_b200.rollout.filters:check_reward_nonzero_std") is check_reward_nonzero_std
+
+
+def test_env_registry_validates():
+    vals = E.validate_env({"RELAX_B200_FUSED_TP": "0", "RELAX_B200_PEER_WAIT_MS": "250", "PATH": "/bin"})
+    assert vals["RELAX_B200_FUSED_TP"] is False and vals["RELAX_B200_PEER_WAIT_MS"] == 250
+    assert vals["RELAX_B200_DECODE_ATTN_VERSION"] == 3
+    with pytest.raises(ValueError):
+        E.validate_env({"RELAX_B200_FUSED_TPP": "1"})
+    with pytest.raises(ValueError):
+        E.validate_env({"RELAX_B200_DECODE_ATTN_VERSION": "7"})
+    with pytest.raises(ValueError):
+        E.validate_env({"RELAX_B200_PEER_WAIT_MS": "soon"})
+
+
+def _reload_worker(rank, world):
+    import torch.distributed as dist
+    from relax_b200.parallel import reloadable as R
+
+    g = R.ReloadableGroup([0, 1])
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t, group=g.group)
+    gen0 = g.generation
+    R.destroy_all()
+    assert not g.alive
+    R.reload_all()
+    t2 = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t2, group=g.group)
+    R.forget_all()
+    return float(t), float(t2), gen0, g.generation
+
+
+def test_reloadable_group_survives_destroy():
+    out = run_distributed(_reload_worker, 2)
+    assert all(o == (3.0, 3.0, 1, 2) for o in out)
+
+
+def test_quant_hooks_roundtrip_only_matrices():
+    torch.manual_seed(0)
+    w = torch.randn(256, 256).bfloat16()
+    h8 = Q.make_hook("fp8")
+    q = h8("layers.0.qkv", w)
+    assert q.shape == w.shape and not torch.equal(q, w) and (q.float() - w.float()).abs().max() < 0.3
+    v = w[0]
+    assert h8("layers.0.input_norm", w) is w and h8("layers.0.qkv", v) is v
+    h4 = Q.make_hook("int4", group=128)
+    q4 = h4("layers.0.down", w)
+    assert q4.shape == w.shape and len(torch.unique(q4[0, :128].float())) <= 16
+    assert Q.make_hook(None) is None
+    with pytest.raises(ValueError):
+        Q.make_hook("fp4")
