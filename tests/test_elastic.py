@@ -1,0 +1,95 @@
+"""Engine pool scale-out / scale-in state machine and the rule-based autoscaler (fake engines, fake clock)."""
+import pytest
+
+from relax_b200.rollout.elastic import Autoscaler, AutoscalerConfig, EnginePool, EngineState, Rule
+from relax_b200.rollout.router import Router
+
+
+class _Eng:
+    def __init__(self, eid, fail_sync=False):
+        self.eid, self.version, self.fail_sync, self.closed, self.aborted = eid, -1, fail_sync, False, False
+
+
+def _pool(fail_ids=(), clock=None):
+    t = clock or [0.0]
+    r = Router(clock=lambda: t[0])
+
+    def sync(seed, new):
+        if new.fail_sync:
+            raise RuntimeError("nvlink copy failed")
+        new.version = seed.version
+        return new.version
+
+    def abort(e):
+        e.aborted = True
+        return ["partial-sample"]
+
+    pool = EnginePool(r, lambda eid: _Eng(eid, eid in fail_ids), sync, precheck=lambda s, n: True,
+                      shutdown=lambda e: setattr(e, "closed", True), abort=abort, clock=lambda: t[0],
+                      sleep=lambda s: t.__setitem__(0, t[0] + s))
+    seed = _Eng("seed")
+    seed.version = 7
+    pool.add_existing("seed", seed, 7)
+    return pool, r, t
+
+
+def test_scale_out_copies_current_weights_and_routes():
+    pool, r, _ = _pool()
+    res = pool.scale_out(2)
+    assert len(res.succeeded) == 2 and not res.failed
+    assert all(pool.engines[e].state == EngineState.ACTIVE and pool.engines[e].weight_version == 7 for e in res.succeeded)
+    assert set(r.workers()) == {"seed", *res.succeeded}
+
+
+def test_partial_success_policies():
+    pool, r, _ = _pool(fail_ids={"scaled-1"})
+    res = pool.scale_out(2, partial_success_policy="keep_partial")
+    assert res.succeeded == ["scaled-0"] and "scaled-1" in res.failed
+    assert pool.engines["scaled-1"].state == EngineState.FAILED and "scaled-1" not in r.workers()
+    pool2, r2, _ = _pool(fail_ids={"scaled-1"})
+    res2 = pool2.scale_out(2, partial_success_policy="rollback_all")
+    assert res2.rolled_back and not res2.succeeded and set(r2.workers()) == {"seed"}
+    assert pool2.engines["scaled-0"].state == EngineState.REMOVED
+
+
+def test_scale_in_drains_then_aborts_after_timeout():
+    pool, r, t = _pool()
+    ids = pool.scale_out(2).succeeded
+    busy = ids[0]
+    # make `busy` hold a request; the other one is idle
+    while r.acquire() != busy:
+        pass
+    for w, st in r.workers().items():
+        if w != busy:
+            for _ in range(st["in_flight"]):
+                r.release(w)
+    returned = []
+    removed = pool.scale_in(ids=ids, shutdown_timeout_s=1.0, on_abort=returned.extend)
+    assert set(removed) == set(ids) and returned == ["partial-sample"]
+    assert all(pool.engines[e].state == EngineState.REMOVED for e in ids) and set(r.workers()) == {"seed"}
+    assert pool.scale_in(1) == []   # never below min_engines
+
+
+def test_autoscaler_hold_time_and_cooldowns():
+    pool, r, t = _pool()
+    m = {"queue_depth_per_engine": 20.0, "kv_cache_utilization": 0.9}
+    cfg = AutoscalerConfig(min_engines=1, max_engines=3, scale_out_cooldown_s=100, scale_in_cooldown_s=100,
+                           rules=[Rule("queue_depth_per_engine", 8, "above", for_s=30), Rule("kv_cache_utilization", 0.3, "below", for_s=60)])
+    a = Autoscaler(pool, cfg, lambda: dict(m), clock=lambda: t[0])
+    assert a.step() is None            # condition just started
+    t[0] = 31
+    assert a.step() == "scale_out" and len(pool.active()) == 2
+    t[0] = 70
+    assert a.step() is None            # hold time restarts, and cooldown
+    t[0] = 140
+    assert a.step() == "scale_out" and len(pool.active()) == 3
+    t[0] = 300
+    assert a.step() is None            # at max_engines
+    m.update(queue_depth_per_engine=0.0, kv_cache_utilization=0.1)
+    t[0] = 310
+    assert a.step() is None
+    t[0] = 380
+    assert a.step() == "scale_in" and len(pool.active()) == 2
+    assert [d[1] for d in a.decisions] == ["scale_out", "scale_out", "scale_in"]
+    cfg2 = AutoscalerConfig.from_dict({"max_engines": 4, "rules": [{"metric": "x", "threshold": 1, "direction": "above"}]})
+    assert cfg2.max_engines == 4 and cfg2.rules[0].metric == "x"
