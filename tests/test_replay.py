@@ -1,0 +1,42 @@
+"""Trajectory replay: capture the loss / advantage stages, replay them, detect a changed implementation."""
+import torch
+
+from relax_b200.algo import loss as L
+from relax_b200.algo.ppo_utils import Segments
+from relax_b200.utils.replay import ReplayRecorder, default_stage_functions, replay_bundle
+
+
+def _loss_inputs():
+    torch.manual_seed(0)
+    seg = Segments.from_lengths([3, 2])
+    lp = torch.randn(5) * 0.1 - 1.0
+    b = L.LossBatch(seg=seg, loss_mask=torch.ones(5), advantages=torch.randn(5), old_log_probs=lp + 0.05 * torch.randn(5),
+                    ref_log_probs=lp.clone(), rollout_log_probs=None, returns=None, values=None, sample_denoms=None)
+    return dict(log_probs=lp, entropy=torch.rand(5), batch=b, cfg=L.LossConfig(eps_clip=0.2, use_kl_loss=True, kl_loss_coef=0.01))
+
+
+def test_capture_and_replay_roundtrip(tmp_path):
+    rec = ReplayRecorder(str(tmp_path))
+    fns = default_stage_functions()
+    run_loss = rec.wrap("loss", fns["loss"], lambda: 3)
+    out = run_loss(**_loss_inputs())
+    adv_in = dict(estimator="grpo", rewards=torch.tensor([1.0, 0.0]), seg=Segments.from_lengths([3, 2]), loss_mask=torch.ones(5))
+    rec.wrap("advantages", fns["advantages"], lambda: 3)(**adv_in)
+    assert len(rec.records) == 2 and rec.records[0]["rollout_id"] == 3
+    reports = replay_bundle(str(tmp_path))
+    assert [r["ok"] for r in reports] == [True, True]
+    # a changed implementation is flagged with the path of the first difference
+    bad = dict(fns)
+    bad["loss"] = lambda **kw: {"loss": fns["loss"](**kw)["loss"] * 1.01, "metrics": fns["loss"](**kw)["metrics"]}
+    rep = replay_bundle(str(tmp_path), bad)
+    assert rep[0]["ok"] is False and rep[0]["diffs"][0][0] == "out.loss" and rep[1]["ok"]
+    assert torch.is_tensor(out["loss"])
+
+
+def test_disabled_recorder_is_free(tmp_path):
+    rec = ReplayRecorder(None)
+    assert rec.capture("loss", 0, {}, {}) is None and not rec.enabled
+    small = ReplayRecorder(str(tmp_path), stages=("loss",), max_records=1)
+    assert small.capture("advantages", 0, {}, {}) is None
+    assert small.capture("loss", 0, {"x": torch.ones(1)}, {"y": 1.0}) is not None
+    assert small.capture("loss", 1, {"x": torch.ones(1)}, {"y": 1.0}) is None
