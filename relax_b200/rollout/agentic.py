@@ -1,0 +1,193 @@
+"""Agentic (multi-turn, tool-using) rollout.
+
+An episode alternates model turns and environment turns (tool results, user replies).  The whole
+conversation is ONE training sample: prompt and environment tokens carry loss mask 0, model tokens
+carry mask 1 and their sampling log-probs, so the trainer sees exactly the tokens the engine
+produced.  Every model turn re-submits "conversation so far" - the session keeps the token ids it
+already has (no re-tokenisation of generated text, whose tokenisation need not round-trip) and the
+engine's group prefix sharing turns the re-submission into a cache hit.
+
+Pieces (relax/agentic/: ``rollout.py`` resident pipeline, ``session/state.py`` ``SessionForest``,
+``session/service.py`` chat API, admission control):
+
+* :class:`AgentEnv` - protocol of an environment: ``reset() -> messages``, ``step(text) -> (observation, reward, done)``.
+* :class:`Session` / :class:`SessionForest` - token-level state of a conversation; ``fork`` branches an
+  episode at a turn (tree search, best-of-n continuation) sharing the parent's prefix.
+* :func:`run_episode` / :func:`run_episodes` - the loop; ``run_episodes`` advances many sessions in
+  lock-step so that every engine call carries a full batch, bounded by an admission limit.
+* env registry (:func:`register_env`) for ``--custom-env`` style lookup.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Protocol, Sequence, Tuple
+
+from ..types import Sample, SampleStatus
+
+
+class AgentEnv(Protocol):
+    def reset(self) -> List[dict]: ...
+
+    def step(self, assistant_text: str) -> Tuple[Optional[str], float, bool]: ...
+
+
+_ENVS: Dict[str, Callable[..., AgentEnv]] = {}
+
+
+def register_env(name: str):
+    def deco(factory):
+        _ENVS[name] = factory
+        return factory
+
+    return deco
+
+
+def make_env(name: str, **kw) -> AgentEnv:
+    if name not in _ENVS:
+        raise KeyError(f"unknown environment {name!r}; registered: {sorted(_ENVS)}")
+    return _ENVS[name](**kw)
+
+
+@dataclass
+class Tokenizer:
+    encode: Callable[[str], List[int]]
+    decode: Callable[[Sequence[int]], str]
+    render_turn: Callable[[str, str], str] = lambda role, content: f"<|{role}|>\n{content}\n"
+    generation_prompt: str = "<|assistant|>\n"
+
+
+@dataclass
+class Session:
+    sid: int
+    tokens: List[int] = field(default_factory=list)
+    loss_mask: List[int] = field(default_factory=list)
+    log_probs: List[float] = field(default_factory=list)
+    weight_versions: List[int] = field(default_factory=list)
+    prompt_len: int = 0
+    turns: int = 0
+    reward: float = 0.0
+    done: bool = False
+    truncated: bool = False
+    parent: Optional[int] = None
+    branch_point: int = 0          # tokens shared with the parent
+
+    def append(self, toks: Sequence[int], mask: int, lps: Optional[Sequence[float]] = None):
+        self.tokens += list(toks)
+        self.loss_mask += [mask] * len(toks)
+        self.log_probs += list(lps) if lps is not None else [0.0] * len(toks)
+
+    def to_sample(self, group_index: Optional[int] = None, index: Optional[int] = None) -> Sample:
+        rl = len(self.tokens) - self.prompt_len
+        return Sample(group_index=group_index, index=index, tokens=list(self.tokens), response_length=rl,
+                      loss_mask=self.loss_mask[self.prompt_len:], rollout_log_probs=self.log_probs[self.prompt_len:],
+                      reward=self.reward, weight_versions=sorted(set(self.weight_versions)),
+                      status=SampleStatus.TRUNCATED if self.truncated else SampleStatus.COMPLETED)
+
+
+class SessionForest:
+    """Sessions with parent links; a fork shares its parent's tokens up to the branch point."""
+
+    def __init__(self):
+        self.sessions: Dict[int, Session] = {}
+        self._ids = itertools.count()
+
+    def new(self) -> Session:
+        s = Session(next(self._ids))
+        self.sessions[s.sid] = s
+        return s
+
+    def fork(self, sid: int, at_tokens: Optional[int] = None) -> Session:
+        p = self.sessions[sid]
+        n = len(p.tokens) if at_tokens is None else at_tokens
+        s = Session(next(self._ids), p.tokens[:n], p.loss_mask[:n], p.log_probs[:n], list(p.weight_versions),
+                    p.prompt_len, p.turns, 0.0, False, False, parent=sid, branch_point=n)
+        self.sessions[s.sid] = s
+        return s
+
+    def shared_prefix(self, a: int, b: int) -> int:
+        ta, tb = self.sessions[a].tokens, self.sessions[b].tokens
+        n = 0
+        for x, y in zip(ta, tb):
+            if x != y:
+                break
+            n += 1
+        return n
+
+    def children(self, sid: int) -> List[int]:
+        return [s.sid for s in self.sessions.values() if s.parent == sid]
+
+
+GenerateFn = Callable[[List[List[int]], int, List[int]], List[Tuple[List[int], List[float], str, List[int]]]]
+"""``generate(prompts, max_new_tokens, group_keys) -> [(tokens, logprobs, finish_reason, weight_versions)]``"""
+
+
+def engine_generate_fn(engine, sampling) -> GenerateFn:
+    """Adapter over :class:`~relax_b200.rollout.engine.RolloutEngine`."""
+    import dataclasses as _dc
+
+    def gen(prompts, max_new, keys):
+        sp = _dc.replace(sampling, max_new_tokens=max_new)
+        res = engine.generate(prompts, sp, group_keys=keys)
+        return [(list(r.output), list(r.logprobs), r.finish_reason, list(r.weight_versions)) for r in res]
+
+    return gen
+
+
+def run_episodes(envs: Sequence[AgentEnv], generate: GenerateFn, tok: Tokenizer, max_turns: int = 8,
+                 max_new_tokens: int = 256, max_context: int = 4096, max_concurrent: Optional[int] = None,
+                 forest: Optional[SessionForest] = None) -> List[Session]:
+    """Advance all episodes turn by turn; each engine call batches the sessions that still run (at most
+    ``max_concurrent`` at a time: admission control against KV-cache exhaustion)."""
+    forest = forest or SessionForest()
+    sess: List[Session] = []
+    for env in envs:
+        s = forest.new()
+        for m in env.reset():
+            s.append(tok.encode(tok.render_turn(m["role"], m["content"])), 0)
+        s.prompt_len = len(s.tokens)
+        sess.append(s)
+    live = list(range(len(envs)))
+    while live:
+        wave = live[:max_concurrent] if max_concurrent else live
+        prompts, budget = [], []
+        for i in wave:
+            s = sess[i]
+            if s.turns == 0 or s.loss_mask[-1] == 0:
+                gp = tok.encode(tok.generation_prompt)
+                if len(s.tokens) + len(gp) < max_context:
+                    s.append(gp, 0)
+                else:
+                    s.truncated = s.done = True
+            room = 0 if s.done else max_context - len(s.tokens)
+            budget.append(max(0, min(max_new_tokens, room)))
+            prompts.append(list(s.tokens))
+        runnable = [(i, p, b) for i, p, b in zip(wave, prompts, budget) if b > 0]
+        for i, _, b in zip(wave, prompts, budget):
+            if b <= 0:
+                sess[i].truncated = sess[i].done = True
+        if runnable:
+            outs = generate([p for _, p, _ in runnable], max(b for _, _, b in runnable), [sess[i].sid for i, _, _ in runnable])
+            for (i, _, b), (toks, lps, reason, versions) in zip(runnable, outs):
+                s = sess[i]
+                toks, lps = toks[:b], lps[:b]
+                s.append(toks, 1, lps)
+                s.weight_versions += versions
+                s.turns += 1
+                obs, reward, done = envs[i].step(tok.decode(toks))
+                s.reward += reward
+                if done or s.turns >= max_turns:
+                    s.done = True
+                    s.truncated = not done
+                elif obs is not None:
+                    ot = tok.encode(tok.render_turn("tool", obs))
+                    if len(s.tokens) + len(ot) >= max_context:   # no room for the observation and a reply to it
+                        s.truncated = s.done = True
+                    else:
+                        s.append(ot, 0)
+        live = [i for i in live if not sess[i].done]
+    return sess
+
+
+def run_episode(env: AgentEnv, generate: GenerateFn, tok: Tokenizer, **kw) -> Session:
+    return run_episodes([env], generate, tok, **kw)[0]

@@ -1,0 +1,114 @@
+"""Agentic multi-turn rollout, session forest, OpenAI-compatible endpoint, generative reward model."""
+import json
+import urllib.request
+
+import pytest
+
+from relax_b200.rewards.genrm import GenRM, JudgeEngine, parse_verdict
+from relax_b200.rollout import agentic as A
+from relax_b200.rollout.openai_api import ChatService, serve
+
+TOK = A.Tokenizer(encode=lambda s: [ord(c) for c in s], decode=lambda t: "".join(chr(x) for x in t))
+
+
+class _CountEnv:
+    """The agent must say 'ping' twice; each tool reply is 'pong'."""
+
+    def __init__(self):
+        self.n = 0
+
+    def reset(self):
+        return [{"role": "user", "content": "play"}]
+
+    def step(self, text):
+        self.n += 1
+        ok = "ping" in text
+        return ("pong", 1.0 if ok else 0.0, self.n >= 2)
+
+
+def _fake_generate(prompts, max_new, keys):
+    return [(TOK.encode("ping")[:max_new], [-0.1] * min(4, max_new), "stop", [3]) for _ in prompts]
+
+
+def test_episode_masks_and_logprobs():
+    s = A.run_episode(_CountEnv(), _fake_generate, TOK, max_turns=5)
+    smp = s.to_sample(group_index=0, index=0)
+    text = TOK.decode(smp.tokens)
+    assert text.count("ping") == 2 and text.count("pong") == 1 and s.reward == 2.0 and s.turns == 2
+    assert len(smp.loss_mask) == smp.response_length == len(smp.rollout_log_probs)
+    gen = [t for t, m in zip(smp.tokens[-smp.response_length:], smp.loss_mask) if m]
+    assert TOK.decode(gen) == "pingping"
+    assert all((lp == -0.1) == bool(m) for lp, m in zip(smp.rollout_log_probs, smp.loss_mask))
+    assert smp.weight_versions == [3]
+
+
+def test_lockstep_batching_admission_and_truncation():
+    calls = []
+
+    def gen(prompts, max_new, keys):
+        calls.append(len(prompts))
+        return _fake_generate(prompts, max_new, keys)
+
+    sess = A.run_episodes([_CountEnv() for _ in range(5)], gen, TOK, max_concurrent=2)
+    assert all(s.done and s.turns == 2 for s in sess) and max(calls) == 2
+    short = A.run_episode(_CountEnv(), _fake_generate, TOK, max_context=30)
+    assert short.truncated and len(short.tokens) <= 30
+
+
+def test_session_forest_fork_shares_prefix():
+    f = A.SessionForest()
+    a = f.new()
+    a.append([1, 2, 3, 4], 0)
+    a.prompt_len = 4
+    a.append([5, 6], 1, [-1.0, -2.0])
+    b = f.fork(a.sid, at_tokens=5)
+    b.append([9], 1, [-3.0])
+    assert f.shared_prefix(a.sid, b.sid) == 5 and f.children(a.sid) == [b.sid] and b.branch_point == 5
+    assert b.to_sample().rollout_log_probs == [-1.0, -3.0]
+
+
+def test_env_registry():
+    A.register_env("count")(_CountEnv)
+    assert isinstance(A.make_env("count"), _CountEnv)
+    with pytest.raises(KeyError):
+        A.make_env("nope")
+
+
+def test_openai_endpoint_roundtrip_and_session_sample():
+    svc = ChatService(_fake_generate, TOK)
+    srv, url = serve(svc)
+    try:
+        def post(body, sid):
+            req = urllib.request.Request(url + "/v1/chat/completions", data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json", "X-Session-Id": sid})
+            return json.loads(urllib.request.urlopen(req, timeout=10).read())
+
+        msgs = [{"role": "user", "content": "hi"}]
+        r1 = post({"messages": msgs, "max_tokens": 8, "logprobs": True}, "s1")
+        assert r1["choices"][0]["message"]["content"] == "ping" and r1["usage"]["completion_tokens"] == 4
+        assert len(r1["choices"][0]["logprobs"]["content"]) == 4
+        msgs += [r1["choices"][0]["message"], {"role": "tool", "content": "pong"}]
+        post({"messages": msgs, "max_tokens": 8}, "s1")
+        smp = svc.finish_session("s1", reward=1.0)
+        assert sum(smp.loss_mask) == 8 and smp.reward == 1.0 and "pong" in TOK.decode(smp.tokens)
+        models = json.loads(urllib.request.urlopen(url + "/v1/models", timeout=10).read())
+        assert models["data"][0]["id"] == svc.model_name
+    finally:
+        srv.shutdown()
+
+
+def test_genrm_parsing_failover_and_default():
+    assert parse_verdict("blah Verdict: correct") == 1.0 and parse_verdict("Verdict: wrong") == 0.0
+    assert parse_verdict("Score: 7") == 0.7 and parse_verdict("score - 3/4") == 0.75 and parse_verdict("??", 0.5) == 0.5
+
+    def broken(prompts, n):
+        raise RuntimeError("engine lost")
+
+    good = JudgeEngine(lambda prompts, n: ["Verdict: correct" if "42" in p.split("Candidate answer:")[1] else "Verdict: incorrect" for p in prompts])
+    rm = GenRM([JudgeEngine(broken), good])
+    assert rm.score(["q", "q"], ["42", "42"], ["it is 42", "it is 41"]) == [1.0, 0.0]
+    assert rm.failures == 1 and not rm.engines[0].healthy
+    rm.recover(lambda e: True)
+    assert rm.engines[0].healthy
+    dead = GenRM([JudgeEngine(broken)], default=0.25)
+    assert dead.score(["q"], ["r"], ["a"]) == [0.25]
