@@ -124,10 +124,12 @@ void lm_head_dlogits(torch::Tensor h, torch::Tensor W, torch::Tensor targets, to
 
 void register_symm(pybind11::module_& m);
 void register_fused(pybind11::module_& m);
+void register_vmm(pybind11::module_& m);
 
 void register_more(pybind11::module_& m) {
   register_symm(m);
   register_fused(m);
+  register_vmm(m);
   m.def("fa_fwd", &fa_fwd);
   m.def("fa_bwd", &fa_bwd);
   m.def("decode_attn_splits", &decode_attn_splits);

@@ -13,6 +13,7 @@ the decode loop - only the collectives inside the model.
 from __future__ import annotations
 
 import math
+import os
 import time
 from collections import deque
 from dataclasses import dataclass, field
@@ -99,12 +100,18 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, tp: Optional[GroupInfo] = None, device="cpu", dtype=None,
                  num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
-                 use_cuda_graph: bool = True, max_model_len: int = 4096):
+                 use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
         self.dtype = dtype or {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
-        self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype)
+        # pausable buffers keep their addresses across release/resume, so CUDA graphs survive the trainer's turn
+        if memory_saver is None:
+            memory_saver = self.device.type == "cuda" and os.environ.get("RELAX_B200_MEMORY_SAVER", "1") == "1"
+        self.memory_saver = bool(memory_saver)
+        self._kv_buf = None
+        self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype,
+                                      memory_saver=self.memory_saver)
         self.block_size = block_size
         self.bm = BlockManager(num_kv_blocks, block_size)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
@@ -130,19 +137,32 @@ class RolloutEngine:
     def _alloc_kv(self):
         c = self.cfg
         hkv = c.num_query_groups // self.tp.size
-        self.kv = torch.zeros(c.num_layers, 2, self.bm.num_blocks, self.block_size, hkv, c.head_dim,
-                              dtype=self.dtype, device=self.device)
+        shape = (c.num_layers, 2, self.bm.num_blocks, self.block_size, hkv, c.head_dim)
+        if self.memory_saver:
+            from ..utils.memory_saver import PausableBuffer
+
+            if self._kv_buf is None:
+                self._kv_buf = PausableBuffer(math.prod(shape) * torch.empty(0, dtype=self.dtype).element_size(), self.device)
+                self.kv = self._kv_buf.tensor(shape, self.dtype)
+            else:
+                self._kv_buf.resume()
+            return
+        self.kv = torch.zeros(*shape, dtype=self.dtype, device=self.device)
 
     def release_memory_occupation(self, tags: Sequence[str] = ("kv_cache", "cuda_graph")):
         """Free device memory by tag (``weights`` / ``kv_cache`` / ``cuda_graph``)
         while the trainer uses the GPU (relax/distributed/ray/rollout.py:1201-1233)."""
         if self.running or self.waiting:
             raise RuntimeError("cannot release memory with requests in flight; abort or drain first")
-        if "cuda_graph" in tags:
+        if "cuda_graph" in tags and not self.memory_saver:
+            # without stable addresses the graphs point at freed memory: drop them (re-captured on demand)
             self._graphs = {}
             self._graph_pool = None
         if "kv_cache" in tags:
-            self.kv = None
+            if self.memory_saver:
+                self._kv_buf.pause()
+            else:
+                self.kv = None
         if "weights" in tags:
             self.weights.release()
         if self.device.type == "cuda":
@@ -151,7 +171,7 @@ class RolloutEngine:
     def resume_memory_occupation(self, tags: Sequence[str] = ("kv_cache",)):
         if "weights" in tags:
             self.weights.resume()
-        if "kv_cache" in tags and self.kv is None:
+        if "kv_cache" in tags and (self.kv is None or (self._kv_buf is not None and self._kv_buf.paused)):
             self._alloc_kv()
 
     def flush_cache(self):

@@ -60,7 +60,8 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
 
 
 class RolloutWeights:
-    def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0):
+    def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
+                 memory_saver: bool = False):
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank
         self.device, self.dtype = torch.device(device), dtype
@@ -72,19 +73,33 @@ class RolloutWeights:
         self.numel = n
         self.flat = None
         self.p: dict[str, torch.Tensor] = {}
+        self.memory_saver = memory_saver
+        self._buf = None
         self.resume()
         self.v_local = self.shapes["embed"][0]
         self.vocab_start = tp_rank * self.v_local
 
     def resume(self):
-        if self.flat is not None:
+        if self.memory_saver:
+            if self._buf is not None:
+                self._buf.resume()     # same addresses, zero-filled: the next weight sync rewrites everything
+                return
+            from ..utils.memory_saver import PausableBuffer
+
+            self._buf = PausableBuffer(self.numel * torch.empty(0, dtype=self.dtype).element_size(), self.device)
+            self.flat = self._buf.tensor((self.numel,), self.dtype)
+        elif self.flat is not None:
             return
-        self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        else:
+            self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
         self.p = {k: self.flat[o:o + math.prod(self.shapes[k])].view(self.shapes[k]) for k, o in self.offsets.items()}
         if self.cfg.tie_word_embeddings:
             self.p["lm_head"] = self.p["embed"]
 
     def release(self):
+        if self.memory_saver:
+            self._buf.pause()          # views in ``self.p`` keep their addresses and must not be used until resume()
+            return
         self.flat, self.p = None, {}
 
     # ------------------------------------------------------------------ model pieces

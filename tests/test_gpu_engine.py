@@ -76,3 +76,50 @@ def test_colocated_grpo_two_steps_on_gpu():
     p = dict(run.actor.named_local_params())
     assert torch.equal(run.engine.weights.p["layers.1.o"], p["decoder.layers.1.self_attention.linear_proj.weight"])
     C.check_error_flag()
+
+
+def test_pausable_buffer_keeps_address_and_returns_memory():
+    from relax_b200.utils.memory_saver import PausableBuffer
+
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    buf = PausableBuffer(256 << 20, "cuda:0")
+    t = buf.tensor((64 << 20,), torch.float32)
+    t.fill_(3.0)
+    ptr = t.data_ptr()
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free0 - free1 >= 200 << 20
+    buf.pause()
+    free2, _ = torch.cuda.mem_get_info()
+    assert free2 - free1 >= 200 << 20          # physical memory went back to the driver
+    buf.resume()
+    assert t.data_ptr() == ptr and float(t.sum()) == 0.0   # same address, fresh zeroed memory
+    t.fill_(1.0)
+    assert float(t[:10].sum()) == 10.0
+    buf.free()
+
+
+def test_graphs_survive_release_and_resume():
+    """With pausable KV/weight buffers the captured decode graphs are reused after the trainer's turn."""
+    from relax_b200.ops import cuda as C
+    from relax_b200.rollout.engine import SamplingParams
+    from relax_b200.weight_sync.plan import TrainerLayout
+    from relax_b200.weight_sync.sync import WeightSync
+
+    cfg, actor, eng = _pair(True)
+    assert eng.memory_saver
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 21, 30)]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=16)
+    out0 = [r.output for r in eng.generate(prompts, sp)]
+    n_graphs = len(eng._graphs)
+    assert n_graphs >= 1
+    graphs0 = dict(eng._graphs)
+    eng.release_memory_occupation(("kv_cache", "cuda_graph", "weights"))
+    eng.resume_memory_occupation(("kv_cache", "weights"))
+    WeightSync(cfg, TrainerLayout(), 1, [0], [0]).update_weights(dict(actor.named_local_params()), eng.weights, eng, 2)
+    out1 = [r.output for r in eng.generate(prompts, sp)]
+    assert out1 == out0                                     # greedy decoding reproduces itself
+    assert all(eng._graphs[k] is graphs0[k] for k in graphs0)   # no re-capture
+    C.check_error_flag()

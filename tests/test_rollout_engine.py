@@ -95,3 +95,25 @@ def test_pause_and_memory_release():
     assert eng.kv is None and eng.weights.flat is None
     eng.resume_memory_occupation(("kv_cache", "weights"))
     assert eng.kv is not None and eng.weights.flat is not None
+
+
+def test_memory_saver_keeps_views_across_pause_resume():
+    """CPU emulation of the pausable buffers: release/resume keeps the tensor objects and generation still works."""
+    import torch
+    from relax_b200.models.config import get_config
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+
+    cfg = get_config("tiny")
+    eng = RolloutEngine(cfg, device="cpu", num_kv_blocks=32, block_size=4, memory_saver=True)
+    eng.weights.flat.normal_(0, 0.02)
+    w0 = eng.weights.flat.clone()
+    kv_obj, p_obj = eng.kv, eng.weights.p["embed"]
+    sp = SamplingParams(temperature=1.0, max_new_tokens=4)
+    out0 = eng.generate([[1, 2, 3]], sp)[0].output
+    eng.release_memory_occupation(("kv_cache", "cuda_graph", "weights"))
+    assert eng._kv_buf.paused and eng.weights._buf.paused
+    eng.resume_memory_occupation(("kv_cache", "weights"))
+    assert eng.kv is kv_obj and eng.weights.p["embed"] is p_obj
+    assert float(eng.weights.flat.abs().sum()) == 0.0     # contents are not preserved
+    eng.weights.flat.copy_(w0)
+    assert len(eng.generate([[1, 2, 3]], sp)[0].output) == len(out0)
