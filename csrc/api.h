@@ -85,6 +85,12 @@ int rb_qkv_post(const void* qkv, int ld, const void* qw, const void* kw, const f
                 void* k_out, void* v_out, void* k_cache, void* v_cache, const long long* slots, int T, int nq, int nkv,
                 float eps, cudaStream_t st);
 int rb_splitk_swiglu(const float* ws, void* out, int M, int F, int splits, cudaStream_t st);
+int rb_dp_reduce_sumsq(float* const* peer_g, unsigned* const* peer_sig, int* state, int dp, int rank, long long lo, long long n,
+                       float* out, float* sumsq, float scale, unsigned long long wait_ns, int* err, cudaStream_t st);
+int rb_dp_adam_allgather(void* const* peer_p, unsigned* const* peer_sig, int* state, int dp, int rank, long long lo,
+                         long long n, void* master, const float* g, float* m, float* v, int step, float lr, float b1,
+                         float b2, float eps, float wd, float gscale, int split, unsigned long long wait_ns, int* err,
+                         cudaStream_t st);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

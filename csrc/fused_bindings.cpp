@@ -114,12 +114,52 @@ void splitk_swiglu(torch::Tensor workspace, torch::Tensor out, int64_t splits) {
                          cur_stream()),
         "rb_splitk_swiglu");
 }
+
+// Distributed-optimizer kernels over peer memory (see dist_optim_sm100.cu).
+void dp_reduce_sumsq(std::vector<int64_t> grad_ptrs, std::vector<int64_t> sig_ptrs, torch::Tensor state, int64_t rank,
+                     int64_t lo, torch::Tensor out, torch::Tensor sumsq, double scale, int64_t wait_ns, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(out.device());
+  const int dp = (int)grad_ptrs.size();
+  TORCH_CHECK(dp >= 1 && dp <= 8 && sig_ptrs.size() == grad_ptrs.size() && state.numel() >= 16);
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && sumsq.scalar_type() == at::kFloat);
+  float* g[8];
+  unsigned* sg[8];
+  for (int r = 0; r < dp; ++r) {
+    g[r] = reinterpret_cast<float*>(grad_ptrs[r]);
+    sg[r] = reinterpret_cast<unsigned*>(sig_ptrs[r]);
+  }
+  check(rb_dp_reduce_sumsq(g, sg, state.data_ptr<int>(), dp, (int)rank, lo, out.numel(), out.data_ptr<float>(),
+                           sumsq.data_ptr<float>(), (float)scale, (unsigned long long)wait_ns, err.data_ptr<int>(), cur_stream()),
+        "rb_dp_reduce_sumsq");
+}
+void dp_adam_allgather(std::vector<int64_t> param_ptrs, std::vector<int64_t> sig_ptrs, torch::Tensor state, int64_t rank,
+                       int64_t lo, torch::Tensor master, torch::Tensor g, torch::Tensor m, torch::Tensor v, int64_t step,
+                       double lr, double b1, double b2, double eps, double wd, double gscale, bool split, int64_t wait_ns,
+                       torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(g.device());
+  const int dp = (int)param_ptrs.size();
+  TORCH_CHECK(dp >= 1 && dp <= 8 && sig_ptrs.size() == param_ptrs.size() && state.numel() >= 16);
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  void* pp[8];
+  unsigned* sg[8];
+  for (int r = 0; r < dp; ++r) {
+    pp[r] = reinterpret_cast<void*>(param_ptrs[r]);
+    sg[r] = reinterpret_cast<unsigned*>(sig_ptrs[r]);
+  }
+  check(rb_dp_adam_allgather(pp, sg, state.data_ptr<int>(), dp, (int)rank, lo, g.numel(), master.data_ptr(),
+                             g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), (int)step, (float)lr, (float)b1,
+                             (float)b2, (float)eps, (float)wd, (float)gscale, split ? 1 : 0, (unsigned long long)wait_ns,
+                             err.data_ptr<int>(), cur_stream()),
+        "rb_dp_adam_allgather");
+}
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
   m.def("gemm_ar_plan", &gemm_ar_plan);
   m.def("ag_gemm", &ag_gemm);
   m.def("qkv_post", &qkv_post);
+  m.def("dp_reduce_sumsq", &dp_reduce_sumsq);
+  m.def("dp_adam_allgather", &dp_adam_allgather);
   m.def("gemm_splitk_partial", &gemm_splitk_partial);
   m.def("splitk_swiglu", &splitk_swiglu);
   m.def("gemm_ar_rmsnorm", &gemm_ar_rmsnorm, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("ws_ptrs"),

@@ -17,6 +17,7 @@ fp32 copy.  Ten bytes of optimizer state per parameter, spread over dp ranks.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Iterable, Optional
 
@@ -40,6 +41,7 @@ class OptimizerConfig:
     lr_decay_iters: Optional[int] = None
     grad_dtype: str = "fp32"           # fp32 | param (accumulate in the parameter dtype)
     split_master: bool = True          # bf16 + int16 remainder instead of an fp32 copy
+    fused_dp: bool = True              # reduce-scatter / all-gather inside the optimizer kernels over NVLink peer memory
 
 
 def lr_at(cfg: OptimizerConfig, it: int) -> float:
@@ -108,9 +110,17 @@ class DistributedOptimizer:
         self.total = (n + chunk - 1) // chunk * chunk
         self.shard = self.total // dp
         self.offsets = offs
-        self.param_buf = torch.zeros(self.total, dtype=self.pdtype, device=dev)
         gdt = torch.float32 if cfg.grad_dtype == "fp32" else self.pdtype
-        self.grad_buf = torch.zeros(self.total, dtype=gdt, device=dev)
+        self._symm = None
+        if (dp > 1 and dev.type == "cuda" and gdt == torch.float32 and self.pdtype == torch.bfloat16
+                and getattr(cfg, "fused_dp", True) and os.environ.get("RELAX_B200_FUSED_DP", "1") == "1"):
+            self._symm = self._setup_symmetric(dev, dp)
+        if self._symm is not None:
+            self.param_buf = self._symm["param"].local((self.total,), self.pdtype)
+            self.grad_buf = self._symm["grad"].local((self.total,), gdt)
+        else:
+            self.param_buf = torch.zeros(self.total, dtype=self.pdtype, device=dev)
+            self.grad_buf = torch.zeros(self.total, dtype=gdt, device=dev)
         for p, o in zip(self.params, offs):
             v = self.param_buf[o:o + p.numel()].view_as(p)
             v.copy_(p.data)
@@ -150,11 +160,49 @@ class DistributedOptimizer:
             for p in self.params:
                 p.grad = p.main_grad
 
+    def _setup_symmetric(self, dev, dp):
+        """Parameter and gradient buffers in NVLink-shared memory of the data-parallel group, so the step's
+        reduce-scatter and all-gather run inside the optimizer kernels (csrc/dist_optim_sm100.cu).  Returns
+        None (NCCL path) when the group does not sit on one node with peer access."""
+        import socket
+
+        from ..ops import cuda as C
+        from ..parallel.symm_mem import SymmBuffer
+
+        g = self.ps.dp_cp
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        info = [None] * g.size
+        dist.all_gather_object(info, (socket.gethostname(), idx), group=g.group)
+        ok = len({h for h, _ in info}) == 1 and len({d for _, d in info}) == g.size
+        ok = ok and all(C._load().can_access_peer(idx, d) for _, d in info if d != idx)
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=g.group)
+        if not int(flag.item()):
+            return None
+        out = {"param": SymmBuffer(self.total * 2, g, dev), "grad": SymmBuffer(self.total * 4, g, dev),
+               "sig": SymmBuffer(1024, g, dev), "state": torch.zeros(16, dtype=torch.int32, device=dev),
+               "sumsq": torch.zeros(1, dtype=torch.float32, device=dev),
+               "wait_ns": int(os.environ.get("RELAX_B200_PEER_WAIT_MS", "5000")) * 1_000_000}
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=g.group)
+        return out
+
     def _reduce_grads(self):
         ps = self.ps
         if ps.tp.size > 1 and self.rep_elems > 0:
             dist.all_reduce(self.grad_buf[: self.rep_elems], group=ps.tp.group)
         g = ps.dp_cp
+        if self._symm is not None:
+            from ..ops import cuda as C
+
+            sy = self._symm
+            out = torch.empty(self.shard, dtype=torch.float32, device=self.grad_buf.device)
+            sy["sumsq"].zero_()
+            C._load().dp_reduce_sumsq(sy["grad"].ptrs, sy["sig"].ptrs, sy["state"], g.rank, self.lo, out, sy["sumsq"],
+                                      1.0 / g.size, sy["wait_ns"], C.err_flag(out.device))
+            self._fused_sumsq = sy["sumsq"].clone()
+            return out
+        self._fused_sumsq = None
         if g.size > 1:
             out = torch.empty(self.shard, dtype=self.grad_buf.dtype, device=self.grad_buf.device)
             dist.reduce_scatter_tensor(out, self.grad_buf, op=dist.ReduceOp.SUM, group=g.group)
@@ -166,10 +214,15 @@ class DistributedOptimizer:
         ps = self.ps
         # replicated parameters appear on every TP rank: count them once
         lo, hi = self.lo, self.hi
-        sq = gshard.float().pow(2)
-        tot = sq.sum()
-        if ps.tp.size > 1 and ps.tp.rank != 0 and self.rep_elems > lo:
-            tot = tot - sq[: max(0, min(hi, self.rep_elems) - lo)].sum()
+        if getattr(self, "_fused_sumsq", None) is not None:
+            tot = self._fused_sumsq[0]      # produced by the fused reduce kernel
+            if ps.tp.size > 1 and ps.tp.rank != 0 and self.rep_elems > lo:
+                tot = tot - gshard[: max(0, min(hi, self.rep_elems) - lo)].float().pow(2).sum()
+        else:
+            sq = gshard.float().pow(2)
+            tot = sq.sum()
+            if ps.tp.size > 1 and ps.tp.rank != 0 and self.rep_elems > lo:
+                tot = tot - sq[: max(0, min(hi, self.rep_elems) - lo)].sum()
         if ps.dp_cp.size > 1:
             dist.all_reduce(tot, group=ps.dp_cp.group)
         if ps.tp.size > 1:
@@ -192,8 +245,18 @@ class DistributedOptimizer:
             clip = cfg.clip_grad / (self.last_grad_norm + 1e-6)
         self.step_count += 1
         lr = lr if lr is not None else lr_at(cfg, self.step_count - 1)
-        self._adam_shard(gshard, lr, grad_scale * clip)
         g = self.ps.dp_cp
+        if self._symm is not None:
+            from ..ops import cuda as C
+
+            sy = self._symm   # Adam on my shard + the parameter all-gather, one kernel
+            C._load().dp_adam_allgather(sy["param"].ptrs, sy["sig"].ptrs, sy["state"], g.rank, self.lo,
+                                        self.master_rem if self.split_master else self.master, gshard, self.exp_avg,
+                                        self.exp_avg_sq, self.step_count, lr, cfg.adam_beta1, cfg.adam_beta2, cfg.adam_eps,
+                                        cfg.weight_decay, grad_scale * clip, self.split_master, sy["wait_ns"],
+                                        C.err_flag(gshard.device))
+            return self.last_grad_norm, False
+        self._adam_shard(gshard, lr, grad_scale * clip)
         if g.size > 1:
             dist.all_gather_into_tensor(self.param_buf, self.param_buf[self.lo:self.hi].clone(), group=g.group)
         return self.last_grad_norm, False
@@ -255,8 +318,8 @@ class DistributedOptimizer:
 
     def release_grads(self):
         """Drop the gradient buffer (it is zeroed at the start of every step anyway)."""
-        if self.grad_buf is None:
-            return
+        if self.grad_buf is None or self._symm is not None:
+            return   # symmetric buffers stay mapped on the peers: they are never dropped
         self._grad_meta = (self.grad_buf.shape, self.grad_buf.dtype, self.grad_buf.device)
         self.grad_buf = None
         for p in self.params:

@@ -176,3 +176,45 @@ def test_peer_wait_runs_out_and_reports():
     finally:
         for p in (ws0, ws1, sg0, sg1):
             _C.symm_free(p, 0)
+
+
+def _dpopt_worker(rank, world):
+    """Two data-parallel ranks: the fused optimizer step (peer loads / stores) against the NCCL statement."""
+    import dataclasses
+
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+    from relax_b200.train.optimizer import DistributedOptimizer, OptimizerConfig
+
+    dev = torch.device("cuda", rank)
+    ps = init_parallel_state(ParallelDims(dp=2))
+    cfg = get_config("qwen3-0.6b", num_layers=2, vocab_size=2048)
+    outs = []
+    for fused in (True, False):
+        torch.manual_seed(0)
+        model = GPTModel(cfg, ps, device=dev, seed=0)
+        opt = DistributedOptimizer(model, ps, OptimizerConfig(lr=1e-3, clip_grad=1.0, weight_decay=0.01, fused_dp=fused))
+        assert (opt._symm is not None) == fused
+        for step in range(3):
+            opt.zero_grad()
+            g = torch.Generator(device="cpu").manual_seed(100 * step + rank)
+            for p in opt.params:
+                p.main_grad.copy_((torch.randn(p.shape, generator=g) * 0.01).to(dev))
+            norm, skipped = opt.step()
+            assert not skipped
+        torch.cuda.synchronize(dev)
+        C.check_error_flag(dev)
+        outs.append((opt.param_buf.float().clone(), float(norm)))
+    (pf, nf), (pn, nn) = outs
+    return float((pf - pn).abs().max()), abs(nf - nn) / max(nn, 1e-9), float(pf.abs().sum())
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_fused_distributed_optimizer_matches_nccl_path():
+    out = run_distributed(_dpopt_worker, 2, backend="nccl", timeout=600)
+    for diff, nrel, mass in out:
+        # the two paths round the clip factor differently in the last bit: allow one bf16 ulp at |w| < 0.06
+        assert diff <= 5e-4 and nrel < 1e-4 and mass > 0, out
+    assert out[0][2] == out[1][2]      # both ranks hold the same parameters after the fused all-gather
