@@ -26,6 +26,7 @@ import subprocess
 import sys
 import threading
 import time
+import faulthandler
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -45,6 +46,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="debug only: override depth (result is then not comparable)")
     ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
     ap.add_argument("--kv-gb", type=float, default=None)
+    ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel size of trainer and engines (default 2 when N >= 2)")
     ap.add_argument("--no-fused-tp", action="store_true",
                     help="A/B: use the NCCL statements instead of the fused GEMM+collective kernels (TP>1 only)")
     return ap.parse_args()
@@ -111,6 +113,9 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    if os.environ.get("RELAX_B200_HANG_DUMP_S"):
+        # debugging aid: print every thread's Python stack and exit if the run is still going after this many seconds
+        faulthandler.dump_traceback_later(int(os.environ["RELAX_B200_HANG_DUMP_S"]), exit=True)
     import torch
     import torch.distributed as dist
 
@@ -135,7 +140,7 @@ def main():
 
     over = {} if args.layers is None else {"num_layers": args.layers}
     mcfg = get_config(args.model, **over)
-    tp = 2 if world >= 2 else 1
+    tp = args.tp if args.tp else (2 if world >= 2 else 1)
     G = args.group_size
     n_prompts = args.prompts_per_gpu * world
     kv_bytes_per_block = mcfg.num_layers * 2 * 16 * (mcfg.num_query_groups // tp) * mcfg.head_dim * 2
@@ -234,8 +239,12 @@ def main():
             "clocks": sampler.summary(),
         }
         print(json.dumps(out))
+    sys.stdout.flush()
     if world > 1:
-        dist.destroy_process_group()
+        from relax_b200.parallel.state import shutdown_distributed
+
+        run.close()
+        shutdown_distributed(timeout_s=20.0, hard_exit_code=0)
     return 0
 
 

@@ -80,6 +80,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// Same, bounded by wall time instead of a poll count: for pipelines whose producer may itself be waiting
+// (bounded) for another GPU, so the consumers' limit must exceed the producer's.
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* g_err,
+                                                unsigned long long limit_ns) {
+  unsigned long long t0 = 0;
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) break;
+    }
+  }
+  *abort_flag = 1;
+  if (g_err) atomicCAS(g_err, kOk, kErrBarrierTimeout);
+  return false;
+}
+
 // ----------------------------------------------------------------------------- TMA (no multicast anywhere)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -136,6 +136,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int k_iters_total = (p.K + BK - 1) / BK;
+  // In the all-gather mode the TMA producer may wait (bounded by p.wait_ns) for another GPU; every other
+  // role then waits on it through the pipeline barriers, so their limit has to be the longer one.
+  auto pipe_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if constexpr (MODE == kEpiAllGather) return mbar_wait_timed(bar, parity, abort_flag, p.err, p.wait_ns + 2000000000ull);
+    else return mbar_wait(bar, parity, abort_flag, p.err);
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -194,7 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         const int k_lo = split * p.k_iters_per_split, k_hi = min(k_iters_total, k_lo + p.k_iters_per_split);
         for (int k = k_lo; k < k_hi; ++k) {
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) { ok = false; break; }
+          if (!pipe_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
           uint8_t* sa = smem + s * S::kStageBytes;
           uint8_t* sb = sa + S::kABytes;
           mbar_expect_tx(&full_bar[s], S::kStageBytes);
@@ -230,11 +236,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         int tm_, tn_, split;
         if (!next_tile<MODE>(p, ti, tm_, tn_, split)) break;
         const int k_lo = split * p.k_iters_per_split, k_hi = min(k_iters_total, k_lo + p.k_iters_per_split);
-        if (!mbar_wait(&tempty_bar[acc], acc_ph ^ 1, abort_flag, p.err)) break;
+        if (!pipe_wait(&tempty_bar[acc], acc_ph ^ 1)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int k = k_lo; k < k_hi; ++k) {
-          if (!mbar_wait(&full_bar[s], ph, abort_flag, p.err)) { ok = false; break; }
+          if (!pipe_wait(&full_bar[s], ph)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * S::kStageBytes);
           const uint32_t sb = sa + S::kABytes;
@@ -299,7 +305,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const int row = tm * BM + lane_grp * 32 + lane;
       st_row = row;
       const int n0 = tn * BN;
-      if (!mbar_wait(&tfull_bar[acc], acc_ph, abort_flag, p.err)) break;
+      if (!pipe_wait(&tfull_bar[acc], acc_ph)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(lane_grp * 32) << 16);
 #pragma unroll 1

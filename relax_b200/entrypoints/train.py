@@ -37,7 +37,9 @@ def main(argv=None) -> int:
     finally:
         ctl.shutdown()
         if dist.is_initialized():
-            dist.destroy_process_group()
+            from ..parallel.state import shutdown_distributed
+
+            shutdown_distributed(timeout_s=30.0)
     return 0
 
 

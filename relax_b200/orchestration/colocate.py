@@ -133,6 +133,18 @@ class ColocatedGRPO:
         self.rollout_id = 0
         self.sync_weights()
 
+    def close(self):
+        """Unmap the peers' symmetric buffers (call on every rank before leaving the process groups)."""
+        from ..ops import fused_comm
+
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        for g in (self.rollout_tp_group, self.ps.tp):
+            fused_comm.detach(g)
+        for c in self.fused_comms:
+            c.close()
+        self.fused_comms = []
+
     # ------------------------------------------------------------------ weight sync
     def sync_weights(self) -> float:
         params = dict(self.actor.named_local_params())

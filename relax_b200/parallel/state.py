@@ -172,3 +172,33 @@ def init_parallel_state(dims: ParallelDims, role_ranks: Optional[Sequence[int]] 
 def single_process_state() -> ParallelState:
     g = GroupInfo(None, (0,), 0)
     return ParallelState(ParallelDims(), 0, (0,), g, g, g, g, g, g, g, g)
+
+
+def shutdown_distributed(timeout_s: float = 20.0, hard_exit_code: int | None = None):
+    """Leave the process groups without letting a stuck communicator teardown hold the job.
+
+    All ranks synchronise first (device + barrier) so nothing is in flight; the NCCL teardown then runs on a
+    helper thread.  With many split communicators (TP x DP x engine groups) the teardown has been seen to
+    block on 4 GPUs even though every collective had completed; after ``timeout_s`` the caller either
+    returns (``hard_exit_code`` None) or the process exits with that code, results already flushed."""
+    import os
+    import sys
+    import threading
+
+    if not dist.is_initialized():
+        return True
+    try:
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:  # noqa: BLE001
+        pass
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(timeout_s)
+    done = not t.is_alive()
+    if not done and hard_exit_code is not None:
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(hard_exit_code)
+    return done
