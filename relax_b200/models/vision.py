@@ -1,0 +1,187 @@
+"""Vision encoder and multimodal glue for the VL model families (Qwen2.5-VL style; the reference trains them
+through Megatron-Bridge models and ships its own ViT for DotsOCR, relax/models/dots_ocr/vision.py:58-217, and the
+M-RoPE index of Qwen3-Omni, relax/models/qwen_omni/modeling_qwen3_omni/utils.py:57).
+
+* :class:`VisionEncoder` - patch embedding over flattened ``[C x Tp x P x P]`` patches, 2-D rotary position
+  embedding (row / column halves), pre-norm blocks with full (non-causal) variable-length attention per image -
+  the same flash-attention kernel as the language model, ``causal=False`` - and SwiGLU MLPs, then a patch merger
+  that folds ``merge x merge`` neighbouring patches into one language-model token.
+* :func:`mrope_positions` - the three position streams (temporal, height, width) of multimodal RoPE: text tokens
+  advance all three together; the tokens of an image share one temporal index and carry their grid row / column;
+  the text after an image continues from the largest index used so far.
+* :class:`VLModel` - language model + encoder: image tokens in the prompt are replaced by encoder outputs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+
+
+@dataclass
+class VisionConfig:
+    patch_size: int = 14
+    temporal_patch_size: int = 2
+    in_channels: int = 3
+    hidden_size: int = 1280
+    num_heads: int = 16
+    intermediate_size: int = 3420
+    depth: int = 32
+    spatial_merge_size: int = 2
+    out_hidden_size: int = 3584
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_heads
+
+    @property
+    def patch_dim(self) -> int:
+        return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size
+
+
+def vision_rope_tables(grid_thw: torch.Tensor, head_dim: int, theta: float, merge: int):
+    """cos/sin ``[N, head_dim/2]`` for all patches of all images, in the merge-window-major order the patches are
+    fed in (``merge x merge`` neighbours adjacent): first half of the frequencies follows the row, second the column."""
+    quarter = head_dim // 4
+    inv = 1.0 / (theta ** (torch.arange(0, quarter, dtype=torch.float32, device=grid_thw.device) / quarter))
+    rows, cols = [], []
+    for t, h, w in grid_thw.tolist():
+        r = torch.arange(h, device=grid_thw.device).view(h // merge, merge, 1, 1).expand(h // merge, merge, w // merge, merge)
+        c = torch.arange(w, device=grid_thw.device).view(1, 1, w // merge, merge).expand(h // merge, merge, w // merge, merge)
+        r = r.permute(0, 2, 1, 3).reshape(-1)
+        c = c.permute(0, 2, 1, 3).reshape(-1)
+        rows.append(r.repeat(t))
+        cols.append(c.repeat(t))
+    r, c = torch.cat(rows).float(), torch.cat(cols).float()
+    ang = torch.cat([r[:, None] * inv[None, :], c[:, None] * inv[None, :]], -1)
+    return ang.cos(), ang.sin()
+
+
+class VisionBlock(nn.Module):
+    def __init__(self, cfg: VisionConfig, dtype, device, gen):
+        super().__init__()
+        h, f = cfg.hidden_size, cfg.intermediate_size
+        self.cfg = cfg
+        mk = lambda *s, std=0.02: nn.Parameter((torch.randn(*s, generator=gen) * std).to(device=device, dtype=dtype))
+        self.norm1 = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        self.norm2 = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        self.qkv = mk(3 * h, h)
+        self.qkv_bias = nn.Parameter(torch.zeros(3 * h, dtype=dtype, device=device))
+        self.proj = mk(h, h, std=0.02 / math.sqrt(2 * cfg.depth))
+        self.fc1 = mk(2 * f, h)        # [gate; up]
+        self.fc2 = mk(h, f, std=0.02 / math.sqrt(2 * cfg.depth))
+
+    def forward(self, x, cos, sin, cu_seqlens, max_seqlen):
+        cfg = self.cfg
+        n, hd = cfg.num_heads, cfg.head_dim
+        y = ops.rmsnorm(x, self.norm1, cfg.rms_norm_eps)
+        qkv = ops.linear(y, self.qkv, self.qkv_bias).view(-1, 3, n, hd)
+        q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
+        q, k = ops.apply_rope(q.contiguous(), cos, sin), ops.apply_rope(k.contiguous(), cos, sin)
+        o = ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=False, max_seqlen=max_seqlen)
+        x = x + ops.linear(o.reshape(o.shape[0], -1), self.proj)
+        y = ops.rmsnorm(x, self.norm2, cfg.rms_norm_eps)
+        return x + ops.linear(ops.swiglu(ops.linear(y, self.fc1)), self.fc2)
+
+
+class VisionEncoder(nn.Module):
+    def __init__(self, cfg: VisionConfig, dtype=torch.float32, device="cpu", seed: int = 0):
+        super().__init__()
+        self.cfg = cfg
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        h = cfg.hidden_size
+        self.patch_embed = nn.Parameter((torch.randn(h, cfg.patch_dim, generator=gen) * 0.02).to(device=device, dtype=dtype))
+        self.blocks = nn.ModuleList([VisionBlock(cfg, dtype, device, gen) for _ in range(cfg.depth)])
+        m2 = cfg.spatial_merge_size ** 2
+        self.merger_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        self.merger_fc1 = nn.Parameter((torch.randn(h * m2, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
+        self.merger_fc2 = nn.Parameter((torch.randn(cfg.out_hidden_size, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
+
+    def forward(self, pixel_patches: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
+        """``pixel_patches [N, patch_dim]`` (all images concatenated, merge-window-major), ``grid_thw [n_img, 3]`` in
+        patches.  Returns ``[N / merge^2, out_hidden]`` language-model embeddings."""
+        cfg = self.cfg
+        x = ops.linear(pixel_patches.to(self.patch_embed.dtype), self.patch_embed)
+        cos, sin = vision_rope_tables(grid_thw, cfg.head_dim, cfg.rope_theta, cfg.spatial_merge_size)
+        lens = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).to(torch.int32)
+        cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=x.device)
+        cu[1:] = lens.cumsum(0)
+        mx = int(lens.max())
+        for blk in self.blocks:
+            x = blk(x, cos, sin, cu, mx)
+        x = ops.rmsnorm(x, self.merger_norm, cfg.rms_norm_eps)
+        x = x.view(-1, cfg.hidden_size * cfg.spatial_merge_size ** 2)
+        return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1)), self.merger_fc2)
+
+
+def mrope_positions(input_ids: Sequence[int], image_grid_thw: Sequence[Sequence[int]], image_token_id: int,
+                    spatial_merge_size: int = 2, device="cpu") -> torch.Tensor:
+    """``[3, T]`` (temporal, height, width) position ids of one sequence whose image placeholders are runs of
+    ``image_token_id`` (one run per image, ``t * h/merge * w/merge`` tokens long)."""
+    ids = list(input_ids)
+    T = len(ids)
+    pos = torch.zeros(3, T, dtype=torch.long)
+    nxt, i, img = 0, 0, 0
+    while i < T:
+        if ids[i] != image_token_id:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+            continue
+        if img >= len(image_grid_thw):
+            raise ValueError(f"placeholder tokens at position {i} but only {len(image_grid_thw)} image grid(s) given")
+        t, h, w = image_grid_thw[img]
+        gh, gw = h // spatial_merge_size, w // spatial_merge_size
+        n = t * gh * gw
+        if ids[i:i + n] != [image_token_id] * n:
+            raise ValueError(f"image {img}: expected a run of {n} placeholder tokens at position {i}")
+        tt = torch.arange(t).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
+        hh = torch.arange(gh).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
+        ww = torch.arange(gw).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
+        pos[0, i:i + n], pos[1, i:i + n], pos[2, i:i + n] = nxt + tt, nxt + hh, nxt + ww
+        nxt = nxt + max(t, gh, gw)
+        i += n
+        img += 1
+    if img != len(image_grid_thw):
+        raise ValueError(f"{len(image_grid_thw)} images given, {img} placeholder runs found")
+    return pos.to(device)
+
+
+def merge_image_embeddings(text_embeds: torch.Tensor, image_embeds: torch.Tensor, input_ids: torch.Tensor,
+                           image_token_id: int) -> torch.Tensor:
+    mask = input_ids == image_token_id
+    if int(mask.sum()) != image_embeds.shape[0]:
+        raise ValueError(f"{int(mask.sum())} image tokens in the prompt but {image_embeds.shape[0]} image embeddings")
+    out = text_embeds.clone()
+    out[mask] = image_embeds.to(out.dtype)
+    return out
+
+
+def vision_config_from_model(mc) -> VisionConfig:
+    """The encoder configuration of a VL preset (``ModelConfig.vision`` of models/config.py)."""
+    v = mc.vision
+    return VisionConfig(patch_size=v.patch_size, temporal_patch_size=v.temporal_patch_size, in_channels=v.in_channels,
+                        hidden_size=v.hidden_size, num_heads=v.num_heads, intermediate_size=v.ffn_hidden_size,
+                        depth=v.num_layers, spatial_merge_size=v.spatial_merge_size, out_hidden_size=v.out_hidden_size,
+                        rms_norm_eps=mc.rms_norm_eps)
+
+
+class VLModel(nn.Module):
+    """Language model + vision encoder.  ``forward`` returns the final hidden states like ``GPTModel.forward``."""
+
+    def __init__(self, lm, vision: VisionEncoder, image_token_id: int):
+        super().__init__()
+        self.lm, self.vision, self.image_token_id = lm, vision, image_token_id
+
+    def forward(self, tokens, positions, cu_seqlens, pixel_patches=None, grid_thw=None, max_seqlen=None):
+        emb = self.lm.embedding.word_embeddings(tokens, False)
+        if pixel_patches is not None and pixel_patches.numel():
+            emb = merge_image_embeddings(emb, self.vision(pixel_patches, grid_thw), tokens, self.image_token_id)
+        return self.lm(tokens, positions, cu_seqlens, inputs_embeds=emb, max_seqlen=max_seqlen)
