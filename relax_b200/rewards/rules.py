@@ -195,3 +195,92 @@ def openr1mm_reward(sample) -> float:
     fmt = 1.0 if re.fullmatch(r"\s*<think>.*?</think>\s*<answer>.*?</answer>\s*", sample.response, flags=re.S) else 0.0
     acc = 1.0 if m and math_equal(m.group(1), str(sample.label)) else 0.0
     return acc + fmt
+
+
+# --------------------------------------------------------------------------- instruction following (ifbench style)
+def _count_words(s: str) -> int:
+    return len(re.findall(r"\b\w+\b", s))
+
+
+_IF_CHECKS = {
+    "min_words": lambda r, v: _count_words(r) >= int(v),
+    "max_words": lambda r, v: _count_words(r) <= int(v),
+    "min_sentences": lambda r, v: len([x for x in re.split(r"[.!?]+", r) if x.strip()]) >= int(v),
+    "include_keywords": lambda r, v: all(k.lower() in r.lower() for k in v),
+    "forbidden_words": lambda r, v: not any(re.search(rf"\b{re.escape(k)}\b", r, flags=re.I) for k in v),
+    "num_paragraphs": lambda r, v: len([p for p in re.split(r"\n\s*\n", r.strip()) if p.strip()]) == int(v),
+    "num_bullets": lambda r, v: len(re.findall(r"^\s*[\*\-] ", r, flags=re.M)) == int(v),
+    "all_lowercase": lambda r, v: (r == r.lower()) == bool(v),
+    "all_uppercase": lambda r, v: (r == r.upper()) == bool(v),
+    "ends_with": lambda r, v: r.strip().endswith(str(v)),
+    "starts_with": lambda r, v: r.strip().startswith(str(v)),
+    "json_format": lambda r, v: _is_json(r) == bool(v),
+    "no_commas": lambda r, v: ("," not in r) == bool(v),
+}
+
+
+def _is_json(r: str) -> bool:
+    import json
+
+    s = r.strip()
+    s = re.sub(r"^```(?:json)?|```$", "", s.strip(), flags=re.M).strip()
+    try:
+        json.loads(s)
+        return True
+    except ValueError:
+        return False
+
+
+@register_reward("ifbench", note="fraction of the label's verifiable constraints the response satisfies")
+def ifbench_reward(sample) -> float:
+    """``sample.label``: dict (or JSON string) constraint -> argument, e.g. ``{"min_words": 50, "forbidden_words": ["very"]}``.
+    Unknown constraints count as failed, so a typo in the data shows up as a low score instead of a free point."""
+    import json
+
+    spec = sample.label
+    if isinstance(spec, str):
+        try:
+            spec = json.loads(spec)
+        except ValueError:
+            return 0.0
+    if not isinstance(spec, dict) or not spec:
+        return 0.0
+    resp = sample.response.split("</think>")[-1]
+    ok = 0
+    for k, v in spec.items():
+        fn = _IF_CHECKS.get(k)
+        try:
+            ok += 1 if fn is not None and fn(resp, v) else 0
+        except (TypeError, ValueError):
+            pass
+    return ok / len(spec)
+
+
+# --------------------------------------------------------------------------- remote / generative judges
+@register_reward("remote_rm", note="POST {prompt, response, label} to --rm-url and read 'reward' from the JSON reply")
+def remote_rm_reward(sample, url: Optional[str] = None, timeout: float = 30.0) -> float:
+    import json
+    import os
+    import urllib.request
+
+    url = url or os.environ.get("RELAX_RM_URL")
+    if not url:
+        raise ValueError("remote_rm needs a reward-model URL (--rm-url / RELAX_RM_URL)")
+    body = json.dumps({"prompt": str(sample.prompt), "response": sample.response, "label": sample.label}).encode()
+    req = urllib.request.Request(url, data=body, headers={"Content-Type": "application/json"})
+    with urllib.request.urlopen(req, timeout=timeout) as r:
+        out = json.loads(r.read())
+    return float(out["reward"] if isinstance(out, dict) else out)
+
+
+def make_dapo_genrm_reward(genrm):
+    """DAPO scoring with a generative judge for the answers the rule cannot parse: rule says correct -> +1; rule finds
+    an answer and it is wrong -> -1; no parsable answer -> ask the judge (``relax_b200.rewards.genrm.GenRM``)."""
+    def fn(sample) -> dict:
+        base = dapo_reward(sample)
+        if base.get("pred") not in (None, "", "[INVALID]"):
+            return base
+        score = genrm.score([str(sample.prompt)], [str(sample.label)], [sample.response])[0]
+        return {"score": 1.0 if score >= 0.5 else -1.0, "acc": score >= 0.5, "pred": "[GENRM]"}
+
+    return fn

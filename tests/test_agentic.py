@@ -112,3 +112,46 @@ def test_genrm_parsing_failover_and_default():
     assert rm.engines[0].healthy
     dead = GenRM([JudgeEngine(broken)], default=0.25)
     assert dead.score(["q"], ["r"], ["a"]) == [0.25]
+
+
+def test_ifbench_remote_and_dapo_genrm_rewards():
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from relax_b200.rewards import get_reward_spec
+    from relax_b200.rewards.rules import make_dapo_genrm_reward, remote_rm_reward
+    from relax_b200.types import Sample
+
+    s = Sample(prompt="p", response="<think>x</think>one two three four. done", label={"min_words": 4, "forbidden_words": ["five"],
+                                                                                       "ends_with": "done", "bogus": 1})
+    assert get_reward_spec("ifbench").fn(s) == 0.75
+    s.label = json.dumps({"max_words": 2})
+    assert get_reward_spec("ifbench").fn(s) == 0.0
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            out = json.dumps({"reward": 1.0 if body["label"] in body["response"] else 0.0}).encode()
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        url = f"http://127.0.0.1:{srv.server_address[1]}"
+        assert remote_rm_reward(Sample(prompt="q", response="the answer is 42", label="42"), url=url) == 1.0
+        assert remote_rm_reward(Sample(prompt="q", response="no idea", label="42"), url=url) == 0.0
+    finally:
+        srv.shutdown()
+
+    rm = GenRM([JudgeEngine(lambda prompts, n: ["Verdict: correct"] * len(prompts))])
+    fn = make_dapo_genrm_reward(rm)
+    assert fn(Sample(prompt="q", response="Answer: 7", label="7"))["score"] == 1.0          # rule decides
+    assert fn(Sample(prompt="q", response="Answer: 8", label="7"))["score"] == -1.0
+    assert fn(Sample(prompt="q", response="it is seven", label="7"))["pred"] == "[GENRM]"   # judge decides
