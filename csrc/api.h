@@ -91,6 +91,13 @@ int rb_dp_adam_allgather(void* const* peer_p, unsigned* const* peer_sig, int* st
                          long long n, void* master, const float* g, float* m, float* v, int step, float lr, float b1,
                          float b2, float eps, float wd, float gscale, int split, unsigned long long wait_ns, int* err,
                          cudaStream_t st);
+int rb_fa_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse, void* dq,
+                 void* dk, void* dv, float* delta, float* dq_acc, const int* cu_q, const int* cu_k, int num_seqs, int Tq,
+                 int Tk, int Hq, int Hkv, int causal, float scale, int max_kv_blocks, int flags, int* err,
+                 cudaStream_t stream);
+int rb_fa_dq_convert(const float* dq_acc, void* dq, long long n, cudaStream_t stream);
+int rb_peer_barrier(unsigned* const* peer_sig, int* state, int n, int rank, int slot, int state_idx,
+                    unsigned long long wait_ns, int* err, cudaStream_t st);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

@@ -414,11 +414,28 @@ __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat1
 
 }  // namespace rb
 
+extern "C" int rb_fa_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                            void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_q, const int* cu_k,
+                            int num_seqs, int Tq, int Tk, int Hq, int Hkv, int causal, float scale, int max_kv_blocks,
+                            int flags, int* err, cudaStream_t stream);
+
 // Scratch: delta fp32 [Hq*Tq], dq_acc fp32 [Tq*Hq*128] (zeroed here).  q/k/v/o/do contiguous [T][H][128].
 extern "C" int rb_fa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
                          void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_q, const int* cu_k,
                          int num_seqs, int Tq, int Tk, int Hq, int Hkv, int causal, float scale, int max_kv_blocks,
                          int* err, cudaStream_t stream) {
+  return rb_fa_bwd_ex(q, k, v, o, d_o, lse, dq, dk, dv, delta, dq_acc, cu_q, cu_k, num_seqs, Tq, Tk, Hq, Hkv, causal, scale,
+                      max_kv_blocks, 0, err, stream);
+}
+
+// flags: 1 = `delta` is given (do not recompute it from o and d_o); 2 = do not zero `dq_acc` first (the caller
+// accumulates several calls into it, possibly into another GPU's buffer through a peer mapping: the dQ
+// reductions are plain fp32 atomics and work across NVLink); 4 = do not convert `dq_acc` to `dq` at the end.
+// q / d_o / lse / delta may alias peer memory (read by TMA without multicast and by read-only loads).
+extern "C" int rb_fa_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                            void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_q, const int* cu_k,
+                            int num_seqs, int Tq, int Tk, int Hq, int Hkv, int causal, float scale, int max_kv_blocks,
+                            int flags, int* err, cudaStream_t stream) {
   using namespace rb;
   if (Tq == 0 || Tk == 0 || num_seqs == 0) return 0;
   if (Hq % Hkv) return -2;
@@ -438,8 +455,8 @@ extern "C" int rb_fa_bwd(const void* q, const void* k, const void* v, const void
     attr_set = true;
   }
   const long long n_dq = (long long)Tq * Hq * FB_D;
-  cudaMemsetAsync(dq_acc, 0, n_dq * sizeof(float), stream);
-  {
+  if (!(flags & 2)) cudaMemsetAsync(dq_acc, 0, n_dq * sizeof(float), stream);
+  if (!(flags & 1)) {
     const long long rows = (long long)Tq * Hq;
     long long blocks = (rows + 7) / 8;
     if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
@@ -453,10 +470,21 @@ extern "C" int rb_fa_bwd(const void* q, const void* k, const void* v, const void
   dim3 grid(max_kv_blocks, Hkv);
   fa_bwd_kernel<<<grid, FB_THREADS, FB_SMEM_TOTAL, stream>>>(tq, tdo, tk, tv, p);
   rb_note_launch(3);
-  {
+  if (!(flags & 4)) {
     long long blocks = (n_dq / 4 + 255) / 256;
     if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
     fa_dq_convert_kernel<<<(int)blocks, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n_dq);
   }
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int rb_fa_dq_convert(const float* dq_acc, void* dq, long long n, cudaStream_t stream) {
+  using namespace rb;
+  if (n == 0) return 0;
+  if (n % 4) return -2;
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
+  fa_dq_convert_kernel<<<(int)blocks, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, n);
+  rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

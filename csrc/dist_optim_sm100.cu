@@ -136,6 +136,23 @@ dp_adam_allgather_kernel(const DpParams p, void* __restrict__ master, const floa
   }
 }
 
+// Barrier between the ranks of a group through their signal pads: every rank adds 1 to word `slot` of every
+// rank's pad (a system-scope release, so its earlier stores - e.g. a buffer it just filled for the peers - are
+// visible first) and waits, bounded, until its own word shows one arrival per rank.  One block, launched in
+// stream order between the kernels it separates.
+__global__ void peer_barrier_kernel(const DpParams p, int slot, int state_idx) {
+  __shared__ int ok;
+  if (threadIdx.x < p.dp) sys_red_add(p.peer_sig[threadIdx.x] + slot, 1u);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned target = static_cast<unsigned>(p.state[state_idx]) + static_cast<unsigned>(p.dp);
+    ok = sys_wait_ge(p.peer_sig[p.rank] + slot, target, p.wait_ns) ? 1 : 0;
+    if (!ok) atomicExch(p.err, 3);
+    p.state[state_idx] += p.dp;
+    __threadfence_system();
+  }
+}
+
 }  // namespace rb
 
 static void fill(rb::DpParams& p, int dp, int rank, float* const* peer_g, void* const* peer_p, unsigned* const* peer_sig,
@@ -177,6 +194,17 @@ extern "C" int rb_dp_adam_allgather(void* const* peer_p, unsigned* const* peer_s
   if (blocks > num_sms() * 4LL) blocks = num_sms() * 4LL;
   if (split) dp_adam_allgather_kernel<true><<<(int)blocks, 256, 0, st>>>(p, master, g, m, v, lr, b1, b2, eps, wd, gscale, bc1, bc2);
   else dp_adam_allgather_kernel<false><<<(int)blocks, 256, 0, st>>>(p, master, g, m, v, lr, b1, b2, eps, wd, gscale, bc1, bc2);
+  rb_note_launch(1);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_peer_barrier(unsigned* const* peer_sig, int* state, int n, int rank, int slot, int state_idx,
+                               unsigned long long wait_ns, int* err, cudaStream_t st) {
+  using namespace rb;
+  if (n < 1 || n > 8 || slot < 0 || slot >= 256 || state_idx < 0) return -2;
+  DpParams p{};
+  fill(p, n, rank, nullptr, nullptr, peer_sig, state, 0, 0, wait_ns, err);
+  peer_barrier_kernel<<<1, 32, 0, st>>>(p, slot, state_idx);
   rb_note_launch(1);
   return (int)cudaGetLastError();
 }

@@ -152,12 +152,46 @@ void dp_adam_allgather(std::vector<int64_t> param_ptrs, std::vector<int64_t> sig
                              err.data_ptr<int>(), cur_stream()),
         "rb_dp_adam_allgather");
 }
+
+void peer_barrier(std::vector<int64_t> sig_ptrs, torch::Tensor state, int64_t rank, int64_t slot, int64_t state_idx,
+                  int64_t wait_ns, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(state.device());
+  const int n = (int)sig_ptrs.size();
+  unsigned* sg[8];
+  TORCH_CHECK(n >= 1 && n <= 8);
+  for (int r = 0; r < n; ++r) sg[r] = reinterpret_cast<unsigned*>(sig_ptrs[r]);
+  check(rb_peer_barrier(sg, state.data_ptr<int>(), n, (int)rank, (int)slot, (int)state_idx, (unsigned long long)wait_ns,
+                        err.data_ptr<int>(), cur_stream()),
+        "rb_peer_barrier");
+}
+
+// Flash-attention backward with caller-controlled scratch handling (flags as in rb_fa_bwd_ex); tensors may alias
+// peer memory.  dq may be an empty tensor when flag 4 is set.
+void fa_bwd_ex(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor o, torch::Tensor d_o, torch::Tensor lse,
+               torch::Tensor dq, torch::Tensor dk, torch::Tensor dv, torch::Tensor delta, torch::Tensor dq_acc,
+               torch::Tensor cu_q, torch::Tensor cu_k, int64_t max_kv_blocks, bool causal, double scale, int64_t flags,
+               torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(k.device());
+  check(rb_fa_bwd_ex(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr<float>(),
+                     dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
+                     cu_q.data_ptr<int>(), cu_k.data_ptr<int>(), (int)cu_q.numel() - 1, (int)q.size(0), (int)k.size(0),
+                     (int)q.size(1), (int)k.size(1), causal, (float)scale, (int)max_kv_blocks, (int)flags,
+                     err.data_ptr<int>(), cur_stream()),
+        "rb_fa_bwd_ex");
+}
+void fa_dq_convert(torch::Tensor dq_acc, torch::Tensor dq) {
+  const c10::cuda::CUDAGuard guard(dq.device());
+  check(rb_fa_dq_convert(dq_acc.data_ptr<float>(), dq.data_ptr(), dq.numel(), cur_stream()), "rb_fa_dq_convert");
+}
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
   m.def("gemm_ar_plan", &gemm_ar_plan);
   m.def("ag_gemm", &ag_gemm);
   m.def("qkv_post", &qkv_post);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("fa_bwd_ex", &fa_bwd_ex);
+  m.def("fa_dq_convert", &fa_dq_convert);
   m.def("dp_reduce_sumsq", &dp_reduce_sumsq);
   m.def("dp_adam_allgather", &dp_adam_allgather);
   m.def("gemm_splitk_partial", &gemm_splitk_partial);

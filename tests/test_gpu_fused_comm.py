@@ -218,3 +218,47 @@ def test_fused_distributed_optimizer_matches_nccl_path():
         # the two paths round the clip factor differently in the last bit: allow one bf16 ulp at |w| < 0.06
         assert diff <= 5e-4 and nrel < 1e-4 and mass > 0, out
     assert out[0][2] == out[1][2]      # both ranks hold the same parameters after the fused all-gather
+
+
+def _cp_worker(rank, world, L, valid):
+    """Zig-zag context parallelism with in-kernel KV reads from the peer, against full attention on one GPU."""
+    from relax_b200 import ops
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.cp_peer import CPComm, peer_attention
+
+    dev = torch.device("cuda", rank)
+    Hq, Hkv, D, cp = 8, 2, 128, world
+    cs = L // (2 * cp)
+    g = torch.Generator().manual_seed(5)
+    qf = (torch.randn(L, Hq, D, generator=g) * 0.5).bfloat16().to(dev)
+    kf = (torch.randn(L, Hkv, D, generator=g) * 0.5).bfloat16().to(dev)
+    vf = (torch.randn(L, Hkv, D, generator=g) * 0.5).bfloat16().to(dev)
+    dof = (torch.randn(L, Hq, D, generator=g) * 0.1).bfloat16().to(dev)
+    idx = torch.cat([torch.arange(rank * cs, (rank + 1) * cs), torch.arange((2 * cp - 1 - rank) * cs, (2 * cp - rank) * cs)]).to(dev)
+    comm = CPComm(_group(world), dev, 2 * cs, Hq, Hkv)
+    worst = 0.0
+    for rep in range(2):
+        # reference: the whole (valid) sequence on this GPU
+        qr, kr, vr = (t[:valid].clone().requires_grad_() for t in (qf, kf, vf))
+        cu = torch.tensor([0, valid], dtype=torch.int32, device=dev)
+        o_ref = ops.attention_varlen(qr, kr, vr, cu, causal=True)
+        o_ref.backward(dof[:valid])
+        pad = lambda t: torch.cat([t, torch.zeros(L - valid, *t.shape[1:], dtype=t.dtype, device=dev)])
+        q, k, v = (t[idx].clone().requires_grad_() for t in (qf, kf, vf))
+        o = peer_attention(q, k, v, comm, valid)
+        o.backward(dof[idx])
+        torch.cuda.synchronize(dev)
+        C.check_error_flag(dev)
+        live = idx < valid
+        for got, ref in ((o, pad(o_ref.detach())[idx]), (q.grad, pad(qr.grad)[idx]), (k.grad, pad(kr.grad)[idx]),
+                         (v.grad, pad(vr.grad)[idx])):
+            worst = max(worst, float((got.float() - ref.float())[live].abs().max()))
+    comm.close()
+    return worst
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+@pytest.mark.parametrize("L,valid", [(1024, 1024), (1024, 900)])
+def test_context_parallel_attention_reads_peer_kv(L, valid):
+    worst = run_distributed(_cp_worker, 2, L, valid, backend="nccl", timeout=600)
+    assert max(worst) < 0.03, worst
