@@ -116,6 +116,25 @@ def all_gather_with_cp(local: torch.Tensor, total_length: int, response_length: 
     return _AllReduceDiff.apply(full, g.group)
 
 
+def gather_response_with_cp(local: torch.Tensor, total_length: int, response_length: int, g: GroupInfo) -> torch.Tensor:
+    """Full ``[R]`` response tensor on every rank, differentiable ONLY through this rank's own pieces: the value
+    is the same everywhere, but a loss computed from it sends gradient to the local tokens alone, so averaging
+    parameter gradients over the dp x cp world gives the gradient of the replicated loss exactly once."""
+    if g.size == 1:
+        return local
+    prompt = total_length - response_length
+    _, _, logits, _ = offsets_with_cp(total_length, response_length, g.size, g.rank)
+    idx, o = [], 0
+    for a, b in logits:
+        if b > a:
+            idx.append(torch.arange(a - (prompt - 1), b - (prompt - 1), device=local.device))
+    idx = torch.cat(idx) if idx else torch.zeros(0, dtype=torch.long, device=local.device)
+    mine = local.new_zeros(response_length).index_put((idx,), local) if idx.numel() else local.new_zeros(response_length)
+    full = mine.detach().clone()
+    dist.all_reduce(full, group=g.group)
+    return full - mine.detach() + mine
+
+
 # ----------------------------------------------------------------------------- dynamic CP
 
 

@@ -144,7 +144,44 @@ class TrainActor:
         mult = self.ps.tp.size * (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
         return pack_samples(tokens, response_lengths, pad_multiple=max(1, mult), device=self.device)
 
+    def _forward_logp_cp(self, pb, with_entropy: bool):
+        """Context-parallel forward: every sample is sharded zig-zag over the CP ranks (two chunks per rank),
+        attention runs as ring attention - or, with a :class:`~relax_b200.parallel.cp_peer.CPComm` attached as
+        ``self.cp_comm``, with in-kernel reads of the peers' K/V - and the per-token outputs are gathered so every
+        rank evaluates the same loss (gradient flows through the local tokens only)."""
+        from ..parallel import cp as CP
+
+        g = self.ps.cp
+        cp, r = g.size, g.rank
+        unit = 2 * cp * max(1, self.ps.tp.size) * (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
+        cu = pb.cu_seqlens.tolist()
+        lps, ens = [], []
+        for si, R in enumerate(pb.response_lengths):
+            toks = pb.tokens[cu[si]:cu[si + 1]]
+            L = int(toks.numel())
+            Lp = (L + unit - 1) // unit * unit
+            cs = Lp // (2 * cp)
+            tok_pad = torch.cat([toks, toks.new_zeros(Lp - L + 1)])
+            idx = torch.cat([torch.arange(r * cs, (r + 1) * cs), torch.arange((2 * cp - 1 - r) * cs, (2 * cp - r) * cs)]).to(toks.device)
+            comm = getattr(self, "cp_comm", None)
+
+            def attn(layer_idx, q, k, v, L=L, comm=comm):
+                if comm is not None and q.is_cuda:
+                    from ..parallel.cp_peer import peer_attention
+
+                    return peer_attention(q, k.contiguous(), v.contiguous(), comm, L)
+                return CP.ring_attention(q, k.contiguous(), v.contiguous(), g, L)
+
+            h = self.model(tok_pad[idx], idx, None, attn_fn=attn)
+            sel = (idx >= L - R - 1) & (idx <= L - 2)
+            lp, en = self.model.log_probs(h[sel], tok_pad[idx + 1][sel], self.cfg.rollout_temperature, with_entropy)
+            lps.append(CP.gather_response_with_cp(lp, L, R, g))
+            ens.append(CP.gather_response_with_cp(en, L, R, g) if with_entropy else lp.new_zeros(R))
+        return torch.cat(lps), torch.cat(ens)
+
     def _forward_logp(self, pb, with_entropy: bool):
+        if self.ps.cp.size > 1:
+            return self._forward_logp_cp(pb, with_entropy)
         h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
         hr = h.index_select(0, pb.logit_rows)
         return self.model.log_probs(hr, pb.targets, self.cfg.rollout_temperature, with_entropy)

@@ -78,3 +78,42 @@ def _ring_worker(rank, world):
 
 def test_ring_attention_matches_full_attention_two_ranks():
     assert all(run_distributed(_ring_worker, 2))
+
+
+def _cp_train_worker(rank, world):
+    """cp=2 trainer forward/backward equals the single-rank one (log-probs and parameter gradients)."""
+    from relax_b200.models.config import get_config
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+    from relax_b200.train.actor import TrainActor, TrainConfig
+
+    ps = init_parallel_state(ParallelDims(cp=2))
+    actor = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512), ps, seed=7)
+    toks = [list(range(3, 40)), list(range(50, 73))]
+    rl = [11, 9]
+    pb = actor._pack(toks, rl)
+    lp, en = actor._forward_logp(pb, True)
+    actor.optimizer.zero_grad()
+    (lp.sum() + 0.1 * en.sum()).backward()
+    gsum = torch.cat([p.main_grad.flatten() for p in actor.optimizer.params]).clone()
+    import torch.distributed as dist
+
+    dist.all_reduce(gsum)      # the optimizer averages over dp x cp; the sum over cp is the full gradient
+    return lp.detach(), en.detach(), gsum
+
+
+def test_trainer_forward_backward_under_cp2_matches_cp1():
+    from relax_b200.models.config import get_config
+    from relax_b200.train.actor import TrainActor, TrainConfig
+
+    out = run_distributed(_cp_train_worker, 2)
+    ref = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512), seed=7)
+    toks = [list(range(3, 40)), list(range(50, 73))]
+    pb = ref._pack(toks, [11, 9])
+    lp, en = ref._forward_logp(pb, True)
+    ref.optimizer.zero_grad()
+    (lp.sum() + 0.1 * en.sum()).backward()
+    g = torch.cat([p.main_grad.flatten() for p in ref.optimizer.params])
+    for r in range(2):
+        assert torch.allclose(out[r][0], lp.detach(), atol=2e-5), (out[r][0] - lp).abs().max()
+        assert torch.allclose(out[r][1], en.detach(), atol=2e-5)
+        assert torch.allclose(out[r][2], g, atol=2e-4, rtol=1e-3), (out[r][2] - g).abs().max()
