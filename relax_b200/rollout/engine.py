@@ -169,6 +169,10 @@ class RolloutEngine:
             torch.cuda.empty_cache()
 
     def resume_memory_occupation(self, tags: Sequence[str] = ("kv_cache",)):
+        if self.memory_saver and self.device.type == "cuda":
+            # pausable buffers take physical memory straight from the driver: hand back what the trainer's
+            # caching allocator no longer uses first
+            torch.cuda.empty_cache()
         if "weights" in tags:
             self.weights.resume()
         if "kv_cache" in tags and (self.kv is None or (self._kv_buf is not None and self._kv_buf.paused)):
