@@ -115,6 +115,54 @@ def main():
         tf, tn, tl = (_time(f, 5, False, dev) for f in (lambda: comm.ag_gemm(x, w), nccl, lambda: ops.linear(xfull, w)))
         say(f"  rows/rank={Ts:5d} N={N:5d} K={H}: fused {tf:6.1f}   NCCL+GEMM {tn:6.1f}   (GEMM alone {tl:6.1f})")
 
+    say(f"== distributed-optimizer step, DP{world}: fused kernels vs NCCL reduce-scatter + Adam + all-gather (ms per step)")
+    from ..train.optimizer import DistributedOptimizer, OptimizerConfig
+    from .state import ParallelDims, init_parallel_state
+
+    ps = init_parallel_state(ParallelDims(dp=world))
+
+    class _Flat(torch.nn.Module):
+        def __init__(self, n):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.zeros(n, dtype=torch.bfloat16, device=dev))
+
+    for n in (64 << 20, 512 << 20):
+        res = {}
+        for fused in (True, False):
+            m = _Flat(n)
+            opt = DistributedOptimizer(m, ps, OptimizerConfig(lr=1e-4, clip_grad=1.0, fused_dp=fused))
+            m.w.main_grad.normal_(0, 1e-3)
+            res[fused] = _time(lambda: opt.step(), 5, False, dev) / 1000
+            del opt, m
+            torch.cuda.empty_cache()
+        say(f"  {n >> 20:5d} Mi parameters: fused {res[True]:7.2f}   NCCL {res[False]:7.2f}   "
+            f"(link bytes per rank {(world - 1) * n // world * 6 / 1e9:.2f} GB)")
+
+    say(f"== context-parallel attention, CP{world}: K/V (fwd) and Q/dO (bwd) read from peer memory inside the kernels")
+    from .cp_peer import CPComm, peer_attention
+
+    Hq, Hkv = 32, 8
+    for L in (8192, 32768):
+        cs = L // (2 * world)
+        comm = CPComm(GroupInfo(dist.group.WORLD, tuple(range(world)), rank), dev, 2 * cs, Hq, Hkv)
+        q = torch.randn(2 * cs, Hq, 128, device=dev).bfloat16().requires_grad_()
+        k = torch.randn(2 * cs, Hkv, 128, device=dev).bfloat16().requires_grad_()
+        v = torch.randn(2 * cs, Hkv, 128, device=dev).bfloat16().requires_grad_()
+        do = torch.randn(2 * cs, Hq, 128, device=dev).bfloat16()
+        tf = _time(lambda: peer_attention(q.detach(), k.detach(), v.detach(), comm, L), 5, False, dev)
+        tfb = _time(lambda: peer_attention(q, k, v, comm, L).backward(do), 5, False, dev)
+        # lower bound: this rank's share of the work if the whole sequence sat on one GPU
+        qf = torch.randn(L, Hq, 128, device=dev).bfloat16().requires_grad_()
+        kf = torch.randn(L, Hkv, 128, device=dev).bfloat16().requires_grad_()
+        vf = torch.randn(L, Hkv, 128, device=dev).bfloat16().requires_grad_()
+        dof = torch.randn(L, Hq, 128, device=dev).bfloat16()
+        cu = torch.tensor([0, L], dtype=torch.int32, device=dev)
+        t1 = _time(lambda: ops.attention_varlen(qf.detach(), kf.detach(), vf.detach(), cu), 5, False, dev)
+        t1b = _time(lambda: ops.attention_varlen(qf, kf, vf, cu).backward(dof), 5, False, dev)
+        say(f"  L={L:6d}: forward {tf:8.1f} us, forward+backward {tfb:8.1f} us   "
+            f"(single-GPU attention of the whole sequence / {world}: {t1 / world:8.1f}, {t1b / world:8.1f})")
+        comm.close()
+
     if args.timeline:
         for (M, K) in [(16, H // world), (128, F // world)]:
             x = torch.randn(M, K, device=dev).bfloat16()
