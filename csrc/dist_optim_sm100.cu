@@ -153,6 +153,19 @@ __global__ void peer_barrier_kernel(const DpParams p, int slot, int state_idx) {
   }
 }
 
+// Copies a contiguous buffer into the same offset of up to 8 destinations (this GPU's or peers' memory mapped
+// here): the push half of an all-gather.  16-byte vectors; completion is ordered by the barrier that follows.
+struct PushParams {
+  uint4* dst[8];
+  int n_dst;
+};
+__global__ void peer_push_kernel(const uint4* __restrict__ src, const PushParams p, long long nvec) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 v = src[i];
+    for (int d = 0; d < p.n_dst; ++d) p.dst[d][i] = v;
+  }
+}
+
 }  // namespace rb
 
 static void fill(rb::DpParams& p, int dp, int rank, float* const* peer_g, void* const* peer_p, unsigned* const* peer_sig,
@@ -205,6 +218,24 @@ extern "C" int rb_peer_barrier(unsigned* const* peer_sig, int* state, int n, int
   DpParams p{};
   fill(p, n, rank, nullptr, nullptr, peer_sig, state, 0, 0, wait_ns, err);
   peer_barrier_kernel<<<1, 32, 0, st>>>(p, slot, state_idx);
+  rb_note_launch(1);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int rb_peer_push(const void* src, void* const* dst, int n_dst, long long nbytes, cudaStream_t st) {
+  using namespace rb;
+  if (nbytes == 0 || n_dst == 0) return 0;
+  if (n_dst < 0 || n_dst > 8 || (nbytes % 16) || (reinterpret_cast<uintptr_t>(src) % 16)) return -2;
+  PushParams p{};
+  p.n_dst = n_dst;
+  for (int d = 0; d < n_dst; ++d) {
+    if (reinterpret_cast<uintptr_t>(dst[d]) % 16) return -2;
+    p.dst[d] = reinterpret_cast<uint4*>(dst[d]);
+  }
+  const long long nvec = nbytes / 16;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > num_sms() * 8LL) blocks = num_sms() * 8LL;
+  peer_push_kernel<<<(int)blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(src), p, nvec);
   rb_note_launch(1);
   return (int)cudaGetLastError();
 }

@@ -183,6 +183,16 @@ void fa_dq_convert(torch::Tensor dq_acc, torch::Tensor dq) {
   const c10::cuda::CUDAGuard guard(dq.device());
   check(rb_fa_dq_convert(dq_acc.data_ptr<float>(), dq.data_ptr(), dq.numel(), cur_stream()), "rb_fa_dq_convert");
 }
+
+// src (contiguous) -> dst_ptrs[i] + offset_bytes for every destination.
+void peer_push(torch::Tensor src, std::vector<int64_t> dst_ptrs, int64_t offset_bytes) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && dst_ptrs.size() <= 8);
+  void* d[8];
+  for (size_t i = 0; i < dst_ptrs.size(); ++i) d[i] = reinterpret_cast<void*>(dst_ptrs[i] + offset_bytes);
+  check(rb_peer_push(src.data_ptr(), d, (int)dst_ptrs.size(), (long long)src.numel() * src.element_size(), cur_stream()),
+        "rb_peer_push");
+}
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
@@ -190,6 +200,7 @@ void register_fused(pybind11::module_& m) {
   m.def("ag_gemm", &ag_gemm);
   m.def("qkv_post", &qkv_post);
   m.def("peer_barrier", &peer_barrier);
+  m.def("peer_push", &peer_push);
   m.def("fa_bwd_ex", &fa_bwd_ex);
   m.def("fa_dq_convert", &fa_dq_convert);
   m.def("dp_reduce_sumsq", &dp_reduce_sumsq);
