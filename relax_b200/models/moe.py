@@ -143,7 +143,25 @@ class MoEMLP(nn.Module):
         xp = x[src_tok]                               # permuted copies [T*k, H]
         counts = torch.bincount(flat_e, minlength=E)  # tokens per (global) expert
 
-        if ps.ep.size > 1:
+        comm = getattr(self, "ep_comm", None) if x.is_cuda else None
+        if ps.ep.size > 1 and comm is not None:
+            # dispatch / combine by peer stores into the expert owners' buffers (parallel/ep_peer.py)
+            from ..parallel.ep_peer import peer_all_to_all
+
+            ep = ps.ep.size
+            allc = comm.exchange_counts(counts).view(ep, ep, self.e_local)          # [src][dst][local expert]
+            matrix = allc.sum(-1).tolist()
+            recv_counts = allc[:, ps.ep.rank, :]
+            xr = peer_all_to_all(xp, matrix, comm)
+            rc = recv_counts.reshape(-1)
+            seg_expert = torch.arange(self.e_local, device=x.device).repeat(ep)
+            reorder = torch.argsort(torch.repeat_interleave(seg_expert, rc), stable=True)
+            ye = grouped_swiglu_mlp(xr[reorder], recv_counts.sum(0).tolist(), self.experts.linear_fc1.weight,
+                                    self.experts.linear_fc2.weight)
+            inv = torch.empty_like(reorder)
+            inv[reorder] = torch.arange(reorder.numel(), device=x.device)
+            yp = peer_all_to_all(ye[inv], [[matrix[d][s_] for d in range(ep)] for s_ in range(ep)], comm)
+        elif ps.ep.size > 1:
             ep = ps.ep.size
             send_counts = counts.view(ep, self.e_local)
             recv_counts = torch.empty_like(send_counts)

@@ -262,3 +262,46 @@ def _cp_worker(rank, world, L, valid):
 def test_context_parallel_attention_reads_peer_kv(L, valid):
     worst = run_distributed(_cp_worker, 2, L, valid, backend="nccl", timeout=600)
     assert max(worst) < 0.03, worst
+
+
+def _ep_worker(rank, world):
+    """Variable-size token exchange by peer stores against all_to_all_single, forward and backward."""
+    import torch.distributed as dist
+
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.ep_peer import EPComm, peer_all_to_all
+
+    dev = torch.device("cuda", rank)
+    H, E = 256, 8
+    comm = EPComm(_group(world), dev, capacity_rows=4096, hidden=H)
+    worst = 0.0
+    for rep in range(3):
+        g = torch.Generator().manual_seed(31 * rep + rank)
+        counts = torch.randint(0, 40, (E,), generator=g).to(dev)
+        allc = comm.exchange_counts(counts)
+        ref = [torch.empty_like(counts) for _ in range(world)]
+        dist.all_gather(ref, counts)
+        assert torch.equal(allc, torch.stack(ref))
+        el = E // world
+        matrix = allc.view(world, world, el).sum(-1).tolist()
+        n_send = int(counts.sum())
+        x = torch.randn(n_send, H, generator=g).bfloat16().to(dev).requires_grad_()
+        y = peer_all_to_all(x, matrix, comm)
+        in_splits, out_splits = matrix[rank], [matrix[s][rank] for s in range(world)]
+        y_ref = torch.empty(sum(out_splits), H, dtype=x.dtype, device=dev)
+        dist.all_to_all_single(y_ref, x.detach().contiguous(), out_splits, in_splits)
+        gy = torch.randn(y.shape, generator=g).bfloat16().to(dev)
+        y.backward(gy)
+        gx_ref = torch.empty(n_send, H, dtype=x.dtype, device=dev)
+        dist.all_to_all_single(gx_ref, gy.contiguous(), in_splits, out_splits)
+        torch.cuda.synchronize(dev)
+        C.check_error_flag(dev)
+        worst = max(worst, float((y.float() - y_ref.float()).abs().max()) if y.numel() else 0.0,
+                    float((x.grad.float() - gx_ref.float()).abs().max()))
+    comm.close()
+    return worst
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_expert_parallel_exchange_by_peer_stores():
+    assert max(run_distributed(_ep_worker, 2, backend="nccl", timeout=600)) == 0.0
