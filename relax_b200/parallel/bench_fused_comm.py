@@ -138,7 +138,7 @@ def main():
         say(f"  {n >> 20:5d} Mi parameters: fused {res[True]:7.2f}   NCCL {res[False]:7.2f}   "
             f"(link bytes per rank {(world - 1) * n // world * 6 / 1e9:.2f} GB)")
 
-    say(f"== context-parallel attention, CP{world}: K/V (fwd) and Q/dO (bwd) read from peer memory inside the kernels")
+    say(f"== context-parallel attention, CP{world}: K/V (fwd) and Q/dO/dQ (bwd) cross NVLink once by peer stores")
     from .cp_peer import CPComm, peer_attention
 
     Hq, Hkv = 32, 8
