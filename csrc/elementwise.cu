@@ -103,6 +103,57 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+// One warp per row, the row held in registers (up to 16 x 16-byte vectors per lane: cols <= 4096 for 16-bit
+// types): a single pass over memory, 16 independent loads in flight per lane, no block barrier.
+template <typename T, bool ADD>
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_warp_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w, T* __restrict__ y,
+                        T* __restrict__ r_out, int rows, int cols, float eps) {
+  constexpr int N = 16 / sizeof(T);
+  constexpr int MAXV = 16;
+  const int lane = threadIdx.x & 31;
+  const int nv = cols / (32 * N);
+  const float inv_cols = 1.f / cols;
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += gridDim.x * 8) {
+    const size_t base = static_cast<size_t>(row) * cols;
+    Vec<T> v[MAXV];
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j)
+      if (j < nv) v[j] = *reinterpret_cast<const Vec<T>*>(x + base + (j * 32 + lane) * N);
+    if constexpr (ADD) {
+#pragma unroll
+      for (int j = 0; j < MAXV; ++j)
+        if (j < nv) {
+          const Vec<T> r = *reinterpret_cast<const Vec<T>*>(res + base + (j * 32 + lane) * N);
+#pragma unroll
+          for (int i = 0; i < N; ++i) v[j].v[i] = Cvt<T>::from(Cvt<T>::to(v[j].v[i]) + Cvt<T>::to(r.v[i]));
+          *reinterpret_cast<Vec<T>*>(r_out + base + (j * 32 + lane) * N) = v[j];
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j)
+      if (j < nv) {
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const float a = Cvt<T>::to(v[j].v[i]);
+          ss += a * a;
+        }
+      }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss * inv_cols + eps);
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j)
+      if (j < nv) {
+        const Vec<T> g = *reinterpret_cast<const Vec<T>*>(w + (j * 32 + lane) * N);
+        Vec<T> o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) o.v[i] = Cvt<T>::from(Cvt<T>::to(v[j].v[i]) * rstd * Cvt<T>::to(g.v[i]));
+        *reinterpret_cast<Vec<T>*>(y + base + (j * 32 + lane) * N) = o;
+      }
+  }
+}
+
 // Backward: dx = rstd * (g - x * rstd^2 * mean(g*x)) with g = dy*w ; dw partials per block.
 template <typename T, int TPR>
 __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
@@ -175,12 +226,20 @@ __global__ void rope_kernel(const T* __restrict__ x, T* __restrict__ y, const fl
     const long long th = pair / half;  // token*H + head
     const long long tok = th / H;
     const size_t base = static_cast<size_t>(th) * D;
-    float a[N], b[N], oa[N], ob[N];
+    float a[N], b[N], oa[N], ob[N], cs[N], sn[N];
     load_vec(x + base + j, a);
     load_vec(x + base + half + j, b);
+    // the tables are fp32 [T][D/2] and j is a multiple of N >= 4: 16-byte loads
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+      const float4 c4 = *reinterpret_cast<const float4*>(cos_t + tok * half + j + i);
+      const float4 s4 = *reinterpret_cast<const float4*>(sin_t + tok * half + j + i);
+      cs[i] = c4.x; cs[i + 1] = c4.y; cs[i + 2] = c4.z; cs[i + 3] = c4.w;
+      sn[i] = s4.x; sn[i + 1] = s4.y; sn[i + 2] = s4.z; sn[i + 3] = s4.w;
+    }
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-      const float c = cos_t[tok * half + j + i], s = sin_sign * sin_t[tok * half + j + i];
+      const float c = cs[i], s = sin_sign * sn[i];
       oa[i] = a[i] * c - b[i] * s;
       ob[i] = b[i] * c + a[i] * s;
     }
@@ -479,6 +538,18 @@ extern "C" int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
   const bool small = cols <= 512;
   const int rpb = small ? 8 : 1;
   const int grid = grid_for((rows + rpb - 1) / rpb, 1);
+  const int vec = 16 / esz;
+  if (!small && cols % (32 * vec) == 0 && cols / (32 * vec) <= 16 && esz == 2) {
+    const int wgrid = grid_for((rows + 7) / 8, 1);
+    RB_DISPATCH(dtype, {
+      const T *xx = (const T*)x, *rr = (const T*)res, *ww = (const T*)w;
+      T *yy = (T*)y, *ro = (T*)r_out;
+      if (res) rmsnorm_fwd_warp_kernel<T, true><<<wgrid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+      else rmsnorm_fwd_warp_kernel<T, false><<<wgrid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+    });
+    rb_note_launch(1);
+    return (int)cudaGetLastError();
+  }
   RB_DISPATCH(dtype, {
     const T *xx = (const T*)x, *rr = (const T*)res, *ww = (const T*)w;
     T *yy = (T*)y, *ro = (T*)r_out;
