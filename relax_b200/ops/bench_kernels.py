@@ -187,8 +187,39 @@ def bench_elementwise(args, pk):
         print(f"  {name:16s} {t * 1e3:7.1f} us {pk.bytes(byts / t / 1e6)}")
 
 
+def bench_train_step(args, pk):
+    """Kernel-time breakdown of one training micro-batch (forward + backward) of a few Qwen3-8B layers."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..algo.loss import LossConfig
+    from ..models.config import get_config
+    from ..train.actor import TrainActor, TrainConfig
+    from ..train.optimizer import OptimizerConfig
+
+    cfg = get_config("qwen3-8b", num_layers=args.layers)
+    actor = TrainActor(cfg, TrainConfig(max_tokens_per_gpu=args.tokens, pad_multiple=128, loss=LossConfig(eps_clip=0.2),
+                                        optim=OptimizerConfig(lr=1e-6, grad_dtype="fp32")), device="cuda", seed=0)
+    n = max(1, args.tokens // args.seq_len)
+    toks = [torch.randint(0, 150000, (args.seq_len,)).tolist() for _ in range(n)]
+    pb = actor._pack(toks, [args.seq_len - 512] * n)
+
+    def step():
+        lp, en = actor._forward_logp(pb, True)
+        (lp.sum() + 0.01 * en.sum()).backward()
+
+    t = _timeit(step, args.iters, args.warmup)
+    print(f"== training micro-batch, {n} x {args.seq_len} tokens, {args.layers} layers + LM head: {t:.2f} ms forward + backward")
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    ev = prof.key_averages()
+    tot = sum(r.device_time_total for r in ev)
+    for r in sorted(ev, key=lambda r: -r.device_time_total)[:16]:
+        print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:96]}")
+
+
 SECTIONS = {"gemm": bench_gemm, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
-            "elementwise": bench_elementwise}
+            "elementwise": bench_elementwise, "train_step": bench_train_step}
 
 
 def main():
@@ -199,12 +230,13 @@ def main():
     ap.add_argument("--batch", type=int, default=80, help="decode batch")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=4, help="transformer layers of the train_step section")
     ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
     args = ap.parse_args()
     pk = _Peaks(args.peaks)
     torch.manual_seed(0)
     for name, fn in SECTIONS.items():
-        if args.only in (None, name):
+        if args.only == name or (args.only is None and name != "train_step"):
             fn(args, pk)
 
 
