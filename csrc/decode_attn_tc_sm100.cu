@@ -28,12 +28,12 @@ constexpr int DT_STAGES = 3;
 constexpr int DT_SMEM_K = 0;                                 // DT_STAGES stages
 constexpr int DT_SMEM_V = DT_SMEM_K + DT_STAGES * DT_KV_BYTES;
 constexpr int DT_SMEM_Q = DT_SMEM_V + DT_STAGES * DT_KV_BYTES;  // [2 halves][16 rows][128 B]
-constexpr int DT_SMEM_P = DT_SMEM_Q + 4096;                  // [2 halves][16 rows][128 B]
-constexpr int DT_SMEM_BAR = DT_SMEM_P + 4096;
+constexpr int DT_SMEM_P = DT_SMEM_Q + 4096;                  // 2 buffers x [2 halves][16 rows][128 B]
+constexpr int DT_SMEM_BAR = DT_SMEM_P + 2 * 4096;
 constexpr int DT_SMEM_RED = DT_SMEM_BAR + 256;               // float [4 warps][16] max + [4][16] sums
 constexpr int DT_SMEM_TOTAL = DT_SMEM_RED + 1024;
 constexpr int DT_TMEM_COLS = 64;
-constexpr int DT_T_S = 0;
+constexpr int DT_T_S = 0;    // two buffers of 16 columns
 constexpr int DT_T_O = 32;
 
 struct DecodeTcParams {
@@ -53,10 +53,12 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
                       const DecodeTcParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DT_SMEM_BAR);
-  uint64_t* bar_s = bars + 0;
-  uint64_t* bar_p = bars + 1;
-  uint64_t* bar_o = bars + 2;
-  uint64_t* kfull = bars + 3;                    // [DT_STAGES]
+  // S, P and the "PV done" signal are double buffered (index = tile & 1) so that the softmax of tile j+1
+  // overlaps the V^T P product of tile j; one barrier per buffer keeps every parity wait unambiguous.
+  uint64_t* bar_s = bars + 0;                    // [2]
+  uint64_t* bar_p = bars + 2;                    // [2]
+  uint64_t* bar_o = bars + 4;                    // [2]
+  uint64_t* kfull = bars + 6;                    // [DT_STAGES]
   uint64_t* vfull = kfull + DT_STAGES;           // [DT_STAGES]
   uint64_t* kvempty = vfull + DT_STAGES;         // [DT_STAGES]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kvempty + DT_STAGES);
@@ -74,9 +76,11 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
   const int* bt = p.block_tables + static_cast<size_t>(b) * p.max_blocks;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_p[i], 128);
+      mbar_init(&bar_o[i], 1);
+    }
     for (int s = 0; s < DT_STAGES; ++s) {
       mbar_init(&kfull[s], 1);
       mbar_init(&vfull[s], 1);
@@ -97,6 +101,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
     const int off = half * 2048 + row * 128 + ((c ^ (row & 7)) << 4);
     *reinterpret_cast<uint4*>(smem + DT_SMEM_Q + off) = v;
     *reinterpret_cast<uint4*>(smem + DT_SMEM_P + off) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(smem + DT_SMEM_P + 4096 + off) = make_uint4(0, 0, 0, 0);
   }
   fence_proxy_async();
   if (warp == 5) {
@@ -149,17 +154,17 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
         for (int kk = 0; kk < DT_D / 16; ++kk) {
           const uint64_t da = make_smem_desc(sk + (kk >> 2) * (DT_KV_BYTES / 2) + (kk & 3) * 32, 16, 1024, kSwizzle128B);
           const uint64_t db = make_smem_desc(sq + (kk >> 2) * 2048 + (kk & 3) * 32, 16, 1024, kSwizzle128B);
-          umma_f16(tmem_base + DT_T_S, da, db, id_s, kk > 0 ? 1u : 0u);
+          umma_f16(tmem_base + DT_T_S + (j & 1) * 16, da, db, id_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(bar_s);
+        umma_commit(&bar_s[j & 1]);
         return true;
       };
       bool ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % DT_STAGES;
-        if (!mbar_wait(bar_p, static_cast<uint32_t>(j) & 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&bar_p[j & 1], static_cast<uint32_t>(j >> 1) & 1, abort_flag, p.err)) break;
         tc_fence_after();
-        if (j + 1 < n_tiles && !issue_s(j + 1)) break;
         if (!mbar_wait(&vfull[s], static_cast<uint32_t>(j / DT_STAGES) & 1, abort_flag, p.err)) break;
         tc_fence_after();
         const uint32_t sv = smem_u32(smem + DT_SMEM_V + s * DT_KV_BYTES);
@@ -168,11 +173,13 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
           // A = V^T: M = d (two 64-wide chunks DT_KV_BYTES/2 apart), K = tokens (16 rows = 2048 bytes)
           const uint64_t da = make_smem_desc(sv + kk * 2048, DT_KV_BYTES / 2, 1024, kSwizzle128B);
           // B = P[16 heads][128 tokens], K-major, two 64-token halves 2048 bytes apart
-          const uint64_t db = make_smem_desc(sp + (kk >> 2) * 2048 + (kk & 3) * 32, 16, 1024, kSwizzle128B);
+          const uint64_t db = make_smem_desc(sp + (j & 1) * 4096 + (kk >> 2) * 2048 + (kk & 3) * 32, 16, 1024, kSwizzle128B);
           umma_f16(tmem_base + DT_T_O, da, db, id_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&kvempty[s]);
-        umma_commit(bar_o);
+        umma_commit(&bar_o[j & 1]);
+        // the S buffer of tile j was consumed before bar_p[j & 1] completed: refill it with tile j + 2
+        if (j + 2 < n_tiles && !issue_s(j + 2)) break;
       }
     }
   } else {
@@ -186,10 +193,10 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
     // Failure handling: a wait that runs out only clears `ok`; the loop keeps its shape so that all
     // 128 threads still meet at the named barriers (every later wait returns at once after an abort).
     for (int j = 0; j < n_tiles; ++j) {
-      if (ok) ok = mbar_wait(bar_s, static_cast<uint32_t>(j) & 1, abort_flag, p.err);
+      if (ok) ok = mbar_wait(&bar_s[j & 1], static_cast<uint32_t>(j >> 1) & 1, abort_flag, p.err);
       tc_fence_after();
       uint32_t raw[16];
-      tmem_ld_32x32b_x16(tmem_base + DT_T_S + lane_addr, raw);
+      tmem_ld_32x32b_x16(tmem_base + DT_T_S + (j & 1) * 16 + lane_addr, raw);
       tmem_wait_ld();
       const int tok = t_begin + j * DT_TILE + r;
       const bool valid = tok < t_end;
@@ -214,10 +221,13 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
           rescale = true;
         }
       }
-      if (j > 0) {   // the previous V^T P must be done before P is overwritten or O^T rescaled
-        if (ok) ok = mbar_wait(bar_o, static_cast<uint32_t>(j - 1) & 1, abort_flag, p.err);
+      if (j >= 2) {  // this P buffer was last read by the V^T P product of tile j - 2
+        if (ok) ok = mbar_wait(&bar_o[j & 1], static_cast<uint32_t>((j - 2) >> 1) & 1, abort_flag, p.err);
+      }
+      if (j > 0 && rescale) {   // O^T may only be rescaled once the product of tile j - 1 has landed (rare: lazy threshold)
+        if (ok) ok = mbar_wait(&bar_o[(j - 1) & 1], static_cast<uint32_t>((j - 1) >> 1) & 1, abort_flag, p.err);
         tc_fence_after();
-        if (rescale) {
+        {
           uint32_t o[16];
           tmem_ld_32x32b_x16(tmem_base + DT_T_O + lane_addr, o);
           tmem_wait_ld();
@@ -229,7 +239,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
       }
       // P[h][token r]: K-major [16 rows][128 tokens] as two 64-token halves
       const int half = r >> 6, col = r & 63;
-      uint8_t* prow = smem + DT_SMEM_P + half * 2048 + ((col & 7) << 1);
+      uint8_t* prow = smem + DT_SMEM_P + (j & 1) * 4096 + half * 2048 + ((col & 7) << 1);
 #pragma unroll
       for (int h = 0; h < 8; ++h) {
         if (h < G) {
@@ -241,9 +251,10 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
       named_bar_sync(1, 128);   // red_max may be rewritten by the next tile only after everyone has read it
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      mbar_arrive(&bar_p[j & 1]);
     }
-    if (ok && n_tiles > 0) ok = mbar_wait(bar_o, static_cast<uint32_t>(n_tiles - 1) & 1, abort_flag, p.err);
+    if (ok && n_tiles > 1) ok = mbar_wait(&bar_o[(n_tiles - 2) & 1], static_cast<uint32_t>((n_tiles - 2) >> 1) & 1, abort_flag, p.err);
+    if (ok && n_tiles > 0) ok = mbar_wait(&bar_o[(n_tiles - 1) & 1], static_cast<uint32_t>((n_tiles - 1) >> 1) & 1, abort_flag, p.err);
     tc_fence_after();
     // ---- total sums per head
 #pragma unroll
