@@ -99,6 +99,8 @@ int rb_fa_dq_convert(const float* dq_acc, void* dq, long long n, cudaStream_t st
 int rb_peer_barrier(unsigned* const* peer_sig, int* state, int n, int rank, int slot, int state_idx,
                     unsigned long long wait_ns, int* err, cudaStream_t st);
 int rb_peer_push(const void* src, void* const* dst, int n_dst, long long nbytes, cudaStream_t st);
+int rb_gemm_fp8_blockscaled(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,
+                            int lda, int ldb, int ldc, int* err, cudaStream_t stream);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

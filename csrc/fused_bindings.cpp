@@ -193,12 +193,30 @@ void peer_push(torch::Tensor src, std::vector<int64_t> dst_ptrs, int64_t offset_
   check(rb_peer_push(src.data_ptr(), d, (int)dst_ptrs.size(), (long long)src.numel() * src.element_size(), cur_stream()),
         "rb_peer_push");
 }
+
+// Block-scaled fp8 GEMM: a_q [M,K] e4m3 with a_scale [M, K/128]; b_q [N,K] e4m3 with b_scale [N/128, K/128]; out bf16.
+void gemm_fp8(torch::Tensor a_q, torch::Tensor a_scale, torch::Tensor b_q, torch::Tensor b_scale, torch::Tensor out,
+              torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(a_q.device());
+  TORCH_CHECK(a_q.element_size() == 1 && b_q.element_size() == 1 && a_q.stride(1) == 1 && b_q.stride(1) == 1, "fp8 operands");
+  TORCH_CHECK(a_scale.scalar_type() == at::kFloat && b_scale.scalar_type() == at::kFloat && a_scale.is_contiguous() &&
+              b_scale.is_contiguous() && out.scalar_type() == at::kBFloat16 && out.stride(1) == 1);
+  const int M = (int)a_q.size(0), K = (int)a_q.size(1), N = (int)b_q.size(0);
+  const int kb = (K + 127) / 128;
+  TORCH_CHECK(a_scale.size(0) == M && a_scale.size(1) == kb && b_scale.size(0) == (N + 127) / 128 && b_scale.size(1) == kb,
+              "scale shapes: a [M, K/128], b [N/128, K/128]");
+  check(rb_gemm_fp8_blockscaled(a_q.data_ptr(), a_scale.data_ptr<float>(), b_q.data_ptr(), b_scale.data_ptr<float>(),
+                                out.data_ptr(), M, N, K, (int)a_q.stride(0), (int)b_q.stride(0), (int)out.stride(0),
+                                err.data_ptr<int>(), cur_stream()),
+        "rb_gemm_fp8_blockscaled");
+}
 }  // namespace
 
 void register_fused(pybind11::module_& m) {
   m.def("gemm_ar_plan", &gemm_ar_plan);
   m.def("ag_gemm", &ag_gemm);
   m.def("qkv_post", &qkv_post);
+  m.def("gemm_fp8", &gemm_fp8);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_push", &peer_push);
   m.def("fa_bwd_ex", &fa_bwd_ex);

@@ -149,6 +149,16 @@ def linear_swiglu(x, w):
     return swiglu(linear(x, w))
 
 
+def fp8_linear(x, w_q, w_scale_inv, block: int = 128):
+    """``x @ dequant(w_q, w_scale_inv)^T`` with block-scaled e4m3 operands (weights: one scale per ``block x block``
+    tile; activations quantised per row and ``block`` columns on the fly).  tcgen05 ``kind::f8f6f4`` on CUDA;
+    elsewhere the dequantised product."""
+    if _use_cuda(x) and block == 128:
+        return _cuda().fp8_linear(x, w_q, w_scale_inv)
+    w = blockwise_dequant_fp8(w_q, w_scale_inv, block, torch.float32)
+    return (x.float() @ w.float().t()).to(torch.bfloat16)
+
+
 def dgrad(dy, w):
     """dy[M,N] @ w[N,K] (input gradient of ``linear``)."""
     if _use_cuda(dy):

@@ -66,6 +66,23 @@ def bench_gemm(args, pk):
             print(f"  {name:8s} {label:24s} {t:7.3f} ms {pk.flops(fl / t)} | cuBLAS {tl:7.3f} ms {fl / tl:7.1f}")
 
 
+def bench_gemm_fp8(args, pk):
+    from .. import ops
+    from . import cuda as C
+
+    T, dev = args.tokens, "cuda"
+    print(f"== block-scaled fp8 GEMM (e4m3, 1x128 / 128x128 scales), {T} tokens: ours fp8 vs ours bf16")
+    for name, (N, K) in {"qkv": (6144, 4096), "gate_up": (24576, 4096), "down": (4096, 12288)}.items():
+        a = torch.randn(T, K, device=dev).bfloat16()
+        w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+        wq, ws = ops.blockwise_cast_to_fp8(w, 128)
+        aq, as_ = C.quantize_rows_fp8(a)
+        fl = 2 * T * N * K / 1e9
+        t8 = _timeit(lambda: C.fp8_linear(a, wq, ws, aq, as_), args.iters, args.warmup)
+        t16 = _timeit(lambda: C.matmul_nt(a, w), args.iters, args.warmup)
+        print(f"  {name:8s} fp8 {t8:7.3f} ms {fl / t8:7.1f} TFLOP/s | bf16 {t16:7.3f} ms {fl / t16:7.1f} TFLOP/s")
+
+
 def bench_attention(args, pk):
     from .. import ops
 
@@ -218,7 +235,7 @@ def bench_train_step(args, pk):
         print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:96]}")
 
 
-SECTIONS = {"gemm": bench_gemm, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
+SECTIONS = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
             "elementwise": bench_elementwise, "train_step": bench_train_step}
 
 

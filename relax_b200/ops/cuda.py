@@ -231,6 +231,29 @@ def qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache=None, v_ca
     return q, k, v
 
 
+def quantize_rows_fp8(x, block: int = 128):
+    """Per-row, per-``block`` columns e4m3 quantisation of activations: ``(q [M, K] float8_e4m3fn, scale [M, K/block])``
+    with ``x ~ q * scale``."""
+    M, K = x.shape
+    kb = (K + block - 1) // block
+    xp = torch.nn.functional.pad(x.float(), (0, kb * block - K)).view(M, kb, block)
+    scale = xp.abs().amax(-1).clamp_min(1e-12) / 448.0
+    q = (xp / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(M, kb * block)[:, :K].contiguous()
+    return q, scale.contiguous()
+
+
+def fp8_linear(x, w_q, w_scale_inv, x_q=None, x_scale=None):
+    """``x @ dequant(w_q)^T`` on the fp8 tensor cores with block scaling: weights are e4m3 with one scale per
+    128 x 128 block (``weight_scale_inv`` of :func:`blockwise_cast_to_fp8`), activations are quantised per row and
+    128 columns here unless given.  Output bf16."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x_q is None:
+        x_q, x_scale = quantize_rows_fp8(x2)
+    out = torch.empty(x2.shape[0], w_q.shape[0], dtype=torch.bfloat16, device=x.device)
+    _load().gemm_fp8(x_q, x_scale.float().contiguous(), w_q, w_scale_inv.float().contiguous(), out, err_flag(x.device))
+    return out.reshape(*x.shape[:-1], w_q.shape[0])
+
+
 class _LinearNN(torch.autograd.Function):
     """y = x @ b with b[K,N] row-major (used when the caller passes ``w.t()``)."""
 

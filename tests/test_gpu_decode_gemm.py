@@ -111,3 +111,28 @@ def test_single_rank_gemm_reduce_residual_rmsnorm(M, N, K):
         torch.testing.assert_close(h.float(), ref_h, atol=6e-2, rtol=2e-2)
         torch.testing.assert_close(y.float(), ref_y, atol=6e-2, rtol=2e-2)
     comm.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(128, 256, 256), (300, 384, 1024), (1024, 4096, 4096), (64, 512, 640)])
+def test_fp8_blockscaled_gemm(M, N, K):
+    """Block-scaled e4m3 GEMM against the fp32 product of the dequantised operands."""
+    from relax_b200 import ops
+    from relax_b200.ops import cuda as C
+
+    dev = "cuda"
+    torch.manual_seed(M + N + K)
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    wq, ws = ops.blockwise_cast_to_fp8(w, 128)
+    xq, xs = C.quantize_rows_fp8(x)
+    y = C.fp8_linear(x, wq, ws, xq, xs)
+    C.check_error_flag()
+    kb = (K + 127) // 128
+    xd = (torch.nn.functional.pad(xq.float(), (0, kb * 128 - K)).view(M, kb, 128) * xs.unsqueeze(-1)).view(M, -1)[:, :K]
+    wd = ops.blockwise_dequant_fp8(wq, ws, 128, torch.float32)
+    ref = xd @ wd.float().t()
+    torch.testing.assert_close(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+    # and the quantisation itself stays close to the bf16 product
+    full = x.float() @ w.float().t()
+    assert float((y.float() - full).abs().max()) < 0.12 * float(full.abs().max())
