@@ -185,7 +185,7 @@ def linear(x, w, bias=None):
 
 
 def matmul_nt_skinny(x, w, bias=None, residual=None):
-    """x[M<=128, K] @ w[N, K]^T for decode: when the N tiles alone cannot fill the SMs the
+    """x[M, K] @ w[N, K]^T for decode (a few hundred rows at most): when the N tiles alone cannot fill the SMs the
     reduction dimension is split across CTAs (fp32 partials in a workspace, one small reduce
     kernel that also adds bias / residual)."""
     x, _ = _rowmajor_2d(x)

@@ -7,7 +7,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("M,N,K", [(80, 4096, 12288), (1, 4096, 4096), (128, 6144, 4096), (37, 1024, 2048), (64, 24576, 4096)])
+@pytest.mark.parametrize("M,N,K", [(80, 4096, 12288), (1, 4096, 4096), (128, 6144, 4096), (37, 1024, 2048), (64, 24576, 4096),
+                                   (256, 3072, 4096), (300, 4096, 6144)])
 def test_skinny_linear_splitk(M, N, K):
     from relax_b200.ops import cuda as C
 
@@ -71,7 +72,7 @@ def test_qkv_post_matches_separate_kernels(norm, dense):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("M", [1, 48, 128])
+@pytest.mark.parametrize("M", [1, 48, 128, 256])
 def test_linear_swiglu_skinny(M):
     from relax_b200 import ops
 
