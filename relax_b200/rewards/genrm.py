@@ -1,6 +1,6 @@
-"""Generative reward model: a judge LLM reads the question, the reference answer and the policy's
+"""Generative reward model: a grader LLM reads the question, the reference answer and the policy's
 answer, writes a verdict, and the verdict is parsed into a score (relax/components/genrm.py,
-relax/distributed/ray/genrm.py, relax/utils/genrm_client.py, rule reward ``dapo_genrm``).  The judge
+relax/distributed/ray/genrm.py, relax/utils/genrm_client.py, rule reward ``dapo_genrm``).  The grader
 runs on its own engines; requests are spread round-robin, an engine that fails is skipped until
 ``recover`` brings it back, and unparsable verdicts score ``default``.
 """
@@ -20,7 +20,7 @@ _SCORE = re.compile(r"score\s*[:\-]\s*(-?\d+(?:\.\d+)?)(?:\s*/\s*(\d+(?:\.\d+)?)
 
 
 def parse_verdict(text: str, default: float = 0.0) -> float:
-    """Last verdict or score in the judge's text -> [0, 1]."""
+    """Last verdict or score in the grader's text -> [0, 1]."""
     v = _VERDICT.findall(text)
     if v:
         return 1.0 if v[-1].lower() in ("correct", "right", "yes") else 0.0

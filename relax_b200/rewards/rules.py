@@ -275,7 +275,7 @@ def remote_rm_reward(sample, url: Optional[str] = None, timeout: float = 30.0) -
 
 def make_dapo_genrm_reward(genrm):
     """DAPO scoring with a generative judge for the answers the rule cannot parse: rule says correct -> +1; rule finds
-    an answer and it is wrong -> -1; no parsable answer -> ask the judge (``relax_b200.rewards.genrm.GenRM``)."""
+    an answer and it is wrong -> -1; no parsable answer -> ask the generative grader (``relax_b200.rewards.genrm.GenRM``)."""
     def fn(sample) -> dict:
         base = dapo_reward(sample)
         if base.get("pred") not in (None, "", "[INVALID]"):
