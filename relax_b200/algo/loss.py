@@ -217,6 +217,15 @@ def sft_loss(log_probs: torch.Tensor, b: LossBatch, cfg: LossConfig):
     return loss, {"loss": loss.detach()}
 
 
+def seq_cls_loss(logits: torch.Tensor, labels: torch.Tensor):
+    """Sum over samples of the class cross entropy (the caller divides by the global batch size, as for the
+    other per-sample losses) and the number of correct predictions
+    (relax/backends/megatron/loss.py :1301-1383)."""
+    ce = torch.nn.functional.cross_entropy(logits.float(), labels.long(), reduction="sum")
+    acc = (logits.argmax(-1) == labels).float().sum()
+    return ce, {"loss": ce.detach(), "accuracy": acc}
+
+
 def scale_loss(loss, *, per_token: bool, num_microbatches: int, global_batch_size: int, dp_cp_world: int,
                num_tokens: Optional[torch.Tensor] = None, is_dummy: bool = False, explicit_scale: Optional[float] = None):
     """Scaling applied before backward so that the gradient AVERAGE over the

@@ -368,7 +368,8 @@ def model_config_from_args(a):
     m = [("num_layers", "num_layers"), ("hidden_size", "hidden_size"), ("ffn_hidden_size", "ffn_hidden_size"),
          ("num_attention_heads", "num_attention_heads"), ("num_query_groups", "num_query_groups"),
          ("kv_channels", "head_dim"), ("vocab_size", "vocab_size"), ("num_experts", "num_experts"),
-         ("moe_router_topk", "moe_top_k"), ("moe_ffn_hidden_size", "moe_ffn_hidden_size")]
+         ("moe_router_topk", "moe_top_k"), ("moe_ffn_hidden_size", "moe_ffn_hidden_size"),
+         ("mtp_num_layers", "mtp_num_layers")]
     for src, dst in m:
         v = getattr(a, src, None)
         if v is not None:
@@ -398,4 +399,6 @@ def train_config_from_args(a):
         normalize_advantages=a.normalize_advantages, rewards_normalization=a.rewards_normalization,
         grpo_std_normalization=a.grpo_std_normalization, balance_data=a.balance_data,
         recompute=a.recompute_granularity == "full", pad_multiple=a.data_pad_size_multiplier,
-        use_rollout_logprobs=a.use_rollout_logprobs, keep_old_actor=a.keep_old_actor, loss=loss, optim=optim)
+        use_rollout_logprobs=a.use_rollout_logprobs, keep_old_actor=a.keep_old_actor,
+        enable_mtp_training=a.enable_mtp_training, mtp_loss_scaling_factor=a.mtp_loss_scaling_factor,
+        mtp_only_training=a.mtp_only_training, loss=loss, optim=optim)

@@ -50,6 +50,9 @@ class ModelConfig:
     image_token_id: int = -1
     # value / classification head
     value_head: bool = False
+    num_classes: int = 0                  # >0: sequence-classification head on the last token
+    # multi-token prediction blocks after the trunk (0 = none)
+    mtp_num_layers: int = 0
     dtype: str = "bf16"
 
     @property

@@ -225,7 +225,7 @@ class GPTModel(nn.Module):
         tp = ps_.tp.size
         v_pad = (cfg.vocab_size + tp - 1) // tp * tp
         self.v_local, self.vocab_start = v_pad // tp, ps_.tp.rank * (v_pad // tp)
-        if self.pre_process or (self.post_process and cfg.tie_word_embeddings):
+        if self.pre_process or (self.post_process and (cfg.tie_word_embeddings or cfg.mtp_num_layers > 0)):
             self.embedding = nn.Module()
             self.embedding.word_embeddings = VocabParallelEmbedding(cfg, ps_, self.dtype, device, gen)
         self.decoder = nn.Module()
@@ -241,6 +241,18 @@ class GPTModel(nn.Module):
             if cfg.value_head:
                 self.value_head = nn.Module()
                 self.value_head.weight = nn.Parameter(torch.zeros(1, cfg.hidden_size, dtype=self.dtype, device=device))
+            if cfg.num_classes > 0:
+                self.score = nn.Module()
+                self.score.weight = nn.Parameter(
+                    gen.draw("score", (cfg.num_classes, cfg.hidden_size), 0.02).to(device=device, dtype=self.dtype))
+                self.score.weight.tp_replicated = True
+            if cfg.mtp_num_layers > 0:
+                from .mtp import MTPBlock
+
+                assert ps_.pp.size == 1 and ps_.cp.size == 1, "MTP blocks share the embedding: pp = cp = 1"
+                self.mtp = nn.Module()
+                self.mtp.layers = nn.ModuleList(
+                    [MTPBlock(cfg, ps_, self.dtype, device, gen, k) for k in range(cfg.mtp_num_layers)])
 
         for n, p in self.named_parameters():
             if any(k in n for k in ("layernorm", "layer_norm", "router", "value_head")) or n.endswith(".bias") and "linear_proj" in n:
@@ -257,7 +269,7 @@ class GPTModel(nn.Module):
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens=None, positions=None, cu_seqlens=None, hidden_in=None, attn_fn=None,
-                inputs_embeds=None, max_seqlen=None):
+                inputs_embeds=None, max_seqlen=None, return_prenorm: bool = False):
         """tokens ``[T]`` (T divisible by tp when sequence-parallel).  Returns the
         normalised final hidden ``[T, H]`` on the last pipeline stage, else the
         stage output (sequence-parallel shard)."""
@@ -276,9 +288,12 @@ class GPTModel(nn.Module):
                 h = layer(h, cos, sin, cu_seqlens, attn_fn, max_seqlen)
         if not self.post_process:
             return h
+        prenorm = h
         h = ops.rmsnorm(h, self.decoder.final_layernorm.weight, self.cfg.rms_norm_eps)
         if sp:
             h = TP.gather_seq(h, self.ps.tp)
+        if return_prenorm:   # the MTP blocks continue from the un-normalised stream (sequence-parallel shard)
+            return h, prenorm
         return h
 
     def logits(self, hidden):
@@ -297,6 +312,12 @@ class GPTModel(nn.Module):
         if not self.sequence_parallel:
             hidden = TP.copy_to_tp(hidden, self.ps.tp)
         return ops.fused_lm_head_logprob(hidden, w, targets, self.ps.tp.group, self.vocab_start, with_entropy, temperature)
+
+    def class_logits(self, hidden):
+        """Sequence-classification logits ``[rows, num_classes]`` from the given (last-token) hidden rows."""
+        if self.sequence_parallel:
+            hidden = _ScaleGrad.apply(hidden, 1.0 / self.ps.tp.size)
+        return ops.linear(hidden, self.score.weight).float()
 
     def values(self, hidden):
         """Scalar value per row (critic).  The head is replicated over TP, so

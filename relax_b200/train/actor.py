@@ -53,8 +53,22 @@ class TrainConfig:
     compute_entropy: bool = True
     ref_on_host: bool = False           # keep the frozen reference weights in pinned host memory
     lora: Optional[object] = None       # a train.lora.LoRAConfig: train adapters only
+    enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
+    mtp_loss_scaling_factor: float = 0.1
+    mtp_only_training: bool = False     # freeze the trunk, train the MTP blocks alone
     loss: L.LossConfig = field(default_factory=L.LossConfig)
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
+
+
+def _shift_mask(mask: torch.Tensor, response_lengths: Sequence[int], k: int) -> torch.Tensor:
+    """``out[j] = mask[j + k]`` inside each sample's response span, 0 past its end."""
+    out = torch.zeros_like(mask)
+    o = 0
+    for R in response_lengths:
+        if R > k:
+            out[o:o + R - k] = mask[o + k:o + R]
+        o += R
+    return out
 
 
 class TrainActor:
@@ -69,6 +83,9 @@ class TrainActor:
             from .lora import apply_lora
 
             apply_lora(self.model, cfg.lora)
+        if cfg.mtp_only_training:
+            for n, p in self.model.named_parameters():
+                p.requires_grad_(n.startswith("mtp."))
         self.optimizer = DistributedOptimizer(self.model, self.ps, cfg.optim) if with_optimizer else None
         self.timer = Timer()
         self.weight_version = 0
@@ -185,6 +202,36 @@ class TrainActor:
         h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
         hr = h.index_select(0, pb.logit_rows)
         return self.model.log_probs(hr, pb.targets, self.cfg.rollout_temperature, with_entropy)
+
+    def _forward_logp_mtp(self, pb, with_entropy: bool, lb):
+        """Main-head log-probs plus the MTP loss of this micro-batch: depth ``k`` at the row that predicts
+        response position ``j`` is trained on position ``j + k`` with that position's loss mask; the depths are
+        averaged and scaled by ``mtp_loss_scaling_factor`` (Megatron's MTP loss scaling)."""
+        from dataclasses import replace as _replace
+
+        from ..models.mtp import mtp_forward
+
+        cfg = self.cfg
+        if cfg.mtp_only_training:
+            with torch.no_grad():
+                h, pre = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen, return_prenorm=True)
+        else:
+            h, pre = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen, return_prenorm=True)
+        lp, en = self.model.log_probs(h.index_select(0, pb.logit_rows), pb.targets, cfg.rollout_temperature, with_entropy)
+        depths = mtp_forward(self.model, pre, pb.tokens, pb.positions, pb.cu_seqlens, pb.logit_rows, pb.max_seqlen)
+        total = lp.new_zeros(())
+        for k, (lpk, valid) in enumerate(depths, start=1):
+            mk = _shift_mask(lb.loss_mask, pb.response_lengths, k) * valid.to(lb.loss_mask.dtype)
+            lk, _ = L.sft_loss(lpk, _replace(lb, loss_mask=mk, sample_denoms=None), cfg.loss)
+            total = total + lk
+        return lp, en, total * (cfg.mtp_loss_scaling_factor / max(1, len(depths)))
+
+    def _forward_class_logits(self, pb):
+        """One row of class logits per sample, read at its last real token
+        (relax/backends/megatron/loss.py sequence-classification loss :1301-1383)."""
+        h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+        last = pb.cu_seqlens[1:1 + len(pb.response_lengths)].to(torch.int64) - 1
+        return self.model.class_logits(h.index_select(0, last))
 
     def _forward_values(self, pb):
         """Critic: one scalar per response position (the hidden state that predicts token t+1 also carries V(s_t))."""
@@ -356,15 +403,27 @@ class TrainActor:
             ids = [idx[j] for j in mb]
             pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
             lb = self._loss_batch(batch, ids, pb)
+            use_mtp = (cfg.enable_mtp_training or cfg.mtp_only_training) and self.mcfg.mtp_num_layers > 0
             if self.role == "critic":
                 loss, m = L.value_loss(self._forward_values(pb), lb, cfg.loss)
+            elif self.role == "seq_cls":
+                labels = torch.as_tensor([batch["labels"][i] for i in ids], device=self.device)
+                loss, m = L.seq_cls_loss(self._forward_class_logits(pb), labels)
+            elif use_mtp:
+                lp, en, mtp = self._forward_logp_mtp(pb, cfg.compute_entropy and self.role != "sft", lb)
+                if cfg.mtp_only_training:
+                    loss, m = mtp, {"loss": mtp.detach()}
+                else:
+                    loss, m = L.sft_loss(lp, lb, cfg.loss) if self.role == "sft" else L.policy_loss(lp, en, lb, cfg.loss)
+                    loss = loss + mtp
+                m["mtp_loss"] = mtp.detach()
             elif self.role == "sft":
                 lp, _ = self._forward_logp(pb, False)
                 loss, m = L.sft_loss(lp, lb, cfg.loss)
             else:
                 lp, en = self._forward_logp(pb, cfg.compute_entropy)
                 loss, m = L.policy_loss(lp, en, lb, cfg.loss)
-            ntok += lb.loss_mask.sum()
+            ntok += lb.loss_mask.sum() if lb.loss_mask is not None else float(len(ids))
             if cfg.loss.calculate_per_token_loss:
                 scaled = loss
             else:
@@ -402,6 +461,25 @@ class TrainActor:
         rollout-time ``values`` and the GAE ``returns`` computed with them; clipped value loss."""
         assert self.role == "critic"
         return self._optimizer_steps(batch)
+
+    def train_seq_cls(self, batch: dict) -> dict:
+        """Sequence-classification fine-tuning: cross entropy of the class head at each sample's last token
+        against ``batch["labels"]``; metrics carry the accuracy."""
+        assert self.role == "seq_cls" and self.mcfg.num_classes > 0
+        return self._optimizer_steps(batch)
+
+    @torch.no_grad()
+    def predict_classes(self, batch: dict) -> list:
+        out = [None] * len(batch["tokens"])
+        lens = [len(t) for t in batch["tokens"]]
+        for mb in self._microbatches(lens, for_train=False):
+            if not mb:
+                self._dummy_forward()
+                continue
+            pb = self._pack([batch["tokens"][i] for i in mb], [batch["response_lengths"][i] for i in mb])
+            for i, row in zip(mb, self._forward_class_logits(pb)):
+                out[i] = row
+        return out
 
     def train_sft(self, batch: dict) -> dict:
         """Supervised step(s): next-token cross entropy over the positions with ``loss_masks`` 1
