@@ -68,6 +68,9 @@ class ColocateConfig:
     fused_tp: bool = True
     fused_workspace_mb: int = 512
     num_prompts: int = 1 << 14
+    # directory for per-step rollout dumps (rollout_<id>.jsonl, read by relax_b200.utils.visualize); engine-replica
+    # rank 0 of data-parallel rank 0 writes its own samples
+    save_debug_rollout_data: Optional[str] = None
 
 
 class ColocatedGRPO:
@@ -180,6 +183,10 @@ class ColocatedGRPO:
             samples = self.generate(rid)
             if cfg.offload_rollout:
                 self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
+            if cfg.save_debug_rollout_data and self.ps.rank == 0:
+                from ..utils.visualize import dump_rollout
+
+                dump_rollout(cfg.save_debug_rollout_data, rid, samples, extra={"weight_version": self.actor.weight_version})
         with self.timer.span("data"):
             batch = convert_samples_to_train_data(
                 samples, advantage_estimator=cfg.train.advantage_estimator,

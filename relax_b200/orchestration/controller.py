@@ -79,7 +79,8 @@ class Controller:
                 kv_blocks=_get(a, "kv_blocks", max(64, a.rollout_batch_size * a.n_samples_per_prompt * (ctx // 16 + 2))),
                 kv_block_size=page if page > 1 else 16,
                 max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
-                offload_rollout=a.offload_rollout, offload_train=a.offload_train)
+                offload_rollout=a.offload_rollout, offload_train=a.offload_train,
+                save_debug_rollout_data=_get(a, "save_debug_rollout_data", None))
             return ColocatedGRPO(cfg, device=self.device)
         if self.mode == "sft":
             from ..train.actor import TrainActor
