@@ -200,6 +200,10 @@ def load_hf_checkpoint(directory: str, dequantize: bool = True, dtype=None) -> d
 
     from .. import ops
 
+    if "://" in directory:   # object-store or file:// source: mirrored once per node, then read locally
+        from ..utils.model_source import resolve_model_path
+
+        directory = resolve_model_path(directory, local_rank=int(os.environ.get("LOCAL_RANK", "0")))
     files = sorted(f for f in os.listdir(directory) if f.endswith(".safetensors"))
     if not files:
         raise FileNotFoundError(f"no .safetensors files in {directory}")
