@@ -176,12 +176,28 @@ def vision_config_from_model(mc) -> VisionConfig:
 class VLModel(nn.Module):
     """Language model + vision encoder.  ``forward`` returns the final hidden states like ``GPTModel.forward``."""
 
-    def __init__(self, lm, vision: VisionEncoder, image_token_id: int):
+    def __init__(self, lm, vision: VisionEncoder, image_token_id: int, branch_sync=None):
         super().__init__()
         self.lm, self.vision, self.image_token_id = lm, vision, image_token_id
+        # a parallel.collective_utils.ConditionalBranchSync over the data-parallel group: when only some ranks
+        # have images in a micro-batch the others run the tower on one placeholder window (times zero), so the
+        # gradient reduction sees the vision parameters on every rank
+        self.branch_sync = branch_sync
+
+    def _dummy_vision(self):
+        m = self.vision.cfg.spatial_merge_size
+        p = torch.zeros(m * m, self.vision.cfg.patch_dim, dtype=self.vision.patch_embed.dtype, device=self.vision.patch_embed.device)
+        return self.vision(p, torch.tensor([[1, m, m]], device=p.device)).sum()
 
     def forward(self, tokens, positions, cu_seqlens, pixel_patches=None, grid_thw=None, max_seqlen=None):
         emb = self.lm.embedding.word_embeddings(tokens, False)
-        if pixel_patches is not None and pixel_patches.numel():
+        has = pixel_patches is not None and pixel_patches.numel() > 0
+        if self.branch_sync is not None and torch.is_grad_enabled():
+            r = self.branch_sync.run(has, lambda: self.vision(pixel_patches, grid_thw), self._dummy_vision)
+            if has:
+                emb = merge_image_embeddings(emb, r, tokens, self.image_token_id)
+            elif r is not None:
+                emb = emb + r.to(emb.dtype)
+        elif has:
             emb = merge_image_embeddings(emb, self.vision(pixel_patches, grid_thw), tokens, self.image_token_id)
         return self.lm(tokens, positions, cu_seqlens, inputs_embeds=emb, max_seqlen=max_seqlen)

@@ -66,3 +66,23 @@ def test_vl_forward_backward_reaches_vision_weights():
     assert model.vision.patch_embed.grad.abs().sum() > 0 and model.vision.blocks[0].qkv.grad.abs().sum() > 0
     with pytest.raises(ValueError):
         merge_image_embeddings(torch.zeros(9, 4), torch.zeros(3, 4), tokens, IMG)
+
+
+def test_vision_branch_runs_as_dummy_when_only_peers_have_images():
+    """The conditional-branch agreement makes a rank without images still produce (zero) vision gradients."""
+    from relax_b200.models.vision import VLModel, VisionConfig, VisionEncoder
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+
+    class PeersHaveImages:            # stands in for the all-reduce MAX over the data-parallel group
+        def run(self, active, branch, dummy):
+            return branch() if active else dummy() * 0.0
+
+    cfg = get_config("tiny", image_token_id=7)
+    vc = VisionConfig(depth=1, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=2, out_hidden_size=cfg.hidden_size)
+    vl = VLModel(GPTModel(cfg, seed=0), VisionEncoder(vc), 7, branch_sync=PeersHaveImages())
+    toks = torch.tensor([3, 4, 5, 6])
+    h = vl(toks, torch.arange(4), torch.tensor([0, 4], dtype=torch.int32))
+    h.sum().backward()
+    g = vl.vision.patch_embed.grad
+    assert g is not None and float(g.abs().sum()) == 0.0
