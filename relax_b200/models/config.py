@@ -53,6 +53,21 @@ class ModelConfig:
     num_classes: int = 0                  # >0: sequence-classification head on the last token
     # multi-token prediction blocks after the trunk (0 = none)
     mtp_num_layers: int = 0
+    # hybrid stacks: every `linear_attention_freq`-th layer is softmax attention, the others Gated DeltaNet (0 = all softmax)
+    linear_attention_freq: int = 0
+    gdn_k_heads: int = 2
+    gdn_v_heads: int = 4
+    gdn_head_dim: int = 32
+    # DeepSeek-style sparse MLA attention in every layer when dsa_topk > 0
+    dsa_topk: int = 0
+    dsa_q_lora: int = 64
+    dsa_kv_lora: int = 32
+    dsa_nope: int = 16
+    dsa_rope: int = 8
+    dsa_v_head: int = 16
+    dsa_index_heads: int = 4
+    dsa_index_dim: int = 16
+    dsa_indexer_loss_coef: float = 1.0
     dtype: str = "bf16"
 
     @property
@@ -99,6 +114,10 @@ _reg(ModelConfig(name="tiny", num_layers=2, hidden_size=256, num_attention_heads
 _reg(ModelConfig(name="tiny-moe", num_layers=2, hidden_size=256, num_attention_heads=4, num_query_groups=2,
                  head_dim=64, ffn_hidden_size=688, vocab_size=1024, num_experts=8, moe_top_k=2,
                  moe_ffn_hidden_size=128, dtype="fp32"))
+_reg(ModelConfig(name="tiny-next", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
+                 ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, dtype="fp32"))
+_reg(ModelConfig(name="tiny-dsa", num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=4, head_dim=32,
+                 ffn_hidden_size=256, vocab_size=512, dsa_topk=8, dtype="fp32"))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,

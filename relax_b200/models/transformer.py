@@ -148,7 +148,11 @@ class TransformerLayer(nn.Module):
     def __init__(self, cfg, ps, dtype, device, gen, layer_idx):
         super().__init__()
         self.cfg = cfg
-        self.self_attention = Attention(cfg, ps, dtype, device, gen, layer_idx)
+        from .hybrid import DSAMixer, GDNMixer, mixer_kind
+
+        kind = mixer_kind(cfg, layer_idx)
+        mixer = {"attention": Attention, "gdn": GDNMixer, "dsa": DSAMixer}[kind]
+        self.self_attention = mixer(cfg, ps, dtype, device, gen, layer_idx)
         if cfg.is_moe and (layer_idx % cfg.moe_layer_freq == 0):
             from .moe import MoEMLP
 
@@ -281,6 +285,9 @@ class GPTModel(nn.Module):
         else:
             h = hidden_in
         cos, sin = self.rope_tables(positions)
+        if self.cfg.dsa_topk > 0:
+            for layer in self.decoder.layers:
+                layer.self_attention.positions = positions
         for layer in self.decoder.layers:
             if self.recompute and torch.is_grad_enabled():
                 h = checkpoint(layer, h, cos, sin, cu_seqlens, attn_fn, max_seqlen, use_reentrant=False)

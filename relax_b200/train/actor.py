@@ -423,6 +423,13 @@ class TrainActor:
             else:
                 lp, en = self._forward_logp(pb, cfg.compute_entropy)
                 loss, m = L.policy_loss(lp, en, lb, cfg.loss)
+            if self.mcfg.dsa_topk > 0:
+                from ..models.hybrid import collect_indexer_loss
+
+                aux = collect_indexer_loss(self.model)
+                if aux is not None:     # per micro-batch mean; weighted like one sample per packed sequence
+                    loss = loss + aux * (self.mcfg.dsa_indexer_loss_coef * len(ids))
+                    m["indexer_loss"] = aux.detach() * len(ids)
             ntok += lb.loss_mask.sum() if lb.loss_mask is not None else float(len(ids))
             if cfg.loss.calculate_per_token_loss:
                 scaled = loss

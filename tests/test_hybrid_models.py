@@ -1,0 +1,63 @@
+"""Hybrid stacks: GDN / full-attention interleave (Qwen3-Next style) and DSA attention (GLM-MoE-DSA style) in the
+trainer (CPU, tiny presets)."""
+import pytest
+import torch
+
+from relax_b200.algo.loss import LossConfig
+from relax_b200.models.config import get_config
+from relax_b200.models.hybrid import DSAMixer, GDNMixer, mixer_kind
+from relax_b200.models.transformer import Attention, GPTModel
+from relax_b200.train.actor import TrainActor, TrainConfig
+from relax_b200.train.optimizer import OptimizerConfig
+
+
+def _batch():
+    toks = [[5, 6, 7, 8, 9, 10, 11, 12, 13, 14], [11, 12, 13, 14, 15, 16, 17]]
+    rl = [6, 4]
+    return {"tokens": toks, "response_lengths": rl, "loss_masks": [[1.0] * r for r in rl]}
+
+
+def _cfg():
+    return TrainConfig(global_batch_size=2, max_tokens_per_gpu=64, pad_multiple=1, loss=LossConfig(),
+                       optim=OptimizerConfig(lr=3e-3, weight_decay=0.0))
+
+
+def test_layer_kinds():
+    nxt = get_config("tiny-next")
+    assert [mixer_kind(nxt, i) for i in range(4)] == ["gdn", "gdn", "gdn", "attention"]
+    m = GPTModel(nxt, seed=0)
+    kinds = [type(l.self_attention) for l in m.decoder.layers]
+    assert kinds == [GDNMixer, GDNMixer, GDNMixer, Attention]
+    d = GPTModel(get_config("tiny-dsa"), seed=0)
+    assert all(isinstance(l.self_attention, DSAMixer) for l in d.decoder.layers)
+
+
+def test_packed_sequences_do_not_leak_in_hybrid_stack():
+    m = GPTModel(get_config("tiny-next"), seed=1)
+    a, b = torch.arange(9) + 3, torch.arange(6) + 40
+    toks = torch.cat([a, b])
+    pos = torch.cat([torch.arange(9), torch.arange(6)])
+    with torch.no_grad():
+        both = m(toks, pos, torch.tensor([0, 9, 15], dtype=torch.int32))
+        alone = m(b, torch.arange(6), torch.tensor([0, 6], dtype=torch.int32))
+    assert torch.allclose(both[9:], alone, atol=1e-4)
+
+
+@pytest.mark.parametrize("preset", ["tiny-next", "tiny-dsa"])
+def test_sft_learns(preset):
+    torch.manual_seed(0)
+    actor = TrainActor(get_config(preset), _cfg(), role="sft")
+    b = _batch()
+    before = actor.evaluate_ppl(b)["eval/nll"]
+    for _ in range(8):
+        m = actor.train_sft(b)
+    assert actor.evaluate_ppl(b)["eval/nll"] < before - 0.3
+    if preset == "tiny-dsa":
+        assert "indexer_loss" in m and m["indexer_loss"] >= 0
+
+
+def test_rollout_engine_refuses_hybrid_stacks():
+    from relax_b200.rollout.weights import RolloutWeights
+
+    with pytest.raises(NotImplementedError):
+        RolloutWeights(get_config("tiny-next"), 1, 0, "cpu", torch.float32)
