@@ -28,6 +28,12 @@ def strip_prefix(name: str) -> str:
     return name
 
 
+def _shared(cfg: ModelConfig) -> str:
+    """HF module name of the shared expert: Qwen2-MoE / Qwen3-Next say ``shared_expert`` (and gate it), DeepSeek-V3 /
+    GLM4-MoE say ``shared_experts``."""
+    return "mlp.shared_expert" if cfg.moe_shared_expert_gate else "mlp.shared_experts"
+
+
 def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
     """One Megatron tensor -> list of ``(hf_name, tensor)``."""
     name = strip_prefix(name)
@@ -64,9 +70,15 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
         "pre_mlp_layernorm.weight": "post_attention_layernorm.weight",
         "mlp.linear_fc2.weight": "mlp.down_proj.weight",
         "mlp.router.weight": "mlp.gate.weight",
+        "mlp.router.expert_bias": "mlp.gate.e_score_correction_bias",
+        "mlp.shared_experts.linear_fc2.weight": _shared(cfg) + ".down_proj.weight",
+        "mlp.shared_experts.gate_weight": "mlp.shared_expert_gate.weight",
     }
     if rest in simple:
         return [(pre + simple[rest], p)]
+    if rest == "mlp.shared_experts.linear_fc1.weight":
+        g, u = p.chunk(2, 0)
+        return [(pre + _shared(cfg) + ".gate_proj.weight", g), (pre + _shared(cfg) + ".up_proj.weight", u)]
     if rest == "mlp.linear_fc1.weight":
         g, u = p.chunk(2, 0)
         return [(pre + "mlp.gate_proj.weight", g), (pre + "mlp.up_proj.weight", u)]
@@ -115,9 +127,17 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
         if cfg.qk_layernorm:
             out[b + "self_attention.q_layernorm.weight"] = hf[pre + "self_attn.q_norm.weight"]
             out[b + "self_attention.k_layernorm.weight"] = hf[pre + "self_attn.k_norm.weight"]
-        if cfg.is_moe and i % cfg.moe_layer_freq == 0:
+        if cfg.is_moe_layer(i):
             out[b + "pre_mlp_layernorm.weight"] = hf[pre + "post_attention_layernorm.weight"]
             out[b + "mlp.router.weight"] = hf[pre + "mlp.gate.weight"]
+            if cfg.moe_router_bias:
+                out[b + "mlp.router.expert_bias"] = hf[pre + "mlp.gate.e_score_correction_bias"]
+            if cfg.moe_shared_expert_ffn > 0:
+                sh = pre + _shared(cfg)
+                out[b + "mlp.shared_experts.linear_fc1.weight"] = torch.cat([hf[sh + ".gate_proj.weight"], hf[sh + ".up_proj.weight"]], 0)
+                out[b + "mlp.shared_experts.linear_fc2.weight"] = hf[sh + ".down_proj.weight"]
+                if cfg.moe_shared_expert_gate:
+                    out[b + "mlp.shared_experts.gate_weight"] = hf[pre + "mlp.shared_expert_gate.weight"]
             out[b + "mlp.experts.linear_fc1.weight"] = torch.stack(
                 [torch.cat([hf[pre + f"mlp.experts.{e}.gate_proj.weight"], hf[pre + f"mlp.experts.{e}.up_proj.weight"]], 0)
                  for e in range(cfg.num_experts)])
@@ -131,7 +151,7 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
 
 
 def hf_config_dict(cfg: ModelConfig) -> dict:
-    arch = "Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_layernorm else "Qwen2ForCausalLM")
+    arch = "DeepseekV3ForCausalLM" if (cfg.is_moe and cfg.moe_router_score == "sigmoid") else "Qwen3MoeForCausalLM" if cfg.is_moe else ("Qwen3ForCausalLM" if cfg.qk_layernorm else "Qwen2ForCausalLM")
     d = {"architectures": [arch], "hidden_size": cfg.hidden_size, "num_hidden_layers": cfg.num_layers,
          "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_query_groups,
          "head_dim": cfg.head_dim, "intermediate_size": cfg.ffn_hidden_size, "vocab_size": cfg.vocab_size,
@@ -140,6 +160,12 @@ def hf_config_dict(cfg: ModelConfig) -> dict:
     if cfg.is_moe:
         d.update(num_experts=cfg.num_experts, num_experts_per_tok=cfg.moe_top_k, moe_intermediate_size=cfg.moe_ffn_hidden_size,
                  norm_topk_prob=cfg.moe_router_norm_topk_prob)
+        if cfg.moe_shared_expert_ffn > 0:
+            d.update(n_shared_experts=1, shared_expert_intermediate_size=cfg.moe_shared_expert_ffn)
+        if cfg.moe_first_dense_layers:
+            d.update(first_k_dense_replace=cfg.moe_first_dense_layers)
+        if cfg.moe_router_score == "sigmoid":
+            d.update(scoring_func="sigmoid", routed_scaling_factor=cfg.moe_routed_scaling_factor, n_routed_experts=cfg.num_experts)
     return d
 
 

@@ -44,6 +44,13 @@ class ModelConfig:
     moe_router_norm_topk_prob: bool = True
     moe_aux_loss_coef: float = 0.0
     moe_layer_freq: int = 1
+    moe_first_dense_layers: int = 0        # DeepSeek-V3 / GLM4-MoE: the first k layers keep a dense MLP
+    moe_shared_expert_ffn: int = 0         # >0: an always-on shared expert of this width beside the routed ones
+    moe_shared_expert_gate: bool = False   # Qwen2-MoE / Qwen3-Next: shared output scaled by sigmoid(gate(x))
+    moe_router_score: str = "softmax"      # softmax | sigmoid (DeepSeek-V3 / GLM4-MoE)
+    moe_router_bias: bool = False          # selection-only per-expert bias, balanced without an auxiliary loss
+    moe_routed_scaling_factor: float = 1.0
+    moe_router_bias_update_rate: float = 1e-3
     # multimodal
     vision: Optional[VisionConfig] = None
     mrope_section: Optional[tuple] = None  # (t, h, w) halves of head_dim/2
@@ -73,6 +80,9 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    def is_moe_layer(self, layer_idx: int) -> bool:
+        return self.is_moe and layer_idx >= self.moe_first_dense_layers and layer_idx % self.moe_layer_freq == 0
 
     @property
     def q_size(self) -> int:
@@ -118,6 +128,10 @@ _reg(ModelConfig(name="tiny-next", num_layers=4, hidden_size=128, num_attention_
                  ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, dtype="fp32"))
 _reg(ModelConfig(name="tiny-dsa", num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=4, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, dsa_topk=8, dtype="fp32"))
+_reg(ModelConfig(name="tiny-dsv3", num_layers=3, hidden_size=256, num_attention_heads=4, num_query_groups=2,
+                 head_dim=64, ffn_hidden_size=688, vocab_size=1024, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=128,
+                 moe_first_dense_layers=1, moe_shared_expert_ffn=128, moe_router_score="sigmoid", moe_router_bias=True,
+                 moe_routed_scaling_factor=2.5, dtype="fp32"))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,

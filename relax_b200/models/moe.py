@@ -98,6 +98,23 @@ def grouped_swiglu_mlp(x, tokens_per_expert, w1, w2):
     return torch.cat(outs, 0)
 
 
+def route_tokens(logits, cfg, bias=None):
+    """``(weights [T, k], indices [T, k], scores [T, E])``.  Softmax routing is the fused top-k op.  Sigmoid routing
+    (DeepSeek-V3, GLM4-MoE): experts are *selected* on ``sigmoid(logits) + bias`` but *weighted* by the plain sigmoid
+    scores, renormalised over the selected set and multiplied by the routed scaling factor.  (Group-limited
+    selection, ``n_group`` / ``topk_group``, is not implemented: all experts form one group.)"""
+    if cfg.moe_router_score == "softmax":
+        w, idx, probs = ops.topk_router(logits, cfg.moe_top_k, cfg.moe_router_norm_topk_prob)
+        return (w * cfg.moe_routed_scaling_factor if cfg.moe_routed_scaling_factor != 1.0 else w), idx, probs
+    scores = torch.sigmoid(logits.float())
+    sel = scores if bias is None else scores + bias.float()[None, :]
+    idx = sel.topk(cfg.moe_top_k, dim=-1).indices
+    w = scores.gather(-1, idx)
+    if cfg.moe_router_norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * cfg.moe_routed_scaling_factor, idx, scores
+
+
 class MoEMLP(nn.Module):
     def __init__(self, cfg, ps: ParallelState, dtype, device, gen, layer_idx: int):
         super().__init__()
@@ -118,6 +135,43 @@ class MoEMLP(nn.Module):
         self.experts.linear_fc1.weight = nn.Parameter(w1[sl].to(dtype).contiguous())
         self.experts.linear_fc2.weight = nn.Parameter(w2[sl].to(dtype).contiguous())
         self.last_aux = None
+        self.last_counts = None
+        if cfg.moe_router_bias:
+            # selection-only bias: no gradient; moved by update_router_bias() towards an even load
+            self.router.expert_bias = nn.Parameter(torch.zeros(E, dtype=dtype, device=device), requires_grad=False)
+            self._bias_fp32 = torch.zeros(E, dtype=torch.float32, device=device)
+        Fs = cfg.moe_shared_expert_ffn
+        if Fs > 0:
+            self.shared_experts = nn.Module()
+            self.shared_experts.linear_fc1 = nn.Module()
+            self.shared_experts.linear_fc2 = nn.Module()
+            self.shared_experts.linear_fc1.weight = nn.Parameter(
+                gen.draw(f"layers.{layer_idx}.shared.fc1", (2 * Fs, H), 0.02).to(device=device, dtype=dtype))
+            self.shared_experts.linear_fc2.weight = nn.Parameter(
+                gen.draw(f"layers.{layer_idx}.shared.fc2", (H, Fs), 0.02 / math.sqrt(2 * cfg.num_layers)).to(device=device, dtype=dtype))
+            if cfg.moe_shared_expert_gate:
+                self.shared_experts.gate_weight = nn.Parameter(
+                    gen.draw(f"layers.{layer_idx}.shared.gate", (1, H), 0.02).to(device=device, dtype=dtype))
+
+    @torch.no_grad()
+    def update_router_bias(self, rate: float = 1e-3, group=None):
+        """Auxiliary-loss-free balancing: after a step, raise the bias of experts that got fewer tokens than the
+        mean and lower the others by ``rate`` (token counts summed over ``group`` when given)."""
+        if self.last_counts is None or not self.cfg.moe_router_bias:
+            return
+        c = self.last_counts.float()
+        if group is not None and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(c, group=group)
+        self._bias_fp32 = self._bias_fp32.to(c.device) + rate * torch.sign(c.mean() - c)
+        self.router.expert_bias.copy_(self._bias_fp32)
+        self.last_counts = None
+
+    def _shared(self, x):
+        se = self.shared_experts
+        y = ops.linear(ops.swiglu(ops.linear(x, se.linear_fc1.weight)), se.linear_fc2.weight)
+        if hasattr(se, "gate_weight"):
+            y = y * torch.sigmoid(ops.linear(x, se.gate_weight).float()).to(y.dtype)
+        return y
 
     def forward(self, x):
         """x ``[T_local, H]`` (the sequence-parallel shard: MoE runs with TP=1 for
@@ -126,13 +180,14 @@ class MoEMLP(nn.Module):
         T, H = x.shape
         k, E = cfg.moe_top_k, cfg.num_experts
         logits = torch.nn.functional.linear(x.float(), self.router.weight.float())
-        w, idx, probs = ops.topk_router(logits, k, cfg.moe_router_norm_topk_prob)
+        w, idx, probs = route_tokens(logits, cfg, self.router.expert_bias if cfg.moe_router_bias else None)
         replay_idx = RoutingReplay.route(self.layer_idx, idx)
         if replay_idx is not idx:
             idx = replay_idx
             w = probs.gather(-1, idx)
             if cfg.moe_router_norm_topk_prob:
                 w = w / w.sum(-1, keepdim=True)
+            w = w * cfg.moe_routed_scaling_factor
         if cfg.moe_aux_loss_coef > 0 and self.training:
             f = torch.zeros(E, device=x.device).index_add_(0, idx.reshape(-1), torch.ones(T * k, device=x.device))
             self.last_aux = cfg.moe_aux_loss_coef * E * ((f / (T * k)) * probs.mean(0)).sum()
@@ -142,6 +197,8 @@ class MoEMLP(nn.Module):
         src_tok = order // k
         xp = x[src_tok]                               # permuted copies [T*k, H]
         counts = torch.bincount(flat_e, minlength=E)  # tokens per (global) expert
+        if cfg.moe_router_bias and self.training:
+            self.last_counts = counts.detach() if self.last_counts is None else self.last_counts + counts.detach()
 
         comm = getattr(self, "ep_comm", None) if x.is_cuda else None
         if ps.ep.size > 1 and comm is not None:
@@ -187,4 +244,6 @@ class MoEMLP(nn.Module):
         wf = w.reshape(-1)[order].to(yp.dtype)
         out = torch.zeros(T, H, dtype=yp.dtype, device=x.device)
         out = out.index_add(0, src_tok, yp * wf[:, None])
+        if cfg.moe_shared_expert_ffn > 0:
+            out = out + self._shared(x).to(out.dtype)
         return out.to(x.dtype)

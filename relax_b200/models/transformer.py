@@ -153,7 +153,7 @@ class TransformerLayer(nn.Module):
         kind = mixer_kind(cfg, layer_idx)
         mixer = {"attention": Attention, "gdn": GDNMixer, "dsa": DSAMixer}[kind]
         self.self_attention = mixer(cfg, ps, dtype, device, gen, layer_idx)
-        if cfg.is_moe and (layer_idx % cfg.moe_layer_freq == 0):
+        if cfg.is_moe_layer(layer_idx):
             from .moe import MoEMLP
 
             self.mlp = MoEMLP(cfg, ps, dtype, device, gen, layer_idx)
@@ -259,7 +259,7 @@ class GPTModel(nn.Module):
                     [MTPBlock(cfg, ps_, self.dtype, device, gen, k) for k in range(cfg.mtp_num_layers)])
 
         for n, p in self.named_parameters():
-            if any(k in n for k in ("layernorm", "layer_norm", "router", "value_head")) or n.endswith(".bias") and "linear_proj" in n:
+            if any(k in n for k in ("layernorm", "layer_norm", "router", "value_head", "shared_expert")) or n.endswith(".bias") and "linear_proj" in n:
                 p.tp_replicated = True
 
     # ------------------------------------------------------------------ helpers

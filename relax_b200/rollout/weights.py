@@ -44,9 +44,16 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
             shapes[p + "k_norm"] = (hd,)
         shapes[p + "o"] = (H, nq * hd)
         shapes[p + "post_norm"] = (H,)
-        if cfg.is_moe and i % cfg.moe_layer_freq == 0:
+        if cfg.is_moe_layer(i):
             el = cfg.num_experts // ep
             shapes[p + "router"] = (cfg.num_experts, H)
+            if cfg.moe_router_bias:
+                shapes[p + "router_bias"] = (cfg.num_experts,)
+            if cfg.moe_shared_expert_ffn > 0:
+                shapes[p + "shared_gate_up"] = (2 * cfg.moe_shared_expert_ffn, H)
+                shapes[p + "shared_down"] = (H, cfg.moe_shared_expert_ffn)
+                if cfg.moe_shared_expert_gate:
+                    shapes[p + "shared_gate"] = (1, H)
             shapes[p + "experts_gate_up"] = (el, 2 * cfg.moe_ffn_hidden_size, H)
             shapes[p + "experts_down"] = (el, H, cfg.moe_ffn_hidden_size)
         else:
@@ -134,8 +141,15 @@ class RolloutWeights:
         pre = f"layers.{i}."
         if pre + "router" in p:
             logits = torch.nn.functional.linear(x.float(), p[pre + "router"].float())
-            w, idx, _ = ops.topk_router(logits, cfg.moe_top_k, cfg.moe_router_norm_topk_prob)
+            from ..models.moe import route_tokens
+
+            w, idx, _ = route_tokens(logits, cfg, p.get(pre + "router_bias"))
             out = torch.zeros_like(x, dtype=torch.float32)
+            if pre + "shared_gate_up" in p and self.ep_rank == 0:     # summed over the EP ranks afterwards: one rank adds it
+                sh = ops.linear(ops.swiglu(ops.linear(x, p[pre + "shared_gate_up"])), p[pre + "shared_down"]).float()
+                if pre + "shared_gate" in p:
+                    sh = sh * torch.sigmoid(ops.linear(x, p[pre + "shared_gate"]).float())
+                out += sh
             el = p[pre + "experts_gate_up"].shape[0]
             e0 = self.ep_rank * el
             for e in range(el):

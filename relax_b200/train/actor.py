@@ -445,6 +445,10 @@ class TrainActor:
                 dist.all_reduce(tot, group=ps.dp_cp.group)
             gscale = dp_cp / float(tot.clamp_min(1))
         norm, skipped = opt.step(grad_scale=gscale)
+        if self.mcfg.moe_router_bias:      # auxiliary-loss-free balancing: token counts of this step, all replicas
+            for mod in self.model.modules():
+                if hasattr(mod, "update_router_bias"):
+                    mod.update_router_bias(self.mcfg.moe_router_bias_update_rate, ps.dp_cp.group if dp_cp > 1 else None)
         # metrics: sum over samples -> mean over the global batch
         keys = sorted(metrics)
         if keys:

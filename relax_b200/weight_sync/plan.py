@@ -80,6 +80,10 @@ def trainer_param_name(layer_local: int, kind: str) -> str:
         "router": base + "mlp.router.weight",
         "experts_fc1": base + "mlp.experts.linear_fc1.weight",
         "experts_fc2": base + "mlp.experts.linear_fc2.weight",
+        "router_bias": base + "mlp.router.expert_bias",
+        "shared_fc1": base + "mlp.shared_experts.linear_fc1.weight",
+        "shared_fc2": base + "mlp.shared_experts.linear_fc2.weight",
+        "shared_gate": base + "mlp.shared_experts.gate_weight",
     }[kind]
 
 
@@ -140,11 +144,20 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
         # o_proj: column sharded
         for sp, so, dp, do, n in _row_sharded(cfg.q_size, src.tp, dst_tp):
             add(BlockCopy(sp, trainer_param_name(ll, "o"), 0, so, dp, p + "o", 0, do, H, n))
-        is_moe = cfg.is_moe and layer % cfg.moe_layer_freq == 0
+        is_moe = cfg.is_moe_layer(layer)
         if is_moe:
             rep(trainer_param_name(ll, "post_norm_moe"), p + "post_norm", H)
             for r in range(dst_tp):
                 add(BlockCopy(r % src.tp, trainer_param_name(ll, "router"), 0, 0, r, p + "router", 0, 0, cfg.num_experts, H))
+            if cfg.moe_router_bias:
+                rep(trainer_param_name(ll, "router_bias"), p + "router_bias", cfg.num_experts)
+            if cfg.moe_shared_expert_ffn > 0:      # replicated on both sides
+                Fsh = cfg.moe_shared_expert_ffn
+                for r in range(dst_tp):
+                    add(BlockCopy(r % src.tp, trainer_param_name(ll, "shared_fc1"), 0, 0, r, p + "shared_gate_up", 0, 0, 2 * Fsh, H))
+                    add(BlockCopy(r % src.tp, trainer_param_name(ll, "shared_fc2"), 0, 0, r, p + "shared_down", 0, 0, H, Fsh))
+                if cfg.moe_shared_expert_gate:
+                    rep(trainer_param_name(ll, "shared_gate"), p + "shared_gate", H)
             F = cfg.moe_ffn_hidden_size
             el_s, el_d = cfg.num_experts // src.ep, cfg.num_experts // dst_ep
             for e in range(cfg.num_experts):
