@@ -65,7 +65,8 @@ class ModelConfig:
     gdn_k_heads: int = 2
     gdn_v_heads: int = 4
     gdn_head_dim: int = 32
-    # DeepSeek-style sparse MLA attention in every layer when dsa_topk > 0
+    # multi-head latent attention (DeepSeek-V3 / GLM-4.7 style, dims below); with dsa_topk > 0 it is sparse (DSA)
+    multi_latent_attention: bool = False
     dsa_topk: int = 0
     dsa_q_lora: int = 64
     dsa_kv_lora: int = 32
@@ -132,6 +133,21 @@ _reg(ModelConfig(name="tiny-dsv3", num_layers=3, hidden_size=256, num_attention_
                  head_dim=64, ffn_hidden_size=688, vocab_size=1024, num_experts=8, moe_top_k=2, moe_ffn_hidden_size=128,
                  moe_first_dense_layers=1, moe_shared_expert_ffn=128, moe_router_score="sigmoid", moe_router_bias=True,
                  moe_routed_scaling_factor=2.5, dtype="fp32"))
+# scripts/models/glm4.7-30B-A3B.sh: MLA + sigmoid-routed MoE with one shared expert and one leading dense layer
+_reg(ModelConfig(name="glm4.7-30b-a3b", num_layers=47, hidden_size=2048, num_attention_heads=20, num_query_groups=20, head_dim=192,
+                 ffn_hidden_size=10240, vocab_size=154880, qkv_bias=True, num_experts=64, moe_top_k=4, moe_ffn_hidden_size=1536,
+                 moe_first_dense_layers=1, moe_shared_expert_ffn=1536, moe_router_score="sigmoid", moe_router_bias=True,
+                 moe_router_bias_update_rate=0.0, moe_routed_scaling_factor=1.8, multi_latent_attention=True, dsa_q_lora=768,
+                 dsa_kv_lora=512, dsa_nope=192, dsa_rope=64, dsa_v_head=256))
+_reg(ModelConfig(name="tiny-mla", num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=4, head_dim=32,
+                 ffn_hidden_size=256, vocab_size=512, multi_latent_attention=True, dtype="fp32"))
+_reg(ModelConfig(name="qwen3-1.7b", num_layers=28, hidden_size=2048, num_attention_heads=16, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=6144, vocab_size=151936, tie_word_embeddings=True))
+_reg(ModelConfig(name="qwen2.5-7b", num_layers=28, hidden_size=3584, num_attention_heads=28, num_query_groups=4,
+                 head_dim=128, ffn_hidden_size=18944, vocab_size=152064, qk_layernorm=False, qkv_bias=True))
+_reg(ModelConfig(name="qwen3-vl-8b", num_layers=36, hidden_size=4096, num_attention_heads=32, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=12288, vocab_size=151936, rope_theta=5e6,
+                 vision=VisionConfig(out_hidden_size=4096), mrope_section=(24, 20, 20), image_token_id=151655))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,

@@ -130,6 +130,8 @@ class DSAAttention(nn.Module):
         self.linear_kv_up_proj.layer_norm_weight = one(kv_lora)
         self.linear_proj = nn.Module()
         self.linear_proj.weight = mk(hidden, heads * v_head)
+        if topk <= 0:        # plain (dense) MLA: no indexer
+            return
         self.indexer = nn.Module()
         self.indexer.linear_wq = nn.Module()
         self.indexer.linear_wq.weight = mk(idx_heads * idx_dim, hidden)
@@ -160,6 +162,10 @@ class DSAAttention(nn.Module):
         q, kv, w_uv = self.absorbed_qkv(x, positions)
         starts, ends = causal_ranges(cu_seqlens, T)
         scale = (self.nope + self.rope) ** -0.5
+        if dense and not return_aux:
+            lat, _ = dense_mla_attention(q, kv, starts, ends, self.kvl, scale)
+            o = torch.einsum("thc,hvc->thv", lat.float(), w_uv.float()).to(x.dtype).reshape(T, self.H * self.vh)
+            return ops.linear(o, self.linear_proj.weight)
         xd = x.detach()        # the indexer learns from its own loss only
         lg = indexer_logits(ops.linear(xd, self.indexer.linear_wq.weight).view(T, self.Hi, self.Di),
                             ops.linear(xd, self.indexer.linear_wk.weight), ops.linear(xd, self.indexer.linear_weights.weight) * self.Hi ** -0.5,

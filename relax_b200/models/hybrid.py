@@ -46,16 +46,18 @@ class DSAMixer(nn.Module):
 
     def forward(self, x_normed, cos, sin, cu_seqlens, attn_fn=None, max_seqlen=None):
         assert cu_seqlens is not None and attn_fn is None and self.positions is not None
+        self.indexer_loss = None
+        if self.dsa.topk <= 0:
+            return self.dsa(x_normed, self.positions, cu_seqlens, dense=True)
         if torch.is_grad_enabled():
             y, self.indexer_loss, _ = self.dsa(x_normed, self.positions, cu_seqlens, return_aux=True)
             return y
-        self.indexer_loss = None
         return self.dsa(x_normed, self.positions, cu_seqlens)
 
 
 def mixer_kind(cfg, layer_idx: int) -> str:
-    if cfg.dsa_topk > 0:
-        return "dsa"
+    if cfg.dsa_topk > 0 or cfg.multi_latent_attention:
+        return "dsa"      # the same module; without a top-k it attends densely (plain MLA) and has no indexer loss
     if cfg.linear_attention_freq > 0 and (layer_idx + 1) % cfg.linear_attention_freq != 0:
         return "gdn"
     return "attention"

@@ -285,7 +285,7 @@ class GPTModel(nn.Module):
         else:
             h = hidden_in
         cos, sin = self.rope_tables(positions)
-        if self.cfg.dsa_topk > 0:
+        if self.cfg.dsa_topk > 0 or self.cfg.multi_latent_attention:
             for layer in self.decoder.layers:
                 layer.self_attention.positions = positions
         for layer in self.decoder.layers:

@@ -69,8 +69,8 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
                  memory_saver: bool = False):
-        if cfg.dsa_topk > 0 or cfg.linear_attention_freq > 0:
-            raise NotImplementedError("the rollout engine serves softmax-attention stacks only; GDN / DSA layers are "
+        if cfg.dsa_topk > 0 or cfg.linear_attention_freq > 0 or cfg.multi_latent_attention:
+            raise NotImplementedError("the rollout engine serves softmax-attention stacks only; GDN / MLA / DSA layers are "
                                       "trainer-side (SFT, log-prob evaluation) for now")
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank

@@ -61,3 +61,17 @@ def test_rollout_engine_refuses_hybrid_stacks():
 
     with pytest.raises(NotImplementedError):
         RolloutWeights(get_config("tiny-next"), 1, 0, "cpu", torch.float32)
+
+
+def test_mla_preset_trains_and_big_presets_resolve():
+    torch.manual_seed(0)
+    actor = TrainActor(get_config("tiny-mla"), _cfg(), role="sft")
+    b = _batch()
+    before = actor.evaluate_ppl(b)["eval/nll"]
+    for _ in range(8):
+        m = actor.train_sft(b)
+    assert actor.evaluate_ppl(b)["eval/nll"] < before - 0.3 and "indexer_loss" not in m
+    glm = get_config("glm4.7-30b-a3b")
+    assert glm.is_moe_layer(1) and not glm.is_moe_layer(0) and mixer_kind(glm, 3) == "dsa"
+    for name in ("qwen3-1.7b", "qwen2.5-7b", "qwen3-vl-8b"):
+        assert get_config(name).num_parameters() > 1e9
