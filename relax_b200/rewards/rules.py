@@ -273,6 +273,56 @@ def remote_rm_reward(sample, url: Optional[str] = None, timeout: float = 30.0) -
     return float(out["reward"] if isinstance(out, dict) else out)
 
 
+# --------------------------------------------------------------------------- mixed-source routing
+_STOP_MARKS = ("<|im_end|>", "<|endoftext|>", "</s>")
+
+
+def _cut_at_stop(text: str) -> str:
+    cut = [i for i in (text.find(m) for m in _STOP_MARKS) if i > 0]
+    return text[:min(cut)] if cut else text
+
+
+def _leading_number(s: str) -> Optional[float]:
+    m = re.match(r"^\s*\$?\s*(-?\d[\d,]*(?:\.\d+)?)", s)
+    return float(m.group(1).replace(",", "")) if m else None
+
+
+@register_reward("gsm8k", note="+1 / -1; 'Answer: x' or '#### x'; text after an end-of-sequence marker ignored; more than five '####' = -1")
+def gsm8k_reward(sample) -> float:
+    """Grade-school-math scorer hardened against two failure modes of small policies: text emitted after a stop
+    marker, and reward hacking by repeating the answer separator.  A prediction with a unit suffix ("100 miles")
+    counts when its leading number equals the label."""
+    label = sample.label
+    if isinstance(label, dict):
+        label = label.get("ground_truth") or label.get("answer", "")
+    resp = _cut_at_stop(sample.response)
+    if resp.count("####") > 5:
+        return -1.0
+    tail = resp[-300:]
+    found = re.findall(r"(?i)answer\s*:\s*([^\n]+)", tail) or re.findall(r"####\s*(\$?-?[\d,]+(?:\.\d+)?)", tail)
+    if not found:
+        return -1.0
+    pred = found[-1].strip()
+    if math_equal(pred, str(label)):
+        return 1.0
+    a, b = _leading_number(pred), _to_float(_strip_math(str(label)))
+    return 1.0 if a is not None and b is not None and abs(a - b) < 1e-9 else -1.0
+
+
+@register_reward("mopd", note="routes by metadata['data_source']: geo3k -> math 0/1, openr1mm, dapo -> its scalar score, else gsm8k")
+def mopd_reward(sample) -> float:
+    """One scalar per sample for multi-source on-policy distillation data: every source is scored exactly as its own
+    ``rm_type`` would score it (relax/engine/rewards/mopd.py get_mopd_reward)."""
+    src = str((sample.metadata or {}).get("data_source", "")).lower()
+    if "geometry3k" in src or "geo3k" in src:
+        return math_reward(sample)
+    if "multimodal-open-r1" in src or "openr1mm" in src:
+        return float(openr1mm_reward(sample))
+    if "dapo" in src:
+        return float(dapo_reward(sample)["score"])
+    return gsm8k_reward(sample)
+
+
 def make_dapo_genrm_reward(genrm):
     """DAPO scoring with a generative judge for the answers the rule cannot parse: rule says correct -> +1; rule finds
     an answer and it is wrong -> -1; no parsable answer -> ask the generative grader (``relax_b200.rewards.genrm.GenRM``)."""

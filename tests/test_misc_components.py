@@ -81,3 +81,21 @@ def test_quant_hooks_roundtrip_only_matrices():
     assert Q.make_hook(None) is None
     with pytest.raises(ValueError):
         Q.make_hook("fp4")
+
+
+def test_gsm8k_and_mixed_source_rewards():
+    from relax_b200.rewards import get_reward_spec
+    from relax_b200.types import Sample
+
+    g = get_reward_spec("gsm8k").fn
+    S = lambda r, l, **md: Sample(response=r, label=l, metadata=md)
+    assert g(S("so 6*7\n#### 42", "42")) == 1.0 and g(S("Answer: 1,200", "1200")) == 1.0
+    assert g(S("Answer: 100 miles", "100")) == 1.0 and g(S("#### 41", "42")) == -1.0 and g(S("no idea", "42")) == -1.0
+    assert g(S("#### 42<|im_end|>\n#### 7", "42")) == 1.0                 # text after the stop marker is ignored
+    assert g(S("#### 42 " * 6, "42")) == -1.0                            # separator spam
+    assert g(S("Answer: 3.5", {"ground_truth": "3.5"})) == 1.0
+    m = get_reward_spec("mopd").fn
+    assert m(S("thus \\boxed{12}", "12", data_source="hiyouga/geometry3k")) == 1.0
+    assert m(S("thus \\boxed{13}", "12", data_source="geo3k")) == 0.0
+    assert m(S("Answer: 5", "5", data_source="dapo-math-17k")) == 1.0 and m(S("Answer: 6", "5", data_source="DAPO")) == -1.0
+    assert m(S("#### 9", "9", data_source="gsm8k")) == 1.0 and m(S("#### 9", "9")) == 1.0
