@@ -99,3 +99,28 @@ def test_gsm8k_and_mixed_source_rewards():
     assert m(S("thus \\boxed{13}", "12", data_source="geo3k")) == 0.0
     assert m(S("Answer: 5", "5", data_source="dapo-math-17k")) == 1.0 and m(S("Answer: 6", "5", data_source="DAPO")) == -1.0
     assert m(S("#### 9", "9", data_source="gsm8k")) == 1.0 and m(S("#### 9", "9")) == 1.0
+
+
+def test_structured_logging_rank_filter_and_json():
+    import io
+    import json as _json
+    import logging
+
+    from relax_b200.utils import logging_utils as LU
+
+    buf = io.StringIO()
+    LU.configure_logging(role="actor", rank=0, level="INFO", json_lines=True, stream=buf, force=True)
+    log = LU.get_logger("train")
+    LU.log_fields(log, logging.INFO, "step done", step=3, loss=0.5)
+    log.debug("hidden")
+    rec = _json.loads(buf.getvalue().strip().splitlines()[-1])
+    assert rec["role"] == "actor" and rec["rank"] == 0 and rec["step"] == 3 and rec["msg"] == "step done" and "hidden" not in buf.getvalue()
+    buf2 = io.StringIO()
+    LU.configure_logging(role="actor", rank=3, level="INFO", json_lines=False, stream=buf2, force=True)
+    log.info("progress line")
+    log.warning("kv cache full")
+    assert "progress line" not in buf2.getvalue() and "[actor r3]" in buf2.getvalue() and "kv cache full" in buf2.getvalue()
+    every = LU.EveryN()
+    hits = [every("k", 60) for _ in range(5)]
+    assert hits == [True, False, False, False, False] and every.take_skipped("k") == 4 and every("other", 60)
+    LU.configure_logging(rank=0, stream=io.StringIO(), force=True)
