@@ -268,3 +268,49 @@ def ring_attention(q, k, v, g: GroupInfo, total_length: int, scale: Optional[flo
         cu = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
         return ops.attention_varlen(q, k, v, cu, causal=True, scale=scale)
     return _RingAttention.apply(q, k, v, g, total_length, scale)
+
+
+# --------------------------------------------------------------------------- whole-sequence ops under CP
+class _GatherZigzag(torch.autograd.Function):
+    """Local zig-zag shard ``[2 * cs, ...]`` -> the full sequence ``[2 * cp * cs, ...]`` in token order on every rank.
+    Backward keeps this rank's rows of the summed gradient (an all-reduce followed by the slice, i.e. a
+    reduce-scatter in zig-zag order)."""
+
+    @staticmethod
+    def forward(ctx, x, g: GroupInfo):
+        ctx.g = g
+        cp, cs = g.size, x.shape[0] // 2
+        parts = [torch.empty_like(x) for _ in range(cp)]
+        dist.all_gather(parts, x.contiguous(), group=g.group)
+        full = x.new_empty((2 * cp * cs,) + tuple(x.shape[1:]))
+        for r, p in enumerate(parts):
+            full[r * cs:(r + 1) * cs] = p[:cs]
+            full[(2 * cp - 1 - r) * cs:(2 * cp - r) * cs] = p[cs:]
+        return full
+
+    @staticmethod
+    def backward(ctx, dy):
+        g = ctx.g
+        cp, r = g.size, g.rank
+        cs = dy.shape[0] // (2 * cp)
+        dy = dy.contiguous()
+        dist.all_reduce(dy, group=g.group)
+        return torch.cat([dy[r * cs:(r + 1) * cs], dy[(2 * cp - 1 - r) * cs:(2 * cp - r) * cs]]), None
+
+
+def zigzag_rows(cp: int, rank: int, cs: int, device=None) -> torch.Tensor:
+    return torch.cat([torch.arange(rank * cs, (rank + 1) * cs, device=device),
+                      torch.arange((2 * cp - 1 - rank) * cs, (2 * cp - rank) * cs, device=device)])
+
+
+def run_on_full_sequence(fn, x_local: torch.Tensor, g: GroupInfo) -> torch.Tensor:
+    """Apply a token mixer that needs the whole sequence in order (a recurrence such as the gated delta rule, a
+    causal convolution) to a context-parallel shard: gather the sequence, run ``fn`` on it on every rank, keep this
+    rank's zig-zag rows (relax/backends/megatron/cp_utils.py GDN helpers :658-774: all-gather forward,
+    reduce-scatter backward).  Each rank divides its output gradient contribution by ``cp`` implicitly: only the
+    local rows of ``fn``'s output are used, so the summed input gradient is exact."""
+    if g.size == 1:
+        return fn(x_local)
+    full = _GatherZigzag.apply(x_local, g)
+    y = fn(full)
+    return y.index_select(0, zigzag_rows(g.size, g.rank, x_local.shape[0] // 2, y.device))

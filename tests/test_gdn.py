@@ -66,3 +66,36 @@ def test_mixer_layer_chunked_equals_recurrent_and_trains():
     assert torch.allclose(a[13:], alone, atol=2e-4)
     a.square().mean().backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in m.parameters())
+
+
+def _cp_worker(rank, world):
+    from relax_b200.parallel.cp import run_on_full_sequence, zigzag_rows
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+
+    ps = init_parallel_state(ParallelDims(cp=2))
+    torch.manual_seed(0)
+    m = GatedDeltaNet(hidden_size=16, num_k_heads=2, num_v_heads=2, head_k_dim=8, head_v_dim=8, chunk=8)
+    x_full = torch.randn(24, 16, generator=torch.Generator().manual_seed(5))
+    rows = zigzag_rows(2, rank, 6)
+    x_loc = x_full[rows].clone().requires_grad_(True)
+    cu = torch.tensor([0, 24], dtype=torch.int32)
+    y = run_on_full_sequence(lambda full: m(full, cu), x_loc, ps.cp)
+    y.square().sum().backward()
+    return rows, y.detach(), x_loc.grad.clone(), m.out_proj.weight.grad.clone()
+
+
+def test_gdn_under_context_parallelism_matches_single_rank():
+    from tests._mp import run_distributed
+
+    outs = run_distributed(_cp_worker, 2)
+    torch.manual_seed(0)
+    m = GatedDeltaNet(hidden_size=16, num_k_heads=2, num_v_heads=2, head_k_dim=8, head_v_dim=8, chunk=8)
+    x = torch.randn(24, 16, generator=torch.Generator().manual_seed(5)).requires_grad_(True)
+    y = m(x, torch.tensor([0, 24], dtype=torch.int32))
+    y.square().sum().backward()
+    wsum = 0
+    for rows, yl, gx, gw in outs:
+        assert torch.allclose(yl, y.detach()[rows], atol=1e-5)
+        assert torch.allclose(gx, x.grad[rows], atol=1e-4)
+        wsum = wsum + gw
+    assert torch.allclose(wsum, m.out_proj.weight.grad, atol=1e-4)     # parameter gradients add up over the CP ranks
