@@ -277,7 +277,7 @@ def log_mel_spectrogram(wav: torch.Tensor, cfg: Optional[MultimodalConfig] = Non
 
 
 def audio_token_count(n_frames: int) -> int:
-    """Tokens the audio tower emits for ``n_frames`` mel frames (two stride-2 convolutions, then pairs merged)."""
+    """Tokens the audio tower emits for ``n_frames`` mel frames (a stride-2 convolution, then pairs of frames merged)."""
     after = (n_frames - 1) // 2 + 1
     return (after - 2) // 2 + 1 if after >= 2 else 1
 
