@@ -152,3 +152,63 @@ class InProcessTeacher:
 
     def score(self, batch: dict) -> List[torch.Tensor]:
         return self.actor.compute_log_prob(batch, self.tag)["log_probs"]
+
+
+class TeacherPool:
+    """Several teacher scorers behind one ``score`` call: the batch is cut into per-teacher slices that run
+    concurrently, a teacher that raises or exceeds the time limit is marked unhealthy and its slice is re-run on
+    the next healthy one, and unhealthy teachers are retried after ``retry_after_s`` (the managed teacher engines of
+    relax/distributed/ray/teacher_manager.py: start, health, pick, recover).  A teacher is any object with
+    ``score(batch) -> list`` (:class:`InProcessTeacher`, a remote scorer, a rollout engine in scoring mode)."""
+
+    def __init__(self, teachers: Sequence, timeout_s: float = 600.0, retry_after_s: float = 60.0):
+        if not teachers:
+            raise ValueError("TeacherPool needs at least one teacher")
+        self.teachers = list(teachers)
+        self.timeout_s, self.retry_after_s = timeout_s, retry_after_s
+        self._down: dict = {}          # index -> time it was marked unhealthy
+        self.failures = 0
+
+    def healthy(self) -> List[int]:
+        import time
+
+        now = time.monotonic()
+        for i, t0 in list(self._down.items()):
+            if now - t0 >= self.retry_after_s:
+                del self._down[i]
+        return [i for i in range(len(self.teachers)) if i not in self._down]
+
+    @staticmethod
+    def _slice(batch: dict, idx: Sequence[int]) -> dict:
+        n = len(batch["tokens"])
+        return {k: ([v[i] for i in idx] if isinstance(v, (list, tuple)) and len(v) == n else v) for k, v in batch.items()}
+
+    def score(self, batch: dict) -> List[torch.Tensor]:
+        import time
+        from concurrent.futures import ThreadPoolExecutor, TimeoutError as _Timeout
+
+        n = len(batch["tokens"])
+        out: List = [None] * n
+        pending = list(range(n))
+        while pending:
+            live = self.healthy()
+            if not live:
+                raise RuntimeError("no healthy teacher left")
+            parts = [pending[j::len(live)] for j in range(len(live))]
+            jobs = [(t, p) for t, p in zip(live, parts) if p]
+            retry: List[int] = []
+            with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
+                futs = [(t, p, ex.submit(self.teachers[t].score, self._slice(batch, p))) for t, p in jobs]
+                for t, p, f in futs:
+                    try:
+                        res = f.result(timeout=self.timeout_s)
+                        if len(res) != len(p):
+                            raise RuntimeError(f"teacher {t} returned {len(res)} rows for {len(p)} samples")
+                        for i, r in zip(p, res):
+                            out[i] = r
+                    except (_Timeout, Exception):   # noqa: BLE001 - any failure of a teacher is handled the same way
+                        self._down[t] = time.monotonic()
+                        self.failures += 1
+                        retry.extend(p)
+            pending = sorted(retry)
+        return out

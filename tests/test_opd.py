@@ -69,3 +69,34 @@ def test_advantage_shaping_and_loss():
     assert abs(float(loss) - 0.5 * (1 + 3 + 4 + 5) / 4) < 1e-6
     loss.backward()
     assert torch.allclose(x.grad, torch.tensor([0.125, 0.0, 0.125, 0.125, 0.125]))
+
+
+def test_teacher_pool_splits_work_and_fails_over():
+    import pytest
+    from relax_b200.algo.opd import TeacherPool
+
+    class T:
+        def __init__(self, tag, fail=False):
+            self.tag, self.fail, self.calls = tag, fail, 0
+
+        def score(self, batch):
+            self.calls += 1
+            if self.fail:
+                raise RuntimeError("engine died")
+            return [torch.full((len(t),), float(self.tag)) for t in batch["tokens"]]
+
+    batch = {"tokens": [[1] * (i + 1) for i in range(7)], "response_lengths": [1] * 7, "temperature": 1.0}
+    a, b = T(1), T(2)
+    out = TeacherPool([a, b]).score(batch)
+    assert [len(o) for o in out] == list(range(1, 8)) and a.calls == 1 and b.calls == 1
+    assert {float(o[0]) for o in out} == {1.0, 2.0}
+    bad = T(9, fail=True)
+    pool = TeacherPool([bad, T(3)], retry_after_s=1000)
+    out = pool.score(batch)
+    assert all(float(o[0]) == 3.0 for o in out) and pool.failures == 1 and pool.healthy() == [1]
+    pool.score(batch)
+    assert bad.calls == 1                      # not retried before retry_after_s
+    pool.retry_after_s = 0.0
+    assert pool.healthy() == [0, 1]
+    with pytest.raises(RuntimeError):
+        TeacherPool([T(1, fail=True)]).score(batch)
