@@ -18,8 +18,12 @@ from .agentic import GenerateFn, Session, SessionForest, Tokenizer
 
 
 class ChatService:
-    def __init__(self, generate: GenerateFn, tok: Tokenizer, model_name: str = "relax-b200-policy", max_context: int = 8192):
+    def __init__(self, generate: GenerateFn, tok: Tokenizer, model_name: str = "relax-b200-policy", max_context: int = 8192,
+                 permits=None, abort_check=None):
         self.generate, self.tok, self.model_name, self.max_context = generate, tok, model_name, max_context
+        # rollout.request_permit.InferencePermitManager: bounds the requests in flight across all front ends that
+        # share the engines; a request that gets its permit after an abort was signalled raises GenerationAborted
+        self.permits, self.abort_check = permits, abort_check
         self.forest = SessionForest()
         self.by_key: Dict[str, Session] = {}
         self._lock = threading.Lock()   # the engine is single-consumer
@@ -46,7 +50,10 @@ class ChatService:
             raise ValueError("messages must be a non-empty list")
         n = int(body.get("n", 1))
         max_new = int(body.get("max_tokens") or body.get("max_completion_tokens") or 256)
-        with self._lock:
+        import contextlib
+
+        gate = self.permits.permit(self.abort_check) if self.permits is not None else contextlib.nullcontext()
+        with gate, self._lock:
             s = self._session(session_key or body.get("user"), msgs)
             room = self.max_context - len(s.tokens)
             if room <= 0:

@@ -130,3 +130,20 @@ def test_agreement_collectives_two_ranks():
     assert torch.equal(o1["grad"], torch.zeros(3)) and torch.equal(o0["grad"], torch.full((3,), 2.0))
     assert o0["none"] is None and o1["none"] is None
     assert o0["calls"] == 3 and torch.equal(o0["flat"], torch.arange(10, dtype=torch.float32) * 3) and torch.equal(o0["flat"], o1["flat"])
+
+
+def test_chat_endpoint_takes_a_permit_and_honours_abort():
+    from relax_b200.rollout.agentic import Tokenizer
+    from relax_b200.rollout.openai_api import ChatService
+
+    tok = Tokenizer(encode=lambda s: [ord(c) for c in s], decode=lambda t: "".join(chr(97 + x % 26) for x in t))
+    m = InferencePermitManager(1)
+    gen = lambda prompts, n, keys: [([5, 6, 7], [-0.1, -0.2, -0.3], "stop", [0]) for _ in prompts]
+    flag = {"abort": False}
+    svc = ChatService(gen, tok, permits=m, abort_check=lambda: flag["abort"])
+    r = svc.chat({"messages": [{"role": "user", "content": "hi"}]})
+    assert r["choices"][0]["message"]["content"] and m.granted == 1 and m.in_use == 0
+    flag["abort"] = True
+    with pytest.raises(GenerationAborted):
+        svc.chat({"messages": [{"role": "user", "content": "hi"}]})
+    assert m.in_use == 0
