@@ -71,6 +71,13 @@ class ColocateConfig:
     # directory for per-step rollout dumps (rollout_<id>.jsonl, read by relax_b200.utils.visualize); engine-replica
     # rank 0 of data-parallel rank 0 writes its own samples
     save_debug_rollout_data: Optional[str] = None
+    # held-out evaluation: rollout.evaluation.EvalDataset objects, run every `eval_interval` steps (and before the
+    # first one unless `skip_eval_before_train`) with these sampling settings
+    eval_datasets: list = field(default_factory=list)
+    eval_interval: Optional[int] = None
+    skip_eval_before_train: bool = False
+    eval_temperature: float = 0.0
+    eval_max_response_len: Optional[int] = None
 
 
 class ColocatedGRPO:
@@ -173,10 +180,36 @@ class ColocatedGRPO:
             s.reward = self.reward_fn(s)
         return flat
 
+    # ------------------------------------------------------------------ evaluation
+    def evaluate(self) -> dict:
+        """Evaluation rollout on every configured set with the current weights; engine replicas split nothing here
+        (each runs the full sets: they are small) and report identical numbers."""
+        from ..rollout.evaluation import evaluate as _eval
+
+        cfg = self.cfg
+        if cfg.offload_rollout:
+            self.engine.resume_memory_occupation(("kv_cache",))
+        sp = SamplingParams(temperature=cfg.eval_temperature, top_p=1.0, top_k=-1,
+                            max_new_tokens=cfg.eval_max_response_len or cfg.max_response_len)
+        with self.timer.span("eval"):
+            m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp)
+        if cfg.offload_rollout:
+            self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
+        return m
+
+    def _eval_due(self, rid: int) -> bool:
+        cfg = self.cfg
+        if not cfg.eval_datasets or not cfg.eval_interval:
+            return False
+        if rid == 0:
+            return not cfg.skip_eval_before_train
+        return rid % cfg.eval_interval == 0
+
     # ------------------------------------------------------------------ one step
     def step(self) -> dict:
         cfg, rid = self.cfg, self.rollout_id
         t_all = time.perf_counter()
+        eval_metrics = self.evaluate() if self._eval_due(rid) else {}
         with self.timer.span("rollout"):
             if cfg.offload_rollout:
                 self.engine.resume_memory_occupation(("kv_cache",))
@@ -224,6 +257,7 @@ class ColocatedGRPO:
                  raw_reward_mean=float(sum(batch["raw_reward"]) / max(1, len(batch["raw_reward"]))),
                  step_time=time.perf_counter() - t_all)
         m.update(self.timer.log_dict())
+        m.update(eval_metrics)
         self.rollout_id += 1
         return m
 

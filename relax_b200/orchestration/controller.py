@@ -31,6 +31,9 @@ def _get(a, name, default=None):
 
 
 class Controller:
+    def _eval_sets(self, a):
+        return _eval_sets_from_args(a, self.model_cfg.vocab_size)
+
     def __init__(self, args, metrics: Optional[MetricsService] = None, device: Optional[str] = None):
         self.args = args
         self.rank = dist.get_rank() if dist.is_initialized() else 0
@@ -80,7 +83,11 @@ class Controller:
                 kv_block_size=page if page > 1 else 16,
                 max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
                 offload_rollout=a.offload_rollout, offload_train=a.offload_train,
-                save_debug_rollout_data=_get(a, "save_debug_rollout_data", None))
+                save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
+                eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
+                skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
+                eval_temperature=_get(a, "eval_temperature", None) or 0.0,
+                eval_max_response_len=_get(a, "eval_max_response_len", None))
             return ColocatedGRPO(cfg, device=self.device)
         if self.mode == "sft":
             from ..train.actor import TrainActor
@@ -196,6 +203,29 @@ class _SFTRunner:
         m = self.actor.train_sft(b)
         m["total_tokens_local"] = sum(len(t) for t in b["tokens"])
         return m
+
+
+def _eval_sets_from_args(a, vocab: int):
+    pairs = getattr(a, "eval_prompt_data", None)
+    if not pairs:
+        return []
+    import json as _json
+
+    from ..rollout.evaluation import load_eval_datasets
+
+    overrides = None
+    if getattr(a, "eval_config", None):
+        with open(a.eval_config) as f:
+            overrides = _json.load(f)
+    tok = _byte_tokenizer(vocab)
+    enc = lambda p: tok(p if isinstance(p, str) else " ".join(str(m.get("content", "")) for m in p))
+    sets = load_eval_datasets(pairs, enc, getattr(a, "eval_input_key", None) or "prompt", getattr(a, "eval_label_key", None) or "label",
+                              getattr(a, "n_samples_per_eval_prompt", 1), getattr(a, "eval_size", None),
+                              getattr(a, "eval_max_prompt_len", None), overrides)
+    for ds in sets:
+        ds.top_p = ds.top_p if ds.top_p is not None else getattr(a, "eval_top_p", None)
+        ds.top_k = ds.top_k if ds.top_k is not None else getattr(a, "eval_top_k", None)
+    return sets
 
 
 def _byte_tokenizer(vocab: int):
