@@ -73,6 +73,10 @@ class ColocateConfig:
     save_debug_rollout_data: Optional[str] = None
     # held-out evaluation: rollout.evaluation.EvalDataset objects, run every `eval_interval` steps (and before the
     # first one unless `skip_eval_before_train`) with these sampling settings
+    # user code by path ("pkg.mod:fn" or "/file.py:fn"): generate(engine, samples, sampling_params) -> samples fills
+    # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
+    custom_generate_function_path: Optional[str] = None
+    custom_rm_path: Optional[str] = None
     eval_datasets: list = field(default_factory=list)
     eval_interval: Optional[int] = None
     skip_eval_before_train: bool = False
@@ -138,7 +142,11 @@ class ColocatedGRPO:
         self.queue = tq.init({"capacity_partitions": 2})
         ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
         self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt)
-        self.reward_fn = get_reward_spec(cfg.rm_type).fn
+        from ..rollout.custom_generate import load_function, load_generate_function
+
+        self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
+            else get_reward_spec(cfg.rm_type).fn
+        self.custom_generate = load_generate_function(cfg.custom_generate_function_path, None)
         self.timer = Timer()
         self.rollout_id = 0
         self.sync_weights()
@@ -170,6 +178,12 @@ class ColocatedGRPO:
         sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                             max_new_tokens=cfg.max_response_len)
         flat = [s for g in mine for s in g]
+        if self.custom_generate is not None:
+            flat = list(self.custom_generate(self.engine, flat, sp))
+            for s in flat:
+                if s.reward is None:
+                    s.reward = self.reward_fn(s)
+            return flat
         res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
         for s, r in zip(flat, res):
             s.tokens = list(r.prompt) + list(r.output)

@@ -84,6 +84,8 @@ class Controller:
                 max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
                 offload_rollout=a.offload_rollout, offload_train=a.offload_train,
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
+                custom_generate_function_path=_get(a, "custom_generate_function_path", None),
+                custom_rm_path=_get(a, "custom_rm_path", None),
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
                 skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,

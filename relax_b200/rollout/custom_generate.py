@@ -30,10 +30,16 @@ def load_object(path: str) -> Any:
         if not os.path.isfile(mod_part):
             raise FileNotFoundError(mod_part)
         name = "relax_b200_user_" + hashlib.sha1(os.path.abspath(mod_part).encode()).hexdigest()[:12]
-        spec = importlib.util.spec_from_file_location(name, mod_part)
-        mod = importlib.util.module_from_spec(spec)
-        sys.modules[name] = mod
-        spec.loader.exec_module(mod)
+        mod = sys.modules.get(name)      # one module object per file, however many attributes are loaded from it
+        if mod is None:
+            spec = importlib.util.spec_from_file_location(name, mod_part)
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[name] = mod
+            try:
+                spec.loader.exec_module(mod)
+            except BaseException:
+                sys.modules.pop(name, None)
+                raise
     else:
         mod = importlib.import_module(mod_part)
     obj = mod

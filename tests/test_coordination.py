@@ -147,3 +147,35 @@ def test_chat_endpoint_takes_a_permit_and_honours_abort():
     with pytest.raises(GenerationAborted):
         svc.chat({"messages": [{"role": "user", "content": "hi"}]})
     assert m.in_use == 0
+
+
+def test_custom_generate_and_reward_paths_drive_the_colocated_loop(tmp_path):
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    f = tmp_path / "user_code.py"
+    f.write_text(
+        "from relax_b200.types import SampleStatus\n"
+        "CALLS = []\n"
+        "def generate(engine, samples, sp):\n"
+        "    res = engine.generate([s.tokens for s in samples], sp, group_keys=[s.group_index for s in samples])\n"
+        "    for s, r in zip(samples, res):\n"
+        "        s.tokens = list(r.prompt) + list(r.output)\n"
+        "        s.response_length = len(r.output)\n"
+        "        s.rollout_log_probs = list(r.logprobs)\n"
+        "        s.status = SampleStatus.COMPLETED\n"
+        "        s.metadata['custom'] = True\n"
+        "    CALLS.append(len(samples))\n"
+        "    return samples\n"
+        "def reward(sample):\n"
+        "    return float(sum(sample.tokens[-sample.response_length:]) % 3 == 0)\n")
+    cfg = ColocateConfig(model=get_config("tiny"), train=TrainConfig(global_batch_size=4, n_samples_per_prompt=2, pad_multiple=1,
+                         max_tokens_per_gpu=256, loss=LossConfig(), optim=OptimizerConfig(lr=1e-4)),
+                         rollout_batch_size=2, prompt_len=8, max_response_len=8, kv_blocks=64, num_prompts=16,
+                         custom_generate_function_path=f"{f}:generate", custom_rm_path=f"{f}:reward")
+    run = ColocatedGRPO(cfg)
+    m = run.step()
+    assert CG.load_object(f"{f}:CALLS") == [4] and 0.0 <= m["raw_reward_mean"] <= 1.0
