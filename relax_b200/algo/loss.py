@@ -46,6 +46,8 @@ class LossConfig:
     value_clip: float = 0.2
     custom_pg_loss_reducer: Optional[Callable] = None
     custom_tis_function: Optional[Callable] = None
+    # fn(log_probs, entropy, LossBatch, LossConfig) -> (loss, metrics): replaces the policy loss (--loss-type custom_loss)
+    custom_loss_function: Optional[Callable] = None
 
     def __post_init__(self):
         if self.eps_clip_high is None:
@@ -57,6 +59,15 @@ class LossConfig:
         for f in LossConfig.__dataclass_fields__:
             if hasattr(args, f):
                 kw[f] = getattr(args, f)
+        from ..rollout.custom_generate import load_function
+
+        # --custom-*-function-path flags name user code ("pkg.mod:fn" or "/file.py:fn")
+        for field_name, flag, npos in (("custom_tis_function", "custom_tis_function_path", 3),
+                                       ("custom_pg_loss_reducer", "custom_pg_loss_reducer_function_path", 3),
+                                       ("custom_loss_function", "custom_loss_function_path", 4)):
+            path = getattr(args, flag, None)
+            if path:
+                kw[field_name] = load_function(path, npos, flag)
         return LossConfig(**kw)
 
 

@@ -420,6 +420,9 @@ class TrainActor:
             elif self.role == "sft":
                 lp, _ = self._forward_logp(pb, False)
                 loss, m = L.sft_loss(lp, lb, cfg.loss)
+            elif cfg.loss.custom_loss_function is not None:
+                lp, en = self._forward_logp(pb, cfg.compute_entropy)
+                loss, m = cfg.loss.custom_loss_function(lp, en, lb, cfg.loss)
             else:
                 lp, en = self._forward_logp(pb, cfg.compute_entropy)
                 loss, m = L.policy_loss(lp, en, lb, cfg.loss)

@@ -124,3 +124,31 @@ def test_structured_logging_rank_filter_and_json():
     hits = [every("k", 60) for _ in range(5)]
     assert hits == [True, False, False, False, False] and every.take_skipped("k") == 4 and every("other", 60)
     LU.configure_logging(rank=0, stream=io.StringIO(), force=True)
+
+
+def test_custom_loss_and_tis_functions_by_path(tmp_path):
+    import torch
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    f = tmp_path / "user_loss.py"
+    f.write_text("import torch\n"
+                 "def loss(lp, en, batch, cfg):\n"
+                 "    l = -(lp * batch.advantages * batch.loss_mask).sum()\n"
+                 "    return l, {'loss': l.detach(), 'mine': torch.tensor(7.0) * batch.seg.num_segments if hasattr(batch.seg, 'num_segments') else torch.tensor(7.0)}\n"
+                 "def tis(old, rollout, cfg):\n"
+                 "    w = torch.ones_like(old)\n"
+                 "    return w, w, torch.zeros_like(old)\n".replace("\\\n", "\n"))
+    a = parse_args(["--model-name", "tiny", "--colocate", "--loss-type", "custom_loss", "--custom-loss-function-path", f"{f}:loss",
+                    "--custom-tis-function-path", f"{f}:tis"])
+    lc = LossConfig.from_args(a)
+    assert lc.custom_loss_function is not None and lc.custom_tis_function is not None
+    actor = TrainActor(get_config("tiny"), TrainConfig(global_batch_size=2, max_tokens_per_gpu=64, pad_multiple=1, loss=lc,
+                                                       optim=OptimizerConfig(lr=1e-3)), role="actor")
+    b = {"tokens": [[5, 6, 7, 8, 9, 10], [11, 12, 13, 14]], "response_lengths": [3, 2], "loss_masks": [[1.0] * 3, [1.0] * 2],
+         "advantages": [[1.0] * 3, [-1.0] * 2], "log_probs": [[-1.0] * 3, [-1.0] * 2]}
+    out, norm = actor._train_step(b, [0, 1])
+    assert "mine" in out and norm > 0
