@@ -138,10 +138,10 @@ def test_custom_loss_and_tis_functions_by_path(tmp_path):
     f.write_text("import torch\n"
                  "def loss(lp, en, batch, cfg):\n"
                  "    l = -(lp * batch.advantages * batch.loss_mask).sum()\n"
-                 "    return l, {'loss': l.detach(), 'mine': torch.tensor(7.0) * batch.seg.num_segments if hasattr(batch.seg, 'num_segments') else torch.tensor(7.0)}\n"
+                 "    return l, {'loss': l.detach(), 'mine': torch.tensor(7.0)}\n"
                  "def tis(old, rollout, cfg):\n"
                  "    w = torch.ones_like(old)\n"
-                 "    return w, w, torch.zeros_like(old)\n".replace("\\\n", "\n"))
+                 "    return w, w, torch.zeros_like(old)\n")
     a = parse_args(["--model-name", "tiny", "--colocate", "--loss-type", "custom_loss", "--custom-loss-function-path", f"{f}:loss",
                     "--custom-tis-function-path", f"{f}:tis"])
     lc = LossConfig.from_args(a)
