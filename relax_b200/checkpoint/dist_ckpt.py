@@ -275,3 +275,27 @@ def resolve_start_rollout_id(load: Optional[str], explicit: Optional[int] = None
         return explicit
     it = read_latest_iteration(load)
     return 0 if it is None else it + 1
+
+
+@torch.no_grad()
+def load_full_state(cfg: ModelConfig, ps: ParallelState, model, full_state: dict, strict: bool = True) -> list:
+    """Copy this rank's boxes out of a FULL (unsharded, Megatron-layout) state dict into the local parameters - the
+    path from a Hugging Face checkpoint into any TP / EP / PP layout.  Vocabulary rows past the checkpoint's size
+    (padding to a multiple of TP) are zeroed.  Returns the names that were not found (raises when ``strict``)."""
+    per = cfg.num_layers // ps.pp.size
+    missing = []
+    for s in local_shards(cfg, ps, model.named_parameters(), layer_offset=ps.pp.rank * per):
+        src = full_state.get(s.fqn)
+        if src is None:
+            missing.append(s.fqn)
+            continue
+        idx = tuple(slice(o, o + n) for o, n in zip(s.offsets, s.tensor.shape))
+        box = src[idx]
+        if box.shape != s.tensor.shape:                      # padded vocabulary shard
+            s.tensor.zero_()
+            s.tensor[tuple(slice(0, n) for n in box.shape)].copy_(box)
+        else:
+            s.tensor.copy_(box)
+    if missing and strict:
+        raise KeyError(f"{len(missing)} parameters missing from the checkpoint, e.g. {missing[:3]}")
+    return missing

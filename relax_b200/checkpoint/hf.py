@@ -255,3 +255,14 @@ def load_hf_checkpoint(directory: str, dequantize: bool = True, dtype=None) -> d
 def is_hf_checkpoint(path: str) -> bool:
     return os.path.isdir(path) and os.path.exists(os.path.join(path, "config.json")) and \
         any(f.endswith(".safetensors") for f in os.listdir(path))
+
+
+def load_hf_into_model(path: str, cfg: ModelConfig, ps, model, strict: bool = True) -> list:
+    """Read a Hugging Face checkpoint (local directory, ``file://`` or ``s3://``), convert it to the Megatron layout
+    and copy this rank's shards into ``model`` (``--hf-checkpoint`` / ``--ref-load`` of the reference,
+    relax/backends/megatron/checkpoint.py _load_checkpoint_hf :250-278)."""
+    from .dist_ckpt import load_full_state
+
+    dtype = next(model.parameters()).dtype
+    full = hf_to_megatron_state(cfg, load_hf_checkpoint(path, dequantize=True, dtype=dtype))
+    return load_full_state(cfg, ps, model, full, strict)

@@ -107,8 +107,33 @@ class Controller:
     def _actor(self):
         return getattr(self.runner, "actor", None)
 
+    def _load_hf_weights(self):
+        """``--hf-checkpoint`` initialises the policy (unless a training checkpoint under ``--load`` takes over) and,
+        with ``--ref-load`` pointing at a Hugging Face directory, the frozen reference snapshot."""
+        from ..checkpoint import hf as H
+
+        a, actor = self.args, self._actor()
+        if actor is None:
+            return
+        src = _get(a, "hf_checkpoint", None)
+        if src and ("://" in src or H.is_hf_checkpoint(src)):
+            H.load_hf_into_model(src, self.model_cfg, actor.ps, actor.model, strict=not _get(a, "only_load_weight", False))
+            if actor.optimizer is not None:
+                actor.optimizer.reload_master_from_params()
+            if "ref" in actor.snapshots:
+                actor.backup("ref")
+            if hasattr(self.runner, "sync_weights"):
+                self.runner.sync_weights()
+        ref = _get(a, "ref_load", None)
+        if ref and ref != src and ("://" in ref or H.is_hf_checkpoint(ref)) and "ref" in actor.snapshots:
+            keep = actor.param_buf.clone()
+            H.load_hf_into_model(ref, self.model_cfg, actor.ps, actor.model)
+            actor.backup("ref", to_host=not actor.snapshots["ref"].is_cuda and actor.device.type == "cuda")
+            actor.param_buf.copy_(keep)
+
     def _maybe_resume(self):
         a, actor = self.args, self._actor()
+        self._load_hf_weights()
         if not a.load or actor is None or not os.path.isdir(a.load):
             return
         if dist_ckpt.read_latest_iteration(a.load) is None:
@@ -127,6 +152,15 @@ class Controller:
                                   None if _get(a, "no_save_optim", False) else actor.optimizer)
         if self.rank == 0:
             dist_ckpt.rotate_checkpoints(a.save, getattr(a, "max_checkpoints_to_keep", None))
+            if _get(a, "save_hf", None):       # also export Hugging Face files from the checkpoint just written
+                from ..checkpoint import hf as H
+
+                full = dist_ckpt.load_full_tensors(dist_ckpt.iter_dir(a.save, rollout_id))
+                full = {k: v for k, v in full.items() if not k.startswith("optimizer.")}
+                out = a.save_hf.format(rollout_id=rollout_id) if "{" in a.save_hf else os.path.join(a.save_hf, f"iter_{rollout_id:07d}")
+                H.save_hf_checkpoint(out, self.model_cfg, H.convert_state_to_hf(self.model_cfg, full),
+                                     quantize_fp8=_get(a, "save_hf_dtype", None) == "fp8",
+                                     fp8_block=_get(a, "save_hf_fp8_block_size", None) or 128)
 
     # ------------------------------------------------------------------ loop
     def _install_signal_handlers(self):

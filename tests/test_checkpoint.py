@@ -116,3 +116,55 @@ def test_rotation_keeps_newest(tmp_path):
     assert D.rotate_checkpoints(save, 2) == [1, 2]
     assert sorted(os.listdir(save)) == ["iter_0000003", "iter_0000010"]
     assert D.rotate_checkpoints(save, None) == []
+
+
+def _hf_tp_worker(rank, world, path):
+    import torch
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+
+    ps = init_parallel_state(ParallelDims(tp=2))
+    cfg = get_config("tiny")
+    m = GPTModel(cfg, ps, seed=99)                 # different init: everything must come from the files
+    assert H.load_hf_into_model(path, cfg, ps, m) == []
+    toks = torch.arange(8) + 3
+    h = m(toks, torch.arange(8), torch.tensor([0, 8], dtype=torch.int32))
+    lp, _ = m.log_probs(h[:-1], toks[1:], with_entropy=False)
+    return lp.detach()
+
+
+def test_hf_checkpoint_loads_into_tp2_and_controller_flags(tmp_path):
+    import torch
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.orchestration.controller import Controller
+    from tests._mp import run_distributed
+
+    cfg = get_config("tiny")
+    src = GPTModel(cfg, seed=5)
+    d = str(tmp_path / "hf")
+    H.save_hf_checkpoint(d, cfg, H.convert_state_to_hf(cfg, {k: v.detach() for k, v in src.named_parameters()}))
+    toks = torch.arange(8) + 3
+    h = src(toks, torch.arange(8), torch.tensor([0, 8], dtype=torch.int32))
+    ref, _ = src.log_probs(h[:-1], toks[1:], with_entropy=False)
+    for lp in run_distributed(_hf_tp_worker, 2, d):
+        assert torch.allclose(lp, ref.detach(), atol=1e-5)
+    # the controller: --hf-checkpoint initialises policy, rollout weights and reference; --save-hf exports after a step
+    out = tmp_path / "ckpt"
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2",
+                    "--global-batch-size", "4", "--num-rollout", "1", "--rollout-max-response-len", "8", "--hf-checkpoint", d,
+                    "--save", str(out), "--save-interval", "1", "--save-hf", str(tmp_path / "export")])
+    c = Controller(a, device="cpu")
+    got = dict(c.runner.actor.model.named_parameters())
+    for k, v in src.named_parameters():
+        assert torch.equal(got[k].detach(), v.detach()), k
+    assert torch.equal(c.runner.engine.weights.p["final_norm"], src.decoder.final_layernorm.weight.detach())
+    c.training_loop()
+    exported = [p for p in (tmp_path / "export").iterdir()]
+    assert exported and H.is_hf_checkpoint(str(exported[0]))
+    back = H.hf_to_megatron_state(cfg, H.load_hf_checkpoint(str(exported[0])))
+    assert set(back) == {k for k, _ in src.named_parameters()}
