@@ -76,6 +76,9 @@ class ColocateConfig:
     # user code by path ("pkg.mod:fn" or "/file.py:fn"): generate(engine, samples, sampling_params) -> samples fills
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
+    dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
+    over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
+    stop_token_ids: tuple = ()
     custom_rm_path: Optional[str] = None
     eval_datasets: list = field(default_factory=list)
     eval_interval: Optional[int] = None
@@ -147,6 +150,9 @@ class ColocatedGRPO:
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
             else get_reward_spec(cfg.rm_type).fn
         self.custom_generate = load_generate_function(cfg.custom_generate_function_path, None)
+        self.group_filter = load_function(cfg.dynamic_sampling_filter_path, 1, "group filter") \
+            if cfg.dynamic_sampling_filter_path else None
+        self.sampling_stats: dict = {}
         self.timer = Timer()
         self.rollout_id = 0
         self.sync_weights()
@@ -170,20 +176,45 @@ class ColocatedGRPO:
         return ms
 
     # ------------------------------------------------------------------ rollout
-    def generate(self, rollout_id: int) -> list[Sample]:
-        cfg = self.cfg
-        groups_all = self.data_source.get_samples(cfg.rollout_batch_size)
-        per = cfg.rollout_batch_size // self.num_engines
-        mine = groups_all[self.engine_id * per:(self.engine_id + 1) * per]
-        sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
-                            max_new_tokens=cfg.max_response_len)
+    def _generate_groups(self, n_groups: int, sp) -> list:
+        """Draw ``n_groups`` prompt groups for this engine replica, generate and score them."""
+        groups_all = self.data_source.get_samples(n_groups * self.num_engines)
+        mine = groups_all[self.engine_id * n_groups:(self.engine_id + 1) * n_groups]
         flat = [s for g in mine for s in g]
         if self.custom_generate is not None:
-            flat = list(self.custom_generate(self.engine, flat, sp))
-            for s in flat:
+            done = list(self.custom_generate(self.engine, flat, sp))
+            for s in done:
                 if s.reward is None:
                     s.reward = self.reward_fn(s)
-            return flat
+            return mine
+        res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
+        for s, r in zip(flat, res):
+            s.tokens = list(r.prompt) + list(r.output)
+            s.response_length = len(r.output)
+            s.rollout_log_probs = list(r.logprobs)
+            s.weight_versions = sorted(set(r.weight_versions))
+            s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
+            s.reward = self.reward_fn(s)
+        return mine
+
+    def generate(self, rollout_id: int) -> list[Sample]:
+        """One rollout batch.  With a group filter (``dynamic_sampling_filter_path``, e.g.
+        ``relax_b200.rollout.filters:check_reward_nonzero_std``) the replica keeps generating
+        ``over_sampling_batch_size`` groups at a time until its share of the batch passed the filter (DAPO dynamic
+        sampling, relax/engine/rollout/sglang_rollout.py generate_rollout_async :763-1136)."""
+        cfg = self.cfg
+        per = cfg.rollout_batch_size // self.num_engines
+        sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
+                            max_new_tokens=cfg.max_response_len, stop_token_ids=tuple(cfg.stop_token_ids or ()))
+        if self.group_filter is None:
+            groups = self._generate_groups(per, sp)
+            self.sampling_stats = {}
+        else:
+            from ..rollout.filters import dynamic_sampling
+
+            over = max(per, (cfg.over_sampling_batch_size or cfg.rollout_batch_size) // self.num_engines)
+            groups, self.sampling_stats = dynamic_sampling(lambda n: self._generate_groups(n, sp), per, over, self.group_filter)
+        return [s for g in groups for s in g]
         res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
         for s, r in zip(flat, res):
             s.tokens = list(r.prompt) + list(r.output)
@@ -272,6 +303,7 @@ class ColocatedGRPO:
                  step_time=time.perf_counter() - t_all)
         m.update(self.timer.log_dict())
         m.update(eval_metrics)
+        m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
         self.rollout_id += 1
         return m
 

@@ -47,7 +47,11 @@ class Controller:
         if getattr(args, "lora_rank", 0):
             from ..train.lora import LoRAConfig
 
-            self.train_cfg.lora = LoRAConfig(rank=args.lora_rank, alpha=2.0 * args.lora_rank)
+            kw = {}
+            if _get(args, "lora_target_modules", None):
+                tm = args.lora_target_modules
+                kw["target_modules"] = tuple(tm.split(",")) if isinstance(tm, str) else tuple(tm)
+            self.train_cfg.lora = LoRAConfig(rank=args.lora_rank, alpha=float(_get(args, "lora_alpha", None) or 2.0 * args.lora_rank), **kw)
         self.mode = self._pick_mode()
         self._stop = False
         self.profiler = TrainProfiler(_get(args, "profile_dir", args.save and os.path.join(args.save, "profile")),
@@ -86,6 +90,9 @@ class Controller:
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),
                 custom_rm_path=_get(a, "custom_rm_path", None),
+                dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
+                over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
+                stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
                 skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,

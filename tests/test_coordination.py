@@ -179,3 +179,26 @@ def test_custom_generate_and_reward_paths_drive_the_colocated_loop(tmp_path):
     run = ColocatedGRPO(cfg)
     m = run.step()
     assert CG.load_object(f"{f}:CALLS") == [4] and 0.0 <= m["raw_reward_mean"] <= 1.0
+
+
+def test_dynamic_sampling_filter_in_the_colocated_loop():
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    cfg = ColocateConfig(model=get_config("tiny"), train=TrainConfig(global_batch_size=8, n_samples_per_prompt=4, pad_multiple=1,
+                         max_tokens_per_gpu=512, loss=LossConfig(), optim=OptimizerConfig(lr=1e-4)),
+                         rollout_batch_size=2, prompt_len=8, max_response_len=8, kv_blocks=128, num_prompts=64, rm_type="token_sum_parity",
+                         dynamic_sampling_filter_path="relax_b200.rollout.filters:check_reward_nonzero_std", over_sampling_batch_size=4,
+                         offload_rollout=False)
+    run = ColocatedGRPO(cfg)
+    m = run.step()
+    assert m["rollout/dynamic_sampling/generated_groups"] >= 4 and m["rollout/dynamic_sampling/rounds"] >= 1
+    # every kept group has mixed rewards, so no group is wasted on a zero advantage
+    samples = run.generate(1)
+    by_group = {}
+    for s in samples:
+        by_group.setdefault(s.group_index, []).append(s.reward)
+    assert len(by_group) == 2 and all(len(set(v)) > 1 for v in by_group.values())
