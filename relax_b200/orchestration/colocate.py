@@ -79,6 +79,17 @@ class ColocateConfig:
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
+    # prompts from JSONL files instead of synthetic ids; `codec` (data.tokenizer) turns prompts into ids and responses
+    # back into the text that rule rewards read
+    prompt_data: Optional[str] = None
+    input_key: str = "prompt"
+    label_key: Optional[str] = "label"
+    metadata_key: str = "metadata"
+    rollout_shuffle: bool = False
+    codec: Optional[object] = None
+    apply_chat_template: bool = False
+    apply_chat_template_kwargs: dict = field(default_factory=dict)
+    system_prompt: Optional[str] = None
     custom_rm_path: Optional[str] = None
     eval_datasets: list = field(default_factory=list)
     eval_interval: Optional[int] = None
@@ -143,8 +154,19 @@ class ColocatedGRPO:
         if not self._aligned and not (ttp == 1 or rtp == 1 or ttp == rtp):
             raise NotImplementedError("colocated sync needs trainer TP group == rollout engine ranks, or TP 1 on one side")
         self.queue = tq.init({"capacity_partitions": 2})
-        ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
-        self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt)
+        if cfg.prompt_data:
+            from ..data.tokenizer import ByteCodec, PromptEncoder
+            from ..rollout.data_source import JsonlPromptDataset
+
+            self.codec = cfg.codec or ByteCodec(cfg.model.vocab_size)
+            enc = PromptEncoder(self.codec, cfg.apply_chat_template, cfg.apply_chat_template_kwargs, cfg.system_prompt, cfg.prompt_len)
+            ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key)
+            if len(ds) == 0:
+                raise ValueError(f"no usable prompt in {cfg.prompt_data} (limit {cfg.prompt_len} tokens)")
+        else:
+            self.codec = cfg.codec
+            ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
+        self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
         from ..rollout.custom_generate import load_function, load_generate_function
 
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
@@ -194,6 +216,8 @@ class ColocatedGRPO:
             s.rollout_log_probs = list(r.logprobs)
             s.weight_versions = sorted(set(r.weight_versions))
             s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
+            if self.codec is not None:
+                s.response = self.codec.decode(r.output)
             s.reward = self.reward_fn(s)
         return mine
 
@@ -237,7 +261,7 @@ class ColocatedGRPO:
         sp = SamplingParams(temperature=cfg.eval_temperature, top_p=1.0, top_k=-1,
                             max_new_tokens=cfg.eval_max_response_len or cfg.max_response_len)
         with self.timer.span("eval"):
-            m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp)
+            m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp, decode=self.codec.decode if self.codec is not None else None)
         if cfg.offload_rollout:
             self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
         return m

@@ -31,6 +31,13 @@ def _get(a, name, default=None):
 
 
 class Controller:
+    def _codec(self, a):
+        from ..data.tokenizer import build_codec
+
+        if not (_get(a, "prompt_data", None) or _get(a, "eval_prompt_data", None)):
+            return None
+        return build_codec(_get(a, "hf_checkpoint", None), self.model_cfg.vocab_size)
+
     def _eval_sets(self, a):
         return _eval_sets_from_args(a, self.model_cfg.vocab_size)
 
@@ -83,6 +90,7 @@ class Controller:
                 rollout_batch_size=a.rollout_batch_size, prompt_len=plen,
                 max_response_len=a.rollout_max_response_len, temperature=a.rollout_temperature,
                 top_p=_get(a, "rollout_top_p", 1.0), top_k=_get(a, "rollout_top_k", -1), rm_type=a.rm_type or "parity",
+                eos_token_id=getattr(self._codec(a), "eos_token_id", None),
                 kv_blocks=_get(a, "kv_blocks", max(64, a.rollout_batch_size * a.n_samples_per_prompt * (ctx // 16 + 2))),
                 kv_block_size=page if page > 1 else 16,
                 max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
@@ -90,6 +98,12 @@ class Controller:
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),
                 custom_rm_path=_get(a, "custom_rm_path", None),
+                prompt_data=_get(a, "prompt_data", None), input_key=_get(a, "input_key", None) or "prompt",
+                label_key=_get(a, "label_key", None), metadata_key=_get(a, "metadata_key", None) or "metadata",
+                rollout_shuffle=bool(_get(a, "rollout_shuffle", False)), codec=self._codec(a),
+                apply_chat_template=bool(_get(a, "apply_chat_template", False)),
+                apply_chat_template_kwargs=_get(a, "apply_chat_template_kwargs", None) or {},
+                system_prompt=_get(a, "system_prompt", None),
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
                 stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
@@ -260,8 +274,10 @@ def _eval_sets_from_args(a, vocab: int):
     if getattr(a, "eval_config", None):
         with open(a.eval_config) as f:
             overrides = _json.load(f)
-    tok = _byte_tokenizer(vocab)
-    enc = lambda p: tok(p if isinstance(p, str) else " ".join(str(m.get("content", "")) for m in p))
+    from ..data.tokenizer import PromptEncoder, build_codec
+
+    enc = PromptEncoder(build_codec(getattr(a, "hf_checkpoint", None), vocab), bool(getattr(a, "apply_chat_template", False)),
+                        getattr(a, "apply_chat_template_kwargs", None) or {}, getattr(a, "system_prompt", None))
     sets = load_eval_datasets(pairs, enc, getattr(a, "eval_input_key", None) or "prompt", getattr(a, "eval_label_key", None) or "label",
                               getattr(a, "n_samples_per_eval_prompt", 1), getattr(a, "eval_size", None),
                               getattr(a, "eval_max_prompt_len", None), overrides)

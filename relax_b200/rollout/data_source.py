@@ -35,9 +35,25 @@ class SyntheticPromptDataset:
 class JsonlPromptDataset:
     """``{"prompt": ..., "label": ...}`` per line; tokenised lazily by ``tokenize``."""
 
-    def __init__(self, path: str, tokenize: Optional[Callable] = None, prompt_key="prompt", label_key="label"):
-        self.rows = [json.loads(l) for l in open(path) if l.strip()]
-        self.tokenize, self.prompt_key, self.label_key = tokenize, prompt_key, label_key
+    def __init__(self, path: str, tokenize: Optional[Callable] = None, prompt_key="prompt", label_key="label",
+                 metadata_key: str = "metadata"):
+        """``path`` may list several files separated by commas.  Rows whose prompt ``tokenize`` rejects (returns
+        None: longer than the prompt limit) are dropped at load time, so the epoch length is known up front."""
+        self.rows = []
+        for one in str(path).split(","):
+            if one:
+                with open(one, encoding="utf-8") as f:
+                    self.rows += [json.loads(l) for l in f if l.strip()]
+        self.tokenize, self.prompt_key, self.label_key, self.metadata_key = tokenize, prompt_key, label_key, metadata_key
+        if tokenize is not None:
+            kept = []
+            for r in self.rows:
+                toks = tokenize(r[prompt_key])
+                if toks is not None:
+                    r["_tokens"] = toks
+                    kept.append(r)
+            self.dropped = len(self.rows) - len(kept)
+            self.rows = kept
 
     def __len__(self):
         return len(self.rows)
@@ -45,8 +61,9 @@ class JsonlPromptDataset:
     def __getitem__(self, i):
         r = self.rows[i]
         p = r[self.prompt_key]
-        toks = self.tokenize(p) if self.tokenize else list(p)
-        return {"prompt": p, "prompt_tokens": toks, "label": r.get(self.label_key), "metadata": r.get("metadata", {})}
+        toks = r["_tokens"] if "_tokens" in r else list(p)
+        return {"prompt": p, "prompt_tokens": toks, "label": r.get(self.label_key) if self.label_key else None,
+                "metadata": r.get(self.metadata_key) or {}}
 
 
 class RolloutDataSource:

@@ -1,0 +1,53 @@
+"""RL prompts from JSONL files: codec, chat rendering, length filter, text rewards on decoded responses (CPU)."""
+import json
+
+from relax_b200.data.tokenizer import ByteCodec, PromptEncoder, build_codec, has_tokenizer_files
+from relax_b200.rollout.data_source import JsonlPromptDataset, RolloutDataSource
+
+
+def test_codec_roundtrip_and_prompt_encoder():
+    c = ByteCodec(1024)
+    ids = c.encode("héllo Answer: 42")
+    assert c.decode(ids) == "héllo Answer: 42" and min(ids) >= 3
+    assert c.decode([0, 1, 2, 900] + c.encode("ok")) == "ok"            # special / out-of-range ids decode to nothing
+    plain = PromptEncoder(c, system_prompt="Be brief.")
+    assert c.decode(plain("2+2?")) == "Be brief.\n2+2?"
+    chat = PromptEncoder(c, apply_chat_template=True, system_prompt="Be brief.", max_prompt_len=200)
+    text = c.decode(chat([{"role": "user", "content": [{"type": "image", "image": "x.png"}, {"type": "text", "text": "what?"}]}]))
+    assert text.startswith("<|system|>\nBe brief.\n<|user|>\nwhat?\n") and text.endswith("<|assistant|>\n")
+    assert chat("x" * 500) is None
+    assert not has_tokenizer_files(None) and isinstance(build_codec(None, 512), ByteCodec)
+
+
+def test_jsonl_dataset_filters_and_feeds_the_data_source(tmp_path):
+    f1, f2 = tmp_path / "a.jsonl", tmp_path / "b.jsonl"
+    f1.write_text(json.dumps({"q": "short one", "ans": 1, "meta": {"data_source": "gsm8k"}}) + "\n" + json.dumps({"q": "y" * 300, "ans": 2}) + "\n")
+    f2.write_text(json.dumps({"q": "another", "ans": 3}) + "\n")
+    enc = PromptEncoder(ByteCodec(1024), max_prompt_len=64)
+    ds = JsonlPromptDataset(f"{f1},{f2}", enc, "q", "ans", "meta")
+    assert len(ds) == 2 and ds.dropped == 1 and ds[0]["label"] == 1 and ds[0]["metadata"] == {"data_source": "gsm8k"}
+    src = RolloutDataSource(ds, 2, shuffle=True, seed=1)
+    groups = src.get_samples(3)                  # wraps into the second epoch
+    assert len(groups) == 3 and all(len(g) == 2 for g in groups) and src.epoch == 1
+    assert {g[0].label for g in groups} == {1, 3}
+
+
+def test_colocated_loop_on_prompt_files_scores_decoded_text(tmp_path):
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "train.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"What is {i}+{i}?", "label": str(2 * i)}) for i in range(6)) + "\n")
+    user = tmp_path / "rm.py"
+    user.write_text("SEEN = []\ndef rm(sample):\n    SEEN.append((sample.prompt, sample.response, sample.label))\n    return float(len(sample.response) % 2)\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--prompt-data", str(f), "--input-key", "prompt",
+                    "--label-key", "label", "--custom-rm-path", f"{user}:rm", "--rollout-shuffle"])
+    c = Controller(a, device="cpu")
+    m = c.runner.step()
+    from relax_b200.rollout.custom_generate import load_object
+
+    seen = load_object(f"{user}:SEEN")
+    assert len(seen) == 4 and all(p.startswith("What is") and isinstance(r, str) and lab.isdigit() for p, r, lab in seen)
+    assert 0.0 <= m["raw_reward_mean"] <= 1.0
