@@ -53,6 +53,10 @@ class TrainConfig:
     compute_entropy: bool = True
     ref_on_host: bool = False           # keep the frozen reference weights in pinned host memory
     lora: Optional[object] = None       # a train.lora.LoRAConfig: train adapters only
+    # regular expressions on parameter names: freeze the matches / train only the matches
+    # (relax/backends/megatron/model_provider.py freeze :603-639)
+    freeze_params_name_list: Optional[Sequence[str]] = None
+    only_train_params_name_list: Optional[Sequence[str]] = None
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
     mtp_only_training: bool = False     # freeze the trunk, train the MTP blocks alone
@@ -86,6 +90,18 @@ class TrainActor:
         if cfg.mtp_only_training:
             for n, p in self.model.named_parameters():
                 p.requires_grad_(n.startswith("mtp."))
+        if cfg.freeze_params_name_list or cfg.only_train_params_name_list:
+            import re
+
+            fr = [re.compile(x) for x in (cfg.freeze_params_name_list or [])]
+            only = [re.compile(x) for x in (cfg.only_train_params_name_list or [])]
+            for n, p in self.model.named_parameters():
+                if not p.requires_grad:
+                    continue
+                if any(r.search(n) for r in fr) or (only and not any(r.search(n) for r in only)):
+                    p.requires_grad_(False)
+            if not any(p.requires_grad for p in self.model.parameters()):
+                raise ValueError("the freeze lists leave no trainable parameter")
         self.optimizer = DistributedOptimizer(self.model, self.ps, cfg.optim) if with_optimizer else None
         self.timer = Timer()
         self.weight_version = 0

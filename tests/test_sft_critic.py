@@ -87,3 +87,23 @@ def test_critic_fits_returns():
     v1 = actor.compute_values(batch)["values"]
     err1 = sum(float(((v - 1.0) ** 2).sum()) for v in v1)
     assert err1 < 0.5 * err0 and "value_loss" in m
+
+
+def test_freeze_and_only_train_lists():
+    import pytest
+    from relax_b200.config.arguments import parse_args, train_config_from_args
+
+    a = parse_args(["--model-name", "tiny", "--colocate", "--only-train-params-name-list", r"layers\.1\.", "--freeze-params-name-list", "layer_norm"])
+    tc = train_config_from_args(a)
+    tc.global_batch_size, tc.pad_multiple, tc.max_tokens_per_gpu = 4, 1, 256
+    actor = TrainActor(get_config("tiny"), tc, role="sft")
+    names = [n for n, p in actor.model.named_parameters() if p.requires_grad]
+    assert names and all(".layers.1." in n and "layer_norm" not in n for n in names)
+    before = {n: p.detach().clone() for n, p in actor.model.named_parameters()}
+    samples = [to_train_sample(*render_chat([{"role": "user", "content": "ab"}, {"role": "assistant", "content": "cdcd"}], _tok)) for _ in range(4)]
+    actor.train_sft({"tokens": [s["tokens"] for s in samples], "response_lengths": [s["response_length"] for s in samples],
+                     "loss_masks": [s["loss_mask"] for s in samples]})
+    changed = {n for n, p in actor.model.named_parameters() if not torch.equal(p, before[n])}
+    assert changed and changed <= set(names)
+    with pytest.raises(ValueError):
+        TrainActor(get_config("tiny"), _cfg().__class__(only_train_params_name_list=["nothing_matches"]), role="sft")
