@@ -79,6 +79,7 @@ class ColocateConfig:
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
+    critic_lr: Optional[float] = None
     # prompts from JSONL files instead of synthetic ids; `codec` (data.tokenizer) turns prompts into ids and responses
     # back into the text that rule rewards read
     prompt_data: Optional[str] = None
@@ -137,6 +138,15 @@ class ColocatedGRPO:
         need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
         cfg.train.n_samples_per_prompt = cfg.train.n_samples_per_prompt
         self.actor = TrainActor(cfg.model, cfg.train, self.ps, device=device, seed=cfg.seed, with_reference=need_ref)
+        # PPO: a value model of the same shape on the same ranks (relax/components/critic.py; separate optimizer and
+        # learning rate), scored before and trained after every policy update
+        self.critic = None
+        if cfg.train.advantage_estimator in ("ppo", "gae"):
+            from dataclasses import replace as _replace
+
+            ccfg = _replace(cfg.train, optim=_replace(cfg.train.optim, lr=cfg.critic_lr or cfg.train.optim.lr), lora=None)
+            self.critic = TrainActor(_replace(cfg.model, value_head=True, mtp_num_layers=0), ccfg, self.ps, device=device,
+                                     seed=cfg.seed + 1, role="critic")
         if cfg.release_rollout_weights and self.actor.optimizer is not None:
             self.actor.optimizer.release_grads()   # before the engine allocates its weights and KV cache
             if self.device.type == "cuda":
@@ -308,8 +318,13 @@ class ColocatedGRPO:
                 self.actor.optimizer.allocate_grads()
             if cfg.offload_train:
                 self.actor.wake_up()
+            if self.critic is not None:
+                data["values"] = self.critic.compute_values(data)["values"]
             m = self.actor.train(rid, data)
             self.actor.after_train()
+            if self.critic is not None:       # `data` now carries the GAE returns computed with those values
+                cm = self.critic.train_critic(rid, data)
+                m.update({f"critic/{k}": v for k, v in cm.items()})
             if cfg.offload_train:
                 self.actor.sleep()
             if cfg.release_rollout_weights:

@@ -106,7 +106,7 @@ class Controller:
                 system_prompt=_get(a, "system_prompt", None),
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
-                stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
+                stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()), critic_lr=_get(a, "critic_lr", None),
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
                 skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,

@@ -107,3 +107,21 @@ def test_freeze_and_only_train_lists():
     assert changed and changed <= set(names)
     with pytest.raises(ValueError):
         TrainActor(get_config("tiny"), _cfg().__class__(only_train_params_name_list=["nothing_matches"]), role="sft")
+
+
+def test_ppo_with_critic_in_the_colocated_loop():
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+
+    cfg = ColocateConfig(model=get_config("tiny"),
+                         train=TrainConfig(advantage_estimator="ppo", global_batch_size=4, n_samples_per_prompt=2, pad_multiple=1,
+                                           max_tokens_per_gpu=256, gamma=1.0, lambd=0.95, loss=LossConfig(),
+                                           optim=OptimizerConfig(lr=1e-4)),
+                         rollout_batch_size=2, prompt_len=8, max_response_len=8, kv_blocks=64, num_prompts=16,
+                         rm_type="token_sum_parity", critic_lr=5e-3)
+    run = ColocatedGRPO(cfg)
+    assert run.critic is not None and run.critic.role == "critic" and run.critic.cfg.optim.lr == 5e-3
+    w0 = run.critic.model.value_head.weight.detach().clone()
+    m = run.step()
+    assert "critic/loss" in m or any(k.startswith("critic/") for k in m)
+    assert not torch.equal(run.critic.model.value_head.weight.detach(), w0)      # the critic was updated
+    assert math.isfinite(m["grad_norm"])
