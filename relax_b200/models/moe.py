@@ -32,10 +32,19 @@ class RoutingReplay:
     mode: Optional[str] = None  # None | "record" | "replay"
     store: dict = {}
     cursor: dict = {}
+    # per-sample form: when a layout (sample ids and token counts of the packed micro-batch) is set, decisions are
+    # stored per (layer, sample) and re-assembled for whatever micro-batch the sample lands in at replay time, so
+    # the recording forward and the training forward may pack their micro-batches differently
+    layout: Optional[tuple] = None
+    per_sample: dict = {}
+
+    @classmethod
+    def set_layout(cls, sample_ids, lengths):
+        cls.layout = (list(sample_ids), [int(x) for x in lengths]) if sample_ids is not None else None
 
     @classmethod
     def begin_record(cls):
-        cls.mode, cls.store = "record", {}
+        cls.mode, cls.store, cls.per_sample = "record", {}, {}
 
     @classmethod
     def begin_replay(cls, store: Optional[dict] = None):
@@ -46,10 +55,28 @@ class RoutingReplay:
 
     @classmethod
     def end(cls):
-        cls.mode = None
+        cls.mode, cls.layout = None, None
 
     @classmethod
     def route(cls, layer_idx: int, idx: torch.Tensor) -> torch.Tensor:
+        if cls.mode is not None and cls.layout is not None:
+            ids, lens = cls.layout
+            if sum(lens) > idx.shape[0]:
+                raise ValueError("per-sample routing replay needs the whole packed micro-batch on this rank (tp = 1)")
+            if cls.mode == "record":
+                o = 0
+                for sid, n in zip(ids, lens):
+                    cls.per_sample[(layer_idx, sid)] = idx[o:o + n].detach().clone()
+                    o += n
+                return idx
+            parts = []
+            for sid, n in zip(ids, lens):
+                rec = cls.per_sample.get((layer_idx, sid))
+                if rec is None or rec.shape[0] != n:
+                    raise ValueError(f"no recorded routing for sample {sid} at layer {layer_idx}")
+                parts.append(rec.to(idx.device))
+            tail = idx[sum(lens):]                       # padding rows keep the router's own choice
+            return torch.cat(parts + [tail]) if parts else idx
         if cls.mode == "record":
             cls.store.setdefault(layer_idx, []).append(idx.detach().clone())
             return idx

@@ -57,6 +57,9 @@ class TrainConfig:
     # (relax/backends/megatron/model_provider.py freeze :603-639)
     freeze_params_name_list: Optional[Sequence[str]] = None
     only_train_params_name_list: Optional[Sequence[str]] = None
+    # MoE: the expert choices of the old-policy forward are replayed in the training forward, so both evaluate the
+    # same experts (--use-routing-replay; relax/backends/megatron/actor.py fill_routing_replay :534-641)
+    use_routing_replay: bool = False
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
     mtp_only_training: bool = False     # freeze the trunk, train the MTP blocks alone
@@ -213,6 +216,10 @@ class TrainActor:
         return torch.cat(lps), torch.cat(ens)
 
     def _forward_logp(self, pb, with_entropy: bool):
+        if self.cfg.use_routing_replay and self.mcfg.is_moe:
+            from ..models.moe import RoutingReplay
+
+            RoutingReplay.set_layout(getattr(self, "_cur_ids", None), pb.total_lengths)
         if self.ps.cp.size > 1:
             return self._forward_logp_cp(pb, with_entropy)
         h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
@@ -300,6 +307,7 @@ class TrainActor:
                 self._dummy_forward()
                 continue
             pb = self._pack([toks[i] for i in mb], [rl[i] for i in mb])
+            self._cur_ids = list(mb)
             lp, en = self._forward_logp(pb, with_entropy)
             for i, a, b in zip(mb, torch.split(lp, pb.response_lengths), torch.split(en, pb.response_lengths)):
                 out_lp[i], out_en[i] = a, b
@@ -354,7 +362,15 @@ class TrainActor:
                 batch["log_probs"] = [torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch["rollout_log_probs"]]
             elif not cfg.loss.true_on_policy:
                 tag = "old_actor" if (cfg.keep_old_actor and "old_actor" in self.snapshots) else "actor"
+                replay = cfg.use_routing_replay and self.mcfg.is_moe
+                if replay:
+                    from ..models.moe import RoutingReplay
+
+                    RoutingReplay.begin_record()
                 batch["log_probs"] = self.compute_log_prob(batch, tag)["log_probs"]
+                if replay:
+                    RoutingReplay.end()
+                    RoutingReplay.begin_replay()          # until the end of this rollout's optimizer steps
 
         seg_all = Segments.from_lengths(resp, device=dev)
         mask_all = torch.cat(masks) if masks else torch.zeros(0, device=dev)
@@ -384,6 +400,10 @@ class TrainActor:
                 m, last_norm = self._train_step(batch, idx)
             for k, v in m.items():
                 agg[k] = agg.get(k, 0) + v / int(nsteps)
+        if cfg.use_routing_replay and self.mcfg.is_moe:
+            from ..models.moe import RoutingReplay
+
+            RoutingReplay.end()
         out = {k: float(v) for k, v in agg.items()}
         out["grad_norm"] = last_norm
         out["train_time"] = time.perf_counter() - t0
@@ -417,6 +437,7 @@ class TrainActor:
                 self._dummy_forward(backward=True)
                 continue
             ids = [idx[j] for j in mb]
+            self._cur_ids = list(ids)
             pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
             lb = self._loss_batch(batch, ids, pb)
             use_mtp = (cfg.enable_mtp_training or cfg.mtp_only_training) and self.mcfg.mtp_num_layers > 0

@@ -40,3 +40,43 @@ def test_disabled_recorder_is_free(tmp_path):
     assert small.capture("advantages", 0, {}, {}) is None
     assert small.capture("loss", 0, {"x": torch.ones(1)}, {"y": 1.0}) is not None
     assert small.capture("loss", 1, {"x": torch.ones(1)}, {"y": 1.0}) is None
+
+
+def test_routing_replay_in_the_trainer_survives_different_microbatching():
+    """The old-policy forward packs all samples in one micro-batch, the training steps pack them two at a time: the
+    per-sample store re-assembles the recorded expert choices, and the first training forward reproduces the
+    old-policy log-probs exactly (ratio 1) even though a perturbed router would choose differently."""
+    import torch
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.models.moe import RoutingReplay
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    torch.manual_seed(0)
+    cfg = TrainConfig(advantage_estimator="grpo", global_batch_size=2, n_samples_per_prompt=2, max_tokens_per_gpu=1024, pad_multiple=1,
+                      use_routing_replay=True, loss=LossConfig(), optim=OptimizerConfig(lr=0.0))
+    actor = TrainActor(get_config("tiny-moe"), cfg, role="actor")
+    g = torch.Generator().manual_seed(1)
+    toks = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (12, 9, 14, 10)]
+    rl = [5, 4, 6, 3]
+    batch = {"tokens": toks, "response_lengths": rl, "loss_masks": [[1.0] * r for r in rl], "rewards": [1.0, 0.0, 0.0, 1.0]}
+    seen = []
+    orig = RoutingReplay.route.__func__
+
+    def spy(cls, layer, idx):
+        out = orig(cls, layer, idx)
+        seen.append((cls.mode, layer, idx.shape[0], bool((out != idx).any()) if out.shape == idx.shape else None))
+        return out
+
+    RoutingReplay.route = classmethod(spy)
+    try:
+        m = actor.train(0, batch)
+    finally:
+        RoutingReplay.route = classmethod(orig)
+    modes = [s[0] for s in seen]
+    assert "record" in modes and "replay" in modes and RoutingReplay.mode is None
+    rec_rows = {s[2] for s in seen if s[0] == "record"}
+    rep_rows = {s[2] for s in seen if s[0] == "replay"}
+    assert rec_rows == {45} and rep_rows == {21, 24}            # one micro-batch of 4 samples vs two steps of 2
+    assert abs(m["ppo_kl"]) < 1e-6 and m["pg_clipfrac"] == 0.0
