@@ -16,6 +16,7 @@ relax/backends/megatron/actor.py:724-842).  Per step:
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Optional
@@ -80,6 +81,9 @@ class ColocateConfig:
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
     critic_lr: Optional[float] = None
+    log_passrate: bool = False                      # rollout/pass@k over the training groups (reward > 0.5 = correct)
+    save_debug_train_data: Optional[str] = None     # directory: the training batch of every step as train_<id>.pt
+    load_debug_rollout_data: Optional[str] = None   # directory of rollout_<id>.jsonl dumps replayed instead of generating
     # prompts from JSONL files instead of synthetic ids; `codec` (data.tokenizer) turns prompts into ids and responses
     # back into the text that rule rewards read
     prompt_data: Optional[str] = None
@@ -259,6 +263,36 @@ class ColocatedGRPO:
             s.reward = self.reward_fn(s)
         return flat
 
+    @property
+    def _rank(self) -> int:
+        return dist.get_rank() if dist.is_initialized() else 0
+
+    def _load_dumped_rollout(self, rid: int) -> list[Sample]:
+        """Replay a dumped rollout step (``--load-debug-rollout-data``): trainer-side debugging with the rollout
+        engine out of the loop; tokens, rewards and rollout log-probs come from the file."""
+        from ..utils.visualize import load_step
+
+        _, rows = load_step(cfg_dir := self.cfg.load_debug_rollout_data, rid)
+        out = []
+        for r in rows:
+            r = dict(r)
+            st = r.pop("status", "completed")
+            s = Sample(**{k: v for k, v in r.items() if k in Sample.__dataclass_fields__})
+            s.status = SampleStatus(st)
+            out.append(s)
+        if not out:
+            raise FileNotFoundError(f"no samples for rollout {rid} under {cfg_dir}")
+        return out
+
+    def _passrate(self, samples) -> dict:
+        from ..rollout.evaluation import summarize
+
+        groups: dict = {}
+        for s in samples:
+            groups.setdefault(s.group_index, []).append(s)
+        m = summarize("train", list(groups.values()))
+        return {k.replace("eval/train", "rollout/pass"): v for k, v in m.items() if "-pass@" in k}
+
     # ------------------------------------------------------------------ evaluation
     def evaluate(self) -> dict:
         """Evaluation rollout on every configured set with the current weights; engine replicas split nothing here
@@ -292,13 +326,14 @@ class ColocatedGRPO:
         with self.timer.span("rollout"):
             if cfg.offload_rollout:
                 self.engine.resume_memory_occupation(("kv_cache",))
-            samples = self.generate(rid)
+            samples = self._load_dumped_rollout(rid) if cfg.load_debug_rollout_data else self.generate(rid)
             if cfg.offload_rollout:
                 self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
-            if cfg.save_debug_rollout_data and self.ps.rank == 0:
+            if cfg.save_debug_rollout_data and self._rank == 0:
                 from ..utils.visualize import dump_rollout
 
                 dump_rollout(cfg.save_debug_rollout_data, rid, samples, extra={"weight_version": self.actor.weight_version})
+        pass_metrics = self._passrate(samples) if cfg.log_passrate else {}
         with self.timer.span("data"):
             batch = convert_samples_to_train_data(
                 samples, advantage_estimator=cfg.train.advantage_estimator,
@@ -320,6 +355,9 @@ class ColocatedGRPO:
                 self.actor.wake_up()
             if self.critic is not None:
                 data["values"] = self.critic.compute_values(data)["values"]
+            if cfg.save_debug_train_data:
+                os.makedirs(cfg.save_debug_train_data, exist_ok=True)
+                torch.save({k: v for k, v in data.items()}, os.path.join(cfg.save_debug_train_data, f"train_{rid}_rank{self._rank}.pt"))
             m = self.actor.train(rid, data)
             self.actor.after_train()
             if self.critic is not None:       # `data` now carries the GAE returns computed with those values
@@ -342,6 +380,7 @@ class ColocatedGRPO:
                  step_time=time.perf_counter() - t_all)
         m.update(self.timer.log_dict())
         m.update(eval_metrics)
+        m.update(pass_metrics)
         m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
         self.rollout_id += 1
         return m

@@ -107,6 +107,8 @@ class Controller:
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
                 stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()), critic_lr=_get(a, "critic_lr", None),
+                log_passrate=bool(_get(a, "log_passrate", False)), save_debug_train_data=_get(a, "save_debug_train_data", None),
+                load_debug_rollout_data=_get(a, "load_debug_rollout_data", None),
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
                 skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,
@@ -207,9 +209,18 @@ class Controller:
                 self.save(max(r for r, _ in out))
             return out
         rid = self.start_rollout_id
+        if a.num_rollout is None and _get(a, "num_epoch", None) and hasattr(self.runner, "data_source"):
+            # --num-epoch: as many rollouts as it takes to see every prompt that many times
+            a.num_rollout = max(1, a.num_epoch * len(self.runner.data_source.dataset) // max(1, a.rollout_batch_size))
+        ref_every = _get(a, "ref_update_interval", None)
         while rid < a.num_rollout and not self._stop:
             t0 = time.perf_counter()
             m = self.runner.step()
+            actor = self._actor()
+            if ref_every and actor is not None and "ref" in actor.snapshots and (rid + 1) % ref_every == 0:
+                # --ref-update-interval: the reference follows the policy every N rollouts
+                actor.backup("ref", to_host=not actor.snapshots["ref"].is_cuda and actor.device.type == "cuda")
+                m["ref_updated"] = 1.0
             dt = time.perf_counter() - t0
             rec = {k: float(v) for k, v in m.items() if isinstance(v, (int, float))}
             rec["perf/step_time"] = dt

@@ -74,3 +74,32 @@ def test_entrypoint_flags_reach_the_loop(tmp_path):
     runner = c.runner if hasattr(c, "runner") else c.build_runner()
     m = runner.step()
     assert m["eval/held/num_prompts"] == 3.0 and "eval/held-pass@2" in m and m["eval/held/response_len/max"] <= 4
+
+
+def test_dump_replay_passrate_epochs_and_reference_refresh(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "train.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"q{i}", "label": str(i)}) for i in range(4)) + "\n")
+    common = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+              "--rollout-max-response-len", "8", "--rm-type", "token_sum_parity", "--prompt-data", str(f), "--input-key", "prompt",
+              "--label-key", "label"]
+    dumps, train = tmp_path / "dumps", tmp_path / "train_data"
+    a = parse_args(common + ["--num-epoch", "1", "--save-debug-rollout-data", str(dumps), "--save-debug-train-data", str(train),
+                             "--log-passrate", "--use-kl-loss", "--kl-loss-coef", "0.01", "--ref-update-interval", "2"])
+    c = Controller(a, device="cpu")
+    hist = c.training_loop()
+    assert len(hist) == 2 and a.num_rollout == 2                       # 4 prompts / 2 per rollout, one epoch
+    assert "rollout/pass-pass@1" in hist[0] and "rollout/pass-pass@2" in hist[0]
+    assert "ref_updated" not in hist[0] and hist[1].get("ref_updated") == 1.0
+    assert sorted(p.name for p in dumps.iterdir()) == ["rollout_0.jsonl", "rollout_1.jsonl"]
+    saved = torch.load(train / "train_0_rank0.pt")
+    assert len(saved["tokens"]) == 4 and "rewards" in saved
+    # replay the dumped rollouts through the trainer: same rewards, no generation
+    b = parse_args(common + ["--num-rollout", "1", "--load-debug-rollout-data", str(dumps)])
+    c2 = Controller(b, device="cpu")
+    calls = []
+    c2.runner.engine.generate = lambda *x, **k: calls.append(1)
+    m = c2.runner.step()
+    assert not calls and abs(m["raw_reward_mean"] - hist[0]["raw_reward_mean"]) < 1e-9
