@@ -401,6 +401,7 @@ def train_config_from_args(a):
         recompute=a.recompute_granularity == "full", pad_multiple=a.data_pad_size_multiplier,
         use_rollout_logprobs=a.use_rollout_logprobs, keep_old_actor=a.keep_old_actor,
         enable_mtp_training=a.enable_mtp_training, mtp_loss_scaling_factor=a.mtp_loss_scaling_factor,
-        mtp_only_training=a.mtp_only_training, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
+        mtp_only_training=a.mtp_only_training,
+        opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         freeze_params_name_list=getattr(a, "freeze_params_name_list", None),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim)

@@ -147,6 +147,13 @@ class Controller:
                 actor.backup("ref")
             if hasattr(self.runner, "sync_weights"):
                 self.runner.sync_weights()
+        teacher = _get(a, "opd_teacher_load", None)
+        if teacher and _get(a, "opd_type", None) and ("://" in teacher or H.is_hf_checkpoint(teacher)):
+            # --opd-type megatron --opd-teacher-load <hf dir>: a teacher of the policy's shape kept as a weight snapshot
+            keep = actor.param_buf.clone()
+            H.load_hf_into_model(teacher, self.model_cfg, actor.ps, actor.model)
+            actor.backup("teacher", to_host=actor.device.type == "cuda")
+            actor.param_buf.copy_(keep)
         ref = _get(a, "ref_load", None)
         if ref and ref != src and ("://" in ref or H.is_hf_checkpoint(ref)) and "ref" in actor.snapshots:
             keep = actor.param_buf.clone()

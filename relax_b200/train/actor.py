@@ -60,6 +60,12 @@ class TrainConfig:
     # MoE: the expert choices of the old-policy forward are replayed in the training forward, so both evaluate the
     # same experts (--use-routing-replay; relax/backends/megatron/actor.py fill_routing_replay :534-641)
     use_routing_replay: bool = False
+    # on-policy distillation: per-token divergence between the policy and a teacher on the sampled tokens, applied to
+    # the advantages as a dense penalty (relax/utils/opd/opd_utils.py apply_opd_to_advantages :1275).  The teacher's
+    # log-probs come with the batch (``teacher_log_probs``, external teacher) or from the ``teacher`` weight snapshot.
+    opd_kl_coef: float = 0.0
+    opd_kl_type: str = "reverse_kl"
+    opd_per_token_clip: Optional[float] = None
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
     mtp_only_training: bool = False     # freeze the trunk, train the MTP blocks alone
@@ -385,6 +391,20 @@ class TrainActor:
         )
         batch["advantages"] = seg_all.split(adv)
         batch["returns"] = seg_all.split(ret)
+        opd_metric = None
+        if cfg.opd_kl_coef != 0.0 and (batch.get("teacher_log_probs") is not None or "teacher" in self.snapshots):
+            from ..algo import opd as OPD
+
+            with self.timer.span("teacher_log_probs"):
+                if batch.get("teacher_log_probs") is None:
+                    batch["teacher_log_probs"] = self.compute_log_prob(batch, "teacher")["log_probs"]
+            student = batch.get("log_probs") or self.compute_log_prob(batch, "actor")["log_probs"]
+            sig = [OPD.per_token_signal("sampled_token", student_lp=torch.as_tensor(a, dtype=torch.float32, device=dev),
+                                        teacher_lp=torch.as_tensor(b, dtype=torch.float32, device=dev), kl_type=cfg.opd_kl_type)
+                   for a, b in zip(student, batch["teacher_log_probs"])]
+            batch["advantages"] = OPD.apply_to_advantages(list(batch["advantages"]), sig, cfg.opd_kl_coef, cfg.opd_per_token_clip)
+            tot = sum(float((d * m).sum()) for d, m in zip(sig, masks))
+            opd_metric = tot / max(1.0, float(mask_all.sum()))
 
         dp = self.ps.dp.size
         per_step = max(1, cfg.global_batch_size // dp)
@@ -405,6 +425,8 @@ class TrainActor:
 
             RoutingReplay.end()
         out = {k: float(v) for k, v in agg.items()}
+        if opd_metric is not None:
+            out["opd_kl"] = opd_metric
         out["grad_norm"] = last_norm
         out["train_time"] = time.perf_counter() - t0
         return out

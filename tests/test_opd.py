@@ -100,3 +100,30 @@ def test_teacher_pool_splits_work_and_fails_over():
     assert pool.healthy() == [0, 1]
     with pytest.raises(RuntimeError):
         TeacherPool([T(1, fail=True)]).score(batch)
+
+
+def test_opd_penalty_in_the_trainer_pulls_towards_the_teacher(tmp_path):
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.orchestration.controller import Controller
+
+    cfg = get_config("tiny")
+    teacher = GPTModel(cfg, seed=77)
+    d = str(tmp_path / "teacher")
+    H.save_hf_checkpoint(d, cfg, H.convert_state_to_hf(cfg, {k: v.detach() for k, v in teacher.named_parameters()}))
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--opd-type", "megatron", "--opd-teacher-load", d,
+                    "--opd-kl-coef", "0.5", "--lr", "1e-4"])
+    c = Controller(a, device="cpu")
+    actor = c.runner.actor
+    assert "teacher" in actor.snapshots and actor.cfg.opd_kl_coef == 0.5
+    # the policy itself was not replaced by the teacher
+    own = GPTModel(cfg, seed=a.seed)
+    name = "decoder.layers.0.mlp.linear_fc2.weight"
+    assert torch.equal(dict(actor.model.named_parameters())[name].detach(), dict(own.named_parameters())[name].detach())
+    assert actor._active_tag == "actor"
+    m = c.runner.step()
+    assert "opd_kl" in m and m["opd_kl"] != 0.0 and math.isfinite(m["grad_norm"])
