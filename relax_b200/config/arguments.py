@@ -194,11 +194,11 @@ FLAGS: dict[str, list] = {
         ("--hidden-size", dict(type=int, default=None)), ("--ffn-hidden-size", dict(type=int, default=None)),
         ("--num-attention-heads", dict(type=int, default=None)), ("--num-query-groups", dict(type=int, default=None)),
         ("--kv-channels", dict(type=int, default=None)), ("--vocab-size", dict(type=int, default=None)),
-        ("--padded-vocab-size", dict(type=int, default=None)), ("--norm-epsilon", dict(type=float, default=1e-6)),
-        ("--rotary-base", dict(type=float, default=1e6)), ("--qk-layernorm", _b()), ("--add-qkv-bias", _b()),
+        ("--padded-vocab-size", dict(type=int, default=None)), ("--norm-epsilon", dict(type=float, default=None)),
+        ("--rotary-base", dict(type=float, default=None)), ("--qk-layernorm", _b()), ("--add-qkv-bias", _b()),
         ("--swiglu", _b(True)), ("--group-query-attention", _b(True)), ("--untie-embeddings-and-output-weights", _b()),
         ("--num-experts", dict(type=int, default=None)), ("--moe-router-topk", dict(type=int, default=None)),
-        ("--moe-ffn-hidden-size", dict(type=int, default=None)), ("--moe-aux-loss-coeff", dict(type=float, default=0.0)),
+        ("--moe-ffn-hidden-size", dict(type=int, default=None)), ("--moe-aux-loss-coeff", dict(type=float, default=None)),
         ("--moe-token-dispatcher-type", dict(type=str, default="alltoall")), ("--moe-grouped-gemm", _b()),
         ("--moe-permute-fusion", _b()), ("--attention-backend", dict(type=str, default="flash")),
         ("--bf16", _b(True)), ("--fp16", _b()), ("--fp8-format", dict(type=str, default=None)), ("--fp8-recipe", dict(type=str, default=None)),
@@ -374,6 +374,22 @@ def model_config_from_args(a):
         v = getattr(a, src, None)
         if v is not None:
             over[dst] = v
+    # Megatron-style shape switches of the reference's scripts/models/*.sh
+    for src, dst in (("norm_epsilon", "rms_norm_eps"), ("rotary_base", "rope_theta"), ("moe_aux_loss_coeff", "moe_aux_loss_coef")):
+        v = getattr(a, src, None)
+        if v is not None:
+            over[dst] = float(v)
+    if a.model_name:          # a preset: the switches only add to it
+        if getattr(a, "add_qkv_bias", False):
+            over["qkv_bias"] = True
+        if getattr(a, "qk_layernorm", False):
+            over["qk_layernorm"] = True
+        if getattr(a, "untie_embeddings_and_output_weights", False):
+            over["tie_word_embeddings"] = False
+    else:                     # a model given by shape flags alone: Megatron's meaning of the switches
+        over["qkv_bias"] = bool(getattr(a, "add_qkv_bias", False))
+        over["qk_layernorm"] = bool(getattr(a, "qk_layernorm", False))
+        over["tie_word_embeddings"] = not getattr(a, "untie_embeddings_and_output_weights", False)
     if a.model_name:
         return get_config(a.model_name, **over)
     return ModelConfig(name="custom", **over)

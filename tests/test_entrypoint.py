@@ -36,3 +36,20 @@ def test_sft_run(tmp_path):
                  "--global-batch-size", "4", "--lr", "1e-3", "--max-tokens-per-gpu", "512", "--save", save]) == 0
     lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
     assert len(lines) == 3 and lines[-1]["loss"] < lines[0]["loss"]
+
+
+def test_model_shape_flags_follow_megatron_meaning():
+    from relax_b200.config.arguments import model_config_from_args, parse_args
+
+    shape = ["--colocate", "--num-layers", "2", "--hidden-size", "64", "--ffn-hidden-size", "128", "--num-attention-heads", "4",
+             "--num-query-groups", "2", "--kv-channels", "16", "--vocab-size", "100"]
+    c = model_config_from_args(parse_args(shape + ["--norm-epsilon", "1e-5", "--rotary-base", "500000", "--add-qkv-bias",
+                                                   "--untie-embeddings-and-output-weights"]))
+    assert (c.rms_norm_eps, c.rope_theta, c.qkv_bias, c.tie_word_embeddings, c.qk_layernorm) == (1e-5, 5e5, True, False, False)
+    c = model_config_from_args(parse_args(shape + ["--qk-layernorm"]))
+    assert c.qk_layernorm and c.tie_word_embeddings and not c.qkv_bias and c.rope_theta == 1e6
+    # a preset keeps its own values unless a flag is given
+    c = model_config_from_args(parse_args(["--colocate", "--model-name", "llama3-8b"]))
+    assert c.rope_theta == 5e5 and c.rms_norm_eps == 1e-5 and not c.qk_layernorm
+    c = model_config_from_args(parse_args(["--colocate", "--model-name", "llama3-8b", "--rotary-base", "1e6"]))
+    assert c.rope_theta == 1e6
