@@ -81,6 +81,12 @@ class ColocateConfig:
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
     critic_lr: Optional[float] = None
+    # more user hooks by path: fn(samples) -> (raw_rewards, shaped_rewards) replaces reward normalisation;
+    # fn(args_like, samples) marks samples with remove_sample = True (their loss mask is zeroed);
+    # fn(args_like, samples) may rewrite the samples of a rollout before they are converted
+    custom_reward_post_process_path: Optional[str] = None
+    rollout_sample_filter_path: Optional[str] = None
+    rollout_data_postprocess_path: Optional[str] = None
     log_passrate: bool = False                      # rollout/pass@k over the training groups (reward > 0.5 = correct)
     save_debug_train_data: Optional[str] = None     # directory: the training batch of every step as train_<id>.pt
     load_debug_rollout_data: Optional[str] = None   # directory of rollout_<id>.jsonl dumps replayed instead of generating
@@ -189,6 +195,11 @@ class ColocatedGRPO:
         self.group_filter = load_function(cfg.dynamic_sampling_filter_path, 1, "group filter") \
             if cfg.dynamic_sampling_filter_path else None
         self.sampling_stats: dict = {}
+        self.reward_post_process = load_function(cfg.custom_reward_post_process_path, 1, "reward post-process") \
+            if cfg.custom_reward_post_process_path else None
+        self.sample_filter = load_function(cfg.rollout_sample_filter_path, 2, "sample filter") if cfg.rollout_sample_filter_path else None
+        self.data_postprocess = load_function(cfg.rollout_data_postprocess_path, 2, "rollout post-process") \
+            if cfg.rollout_data_postprocess_path else None
         self.timer = Timer()
         self.rollout_id = 0
         self.sync_weights()
@@ -333,13 +344,18 @@ class ColocatedGRPO:
                 from ..utils.visualize import dump_rollout
 
                 dump_rollout(cfg.save_debug_rollout_data, rid, samples, extra={"weight_version": self.actor.weight_version})
+        if self.sample_filter is not None:
+            self.sample_filter(cfg, samples)
+        if self.data_postprocess is not None:
+            samples = self.data_postprocess(cfg, samples) or samples
         pass_metrics = self._passrate(samples) if cfg.log_passrate else {}
         with self.timer.span("data"):
             batch = convert_samples_to_train_data(
                 samples, advantage_estimator=cfg.train.advantage_estimator,
                 n_samples_per_prompt=cfg.train.n_samples_per_prompt,
                 rewards_normalization=cfg.train.rewards_normalization,
-                grpo_std_normalization=cfg.train.grpo_std_normalization)
+                grpo_std_normalization=cfg.train.grpo_std_normalization,
+                custom_reward_post_process=self.reward_post_process)
             # ranks of one engine hold identical rows; only the rows of replicas that
             # differ from mine have to travel
             batch = self._exchange(batch)

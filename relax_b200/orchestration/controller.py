@@ -107,6 +107,9 @@ class Controller:
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
                 stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()), critic_lr=_get(a, "critic_lr", None),
+                custom_reward_post_process_path=_get(a, "custom_reward_post_process_path", None),
+                rollout_sample_filter_path=_get(a, "rollout_sample_filter_path", None),
+                rollout_data_postprocess_path=_get(a, "rollout_data_postprocess_path", None),
                 log_passrate=bool(_get(a, "log_passrate", False)), save_debug_train_data=_get(a, "save_debug_train_data", None),
                 load_debug_rollout_data=_get(a, "load_debug_rollout_data", None),
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),

@@ -202,3 +202,33 @@ def test_dynamic_sampling_filter_in_the_colocated_loop():
     for s in samples:
         by_group.setdefault(s.group_index, []).append(s.reward)
     assert len(by_group) == 2 and all(len(set(v)) > 1 for v in by_group.values())
+
+
+def test_reward_postprocess_sample_filter_and_rollout_postprocess_hooks(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "hooks.py"
+    f.write_text(
+        "import torch\n"
+        "LOG = []\n"
+        "def post(samples):\n"
+        "    raw = torch.tensor([float(s.reward) for s in samples])\n"
+        "    LOG.append(('post', len(samples)))\n"
+        "    return raw, raw * 2 - 1\n"
+        "def drop_first(cfg, samples):\n"
+        "    samples[0].remove_sample = True\n"
+        "    LOG.append(('filter', len(samples)))\n"
+        "def tag(cfg, samples):\n"
+        "    for s in samples:\n"
+        "        s.metadata['tagged'] = True\n"
+        "    LOG.append(('tag', len(samples)))\n"
+        "    return samples\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--rm-type", "token_sum_parity",
+                    "--custom-reward-post-process-path", f"{f}:post", "--rollout-sample-filter-path", f"{f}:drop_first",
+                    "--rollout-data-postprocess-path", f"{f}:tag"])
+    c = Controller(a, device="cpu")
+    m = c.runner.step()
+    assert [k for k, _ in CG.load_object(f"{f}:LOG")] == ["filter", "tag", "post"]
+    assert 0.0 <= m["raw_reward_mean"] <= 1.0
