@@ -56,6 +56,9 @@ class ColocateConfig:
     kv_blocks: int = 512
     kv_block_size: int = 16
     max_running: int = 256
+    max_prefill_tokens: int = 16384
+    use_cuda_graph: bool = True
+    engine_memory_saver: Optional[bool] = None      # None: the engine's default (environment switch)
     seed: int = 0
     rollout_seed: int = 42
     offload_train: bool = False
@@ -164,6 +167,8 @@ class ColocatedGRPO:
         self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
                                     num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
                                     max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
+                                    max_prefill_tokens=cfg.max_prefill_tokens, use_cuda_graph=cfg.use_cuda_graph,
+                                    memory_saver=cfg.engine_memory_saver,
                                     max_model_len=cfg.prompt_len + cfg.max_response_len,
                                     eos_token_id=cfg.eos_token_id)
         # the trainer replica that feeds my engine is the one I belong to (colocated)

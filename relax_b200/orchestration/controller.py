@@ -82,8 +82,8 @@ class Controller:
             from .colocate import ColocatedGRPO, ColocateConfig
 
             plen = _get(a, "rollout_max_prompt_len", 512)
-            ctx = _get(a, "rollout_max_context_len", plen + a.rollout_max_response_len)
-            page = _get(a, "sglang_page_size", 16)
+            ctx = _get(a, "engine_context_length", None) or _get(a, "rollout_max_context_len", plen + a.rollout_max_response_len)
+            page = _get(a, "engine_block_size", 16)
             cfg = ColocateConfig(
                 model=self.model_cfg, train=self.train_cfg, trainer_tp=a.tensor_model_parallel_size,
                 trainer_cp=a.context_parallel_size, rollout_tp=_get(a, "rollout_num_gpus_per_engine", 1),
@@ -93,7 +93,9 @@ class Controller:
                 eos_token_id=getattr(self._codec(a), "eos_token_id", None),
                 kv_blocks=_get(a, "kv_blocks", max(64, a.rollout_batch_size * a.n_samples_per_prompt * (ctx // 16 + 2))),
                 kv_block_size=page if page > 1 else 16,
-                max_running=_get(a, "sglang_max_running_requests", 256), seed=a.seed, rollout_seed=a.rollout_seed,
+                max_running=_get(a, "engine_max_running", 256), max_prefill_tokens=_get(a, "engine_max_prefill_tokens", 16384),
+                use_cuda_graph=not _get(a, "engine_disable_cuda_graph", False),
+                engine_memory_saver=True if _get(a, "engine_memory_saver", False) else None, seed=a.seed, rollout_seed=a.rollout_seed,
                 offload_rollout=a.offload_rollout, offload_train=a.offload_train,
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),

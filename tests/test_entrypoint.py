@@ -53,3 +53,14 @@ def test_model_shape_flags_follow_megatron_meaning():
     assert c.rope_theta == 5e5 and c.rms_norm_eps == 1e-5 and not c.qk_layernorm
     c = model_config_from_args(parse_args(["--colocate", "--model-name", "llama3-8b", "--rotary-base", "1e6"]))
     assert c.rope_theta == 1e6
+
+
+def test_engine_flags_reach_the_rollout_engine():
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--sglang-page-size", "8", "--sglang-max-running-requests", "3",
+                    "--sglang-chunked-prefill-size", "64", "--sglang-disable-cuda-graph"])
+    eng = Controller(a, device="cpu").runner.engine
+    assert eng.block_size == 8 and eng.max_running == 3 and eng.max_prefill_tokens == 64 and not eng.use_cuda_graph
