@@ -84,6 +84,7 @@ class ColocateConfig:
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
     critic_lr: Optional[float] = None
+    num_critic_only_steps: int = 0      # PPO: the first rollouts train the critic alone
     # more user hooks by path: fn(samples) -> (raw_rewards, shaped_rewards) replaces reward normalisation;
     # fn(args_like, samples) marks samples with remove_sample = True (their loss mask is zeroed);
     # fn(args_like, samples) may rewrite the samples of a rollout before they are converted
@@ -379,7 +380,7 @@ class ColocatedGRPO:
             if cfg.save_debug_train_data:
                 os.makedirs(cfg.save_debug_train_data, exist_ok=True)
                 torch.save({k: v for k, v in data.items()}, os.path.join(cfg.save_debug_train_data, f"train_{rid}_rank{self._rank}.pt"))
-            m = self.actor.train(rid, data)
+            m = self.actor.train(rid, data, update_policy=not (self.critic is not None and rid < cfg.num_critic_only_steps))
             self.actor.after_train()
             if self.critic is not None:       # `data` now carries the GAE returns computed with those values
                 cm = self.critic.train_critic(rid, data)

@@ -351,9 +351,10 @@ class TrainActor:
         return {k: ([v[i] for i in idx] if isinstance(v, list) and len(v) == n else v) for k, v in batch.items()}
 
     # ------------------------------------------------------------------ training
-    def train(self, rollout_id: int, batch: dict) -> dict:
+    def train(self, rollout_id: int, batch: dict, update_policy: bool = True) -> dict:
         """One rollout's worth of optimizer steps on this replica's samples
-        (``batch`` already split for data parallelism).  Returns reduced metrics."""
+        (``batch`` already split for data parallelism).  Returns reduced metrics.  With ``update_policy=False`` only
+        the forward passes, advantages and returns are computed (critic warm-up steps of PPO)."""
         cfg, dev = self.cfg, self.device
         t0 = time.perf_counter()
         n = len(batch["tokens"])
@@ -414,7 +415,7 @@ class TrainActor:
             dist.all_reduce(nsteps, op=dist.ReduceOp.MAX, group=self.ps.dp_cp.group)
         agg: dict[str, torch.Tensor] = {}
         last_norm = 0.0
-        for s in range(int(nsteps)):
+        for s in range(int(nsteps) if update_policy else 0):
             idx = list(range(s * per_step, min(n, (s + 1) * per_step)))
             with self.timer.span("train_step"):
                 m, last_norm = self._train_step(batch, idx)

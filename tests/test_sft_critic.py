@@ -125,3 +125,20 @@ def test_ppo_with_critic_in_the_colocated_loop():
     assert "critic/loss" in m or any(k.startswith("critic/") for k in m)
     assert not torch.equal(run.critic.model.value_head.weight.detach(), w0)      # the critic was updated
     assert math.isfinite(m["grad_norm"])
+
+
+def test_critic_only_warmup_steps_leave_the_policy_untouched():
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+
+    cfg = ColocateConfig(model=get_config("tiny"),
+                         train=TrainConfig(advantage_estimator="ppo", global_batch_size=4, n_samples_per_prompt=2, pad_multiple=1,
+                                           max_tokens_per_gpu=256, loss=LossConfig(), optim=OptimizerConfig(lr=1e-2)),
+                         rollout_batch_size=2, prompt_len=8, max_response_len=8, kv_blocks=64, num_prompts=16,
+                         rm_type="token_sum_parity", critic_lr=5e-3, num_critic_only_steps=1)
+    run = ColocatedGRPO(cfg)
+    p0 = run.actor.param_buf.clone()
+    c0 = run.critic.param_buf.clone()
+    run.step()
+    assert torch.equal(run.actor.param_buf, p0) and not torch.equal(run.critic.param_buf, c0)
+    run.step()
+    assert not torch.equal(run.actor.param_buf, p0)
