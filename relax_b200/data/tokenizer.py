@@ -81,3 +81,19 @@ class PromptEncoder:
     def __call__(self, prompt: Any) -> Optional[List[int]]:
         ids = self.codec.encode(self.text(prompt))
         return None if self.max_len and len(ids) > self.max_len else ids
+
+
+def cut_at_stop_strings(codec, ids: Sequence[int], stops: Sequence[str]) -> Optional[int]:
+    """Smallest token count whose decoded text contains one of ``stops`` (None when none occurs): containment is
+    monotone in the prefix length, so a bisection over prefixes needs only O(log n) decodes."""
+    stops = [s for s in (stops or []) if s]
+    if not stops or not ids:
+        return None
+    has = lambda n: any(s in codec.decode(ids[:n]) for s in stops)
+    if not has(len(ids)):
+        return None
+    lo, hi = 0, len(ids)          # has(lo) is False, has(hi) is True
+    while hi - lo > 1:
+        mid = (lo + hi) // 2
+        lo, hi = (lo, mid) if has(mid) else (mid, hi)
+    return hi

@@ -83,6 +83,7 @@ class ColocateConfig:
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     stop_token_ids: tuple = ()
+    stop_strings: tuple = ()        # --rollout-stop: the response ends with the first of these strings (needs a codec)
     critic_lr: Optional[float] = None
     num_critic_only_steps: int = 0      # PPO: the first rollouts train the critic alone
     # more user hooks by path: fn(samples) -> (raw_rewards, shaped_rewards) replaces reward normalisation;
@@ -248,7 +249,15 @@ class ColocatedGRPO:
             s.weight_versions = sorted(set(r.weight_versions))
             s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
             if self.codec is not None:
-                s.response = self.codec.decode(r.output)
+                if self.cfg.stop_strings:
+                    from ..data.tokenizer import cut_at_stop_strings
+
+                    n = cut_at_stop_strings(self.codec, list(r.output), self.cfg.stop_strings)
+                    if n is not None and n < len(r.output):      # generated past the stop string: drop the rest
+                        s.tokens = list(r.prompt) + list(r.output[:n])
+                        s.response_length, s.rollout_log_probs = n, list(r.logprobs[:n])
+                        s.status = SampleStatus.COMPLETED
+                s.response = self.codec.decode(s.tokens[len(s.tokens) - s.response_length:]) if s.response_length else ""
             s.reward = self.reward_fn(s)
         return mine
 

@@ -34,7 +34,7 @@ class Controller:
     def _codec(self, a):
         from ..data.tokenizer import build_codec
 
-        if not (_get(a, "prompt_data", None) or _get(a, "eval_prompt_data", None)):
+        if not (_get(a, "prompt_data", None) or _get(a, "eval_prompt_data", None) or _get(a, "rollout_stop", None)):
             return None
         return build_codec(_get(a, "hf_checkpoint", None), self.model_cfg.vocab_size)
 
@@ -108,7 +108,8 @@ class Controller:
                 system_prompt=_get(a, "system_prompt", None),
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
-                stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()), critic_lr=_get(a, "critic_lr", None), num_critic_only_steps=_get(a, "num_critic_only_steps", 0) or 0,
+                stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
+                stop_strings=tuple(_get(a, "rollout_stop", None) or ()), critic_lr=_get(a, "critic_lr", None), num_critic_only_steps=_get(a, "num_critic_only_steps", 0) or 0,
                 custom_reward_post_process_path=_get(a, "custom_reward_post_process_path", None),
                 rollout_sample_filter_path=_get(a, "rollout_sample_filter_path", None),
                 rollout_data_postprocess_path=_get(a, "rollout_data_postprocess_path", None),

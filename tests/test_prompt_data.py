@@ -51,3 +51,35 @@ def test_colocated_loop_on_prompt_files_scores_decoded_text(tmp_path):
     seen = load_object(f"{user}:SEEN")
     assert len(seen) == 4 and all(p.startswith("What is") and isinstance(r, str) and lab.isdigit() for p, r, lab in seen)
     assert 0.0 <= m["raw_reward_mean"] <= 1.0
+
+
+def test_stop_strings_cut_the_response():
+    from relax_b200.data.tokenizer import cut_at_stop_strings
+
+    c = ByteCodec(1024)
+    ids = c.encode("The answer is 42.</answer> and then more text")
+    n = cut_at_stop_strings(c, ids, ["</answer>", "###"])
+    assert c.decode(ids[:n]) == "The answer is 42.</answer>"
+    assert cut_at_stop_strings(c, ids, ["nope"]) is None and cut_at_stop_strings(c, ids, []) is None
+    assert cut_at_stop_strings(c, c.encode("###"), ["###"]) == 3
+
+
+def test_rollout_stop_flag_trims_samples(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.custom_generate import load_object
+
+    user = tmp_path / "rm2.py"
+    user.write_text("SEEN = []\ndef rm(sample):\n    SEEN.append((sample.response, sample.response_length, len(sample.rollout_log_probs)))\n    return 1.0\n")
+    # random byte-level text: use a stop string that certainly occurs - every single byte value the model can emit
+    stops = [chr(b) for b in range(32, 127)]
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "12", "--custom-rm-path", f"{user}:rm", "--rollout-stop"] + stops)
+    c = Controller(a, device="cpu")
+    c.runner.step()
+    seen = load_object(f"{user}:SEEN")
+    assert len(seen) == 4
+    for text, n, nlp in seen:
+        assert n == nlp and n <= 12
+        if any(ch in text for ch in stops):                  # cut right after the first printable character
+            assert sum(ch in stops for ch in text) == 1 and text[-1] in stops
