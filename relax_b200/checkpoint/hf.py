@@ -47,6 +47,16 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
         return [("model.norm.weight", p)]
     if name == "value_head.weight":
         return [("score.weight", p)]
+    mt = re.match(r"mtp\.layers\.(\d+)\.(.+)", name)
+    if mt:      # DeepSeek-V3 convention: MTP depth k lives at layer index num_layers + k
+        li, sub = cfg.num_layers + int(mt.group(1)), mt.group(2)
+        own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
+               "final_layernorm.weight": "shared_head.norm.weight"}
+        if sub in own:
+            return [(f"model.layers.{li}.{own[sub]}", p)]
+        if sub.startswith("transformer_layer."):
+            return megatron_to_hf(cfg, f"decoder.layers.{li}." + sub[len("transformer_layer."):], p)
+        raise ValueError(f"unknown MTP parameter {name!r}")
     m = _LAYER.match(name)
     if not m:
         raise ValueError(f"unknown parameter name {name!r}")
@@ -111,8 +121,15 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
            "decoder.final_layernorm.weight": hf["model.norm.weight"]}
     if not cfg.tie_word_embeddings:
         out["output_layer.weight"] = hf.get("lm_head.weight", hf["model.embed_tokens.weight"])
-    for i in range(cfg.num_layers):
+    for i in range(cfg.num_layers + cfg.mtp_num_layers):
         pre, b = f"model.layers.{i}.", f"decoder.layers.{i}."
+        if i >= cfg.num_layers:
+            k = i - cfg.num_layers
+            b = f"mtp.layers.{k}.transformer_layer."
+            out[f"mtp.layers.{k}.enorm.weight"] = hf[pre + "enorm.weight"]
+            out[f"mtp.layers.{k}.hnorm.weight"] = hf[pre + "hnorm.weight"]
+            out[f"mtp.layers.{k}.eh_proj.weight"] = hf[pre + "eh_proj.weight"]
+            out[f"mtp.layers.{k}.final_layernorm.weight"] = hf[pre + "shared_head.norm.weight"]
         q = hf[pre + "self_attn.q_proj.weight"].view(ng, qpg, hd, H)
         k = hf[pre + "self_attn.k_proj.weight"].view(ng, 1, hd, H)
         v = hf[pre + "self_attn.v_proj.weight"].view(ng, 1, hd, H)

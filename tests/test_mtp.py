@@ -127,3 +127,17 @@ def test_sequence_classification_head_learns():
     assert last["loss"] < first["loss"] * 0.5 and last["accuracy"] == 1.0
     pred = [int(r.argmax()) for r in actor.predict_classes(batch)]
     assert pred == batch["labels"]
+
+
+def test_mtp_parameters_round_trip_through_hf_names():
+    from relax_b200.checkpoint import hf as H
+
+    cfg = get_config("tiny", mtp_num_layers=2)
+    m = GPTModel(cfg, seed=6)
+    state = {k: v.detach() for k, v in m.named_parameters()}
+    hf = H.convert_state_to_hf(cfg, state)
+    L = cfg.num_layers
+    assert f"model.layers.{L}.eh_proj.weight" in hf and f"model.layers.{L + 1}.shared_head.norm.weight" in hf
+    assert f"model.layers.{L}.self_attn.q_proj.weight" in hf and f"model.layers.{L}.mlp.down_proj.weight" in hf
+    back = H.hf_to_megatron_state(cfg, hf)
+    assert set(back) == set(state) and all(torch.equal(back[k], state[k]) for k in state)
