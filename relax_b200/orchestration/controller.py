@@ -62,7 +62,9 @@ class Controller:
         self.mode = self._pick_mode()
         self._stop = False
         self.profiler = TrainProfiler(_get(args, "profile_dir", args.save and os.path.join(args.save, "profile")),
-                                      _get(args, "profile_step_start", -1), _get(args, "profile_step_end", -1), self.rank)
+                                      _get(args, "profile_step_start", -1), _get(args, "profile_step_end", -1), self.rank,
+                                      with_stack=bool(_get(args, "profile_with_stack", False)),
+                                      record_memory=bool(_get(args, "profile_with_memory", False) or _get(args, "record_memory_history", False)))
         self.start_rollout_id = dist_ckpt.resolve_start_rollout_id(args.load, args.start_rollout_id)
         self.runner = self._build_runner()
         self._maybe_resume()
