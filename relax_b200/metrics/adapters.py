@@ -112,14 +112,19 @@ def build_adapters(args) -> list:
             print(f"[metrics] {what} requested but not importable ({e}); skipped", file=sys.stderr)
 
     if getattr(args, "use_tensorboard", False):
-        _try(lambda: TensorBoardAdapter(getattr(args, "tb_dir", None) or os.path.join(out_dir or ".", "tb")), "tensorboard")
+        tb = getattr(args, "tb_dir", None) or os.path.join(out_dir or ".", "tb")
+        for part in (getattr(args, "tb_project_name", None), getattr(args, "tb_experiment_name", None)):
+            if part:
+                tb = os.path.join(tb, str(part))
+        _try(lambda: TensorBoardAdapter(tb), "tensorboard")
     if getattr(args, "use_wandb", False):
         _try(lambda: WandbAdapter(getattr(args, "wandb_project", "relax"), getattr(args, "wandb_group", None),
                                   mode=getattr(args, "wandb_mode", "offline")), "wandb")
     if getattr(args, "use_clearml", False):
         _try(lambda: ClearMLAdapter(getattr(args, "clearml_project", "relax"), getattr(args, "clearml_task", "run")), "clearml")
-    if getattr(args, "apprise_urls", None):
-        _try(lambda: AppriseAdapter(list(args.apprise_urls)), "apprise")
+    urls = list(getattr(args, "apprise_urls", None) or []) + list(getattr(args, "notify_urls", None) or [])
+    if urls:
+        _try(lambda: AppriseAdapter(urls), "apprise")
     if getattr(args, "log_to_console", True):
         out.append(ConsoleAdapter())
     return out
