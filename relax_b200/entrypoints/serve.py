@@ -1,0 +1,56 @@
+"""Stand-alone control-plane services: ``python -m relax_b200.entrypoints.serve <service> [--host H] [--port P]``.
+
+* ``metrics``     - the metrics service (``/log_metric``, ``/log_metrics_batch``, ``/report_step``, ``/log_error``) with the
+  tracking adapters chosen by the usual flags (relax/entrypoints/deploy_metrics_service.py);
+* ``coordinator`` - the weight-sync coordinator (register / heartbeat / topology / weight-metadata long poll,
+  relax/checkpoint_service/coordinator/service.py);
+* ``viewer``      - the rollout result viewer (relax/entrypoints/visualize.py).
+
+Each serves until interrupted; the bound address is printed first so that launch scripts can read it.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description="relax_b200 control-plane services")
+    ap.add_argument("service", choices=["metrics", "coordinator", "viewer"])
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=0)
+    ap.add_argument("--dir", default=None, help="viewer: dump directory; metrics: output directory of metrics.jsonl")
+    ap.add_argument("--use-tensorboard", action="store_true")
+    ap.add_argument("--max-seconds", type=float, default=None, help="leave after this long (tests, batch jobs)")
+    a = ap.parse_args(argv)
+    if a.service == "metrics":
+        from ..metrics.adapters import build_adapters
+        from ..metrics.service import MetricsService, serve
+
+        ns = argparse.Namespace(metrics_dir=a.dir, save=None, use_tensorboard=a.use_tensorboard, log_to_console=True)
+        srv, _ = serve(MetricsService(build_adapters(ns)), a.host, a.port)
+    elif a.service == "coordinator":
+        from ..weight_sync.dcs import Coordinator, serve
+
+        srv, _ = serve(Coordinator(), a.host, a.port)
+    else:
+        from ..utils.visualize import serve_in_thread
+
+        if not a.dir:
+            ap.error("viewer needs --dir")
+        srv, _ = serve_in_thread(a.dir, a.host, a.port)
+    print(f"{a.service} listening on http://{srv.server_address[0]}:{srv.server_address[1]}", flush=True)
+    t0 = time.monotonic()
+    try:
+        while a.max_seconds is None or time.monotonic() - t0 < a.max_seconds:
+            time.sleep(0.2)
+    except KeyboardInterrupt:
+        pass
+    srv.shutdown()
+    srv.server_close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

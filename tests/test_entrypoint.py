@@ -64,3 +64,35 @@ def test_engine_flags_reach_the_rollout_engine():
                     "--sglang-chunked-prefill-size", "64", "--sglang-disable-cuda-graph"])
     eng = Controller(a, device="cpu").runner.engine
     assert eng.block_size == 8 and eng.max_running == 3 and eng.max_prefill_tokens == 64 and not eng.use_cuda_graph
+
+
+def test_standalone_services_start_and_answer(tmp_path):
+    import json
+    import re
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+
+    from relax_b200.utils.visualize import dump_rollout
+    from relax_b200.types import Sample
+
+    dump_rollout(str(tmp_path), 0, [Sample(response="x", response_length=1, reward=1.0, tokens=[1, 2])])
+    for svc, extra, path in (("viewer", ["--dir", str(tmp_path)], "/api/steps"), ("coordinator", [], "/health"),
+                             ("metrics", ["--dir", str(tmp_path)], None)):
+        p = subprocess.Popen([sys.executable, "-m", "relax_b200.entrypoints.serve", svc, "--max-seconds", "20"] + extra,
+                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        try:
+            line = p.stdout.readline()
+            m = re.search(r"listening on (http://[\d.]+:\d+)", line)
+            assert m, line
+            if path:
+                body = urllib.request.urlopen(m.group(1) + path, timeout=10).read()
+                assert body
+            else:
+                req = urllib.request.Request(m.group(1) + "/log_metric", data=json.dumps({"step": 1, "name": "loss", "value": 0.5}).encode(),
+                                             headers={"Content-Type": "application/json"})
+                assert urllib.request.urlopen(req, timeout=10).status == 200
+        finally:
+            p.terminate()
+            p.wait(10)
