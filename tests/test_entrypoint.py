@@ -96,3 +96,32 @@ def test_standalone_services_start_and_answer(tmp_path):
         finally:
             p.terminate()
             p.wait(10)
+
+
+def test_openapi_routes_exist_on_live_servers(tmp_path):
+    import json
+    import urllib.error
+    import urllib.request
+
+    from relax_b200.metrics.service import MetricsService, serve as serve_metrics
+    from relax_b200.utils import openapi
+    from relax_b200.weight_sync.dcs import Coordinator, serve as serve_coord
+
+    assert openapi.main(["--service", "all", "--out-dir", str(tmp_path)]) == 0
+    spec = json.load(open(tmp_path / "coordinator.openapi.json"))
+    assert "/recv_weight_meta" in spec["paths"] and spec["openapi"].startswith("3.")
+    for name, (srv, url) in (("metrics", serve_metrics(MetricsService([]))), ("coordinator", serve_coord(Coordinator()))):
+        try:
+            for method, path, _, schema in openapi.ROUTES[name]:
+                if path == "/recv_weight_meta":
+                    continue            # a long poll: it answers only once a layout is published
+                data = json.dumps({}).encode() if method == "post" else None
+                req = urllib.request.Request(url + path, data=data, headers={"Content-Type": "application/json"}, method=method.upper())
+                try:
+                    code = urllib.request.urlopen(req, timeout=10).status
+                except urllib.error.HTTPError as e:
+                    code = e.code
+                assert code != 404, (name, path)       # the route exists (an empty body may be a 400)
+        finally:
+            srv.shutdown()
+            srv.server_close()
