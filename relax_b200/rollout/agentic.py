@@ -191,3 +191,49 @@ def run_episodes(envs: Sequence[AgentEnv], generate: GenerateFn, tok: Tokenizer,
 
 def run_episode(env: AgentEnv, generate: GenerateFn, tok: Tokenizer, **kw) -> Session:
     return run_episodes([env], generate, tok, **kw)[0]
+
+
+# --------------------------------------------------------------------------- as a rollout generate function
+_CODEC = None
+
+
+def set_codec(codec) -> None:
+    """Text codec (``data.tokenizer``) used by :func:`env_generate`; defaults to the byte-level codec."""
+    global _CODEC
+    _CODEC = codec
+
+
+def env_generate(engine, samples, sampling_params):
+    """Multi-turn, tool-using rollouts behind the single-turn interface of the training loop:
+    ``--custom-generate-function-path relax_b200.rollout.agentic:env_generate``.
+
+    Every sample names its environment in ``metadata["env"]`` (``{"name": ..., **kwargs}``; the registry of
+    :func:`register_env`), optionally ``max_turns`` / ``max_new_tokens``.  The sample's prompt is replaced by the
+    environment's opening messages; the returned sample carries the whole conversation, a loss mask that covers the
+    model's own tokens only, the rollout log-probs of those tokens and the episode reward (so no reward function runs
+    afterwards)."""
+    from ..data.tokenizer import ByteCodec
+
+    codec = _CODEC or ByteCodec(engine.cfg.vocab_size)
+    tok = Tokenizer(encode=codec.encode, decode=codec.decode)
+    envs, turns, new_tokens = [], 8, sampling_params.max_new_tokens
+    for s in samples:
+        spec = dict((s.metadata or {}).get("env") or {})
+        if "name" not in spec:
+            raise ValueError("env_generate: sample.metadata['env'] = {'name': ..., **kwargs} is required")
+        turns = int((s.metadata or {}).get("max_turns", turns))
+        envs.append(make_env(spec.pop("name"), **spec))
+    max_ctx = getattr(engine, "max_model_len", None) or 4096
+    sessions = run_episodes(envs, engine_generate_fn(engine, sampling_params), tok, max_turns=turns,
+                            max_new_tokens=new_tokens, max_context=max_ctx)
+    for s, sess in zip(samples, sessions):
+        done = sess.to_sample(s.group_index, s.index)
+        s.tokens, s.response_length, s.loss_mask = done.tokens, done.response_length, done.loss_mask
+        s.rollout_log_probs, s.reward, s.status = done.rollout_log_probs, done.reward, done.status
+        s.weight_versions = done.weight_versions
+        s.response = codec.decode(done.tokens[len(done.tokens) - done.response_length:])
+        s.metadata = dict(s.metadata or {}, turns=sess.turns)
+    return samples
+
+
+env_generate.manages_inference_permit = True

@@ -155,3 +155,38 @@ def test_ifbench_remote_and_dapo_genrm_rewards():
     assert fn(Sample(prompt="q", response="Answer: 7", label="7"))["score"] == 1.0          # rule decides
     assert fn(Sample(prompt="q", response="Answer: 8", label="7"))["score"] == -1.0
     assert fn(Sample(prompt="q", response="it is seven", label="7"))["pred"] == "[GENRM]"   # judge decides
+
+
+def test_env_generate_plugs_into_the_colocated_loop(tmp_path):
+    import json
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    @A.register_env("echo_once")
+    class EchoOnce:
+        def __init__(self, bonus=0.0):
+            self.bonus, self.n = bonus, 0
+
+        def reset(self):
+            return [{"role": "user", "content": "say something"}]
+
+        def step(self, text):
+            self.n += 1
+            return ("tool says hi", 0.0, False) if self.n == 1 else (None, 1.0 + self.bonus, True)
+
+    f = tmp_path / "prompts.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": "unused", "label": None, "metadata": {"env": {"name": "echo_once", "bonus": 0.5 * i}, "max_turns": 3}})
+                           for i in range(2)) + "\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "6", "--rollout-max-prompt-len", "256", "--prompt-data", str(f),
+                    "--input-key", "prompt", "--custom-generate-function-path", "relax_b200.rollout.agentic:env_generate",
+                    "--disable-rewards-normalization"])
+    c = Controller(a, device="cpu")
+    samples = c.runner.generate(0)
+    assert len(samples) == 4 and all(s.metadata["turns"] == 2 for s in samples)
+    assert sorted({s.reward for s in samples}) == [1.0, 1.5]
+    s = samples[0]
+    assert len(s.loss_mask) == s.response_length == len(s.rollout_log_probs) and 0 < sum(s.loss_mask) < s.response_length
+    m = c.runner.step()
+    assert m["raw_reward_mean"] == 1.25
