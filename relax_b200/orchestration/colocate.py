@@ -102,6 +102,8 @@ class ColocateConfig:
     label_key: Optional[str] = "label"
     metadata_key: str = "metadata"
     rollout_shuffle: bool = False
+    use_streaming_dataset: bool = False     # read the prompt files lazily through a shuffle buffer
+    streaming_buffer_size: int = 1024
     codec: Optional[object] = None
     apply_chat_template: bool = False
     apply_chat_template_kwargs: dict = field(default_factory=dict)
@@ -187,13 +189,22 @@ class ColocatedGRPO:
 
             self.codec = cfg.codec or ByteCodec(cfg.model.vocab_size)
             enc = PromptEncoder(self.codec, cfg.apply_chat_template, cfg.apply_chat_template_kwargs, cfg.system_prompt, cfg.prompt_len)
-            ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key)
-            if len(ds) == 0:
-                raise ValueError(f"no usable prompt in {cfg.prompt_data} (limit {cfg.prompt_len} tokens)")
+            if cfg.use_streaming_dataset:
+                from ..rollout.data_source import StreamingRolloutDataSource
+
+                ds = None
+                self.data_source = StreamingRolloutDataSource(cfg.prompt_data, enc, cfg.train.n_samples_per_prompt, cfg.streaming_buffer_size,
+                                                              cfg.rollout_seed, cfg.input_key, cfg.label_key, cfg.metadata_key,
+                                                              shuffle=cfg.rollout_shuffle)
+            else:
+                ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key)
+                if len(ds) == 0:
+                    raise ValueError(f"no usable prompt in {cfg.prompt_data} (limit {cfg.prompt_len} tokens)")
         else:
             self.codec = cfg.codec
             ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
-        self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
+        if ds is not None:
+            self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
         from ..rollout.custom_generate import load_function, load_generate_function
 
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \

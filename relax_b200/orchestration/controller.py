@@ -105,6 +105,8 @@ class Controller:
                 prompt_data=_get(a, "prompt_data", None), input_key=_get(a, "input_key", None) or "prompt",
                 label_key=_get(a, "label_key", None), metadata_key=_get(a, "metadata_key", None) or "metadata",
                 rollout_shuffle=bool(_get(a, "rollout_shuffle", False)), codec=self._codec(a),
+                use_streaming_dataset=bool(_get(a, "use_streaming_dataset", False)),
+                streaming_buffer_size=_get(a, "streaming_buffer_size", None) or 1024,
                 apply_chat_template=bool(_get(a, "apply_chat_template", False)),
                 apply_chat_template_kwargs=_get(a, "apply_chat_template_kwargs", None) or {},
                 system_prompt=_get(a, "system_prompt", None),

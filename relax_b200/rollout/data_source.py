@@ -153,3 +153,88 @@ class RolloutDataSourceWithBuffer(RolloutDataSource):
     def load_state_dict(self, sd):
         super().load_state_dict(sd)
         self.buffer = [[Sample.from_dict(d) for d in g] for g in sd.get("buffer", [])]
+
+
+class StreamingRolloutDataSource:
+    """Prompts read lazily from (possibly huge) JSONL files through a shuffle buffer, epoch after epoch
+    (``--use-streaming-dataset``, ``--streaming-buffer-size``; relax/utils/data/streaming_dataset.py).  Memory holds
+    ``buffer_size`` rows, not the data set.  The order is a pure function of ``(seed, epoch)``, so a resumed run
+    replays the stream up to the saved position and continues with exactly the prompts the original run would
+    have drawn."""
+
+    def __init__(self, paths, tokenize: Optional[Callable], n_samples_per_prompt: int, buffer_size: int = 1024, seed: int = 42,
+                 prompt_key: str = "prompt", label_key: Optional[str] = "label", metadata_key: str = "metadata", shuffle: bool = True):
+        self.paths = [p for p in (paths.split(",") if isinstance(paths, str) else list(paths)) if p]
+        self.tokenize, self.n = tokenize, n_samples_per_prompt
+        self.buffer_size, self.seed, self.shuffle = max(1, buffer_size), seed, shuffle
+        self.prompt_key, self.label_key, self.metadata_key = prompt_key, label_key, metadata_key
+        self.epoch, self.consumed = 0, 0           # rows handed out in the current epoch
+        self.sample_index, self.group_index = 0, 0
+        self._it = self._rows(self.epoch)
+
+    def _raw(self):
+        for p in self.paths:
+            with open(p, encoding="utf-8") as f:
+                for line in f:
+                    if line.strip():
+                        yield json.loads(line)
+
+    def _rows(self, epoch: int):
+        rng = random.Random(self.seed * 1000003 + epoch)
+        buf = []
+        for r in self._raw():
+            toks = self.tokenize(r[self.prompt_key]) if self.tokenize else list(r[self.prompt_key])
+            if toks is None:
+                continue
+            item = {"prompt": r[self.prompt_key], "prompt_tokens": toks, "label": r.get(self.label_key) if self.label_key else None,
+                    "metadata": r.get(self.metadata_key) or {}}
+            if not self.shuffle:
+                yield item
+                continue
+            buf.append(item)
+            if len(buf) >= self.buffer_size:
+                yield buf.pop(rng.randrange(len(buf)))
+        rng.shuffle(buf)
+        yield from buf
+
+    def _next_row(self):
+        for _ in range(2):
+            try:
+                row = next(self._it)
+                self.consumed += 1
+                return row
+            except StopIteration:
+                if self.consumed == 0:
+                    raise ValueError(f"no usable prompt in {self.paths}")
+                self.epoch, self.consumed = self.epoch + 1, 0
+                self._it = self._rows(self.epoch)
+        raise RuntimeError("unreachable")
+
+    def get_samples(self, num_groups: int) -> list:
+        groups = []
+        for _ in range(num_groups):
+            row = self._next_row()
+            grp = []
+            for _ in range(self.n):
+                grp.append(Sample(group_index=self.group_index, index=self.sample_index, prompt=row["prompt"],
+                                  tokens=list(row["prompt_tokens"]), label=row["label"], metadata=dict(row["metadata"])))
+                self.sample_index += 1
+            self.group_index += 1
+            groups.append(grp)
+        return groups
+
+    def add_samples(self, groups):
+        raise RuntimeError("the streaming source has no buffer for returned samples")
+
+    def state_dict(self):
+        return {"epoch": self.epoch, "consumed": self.consumed, "sample_index": self.sample_index,
+                "group_index": self.group_index, "seed": self.seed}
+
+    def load_state_dict(self, sd):
+        self.seed = sd.get("seed", self.seed)
+        self.epoch, self.sample_index, self.group_index = sd["epoch"], sd["sample_index"], sd["group_index"]
+        self._it = self._rows(self.epoch)
+        self.consumed = 0
+        for _ in range(sd["consumed"]):       # replay to the saved position
+            next(self._it)
+            self.consumed += 1

@@ -83,3 +83,43 @@ def test_rollout_stop_flag_trims_samples(tmp_path):
         assert n == nlp and n <= 12
         if any(ch in text for ch in stops):                  # cut right after the first printable character
             assert sum(ch in stops for ch in text) == 1 and text[-1] in stops
+
+
+def test_streaming_source_covers_epochs_and_resumes_exactly(tmp_path):
+    from relax_b200.rollout.data_source import StreamingRolloutDataSource
+
+    files = []
+    for k in range(2):
+        p = tmp_path / f"p{k}.jsonl"
+        p.write_text("\n".join(json.dumps({"prompt": f"q{k}-{i}", "label": 10 * k + i}) for i in range(7)) + "\n")
+        files.append(str(p))
+    enc = PromptEncoder(ByteCodec(1024), max_prompt_len=64)
+    mk = lambda: StreamingRolloutDataSource(",".join(files), enc, 1, buffer_size=4, seed=3)
+    src = mk()
+    first = [g[0].label for g in src.get_samples(14)]
+    assert sorted(first) == sorted(list(range(7)) + list(range(10, 17))) and first != sorted(first)      # every row once, shuffled
+    second = [g[0].label for g in src.get_samples(14)]
+    assert sorted(second) == sorted(first) and second != first and src.epoch == 1                        # a new order per epoch
+    a = mk()
+    a.get_samples(5)
+    st = a.state_dict()
+    rest = [g[0].label for g in a.get_samples(12)]
+    b = mk()
+    b.load_state_dict(st)
+    assert [g[0].label for g in b.get_samples(12)] == rest and b.group_index == a.group_index
+
+
+def test_streaming_flag_in_the_loop(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.data_source import StreamingRolloutDataSource
+
+    f = tmp_path / "train.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"What is {i}?", "label": str(i)}) for i in range(6)) + "\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--prompt-data", str(f), "--input-key", "prompt",
+                    "--use-streaming-dataset", "--streaming-buffer-size", "3", "--rollout-shuffle"])
+    c = Controller(a, device="cpu")
+    assert isinstance(c.runner.data_source, StreamingRolloutDataSource)
+    m = c.runner.step()
+    assert m["response_tokens_local"] > 0
