@@ -183,6 +183,14 @@ class Controller:
             self.runner.sync_weights()
         if hasattr(self.runner, "rollout_id"):
             self.runner.rollout_id = self.start_rollout_id
+        ds = getattr(self.runner, "data_source", None)
+        it = dist_ckpt.read_latest_iteration(a.load)
+        state_file = os.path.join(dist_ckpt.iter_dir(a.load, it), "rollout_data_source.json")
+        if ds is not None and hasattr(ds, "load_state_dict") and os.path.exists(state_file):
+            import json as _json
+
+            with open(state_file) as f:
+                ds.load_state_dict(_json.load(f))
 
     def save(self, rollout_id: int):
         a, actor = self.args, self._actor()
@@ -190,6 +198,13 @@ class Controller:
             return
         dist_ckpt.save_checkpoint(a.save, rollout_id, self.model_cfg, actor.ps, actor.model,
                                   None if _get(a, "no_save_optim", False) else actor.optimizer)
+        ds = getattr(self.runner, "data_source", None)
+        if self.rank == 0 and ds is not None and hasattr(ds, "state_dict"):
+            # where the prompt stream stands, so a resumed run goes on with the next unseen prompt
+            import json as _json
+
+            with open(os.path.join(dist_ckpt.iter_dir(a.save, rollout_id), "rollout_data_source.json"), "w") as f:
+                _json.dump(ds.state_dict(), f)
         if self.rank == 0:
             dist_ckpt.rotate_checkpoints(a.save, getattr(a, "max_checkpoints_to_keep", None))
             if _get(a, "save_hf", None):       # also export Hugging Face files from the checkpoint just written

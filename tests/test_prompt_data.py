@@ -123,3 +123,21 @@ def test_streaming_flag_in_the_loop(tmp_path):
     assert isinstance(c.runner.data_source, StreamingRolloutDataSource)
     m = c.runner.step()
     assert m["response_tokens_local"] > 0
+
+
+def test_resume_continues_the_prompt_stream(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "train.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"What is {i}?", "label": str(i)}) for i in range(8)) + "\n")
+    common = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+              "--rollout-max-response-len", "8", "--prompt-data", str(f), "--input-key", "prompt", "--label-key", "label",
+              "--save", str(tmp_path / "ck"), "--load", str(tmp_path / "ck"), "--save-interval", "1"]
+    c = Controller(parse_args(common + ["--num-rollout", "2"]), device="cpu")
+    c.training_loop()
+    assert c.runner.data_source.state_dict()["offset"] == 4
+    c2 = Controller(parse_args(common + ["--num-rollout", "3"]), device="cpu")
+    assert c2.start_rollout_id == 2 and c2.runner.data_source.state_dict()["offset"] == 4
+    labels = [g[0].label for g in c2.runner.data_source.get_samples(2)]
+    assert labels == ["4", "5"]
