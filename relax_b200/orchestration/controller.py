@@ -183,6 +183,11 @@ class Controller:
             self.runner.sync_weights()
         if hasattr(self.runner, "rollout_id"):
             self.runner.rollout_id = self.start_rollout_id
+        critic = getattr(self.runner, "critic", None)
+        cdir = _get(a, "critic_load", None) or a.load.rstrip("/") + "_critic"
+        if critic is not None and os.path.isdir(cdir) and dist_ckpt.read_latest_iteration(cdir) is not None:
+            dist_ckpt.load_checkpoint(cdir, critic.mcfg, critic.ps, critic.model,
+                                      None if _get(a, "no_load_optim", False) else critic.optimizer)
         ds = getattr(self.runner, "data_source", None)
         it = dist_ckpt.read_latest_iteration(a.load)
         state_file = os.path.join(dist_ckpt.iter_dir(a.load, it), "rollout_data_source.json")
@@ -198,6 +203,13 @@ class Controller:
             return
         dist_ckpt.save_checkpoint(a.save, rollout_id, self.model_cfg, actor.ps, actor.model,
                                   None if _get(a, "no_save_optim", False) else actor.optimizer)
+        critic = getattr(self.runner, "critic", None)
+        if critic is not None:      # PPO: the value model has its own checkpoint tree (--critic-save, default <save>_critic)
+            cdir = _get(a, "critic_save", None) or a.save.rstrip("/") + "_critic"
+            dist_ckpt.save_checkpoint(cdir, rollout_id, critic.mcfg, critic.ps, critic.model,
+                                      None if _get(a, "no_save_optim", False) else critic.optimizer)
+            if self.rank == 0:
+                dist_ckpt.rotate_checkpoints(cdir, getattr(a, "max_checkpoints_to_keep", None))
         ds = getattr(self.runner, "data_source", None)
         if self.rank == 0 and ds is not None and hasattr(ds, "state_dict"):
             # where the prompt stream stands, so a resumed run goes on with the next unseen prompt

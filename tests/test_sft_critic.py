@@ -142,3 +142,18 @@ def test_critic_only_warmup_steps_leave_the_policy_untouched():
     assert torch.equal(run.actor.param_buf, p0) and not torch.equal(run.critic.param_buf, c0)
     run.step()
     assert not torch.equal(run.actor.param_buf, p0)
+
+
+def test_ppo_resume_restores_the_critic(tmp_path):
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    common = ["--model-name", "tiny", "--colocate", "--advantage-estimator", "ppo", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2",
+              "--global-batch-size", "4", "--rollout-max-response-len", "8", "--rm-type", "token_sum_parity", "--critic-lr", "5e-3",
+              "--save", str(tmp_path / "ck"), "--load", str(tmp_path / "ck"), "--save-interval", "1"]
+    c = Controller(parse_args(common + ["--num-rollout", "1"]), device="cpu")
+    c.training_loop()
+    trained = c.runner.critic.param_buf.clone()
+    assert (tmp_path / "ck_critic").is_dir()
+    c2 = Controller(parse_args(common + ["--num-rollout", "2"]), device="cpu")
+    assert torch.equal(c2.runner.critic.param_buf, trained) and c2.start_rollout_id == 1
