@@ -253,6 +253,9 @@ class Controller:
                 self.save(max(r for r, _ in out))
             return out
         rid = self.start_rollout_id
+        if _get(a, "timeline_dump_dir", None) and getattr(self.runner, "timer", None) is not None:
+            self.runner.timer.record_timeline = True
+            self.runner.timer.pid = self.rank
         if a.num_rollout is None and _get(a, "num_epoch", None) and hasattr(self.runner, "data_source"):
             # --num-epoch: as many rollouts as it takes to see every prompt that many times
             a.num_rollout = max(1, a.num_epoch * len(self.runner.data_source.dataset) // max(1, a.rollout_batch_size))
@@ -285,6 +288,11 @@ class Controller:
         if self._stop and a.save and rid > self.start_rollout_id:
             self.save(rid - 1)   # interrupted: keep what was learned
         self.profiler.close()
+        tdir = _get(a, "timeline_dump_dir", None)
+        timer = getattr(self.runner, "timer", None)
+        if tdir and timer is not None and hasattr(timer, "dump_chrome_trace"):     # one Chrome trace of the phase spans per rank
+            os.makedirs(tdir, exist_ok=True)
+            timer.dump_chrome_trace(os.path.join(tdir, f"timeline_rank{self.rank}.json"))
         return history
 
     def shutdown(self):

@@ -125,3 +125,16 @@ def test_openapi_routes_exist_on_live_servers(tmp_path):
         finally:
             srv.shutdown()
             srv.server_close()
+
+
+def test_timeline_dump(tmp_path):
+    import json
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--timeline-dump-dir", str(tmp_path / "tl")])
+    Controller(a, device="cpu").training_loop()
+    tr = json.load(open(tmp_path / "tl" / "timeline_rank0.json"))
+    names = {e["name"] for e in (tr["traceEvents"] if isinstance(tr, dict) else tr)}
+    assert {"rollout", "train"} <= names
