@@ -85,6 +85,10 @@ class ColocateConfig:
     stop_token_ids: tuple = ()
     stop_strings: tuple = ()        # --rollout-stop: the response ends with the first of these strings (needs a codec)
     critic_lr: Optional[float] = None
+    # rollout recovery (--use-health-check): a generate call that raises is retried after the engine's requests are
+    # aborted, its cache flushed and the weights re-synchronised; after this many consecutive failures the error is raised
+    use_health_check: bool = False
+    max_consecutive_failures: int = 3
     num_critic_only_steps: int = 0      # PPO: the first rollouts train the critic alone
     # more user hooks by path: fn(samples) -> (raw_rewards, shaped_rewards) replaces reward normalisation;
     # fn(args_like, samples) marks samples with remove_sample = True (their loss mask is zeroed);
@@ -213,6 +217,7 @@ class ColocatedGRPO:
         self.group_filter = load_function(cfg.dynamic_sampling_filter_path, 1, "group filter") \
             if cfg.dynamic_sampling_filter_path else None
         self.sampling_stats: dict = {}
+        self.recoveries = 0
         self.reward_post_process = load_function(cfg.custom_reward_post_process_path, 1, "reward post-process") \
             if cfg.custom_reward_post_process_path else None
         self.sample_filter = load_function(cfg.rollout_sample_filter_path, 2, "sample filter") if cfg.rollout_sample_filter_path else None
@@ -241,6 +246,22 @@ class ColocatedGRPO:
         return ms
 
     # ------------------------------------------------------------------ rollout
+    def _generate_with_recovery(self, prompts, sp, keys):
+        if not self.cfg.use_health_check:
+            return self.engine.generate(prompts, sp, group_keys=keys)
+        failures = 0
+        while True:
+            try:
+                return self.engine.generate(prompts, sp, group_keys=keys)
+            except Exception as e:   # noqa: BLE001 - any engine failure takes the same recovery path
+                failures += 1
+                self.recoveries += 1
+                if failures >= self.cfg.max_consecutive_failures:
+                    raise RuntimeError(f"rollout engine failed {failures} times in a row") from e
+                self.engine.abort_all()
+                self.engine.flush_cache()
+                self.sync_weights()
+
     def _generate_groups(self, n_groups: int, sp) -> list:
         """Draw ``n_groups`` prompt groups for this engine replica, generate and score them."""
         groups_all = self.data_source.get_samples(n_groups * self.num_engines)
@@ -252,7 +273,7 @@ class ColocatedGRPO:
                 if s.reward is None:
                     s.reward = self.reward_fn(s)
             return mine
-        res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
+        res = self._generate_with_recovery([s.tokens for s in flat], sp, [s.group_index for s in flat])
         for s, r in zip(flat, res):
             s.tokens = list(r.prompt) + list(r.output)
             s.response_length = len(r.output)
@@ -423,6 +444,8 @@ class ColocatedGRPO:
         m.update(self.timer.log_dict())
         m.update(eval_metrics)
         m.update(pass_metrics)
+        if cfg.use_health_check:
+            m["rollout/recoveries"] = float(self.recoveries)
         m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
         self.rollout_id += 1
         return m

@@ -93,3 +93,29 @@ def test_autoscaler_hold_time_and_cooldowns():
     assert [d[1] for d in a.decisions] == ["scale_out", "scale_out", "scale_in"]
     cfg2 = AutoscalerConfig.from_dict({"max_engines": 4, "rules": [{"metric": "x", "threshold": 1, "direction": "above"}]})
     assert cfg2.max_engines == 4 and cfg2.rules[0].metric == "x"
+
+
+def test_colocated_loop_recovers_from_engine_failures():
+    import pytest
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "8", "--use-health-check",
+                    "--rollout-health-check-max-consecutive-failures", "3"])
+    c = Controller(a, device="cpu")
+    eng = c.runner.engine
+    real, calls = eng.generate, {"n": 0, "fail": 2}
+
+    def flaky(*x, **k):                      # the failure is made on the host: the call raises before any work
+        calls["n"] += 1
+        if calls["n"] <= calls["fail"]:
+            raise RuntimeError("engine lost")
+        return real(*x, **k)
+
+    eng.generate = flaky
+    m = c.runner.step()
+    assert calls["n"] == 3 and m["rollout/recoveries"] == 2.0 and m["response_tokens_local"] > 0
+    calls.update(n=0, fail=99)
+    with pytest.raises(RuntimeError, match="3 times in a row"):
+        c.runner.step()
