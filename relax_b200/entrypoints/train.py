@@ -23,12 +23,16 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     use_cuda = torch.cuda.is_available()
     if world > 1 and not dist.is_initialized():
+        import datetime
+
+        minutes = getattr(args, "distributed_timeout_minutes", None)
+        kw = {"timeout": datetime.timedelta(minutes=minutes)} if minutes else {}
         if use_cuda:
             local = int(os.environ.get("LOCAL_RANK", "0"))
             torch.cuda.set_device(local)
-            dist.init_process_group(args.distributed_backend or "nccl", device_id=torch.device("cuda", local))
+            dist.init_process_group(args.distributed_backend or "nccl", device_id=torch.device("cuda", local), **kw)
         else:
-            dist.init_process_group("gloo")
+            dist.init_process_group("gloo", **kw)
     rank = dist.get_rank() if dist.is_initialized() else 0
     metrics = MetricsService(build_adapters(args) if rank == 0 else [])
     ctl = Controller(args, metrics)

@@ -38,6 +38,15 @@ class Controller:
             return None
         return build_codec(_get(a, "hf_checkpoint", None), self.model_cfg.vocab_size)
 
+    @staticmethod
+    def _hf_post_hook(a):
+        path = _get(a, "save_hf_post_hook_path", None)
+        if not path:
+            return None
+        from ..rollout.custom_generate import load_function
+
+        return load_function(path, 1, "HF export hook")
+
     def _eval_sets(self, a):
         return _eval_sets_from_args(a, self.model_cfg.vocab_size)
 
@@ -179,7 +188,8 @@ class Controller:
             return
         if dist_ckpt.read_latest_iteration(a.load) is None:
             return
-        dist_ckpt.load_checkpoint(a.load, self.model_cfg, actor.ps, actor.model, None if _get(a, "no_load_optim", False) else actor.optimizer)
+        skip_opt = _get(a, "no_load_optim", False) or _get(a, "reset_optimizer_states", False)
+        dist_ckpt.load_checkpoint(a.load, self.model_cfg, actor.ps, actor.model, None if skip_opt else actor.optimizer)
         if hasattr(self.runner, "sync_weights"):
             self.runner.sync_weights()
         if hasattr(self.runner, "rollout_id"):
@@ -219,7 +229,7 @@ class Controller:
             with open(os.path.join(dist_ckpt.iter_dir(a.save, rollout_id), "rollout_data_source.json"), "w") as f:
                 _json.dump(ds.state_dict(), f)
         if self.rank == 0:
-            dist_ckpt.rotate_checkpoints(a.save, getattr(a, "max_checkpoints_to_keep", None))
+            dist_ckpt.rotate_checkpoints(a.save, getattr(a, "max_checkpoints_to_keep", None) or _get(a, "max_actor_ckpt_to_keep", None))
             if _get(a, "save_hf", None):       # also export Hugging Face files from the checkpoint just written
                 from ..checkpoint import hf as H
 
@@ -228,7 +238,8 @@ class Controller:
                 out = a.save_hf.format(rollout_id=rollout_id) if "{" in a.save_hf else os.path.join(a.save_hf, f"iter_{rollout_id:07d}")
                 H.save_hf_checkpoint(out, self.model_cfg, H.convert_state_to_hf(self.model_cfg, full),
                                      quantize_fp8=_get(a, "save_hf_dtype", None) == "fp8",
-                                     fp8_block=_get(a, "save_hf_fp8_block_size", None) or 128)
+                                     fp8_block=_get(a, "save_hf_fp8_block_size", None) or 128,
+                                     post_hook=self._hf_post_hook(a))
 
     # ------------------------------------------------------------------ loop
     def _install_signal_handlers(self):
