@@ -304,6 +304,11 @@ class TrainActor:
     def compute_log_prob(self, batch: dict, tag: str = "actor", with_entropy: bool = False) -> dict:
         """Forward-only pass; returns per-sample lists ``log_probs`` (and ``entropy``)."""
         self.switch_model(tag)
+        suspended = None
+        if tag not in ("actor", "old_actor") and self.cfg.use_routing_replay and self.mcfg.is_moe:
+            from ..models.moe import RoutingReplay
+
+            suspended, RoutingReplay.mode = RoutingReplay.mode, None     # reference / teacher route for themselves
         toks, rl = batch["tokens"], batch["response_lengths"]
         mbs = self._microbatches([len(t) for t in toks])
         out_lp = [None] * len(toks)
@@ -318,6 +323,10 @@ class TrainActor:
             for i, a, b in zip(mb, torch.split(lp, pb.response_lengths), torch.split(en, pb.response_lengths)):
                 out_lp[i], out_en[i] = a, b
         self.switch_model("actor")
+        if suspended is not None:
+            from ..models.moe import RoutingReplay
+
+            RoutingReplay.mode = suspended
         res = {"log_probs": out_lp}
         if with_entropy:
             res["entropy"] = out_en
