@@ -23,8 +23,11 @@ class ByteCodec:
     def decode(self, ids: Sequence[int]) -> str:
         return bytes(i - self.offset for i in ids if self.offset <= i < self.offset + 256).decode("utf-8", errors="replace")
 
-    def render(self, messages: Sequence[dict], add_generation_prompt: bool = True, **kw) -> str:
-        out = "".join(f"<|{m['role']}|>\n{_text_of(m.get('content'))}\n" for m in messages)
+    def render(self, messages: Sequence[dict], add_generation_prompt: bool = True, tools=None, **kw) -> str:
+        import json as _json
+
+        head = f"<|tools|>\n{_json.dumps(tools)}\n" if tools else ""
+        out = head + "".join(f"<|{m['role']}|>\n{_text_of(m.get('content'))}\n" for m in messages)
         return out + ("<|assistant|>\n" if add_generation_prompt else "")
 
 
@@ -70,16 +73,17 @@ class PromptEncoder:
         self.codec, self.chat, self.kw = codec, apply_chat_template, dict(template_kwargs or {})
         self.system_prompt, self.max_len = system_prompt, max_prompt_len
 
-    def text(self, prompt: Any) -> str:
-        if isinstance(prompt, str) and not self.chat:
+    def text(self, prompt: Any, tools: Optional[list] = None) -> str:
+        if isinstance(prompt, str) and not self.chat and not tools:
             return (self.system_prompt + "\n" if self.system_prompt else "") + prompt
         msgs = [{"role": "user", "content": prompt}] if isinstance(prompt, str) else [dict(m) for m in prompt]
         if self.system_prompt and not (msgs and msgs[0].get("role") == "system"):
             msgs.insert(0, {"role": "system", "content": self.system_prompt})
-        return self.codec.render(msgs, add_generation_prompt=True, **self.kw)
+        kw = dict(self.kw, tools=tools) if tools else self.kw      # tool definitions go through the chat template
+        return self.codec.render(msgs, add_generation_prompt=True, **kw)
 
-    def __call__(self, prompt: Any) -> Optional[List[int]]:
-        ids = self.codec.encode(self.text(prompt))
+    def __call__(self, prompt: Any, tools: Optional[list] = None) -> Optional[List[int]]:
+        ids = self.codec.encode(self.text(prompt, tools))
         return None if self.max_len and len(ids) > self.max_len else ids
 
 

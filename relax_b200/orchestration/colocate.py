@@ -105,6 +105,7 @@ class ColocateConfig:
     input_key: str = "prompt"
     label_key: Optional[str] = "label"
     metadata_key: str = "metadata"
+    tool_key: Optional[str] = None      # row field with tool definitions, rendered by the chat template
     rollout_shuffle: bool = False
     use_streaming_dataset: bool = False     # read the prompt files lazily through a shuffle buffer
     streaming_buffer_size: int = 1024
@@ -201,7 +202,7 @@ class ColocatedGRPO:
                                                               cfg.rollout_seed, cfg.input_key, cfg.label_key, cfg.metadata_key,
                                                               shuffle=cfg.rollout_shuffle)
             else:
-                ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key)
+                ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key, cfg.tool_key)
                 if len(ds) == 0:
                     raise ValueError(f"no usable prompt in {cfg.prompt_data} (limit {cfg.prompt_len} tokens)")
         else:

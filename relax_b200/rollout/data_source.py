@@ -36,7 +36,7 @@ class JsonlPromptDataset:
     """``{"prompt": ..., "label": ...}`` per line; tokenised lazily by ``tokenize``."""
 
     def __init__(self, path: str, tokenize: Optional[Callable] = None, prompt_key="prompt", label_key="label",
-                 metadata_key: str = "metadata"):
+                 metadata_key: str = "metadata", tool_key: Optional[str] = None):
         """``path`` may list several files separated by commas.  Rows whose prompt ``tokenize`` rejects (returns
         None: longer than the prompt limit) are dropped at load time, so the epoch length is known up front."""
         self.rows = []
@@ -48,7 +48,10 @@ class JsonlPromptDataset:
         if tokenize is not None:
             kept = []
             for r in self.rows:
-                toks = tokenize(r[prompt_key])
+                tools = r.get(tool_key) if tool_key else None
+                if isinstance(tools, str):
+                    tools = json.loads(tools) if tools.strip() else None
+                toks = tokenize(r[prompt_key], tools=tools) if tools else tokenize(r[prompt_key])
                 if toks is not None:
                     r["_tokens"] = toks
                     kept.append(r)

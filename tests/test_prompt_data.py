@@ -141,3 +141,15 @@ def test_resume_continues_the_prompt_stream(tmp_path):
     assert c2.start_rollout_id == 2 and c2.runner.data_source.state_dict()["offset"] == 4
     labels = [g[0].label for g in c2.runner.data_source.get_samples(2)]
     assert labels == ["4", "5"]
+
+
+def test_tool_definitions_are_rendered_into_the_prompt(tmp_path):
+    c = ByteCodec(4096)
+    f = tmp_path / "t.jsonl"
+    tools = [{"type": "function", "function": {"name": "search", "parameters": {}}}]
+    f.write_text(json.dumps({"prompt": [{"role": "user", "content": "find it"}], "tools": json.dumps(tools)}) + "\n" +
+                 json.dumps({"prompt": [{"role": "user", "content": "no tools"}]}) + "\n")
+    ds = JsonlPromptDataset(str(f), PromptEncoder(c, apply_chat_template=True), "prompt", None, "metadata", tool_key="tools")
+    with_tools, without = c.decode(ds[0]["prompt_tokens"]), c.decode(ds[1]["prompt_tokens"])
+    assert with_tools.startswith("<|tools|>") and '"search"' in with_tools and "find it" in with_tools
+    assert not without.startswith("<|tools|>") and ds[0]["label"] is None
