@@ -119,6 +119,7 @@ class ColocateConfig:
     skip_eval_before_train: bool = False
     eval_temperature: float = 0.0
     eval_max_response_len: Optional[int] = None
+    eval_reward_key: Optional[str] = None
 
 
 class ColocatedGRPO:
@@ -364,7 +365,8 @@ class ColocatedGRPO:
         sp = SamplingParams(temperature=cfg.eval_temperature, top_p=1.0, top_k=-1,
                             max_new_tokens=cfg.eval_max_response_len or cfg.max_response_len)
         with self.timer.span("eval"):
-            m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp, decode=self.codec.decode if self.codec is not None else None)
+            m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp, decode=self.codec.decode if self.codec is not None else None,
+                      reward_key=cfg.eval_reward_key)
         if cfg.offload_rollout:
             self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
         return m

@@ -133,7 +133,8 @@ class Controller:
                 eval_datasets=self._eval_sets(a), eval_interval=_get(a, "eval_interval", None),
                 skip_eval_before_train=bool(_get(a, "skip_eval_before_train", False)),
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,
-                eval_max_response_len=_get(a, "eval_max_response_len", None))
+                eval_max_response_len=_get(a, "eval_max_response_len", None),
+                eval_reward_key=_get(a, "eval_reward_key", None) or _get(a, "reward_key", None))
             return ColocatedGRPO(cfg, device=self.device)
         if self.mode == "sft":
             from ..train.actor import TrainActor

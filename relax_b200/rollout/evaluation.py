@@ -42,15 +42,17 @@ def pass_at_k(n: int, c: int, k: int) -> float:
     return 1.0 - math.prod((n - c - i) / (n - i) for i in range(k))
 
 
-def _scalar(r) -> float:
+def _scalar(r, key: Optional[str] = None) -> float:
     if isinstance(r, dict):
-        r = r.get("score", r.get("reward", 0.0))
+        r = r[key] if key and key in r else r.get("score", r.get("reward", 0.0))
     return float(r)
 
 
-def summarize(name: str, groups: Sequence[Sequence[Sample]], correct_threshold: float = 0.5) -> Dict[str, float]:
-    """Metrics of one evaluated set; ``groups[i]`` are the samples of prompt ``i``."""
-    rewards = [_scalar(s.reward) for g in groups for s in g]
+def summarize(name: str, groups: Sequence[Sequence[Sample]], correct_threshold: float = 0.5,
+              reward_key: Optional[str] = None) -> Dict[str, float]:
+    """Metrics of one evaluated set; ``groups[i]`` are the samples of prompt ``i``.  ``reward_key`` picks the entry of
+    dict-valued rewards (``--eval-reward-key``)."""
+    rewards = [_scalar(s.reward, reward_key) for g in groups for s in g]
     lens = [s.response_length for g in groups for s in g]
     trunc = [s.status == SampleStatus.TRUNCATED for g in groups for s in g]
     out = {f"eval/{name}": statistics.fmean(rewards) if rewards else 0.0,
@@ -61,7 +63,7 @@ def summarize(name: str, groups: Sequence[Sequence[Sample]], correct_threshold: 
     n = min((len(g) for g in groups), default=0)
     k = 1
     while n >= 1 and k <= n:
-        vals = [pass_at_k(len(g), sum(_scalar(s.reward) > correct_threshold for s in g), k) for g in groups]
+        vals = [pass_at_k(len(g), sum(_scalar(s.reward, reward_key) > correct_threshold for s in g), k) for g in groups]
         out[f"eval/{name}-pass@{k}"] = statistics.fmean(vals)
         k *= 2
     return out
@@ -100,7 +102,8 @@ def load_eval_datasets(pairs: Sequence[str], tokenize: Callable[[Any], list], in
 
 
 def evaluate(engine, datasets: Sequence[EvalDataset], reward_fn: Callable[[Sample], Any], sampling_defaults,
-             decode: Optional[Callable[[list], str]] = None, reward_fns: Optional[Dict[str, Callable]] = None) -> Dict[str, float]:
+             decode: Optional[Callable[[list], str]] = None, reward_fns: Optional[Dict[str, Callable]] = None,
+             reward_key: Optional[str] = None) -> Dict[str, float]:
     """Run every set through ``engine.generate`` (one call per set, all samples batched) and score it.
     ``sampling_defaults`` is a :class:`~relax_b200.rollout.engine.SamplingParams`; per-set fields override it."""
     import dataclasses as _dc
@@ -125,5 +128,5 @@ def evaluate(engine, datasets: Sequence[EvalDataset], reward_fn: Callable[[Sampl
                 s.response = decode(list(r.output))
             s.reward = score(s)
             groups[gi].append(s)
-        metrics.update(summarize(ds.name, groups))
+        metrics.update(summarize(ds.name, groups, reward_key=reward_key))
     return metrics

@@ -103,3 +103,12 @@ def test_dump_replay_passrate_epochs_and_reference_refresh(tmp_path):
     c2.runner.engine.generate = lambda *x, **k: calls.append(1)
     m = c2.runner.step()
     assert not calls and abs(m["raw_reward_mean"] - hist[0]["raw_reward_mean"]) < 1e-9
+
+
+def test_reward_key_selects_the_dict_entry():
+    def S(r):
+        return Sample(reward=r, response_length=1, status=SampleStatus.COMPLETED)
+    groups = [[S({"score": 0.0, "acc": 1.0}), S({"score": 0.0, "acc": 0.0})]]
+    assert E.summarize("x", groups)["eval/x"] == 0.0
+    m = E.summarize("x", groups, reward_key="acc")
+    assert m["eval/x"] == 0.5 and m["eval/x-pass@2"] == 1.0
