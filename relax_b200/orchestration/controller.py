@@ -325,7 +325,10 @@ class _SFTRunner:
 
         self.actor = actor
         files = [p for p in str(args.prompt_data).split(",") if p]
-        tok = _byte_tokenizer(actor.mcfg.vocab_size)
+        from ..data.tokenizer import build_codec, has_tokenizer_files
+
+        hf = _get(args, "hf_checkpoint", None)      # the model's own tokenizer when its files are there, bytes otherwise
+        tok = build_codec(hf, actor.mcfg.vocab_size).encode if has_tokenizer_files(hf) else _byte_tokenizer(actor.mcfg.vocab_size)
         ds = StreamingSFTDataset(files, tok, actor.ps.dp.rank, actor.ps.dp.size,
                                  max_len=_get(args, "rollout_max_context_len", 4096), epochs=None)
         per_rank = max(1, actor.cfg.global_batch_size // actor.ps.dp.size)
