@@ -153,3 +153,23 @@ def test_tool_definitions_are_rendered_into_the_prompt(tmp_path):
     with_tools, without = c.decode(ds[0]["prompt_tokens"]), c.decode(ds[1]["prompt_tokens"])
     assert with_tools.startswith("<|tools|>") and '"search"' in with_tools and "find it" in with_tools
     assert not without.startswith("<|tools|>") and ds[0]["label"] is None
+
+
+def test_hf_codec_with_a_locally_built_tokenizer(tmp_path):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from relax_b200.data.tokenizer import HFCodec
+
+    vocab = {"[UNK]": 0, "[EOS]": 1, "hello": 2, "world": 3, "what": 4, "is": 5, "?": 6, "user": 7, "assistant": 8}
+    t = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    t.pre_tokenizer = pre_tokenizers.Whitespace()
+    fast = PreTrainedTokenizerFast(tokenizer_object=t, unk_token="[UNK]", eos_token="[EOS]")
+    fast.chat_template = ("{% for m in messages %}{{ m['role'] }} {{ m['content'] }} {% endfor %}"
+                          "{% if add_generation_prompt %}assistant {% endif %}")
+    fast.save_pretrained(str(tmp_path))
+    assert has_tokenizer_files(str(tmp_path))
+    c = build_codec(str(tmp_path), 100)
+    assert isinstance(c, HFCodec) and c.encode("hello world") == [2, 3] and c.decode([2, 3]) == "hello world" and c.eos_token_id == 1
+    ids = PromptEncoder(c, apply_chat_template=True)([{"role": "user", "content": "what is hello ?"}])
+    assert ids == [7, 4, 5, 2, 6, 8]
