@@ -138,3 +138,26 @@ def test_timeline_dump(tmp_path):
     tr = json.load(open(tmp_path / "tl" / "timeline_rank0.json"))
     names = {e["name"] for e in (tr["traceEvents"] if isinstance(tr, dict) else tr)}
     assert {"rollout", "train"} <= names
+
+
+def test_openapi_chat_routes_exist_on_a_live_server():
+    import json
+    import urllib.error
+    import urllib.request
+
+    from relax_b200.rollout.agentic import Tokenizer
+    from relax_b200.rollout.openai_api import ChatService, serve
+    from relax_b200.utils import openapi
+
+    tok = Tokenizer(encode=lambda s: [ord(c) for c in s], decode=lambda t: "".join(chr(97 + x % 26) for x in t))
+    gen = lambda prompts, n, keys: [([5, 6], [-0.1, -0.2], "stop", [0]) for _ in prompts]
+    srv, url = serve(ChatService(gen, tok))
+    try:
+        for method, path, _, schema in openapi.ROUTES["chat"]:
+            body = {"messages": [{"role": "user", "content": "hi"}]} if method == "post" else None
+            req = urllib.request.Request(url + path, data=json.dumps(body).encode() if body else None,
+                                         headers={"Content-Type": "application/json"}, method=method.upper())
+            assert urllib.request.urlopen(req, timeout=10).status == 200, path
+    finally:
+        srv.shutdown()
+        srv.server_close()
