@@ -79,7 +79,9 @@ def chunked_log_probs_and_entropy(hidden, weight, targets, tp_group=None, vocab_
     """LM head + log-prob over token chunks so at most ``chunk_size x V_local``
     logits exist at once (the role of ``--log-probs-chunk-size``)."""
     lps, ents = [], []
-    for s in range(0, hidden.shape[0], chunk_size):
+    # a rank may hold no rows at all (context parallelism: the response can sit wholly on the other ranks); it
+    # still runs one empty chunk so the tensor-parallel collectives inside match and the graph reaches the weights
+    for s in range(0, max(1, hidden.shape[0]), chunk_size):
         h = hidden[s : s + chunk_size]
         logits = h @ weight.t()
         lp, en = vocab_parallel_log_probs_and_entropy(

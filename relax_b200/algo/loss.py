@@ -270,6 +270,7 @@ def compute_advantages_and_returns(
     normalize_advantages: bool = False,
     dp_group=None,
     custom_advantage: Optional[torch.Tensor] = None,
+    stats_out: Optional[dict] = None,
 ):
     """Advantage/return estimation for all supported estimators
     (relax/backends/megatron/loss.py:532-738).  ``rewards`` are the already
@@ -302,5 +303,11 @@ def compute_advantages_and_returns(
         raise ValueError(f"unknown advantage estimator {estimator}")
 
     if normalize_advantages:
-        adv = P.masked_whiten(adv, loss_mask, group=dp_group) * (loss_mask != 0)
+        if estimator in ("reinforce_plus_plus", "reinforce_plus_plus_baseline"):
+            # population moments with a variance floor, not the Bessel-corrected whitening of the other estimators
+            adv, st = P.masked_normalize(adv, loss_mask, group=dp_group, return_stats=True)
+            if stats_out is not None:
+                stats_out.update(st)
+        else:
+            adv = P.masked_whiten(adv, loss_mask, group=dp_group) * (loss_mask != 0)
     return adv, ret

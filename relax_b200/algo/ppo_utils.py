@@ -394,18 +394,35 @@ def masked_whiten(x, mask, shift_mean: bool = True, group=None, eps: float = 1e-
     return out
 
 
-def masked_normalize(x, mask, group=None, eps: float = 1e-8):
-    """Mean-centre then divide by the masked RMS of the centred values."""
+def masked_normalize(x, mask, group=None, variance_floor: float = 1e-8, return_stats: bool = False):
+    """REINFORCE++ advantage normalisation (relax/utils/distributed_utils.py distributed_masked_normalize
+    :161-213): mean and POPULATION variance (ddof = 0) over every mask-nonzero element of the whole
+    data-parallel group, ``(x - mean) * rsqrt(max(var, floor))`` inside the mask and exactly zero outside.
+    With ``return_stats`` also returns ``{raw_mean, raw_std, normalized_mean, normalized_std, valid_token_count,
+    zero_variance}`` as the reference logs them (relax/backends/megatron/loss.py:706-726)."""
     import torch.distributed as dist
 
-    m = mask.to(x.dtype)
-    s = torch.stack([(x * m).sum(), m.sum()])
+    if variance_floor <= 0:
+        raise ValueError("variance_floor must be positive")
+    wd = torch.float64 if x.dtype == torch.float64 else torch.float32
+    xv = x.to(wd)
+    valid = mask != 0
+    m = valid.to(wd)
+    s = torch.stack([torch.where(valid, xv, torch.zeros_like(xv)).sum(), m.sum()])
     if group is not None and dist.is_initialized():
         dist.all_reduce(s, group=group)
-    mean = s[0] / s[1].clamp_min(1)
-    c = x - mean
-    v = torch.stack([(c * c * m).sum()])
+    cnt = s[1].clamp_min(1)
+    mean = s[0] / cnt
+    c = torch.where(valid, xv - mean, torch.zeros_like(xv))
+    v = c.square().sum().reshape(1)
     if group is not None and dist.is_initialized():
         dist.all_reduce(v, group=group)
-    var = v[0] / s[1].clamp_min(1)
-    return c * torch.rsqrt(var + eps)
+    var = (v[0] / cnt).clamp_min(0.0)
+    out = torch.where(valid, (xv - mean) * torch.rsqrt(var.clamp_min(variance_floor)), torch.zeros_like(xv)).to(x.dtype)
+    if not return_stats:
+        return out
+    nvar = var / torch.maximum(var, torch.tensor(variance_floor, dtype=wd, device=x.device))
+    stats = {"reinforce_pp_advantage_raw_mean": mean.detach(), "reinforce_pp_advantage_raw_std": var.sqrt().detach(),
+             "reinforce_pp_advantage_normalized_mean": torch.zeros_like(mean), "reinforce_pp_advantage_normalized_std": nvar.sqrt().detach(),
+             "reinforce_pp_valid_token_count": s[1].detach(), "reinforce_pp_zero_variance": (var == 0).to(wd).detach()}
+    return out, stats

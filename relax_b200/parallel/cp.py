@@ -63,18 +63,21 @@ def slice_sequence_with_cp(x: torch.Tensor, cp: int, rank: int, pad_value=0) -> 
     return torch.cat([x[rank * cs:(rank + 1) * cs], x[(2 * cp - rank - 1) * cs:(2 * cp - rank) * cs]], 0)
 
 
-def slice_log_prob_with_cp(x: torch.Tensor, total_length: int, response_length: int, cp: int, rank: int) -> torch.Tensor:
-    """Local part of a per-response-token tensor ``[R]`` (log-probs, advantages, masks)."""
+def slice_log_prob_with_cp(x: torch.Tensor, total_length: int, response_length: int, cp: int, rank: int,
+                           padded_total_length: Optional[int] = None) -> torch.Tensor:
+    """Local part of a per-response-token tensor ``[R]`` (log-probs, advantages, masks).  ``padded_total_length``
+    is the length the forward sharded the sequence at (a multiple of ``2*cp``); it must be the same value here."""
     if cp == 1:
         return x
     prompt = total_length - response_length
-    _, _, logits, _ = offsets_with_cp(total_length, response_length, cp, rank)
+    _, _, logits, _ = offsets_with_cp(total_length, response_length, cp, rank, padded_total_length)
     parts = [x[a - (prompt - 1): b - (prompt - 1)] for a, b in logits if b > a]
     return torch.cat(parts) if parts else x[:0]
 
 
-def local_num_response_tokens(total_length: int, response_length: int, cp: int, rank: int) -> int:
-    _, _, logits, _ = offsets_with_cp(total_length, response_length, cp, rank)
+def local_num_response_tokens(total_length: int, response_length: int, cp: int, rank: int,
+                              padded_total_length: Optional[int] = None) -> int:
+    _, _, logits, _ = offsets_with_cp(total_length, response_length, cp, rank, padded_total_length)
     return sum(b - a for a, b in logits)
 
 
@@ -96,14 +99,15 @@ class _AllReduceDiff(torch.autograd.Function):
         return g, None
 
 
-def all_gather_with_cp(local: torch.Tensor, total_length: int, response_length: int, g: GroupInfo) -> torch.Tensor:
+def all_gather_with_cp(local: torch.Tensor, total_length: int, response_length: int, g: GroupInfo,
+                       padded_total_length: Optional[int] = None) -> torch.Tensor:
     """Rebuild the full ``[R]`` response tensor from CP-local pieces: every rank writes its pieces into a
     zero tensor at their offsets and the tensors are summed (differentiable;
     relax/backends/megatron/cp_utils.py:288-355)."""
     if g.size == 1:
         return local
     prompt = total_length - response_length
-    _, _, logits, _ = offsets_with_cp(total_length, response_length, g.size, g.rank)
+    _, _, logits, _ = offsets_with_cp(total_length, response_length, g.size, g.rank, padded_total_length)
     full = local.new_zeros(response_length)
     pieces, o = [], 0
     for a, b in logits:
@@ -116,20 +120,29 @@ def all_gather_with_cp(local: torch.Tensor, total_length: int, response_length: 
     return _AllReduceDiff.apply(full, g.group)
 
 
-def gather_response_with_cp(local: torch.Tensor, total_length: int, response_length: int, g: GroupInfo) -> torch.Tensor:
+def gather_response_with_cp(local: torch.Tensor, total_length: int, response_length: int, g: GroupInfo,
+                            padded_total_length: Optional[int] = None) -> torch.Tensor:
     """Full ``[R]`` response tensor on every rank, differentiable ONLY through this rank's own pieces: the value
     is the same everywhere, but a loss computed from it sends gradient to the local tokens alone, so averaging
     parameter gradients over the dp x cp world gives the gradient of the replicated loss exactly once."""
     if g.size == 1:
         return local
     prompt = total_length - response_length
-    _, _, logits, _ = offsets_with_cp(total_length, response_length, g.size, g.rank)
+    _, _, logits, _ = offsets_with_cp(total_length, response_length, g.size, g.rank, padded_total_length)
+    if local.numel() != sum(b - a for a, b in logits):
+        raise ValueError(f"rank {g.rank} holds {local.numel()} response rows, the layout expects "
+                         f"{sum(b - a for a, b in logits)} (sequence sharded at a different padded length?)")
     idx, o = [], 0
     for a, b in logits:
         if b > a:
             idx.append(torch.arange(a - (prompt - 1), b - (prompt - 1), device=local.device))
     idx = torch.cat(idx) if idx else torch.zeros(0, dtype=torch.long, device=local.device)
-    mine = local.new_zeros(response_length).index_put((idx,), local) if idx.numel() else local.new_zeros(response_length)
+    if idx.numel():
+        mine = local.new_zeros(response_length).index_put((idx,), local)
+    else:
+        # no response row of this sample lives here: stay in the autograd graph all the same, so this rank's
+        # backward runs and takes part in the ring exchanges of the ranks that do hold rows
+        mine = local.new_zeros(response_length) + local.sum() * 0
     full = mine.detach().clone()
     dist.all_reduce(full, group=g.group)
     return full - mine.detach() + mine

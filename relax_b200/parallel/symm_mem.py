@@ -71,14 +71,27 @@ class SymmBuffer:
     def local(self, shape, dtype) -> torch.Tensor:
         return _C().tensor_from_ptr(self.local_ptr, list(shape), dtype, self.dev_index)
 
-    def close(self):
+    def unmap_peers(self):
         C = _C()
         for p in self._opened:
             C.ipc_close(p, self.dev_index)
         self._opened = []
+
+    def free_local(self):
         if self.local_ptr:
-            C.symm_free(self.local_ptr, self.dev_index)
+            _C().symm_free(self.local_ptr, self.dev_index)
             self.local_ptr = 0
+
+    def close(self, barrier: bool = True):
+        """Collective over the group: every rank unmaps its peers' buffers, all ranks meet, then each frees its own.
+        Freeing an exported allocation while an importer still has it mapped is undefined in CUDA IPC, so the
+        meeting point is not optional when the group is still alive (``barrier=False`` is for callers that close
+        several buffers and meet once themselves)."""
+        self.unmap_peers()
+        if barrier and self.g.size > 1 and dist.is_initialized() and self.local_ptr:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.g.group)
+        self.free_local()
 
 
 def workspace_bytes(tp: int, splits: int, rows_out: int, n: int) -> int:
@@ -214,9 +227,19 @@ class SymmComm:
         return y, None
 
     def close(self):
-        self.ws.close()
-        self.sig.close()
-        self.ag.close()
+        """Collective over the group (see :meth:`SymmBuffer.close`): unmap everything, meet once, free."""
+        bufs = (self.ws, self.sig, self.ag)
+        if self.g.size == 1:
+            for b in bufs:
+                b.close()
+            return
+        for b in bufs:
+            b.unmap_peers()
+        if dist.is_initialized() and self.ws.local_ptr:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.g.group)
+        for b in bufs:
+            b.free_local()
 
 
 def attach_group(g: GroupInfo, device: torch.device, workspace_mb: int = 256) -> Optional[SymmComm]:

@@ -48,6 +48,9 @@ class TrainConfig:
     balance_data: bool = False
     recompute: bool = False
     pad_multiple: int = 128
+    # context parallelism: every zig-zag chunk is padded to a multiple of this many tokens (None: ``pad_multiple``
+    # on a GPU, where the attention tiles want whole 128-row blocks, 1 on the CPU)
+    cp_chunk_multiple: Optional[int] = None
     use_rollout_logprobs: bool = False
     keep_old_actor: bool = False
     compute_entropy: bool = True
@@ -195,7 +198,8 @@ class TrainActor:
 
         g = self.ps.cp
         cp, r = g.size, g.rank
-        unit = 2 * cp * max(1, self.ps.tp.size) * (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
+        mult = self.cfg.cp_chunk_multiple or (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
+        unit = 2 * cp * max(1, self.ps.tp.size) * mult
         cu = pb.cu_seqlens.tolist()
         lps, ens = [], []
         for si, R in enumerate(pb.response_lengths):
@@ -217,8 +221,8 @@ class TrainActor:
             h = self.model(tok_pad[idx], idx, None, attn_fn=attn)
             sel = (idx >= L - R - 1) & (idx <= L - 2)
             lp, en = self.model.log_probs(h[sel], tok_pad[idx + 1][sel], self.cfg.rollout_temperature, with_entropy)
-            lps.append(CP.gather_response_with_cp(lp, L, R, g))
-            ens.append(CP.gather_response_with_cp(en, L, R, g) if with_entropy else lp.new_zeros(R))
+            lps.append(CP.gather_response_with_cp(lp, L, R, g, padded_total_length=Lp))
+            ens.append(CP.gather_response_with_cp(en, L, R, g, padded_total_length=Lp) if with_entropy else lp.new_zeros(R))
         return torch.cat(lps), torch.cat(ens)
 
     def _forward_logp(self, pb, with_entropy: bool):
@@ -397,7 +401,7 @@ class TrainActor:
             cfg.advantage_estimator, rewards, seg_all, mask_all,
             log_probs=cat("log_probs"), ref_log_probs=cat("ref_log_probs"), values=cat("values"),
             kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type, gamma=cfg.gamma, lambd=cfg.lambd,
-            normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group,
+            normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group, stats_out=(adv_stats := {}),
         )
         batch["advantages"] = seg_all.split(adv)
         batch["returns"] = seg_all.split(ret)
@@ -437,6 +441,7 @@ class TrainActor:
         out = {k: float(v) for k, v in agg.items()}
         if opd_metric is not None:
             out["opd_kl"] = opd_metric
+        out.update({k: float(v) for k, v in adv_stats.items()})
         out["grad_norm"] = last_norm
         out["train_time"] = time.perf_counter() - t0
         return out

@@ -326,20 +326,31 @@ class DistributedOptimizer:
             p.main_grad = None
             p.grad = None
 
+    def _bind_grads(self, buf: torch.Tensor):
+        self.grad_buf = buf
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = buf[o:o + p.numel()].view_as(p)
+            if buf.dtype == self.pdtype:
+                p.grad = p.main_grad
+
     def allocate_grads(self):
         if self.grad_buf is not None:
             return
         shape, dtype, dev = self._grad_meta
-        self.grad_buf = torch.zeros(shape, dtype=dtype, device=dev)
-        for p, o in zip(self.params, self.offsets):
-            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
-            if dtype == self.pdtype:
-                p.grad = p.main_grad
+        if self._symm is not None:
+            # the fused reduce-scatter reads every rank's SYMMETRIC gradient buffer: accumulate there, never in a
+            # private tensor
+            buf = self._symm["grad"].local(tuple(shape), dtype)
+            buf.zero_()
+        else:
+            buf = torch.zeros(shape, dtype=dtype, device=dev)
+        self._bind_grads(buf)
 
     # ------------------------------------------------------------------ offload (colocate sleep / wake_up)
     def offload_state(self):
         """Move optimizer state to pinned host memory and release the gradient
-        buffer (relax/backends/megatron/weight_update/train_offload.py:135-346)."""
+        buffer (relax/backends/megatron/weight_update/train_offload.py:135-346).  A symmetric gradient buffer
+        stays where it is: the peers have it mapped and the fused step reads it by address."""
         self._host = {}
         for name in ("exp_avg", "exp_avg_sq", "master", "master_rem"):
             t = getattr(self, name, None)
@@ -348,24 +359,43 @@ class DistributedOptimizer:
             h = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
             h.copy_(t, non_blocking=True)
             self._host[name] = h
-        if self.grad_buf.is_cuda:
+        if self.grad_buf is not None and self.grad_buf.is_cuda:
             torch.cuda.current_stream().synchronize()
             for name in self._host:
                 setattr(self, name, None)
-            self._grad_meta = (self.grad_buf.shape, self.grad_buf.dtype, self.grad_buf.device)
-            self.grad_buf = None
-            for p in self.params:
-                p.main_grad = None
-                p.grad = None
+            if self._symm is None:
+                self._grad_meta = (self.grad_buf.shape, self.grad_buf.dtype, self.grad_buf.device)
+                self.grad_buf = None
+                for p in self.params:
+                    p.main_grad = None
+                    p.grad = None
 
     def onload_state(self):
         host = getattr(self, "_host", None)
         if not host:
             return
-        shape, dtype, dev = self._grad_meta
+        dev = self.param_buf.device
         for name, h in host.items():
             setattr(self, name, h.to(dev, non_blocking=True))
-        self.grad_buf = torch.zeros(shape, dtype=dtype, device=dev)
-        for p, o in zip(self.params, self.offsets):
-            p.main_grad = self.grad_buf[o:o + p.numel()].view_as(p)
+        if self.grad_buf is None:
+            self.allocate_grads()
         self._host = None
+
+    def close(self):
+        """Unmap the peers' symmetric buffers and free this rank's (every rank of the data-parallel group calls
+        this, after its last step has completed on the device and before the process groups are destroyed)."""
+        sy, self._symm = self._symm, None
+        if sy is None:
+            return
+        for p in self.params:
+            p.main_grad = None
+            p.grad = None
+        self.grad_buf = None
+        bufs = [sy[k] for k in ("param", "grad", "sig")]
+        for b in bufs:
+            b.unmap_peers()
+        if dist.is_initialized() and self.ps.dp_cp.size > 1:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.ps.dp_cp.group)
+        for b in bufs:
+            b.free_local()

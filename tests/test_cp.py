@@ -80,14 +80,15 @@ def test_ring_attention_matches_full_attention_two_ranks():
     assert all(run_distributed(_ring_worker, 2))
 
 
-def _cp_train_worker(rank, world):
+def _cp_train_worker(rank, world, chunk_multiple=None):
     """cp=2 trainer forward/backward equals the single-rank one (log-probs and parameter gradients)."""
     from relax_b200.models.config import get_config
     from relax_b200.parallel.state import ParallelDims, init_parallel_state
     from relax_b200.train.actor import TrainActor, TrainConfig
 
     ps = init_parallel_state(ParallelDims(cp=2))
-    actor = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512), ps, seed=7)
+    actor = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512, cp_chunk_multiple=chunk_multiple),
+                       ps, seed=7)
     toks = [list(range(3, 40)), list(range(50, 73))]
     rl = [11, 9]
     pb = actor._pack(toks, rl)
@@ -101,11 +102,29 @@ def _cp_train_worker(rank, world):
     return lp.detach(), en.detach(), gsum
 
 
-def test_trainer_forward_backward_under_cp2_matches_cp1():
+def test_padded_layout_offsets_cover_each_token_once():
+    """With chunks padded to a tile multiple (the GPU layout) the loss-side offsets still cover every response
+    row exactly once and differ from the unpadded layout's."""
+    L, R, cp, Lp = 1000, 600, 2, 1024
+    seen = []
+    for r in range(cp):
+        cs, _, logits, _ = CP.offsets_with_cp(L, R, cp, r, padded_total_length=Lp)
+        assert cs == Lp // (2 * cp)
+        seen += [i for a, b in logits for i in range(a, b)]
+    assert sorted(seen) == list(range(L - R - 1, L - 1))
+    assert CP.local_num_response_tokens(L, R, cp, 0, Lp) != CP.local_num_response_tokens(L, R, cp, 0)
+    assert sum(CP.local_num_response_tokens(L, R, cp, r, Lp) for r in range(cp)) == R
+
+
+import pytest
+
+
+@pytest.mark.parametrize("chunk_multiple", [None, 8])
+def test_trainer_forward_backward_under_cp2_matches_cp1(chunk_multiple):
     from relax_b200.models.config import get_config
     from relax_b200.train.actor import TrainActor, TrainConfig
 
-    out = run_distributed(_cp_train_worker, 2)
+    out = run_distributed(_cp_train_worker, 2, chunk_multiple)
     ref = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512), seed=7)
     toks = [list(range(3, 40)), list(range(50, 73))]
     pb = ref._pack(toks, [11, 9])

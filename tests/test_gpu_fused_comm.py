@@ -211,6 +211,55 @@ def _dpopt_worker(rank, world):
     return float((pf - pn).abs().max()), abs(nf - nn) / max(nn, 1e-9), float(pf.abs().sum())
 
 
+def _dpopt_sleep_worker(rank, world):
+    """Step, offload (sleep), onload (wake up), step on different gradients: the fused path must reduce the NEW
+    gradients, i.e. keep accumulating into the symmetric buffer its reduce kernel reads."""
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.ops import cuda as C
+    from relax_b200.parallel.state import ParallelDims, init_parallel_state
+    from relax_b200.train.optimizer import DistributedOptimizer, OptimizerConfig
+
+    dev = torch.device("cuda", rank)
+    ps = init_parallel_state(ParallelDims(dp=2))
+    cfg = get_config("qwen3-0.6b", num_layers=2, vocab_size=2048)
+    outs = []
+    for fused in (True, False):
+        model = GPTModel(cfg, ps, device=dev, seed=0)
+        opt = DistributedOptimizer(model, ps, OptimizerConfig(lr=1e-3, clip_grad=1.0, fused_dp=fused))
+        norms = []
+        for step in range(3):
+            opt.zero_grad()
+            g = torch.Generator(device="cpu").manual_seed(100 * step + rank)
+            for p in opt.params:
+                p.main_grad.copy_((torch.randn(p.shape, generator=g) * 0.01 * (step + 1)).to(dev))
+            norm, skipped = opt.step()
+            norms.append(float(norm))
+            assert not skipped
+            opt.offload_state()
+            if fused:
+                assert opt.grad_buf is not None and opt.grad_buf.data_ptr() == opt._symm["grad"].local_ptr
+            opt.onload_state()
+            if fused:
+                assert opt.params[0].main_grad.data_ptr() >= opt._symm["grad"].local_ptr
+        torch.cuda.synchronize(dev)
+        C.check_error_flag(dev)
+        master = opt.master_shard_fp32().clone()
+        outs.append((opt.param_buf.float().clone(), norms, master))
+        opt.close()
+    (pf, nf, mf), (pn, nn, mn) = outs
+    nrel = max(abs(a - b) / max(b, 1e-9) for a, b in zip(nf, nn))
+    return float((pf - pn).abs().max()), nrel, float((mf - mn).abs().max()), nn
+
+
+@pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
+def test_fused_distributed_optimizer_survives_sleep_and_wake_up():
+    out = run_distributed(_dpopt_sleep_worker, 2, backend="nccl", timeout=600)
+    for diff, nrel, mdiff, norms in out:
+        assert norms[0] != norms[1] != norms[2]          # every step saw its own gradients
+        assert diff <= 5e-4 and nrel < 1e-4 and mdiff <= 1e-6, out
+
+
 @pytest.mark.skipif(not _two_gpus(), reason="needs 2 GPUs")
 def test_fused_distributed_optimizer_matches_nccl_path():
     out = run_distributed(_dpopt_worker, 2, backend="nccl", timeout=600)

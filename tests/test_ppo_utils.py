@@ -171,3 +171,37 @@ def test_masked_whiten():
     w = P.masked_whiten(x, m)
     assert w[:3].mean().abs() < 1e-6
     assert torch.allclose(w[:3].std(), torch.tensor(1.0), atol=1e-3)
+
+
+def test_reinforce_pp_normalisation_uses_population_moments_and_reports_stats():
+    """REINFORCE++ advantages: (x - mean) * rsqrt(max(var_pop, 1e-8)) inside the mask, 0 outside; zero variance
+    maps to zeros and is flagged (relax/utils/distributed_utils.py:161-213)."""
+    from relax_b200.algo import loss as L
+    from relax_b200.algo import ppo_utils as P
+    from relax_b200.algo.ppo_utils import Segments
+
+    x = torch.tensor([1.0, 2.0, 4.0, 100.0, 7.0])
+    mask = torch.tensor([1.0, 1.0, 1.0, 0.0, 1.0])
+    out, st = P.masked_normalize(x, mask, return_stats=True)
+    v = x[mask != 0]
+    mean, var = v.mean(), v.var(unbiased=False)
+    exp = torch.where(mask != 0, (x - mean) / var.sqrt(), torch.zeros_like(x))
+    assert torch.allclose(out, exp, atol=1e-6) and out[3] == 0
+    assert abs(float(st["reinforce_pp_advantage_raw_mean"]) - float(mean)) < 1e-6
+    assert abs(float(st["reinforce_pp_advantage_raw_std"]) - float(var.sqrt())) < 1e-6
+    assert float(st["reinforce_pp_valid_token_count"]) == 4 and float(st["reinforce_pp_zero_variance"]) == 0
+    assert abs(float(st["reinforce_pp_advantage_normalized_std"]) - 1.0) < 1e-6
+    # differs from the Bessel-corrected whitening used for the other estimators
+    assert not torch.allclose(out, P.masked_whiten(x, mask) * (mask != 0), atol=1e-3)
+    # zero variance: zeros, flagged, no NaN
+    out0, st0 = P.masked_normalize(torch.full((4,), 3.0), torch.ones(4), return_stats=True)
+    assert torch.equal(out0, torch.zeros(4)) and float(st0["reinforce_pp_zero_variance"]) == 1
+    assert float(st0["reinforce_pp_advantage_normalized_std"]) == 0
+    # dispatch inside compute_advantages_and_returns
+    seg = Segments.from_lengths([3, 2])
+    stats = {}
+    adv, _ = L.compute_advantages_and_returns("reinforce_plus_plus_baseline", torch.tensor([1.0, -1.0]), seg, torch.ones(5),
+                                             normalize_advantages=True, stats_out=stats)
+    raw = torch.tensor([1.0, 1.0, 1.0, -1.0, -1.0])
+    assert torch.allclose(adv, (raw - raw.mean()) / raw.var(unbiased=False).sqrt(), atol=1e-6)
+    assert "reinforce_pp_advantage_raw_std" in stats
