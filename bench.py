@@ -16,17 +16,28 @@ weight sync after every step.
 clock around the same public-API calls, which include, per step, the host->device
 copy of that step's prompts from pinned memory and the device->host read of the
 step's loss.
+
+Wall-time budget: the whole run (start-up + warm-up + timed steps + teardown) is
+planned to end inside `--time-budget-s` seconds (default 780, or the environment
+variable RELAX_B200_BENCH_BUDGET_S).  After the first warm-up step its duration is
+known; if W warm-up and K timed steps cannot fit, fewer are run - never less work
+per step - and the line reports the counts really run next to `steps_requested`
+and `warmup_requested`.  On SIGTERM rank 0 prints the line for the steps completed
+so far (`"partial": true`) before leaving.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import signal
 import subprocess
 import sys
 import threading
 import time
 import faulthandler
+
+T_PROCESS_START = time.perf_counter()
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -49,6 +60,9 @@ def parse():
     ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel size of trainer and engines (default 2 when N >= 2)")
     ap.add_argument("--no-fused-tp", action="store_true",
                     help="A/B: use the NCCL statements instead of the fused GEMM+collective kernels (TP>1 only)")
+    ap.add_argument("--time-budget-s", type=float, default=float(os.environ.get("RELAX_B200_BENCH_BUDGET_S", "780")),
+                    help="wall-clock budget of the whole process; warm-up / timed step counts shrink to fit (0: no budget)")
+    ap.add_argument("--decode-window", type=int, default=None, help="decode steps per host round trip in the rollout engine")
     return ap.parse_args()
 
 
@@ -160,66 +174,64 @@ def main():
         kv_blocks=kv_blocks, kv_block_size=16, max_running=512, seed=0, rollout_seed=42,
         offload_rollout=True, release_rollout_weights=True, pinned_prompts=True,
         fused_tp=not args.no_fused_tp)
+    if args.decode_window is not None:
+        os.environ["RELAX_B200_DECODE_WINDOW"] = str(args.decode_window)
     run = ColocatedGRPO(cfg, device=dev)
+    torch.cuda.synchronize()
+    startup_s = time.perf_counter() - T_PROCESS_START
+    budget = args.time_budget_s if args.time_budget_s > 0 else float("inf")
+    TEARDOWN_RESERVE_S = 25.0
 
-    def one_step():
-        m = run.step()
-        return m
+    def agree_max(x: float) -> float:
+        """Every rank takes the same scheduling decision: the slowest rank's clock counts."""
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
 
-    for _ in range(args.warmup):
-        one_step()
+    def elapsed() -> float:
+        return time.perf_counter() - T_PROCESS_START
+
+    # ---- warm-up: after the first step its cost is known and the rest of the run is planned against the budget
+    warm_req, steps_req = args.warmup, args.steps
+    warm_done, step_est = 0, 0.0
+    plan_steps = steps_req
+    while warm_done < warm_req:
+        t_w = time.perf_counter()
+        run.step()
+        torch.cuda.synchronize()
+        warm_done += 1
+        step_est = agree_max(time.perf_counter() - t_w)
+        left = budget - agree_max(elapsed()) - TEARDOWN_RESERVE_S
+        fit = int(left // max(step_est, 1e-3))             # whole steps that still fit
+        if fit >= (warm_req - warm_done) + steps_req:
+            continue
+        # not everything fits: keep at least one timed step, then up to three warm-up steps in total, then timed steps
+        more_warm = max(0, min(warm_req, 3) - warm_done)
+        more_warm = max(0, min(more_warm, fit - 1))
+        plan_steps = max(1, min(steps_req, fit - more_warm))
+        warm_req = warm_done + more_warm
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     sampler = ClockSampler(local)
     sampler.start()
     C.reset_launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0 = torch.cuda.Event(enable_timing=True)
+    step_events = []
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     ev0.record()
-    resp_tokens = total_tokens = 0
-    sync_ms, losses, h2d, d2h = [], [], 0, 0
-    parts = {}
-    for _ in range(args.steps):
-        m = one_step()
-        resp_tokens += m["response_tokens_local"]
-        total_tokens += m["total_tokens_local"]
-        sync_ms.append(m["weight_sync_ms"])
-        losses.append(m["loss"])
-        lp_diff = next((float(v) for k, v in m.items() if k.endswith("train_rollout_logprob_abs_diff")), None)
-        h2d += m.get("h2d_bytes", 0)
-        d2h += m.get("d2h_bytes", 0)
-        for k, v in m.items():
-            if k.startswith("perf/"):
-                parts[k] = parts.get(k, 0.0) + v
-    ev1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    wall = time.perf_counter() - t0
-    dev_s = ev0.elapsed_time(ev1) / 1e3
-    sampler.stop_flag = True
-    launches = C.launch_count()
-    # each engine's TP ranks hold identical samples: count every sequence once
-    stat = torch.tensor([dev_s, wall, resp_tokens / tp, total_tokens / tp, float(launches)], device=dev, dtype=torch.float64)
-    if world > 1:
-        mx = stat.clone()
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-        sm = stat.clone()
-        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        dev_s, wall = float(mx[0]), float(mx[1])
-        resp_all, tot_all = float(sm[2]), float(sm[3])
-        launches = int(mx[4])
-    else:
-        resp_all, tot_all = resp_tokens, total_tokens
-    C.check_error_flag()
-    if rank == 0:
-        value = resp_all / dev_s
+    acc = {"resp": 0, "tot": 0, "sync_ms": [], "losses": [], "h2d": 0, "d2h": 0, "parts": {}, "lp_diff": None, "steps": 0,
+           "wall": 0.0}
+
+    def build_line(dev_s, wall, resp_all, tot_all, launches, n_steps, partial=False):
+        value = resp_all / max(dev_s, 1e-9)
         out = {
             "metric": "grpo_e2e_response_tokens_per_sec_per_box",
-            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": round(dev_s * 1e3 / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": n_steps, "warmup": warm_done,
+            "ms_per_step": round(dev_s * 1e3 / max(1, n_steps), 2), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic prompts (random token ids), random-init weights, parity reward",
             "config": {
                 "model": mcfg.name + ("" if args.layers is None else f"-{args.layers}L-debug"),
@@ -229,22 +241,94 @@ def main():
                 "loss": "grpo clip 0.2 + k1 kl 0.001 to frozen reference", "weight_sync_every_step": True,
                 "cache": "working set per step (weights + activations + KV) far exceeds the 126 MB L2; no flush needed",
             },
-            "total_tokens_per_sec": round(tot_all / dev_s, 2),
-            "weight_sync_ms": round(sum(sync_ms) / len(sync_ms), 3),
-            "phase_seconds_per_step": {k[5:]: round(v / args.steps, 3) for k, v in sorted(parts.items())},
-            "loss": losses[-1], "train_rollout_logprob_abs_diff": lp_diff,
-            "e2e": {"value": round(resp_all / wall, 2), "unit": "tokens/s", "h2d_bytes_per_step": h2d // max(1, args.steps),
-                    "d2h_bytes_per_step": d2h // max(1, args.steps)},
+            "steps_requested": steps_req, "warmup_requested": args.warmup, "time_budget_s": None if budget == float("inf") else budget,
+            "startup_s": round(startup_s, 1),
+            "total_tokens_per_sec": round(tot_all / max(dev_s, 1e-9), 2),
+            "weight_sync_ms": round(sum(acc["sync_ms"]) / max(1, len(acc["sync_ms"])), 3),
+            "phase_seconds_per_step": {k[5:]: round(v / max(1, n_steps), 3) for k, v in sorted(acc["parts"].items())},
+            "loss": acc["losses"][-1] if acc["losses"] else None, "train_rollout_logprob_abs_diff": acc["lp_diff"],
+            "e2e": {"value": round(resp_all / max(wall, 1e-9), 2), "unit": "tokens/s", "h2d_bytes_per_step": acc["h2d"] // max(1, n_steps),
+                    "d2h_bytes_per_step": acc["d2h"] // max(1, n_steps)},
             "gpu_launches": launches,
             "clocks": sampler.summary(),
         }
-        print(json.dumps(out))
+        if partial:
+            out["partial"] = True
+            out["note"] = "terminated by a signal: this rank's clock over the steps completed so far, not the max over ranks"
+        return out
+
+    printed = {"done": False}
+
+    def on_term(signum, frame):
+        # leave a line for what was measured; only completed steps count (their end events have been recorded)
+        if rank == 0 and not printed["done"] and acc["steps"] > 0:
+            printed["done"] = True
+            try:
+                ev = step_events[acc["steps"] - 1]
+                dev_s = ev0.elapsed_time(ev) / 1e3 if ev.query() else acc["wall"]
+            except Exception:  # noqa: BLE001
+                dev_s = acc["wall"]
+            print(json.dumps(build_line(dev_s, acc["wall"], acc["resp"] * world / tp / 1.0 if world > 1 else acc["resp"],
+                                        acc["tot"] * world / tp if world > 1 else acc["tot"], C.launch_count(), acc["steps"], True)))
+            sys.stdout.flush()
+        os._exit(143)
+
+    signal.signal(signal.SIGTERM, on_term)
+    for i in range(plan_steps):
+        if i > 0 and budget != float("inf"):
+            # stop when one more step would pass the budget (the estimate follows the steps already timed)
+            if agree_max(elapsed() + step_est) > budget - TEARDOWN_RESERVE_S:
+                break
+        t_s = time.perf_counter()
+        m = run.step()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        step_events.append(ev)
+        acc["resp"] += m["response_tokens_local"]
+        acc["tot"] += m["total_tokens_local"]
+        acc["sync_ms"].append(m["weight_sync_ms"])
+        acc["losses"].append(m["loss"])
+        acc["lp_diff"] = next((float(v) for k, v in m.items() if k.endswith("train_rollout_logprob_abs_diff")), None)
+        acc["h2d"] += m.get("h2d_bytes", 0)
+        acc["d2h"] += m.get("d2h_bytes", 0)
+        for k, v in m.items():
+            if k.startswith("perf/"):
+                acc["parts"][k] = acc["parts"].get(k, 0.0) + v
+        acc["steps"] += 1
+        acc["wall"] = time.perf_counter() - t0
+        step_est = max(step_est * 0.5, time.perf_counter() - t_s)
+    n_steps = acc["steps"]
+    ev1 = step_events[-1]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    dev_s = ev0.elapsed_time(ev1) / 1e3
+    sampler.stop_flag = True
+    launches = C.launch_count()
+    # each engine's TP ranks hold identical samples: count every sequence once
+    stat = torch.tensor([dev_s, wall, acc["resp"] / tp, acc["tot"] / tp, float(launches)], device=dev, dtype=torch.float64)
+    if world > 1:
+        mx = stat.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stat.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        dev_s, wall = float(mx[0]), float(mx[1])
+        resp_all, tot_all = float(sm[2]), float(sm[3])
+        launches = int(mx[4])
+    else:
+        resp_all, tot_all = acc["resp"], acc["tot"]
+    C.check_error_flag()
+    signal.signal(signal.SIGTERM, signal.SIG_DFL)
+    if rank == 0 and not printed["done"]:
+        printed["done"] = True
+        print(json.dumps(build_line(dev_s, wall, resp_all, tot_all, launches, n_steps)))
     sys.stdout.flush()
+    run.close()
     if world > 1:
         from relax_b200.parallel.state import shutdown_distributed
 
-        run.close()
-        shutdown_distributed(timeout_s=20.0, hard_exit_code=0)
+        shutdown_distributed(timeout_s=120.0)
     return 0
 
 

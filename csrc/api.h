@@ -13,6 +13,9 @@ int rb_gemm(const void* A, const void* B, void* C, const void* bias, int M, int 
             int a_mn_major, int b_mn_major, int out_fp32, int accumulate, int is_fp16, int force_bn, int lbo_a,
             int sbo_a, int lbo_b, int sbo_b, int* err_flag, cudaStream_t stream);
 
+int rb_gemm_pair(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int a_mn_major,
+                 int b_mn_major, int out_fp32, int accumulate, int force_bn, int* err_flag, cudaStream_t stream);
+
 int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* r_out, int rows, int cols, float eps,
                    int dtype, cudaStream_t st);
 int rb_rmsnorm_bwd_parts(int rows, int cols);
@@ -68,6 +71,13 @@ int rb_sample(const float* logits, int B, int V, int ld, const float* temperatur
               const float* top_p, const float* uniform, long long* tok, float* logp, cudaStream_t st);
 int rb_topk_router(const float* logits, int T, int E, int K, int norm, float* w, long long* idx, float* probs,
                    cudaStream_t st);
+int rb_sample_v2(const void* logits, int is_bf16, int B, int V, long long ld, const float* temperature,
+                 const long long* top_k, const float* top_p, const float* uniform, long long* tok, float* logp,
+                 cudaStream_t st);
+int rb_decode_advance(const long long* tok_new, const float* lp_new, long long* tok_in, long long* pos, int* ctx,
+                      long long* slot, const int* block_table, int max_blocks, int block_size, int* active, int* remain,
+                      const long long* eos, const long long* stop_ids, int n_stop, long long* out_tok, float* out_lp,
+                      int* counter, int window, const float* u_all, float* u_next, int B, cudaStream_t st);
 int rb_gemm_splitk_plan(int M, int N, int K, int* bn_out);
 int rb_gemm_splitk(const void* A, const void* B, void* C, const void* bias, const void* residual, float* workspace, int M,
                    int N, int K, int lda, int ldb, int ldc, int splits, int bn, int is_fp16, int* err_flag,

@@ -74,6 +74,20 @@ void gemm(torch::Tensor A, torch::Tensor B, torch::Tensor C, c10::optional<torch
         "rb_gemm");
 }
 
+// CTA-pair kernel; returns false when the problem does not qualify (the caller then uses `gemm`).
+bool gemm_pair(torch::Tensor A, torch::Tensor B, torch::Tensor C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+               int64_t ldc, bool a_mn, bool b_mn, bool accumulate, int64_t force_bn, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_pair inputs must be bf16");
+  const bool out_fp32 = C.scalar_type() == at::kFloat;
+  TORCH_CHECK(out_fp32 || C.scalar_type() == at::kBFloat16, "output must be fp32 or bf16");
+  const int rc = rb_gemm_pair(A.data_ptr(), B.data_ptr(), C.data_ptr(), (int)M, (int)N, (int)K, (int)lda, (int)ldb, (int)ldc,
+                              a_mn, b_mn, out_fp32, accumulate, (int)force_bn, err.data_ptr<int>(), cur_stream());
+  if (rc == -20) return false;
+  check(rc, "rb_gemm_pair");
+  return true;
+}
+
 void rmsnorm_fwd(torch::Tensor x, c10::optional<torch::Tensor> res, torch::Tensor w, torch::Tensor y,
                  c10::optional<torch::Tensor> r_out, int64_t rows, int64_t cols, double eps) {
   const c10::cuda::CUDAGuard guard(x.device());
@@ -160,6 +174,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", []() { return (int64_t)rb_launch_count(); });
   m.def("reset_launch_count", []() { rb_reset_launch_count(); });
   m.def("gemm", &gemm);
+  m.def("gemm_pair", &gemm_pair);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd_parts", &rmsnorm_bwd_parts);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

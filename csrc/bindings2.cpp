@@ -77,6 +77,37 @@ void sample(torch::Tensor logits, torch::Tensor temperature, torch::Tensor top_k
                   uniform.data_ptr<float>(), (long long*)tok.data_ptr<int64_t>(), logp.data_ptr<float>(), cur_stream()),
         "rb_sample");
 }
+void sample_v2(torch::Tensor logits, torch::Tensor temperature, torch::Tensor top_k, torch::Tensor top_p,
+               torch::Tensor uniform, torch::Tensor tok, torch::Tensor logp, int64_t V) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "sample: logits rows must be contiguous");
+  const bool bf = logits.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(bf || logits.scalar_type() == at::kFloat, "sample: bf16 or fp32 logits");
+  check(rb_sample_v2(logits.data_ptr(), bf ? 1 : 0, (int)logits.size(0), (int)V, (long long)logits.stride(0),
+                     temperature.data_ptr<float>(), (const long long*)top_k.data_ptr<int64_t>(), top_p.data_ptr<float>(),
+                     uniform.data_ptr<float>(), (long long*)tok.data_ptr<int64_t>(), logp.data_ptr<float>(), cur_stream()),
+        "rb_sample_v2");
+}
+void decode_advance(torch::Tensor tok_new, torch::Tensor lp_new, torch::Tensor tok_in, torch::Tensor pos, torch::Tensor ctx,
+                    torch::Tensor slot, torch::Tensor block_table, int64_t block_size, torch::Tensor active,
+                    torch::Tensor remain, torch::Tensor eos, torch::Tensor stop_ids, torch::Tensor out_tok,
+                    torch::Tensor out_lp, torch::Tensor counter, torch::Tensor u_all, torch::Tensor u_next) {
+  const c10::cuda::CUDAGuard guard(tok_new.device());
+  const int B = (int)tok_in.size(0);
+  TORCH_CHECK(block_table.dim() == 2 && block_table.size(0) == B && block_table.is_contiguous(), "block table [B, max_blocks]");
+  TORCH_CHECK(out_tok.dim() == 2 && out_tok.size(1) == B && out_tok.is_contiguous() && out_lp.is_contiguous(), "window ring [W, B]");
+  TORCH_CHECK(u_all.dim() == 2 && u_all.size(0) == out_tok.size(0) && u_all.size(1) == B && u_all.is_contiguous(), "u_all [W, B]");
+  TORCH_CHECK(stop_ids.dim() == 2 && stop_ids.size(0) == B && stop_ids.is_contiguous(), "stop ids [B, n]");
+  check(rb_decode_advance((const long long*)tok_new.data_ptr<int64_t>(), lp_new.data_ptr<float>(),
+                          (long long*)tok_in.data_ptr<int64_t>(), (long long*)pos.data_ptr<int64_t>(), ctx.data_ptr<int>(),
+                          (long long*)slot.data_ptr<int64_t>(), block_table.data_ptr<int>(), (int)block_table.size(1),
+                          (int)block_size, active.data_ptr<int>(), remain.data_ptr<int>(),
+                          (const long long*)eos.data_ptr<int64_t>(), (const long long*)stop_ids.data_ptr<int64_t>(),
+                          (int)stop_ids.size(1), (long long*)out_tok.data_ptr<int64_t>(), out_lp.data_ptr<float>(),
+                          counter.data_ptr<int>(), (int)out_tok.size(0), u_all.data_ptr<float>(), u_next.data_ptr<float>(), B,
+                          cur_stream()),
+        "rb_decode_advance");
+}
 void topk_router(torch::Tensor logits, int64_t K, bool norm, torch::Tensor w, torch::Tensor idx, torch::Tensor probs) {
   const c10::cuda::CUDAGuard guard(logits.device());
   check(rb_topk_router(logits.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)K, norm,
@@ -135,6 +166,8 @@ void register_more(pybind11::module_& m) {
   m.def("decode_attn_splits", &decode_attn_splits);
   m.def("decode_attn", &decode_attn);
   m.def("sample", &sample);
+  m.def("sample_v2", &sample_v2);
+  m.def("decode_advance", &decode_advance);
   m.def("topk_router", &topk_router);
   m.def("gemm_splitk_plan", &gemm_splitk_plan);
   m.def("gemm_splitk", &gemm_splitk);

@@ -23,11 +23,14 @@ constexpr int DT_TILE = 128;   // tokens per tile
 constexpr int DT_PAGE = 16;    // tokens per KV page (block_size)
 constexpr int DT_NPAD = 16;    // query heads padded to the MMA N
 constexpr int DT_THREADS = 192;
-constexpr int DT_KV_BYTES = DT_TILE * DT_D * 2;              // 32 KB
-constexpr int DT_STAGES = 3;
-constexpr int DT_SMEM_K = 0;                                 // DT_STAGES stages
-constexpr int DT_SMEM_V = DT_SMEM_K + DT_STAGES * DT_KV_BYTES;
-constexpr int DT_SMEM_Q = DT_SMEM_V + DT_STAGES * DT_KV_BYTES;  // [2 halves][16 rows][128 B]
+constexpr int DT_KV_BYTES = DT_TILE * DT_D * 2;              // 32 KB: one K tile or one V tile
+// K and V tiles share ONE ring of 32 KB buffers (tile j: K in buffer 2j, V in buffer 2j + 1, modulo the ring).  A K
+// buffer is free again as soon as the S product has read it, so three buffers keep the loads of a CTA streaming,
+// and the CTA is small enough (about 109 KB) for TWO to share an SM: while one CTA is in its prologue or epilogue
+// (barrier set-up, TMEM allocation, first-load latency, output stores) the other keeps the memory pipe busy.
+constexpr int DT_NBUF = 3;
+constexpr int DT_SMEM_KV = 0;
+constexpr int DT_SMEM_Q = DT_SMEM_KV + DT_NBUF * DT_KV_BYTES;   // [2 halves][16 rows][128 B]
 constexpr int DT_SMEM_P = DT_SMEM_Q + 4096;                  // 2 buffers x [2 halves][16 rows][128 B]
 constexpr int DT_SMEM_BAR = DT_SMEM_P + 2 * 4096;
 constexpr int DT_SMEM_RED = DT_SMEM_BAR + 256;               // float [4 warps][16] max + [4][16] sums
@@ -48,7 +51,7 @@ struct DecodeTcParams {
   int* err;
 };
 
-__global__ void __launch_bounds__(DT_THREADS, 1)
+__global__ void __launch_bounds__(DT_THREADS, 2)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                       const DecodeTcParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -58,10 +61,9 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
   uint64_t* bar_s = bars + 0;                    // [2]
   uint64_t* bar_p = bars + 2;                    // [2]
   uint64_t* bar_o = bars + 4;                    // [2]
-  uint64_t* kfull = bars + 6;                    // [DT_STAGES]
-  uint64_t* vfull = kfull + DT_STAGES;           // [DT_STAGES]
-  uint64_t* kvempty = vfull + DT_STAGES;         // [DT_STAGES]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kvempty + DT_STAGES);
+  uint64_t* full = bars + 6;                     // [DT_NBUF]: tile data landed
+  uint64_t* empty = full + DT_NBUF;              // [DT_NBUF]: the MMAs that read the buffer have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(empty + DT_NBUF);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* red_max = reinterpret_cast<float*>(smem + DT_SMEM_RED);   // [4][16]
   float* red_sum = red_max + 64;                                     // [4][16]
@@ -81,10 +83,9 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
       mbar_init(&bar_p[i], 128);
       mbar_init(&bar_o[i], 1);
     }
-    for (int s = 0; s < DT_STAGES; ++s) {
-      mbar_init(&kfull[s], 1);
-      mbar_init(&vfull[s], 1);
-      mbar_init(&kvempty[s], 1);
+    for (int s = 0; s < DT_NBUF; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
     }
     *abort_flag = 0;
     if ((smem_u32(smem) & 1023u) != 0) {
@@ -117,25 +118,19 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
   if (warp == 4) {
     // ================================================================ TMA producer (page gather)
     if (lane == 0 && !dead) {
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j % DT_STAGES;
-        if (!mbar_wait(&kvempty[s], (static_cast<uint32_t>(j / DT_STAGES) & 1) ^ 1, abort_flag, p.err)) break;
-        uint8_t* sk = smem + DT_SMEM_K + s * DT_KV_BYTES;
-        uint8_t* sv = smem + DT_SMEM_V + s * DT_KV_BYTES;
-        const int page0 = (t_begin + j * DT_TILE) / DT_PAGE;
-        mbar_expect_tx(&kfull[s], DT_KV_BYTES);
+      bool ok = true;
+      for (int u = 0; u < 2 * n_tiles && ok; ++u) {      // u even: K of tile u/2, u odd: V of tile u/2
+        const int s = u % DT_NBUF;
+        if (!mbar_wait(&empty[s], (static_cast<uint32_t>(u / DT_NBUF) & 1) ^ 1, abort_flag, p.err)) { ok = false; break; }
+        uint8_t* dst = smem + DT_SMEM_KV + s * DT_KV_BYTES;
+        const CUtensorMap* map = (u & 1) ? &tma_v : &tma_k;
+        const int page0 = (t_begin + (u >> 1) * DT_TILE) / DT_PAGE;
+        mbar_expect_tx(&full[s], DT_KV_BYTES);
         for (int pg = 0; pg < DT_TILE / DT_PAGE; ++pg) {
           const int idx = min(page0 + pg, p.max_blocks - 1);
           const int row = bt[idx] * DT_PAGE;
-          tma_load_3d(sk + pg * 2048, &tma_k, &kfull[s], 0, kvh, row);
-          tma_load_3d(sk + DT_KV_BYTES / 2 + pg * 2048, &tma_k, &kfull[s], 64, kvh, row);
-        }
-        mbar_expect_tx(&vfull[s], DT_KV_BYTES);
-        for (int pg = 0; pg < DT_TILE / DT_PAGE; ++pg) {
-          const int idx = min(page0 + pg, p.max_blocks - 1);
-          const int row = bt[idx] * DT_PAGE;
-          tma_load_3d(sv + pg * 2048, &tma_v, &vfull[s], 0, kvh, row);
-          tma_load_3d(sv + DT_KV_BYTES / 2 + pg * 2048, &tma_v, &vfull[s], 64, kvh, row);
+          tma_load_3d(dst + pg * 2048, map, &full[s], 0, kvh, row);
+          tma_load_3d(dst + DT_KV_BYTES / 2 + pg * 2048, map, &full[s], 64, kvh, row);
         }
       }
     }
@@ -146,28 +141,29 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
       const uint32_t id_o = make_idesc_f16(128, DT_NPAD, true, true, false);    // V^T (MN-major) x P (K-major)
       const uint32_t sq = smem_u32(smem + DT_SMEM_Q), sp = smem_u32(smem + DT_SMEM_P);
       auto issue_s = [&](int j) -> bool {
-        const int s = j % DT_STAGES;
-        if (!mbar_wait(&kfull[s], static_cast<uint32_t>(j / DT_STAGES) & 1, abort_flag, p.err)) return false;
+        const int u = 2 * j, s = u % DT_NBUF;
+        if (!mbar_wait(&full[s], static_cast<uint32_t>(u / DT_NBUF) & 1, abort_flag, p.err)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + DT_SMEM_K + s * DT_KV_BYTES);
+        const uint32_t sk = smem_u32(smem + DT_SMEM_KV + s * DT_KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < DT_D / 16; ++kk) {
           const uint64_t da = make_smem_desc(sk + (kk >> 2) * (DT_KV_BYTES / 2) + (kk & 3) * 32, 16, 1024, kSwizzle128B);
           const uint64_t db = make_smem_desc(sq + (kk >> 2) * 2048 + (kk & 3) * 32, 16, 1024, kSwizzle128B);
           umma_f16(tmem_base + DT_T_S + (j & 1) * 16, da, db, id_s, kk > 0 ? 1u : 0u);
         }
+        umma_commit(&empty[s]);       // the K buffer can be refilled once these MMAs have read it
         umma_commit(&bar_s[j & 1]);
         return true;
       };
       bool ok = issue_s(0);
       if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % DT_STAGES;
+        const int u = 2 * j + 1, s = u % DT_NBUF;
         if (!mbar_wait(&bar_p[j & 1], static_cast<uint32_t>(j >> 1) & 1, abort_flag, p.err)) break;
         tc_fence_after();
-        if (!mbar_wait(&vfull[s], static_cast<uint32_t>(j / DT_STAGES) & 1, abort_flag, p.err)) break;
+        if (!mbar_wait(&full[s], static_cast<uint32_t>(u / DT_NBUF) & 1, abort_flag, p.err)) break;
         tc_fence_after();
-        const uint32_t sv = smem_u32(smem + DT_SMEM_V + s * DT_KV_BYTES);
+        const uint32_t sv = smem_u32(smem + DT_SMEM_KV + s * DT_KV_BYTES);
 #pragma unroll
         for (int kk = 0; kk < DT_TILE / 16; ++kk) {
           // A = V^T: M = d (two 64-wide chunks DT_KV_BYTES/2 apart), K = tokens (16 rows = 2048 bytes)
@@ -176,7 +172,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_co
           const uint64_t db = make_smem_desc(sp + (j & 1) * 4096 + (kk >> 2) * 2048 + (kk & 3) * 32, 16, 1024, kSwizzle128B);
           umma_f16(tmem_base + DT_T_O, da, db, id_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&kvempty[s]);
+        umma_commit(&empty[s]);
         umma_commit(&bar_o[j & 1]);
         // the S buffer of tile j was consumed before bar_p[j & 1] completed: refill it with tile j + 2
         if (j + 2 < n_tiles && !issue_s(j + 2)) break;

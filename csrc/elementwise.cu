@@ -539,7 +539,9 @@ extern "C" int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
   const int rpb = small ? 8 : 1;
   const int grid = grid_for((rows + rpb - 1) / rpb, 1);
   const int vec = 16 / esz;
-  if (!small && cols % (32 * vec) == 0 && cols / (32 * vec) <= 16 && esz == 2) {
+  // the warp-per-row kernel needs thousands of rows to fill the machine (8 rows per CTA); decode batches of a few
+  // hundred rows take the CTA-per-row kernel, which spreads them over as many SMs as there are rows
+  if (!small && rows >= 2048 && cols % (32 * vec) == 0 && cols / (32 * vec) <= 16 && esz == 2) {
     const int wgrid = grid_for((rows + 7) / 8, 1);
     RB_DISPATCH(dtype, {
       const T *xx = (const T*)x, *rr = (const T*)res, *ww = (const T*)w;

@@ -86,6 +86,22 @@ inline int encode_tma_2d_8bit(CUtensorMap* map, const void* ptr, uint64_t inner,
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
+// 2-D row-major tensor of 32-bit elements (fp32 outputs written or reduce-added by TMA): pitch `ld` elements.
+inline int encode_tma_2d_32bit(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                               uint32_t box_inner, uint32_t box_outer) {
+  ensure_context();
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
 // 3-D variant (e.g. [tokens][heads][head_dim] with a head stride).
 inline int encode_tma_3d_16bit(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2,
                                uint64_t stride1_elems, uint64_t stride2_elems, uint32_t b0, uint32_t b1, uint32_t b2,

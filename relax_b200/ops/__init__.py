@@ -72,6 +72,13 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return ref.sample(logits, temperature, top_k, top_p, uniform)
 
 
+def decode_advance(tok_new, lp_new, state, block_size):
+    """In-place advance of the rollout engine's device-resident batch state after one decode step."""
+    if _use_cuda(tok_new):
+        return _cuda().decode_advance(tok_new, lp_new, state, block_size)
+    return ref.decode_advance(tok_new, lp_new, state, block_size)
+
+
 def topk_router(logits, top_k, norm_topk_prob=True):
     if _use_cuda(logits):
         return _cuda().topk_router(logits, top_k, norm_topk_prob)

@@ -152,7 +152,7 @@ def bench_decode(args, pk):
         t, tl = _timeit(ours, args.iters, args.warmup), _timeit(lib, args.iters, args.warmup)
         print(f"  skinny GEMM {name:8s} {t * 1e3:7.1f} us {pk.bytes(N * K * 2 / t / 1e6)} | cuBLAS {tl * 1e3:7.1f} us")
     V = 151936
-    logits = torch.randn(B, V, device=dev)
+    logits = torch.randn(B, V, device=dev).bfloat16()     # what the rollout LM head writes
     from .. import ops
 
     temp = torch.ones(B, device=dev)
@@ -160,7 +160,7 @@ def bench_decode(args, pk):
     tp = torch.ones(B, device=dev)
     u = torch.rand(B, device=dev)
     t = _timeit(lambda: ops.sample(logits, temp, tk, tp, u), args.iters, args.warmup)
-    print(f"  sampling (temperature/top-k/top-p, V={V}) {t * 1e3:7.1f} us {pk.bytes(B * V * 4 / t / 1e6)}")
+    print(f"  sampling (temperature/top-k/top-p, V={V}, bf16 logits) {t * 1e3:7.1f} us {pk.bytes(B * V * 2 / t / 1e6)}")
 
 
 def bench_lm_head(args, pk):
@@ -235,7 +235,64 @@ def bench_train_step(args, pk):
         print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:96]}")
 
 
-SECTIONS = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
+def bench_decode_step(args, pk):
+    """One whole decode step of the rollout engine (all layers + LM head + sampling + device-side advance) as the
+    engine runs it: a CUDA graph replayed back to back.  Reports ms per step against the bytes a step must read
+    (weights + KV cache of the batch) and the per-kernel shares of one replay."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..models.config import get_config
+    from ..rollout.engine import RolloutEngine, SamplingParams
+
+    cfg = get_config("qwen3-8b", num_layers=args.decode_layers)
+    B, ctx, bs = args.batch, args.ctx, 16
+    blocks = B * ((ctx + 64 + bs - 1) // bs + 1) + 8
+    eng = RolloutEngine(cfg, device="cuda", dtype=torch.bfloat16, num_kv_blocks=blocks, block_size=bs, max_running=B,
+                        max_model_len=ctx + 64, decode_window=args.window, memory_saver=False)
+    eng.weights.flat.normal_(0, 0.02)
+    for k, v in eng.weights.p.items():
+        if "norm" in k:
+            v.fill_(1.0)
+    eng.kv.normal_(0, 1.0)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (ctx,), generator=g).tolist() for _ in range(B)]
+    sp = SamplingParams(max_new_tokens=64, ignore_eos=True)
+    for p_ in prompts:
+        eng.add_request(p_, sp)
+    while eng.waiting:          # prefill everything
+        eng.step()
+    eng.step()                  # first window: captures the graph
+    torch.cuda.synchronize()
+    st = eng._graphs[next(b for b in eng.GRAPH_BUCKETS if b >= B)]
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = args.window
+    s.record()
+    for _ in range(n):
+        st["graph"].replay()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / n
+    wbytes = sum(v.numel() * 2 for k, v in eng.weights.p.items() if k != "embed")
+    kvbytes = 2 * B * (ctx + 4) * (cfg.num_query_groups * cfg.head_dim) * 2 * cfg.num_layers
+    print(f"== decode step, batch {B}, context {ctx}, {cfg.num_layers} layers: {ms:.3f} ms per step (graph replay), "
+          f"{pk.bytes((wbytes + kvbytes) / ms / 1e6)} over weights {wbytes / 1e9:.2f} GB + KV {kvbytes / 1e9:.2f} GB")
+    import time as _t
+
+    t0 = _t.perf_counter()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    print(f"   engine.step() with a window of {args.window}: {(_t.perf_counter() - t0) / (3 * args.window) * 1e3:.3f} ms per decode step, host included")
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        st["graph"].replay()
+        torch.cuda.synchronize()
+    ev = prof.key_averages()
+    tot = sum(r.device_time_total for r in ev)
+    for r in sorted(ev, key=lambda r: -r.device_time_total)[:14]:
+        print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:110]}")
+
+
+SECTIONS = {"decode_step": bench_decode_step, "gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
             "elementwise": bench_elementwise, "train_step": bench_train_step}
 
 
@@ -248,12 +305,15 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=4, help="transformer layers of the train_step section")
+    ap.add_argument("--decode-layers", type=int, default=36, help="layers of the decode_step section")
+    ap.add_argument("--ctx", type=int, default=1536, help="context length of the decode_step section")
+    ap.add_argument("--window", type=int, default=16, help="decode steps per host round trip (decode_step section)")
     ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
     args = ap.parse_args()
     pk = _Peaks(args.peaks)
     torch.manual_seed(0)
     for name, fn in SECTIONS.items():
-        if args.only == name or (args.only is None and name != "train_step"):
+        if args.only == name or (args.only is None and name not in ("train_step", "decode_step")):
             fn(args, pk)
 
 

@@ -62,10 +62,23 @@ def check_error_flag(device=None):
 # --------------------------------------------------------------------------- GEMM
 
 
+_PAIR = os.environ.get("RELAX_B200_GEMM_PAIR", "1") == "1"
+
+
 def gemm_raw(a, b, out, M, N, K, lda, ldb, ldc, a_mn=False, b_mn=False, accumulate=False, bias=None, force_bn=0,
-             lbo_a=0, sbo_a=0, lbo_b=0, sbo_b=0):
-    _load().gemm(a, b, out, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, force_bn, lbo_a, sbo_a, lbo_b, sbo_b,
-                 err_flag(a.device))
+             lbo_a=0, sbo_a=0, lbo_b=0, sbo_b=0, pair=None):
+    """One GEMM launch.  Problems with at least one full 256-row pair tile go to the CTA-pair kernel
+    (csrc/gemm2_sm100.cu: ``cta_group::2``, TMA-store / TMA-reduce epilogue); the rest, and anything with a bias,
+    a forced tile width or a non-default descriptor, to the single-CTA kernel (csrc/gemm_sm100.cu)."""
+    L = _load()
+    use_pair = _PAIR if pair is None else pair
+    if (use_pair and bias is None and force_bn == 0 and M >= 256 and N >= 128 and a.dtype == torch.bfloat16
+            and not (lbo_a or sbo_a or lbo_b or sbo_b) and (out.dtype == torch.float32 or not accumulate)):
+        if L.gemm_pair(a, b, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, 256 if N >= 256 else 128,
+                       err_flag(a.device)):
+            return out
+    L.gemm(a, b, out, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, accumulate, force_bn, lbo_a, sbo_a, lbo_b, sbo_b,
+           err_flag(a.device))
     return out
 
 
@@ -565,15 +578,24 @@ def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scal
 
 
 def sample(logits, temperature, top_k, top_p, uniform):
-    logits = logits.float()
+    """Rows of bf16 or fp32 logits (unit inner stride; any row pitch) -> ``(token int64 [B], log-prob fp32 [B])``."""
+    if logits.dtype not in (torch.bfloat16, torch.float32):
+        logits = logits.float()
     if logits.stride(1) != 1:
         logits = logits.contiguous()
     B, V = logits.shape
     tok = torch.empty(B, dtype=torch.int64, device=logits.device)
     lp = torch.empty(B, dtype=torch.float32, device=logits.device)
-    _load().sample(logits, temperature.float().contiguous(), top_k.to(torch.int64).contiguous(),
-                   top_p.float().contiguous(), uniform.float().contiguous(), tok, lp, V)
+    _load().sample_v2(logits, temperature.float().contiguous(), top_k.to(torch.int64).contiguous(),
+                      top_p.float().contiguous(), uniform.float().contiguous(), tok, lp, V)
     return tok, lp
+
+
+def decode_advance(tok_new, lp_new, st, block_size: int):
+    """Device-side tail of one decode step (see :func:`relax_b200.ops.reference.decode_advance` for the statement)."""
+    _load().decode_advance(tok_new, lp_new, st["tok"], st["pos"], st["ctx"], st["slots"], st["bt"], int(block_size),
+                           st["active"], st["remain"], st["eos"], st["stop"], st["out_tok"], st["out_lp"], st["counter"],
+                           st["u_all"], st["u"])
 
 
 class _TopKRouter(torch.autograd.Function):

@@ -162,6 +162,42 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return tok, logp_full.gather(-1, tok[:, None])[:, 0]
 
 
+def decode_advance(tok_new, lp_new, st, block_size: int):
+    """Turn the tokens sampled by one decode step into the next step's inputs, in place, without the host.
+
+    ``st`` holds the batch state, one entry per row: ``tok`` (next input token), ``pos`` (its position), ``ctx``
+    (context length including it), ``slots`` (its KV-cache row), ``bt`` (block table ``[B, max_blocks]``), ``active``
+    (0 once the row stopped), ``remain`` (tokens it may still emit), ``eos`` (-1: none), ``stop`` (``[B, n]`` extra
+    stop ids, -1 padding); the window ring ``out_tok`` / ``out_lp`` ``[W, B]`` with its write index ``counter``; the
+    uniform draws of the whole window ``u_all [W, B]`` and of the coming step ``u [B]``.  Rows that already stopped
+    append -1 and change nothing."""
+    c = int(st["counter"][0])
+    W = st["out_tok"].shape[0]
+    if c >= W:
+        return
+    act = st["active"] != 0
+    st["out_tok"][c] = torch.where(act, tok_new, torch.full_like(tok_new, -1))
+    st["out_lp"][c] = torch.where(act, lp_new, torch.zeros_like(lp_new))
+    left = st["remain"] - act.to(st["remain"].dtype)
+    stop = (st["eos"] >= 0) & (tok_new == st["eos"])
+    if st["stop"].shape[1]:
+        stop = stop | ((st["stop"] >= 0) & (st["stop"] == tok_new[:, None])).any(-1)
+    p = st["pos"] + 1
+    blk = p // block_size
+    fits = blk < st["bt"].shape[1]
+    go = act & ~stop & (left > 0) & fits
+    new_slot = st["bt"].gather(1, blk.clamp_max(st["bt"].shape[1] - 1)[:, None].long())[:, 0].long() * block_size + p % block_size
+    st["tok"].copy_(torch.where(go, tok_new, st["tok"]))
+    st["pos"].copy_(torch.where(go, p, st["pos"]))
+    st["ctx"].copy_(torch.where(go, (p + 1).to(st["ctx"].dtype), st["ctx"]))
+    st["slots"].copy_(torch.where(go, new_slot, st["slots"]))
+    st["active"].copy_((go).to(st["active"].dtype))
+    st["remain"].copy_(left)
+    if c + 1 < W:
+        st["u"].copy_(st["u_all"][c + 1])
+    st["counter"] += 1
+
+
 def topk_router(logits, top_k: int, norm_topk_prob: bool = True):
     """fp32 softmax over experts then top-k; returns ``(weights[T,k], idx[T,k], probs[T,E])``."""
     p = torch.softmax(logits.float(), -1)

@@ -230,7 +230,9 @@ class ColocatedGRPO:
         self.sync_weights()
 
     def close(self):
-        """Unmap the peers' symmetric buffers (call on every rank before leaving the process groups)."""
+        """Collective over all ranks, before the process groups are destroyed: unmap the peers' symmetric buffers
+        (tensor-parallel workspaces, the distributed optimizer's parameter / gradient buffers), meet, free this
+        rank's, and destroy the engine sub-groups this object created."""
         from ..ops import fused_comm
 
         if self.device.type == "cuda":
@@ -240,6 +242,12 @@ class ColocatedGRPO:
         for c in self.fused_comms:
             c.close()
         self.fused_comms = []
+        for a in (self.actor, self.critic):
+            opt = getattr(a, "optimizer", None) if a is not None else None
+            if opt is not None and hasattr(opt, "close"):
+                opt.close()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
 
     # ------------------------------------------------------------------ weight sync
     def sync_weights(self) -> float:
@@ -313,15 +321,6 @@ class ColocatedGRPO:
             over = max(per, (cfg.over_sampling_batch_size or cfg.rollout_batch_size) // self.num_engines)
             groups, self.sampling_stats = dynamic_sampling(lambda n: self._generate_groups(n, sp), per, over, self.group_filter)
         return [s for g in groups for s in g]
-        res = self.engine.generate([s.tokens for s in flat], sp, group_keys=[s.group_index for s in flat])
-        for s, r in zip(flat, res):
-            s.tokens = list(r.prompt) + list(r.output)
-            s.response_length = len(r.output)
-            s.rollout_log_probs = list(r.logprobs)
-            s.weight_versions = sorted(set(r.weight_versions))
-            s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
-            s.reward = self.reward_fn(s)
-        return flat
 
     @property
     def _rank(self) -> int:

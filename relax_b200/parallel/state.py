@@ -174,31 +174,51 @@ def single_process_state() -> ParallelState:
     return ParallelState(ParallelDims(), 0, (0,), g, g, g, g, g, g, g, g)
 
 
-def shutdown_distributed(timeout_s: float = 20.0, hard_exit_code: int | None = None):
-    """Leave the process groups without letting a stuck communicator teardown hold the job.
+def shutdown_distributed(timeout_s: float = 120.0):
+    """Leave the process groups in a fixed order that is the same on every rank.
 
-    All ranks synchronise first (device + barrier) so nothing is in flight; the NCCL teardown then runs on a
-    helper thread.  With many split communicators (TP x DP x engine groups) the teardown has been seen to
-    block on 4 GPUs even though every collective had completed; after ``timeout_s`` the caller either
-    returns (``hard_exit_code`` None) or the process exits with that code, results already flushed."""
+    Symmetric (CUDA IPC) buffers must have been closed by their owners before this is called: freeing an exported
+    allocation that a peer still maps, or destroying communicators while such mappings are live, is where a
+    four-rank teardown was seen to block.  All ranks synchronise their devices and meet; the sub-groups are then
+    destroyed one by one, newest first, and the default group last, on the calling thread with its device
+    current.  A watchdog thread only observes: if the teardown has not finished after ``timeout_s`` it prints
+    which group was being destroyed and ends the process with exit code 3, so a stuck teardown is reported rather
+    than hidden.  Returns True when every group was destroyed."""
     import os
     import sys
     import threading
 
     if not dist.is_initialized():
         return True
-    try:
-        if torch.cuda.is_available():
-            torch.cuda.synchronize()
-        dist.barrier()
-    except Exception:  # noqa: BLE001
-        pass
-    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
-    t.start()
-    t.join(timeout_s)
-    done = not t.is_alive()
-    if not done and hard_exit_code is not None:
-        sys.stdout.flush()
-        sys.stderr.flush()
-        os._exit(hard_exit_code)
-    return done
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    dist.barrier()
+    progress = {"at": "start"}
+    done = threading.Event()
+
+    def watchdog():
+        if not done.wait(timeout_s):
+            sys.stderr.write(f"[relax_b200] process-group teardown still running after {timeout_s:.0f} s "
+                             f"(rank {os.environ.get('RANK', '0')}, at: {progress['at']}); exiting with code 3\n")
+            sys.stderr.flush()
+            sys.stdout.flush()
+            os._exit(3)
+
+    threading.Thread(target=watchdog, daemon=True).start()
+    from torch.distributed import distributed_c10d as c10d
+
+    world = c10d._get_default_group()
+    names = dict(c10d._world.pg_names)
+    # creation order is the numeric order of the generated names; every rank created every group in the same order
+    def order(pg):
+        n = names.get(pg, "0")
+        return int(n) if str(n).isdigit() else 1 << 30
+
+    subs = sorted((pg for pg in names if pg is not world), key=order, reverse=True)
+    for pg in subs:
+        progress["at"] = f"sub-group {names.get(pg)}"
+        dist.destroy_process_group(pg)
+    progress["at"] = "default group"
+    dist.destroy_process_group()
+    done.set()
+    return True

@@ -100,7 +100,8 @@ class RolloutEngine:
     def __init__(self, cfg: ModelConfig, tp: Optional[GroupInfo] = None, device="cpu", dtype=None,
                  num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
-                 use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None):
+                 use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
+                 decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
@@ -127,10 +128,18 @@ class RolloutEngine:
         self._alloc_kv()
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         self.max_model_len = max_model_len
+        # decode steps issued back to back between two host synchronisations: the batch state (tokens, positions,
+        # context lengths, cache slots) is advanced on the device, the host reads the sampled tokens once per window
+        if decode_window is None:
+            decode_window = int(os.environ.get("RELAX_B200_DECODE_WINDOW", "16"))
+        self.decode_window = max(1, int(decode_window))
+        self.windowed_decode = self.use_cuda_graph if windowed_decode is None else bool(windowed_decode)
+        if os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") == "1" and self.device.type == "cuda":
+            self.windowed_decode = False     # the library-path arm keeps the host-driven loop
         self._graphs = {}
         self._graph_pool = None
         # padding rows of a graph bucket read/write this block; it is never handed to a request
-        self._scratch_block = self.bm.alloc() if self.use_cuda_graph else 0
+        self._scratch_block = self.bm.alloc() if (self.use_cuda_graph or self.windowed_decode) else 0
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0}
 
     # ------------------------------------------------------------------ memory
@@ -182,8 +191,10 @@ class RolloutEngine:
         if self.running:
             raise RuntimeError("flush_cache with running requests")
         self.bm = BlockManager(self.bm.num_blocks, self.block_size)
-        if self.use_cuda_graph:
+        if self.use_cuda_graph or self.windowed_decode:
             self._scratch_block = self.bm.alloc()
+        for st in self._graphs.values():     # device-resident batch state refers to blocks of the old manager
+            st["rows"] = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: SamplingParams, group_key: Optional[int] = None,
@@ -286,8 +297,9 @@ class RolloutEngine:
         return done
 
     def _stage(self, arrays):
-        """Host lists -> device tensors through ONE pinned staging buffer and ONE
-        asynchronous host-to-device copy.  ``arrays`` is a list of ``(list, dtype)``."""
+        """Host lists -> device tensors through a pinned staging buffer and ONE asynchronous host-to-device
+        copy.  ``arrays`` is a list of ``(list, dtype)``.  Pinned and device buffers come in pairs that alternate;
+        a pinned buffer is rewritten only after the copy that last read it has completed (its event)."""
         if self.device.type != "cuda":
             return [torch.tensor(a, dtype=dt) for a, dt in arrays]
         cpu = [torch.tensor(a, dtype=dt) for a, dt in arrays]
@@ -295,19 +307,27 @@ class RolloutEngine:
         for t in cpu:
             offs.append(n)
             n += (t.numel() * t.element_size() + 15) // 16 * 16
-        if getattr(self, "_pin", None) is None or self._pin.numel() < n:
+        if getattr(self, "_pin", None) is None or self._pin[0].numel() < n:
+            if getattr(self, "_pin_ev", None) is not None:
+                for ev in self._pin_ev:
+                    ev.synchronize()
             cap = max(n * 2, 1 << 16)
-            self._pin = torch.empty(cap, dtype=torch.uint8, pin_memory=True)
+            self._pin = [torch.empty(cap, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
             self._dev_stage = [torch.empty(cap, dtype=torch.uint8, device=self.device) for _ in range(2)]
+            self._pin_ev = [torch.cuda.Event() for _ in range(2)]
+            for ev in self._pin_ev:
+                ev.record()
             self._stage_flip = 0
         self._stage_flip ^= 1
-        dbuf = self._dev_stage[self._stage_flip]
+        pin, dbuf, ev = self._pin[self._stage_flip], self._dev_stage[self._stage_flip], self._pin_ev[self._stage_flip]
+        ev.synchronize()
         for t, o in zip(cpu, offs):
             nb = t.numel() * t.element_size()
             if nb:
-                self._pin[o:o + nb].copy_(t.view(-1).view(torch.uint8))
+                pin[o:o + nb].copy_(t.view(-1).view(torch.uint8))
         if n:
-            dbuf[:n].copy_(self._pin[:n], non_blocking=True)
+            dbuf[:n].copy_(pin[:n], non_blocking=True)
+            ev.record()
         self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + n
         out = []
         for t, o in zip(cpu, offs):
@@ -354,7 +374,7 @@ class RolloutEngine:
             r.t_first = now
 
     def _decode(self):
-        if self.use_cuda_graph and self._decode_graph():
+        if self.windowed_decode and self._decode_window():
             return
         reqs = self.running
         dev = self.device
@@ -379,108 +399,167 @@ class RolloutEngine:
         self.stats["decode_tokens"] += B
         self._sample_and_append(reqs, logits)
 
-    # ------------------------------------------------------------------ CUDA-graph decode
+    # ------------------------------------------------------------------ windowed decode (CUDA graph of one step)
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+    N_STOP = 4      # stop ids per row known to the device; longer lists are still honoured by the host
 
-    def _graph_state(self, bucket: int):
-        """Static input/output buffers and the captured graph of one batch-size bucket.
-        All inputs of a step live in ONE device buffer refreshed by ONE async H2D copy."""
+    def _window_state(self, bucket: int):
+        """Device-resident batch state, window ring and (on CUDA) the captured graph of one decode step for one
+        batch-size bucket.  Two regions of ONE pinned host mirror: the per-window part (step counter, uniform draws)
+        is uploaded before every window, the batch part (tokens, positions, block tables, sampling parameters, stop
+        rules) only when the set of running requests changed."""
         st = self._graphs.get(bucket)
         if st is not None:
             return st
         dev, bs = self.device, self.block_size
         maxb = (self.bm.blocks_for(self._max_model_len()) + 7) // 8 * 8
+        W = self.decode_window
         i64, i32, f32 = torch.int64, torch.int32, torch.float32
-        fields = [("tok", i64, (bucket,)), ("pos", i64, (bucket,)), ("slots", i64, (bucket,)), ("topk", i64, (bucket,)),
-                  ("ctx", i32, (bucket,)), ("bt", i32, (bucket, maxb)), ("temp", f32, (bucket,)), ("topp", f32, (bucket,)),
-                  ("u", f32, (bucket,))]
+        per_window = [("counter", i32, (4,)), ("u", f32, (bucket,)), ("u_all", f32, (W, bucket))]
+        per_batch = [("tok", i64, (bucket,)), ("pos", i64, (bucket,)), ("slots", i64, (bucket,)), ("topk", i64, (bucket,)),
+                     ("eos", i64, (bucket,)), ("stop", i64, (bucket, self.N_STOP)), ("ctx", i32, (bucket,)),
+                     ("active", i32, (bucket,)), ("remain", i32, (bucket,)), ("bt", i32, (bucket, maxb)),
+                     ("temp", f32, (bucket,)), ("topp", f32, (bucket,))]
         offs, n = {}, 0
-        for name, dt, shp in fields:
+        for name, dt, shp in per_window + per_batch:
+            if name == "tok":
+                n_window = n
             offs[name] = n
             n += (math.prod(shp) * torch.empty(0, dtype=dt).element_size() + 15) // 16 * 16
-        host = torch.zeros(n, dtype=torch.uint8, pin_memory=True)
+        cuda = dev.type == "cuda"
+        host = torch.zeros(n, dtype=torch.uint8, pin_memory=cuda)
         devb = torch.zeros(n, dtype=torch.uint8, device=dev)
 
         def views(buf):
             out = {}
-            for name, dt, shp in fields:
+            for name, dt, shp in per_window + per_batch:
                 nb = math.prod(shp) * torch.empty(0, dtype=dt).element_size()
                 out[name] = buf[offs[name]:offs[name] + nb].view(dt).view(shp)
             return out
 
-        st = {"host": host, "dev": devb, "h": views(host), "d": views(devb), "nbytes": n, "maxb": maxb}
-        # neutral padding rows: context of one token held in the scratch block
-        h = st["h"]
-        h["ctx"].fill_(1)
-        h["bt"].fill_(self._scratch_block)
-        h["slots"].fill_(self._scratch_block * bs)
-        h["temp"].fill_(1.0)
-        h["topp"].fill_(1.0)
-        h["topk"].fill_(-1)
-        h["u"].fill_(0.5)
-        devb.copy_(host)
+        st = {"host": host, "dev": devb, "h": views(host), "d": views(devb), "nbytes": n, "n_window": n_window,
+              "maxb": maxb, "rows": None, "bucket": bucket}
         d = st["d"]
+        d["out_tok"] = torch.full((W, bucket), -1, dtype=i64, device=dev)
+        d["out_lp"] = torch.zeros(W, bucket, dtype=f32, device=dev)
+        st["host_tok"] = torch.zeros(W, bucket, dtype=i64, pin_memory=cuda)
+        st["host_lp"] = torch.zeros(W, bucket, dtype=f32, pin_memory=cuda)
+        self._pad_rows(st, 0, bucket)
+        devb.copy_(host)
+        counter = d["counter"]
+        d["counter"] = counter[:1]
 
         def run():
             logits = self.weights.forward_decode(d["tok"], d["pos"], d["bt"], d["ctx"], d["slots"], self.kv, self.tp)
-            return ops.sample(logits[:, :self.cfg.vocab_size], d["temp"], d["topk"], d["topp"], d["u"])
+            tok, lp = ops.sample(logits[:, :self.cfg.vocab_size], d["temp"], d["topk"], d["topp"], d["u"])
+            ops.decode_advance(tok, lp, d, bs)
 
-        run()                                   # eager warm-up (lazy initialisation, communicator set-up)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, pool=self._graph_pool):
-            st["out_tok"], st["out_lp"] = run()
-        if self._graph_pool is None:
-            self._graph_pool = g.pool()
-        st["graph"] = g
+        st["run"] = run
+        if self.use_cuda_graph:
+            run()                                   # eager warm-up (lazy initialisation, communicator set-up)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=self._graph_pool):
+                run()
+            if self._graph_pool is None:
+                self._graph_pool = g.pool()
+            st["graph"] = g
+            devb.copy_(host)                        # the warm-up and the capture advanced the padding rows' ring index
         self._graphs[bucket] = st
         return st
+
+    def _pad_rows(self, st, lo: int, hi: int):
+        """Neutral padding rows: a stopped row with a context of one token held in the scratch block."""
+        h, bs = st["h"], self.block_size
+        h["tok"][lo:hi] = 0
+        h["pos"][lo:hi] = 0
+        h["ctx"][lo:hi] = 1
+        h["bt"][lo:hi] = self._scratch_block
+        h["slots"][lo:hi] = self._scratch_block * bs
+        h["temp"][lo:hi] = 1.0
+        h["topp"][lo:hi] = 1.0
+        h["topk"][lo:hi] = -1
+        h["eos"][lo:hi] = -1
+        h["stop"][lo:hi] = -1
+        h["active"][lo:hi] = 0
+        h["remain"][lo:hi] = 0
 
     def _max_model_len(self) -> int:
         return getattr(self, "max_model_len", 0) or 4096
 
-    def _decode_graph(self):
+    def _decode_window(self) -> bool:
+        """Up to ``decode_window`` decode steps for the running batch with one host round trip.  Returns False when
+        the batch does not fit a bucket or the model length (the caller then takes the host-driven step)."""
         reqs = self.running
         bs = self.block_size
-        for r in reqs:
-            p = r.num_tokens - 1
-            if p // bs >= len(r.blocks):
-                r.blocks.append(self.bm.alloc())
-                r._reserve = max(0, r._reserve - 1)
         B = len(reqs)
         bucket = next((b for b in self.GRAPH_BUCKETS if b >= B), None)
-        if bucket is None or max(r.num_tokens for r in reqs) > self._max_model_len():
+        if bucket is None or any(len(r.prompt) + r.params.max_new_tokens > self._max_model_len() for r in reqs):
             return False
-        st = self._graph_state(bucket)
-        h = st["h"]
-        h["tok"][:B] = torch.tensor([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], dtype=torch.int64)
-        h["pos"][:B] = torch.tensor([r.num_tokens - 1 for r in reqs], dtype=torch.int64)
-        h["ctx"][:B] = torch.tensor([r.num_tokens for r in reqs], dtype=torch.int32)
-        h["slots"][:B] = torch.tensor([r.blocks[(r.num_tokens - 1) // bs] * bs + (r.num_tokens - 1) % bs for r in reqs],
-                                      dtype=torch.int64)
-        maxb = st["maxb"]
-        h["bt"][:B] = torch.tensor([r.blocks + [self._scratch_block] * (maxb - len(r.blocks)) for r in reqs], dtype=torch.int32)
-        h["temp"][:B] = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32)
-        h["topk"][:B] = torch.tensor([r.params.top_k for r in reqs], dtype=torch.int64)
-        h["topp"][:B] = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32)
-        h["u"][:B] = torch.rand(B, generator=self.gen)
-        if B < bucket and st.get("last_B", 0) > B:   # rows that held real requests last time become padding again
-            lb = st["last_B"]
-            h["ctx"][B:lb] = 1
-            h["bt"][B:lb] = self._scratch_block
-            h["slots"][B:lb] = self._scratch_block * bs
-            h["temp"][B:lb] = 1.0
-            h["topk"][B:lb] = -1
-            h["topp"][B:lb] = 1.0
-        st["last_B"] = B
-        st["dev"].copy_(st["host"], non_blocking=True)
-        st["graph"].replay()
-        tok_l, lp_l = st["out_tok"][:B].tolist(), st["out_lp"][:B].tolist()
-        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + st["nbytes"]
-        self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + B * 12
-        self.stats["decode_tokens"] += B
-        self.stats["graph_replays"] = self.stats.get("graph_replays", 0) + 1
-        self._append_tokens(reqs, tok_l, lp_l)
+        # the device advances positions on its own: hand every request all the blocks it can ever need now (they
+        # were already counted against the free pool at admission)
+        for r in reqs:
+            need = self.bm.blocks_for(len(r.prompt) + r.params.max_new_tokens)
+            while len(r.blocks) < need:
+                r.blocks.append(self.bm.alloc())
+            r._reserve = 0
+        st = self._window_state(bucket)
+        h, d = st["h"], st["d"]
+        W = min(self.decode_window, max(r.params.max_new_tokens - len(r.output) for r in reqs))
+        rows = tuple(r.rid for r in reqs)
+        fresh = st["rows"] != rows
+        if fresh:
+            maxb = st["maxb"]
+            last = [(r.output[-1] if r.output else r.prompt[-1]) for r in reqs]
+            npos = [r.num_tokens - 1 for r in reqs]
+            h["tok"][:B] = torch.tensor(last, dtype=torch.int64)
+            h["pos"][:B] = torch.tensor(npos, dtype=torch.int64)
+            h["ctx"][:B] = torch.tensor([p + 1 for p in npos], dtype=torch.int32)
+            h["slots"][:B] = torch.tensor([r.blocks[p // bs] * bs + p % bs for r, p in zip(reqs, npos)], dtype=torch.int64)
+            h["bt"][:B] = torch.tensor([r.blocks + [self._scratch_block] * (maxb - len(r.blocks)) for r in reqs], dtype=torch.int32)
+            h["temp"][:B] = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32)
+            h["topk"][:B] = torch.tensor([r.params.top_k for r in reqs], dtype=torch.int64)
+            h["topp"][:B] = torch.tensor([r.params.top_p for r in reqs], dtype=torch.float32)
+            h["eos"][:B] = torch.tensor([(-1 if (r.params.ignore_eos or self.eos is None) else self.eos) for r in reqs], dtype=torch.int64)
+            stops = [([-1] if r.params.ignore_eos else list(r.params.stop_token_ids)[:self.N_STOP]) for r in reqs]
+            h["stop"][:B] = torch.tensor([s_ + [-1] * (self.N_STOP - len(s_)) for s_ in stops], dtype=torch.int64)
+            h["active"][:B] = 1
+            h["remain"][:B] = torch.tensor([r.params.max_new_tokens - len(r.output) for r in reqs], dtype=torch.int32)
+            if B < bucket:
+                self._pad_rows(st, B, bucket)
+            st["rows"] = rows
+        h["counter"][:] = 0
+        for i in range(W):      # one draw per step, in the order the host-driven loop makes them
+            h["u_all"][i, :B] = torch.rand(B, generator=self.gen)
+        h["u"][:] = h["u_all"][0]
+        nb = st["nbytes"] if fresh else st["n_window"]
+        st["dev"][:nb].copy_(st["host"][:nb], non_blocking=True)
+        if "graph" in st:
+            for _ in range(W):
+                st["graph"].replay()
+        else:
+            for _ in range(W):
+                st["run"]()
+        st["host_tok"][:W].copy_(d["out_tok"][:W], non_blocking=True)
+        st["host_lp"][:W].copy_(d["out_lp"][:W], non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()    # also completes the upload: the mirror may be rewritten
+        tok_w, lp_w = st["host_tok"][:W, :B].tolist(), st["host_lp"][:W, :B].tolist()
+        self.stats["h2d_bytes"] = self.stats.get("h2d_bytes", 0) + nb
+        self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + W * bucket * 12
+        self.stats["graph_replays"] = self.stats.get("graph_replays", 0) + W
+        self.stats["steps"] += W - 1
+        for i in range(W):
+            live = [(j, r) for j, r in enumerate(reqs) if r.status == "running"]
+            if not live:
+                break
+            row_t, row_l = tok_w[i], lp_w[i]
+            if any(row_t[j] < 0 for j, _ in live):
+                raise RuntimeError("decode window: the device stopped a row the host still considers running")
+            self.stats["decode_tokens"] += len(live)
+            self._append_tokens([r for _, r in live], [row_t[j] for j, _ in live], [row_l[j] for j, _ in live])
+        if any(r.status != "running" for r in reqs):
+            st["rows"] = None
         return True
 
     def _sample_and_append(self, reqs: list[Request], logits: torch.Tensor):

@@ -129,7 +129,9 @@ class RolloutWeights:
         return x
 
     def _logits(self, h, tp: GroupInfo):
-        z = ops.linear(h, self.p["lm_head"]).float()
+        z = ops.linear(h, self.p["lm_head"])
+        if not z.is_cuda:
+            z = z.float()       # the sampling kernel reads bf16 rows directly; the CPU statement wants fp32
         if tp.size > 1:
             out = torch.empty(tp.size * z.shape[0], z.shape[1], dtype=z.dtype, device=z.device)
             dist.all_gather_into_tensor(out, z.contiguous(), group=tp.group)

@@ -117,3 +117,38 @@ def test_memory_saver_keeps_views_across_pause_resume():
     assert float(eng.weights.flat.abs().sum()) == 0.0     # contents are not preserved
     eng.weights.flat.copy_(w0)
     assert len(eng.generate([[1, 2, 3]], sp)[0].output) == len(out0)
+
+
+def test_windowed_decode_equals_host_driven_loop():
+    """Several decode steps per host round trip (batch state advanced by ``decode_advance``) give the same tokens,
+    log-probs and finish reasons as one host round trip per step, for fixed-length and for EOS-terminated requests,
+    under KV pressure (requests admitted while others run) and with a group sharing its prompt blocks."""
+    outs = []
+    for windowed in (False, True):
+        cfg, actor, eng = _pair(kv_blocks=64, max_running=8, windowed_decode=windowed, decode_window=5)
+        torch.manual_seed(1)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (5, 11, 8, 3)]
+        fixed = eng.generate(prompts, SamplingParams(max_new_tokens=13, ignore_eos=True))
+        grp = eng.generate([list(range(3, 22))] * 3, SamplingParams(max_new_tokens=7, ignore_eos=True), group_keys=[0] * 3)
+        assert eng.bm.num_free == eng.bm.num_blocks - (1 if windowed else 0)     # the scratch block of padding rows
+        outs.append([(r.output, r.logprobs, r.finish_reason) for r in fixed + grp])
+        if windowed:
+            assert eng.stats["graph_replays"] >= 13 + 7 - 2
+    for (o0, l0, f0), (o1, l1, f1) in zip(*outs):
+        assert o0 == o1 and f0 == f1 == "length"
+        assert torch.allclose(torch.tensor(l0), torch.tensor(l1), atol=1e-6)
+    # EOS inside a window: the row stops on the device too, later ring entries are ignored, blocks come back
+    cfg, actor, eng = _pair(kv_blocks=24, max_running=4, windowed_decode=True, decode_window=6)
+    eng.eos = 7
+    res = eng.generate([[i + 1] * 8 for i in range(6)], SamplingParams(max_new_tokens=20, stop_token_ids=(9,)))
+    assert len(res) == 6 and all(r.status == "finished" for r in res)
+    for r in res:
+        assert r.finish_reason in ("stop", "length") and len(r.output) <= 20
+        if r.finish_reason == "stop":
+            assert r.output[-1] in (7, 9) and not any(t in (7, 9) for t in r.output[:-1])
+        else:
+            assert not any(t in (7, 9) for t in r.output)
+    assert eng.bm.num_free == eng.bm.num_blocks - 1
+    batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [len(r.output) for r in res]}
+    for r, l in zip(res, actor.compute_log_prob(batch)["log_probs"]):
+        assert torch.allclose(torch.tensor(r.logprobs), l, atol=1e-4)
