@@ -241,6 +241,117 @@ ENGINE_FLAGS = {
 }
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# Flags of the reference's recipes that this build accepts but does not (fully) implement.  A recipe must never
+# run with different math, precision or layout than it asks for without saying so:
+#   "raise": the flag changes what is computed or where; a non-default value stops the run at parse time.
+#   "warn":  the flag tunes an operational detail (a timeout, a concurrency cap, a library choice) that has no
+#            counterpart here or is always on; a non-default value is reported once and the run goes on.
+# Everything not listed is consumed by the controller, the trainer, the rollout engine or a service.
+_R, _W = "raise", "warn"
+FLAG_POLICY: dict[str, tuple] = {
+    # numerics / layout
+    "--fp8-format": (_R, "fp8 training is not wired (the block-scaled fp8 GEMM exists as an operator only)"),
+    "--fp8-recipe": (_R, "fp8 training is not wired"),
+    "--optimizer-cpu-offload": (_R, "optimizer state lives on the GPU (or is offloaded whole between phases with --offload-train)"),
+    "--expert-tensor-parallel-size": (_R, "experts are not tensor-parallel here (expert TP = 1)"),
+    "--qkv-format": (_R, "only the packed thd layout is implemented"),
+    "--padded-vocab-size": (_R, "the vocabulary is padded to a multiple of the tensor-parallel size only"),
+    "--num-iters-per-train-update": (_R, "one optimizer pass per rollout batch"),
+    "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
+    # rollout behaviour
+    "--use-rollout-routing-replay": (_R, "the rollout engine does not return routed experts (R3); use --use-routing-replay (R2)"),
+    "--sglang-enable-return-routed-experts": (_R, "the rollout engine does not return routed experts"),
+    "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
+    "--use-rollout-entropy": (_R, "the rollout engine returns log-probs only"),
+    "--rollout-external": (_R, "external rollout engines are not supported"),
+    "--rollout-external-engine-addrs": (_R, "external rollout engines are not supported"),
+    "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
+    "--buffer-filter-path": (_R, "no rollout buffer filter hook"),
+    "--mask-offpolicy-in-partial-rollout": (_R, "partial rollouts keep all their tokens in the loss"),
+    "--partial-rollout-max-aborted-count": (_R, "aborted samples are resumed until they finish"),
+    "--disable-rollout-global-dataset": (_R, "prompts always come from the global dataset"),
+    "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
+    "--use-agentic-rollout": (_R, "agentic rollouts are driven through --custom-generate-function-path (rollout/agentic.py)"),
+    # algorithm
+    "--disable-compute-advantages-and-returns": (_R, "advantages are always computed by the trainer"),
+    "--critic-train-only": (_R, "use --num-critic-only-steps for critic warm-up"),
+    "--opd-teacher-urls": (_R, "remote teachers are not wired into the loop (teacher snapshot via --opd-teacher-load)"),
+    "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
+    "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
+    "--lora-dropout": (_R, "LoRA dropout is not implemented"),
+    "--genrm-num-gpus": (_R, "no generative reward-model engines (rewards/genrm.py parses verdicts of a remote one)"),
+    "--ref-ckpt-step": (_R, "the reference is loaded from --ref-load as a whole"),
+    "--freeze-language-model": (_R, "use --freeze-params-name-list"),
+    "--freeze-vision-model": (_R, "use --freeze-params-name-list"),
+    "--freeze-vision-projection": (_R, "use --freeze-params-name-list"),
+    "--num-labels": (_R, "set the classifier width through the model preset (num_classes)"),
+    "--problem-type": (_R, "single-label classification only"),
+    "--autoscaler-config": (_R, "the autoscaler rule engine is a library (rollout/elastic.py), not a running service"),
+    # operational, no effect here
+    "--async-save": (_W, "checkpoints are written synchronously"),
+    "--attention-backend": (_W, "there is one attention implementation (tcgen05 flash attention)"),
+    "--moe-grouped-gemm": (_W, "always on"), "--moe-permute-fusion": (_W, "always on"),
+    "--moe-token-dispatcher-type": (_W, "all-to-all dispatch is the only dispatcher"),
+    "--overlap-grad-reduce": (_W, "the gradient reduce-scatter is fused into the optimizer kernel"),
+    "--overlap-param-gather": (_W, "the parameter all-gather is fused into the optimizer kernel"),
+    "--recompute-method": (_W, "--recompute-granularity full recomputes every layer"),
+    "--recompute-num-layers": (_W, "--recompute-granularity full recomputes every layer"),
+    "--log-probs-chunk-size": (_W, "the fused LM head never materialises the logits"),
+    "--agentic-concurrency": (_W, None), "--sglang-server-concurrency": (_W, None),
+    "--sglang-mem-fraction-static": (_W, "the KV cache is sized from the batch shape"),
+    "--classification-threshold": (_W, None), "--critic-num-nodes": (_W, "the critic shares the actor's ranks"),
+    "--critic-num-gpus-per-node": (_W, "the critic shares the actor's ranks"),
+    "--disable-rollout-trim-samples": (_W, None), "--disable-weights-backuper": (_W, None),
+    "--enable-affinity": (_W, "no Ray node affinity"), "--genrm-num-gpus-per-engine": (_W, None),
+    "--log-multi-turn": (_W, None), "--log-reward-category": (_W, None), "--loss-mask-type": (_W, None),
+    "--megatron-to-hf-mode": (_W, "one converter"), "--optimize-routing-replay": (_W, None),
+    "--profile-target": (_W, "the trainer is the profiled role"), "--reward-max-concurrency": (_W, None),
+    "--reward-num-workers": (_W, None), "--rollout-engine-init-timeout": (_W, None), "--rollout-http-timeout": (_W, None),
+    "--rollout-skip-special-tokens": (_W, None), "--selective-offload": (_W, None), "--sft-chunked-logits": (_W, "always on"),
+    "--sft-logits-chunk-size": (_W, None), "--sft-max-in-flight-steps": (_W, None), "--sft-prefetch-buffer-size": (_W, None),
+    "--slime-router-health-check-failure-threshold": (_W, None), "--slime-router-max-connections": (_W, None),
+    "--slime-router-middleware-paths": (_W, None), "--slime-router-sticky": (_W, None), "--slime-router-timeout": (_W, None),
+    "--use-slime-router": (_W, "the in-process router is used when several engines serve one rank"),
+    "--train-env-vars": (_W, None), "--train-memory-margin-bytes": (_W, None), "--update-weight-buffer-size": (_W, None),
+    "--scale-out-timeout": (_W, None), "--scale-in-drain-timeout": (_W, None), "--scale-in-shutdown-timeout": (_W, None),
+    "--scale-weight-sync-precheck": (_W, None), "--scale-out-partial-success-policy": (_W, None),
+}
+_WARNED: set = set()
+
+
+def apply_flag_policy(a: argparse.Namespace, parser: Optional[argparse.ArgumentParser] = None, warn=None) -> list:
+    """Stop on (or report) accepted-but-unimplemented flags that were given a non-default value.
+    Returns the warnings issued (for tests)."""
+    import warnings as _warnings
+
+    parser = parser or build_parser()
+    by_flag = {}
+    for act in parser._actions:
+        for opt in act.option_strings:
+            by_flag[opt] = act
+    out = []
+    for flag, (kind, why) in FLAG_POLICY.items():
+        act = by_flag.get(flag)
+        if act is None:
+            continue
+        val = getattr(a, act.dest, act.default)
+        if val == act.default or (val in (None, [], {}, 0, False) and act.default in (None, [], {}, 0, False)):
+            continue
+        if flag in ("--expert-tensor-parallel-size",) and val in (None, 1):
+            continue
+        if flag == "--sglang-dp-size" and val in (None, 1):
+            continue
+        msg = f"{flag}={val!r} is accepted for recipe compatibility but not implemented here" + (f": {why}" if why else "")
+        if kind == _R:
+            raise ValueError(msg)
+        if flag not in _WARNED:
+            _WARNED.add(flag)
+            (warn or _warnings.warn)(msg)
+        out.append(msg)
+    return out
+
+
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser("relax_b200", allow_abbrev=False)
     for group, flags in FLAGS.items():
@@ -349,6 +460,9 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
         a.train_iters = a.num_rollout * a.rollout_batch_size * a.n_samples_per_prompt // a.global_batch_size
         if a.lr_decay_iters is None:
             a.lr_decay_iters = a.train_iters
+    if getattr(a, "dump_details", None):       # one switch for both debug dumps (relax/utils/arguments.py:3542-3544)
+        a.save_debug_rollout_data = a.save_debug_rollout_data or f"{a.dump_details}/rollout_data"
+        a.save_debug_train_data = a.save_debug_train_data or f"{a.dump_details}/train_data"
     if a.partial_rollout and not a.over_sampling_batch_size:
         a.over_sampling_batch_size = a.rollout_batch_size
     if a.rm_type is None and a.custom_rm_path is None and not a.debug_train_only:
@@ -357,7 +471,10 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
 
 
 def parse_args(argv: Optional[Sequence[str]] = None) -> argparse.Namespace:
-    return validate_args(build_parser().parse_args(argv))
+    parser = build_parser()
+    a = parser.parse_args(argv)
+    apply_flag_policy(a, parser)
+    return validate_args(a)
 
 
 def model_config_from_args(a):
@@ -395,6 +512,13 @@ def model_config_from_args(a):
     return ModelConfig(name="custom", **over)
 
 
+def _ci_config(a):
+    from ..train.ci_utils import CIConfig
+
+    ci = CIConfig.from_args(a)
+    return ci if (ci.enabled or ci.save_grad_norm or ci.load_grad_norm) else None
+
+
 def train_config_from_args(a):
     from ..algo.loss import LossConfig
     from ..train.actor import TrainConfig
@@ -420,4 +544,5 @@ def train_config_from_args(a):
         mtp_only_training=a.mtp_only_training,
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         freeze_params_name_list=getattr(a, "freeze_params_name_list", None),
-        only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim)
+        only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
+        ci=_ci_config(a))

@@ -478,18 +478,25 @@ def build_copy_table_raw(entries, device, elem_size: int, chunk_bytes: int = 1 <
     return CopyTable(table, cs, len(entries), total, chunk_rows, elem_size, None)
 
 
-def build_copy_table(blocks, trainer_params: dict, rollout_weights) -> CopyTable:
+def copy_entries(blocks, trainer_params: dict, dst_params: dict) -> list:
+    """Raw ``(src_ptr, dst_ptr, rows, cols, src_ld, dst_ld)`` entries of plan blocks; ``dst_params`` maps rollout
+    parameter names to tensors, which may be views of ANOTHER GPU's memory mapped into this process."""
     entries = []
     es = next(iter(trainer_params.values())).element_size()
     for b in blocks:
         src = trainer_params[b.src_name]
-        dst = rollout_weights.p[b.dst_name]
+        dst = dst_params[b.dst_name]
         s2 = src[b.src_batch] if src.dim() == 3 else (src.view(1, -1) if src.dim() == 1 else src)
         d2 = dst[b.dst_batch] if dst.dim() == 3 else (dst.view(1, -1) if dst.dim() == 1 else dst)
         sp = s2.data_ptr() + (b.src_row * s2.stride(0) + b.src_col) * es
         dp = d2.data_ptr() + (b.dst_row * d2.stride(0) + b.dst_col) * es
         entries.append((sp, dp, b.rows, b.cols, s2.stride(0), d2.stride(0)))
-    t = build_copy_table_raw(entries, rollout_weights.device, es)
+    return entries
+
+
+def build_copy_table(blocks, trainer_params: dict, rollout_weights) -> CopyTable:
+    es = next(iter(trainer_params.values())).element_size()
+    t = build_copy_table_raw(copy_entries(blocks, trainer_params, rollout_weights.p), rollout_weights.device, es)
     t.keepalive = (trainer_params, rollout_weights)
     return t
 

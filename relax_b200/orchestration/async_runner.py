@@ -26,7 +26,60 @@ class AsyncRunner:
         return self.pipe.run(timeout=self.timeout)
 
 
-def build_async_runner(args, model_cfg, train_cfg, device, start_rollout_id: int = 0) -> AsyncRunner:
+class DisaggRunner:
+    """Adapter of :class:`~relax_b200.orchestration.disagg.DisaggregatedRL` to the controller's runner protocol."""
+
+    def __init__(self, rl):
+        self.rl = rl
+        self.actor, self.engine = rl.actor, rl.engine
+
+    def run(self):
+        out = self.rl.run()
+        if not self.rl.is_trainer:
+            return []
+        extra = {k: float(v) for k, v in self.rl.stats.items() if isinstance(v, (int, float))}
+        return [(rid, {**m, **({f"async/{k}": v for k, v in extra.items()} if rid == out[-1][0] else {})}) for rid, m in out]
+
+    def close(self):
+        self.rl.close()
+
+
+def build_disagg_runner(args, model_cfg, train_cfg, device, start_rollout_id: int = 0) -> DisaggRunner:
+    """Trainer and rollout pools on disjoint ranks, placed by ``--resource`` (one process per GPU)."""
+    import torch.distributed as dist
+
+    from .disagg import DisaggConfig, DisaggregatedRL
+    from .registry import assign_ranks
+
+    world = dist.get_world_size()
+    res = dict(getattr(args, "resource_map", None) or {})
+    if "actor" not in res or "rollout" not in res:
+        n_roll = _get(args, "rollout_num_gpus", None) or world // 2
+        res = {"actor": (1, world - n_roll), "rollout": (1, n_roll)}
+    ranks = assign_ranks({k: res[k] for k in ("actor", "rollout")}, world, colocate=False)
+    plen = _get(args, "rollout_max_prompt_len", 512)
+    ctx = _get(args, "rollout_max_context_len", plen + args.rollout_max_response_len)
+    page = _get(args, "engine_block_size", 16)
+    rtp = _get(args, "rollout_num_gpus_per_engine", 1)
+    n_seq = args.rollout_batch_size * args.n_samples_per_prompt // max(1, len(ranks["rollout"]) // rtp)
+    cfg = DisaggConfig(
+        model=model_cfg, train=train_cfg, trainer_ranks=ranks["actor"], rollout_ranks=ranks["rollout"],
+        trainer_tp=args.tensor_model_parallel_size, rollout_tp=rtp, rollout_batch_size=args.rollout_batch_size,
+        prompt_len=plen, max_response_len=args.rollout_max_response_len, temperature=args.rollout_temperature,
+        top_p=_get(args, "rollout_top_p", 1.0), top_k=_get(args, "rollout_top_k", -1), rm_type=args.rm_type or "parity",
+        kv_blocks=_get(args, "kv_blocks", max(64, n_seq * (ctx // page + 2))), kv_block_size=page,
+        max_running=_get(args, "engine_max_running", 256), use_cuda_graph=not _get(args, "engine_disable_cuda_graph", False),
+        num_rollout=args.num_rollout - start_rollout_id, max_staleness=args.max_staleness,
+        update_weights_interval=args.update_weights_interval, seed=args.seed, rollout_seed=args.rollout_seed,
+        weight_push=_get(args, "weight_push", "peer"))
+    return DisaggRunner(DisaggregatedRL(cfg, device=device))
+
+
+def build_async_runner(args, model_cfg, train_cfg, device, start_rollout_id: int = 0):
+    import torch.distributed as dist
+
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        return build_disagg_runner(args, model_cfg, train_cfg, device, start_rollout_id)
     ps = single_process_state()
     need_ref = train_cfg.loss.use_kl_loss or train_cfg.kl_coef != 0
     actor = TrainActor(model_cfg, train_cfg, ps, device=device, seed=args.seed, with_reference=need_ref)

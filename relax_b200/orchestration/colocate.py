@@ -237,6 +237,7 @@ class ColocatedGRPO:
 
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+        self.engine.close()        # graphs that captured NCCL operations must die before their communicator can
         for g in (self.rollout_tp_group, self.ps.tp):
             fused_comm.detach(g)
         for c in self.fused_comms:

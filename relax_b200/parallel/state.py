@@ -177,9 +177,12 @@ def single_process_state() -> ParallelState:
 def shutdown_distributed(timeout_s: float = 120.0):
     """Leave the process groups in a fixed order that is the same on every rank.
 
-    Symmetric (CUDA IPC) buffers must have been closed by their owners before this is called: freeing an exported
-    allocation that a peer still maps, or destroying communicators while such mappings are live, is where a
-    four-rank teardown was seen to block.  All ranks synchronise their devices and meet; the sub-groups are then
+    Two things must have been released by their owners before this is called.  (1) CUDA graphs that captured NCCL
+    operations (the rollout engine's decode graphs under tensor parallelism): NCCL's communicator destroy polls
+    until every graph referencing the communicator is gone, so with such a graph alive the teardown never returns -
+    this is what blocked multi-rank runs of the benchmark (``RolloutEngine.close`` destroys the graphs).
+    (2) Symmetric (CUDA IPC) buffers: freeing an exported allocation that a peer still maps is undefined.
+    All ranks synchronise their devices and meet; the sub-groups are then
     destroyed one by one, newest first, and the default group last, on the calling thread with its device
     current.  A watchdog thread only observes: if the teardown has not finished after ``timeout_s`` it prints
     which group was being destroyed and ends the process with exit code 3, so a stuck teardown is reported rather

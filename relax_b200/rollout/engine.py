@@ -101,7 +101,8 @@ class RolloutEngine:
                  num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
                  use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
-                 decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None):
+                 decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None,
+                 weights_shared_path: Optional[str] = None):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
@@ -112,7 +113,7 @@ class RolloutEngine:
         self.memory_saver = bool(memory_saver)
         self._kv_buf = None
         self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype,
-                                      memory_saver=self.memory_saver)
+                                      memory_saver=self.memory_saver, shared_path=weights_shared_path)
         self.block_size = block_size
         self.bm = BlockManager(num_kv_blocks, block_size)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
@@ -186,6 +187,24 @@ class RolloutEngine:
             self.weights.resume()
         if "kv_cache" in tags and (self.kv is None or (self._kv_buf is not None and self._kv_buf.paused)):
             self._alloc_kv()
+
+    def close(self):
+        """Destroy the captured CUDA graphs (and their device buffers).  Must run before the process groups are
+        destroyed: under tensor parallelism the graphs contain NCCL collectives (embedding all-reduce, logits
+        all-gather), and NCCL keeps a communicator alive - its destroy call polls forever - while a graph that
+        captured its operations exists."""
+        import gc
+
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        for st in self._graphs.values():
+            st.pop("graph", None)
+            st.pop("run", None)
+        self._graphs = {}
+        self._graph_pool = None
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
 
     def flush_cache(self):
         if self.running:

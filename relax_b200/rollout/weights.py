@@ -66,21 +66,30 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
     return shapes
 
 
+def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1):
+    """``(shapes, element offsets, total elements)`` of one rank's flat parameter buffer.  A pure function of the
+    configuration, so a trainer rank can address tensors inside a rollout rank's buffer without asking it."""
+    shapes = rollout_param_shapes(cfg, tp, ep)
+    offsets, n = {}, 0
+    for k, s in shapes.items():
+        offsets[k] = n
+        n += (math.prod(s) + 127) // 128 * 128
+    return shapes, offsets, n
+
+
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
-                 memory_saver: bool = False):
+                 memory_saver: bool = False, shared_path: Optional[str] = None):
         if cfg.dsa_topk > 0 or cfg.linear_attention_freq > 0 or cfg.multi_latent_attention:
             raise NotImplementedError("the rollout engine serves softmax-attention stacks only; GDN / MLA / DSA layers are "
                                       "trainer-side (SFT, log-prob evaluation) for now")
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank
         self.device, self.dtype = torch.device(device), dtype
-        self.shapes = rollout_param_shapes(cfg, tp_size, ep_size)
-        self.offsets, n = {}, 0
-        for k, s in self.shapes.items():
-            self.offsets[k] = n
-            n += (math.prod(s) + 127) // 128 * 128
-        self.numel = n
+        self.shapes, self.offsets, self.numel = rollout_layout(cfg, tp_size, ep_size)
+        # CPU only: back the buffer by a shared-memory file so that other processes can map and write it (the CPU
+        # stand-in for a peer mapping of device memory; see weight_sync/peer_push.py)
+        self.shared_path = shared_path
         self.flat = None
         self.p: dict[str, torch.Tensor] = {}
         self.memory_saver = memory_saver
@@ -100,6 +109,9 @@ class RolloutWeights:
             self.flat = self._buf.tensor((self.numel,), self.dtype)
         elif self.flat is not None:
             return
+        elif self.shared_path is not None and self.device.type == "cpu":
+            self.flat = torch.from_file(self.shared_path, shared=True, size=self.numel, dtype=self.dtype)
+            self.flat.zero_()
         else:
             self.flat = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
         self.p = {k: self.flat[o:o + math.prod(self.shapes[k])].view(self.shapes[k]) for k, o in self.offsets.items()}

@@ -72,6 +72,7 @@ class TrainConfig:
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
     mtp_only_training: bool = False     # freeze the trunk, train the MTP blocks alone
+    ci: Optional[object] = None         # a train.ci_utils.CIConfig: first-step KL checks, grad-norm record / compare
     loss: L.LossConfig = field(default_factory=L.LossConfig)
     optim: OptimizerConfig = field(default_factory=OptimizerConfig)
 
@@ -432,6 +433,13 @@ class TrainActor:
             idx = list(range(s * per_step, min(n, (s + 1) * per_step)))
             with self.timer.span("train_step"):
                 m, last_norm = self._train_step(batch, idx)
+            if cfg.ci is not None and (cfg.ci.enabled or cfg.ci.save_grad_norm or cfg.ci.load_grad_norm):
+                from . import ci_utils as CI
+
+                self._ci_steps = getattr(self, "_ci_steps", 0)
+                CI.check_first_step_kl(cfg.ci, m, s, self._ci_steps)
+                CI.save_or_check_grad_norm(cfg.ci, self.role, rollout_id, s, last_norm, self.ps.global_rank)
+                self._ci_steps += 1
             for k, v in m.items():
                 agg[k] = agg.get(k, 0) + v / int(nsteps)
         if cfg.use_routing_replay and self.mcfg.is_moe:
