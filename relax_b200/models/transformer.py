@@ -261,6 +261,9 @@ class GPTModel(nn.Module):
         for n, p in self.named_parameters():
             if any(k in n for k in ("layernorm", "layer_norm", "router", "value_head", "shared_expert")) or n.endswith(".bias") and "linear_proj" in n:
                 p.tp_replicated = True
+        if hasattr(self, "embedding") and not self.pre_process:
+            # the last stage's copy of an embedding the first stage owns (tied output layer, MTP blocks)
+            self.embedding.word_embeddings.weight.pp_duplicate = True
 
     # ------------------------------------------------------------------ helpers
     def lm_head_weight(self):

@@ -44,6 +44,7 @@ class ColocateConfig:
     train: TrainConfig = field(default_factory=TrainConfig)
     trainer_tp: int = 1
     trainer_cp: int = 1
+    trainer_pp: int = 1
     rollout_tp: int = 1
     rollout_batch_size: int = 8          # prompts per rollout step (global)
     prompt_len: int = 64
@@ -128,10 +129,12 @@ class ColocatedGRPO:
         self.device = torch.device(device)
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.rank = dist.get_rank() if dist.is_initialized() else 0
-        ttp, tcp = cfg.trainer_tp, cfg.trainer_cp
-        dp = self.world // (ttp * tcp)
+        ttp, tcp, tpp = cfg.trainer_tp, cfg.trainer_cp, cfg.trainer_pp
+        dp = self.world // (ttp * tcp * tpp)
+        if tpp > 1 and (tcp != 1 or cfg.rollout_tp != ttp):
+            raise NotImplementedError("a pipeline-parallel trainer is colocated with engines of the same TP size, without CP")
         if self.world > 1:
-            self.ps = init_parallel_state(ParallelDims(tp=ttp, cp=tcp, dp=dp))
+            self.ps = init_parallel_state(ParallelDims(tp=ttp, cp=tcp, dp=dp, pp=tpp))
         else:
             self.ps = single_process_state()
         # rollout engines: consecutive blocks of rollout_tp ranks
@@ -184,9 +187,21 @@ class ColocatedGRPO:
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank
         tr_ranks = [r for r in self.ps.tp.ranks]
-        self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
-        self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks
-        if not self._aligned and not (ttp == 1 or rtp == 1 or ttp == rtp):
+        if tpp > 1:
+            # my replica spans tpp stages of ttp ranks; at every stage position sits one engine, and each engine needs
+            # the layers of ALL stages: one sync object per engine of the replica, walked in the same order everywhere
+            grid = {(st, j): j + ttp * (my_dp + dp * st) for st in range(tpp) for j in range(ttp)}
+            self.syncs = []
+            for st in range(tpp):
+                er = [grid[(st, j)] for j in range(ttp)]
+                self.syncs.append((WeightSync(cfg.model, TrainerLayout(tp=ttp, pp=tpp), rtp, grid, er), tuple(er) == eng_ranks))
+            self.sync = next(sy for sy, mine in self.syncs if mine)
+            self._aligned = False
+        else:
+            self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
+            self.syncs = [(self.sync, True)]
+            self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks
+        if not self._aligned and tpp == 1 and not (ttp == 1 or rtp == 1 or ttp == rtp):
             raise NotImplementedError("colocated sync needs trainer TP group == rollout engine ranks, or TP 1 on one side")
         self.queue = tq.init({"capacity_partitions": 2})
         if cfg.prompt_data:
@@ -253,7 +268,10 @@ class ColocatedGRPO:
     # ------------------------------------------------------------------ weight sync
     def sync_weights(self) -> float:
         params = dict(self.actor.named_local_params())
-        ms = self.sync.update_weights(params, self.engine.weights, self.engine, version=self.actor.weight_version)
+        ms = 0.0
+        for sync, mine in self.syncs:
+            ms += sync.update_weights(params, self.engine.weights if mine else None, self.engine if mine else None,
+                                      version=self.actor.weight_version)
         return ms
 
     # ------------------------------------------------------------------ rollout

@@ -97,7 +97,8 @@ class Controller:
             page = _get(a, "engine_block_size", 16)
             cfg = ColocateConfig(
                 model=self.model_cfg, train=self.train_cfg, trainer_tp=a.tensor_model_parallel_size,
-                trainer_cp=a.context_parallel_size, rollout_tp=_get(a, "rollout_num_gpus_per_engine", 1),
+                trainer_cp=a.context_parallel_size, trainer_pp=_get(a, "pipeline_model_parallel_size", 1),
+                rollout_tp=_get(a, "rollout_num_gpus_per_engine", 1),
                 rollout_batch_size=a.rollout_batch_size, prompt_len=plen,
                 max_response_len=a.rollout_max_response_len, temperature=a.rollout_temperature,
                 top_p=_get(a, "rollout_top_p", 1.0), top_k=_get(a, "rollout_top_k", -1), rm_type=a.rm_type or "parity",
@@ -140,8 +141,9 @@ class Controller:
             from ..train.actor import TrainActor
             from ..parallel.state import ParallelDims, init_parallel_state, single_process_state
 
-            ps = (init_parallel_state(ParallelDims(tp=a.tensor_model_parallel_size, cp=a.context_parallel_size,
-                                                   dp=self.world // (a.tensor_model_parallel_size * a.context_parallel_size)))
+            pp = _get(a, "pipeline_model_parallel_size", 1)
+            ps = (init_parallel_state(ParallelDims(tp=a.tensor_model_parallel_size, cp=a.context_parallel_size, pp=pp,
+                                                   dp=self.world // (a.tensor_model_parallel_size * a.context_parallel_size * pp)))
                   if self.world > 1 else single_process_state())
             return _SFTRunner(TrainActor(self.model_cfg, self.train_cfg, ps, device=self.device, seed=a.seed, role="sft"), a)
         from .async_runner import build_async_runner

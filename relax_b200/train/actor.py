@@ -231,6 +231,8 @@ class TrainActor:
             from ..models.moe import RoutingReplay
 
             RoutingReplay.set_layout(getattr(self, "_cur_ids", None), pb.total_lengths)
+        if self.ps.pp.size > 1:
+            return self._forward_logp_pp(pb, with_entropy)
         if self.ps.cp.size > 1:
             return self._forward_logp_cp(pb, with_entropy)
         h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
@@ -336,6 +338,101 @@ class TrainActor:
         if with_entropy:
             res["entropy"] = out_en
         return res
+
+    # ------------------------------------------------------------------ pipeline parallelism
+    def _stage_forward(self, pb, x):
+        """This pipeline stage's layers on one packed micro-batch: the first stage embeds the tokens, later stages
+        continue from the activations ``x`` received from upstream; the last stage returns the normalised hidden
+        states, the others their stage output."""
+        if self.model.pre_process:
+            return self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+        return self.model(None, pb.positions, pb.cu_seqlens, hidden_in=x, max_seqlen=pb.max_seqlen)
+
+    def _forward_logp_pp(self, pb, with_entropy: bool):
+        """Forward-only pass through the pipeline for one micro-batch; every stage returns the log-probs (the last
+        stage computes them and shares them with its pipeline group, so the callers are layout-agnostic).  Sends are
+        asynchronous, so consecutive micro-batches overlap across stages."""
+        from ..parallel import pp as PP
+
+        g = self.ps.pp
+        first, last = g.rank == 0, g.rank == g.size - 1
+        x = None if first else PP._recv(g.ranks[g.rank - 1], g.group, self.device, self.model.dtype)
+        h = self._stage_forward(pb, x)
+        n = int(sum(pb.response_lengths))
+        if last:
+            lp, en = self.model.log_probs(h.index_select(0, pb.logit_rows), pb.targets, self.cfg.rollout_temperature, with_entropy)
+            buf = torch.stack([lp.float(), en.float()])
+        else:
+            PP._send(h, g.ranks[g.rank + 1], g.group)
+            buf = torch.empty(2, n, dtype=torch.float32, device=self.device)
+        dist.broadcast(buf, src=g.ranks[-1], group=g.group)
+        PP._reap(all_=True)
+        return buf[0], buf[1]
+
+    def _sync_tied_embedding_grads(self):
+        """With tied input / output embeddings and more than one stage, the first and the last stage each hold a copy
+        of the table; their gradients are summed so both copies take the same step."""
+        g = self.ps.pp
+        if g.size == 1 or not self.mcfg.tie_word_embeddings:
+            return
+        emb = getattr(getattr(self.model, "embedding", None), "word_embeddings", None)
+        if emb is not None:
+            grad = emb.weight.main_grad if getattr(emb.weight, "main_grad", None) is not None else emb.weight.grad
+        else:       # middle stages take part with zeros (the group has no two-rank sub-group of its own)
+            v = (self.mcfg.vocab_size + self.ps.tp.size - 1) // self.ps.tp.size
+            grad = torch.zeros(v, self.mcfg.hidden_size, dtype=torch.float32, device=self.device)
+        dist.all_reduce(grad, group=g.group)
+
+    def _train_microbatches_pp(self, batch, idx, mbs, metrics, ntok):
+        """One optimizer step's micro-batches through the 1F1B schedule.  Every stage holds the whole batch (rows are
+        split over data-parallel replicas only), so each packs the micro-batch it works on locally and only
+        activations / activation gradients travel."""
+        from ..parallel import pp as PP
+
+        cfg, g = self.cfg, self.ps.pp
+        last = g.rank == g.size - 1
+        dp_cp = self.ps.dp_cp.size
+        counter = {"i": 0}
+
+        def forward_step(_mb, x):
+            mb = mbs[counter["i"]]
+            counter["i"] += 1
+            ids = [idx[j] for j in mb]
+            if ids:
+                pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
+            else:
+                pb = self._pack([[0, 0]], [1])
+            self._cur_ids = list(ids)
+            h = self._stage_forward(pb, x)
+            if not last:
+                return h, None
+            hr = h.index_select(0, pb.logit_rows)
+            if not ids:        # a dummy micro-batch keeps the replicas' schedules aligned; it contributes nothing
+                lp, _ = self.model.log_probs(hr, pb.targets, cfg.rollout_temperature, False)
+                return h, lp.sum() * 0.0
+            lb = self._loss_batch(batch, ids, pb)
+            if self.role == "sft":
+                lp, _ = self.model.log_probs(hr, pb.targets, cfg.rollout_temperature, False)
+                loss, m = L.sft_loss(lp, lb, cfg.loss)
+            else:
+                lp, en = self.model.log_probs(hr, pb.targets, cfg.rollout_temperature, cfg.compute_entropy)
+                loss, m = L.policy_loss(lp, en, lb, cfg.loss)
+            ntok.add_(lb.loss_mask.sum() if lb.loss_mask is not None else float(len(ids)))
+            for k, v in m.items():
+                metrics[k] = metrics.get(k, 0) + v.detach().float()
+            return h, loss if cfg.loss.calculate_per_token_loss else loss * (dp_cp / cfg.global_batch_size)
+
+        PP.forward_backward_1f1b(iter(mbs) if g.rank == 0 else None, forward_step, g, self.device, self.model.dtype)
+        self._sync_tied_embedding_grads()
+        # the loss metrics live on the last stage: share them so every stage reports (and reduces) the same numbers
+        obj = [sorted(metrics)] if last else [None]
+        dist.broadcast_object_list(obj, src=g.ranks[-1], group=g.group)
+        keys = obj[0]
+        vec = torch.stack([metrics[k] for k in keys] + [ntok[0]]) if last else torch.zeros(len(keys) + 1, device=self.device)
+        dist.broadcast(vec, src=g.ranks[-1], group=g.group)
+        metrics.clear()
+        metrics.update({k: vec[i] for i, k in enumerate(keys)})
+        ntok.copy_(vec[-1:])
 
     def _dummy_forward(self, backward: bool = False):
         pb = self._pack([[0, 0]], [1])
@@ -477,6 +574,11 @@ class TrainActor:
         dp_cp = ps.dp_cp.size
         metrics: dict[str, torch.Tensor] = {}
         ntok = torch.zeros(1, device=self.device)
+        if ps.pp.size > 1:
+            if self.role not in ("actor", "sft") or cfg.loss.custom_loss_function is not None or self.mcfg.mtp_num_layers > 0:
+                raise NotImplementedError("pipeline parallelism covers the policy and SFT losses of the plain decoder")
+            self._train_microbatches_pp(batch, idx, mbs, metrics, ntok)
+            mbs = []
         for mb in mbs:
             if not mb:
                 self._dummy_forward(backward=True)

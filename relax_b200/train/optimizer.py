@@ -106,6 +106,9 @@ class DistributedOptimizer:
         for p, o in zip(self.params, offs):
             if is_rep(p):
                 self.rep_elems = o + p.numel()
+        # parameters that ANOTHER pipeline stage also holds (the last stage's copy of a tied embedding): their
+        # gradient is identical on both stages after the tie all-reduce and must enter the global norm once
+        self.dup_ranges = [(o, o + p.numel()) for p, o in zip(self.params, offs) if getattr(p, "pp_duplicate", False)]
         chunk = self.ALIGN * dp
         self.total = (n + chunk - 1) // chunk * chunk
         self.shard = self.total // dp
@@ -223,6 +226,10 @@ class DistributedOptimizer:
             tot = sq.sum()
             if ps.tp.size > 1 and ps.tp.rank != 0 and self.rep_elems > lo:
                 tot = tot - sq[: max(0, min(hi, self.rep_elems) - lo)].sum()
+        for a, b in self.dup_ranges:
+            a2, b2 = max(a, lo), min(b, hi)
+            if a2 < b2:
+                tot = tot - gshard[a2 - lo:b2 - lo].float().pow(2).sum()
         if ps.dp_cp.size > 1:
             dist.all_reduce(tot, group=ps.dp_cp.group)
         if ps.tp.size > 1:

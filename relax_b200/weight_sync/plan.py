@@ -37,6 +37,7 @@ class BlockCopy:
     cols: int
     src_batch: int = 0   # leading index for stacked expert tensors
     dst_batch: int = 0
+    src_stage: int = 0   # pipeline stage of the trainer that owns the source tensor
 
 
 @dataclass(frozen=True)
@@ -174,6 +175,16 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
                 add(BlockCopy(sp, trainer_param_name(ll, "fc1"), Fs + so, 0, dp, p + "gate_up", Fd + do, 0, n, H))  # up
             for sp, so, dp, do, n in _row_sharded(F, src.tp, dst_tp):
                 add(BlockCopy(sp, trainer_param_name(ll, "fc2"), 0, so, dp, p + "down", 0, do, H, n))
+    if src.pp > 1:
+        from dataclasses import replace as _replace
+
+        def stage_of(b: BlockCopy) -> int:
+            if b.dst_name.startswith("layers."):
+                return int(b.dst_name.split(".")[1]) // per_stage
+            if b.dst_name == "embed":
+                return 0
+            return src.pp - 1          # final norm, output layer
+        plan = [_replace(b, src_stage=stage_of(b)) for b in plan]
     return plan
 
 

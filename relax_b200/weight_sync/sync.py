@@ -52,7 +52,12 @@ class WeightSync:
         # ``post_hook(name, tensor) -> tensor`` runs on every rollout tensor after the copy (quantisation round trip)
         self.post_hook = post_hook
         self.plan = build_plan(cfg, trainer_layout, rollout_tp, rollout_ep)
-        self.trainer_ranks, self.rollout_ranks = list(trainer_ranks), list(rollout_ranks)
+        # ``trainer_ranks``: list indexed by TP rank (one pipeline stage), or ``{(stage, tp_rank): global rank}``
+        if isinstance(trainer_ranks, dict):
+            self.trainer_ranks = dict(trainer_ranks)
+        else:
+            self.trainer_ranks = {(0, i): r for i, r in enumerate(trainer_ranks)}
+        self.rollout_ranks = list(rollout_ranks)
         self.me = dist.get_rank() if dist.is_initialized() else 0
         self.group = group
         self.last_ms = 0.0
@@ -61,7 +66,7 @@ class WeightSync:
     def _pairs(self):
         pairs: dict = {}
         for b in self.plan:
-            s, d = self.trainer_ranks[b.src_rank], self.rollout_ranks[b.dst_rank]
+            s, d = self.trainer_ranks[(b.src_stage, b.src_rank)], self.rollout_ranks[b.dst_rank]
             pairs.setdefault((s, d), []).append(b)
         return pairs
 
