@@ -545,4 +545,4 @@ def train_config_from_args(a):
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         freeze_params_name_list=getattr(a, "freeze_params_name_list", None),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
-        ci=_ci_config(a))
+        ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

@@ -283,6 +283,38 @@ def ring_attention(q, k, v, g: GroupInfo, total_length: int, scale: Optional[flo
     return _RingAttention.apply(q, k, v, g, total_length, scale)
 
 
+def allgather_attention(q, k, v, g: GroupInfo, total_length: int, scale: Optional[float] = None):
+    """The all-gather variant of context parallelism (``--allgather-cp``): K and V of the whole sequence are gathered
+    on every rank (backward: their gradients are summed and each rank keeps its rows), and each of the rank's two
+    zig-zag query chunks attends to the key prefix that ends with it - two calls of the ordinary causal attention
+    operator with a query block shorter than its keys, no ring, no partial-result merging.  Costs ``O(L)`` K/V
+    memory per rank instead of ``O(L / cp)``; fewer, larger attention calls."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if g.size == 1:
+        cu = torch.tensor([0, q.shape[0]], dtype=torch.int32, device=q.device)
+        return ops.attention_varlen(q, k, v, cu, causal=True, scale=scale)
+    cp, r = g.size, g.rank
+    cs = q.shape[0] // 2
+    kf = _GatherZigzag.apply(k.contiguous(), g)
+    vf = _GatherZigzag.apply(v.contiguous(), g)
+    outs = []
+    for ai, a in enumerate((r, 2 * cp - 1 - r)):
+        qn = max(0, min(cs, total_length - a * cs))        # real rows of this chunk
+        qa = q[ai * cs:(ai + 1) * cs]
+        if qn == 0:
+            outs.append(qa * 0)
+            continue
+        klen = a * cs + qn
+        cu_q = torch.tensor([0, qn], dtype=torch.int32, device=q.device)
+        cu_k = torch.tensor([0, klen], dtype=torch.int32, device=q.device)
+        o = ops.attention_varlen(qa[:qn].contiguous(), kf[:klen], vf[:klen], cu_q, causal=True, scale=scale,
+                                 cu_seqlens_k=cu_k, max_seqlen=klen)
+        if qn < cs:
+            o = torch.cat([o, qa[qn:] * 0])
+        outs.append(o)
+    return torch.cat(outs)
+
+
 # --------------------------------------------------------------------------- whole-sequence ops under CP
 class _GatherZigzag(torch.autograd.Function):
     """Local zig-zag shard ``[2 * cs, ...]`` -> the full sequence ``[2 * cp * cs, ...]`` in token order on every rank.

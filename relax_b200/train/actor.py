@@ -51,6 +51,10 @@ class TrainConfig:
     # context parallelism: every zig-zag chunk is padded to a multiple of this many tokens (None: ``pad_multiple``
     # on a GPU, where the attention tiles want whole 128-row blocks, 1 on the CPU)
     cp_chunk_multiple: Optional[int] = None
+    # context-parallel attention: "peer" (GPU default: K/V staged once in every peer's memory over NVLink, partial
+    # results merged by log-sum-exp), "allgather" (K/V gathered, two plain attention calls per rank; --allgather-cp),
+    # "ring" (send/recv ring with the PyTorch statement of attention: the CPU oracle)
+    cp_attention: Optional[str] = None
     use_rollout_logprobs: bool = False
     keep_old_actor: bool = False
     compute_entropy: bool = True
@@ -210,13 +214,19 @@ class TrainActor:
             cs = Lp // (2 * cp)
             tok_pad = torch.cat([toks, toks.new_zeros(Lp - L + 1)])
             idx = torch.cat([torch.arange(r * cs, (r + 1) * cs), torch.arange((2 * cp - 1 - r) * cs, (2 * cp - r) * cs)]).to(toks.device)
-            comm = getattr(self, "cp_comm", None)
+            mode = self.cfg.cp_attention or ("peer" if self.device.type == "cuda" else "ring")
+            if mode == "ring" and self.device.type == "cuda":
+                raise RuntimeError("the ring statement of context-parallel attention is a CPU oracle (it materialises "
+                                   "the score matrix); use cp_attention='peer' or 'allgather' on a GPU")
+            comm = self._cp_comm_for(2 * cs) if mode == "peer" else None
 
-            def attn(layer_idx, q, k, v, L=L, comm=comm):
-                if comm is not None and q.is_cuda:
+            def attn(layer_idx, q, k, v, L=L, comm=comm, mode=mode):
+                if mode == "peer":
                     from ..parallel.cp_peer import peer_attention
 
                     return peer_attention(q, k.contiguous(), v.contiguous(), comm, L)
+                if mode == "allgather":
+                    return CP.allgather_attention(q, k, v, g, L)
                 return CP.ring_attention(q, k.contiguous(), v.contiguous(), g, L)
 
             h = self.model(tok_pad[idx], idx, None, attn_fn=attn)
@@ -225,6 +235,22 @@ class TrainActor:
             lps.append(CP.gather_response_with_cp(lp, L, R, g, padded_total_length=Lp))
             ens.append(CP.gather_response_with_cp(en, L, R, g, padded_total_length=Lp) if with_entropy else lp.new_zeros(R))
         return torch.cat(lps), torch.cat(ens)
+
+    def _cp_comm_for(self, rows: int):
+        """The NVLink staging buffers of this rank's context-parallel group, (re)made when a sequence needs more local
+        rows than they hold.  Collective over the group: every CP rank sees the same sequences in the same order."""
+        comm = getattr(self, "cp_comm", None)
+        if comm is not None and comm.rows >= rows:
+            return comm
+        from ..parallel.cp_peer import CPComm
+
+        if comm is not None:
+            comm.close()
+        tp = self.ps.tp.size
+        cap = max(rows, 1 << max(10, (rows - 1).bit_length()))      # grow in powers of two
+        self.cp_comm = CPComm(self.ps.cp, self.device, cap, self.mcfg.num_attention_heads // tp,
+                              self.mcfg.num_query_groups // tp, self.mcfg.head_dim)
+        return self.cp_comm
 
     def _forward_logp(self, pb, with_entropy: bool):
         if self.cfg.use_routing_replay and self.mcfg.is_moe:

@@ -80,15 +80,15 @@ def test_ring_attention_matches_full_attention_two_ranks():
     assert all(run_distributed(_ring_worker, 2))
 
 
-def _cp_train_worker(rank, world, chunk_multiple=None):
+def _cp_train_worker(rank, world, chunk_multiple=None, cp_attention=None):
     """cp=2 trainer forward/backward equals the single-rank one (log-probs and parameter gradients)."""
     from relax_b200.models.config import get_config
     from relax_b200.parallel.state import ParallelDims, init_parallel_state
     from relax_b200.train.actor import TrainActor, TrainConfig
 
     ps = init_parallel_state(ParallelDims(cp=2))
-    actor = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512, cp_chunk_multiple=chunk_multiple),
-                       ps, seed=7)
+    actor = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512, cp_chunk_multiple=chunk_multiple,
+                                                      cp_attention=cp_attention), ps, seed=7)
     toks = [list(range(3, 40)), list(range(50, 73))]
     rl = [11, 9]
     pb = actor._pack(toks, rl)
@@ -119,12 +119,12 @@ def test_padded_layout_offsets_cover_each_token_once():
 import pytest
 
 
-@pytest.mark.parametrize("chunk_multiple", [None, 8])
-def test_trainer_forward_backward_under_cp2_matches_cp1(chunk_multiple):
+@pytest.mark.parametrize("chunk_multiple,cp_attention", [(None, None), (8, None), (None, "allgather"), (8, "allgather")])
+def test_trainer_forward_backward_under_cp2_matches_cp1(chunk_multiple, cp_attention):
     from relax_b200.models.config import get_config
     from relax_b200.train.actor import TrainActor, TrainConfig
 
-    out = run_distributed(_cp_train_worker, 2, chunk_multiple)
+    out = run_distributed(_cp_train_worker, 2, chunk_multiple, cp_attention)
     ref = TrainActor(get_config("tiny"), TrainConfig(pad_multiple=1, max_tokens_per_gpu=512), seed=7)
     toks = [list(range(3, 40)), list(range(50, 73))]
     pb = ref._pack(toks, [11, 9])
