@@ -111,6 +111,12 @@ int rb_peer_barrier(unsigned* const* peer_sig, int* state, int n, int rank, int 
 int rb_peer_push(const void* src, void* const* dst, int n_dst, long long nbytes, cudaStream_t st);
 int rb_gemm_fp8_blockscaled(const void* A, const float* sa, const void* B, const float* sb, void* C, int M, int N, int K,
                             int lda, int ldb, int ldc, int* err, cudaStream_t stream);
+int rb_grouped_gemm_fwd(const void* X, const void* W, void* Y, const int* tile_expert, int rows_cap, int N, int K, int E,
+                        int* err, cudaStream_t st);
+int rb_grouped_gemm_dgrad(const void* dY, const void* W, void* dX, const int* tile_expert, int rows_cap, int Nw, int Kw,
+                          int E, int* err, cudaStream_t st);
+int rb_grouped_gemm_wgrad(const void* dY, const void* X, void* dW, const int* expert_rows, int rows_cap, int Nw, int Kw,
+                          int E, int out_fp32, int accumulate, int* err, cudaStream_t st);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

@@ -108,6 +108,37 @@ void decode_advance(torch::Tensor tok_new, torch::Tensor lp_new, torch::Tensor t
                           cur_stream()),
         "rb_decode_advance");
 }
+void grouped_gemm_fwd(torch::Tensor X, torch::Tensor W, torch::Tensor Y, torch::Tensor tile_expert, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(X.device());
+  TORCH_CHECK(X.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && Y.scalar_type() == at::kBFloat16, "bf16 only");
+  TORCH_CHECK(X.is_contiguous() && W.is_contiguous() && Y.is_contiguous() && W.dim() == 3, "contiguous X [cap,K], W [E,N,K]");
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.numel() * 128 == X.size(0), "tile map: one int32 per 128 rows");
+  check(rb_grouped_gemm_fwd(X.data_ptr(), W.data_ptr(), Y.data_ptr(), tile_expert.data_ptr<int>(), (int)X.size(0),
+                            (int)W.size(1), (int)W.size(2), (int)W.size(0), err.data_ptr<int>(), cur_stream()),
+        "rb_grouped_gemm_fwd");
+}
+void grouped_gemm_dgrad(torch::Tensor dY, torch::Tensor W, torch::Tensor dX, torch::Tensor tile_expert, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(dY.device());
+  TORCH_CHECK(dY.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && dX.scalar_type() == at::kBFloat16, "bf16 only");
+  TORCH_CHECK(dY.is_contiguous() && W.is_contiguous() && dX.is_contiguous() && W.dim() == 3, "contiguous dY [cap,N], W [E,N,K]");
+  TORCH_CHECK(tile_expert.scalar_type() == at::kInt && tile_expert.numel() * 128 == dY.size(0), "tile map: one int32 per 128 rows");
+  check(rb_grouped_gemm_dgrad(dY.data_ptr(), W.data_ptr(), dX.data_ptr(), tile_expert.data_ptr<int>(), (int)dY.size(0),
+                              (int)W.size(1), (int)W.size(2), (int)W.size(0), err.data_ptr<int>(), cur_stream()),
+        "rb_grouped_gemm_dgrad");
+}
+void grouped_gemm_wgrad(torch::Tensor dY, torch::Tensor X, torch::Tensor dW, torch::Tensor expert_rows, bool accumulate,
+                        torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(dY.device());
+  TORCH_CHECK(dY.scalar_type() == at::kBFloat16 && X.scalar_type() == at::kBFloat16, "bf16 inputs");
+  TORCH_CHECK(dY.is_contiguous() && X.is_contiguous() && dW.is_contiguous() && dW.dim() == 3, "contiguous dY, X, dW [E,N,K]");
+  TORCH_CHECK(expert_rows.scalar_type() == at::kInt && expert_rows.numel() == dW.size(0) + 1, "expert_rows: int32 [E + 1]");
+  const bool f32 = dW.scalar_type() == at::kFloat;
+  TORCH_CHECK(f32 || dW.scalar_type() == at::kBFloat16, "dW must be fp32 or bf16");
+  check(rb_grouped_gemm_wgrad(dY.data_ptr(), X.data_ptr(), dW.data_ptr(), expert_rows.data_ptr<int>(), (int)dY.size(0),
+                              (int)dW.size(1), (int)dW.size(2), (int)dW.size(0), f32, accumulate, err.data_ptr<int>(),
+                              cur_stream()),
+        "rb_grouped_gemm_wgrad");
+}
 void topk_router(torch::Tensor logits, int64_t K, bool norm, torch::Tensor w, torch::Tensor idx, torch::Tensor probs) {
   const c10::cuda::CUDAGuard guard(logits.device());
   check(rb_topk_router(logits.data_ptr<float>(), (int)logits.size(0), (int)logits.size(1), (int)K, norm,
@@ -168,6 +199,9 @@ void register_more(pybind11::module_& m) {
   m.def("sample", &sample);
   m.def("sample_v2", &sample_v2);
   m.def("decode_advance", &decode_advance);
+  m.def("grouped_gemm_fwd", &grouped_gemm_fwd);
+  m.def("grouped_gemm_dgrad", &grouped_gemm_dgrad);
+  m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad);
   m.def("topk_router", &topk_router);
   m.def("gemm_splitk_plan", &gemm_splitk_plan);
   m.def("gemm_splitk", &gemm_splitk);

@@ -105,24 +105,46 @@ class _AllToAll(torch.autograd.Function):
         return dx, None, None, None
 
 
-def grouped_swiglu_mlp(x, tokens_per_expert, w1, w2):
-    """x ``[N, H]`` sorted by expert; w1 ``[E, 2F, H]``, w2 ``[E, H, F]``."""
-    if x.is_cuda:
-        from ..ops import cuda as _c
+EXPERT_ROW_ALIGN = 128       # the grouped GEMM walks 128-row tiles; no tile may hold rows of two experts
 
-        if hasattr(_c, "grouped_swiglu_mlp") and not ops._force_ref():
-            return _c.grouped_swiglu_mlp(x, tokens_per_expert, w1, w2)
-    outs, s = [], 0
-    for e, n in enumerate(tokens_per_expert):
-        if n == 0:
-            continue
-        xe = x[s:s + n]
-        a = ops.swiglu(ops.linear(xe, w1[e]))
-        outs.append(ops.linear(a, w2[e]))
-        s += n
-    if not outs:
-        return x.new_zeros(0, w2.shape[1]) + 0.0 * (w1.sum() + w2.sum())
-    return torch.cat(outs, 0)
+
+def padded_expert_layout(expert_of_row: torch.Tensor, num_experts: int, align: int = EXPERT_ROW_ALIGN):
+    """Where every row goes in the expert-sorted buffer whose expert groups are padded to ``align`` rows.
+
+    Everything stays on the device (no count is read back): the buffer is sized for the worst case
+    ``rows + num_experts * (align - 1)``, unused tiles are marked in the tile map.  Returns ``(order, dest, cap,
+    tile_expert, expert_rows)``: ``order`` sorts the rows by expert (stable), ``dest[i]`` is the buffer row of sorted
+    position ``i``, ``tile_expert`` (int32, one entry per ``align`` rows) names each tile's expert or -1,
+    ``expert_rows`` (int32 ``[E + 1]``) are the padded group boundaries."""
+    R, dev = expert_of_row.numel(), expert_of_row.device
+    counts = torch.bincount(expert_of_row, minlength=num_experts)
+    padded = (counts + (align - 1)) // align * align
+    ends_pad = torch.cumsum(padded, 0)
+    offs_pad = ends_pad - padded
+    offs = torch.cumsum(counts, 0) - counts
+    order = torch.argsort(expert_of_row, stable=True)
+    e_sorted = expert_of_row[order]
+    dest = offs_pad[e_sorted] + (torch.arange(R, device=dev) - offs[e_sorted])
+    cap = (R + num_experts * (align - 1) + align - 1) // align * align
+    tile_start = torch.arange(cap // align, device=dev) * align
+    te = torch.searchsorted(ends_pad, tile_start, right=True)
+    tile_expert = torch.where(te < num_experts, te, torch.full_like(te, -1)).to(torch.int32)
+    expert_rows = torch.cat([ends_pad.new_zeros(1), ends_pad]).to(torch.int32)
+    return order, dest, cap, tile_expert, expert_rows
+
+
+def grouped_swiglu_mlp(x, expert_of_row, w1, w2):
+    """SwiGLU expert MLPs for rows ``x [R, H]`` with (local) expert ids ``expert_of_row [R]``, in the ORIGINAL row
+    order: rows are scattered into the padded expert-sorted buffer, the two grouped GEMMs (one launch each for all
+    experts) and the activation run on it, and the rows are gathered back.  ``w1 [E, 2F, H]``, ``w2 [E, H, F]``."""
+    E = w1.shape[0]
+    order, dest, cap, tile_expert, expert_rows = padded_expert_layout(expert_of_row, E)
+    xp = x.new_zeros(cap, x.shape[1]).index_copy(0, dest, x.index_select(0, order))
+    a = ops.swiglu(ops.grouped_linear(xp, w1, tile_expert, expert_rows))
+    yp = ops.grouped_linear(a, w2, tile_expert, expert_rows)
+    inv = torch.empty_like(order)
+    inv[order] = dest                       # buffer row of every original row
+    return yp.index_select(0, inv)
 
 
 def route_tokens(logits, cfg, bias=None):
@@ -239,12 +261,9 @@ class MoEMLP(nn.Module):
             xr = peer_all_to_all(xp, matrix, comm)
             rc = recv_counts.reshape(-1)
             seg_expert = torch.arange(self.e_local, device=x.device).repeat(ep)
-            reorder = torch.argsort(torch.repeat_interleave(seg_expert, rc), stable=True)
-            ye = grouped_swiglu_mlp(xr[reorder], recv_counts.sum(0).tolist(), self.experts.linear_fc1.weight,
+            ye = grouped_swiglu_mlp(xr, torch.repeat_interleave(seg_expert, rc), self.experts.linear_fc1.weight,
                                     self.experts.linear_fc2.weight)
-            inv = torch.empty_like(reorder)
-            inv[reorder] = torch.arange(reorder.numel(), device=x.device)
-            yp = peer_all_to_all(ye[inv], [[matrix[d][s_] for d in range(ep)] for s_ in range(ep)], comm)
+            yp = peer_all_to_all(ye, [[matrix[d][s_] for d in range(ep)] for s_ in range(ep)], comm)
         elif ps.ep.size > 1:
             ep = ps.ep.size
             send_counts = counts.view(ep, self.e_local)
@@ -257,16 +276,12 @@ class MoEMLP(nn.Module):
             rc = recv_counts.reshape(-1)
             seg_expert = torch.arange(self.e_local, device=x.device).repeat(ep)
             row_expert = torch.repeat_interleave(seg_expert, rc)
-            reorder = torch.argsort(row_expert, stable=True)
-            xe = xr[reorder]
-            tpe = recv_counts.sum(0).tolist()
-            ye = grouped_swiglu_mlp(xe, tpe, self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
-            inv = torch.empty_like(reorder)
-            inv[reorder] = torch.arange(reorder.numel(), device=x.device)
-            yr = ye[inv]
+            yr = grouped_swiglu_mlp(xr, row_expert, self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
             yp = _AllToAll.apply(yr, in_splits, out_splits, ps.ep.group)
         else:
-            yp = grouped_swiglu_mlp(xp, counts.tolist(), self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
+            # rows of ``xp`` are already sorted by expert; the grouped path re-derives the (padded) layout on the
+            # device, so no count leaves the GPU
+            yp = grouped_swiglu_mlp(xp, flat_e[order], self.experts.linear_fc1.weight, self.experts.linear_fc2.weight)
 
         wf = w.reshape(-1)[order].to(yp.dtype)
         out = torch.zeros(T, H, dtype=yp.dtype, device=x.device)

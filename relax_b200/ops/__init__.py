@@ -72,6 +72,14 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return ref.sample(logits, temperature, top_k, top_p, uniform)
 
 
+def grouped_linear(x, w, tile_expert, expert_rows):
+    """Per-expert linear over an expert-sorted token buffer whose expert groups start at multiples of 128 rows
+    (see :func:`relax_b200.models.moe.padded_expert_layout`); ``w`` is ``[E, N, K]``."""
+    if _use_cuda(x):
+        return _cuda().grouped_linear(x, w, tile_expert, expert_rows)
+    return ref.grouped_linear(x, w, tile_expert, expert_rows)
+
+
 def decode_advance(tok_new, lp_new, state, block_size):
     """In-place advance of the rollout engine's device-resident batch state after one decode step."""
     if _use_cuda(tok_new):

@@ -726,6 +726,50 @@ def fused_lm_head_logprob(hidden, weight, targets, tp_group=None, vocab_start=0,
     return _FusedLMHead.apply(hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature)
 
 
+# --------------------------------------------------------------------------- grouped (MoE expert) GEMM
+
+
+class _GroupedLinear(torch.autograd.Function):
+    """``y[row] = x[row] @ w[expert(row)].T`` over an expert-sorted, 128-row aligned token buffer: ONE kernel launch
+    per product for all local experts, tile -> expert map read on the device (csrc/grouped_gemm_sm100.cu)."""
+
+    @staticmethod
+    def forward(ctx, x, w, tile_expert, expert_rows):
+        x = x.contiguous()
+        wc = w if w.is_contiguous() else w.contiguous()
+        y = torch.empty(x.shape[0], w.shape[1], dtype=x.dtype, device=x.device)
+        _load().grouped_gemm_fwd(x, wc, y, tile_expert, err_flag(x.device))
+        ctx.save_for_backward(x, wc, tile_expert, expert_rows)
+        ctx.weight = w
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, wc, tile_expert, expert_rows = ctx.saved_tensors
+        w = ctx.weight
+        dy = dy.contiguous()
+        L = _load()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            L.grouped_gemm_dgrad(dy, wc, dx, tile_expert, err_flag(x.device))
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None and mg.dtype == torch.float32 and mg.shape == w.shape and mg.is_contiguous():
+                L.grouped_gemm_wgrad(dy, x, mg, expert_rows, True, err_flag(x.device))
+            else:
+                dw = torch.empty_like(wc)
+                L.grouped_gemm_wgrad(dy, x, dw, expert_rows, False, err_flag(x.device))
+        return dx, dw, None, None
+
+
+def grouped_linear(x, w, tile_expert, expert_rows):
+    if x.dtype != torch.bfloat16 or x.shape[0] % 128 or w.shape[1] % 64 or w.shape[2] % 64:
+        raise ValueError("grouped GEMM: bf16, token rows padded to 128 per expert, expert dims multiples of 64")
+    return _GroupedLinear.apply(x, w, tile_expert, expert_rows)
+
+
 def launch_count() -> int:
     """Number of kernels of this extension launched since the last reset (all threads)."""
     return int(_load().launch_count())

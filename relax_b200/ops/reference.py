@@ -162,6 +162,19 @@ def sample(logits, temperature, top_k, top_p, uniform):
     return tok, logp_full.gather(-1, tok[:, None])[:, 0]
 
 
+def grouped_linear(x, w, tile_expert, expert_rows):
+    """``y[row] = x[row] @ w[e].T`` for the rows of expert ``e`` (``expert_rows[e] : expert_rows[e + 1]`` of the padded,
+    expert-sorted buffer); rows outside every expert's range stay zero."""
+    y = x.new_zeros(x.shape[0], w.shape[1])
+    bounds = expert_rows.tolist()
+    parts = []
+    for e in range(w.shape[0]):
+        a, b = bounds[e], bounds[e + 1]
+        parts.append(x[a:b] @ w[e].t().to(x.dtype))
+    tail = x.new_zeros(x.shape[0] - bounds[-1], w.shape[1]) + 0.0 * w.sum().to(x.dtype)
+    return torch.cat(parts + [tail]) if parts else y
+
+
 def decode_advance(tok_new, lp_new, st, block_size: int):
     """Turn the tokens sampled by one decode step into the next step's inputs, in place, without the host.
 
