@@ -183,7 +183,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       k_range(a, k_lo, k_hi, e);
       const int n0 = tn * BN;
       const bool empty = k_lo >= k_hi;
-      if (empty && (MODE != kWgrad || p.accumulate)) continue;   // unused tile, or an empty expert adds nothing
+      // an expert without tokens adds nothing to an accumulated gradient; everywhere else an empty work item (an
+      // unused tile of the padded buffer, an expert without tokens) is written as zeros so no row is left undefined
+      if (empty && MODE == kWgrad && p.accumulate) continue;
       int out_row, out_rows, out_cols;
       size_t out_base;
       if constexpr (MODE == kWgrad) {

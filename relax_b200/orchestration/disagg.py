@@ -178,8 +178,10 @@ class DisaggregatedRL:
                 self.pusher = PeerWeightPusher(cfg.model, TrainerLayout(tp=cfg.trainer_tp), rtp, self.ps.tp.rank, mine,
                                                self.tag, device, dtype)
         if cfg.weight_push == "broadcast" and (self.is_rollout or (self.is_trainer and self.ps.dp.rank == 0)):
+            # one group per source rank of replica 0: a trainer rank takes part in its own group only
             self.bcast = [BroadcastPusher(cfg.model, TrainerLayout(tp=cfg.trainer_tp), rtp, tr[:cfg.trainer_tp], self.engines,
-                                          g, device, dtype) for g in self.bcast_groups]
+                                          g, device, dtype, src_index=i)
+                          for i, g in enumerate(self.bcast_groups) if self.is_rollout or self.rank == tr[i]]
         self.metrics: list = []
         self.stats = {"idle_s": 0.0, "busy_s": 0.0, "sync_ms": [], "push_kernel_ms": [], "rollout_started": []}
         # the engines start from the trainer's initial weights (version 0)

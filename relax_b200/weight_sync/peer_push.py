@@ -61,6 +61,33 @@ class SharedWeightRegion:
         self.server.close()
 
 
+class _PtrView:
+    """Address arithmetic over a row-major tensor that lives in ANOTHER GPU's memory.  Deliberately not a
+    ``torch.Tensor``: nothing but the copy kernel's address table may touch peer memory (a library kernel handed a
+    peer pointer could issue loads that are not safe across GPUs), so the view only answers the questions the table
+    builder asks."""
+
+    def __init__(self, ptr: int, shape, itemsize: int):
+        self.ptr, self.shape, self.itemsize = int(ptr), tuple(int(x) for x in shape), int(itemsize)
+
+    def dim(self) -> int:
+        return len(self.shape)
+
+    def data_ptr(self) -> int:
+        return self.ptr
+
+    def stride(self, d: int) -> int:
+        return int(math.prod(self.shape[d + 1:]))
+
+    def __getitem__(self, i: int) -> "_PtrView":
+        return _PtrView(self.ptr + int(i) * self.stride(0) * self.itemsize, self.shape[1:], self.itemsize)
+
+    def view(self, *shape) -> "_PtrView":
+        n = math.prod(self.shape)
+        shape = tuple(n // max(1, -math.prod(shape)) if x == -1 else x for x in shape)
+        return _PtrView(self.ptr, shape, self.itemsize)
+
+
 class PeerRegion:
     """Importer side (a trainer rank): another rank's flat weight buffer mapped here, with per-parameter views."""
 
@@ -84,8 +111,12 @@ class PeerRegion:
             finally:
                 for fd in fds:
                     os.close(fd)
-            self.flat = self._C.tensor_from_ptr(self._ptr, [numel], dtype, idx)
-        self.p = {k: self.flat[o:o + math.prod(shapes[k])].view(shapes[k]) for k, o in offsets.items()}
+            self.flat = None
+        if self.flat is not None:
+            self.p = {k: self.flat[o:o + math.prod(shapes[k])].view(shapes[k]) for k, o in offsets.items()}
+        else:
+            es = torch.empty(0, dtype=dtype).element_size()
+            self.p = {k: _PtrView(self._ptr + o * es, shapes[k], es) for k, o in offsets.items()}
         if cfg.tie_word_embeddings:
             self.p["lm_head"] = self.p["embed"]
 
@@ -164,7 +195,10 @@ class BroadcastPusher:
     ``rollout_weights`` None on sources)."""
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int, src_global_ranks: Sequence[int],
-                 engines: Sequence[Sequence[int]], group, device, dtype):
+                 engines: Sequence[Sequence[int]], group, device, dtype, src_index: Optional[int] = None):
+        # ``src_index``: this object moves the blocks of ONE source rank (its group holds that rank and the
+        # destinations); None: all sources through one group that contains them all
+        self.src_index = src_index
         self.plan = build_plan(cfg, trainer_layout, rollout_tp, 1)
         self.src, self.engines, self.group = list(src_global_ranks), [list(e) for e in engines], group
         self.device, self.dtype = torch.device(device), dtype
@@ -176,6 +210,8 @@ class BroadcastPusher:
         t0 = time.perf_counter()
         my_tp = next((j for e in self.engines for j, g in enumerate(e) if g == self.me), None)
         for s, src_global in enumerate(self.src):
+            if self.src_index is not None and s != self.src_index:
+                continue
             blocks = [b for b in self.plan if b.src_rank == s]
             # identical (src tensor, rows, cols) regions are sent once even when several destinations take them
             uniq, order = {}, []

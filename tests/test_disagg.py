@@ -82,3 +82,9 @@ def test_disjoint_pools_trainer_tp2_to_rollout_tp2_by_peer_stores():
     a, b = ({k: torch.from_numpy(v) for k, v in o["weights"].items()} for o in ro)
     assert all(torch.isfinite(v).all() for v in a.values())
     assert not torch.equal(a["layers.0.qkv"], b["layers.0.qkv"]) and torch.equal(a["final_norm"], b["final_norm"])
+
+
+def test_disjoint_pools_trainer_tp2_broadcast_arm():
+    out = run_distributed(_worker, 4, "broadcast", 2, 2, 2, os.getpid() % 10000 + 4, timeout=600)
+    ro = [o for o in out if o["role"] == "rollout"]
+    assert len(ro) == 2 and all(o["version"] == 3 for o in ro)
