@@ -117,7 +117,9 @@ def padded_expert_layout(expert_of_row: torch.Tensor, num_experts: int, align: i
     position ``i``, ``tile_expert`` (int32, one entry per ``align`` rows) names each tile's expert or -1,
     ``expert_rows`` (int32 ``[E + 1]``) are the padded group boundaries."""
     R, dev = expert_of_row.numel(), expert_of_row.device
-    counts = torch.bincount(expert_of_row, minlength=num_experts)
+    # (not torch.bincount: it reads the maximum back to size its output, a host sync that also forbids graph capture)
+    counts = torch.zeros(num_experts, dtype=torch.int64, device=dev).index_add_(
+        0, expert_of_row, torch.ones(R, dtype=torch.int64, device=dev))
     padded = (counts + (align - 1)) // align * align
     ends_pad = torch.cumsum(padded, 0)
     offs_pad = ends_pad - padded
@@ -133,12 +135,20 @@ def padded_expert_layout(expert_of_row: torch.Tensor, num_experts: int, align: i
     return order, dest, cap, tile_expert, expert_rows
 
 
-def grouped_swiglu_mlp(x, expert_of_row, w1, w2):
+def grouped_swiglu_mlp(x, expert_of_row, w1, w2, skip_foreign: bool = False):
     """SwiGLU expert MLPs for rows ``x [R, H]`` with (local) expert ids ``expert_of_row [R]``, in the ORIGINAL row
     order: rows are scattered into the padded expert-sorted buffer, the two grouped GEMMs (one launch each for all
-    experts) and the activation run on it, and the rows are gathered back.  ``w1 [E, 2F, H]``, ``w2 [E, H, F]``."""
+    experts) and the activation run on it, and the rows are gathered back.  ``w1 [E, 2F, H]``, ``w2 [E, H, F]``.
+    With ``skip_foreign`` rows whose id is outside ``[0, E)`` (experts that live on another rank) are parked in an
+    extra bucket whose tiles are marked unused: they cost no math and come back as zeros."""
     E = w1.shape[0]
-    order, dest, cap, tile_expert, expert_rows = padded_expert_layout(expert_of_row, E)
+    if skip_foreign:
+        eo = torch.where((expert_of_row >= 0) & (expert_of_row < E), expert_of_row, torch.full_like(expert_of_row, E))
+        order, dest, cap, tile_expert, expert_rows = padded_expert_layout(eo, E + 1)
+        tile_expert = torch.where(tile_expert == E, torch.full_like(tile_expert, -1), tile_expert)
+        expert_rows = expert_rows[:E + 1].contiguous()
+    else:
+        order, dest, cap, tile_expert, expert_rows = padded_expert_layout(expert_of_row, E)
     xp = x.new_zeros(cap, x.shape[1]).index_copy(0, dest, x.index_select(0, order))
     a = ops.swiglu(ops.grouped_linear(xp, w1, tile_expert, expert_rows))
     yp = ops.grouped_linear(a, w2, tile_expert, expert_rows)

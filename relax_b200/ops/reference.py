@@ -171,7 +171,7 @@ def grouped_linear(x, w, tile_expert, expert_rows):
     for e in range(w.shape[0]):
         a, b = bounds[e], bounds[e + 1]
         parts.append(x[a:b] @ w[e].t().to(x.dtype))
-    tail = x.new_zeros(x.shape[0] - bounds[-1], w.shape[1]) + 0.0 * w.sum().to(x.dtype)
+    tail = x.new_zeros(x.shape[0] - bounds[w.shape[0]], w.shape[1]) + 0.0 * w.sum().to(x.dtype)
     return torch.cat(parts + [tail]) if parts else y
 
 

@@ -45,7 +45,9 @@ class ColocateConfig:
     trainer_tp: int = 1
     trainer_cp: int = 1
     trainer_pp: int = 1
+    trainer_ep: int = 1                  # expert parallelism of the trainer (divides dp x cp; experts keep TP 1)
     rollout_tp: int = 1
+    rollout_ep: int = 1                  # ranks of one engine that split the experts (attention replicated)
     rollout_batch_size: int = 8          # prompts per rollout step (global)
     prompt_len: int = 64
     max_response_len: int = 64
@@ -133,23 +135,30 @@ class ColocatedGRPO:
         dp = self.world // (ttp * tcp * tpp)
         if tpp > 1 and (tcp != 1 or cfg.rollout_tp != ttp):
             raise NotImplementedError("a pipeline-parallel trainer is colocated with engines of the same TP size, without CP")
+        tep, rep_ = cfg.trainer_ep, cfg.rollout_ep
+        if tep > 1 or rep_ > 1:
+            if not (ttp == 1 and tcp == 1 and tpp == 1 and cfg.rollout_tp == 1 and tep == rep_):
+                raise NotImplementedError("expert parallelism is colocated as trainer TP 1 x EP n with engines of EP n on the same ranks")
         if self.world > 1:
-            self.ps = init_parallel_state(ParallelDims(tp=ttp, cp=tcp, dp=dp, pp=tpp))
+            self.ps = init_parallel_state(ParallelDims(tp=ttp, cp=tcp, dp=dp, pp=tpp, ep=tep))
         else:
             self.ps = single_process_state()
-        # rollout engines: consecutive blocks of rollout_tp ranks
+        # rollout engines: consecutive blocks of rollout_tp (or rollout_ep) ranks
         rtp = cfg.rollout_tp
-        self.num_engines = self.world // rtp
-        self.engine_id = self.rank // rtp
+        span = rtp * rep_
+        self.num_engines = self.world // span
+        self.engine_id = self.rank // span
         eng_group = None
-        eng_ranks = tuple(range(self.engine_id * rtp, (self.engine_id + 1) * rtp))
-        if rtp > 1:
+        eng_ranks = tuple(range(self.engine_id * span, (self.engine_id + 1) * span))
+        if span > 1:
             for e in range(self.num_engines):
-                rr = list(range(e * rtp, (e + 1) * rtp))
+                rr = list(range(e * span, (e + 1) * span))
                 g = dist.new_group(rr)
                 if e == self.engine_id:
                     eng_group = g
-        self.rollout_tp_group = GroupInfo(eng_group, eng_ranks, self.rank % rtp)
+        eng_info = GroupInfo(eng_group, eng_ranks, self.rank % span)
+        self.rollout_ep_group = eng_info if rep_ > 1 else None
+        self.rollout_tp_group = eng_info if rep_ == 1 else GroupInfo(None, (self.rank,), 0)
         self.fused_comms = []
         if cfg.fused_tp and self.device.type == "cuda":
             from ..ops import fused_comm
@@ -183,7 +192,7 @@ class ColocatedGRPO:
                                     max_prefill_tokens=cfg.max_prefill_tokens, use_cuda_graph=cfg.use_cuda_graph,
                                     memory_saver=cfg.engine_memory_saver,
                                     max_model_len=cfg.prompt_len + cfg.max_response_len,
-                                    eos_token_id=cfg.eos_token_id)
+                                    eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group)
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank
         tr_ranks = [r for r in self.ps.tp.ranks]
@@ -197,6 +206,11 @@ class ColocatedGRPO:
                 self.syncs.append((WeightSync(cfg.model, TrainerLayout(tp=ttp, pp=tpp), rtp, grid, er), tuple(er) == eng_ranks))
             self.sync = next(sy for sy, mine in self.syncs if mine)
             self._aligned = False
+        elif tep > 1:
+            self.sync = WeightSync(cfg.model, TrainerLayout(tp=1, ep=tep), 1, [self.rank], list(eng_ranks), rollout_ep=rep_,
+                                   aligned_ep_rank=self.ps.ep.rank)
+            self.syncs = [(self.sync, True)]
+            self._aligned = False        # the ranks of one engine generate the same samples: rows are re-split over DP
         else:
             self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
             self.syncs = [(self.sync, True)]
@@ -259,6 +273,11 @@ class ColocatedGRPO:
             c.close()
         self.fused_comms = []
         for a in (self.actor, self.critic):
+            for name in ("ep_comm", "cp_comm"):
+                c = getattr(a, name, None) if a is not None else None
+                if c is not None:
+                    c.close()
+                    setattr(a, name, None)
             opt = getattr(a, "optimizer", None) if a is not None else None
             if opt is not None and hasattr(opt, "close"):
                 opt.close()
@@ -478,7 +497,8 @@ class ColocatedGRPO:
         if self.world == 1 or (self._aligned and not self.cfg.train.balance_data):
             return batch
         # one contributor per engine (its tp rank 0)
-        contrib = batch if self.rollout_tp_group.rank == 0 else None
+        leader = (self.rollout_ep_group.rank == 0) if self.rollout_ep_group is not None else (self.rollout_tp_group.rank == 0)
+        contrib = batch if leader else None
         gathered = [None] * self.world
         dist.all_gather_object(gathered, contrib)
         merged: dict = {}

@@ -98,7 +98,8 @@ class Controller:
             cfg = ColocateConfig(
                 model=self.model_cfg, train=self.train_cfg, trainer_tp=a.tensor_model_parallel_size,
                 trainer_cp=a.context_parallel_size, trainer_pp=_get(a, "pipeline_model_parallel_size", 1),
-                rollout_tp=_get(a, "rollout_num_gpus_per_engine", 1),
+                trainer_ep=_get(a, "expert_model_parallel_size", 1), rollout_ep=_get(a, "engine_ep", 1),
+                rollout_tp=(_get(a, "rollout_num_gpus_per_engine", 1) if _get(a, "engine_ep", 1) == 1 else 1),
                 rollout_batch_size=a.rollout_batch_size, prompt_len=plen,
                 max_response_len=a.rollout_max_response_len, temperature=a.rollout_temperature,
                 top_p=_get(a, "rollout_top_p", 1.0), top_k=_get(a, "rollout_top_k", -1), rm_type=a.rm_type or "parity",

@@ -102,7 +102,7 @@ class RolloutEngine:
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
                  use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
                  decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None,
-                 weights_shared_path: Optional[str] = None):
+                 weights_shared_path: Optional[str] = None, ep: Optional[GroupInfo] = None):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
@@ -112,8 +112,15 @@ class RolloutEngine:
             memory_saver = self.device.type == "cuda" and os.environ.get("RELAX_B200_MEMORY_SAVER", "1") == "1"
         self.memory_saver = bool(memory_saver)
         self._kv_buf = None
+        # expert parallelism inside one engine: every rank of ``ep`` runs the whole batch (attention replicated),
+        # holds ``num_experts / ep`` experts and the experts' partial outputs are summed over the group
+        self.ep = ep if (ep is not None and ep.size > 1) else None
+        if self.ep is not None and self.tp.size > 1:
+            raise NotImplementedError("an engine is tensor-parallel or expert-parallel, not both")
         self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype,
+                                      ep_size=self.ep.size if self.ep else 1, ep_rank=self.ep.rank if self.ep else 0,
                                       memory_saver=self.memory_saver, shared_path=weights_shared_path)
+        self.weights.ep_group = self.ep
         self.block_size = block_size
         self.bm = BlockManager(num_kv_blocks, block_size)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens

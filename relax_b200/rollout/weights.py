@@ -85,6 +85,7 @@ class RolloutWeights:
                                       "trainer-side (SFT, log-prob evaluation) for now")
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank
+        self.ep_group: Optional[GroupInfo] = None     # the engine's expert-parallel group (set by the engine when ep > 1)
         self.device, self.dtype = torch.device(device), dtype
         self.shapes, self.offsets, self.numel = rollout_layout(cfg, tp_size, ep_size)
         # CPU only: back the buffer by a shared-memory file so that other processes can map and write it (the CPU
@@ -164,19 +165,19 @@ class RolloutWeights:
                 if pre + "shared_gate" in p:
                     sh = sh * torch.sigmoid(ops.linear(x, p[pre + "shared_gate"]).float())
                 out += sh
+            # every routed (token, slot) pair through the grouped expert GEMMs in one go: rows of experts that live on
+            # another EP rank are parked (no math), the per-token sum over the k slots applies the gate weights
+            from ..models.moe import grouped_swiglu_mlp
+
             el = p[pre + "experts_gate_up"].shape[0]
-            e0 = self.ep_rank * el
-            for e in range(el):
-                m = (idx == e0 + e)
-                rows = m.any(-1).nonzero()[:, 0]
-                if rows.numel() == 0:
-                    continue
-                a = ops.swiglu(ops.linear(x[rows], p[pre + "experts_gate_up"][e]))
-                y = ops.linear(a, p[pre + "experts_down"][e]).float()
-                out.index_add_(0, rows, y * (w * m)[rows].sum(-1, keepdim=True))
-            return out.to(x.dtype), self.ep_size > 1
+            T, k = idx.shape
+            rows = x.repeat_interleave(k, 0)                        # row t*k + j = token t, slot j
+            y = grouped_swiglu_mlp(rows, idx.reshape(-1) - self.ep_rank * el, p[pre + "experts_gate_up"],
+                                   p[pre + "experts_down"], skip_foreign=True)
+            out += (y.float().view(T, k, -1) * w.float().unsqueeze(-1)).sum(1)
+            return out.to(x.dtype), (self.ep_group if self.ep_size > 1 else None)
         a = ops.linear_swiglu(x, p[pre + "gate_up"])
-        return ops.linear(a, p[pre + "down"]), tp.size > 1
+        return ops.linear(a, p[pre + "down"]), (tp if tp.size > 1 else None)
 
     def _fused(self, tp: GroupInfo, rows: int, n: int):
         """The symmetric-memory communicator of ``tp`` when the fused GEMM + all-reduce + residual +
@@ -212,9 +213,9 @@ class RolloutWeights:
         if comm is not None and (pre + "router") not in p:
             a = ops.linear_swiglu(x, p[pre + "gate_up"])
             return comm.gemm_ar_add_rmsnorm(a, p[pre + "down"], h, next_norm, cfg.rms_norm_eps)
-        m, need_ar = self._mlp(i, x, tp)
-        if need_ar:
-            m = self._allreduce(m, tp)
+        m, reduce_over = self._mlp(i, x, tp)
+        if reduce_over is not None:       # partial sums: over TP ranks (dense MLP) or over EP ranks (each holds some experts)
+            m = self._allreduce(m, reduce_over)
         x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
         return h, x
 

@@ -12,6 +12,7 @@ reference log-probs -> old-policy log-probs -> advantages -> optimizer steps.
 from __future__ import annotations
 
 import math
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
@@ -100,6 +101,10 @@ class TrainActor:
         self.ps = ps or single_process_state()
         self.device = torch.device(device)
         self.model = GPTModel(model_cfg, self.ps, device=device, seed=seed, recompute=cfg.recompute)
+        self.ep_comm = None
+        if (self.device.type == "cuda" and self.ps.ep.size > 1 and model_cfg.is_moe
+                and os.environ.get("RELAX_B200_EP_PEER", "1") == "1"):
+            self._attach_ep_comm()
         if cfg.lora is not None:
             from .lora import apply_lora
 
@@ -130,6 +135,25 @@ class TrainActor:
             self.backup("ref", to_host=cfg.ref_on_host)
             if cfg.ref_on_host and self.device.type == "cuda":
                 torch.cuda.synchronize()
+
+    def _attach_ep_comm(self):
+        """Expert-parallel dispatch / combine by peer stores over NVLink (parallel/ep_peer.py) when the whole EP group
+        sits on this node; otherwise the layers keep the NCCL all-to-all.  One communicator serves every MoE layer."""
+        import socket
+
+        from ..models.moe import MoEMLP
+        from ..parallel.ep_peer import EPComm
+
+        g = self.ps.ep
+        hosts = [None] * g.size
+        dist.all_gather_object(hosts, socket.gethostname(), group=g.group)
+        if len(set(hosts)) != 1:
+            return
+        rows = self.cfg.max_tokens_per_gpu * self.mcfg.moe_top_k * 2      # room for an uneven routing
+        self.ep_comm = EPComm(g, self.device, rows, self.mcfg.hidden_size, max_experts=max(512, self.mcfg.num_experts))
+        for mod in self.model.modules():
+            if isinstance(mod, MoEMLP):
+                mod.ep_comm = self.ep_comm
 
     # ------------------------------------------------------------------ tagged weights
     def _flatten_params(self):

@@ -47,7 +47,7 @@ class WeightSync:
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int,
                  trainer_ranks: Sequence[int], rollout_ranks: Sequence[int], rollout_ep: int = 1,
-                 group=None, post_hook=None):
+                 group=None, post_hook=None, aligned_ep_rank: Optional[int] = None):
         self.cfg = cfg
         # ``post_hook(name, tensor) -> tensor`` runs on every rollout tensor after the copy (quantisation round trip)
         self.post_hook = post_hook
@@ -58,6 +58,9 @@ class WeightSync:
         else:
             self.trainer_ranks = {(0, i): r for i, r in enumerate(trainer_ranks)}
         self.rollout_ranks = list(rollout_ranks)
+        # expert-parallel trainer colocated with an expert-parallel engine on the same ranks (TP 1, equal EP): every
+        # rank holds all dense weights and its own experts on both sides, so its whole share is a local copy
+        self.aligned_ep_rank = aligned_ep_rank
         self.me = dist.get_rank() if dist.is_initialized() else 0
         self.group = group
         self.last_ms = 0.0
@@ -65,6 +68,10 @@ class WeightSync:
 
     def _pairs(self):
         pairs: dict = {}
+        if self.aligned_ep_rank is not None:
+            k = self.aligned_ep_rank
+            mine = [b for b in self.plan if (".experts." not in b.src_name) or (b.src_rank == k and b.dst_rank == k)]
+            return {(self.me, self.me): mine}
         for b in self.plan:
             s, d = self.trainer_ranks[(b.src_stage, b.src_rank)], self.rollout_ranks[b.dst_rank]
             pairs.setdefault((s, d), []).append(b)

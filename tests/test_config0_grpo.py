@@ -86,3 +86,27 @@ def test_grpo_pipeline_parallel_trainer_two_stages():
     out = run_distributed(_pp_worker, 2, timeout=600)
     assert out[0][0] == out[1][0]                 # both stages report the same loss / grad norm
     assert abs(out[0][1] - out[1][1]) < 1e-6      # both engines hold the same full set of weights
+
+
+def _ep_worker(rank, world):
+    """Colocated GRPO of a mixture-of-experts model with expert parallelism on both sides: trainer TP1 x EP2 (the two
+    ranks are also the two data-parallel replicas), one engine of EP2 on the same ranks."""
+    import dataclasses
+
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.colocate import ColocatedGRPO
+
+    cfg = dataclasses.replace(_make_cfg(1, 1), model=get_config("tiny-moe"), trainer_ep=2, rollout_ep=2)
+    run = ColocatedGRPO(cfg)
+    assert run.ps.ep.size == 2 and run.engine.ep is not None and run.num_engines == 1
+    assert run.engine.weights.p["layers.0.experts_gate_up"].shape[0] == cfg.model.num_experts // 2
+    hist = [run.step() for _ in range(2)]
+    for m in hist:
+        assert math.isfinite(m["loss"]) and m["grad_norm"] > 0
+        assert m["train_rollout_logprob_abs_diff"] < 1e-4      # the EP engine computes what the EP trainer computes
+    return [(m["loss"], m["grad_norm"]) for m in hist]
+
+
+def test_grpo_expert_parallel_trainer_and_engine():
+    out = run_distributed(_ep_worker, 2, timeout=600)
+    assert out[0] == out[1]

@@ -152,3 +152,18 @@ def test_windowed_decode_equals_host_driven_loop():
     batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [len(r.output) for r in res]}
     for r, l in zip(res, actor.compute_log_prob(batch)["log_probs"]):
         assert torch.allclose(torch.tensor(r.logprobs), l, atol=1e-4)
+
+
+def test_moe_engine_logprobs_match_trainer_forward():
+    """A mixture-of-experts model in the rollout engine (grouped expert path, rows of foreign experts parked) returns
+    the log-probs the trainer computes for the same tokens."""
+    cfg = get_config("tiny-moe")
+    actor = TrainActor(cfg, TrainConfig(), seed=0, with_optimizer=False)
+    eng = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8)
+    WeightSync(cfg, TrainerLayout(), 1, [0], [0]).update_weights(dict(actor.named_local_params()), eng.weights, eng, 1)
+    torch.manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (6, 9)]
+    res = eng.generate(prompts, SamplingParams(max_new_tokens=7))
+    batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [len(r.output) for r in res]}
+    for r, l in zip(res, actor.compute_log_prob(batch)["log_probs"]):
+        assert torch.allclose(torch.tensor(r.logprobs), l, atol=1e-4)
