@@ -77,6 +77,110 @@ class Controller:
         self.start_rollout_id = dist_ckpt.resolve_start_rollout_id(args.load, args.start_rollout_id)
         self.runner = self._build_runner()
         self._maybe_resume()
+        self._setup_health()
+
+    # ------------------------------------------------------------------ health / two-tier recovery
+    def _setup_health(self):
+        """``--use-fault-tolerance``: a health registry for the roles of this process and the manager that maps a
+        failure to a restart tier (relax/core/controller.py:977-1257): stateless roles restart in place (engine
+        re-created from the trainer's weights), actor / rollout failures - or a role that keeps failing - restart
+        globally (latest checkpoint reloaded, engine flushed and re-synchronised), at most ``--max-global-restart``
+        times before the run stops with an error."""
+        a = self.args
+        self.health = self.health_mgr = None
+        self.restarts = {"inplace": 0, "global": 0}
+        self._fatal = None
+        if not _get(a, "use_fault_tolerance", False):
+            return
+        from ..health.monitor import HealthManager, HealthRegistry
+
+        self.health = HealthRegistry(heartbeat_timeout=float(_get(a, "rollout_health_check_timeout", 30.0)) * 4)
+        for role in ("actor", "rollout"):
+            self.health.register(role)
+        self.health_mgr = HealthManager(self.health, self._restart_inplace, self._restart_global, self._on_fatal,
+                                        max_global_restart=int(_get(a, "max_global_restart", 3)))
+
+    def _recover_engine(self):
+        eng = getattr(self.runner, "engine", None)
+        if eng is not None:
+            eng.abort_all()
+            eng.flush_cache()
+        q = getattr(self.runner, "queue", None)
+        if q is not None:
+            for part in list(q.get_partition_list()):
+                q.clear_partition(part)
+        if hasattr(self.runner, "sync_weights"):
+            self.runner.sync_weights()
+
+    def _restart_inplace(self, role: str):
+        self.restarts["inplace"] += 1
+        self._recover_engine()
+
+    def _restart_global(self, role: str):
+        """Back to the last durable state: the newest checkpoint under ``--save`` / ``--load`` when there is one (the
+        step counter follows it), else the weights in memory; then the engine is rebuilt from them."""
+        a, actor = self.args, self._actor()
+        self.restarts["global"] += 1
+        src = next((d for d in (_get(a, "save", None), _get(a, "load", None))
+                    if d and os.path.isdir(d) and dist_ckpt.read_latest_iteration(d) is not None), None)
+        if src is not None and actor is not None:
+            it = dist_ckpt.read_latest_iteration(src)
+            dist_ckpt.load_checkpoint(src, self.model_cfg, actor.ps, actor.model, actor.optimizer)
+            if hasattr(self.runner, "rollout_id"):
+                self.runner.rollout_id = it + 1
+        self._recover_engine()
+
+    def _on_fatal(self, msg: str):
+        self._fatal = msg
+
+    def _agree_failed(self, failed: bool) -> bool:
+        """A failure on any rank restarts every rank (the roles are SPMD)."""
+        if not dist.is_initialized() or dist.get_world_size() == 1:
+            return failed
+        dev = self.device if str(self.device).startswith("cuda") and dist.get_backend() == "nccl" else "cpu"
+        t = torch.tensor([1 if failed else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return bool(int(t[0]))
+
+    def _guarded_step(self):
+        """One runner step under the health manager.  Returns the step's metrics, or None after a recovery (the
+        caller re-reads the step counter).  Only failures raised on the host between collectives can be recovered;
+        a rank that dies inside a collective ends the job through the process-group timeout."""
+        if self.health is None:
+            return self.runner.step()
+        multi = dist.is_initialized() and dist.get_world_size() > 1
+        # between steps: a failure that any rank's monitors reported since the last step (an engine marked unhealthy, a
+        # role that stopped beating) is agreed on by all ranks BEFORE anyone launches the next step, and all restart
+        if self._agree_failed(bool(self.health.unhealthy())):
+            if not self.health.unhealthy():
+                self.health.report_error("rollout", "failure reported by another rank")
+            return self._recover(None)
+        err = None
+        try:
+            m = self.runner.step()
+        except Exception as e:  # noqa: BLE001 - any role failure takes the recovery path
+            import traceback
+
+            where = "".join(traceback.format_tb(e.__traceback__))
+            role = "rollout" if ("generate" in where or "rollout" in where and "train" not in where) else "actor"
+            self.health.report_error(role, repr(e))
+            if multi:
+                # the other ranks are inside this step's collectives and cannot be called back from here: the job ends
+                # (its launcher restarts it from the checkpoint); only a single-process job recovers in place
+                raise
+            err = e
+        if err is None:
+            step = getattr(self.runner, "rollout_id", 0)
+            for role in ("actor", "rollout"):
+                self.health.heartbeat(role, step)
+            return m
+        return self._recover(err)
+
+    def _recover(self, err):
+        self.health_mgr.check_once()
+        if self._fatal is not None:
+            raise RuntimeError(f"giving up after {self.health_mgr.global_restarts} global restarts: {self._fatal}") from err
+        return None
 
     # ------------------------------------------------------------------ mode
     def _pick_mode(self) -> str:
@@ -279,7 +383,10 @@ class Controller:
         ref_every = _get(a, "ref_update_interval", None)
         while rid < a.num_rollout and not self._stop:
             t0 = time.perf_counter()
-            m = self.runner.step()
+            m = self._guarded_step()
+            if m is None:                     # recovered from a failure: go on from where the restart left the job
+                rid = getattr(self.runner, "rollout_id", rid)
+                continue
             actor = self._actor()
             if ref_every and actor is not None and "ref" in actor.snapshots and (rid + 1) % ref_every == 0:
                 # --ref-update-interval: the reference follows the policy every N rollouts
