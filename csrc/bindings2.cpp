@@ -108,6 +108,17 @@ void decode_advance(torch::Tensor tok_new, torch::Tensor lp_new, torch::Tensor t
                           cur_stream()),
         "rb_decode_advance");
 }
+// Weight-streaming decode GEMM; returns false when the shape is outside its range (the caller uses the split-K path).
+bool decode_gemm(torch::Tensor x, torch::Tensor W, torch::Tensor y, bool swiglu, int64_t splits, torch::Tensor err) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && y.scalar_type() == at::kBFloat16, "bf16 only");
+  TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && x.stride(1) == 1 && W.stride(1) == 1 && y.is_contiguous(), "row-major operands");
+  const int rc = rb_decode_gemm(x.data_ptr(), W.data_ptr(), y.data_ptr(), (int)x.size(0), (int)W.size(0), (int)x.size(1),
+                                (int)x.stride(0), (int)W.stride(0), swiglu, (int)splits, err.data_ptr<int>(), cur_stream());
+  if (rc == -20) return false;
+  check(rc, "rb_decode_gemm");
+  return true;
+}
 void grouped_gemm_fwd(torch::Tensor X, torch::Tensor W, torch::Tensor Y, torch::Tensor tile_expert, torch::Tensor err) {
   const c10::cuda::CUDAGuard guard(X.device());
   TORCH_CHECK(X.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16 && Y.scalar_type() == at::kBFloat16, "bf16 only");
@@ -199,6 +210,7 @@ void register_more(pybind11::module_& m) {
   m.def("sample", &sample);
   m.def("sample_v2", &sample_v2);
   m.def("decode_advance", &decode_advance);
+  m.def("decode_gemm", &decode_gemm);
   m.def("grouped_gemm_fwd", &grouped_gemm_fwd);
   m.def("grouped_gemm_dgrad", &grouped_gemm_dgrad);
   m.def("grouped_gemm_wgrad", &grouped_gemm_wgrad);
