@@ -260,8 +260,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--num-iters-per-train-update": (_R, "one optimizer pass per rollout batch"),
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
-    "--use-rollout-routing-replay": (_R, "the rollout engine does not return routed experts (R3); use --use-routing-replay (R2)"),
-    "--sglang-enable-return-routed-experts": (_R, "the rollout engine does not return routed experts"),
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
     "--use-rollout-entropy": (_R, "the rollout engine returns log-probs only"),
     "--rollout-external": (_R, "external rollout engines are not supported"),
@@ -543,6 +541,7 @@ def train_config_from_args(a):
         enable_mtp_training=a.enable_mtp_training, mtp_loss_scaling_factor=a.mtp_loss_scaling_factor,
         mtp_only_training=a.mtp_only_training,
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
+        use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
         freeze_params_name_list=getattr(a, "freeze_params_name_list", None),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
         ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

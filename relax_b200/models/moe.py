@@ -69,12 +69,17 @@ class RoutingReplay:
                     cls.per_sample[(layer_idx, sid)] = idx[o:o + n].detach().clone()
                     o += n
                 return idx
-            parts = []
+            parts, o = [], 0
             for sid, n in zip(ids, lens):
                 rec = cls.per_sample.get((layer_idx, sid))
+                if rec is not None and rec.shape[0] == n - 1:
+                    # recorded by the rollout engine: it never feeds a sample's last token, whose row keeps the
+                    # router's own choice (no loss is taken at that position)
+                    rec = torch.cat([rec.to(idx.device), idx[o + n - 1:o + n]])
                 if rec is None or rec.shape[0] != n:
                     raise ValueError(f"no recorded routing for sample {sid} at layer {layer_idx}")
                 parts.append(rec.to(idx.device))
+                o += n
             tail = idx[sum(lens):]                       # padding rows keep the router's own choice
             return torch.cat(parts + [tail]) if parts else idx
         if cls.mode == "record":

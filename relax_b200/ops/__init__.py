@@ -159,7 +159,7 @@ def qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache=None, v_ca
 
 def linear_swiglu(x, w):
     """``swiglu(x @ w.T)`` with ``w`` = [gate; up]; fused split-K reduction + activation for decode shapes."""
-    if _use_cuda(x) and x.shape[0] <= 128 and not torch.is_grad_enabled() and x.dim() == 2:
+    if _use_cuda(x) and x.shape[0] <= 256 and not torch.is_grad_enabled() and x.dim() == 2:
         return _cuda().linear_swiglu_skinny(x, w)
     return swiglu(linear(x, w))
 

@@ -235,6 +235,44 @@ def bench_train_step(args, pk):
         print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:96]}")
 
 
+def bench_moe(args, pk):
+    """Grouped expert GEMMs of a Qwen3-30B-A3B layer on one EP rank (16 local experts, hidden 2048, expert FFN 768):
+    one launch for all experts against a loop of library GEMMs over the same expert-sorted rows."""
+    from .. import ops
+    from ..models.moe import padded_expert_layout
+
+    dev, E, H, F = "cuda", 16, 2048, 768
+    rows = args.tokens * 8 // 8                      # tokens x top-8 spread over 8 EP ranks
+    g = torch.Generator(device=dev).manual_seed(0)
+    e_of = torch.randint(0, E, (rows,), device=dev, generator=g)
+    x = torch.randn(rows, H, device=dev, generator=g).bfloat16()
+    w1 = (torch.randn(E, 2 * F, H, device=dev, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn(E, H, F, device=dev, generator=g) * 0.02).bfloat16()
+    order, dest, cap, tile_expert, expert_rows = padded_expert_layout(e_of, E)
+    xp = x.new_zeros(cap, H).index_copy(0, dest, x[order])
+    counts = torch.bincount(e_of, minlength=E).tolist()
+    xs = x[order]
+
+    def ours():
+        with torch.no_grad():
+            a = ops.swiglu(ops.grouped_linear(xp, w1, tile_expert, expert_rows))
+            return ops.grouped_linear(a, w2, tile_expert, expert_rows)
+
+    def lib():
+        o, outs = 0, []
+        for e, n in enumerate(counts):
+            h = torch.matmul(xs[o:o + n], w1[e].t())
+            a = torch.nn.functional.silu(h[:, :F]) * h[:, F:]
+            outs.append(torch.matmul(a, w2[e].t()))
+            o += n
+        return outs
+
+    t, tl = _timeit(ours, args.iters, args.warmup), _timeit(lib, args.iters, args.warmup)
+    fl = 2 * rows * (2 * F * H + H * F) / 1e9
+    print(f"== MoE expert MLPs, {rows} routed rows over {E} local experts (H {H}, F {F})")
+    print(f"  grouped GEMMs + SwiGLU (3 launches)   {t:7.3f} ms {pk.flops(fl / t)} | loop of library GEMMs ({3 * E} launches) {tl:7.3f} ms")
+
+
 def bench_decode_step(args, pk):
     """One whole decode step of the rollout engine (all layers + LM head + sampling + device-side advance) as the
     engine runs it: a CUDA graph replayed back to back.  Reports ms per step against the bytes a step must read
@@ -292,7 +330,7 @@ def bench_decode_step(args, pk):
         print(f"  {r.device_time_total / 1000:8.3f} ms {100 * r.device_time_total / tot:5.1f}%  x{r.count:4d}  {r.key[:110]}")
 
 
-SECTIONS = {"decode_step": bench_decode_step, "gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
+SECTIONS = {"decode_step": bench_decode_step, "moe": bench_moe, "gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "attention": bench_attention, "decode": bench_decode, "lm_head": bench_lm_head,
             "elementwise": bench_elementwise, "train_step": bench_train_step}
 
 

@@ -182,7 +182,7 @@ def linear(x, w, bias=None):
         raise TypeError("the sm_100a GEMM takes bf16/fp16 inputs")
     if w.dim() != 2:
         raise ValueError("weight must be 2-D")
-    if x2.shape[0] <= 128 and not (torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad)) \
+    if x2.shape[0] <= 256 and not (torch.is_grad_enabled() and (x2.requires_grad or w.requires_grad)) \
             and w.is_contiguous() and w.shape[0] % 64 == 0:
         y = matmul_nt_skinny(x2, w, bias)
         bias = None
@@ -197,6 +197,22 @@ def linear(x, w, bias=None):
     return y.reshape(*shp[:-1], y.shape[-1])
 
 
+_DECODE_GEMM = os.environ.get("RELAX_B200_DECODE_GEMM", "1") == "1"
+
+
+def _decode_gemm(x, w, swiglu: bool):
+    """Weight-streaming decode GEMM (csrc/gemm_decode_sm100.cu) when the shape is in its range, else None."""
+    if not _DECODE_GEMM or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] > 256:
+        return None
+    if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16:
+        return None
+    N = w.shape[0]
+    out = torch.empty(x.shape[0], N // 2 if swiglu else N, dtype=x.dtype, device=x.device)
+    if _load().decode_gemm(x, w, out, swiglu, 0, err_flag(x.device)):
+        return out
+    return None
+
+
 def matmul_nt_skinny(x, w, bias=None, residual=None):
     """x[M, K] @ w[N, K]^T for decode (a few hundred rows at most): when the N tiles alone cannot fill the SMs the
     reduction dimension is split across CTAs (fp32 partials in a workspace, one small reduce
@@ -205,6 +221,10 @@ def matmul_nt_skinny(x, w, bias=None, residual=None):
     M, K = x.shape
     N = w.shape[0]
     C = _load()
+    if bias is None and residual is None:
+        y = _decode_gemm(x, w, False)
+        if y is not None:
+            return y
     splits, bn = C.gemm_splitk_plan(M, N, K)
     out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     if splits <= 1:
@@ -222,6 +242,9 @@ def linear_swiglu_skinny(x, w):
     M, K = x.shape
     N = w.shape[0]
     C = _load()
+    y = _decode_gemm(x, w, True)
+    if y is not None:
+        return y
     splits, bn = C.gemm_splitk_plan(M, N, K)
     if splits <= 1 or x.dtype != torch.bfloat16 or (N // 2) % 4:
         return swiglu(linear(x, w))

@@ -192,7 +192,8 @@ class ColocatedGRPO:
                                     max_prefill_tokens=cfg.max_prefill_tokens, use_cuda_graph=cfg.use_cuda_graph,
                                     memory_saver=cfg.engine_memory_saver,
                                     max_model_len=cfg.prompt_len + cfg.max_response_len,
-                                    eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group)
+                                    eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
+                                    return_routed_experts=cfg.train.use_rollout_routing_replay)
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank
         tr_ranks = [r for r in self.ps.tp.ranks]
@@ -328,6 +329,8 @@ class ColocatedGRPO:
             s.rollout_log_probs = list(r.logprobs)
             s.weight_versions = sorted(set(r.weight_versions))
             s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
+            if r.routed_experts:
+                s.rollout_routed_experts = r.routed_experts
             if self.codec is not None:
                 if self.cfg.stop_strings:
                     from ..data.tokenizer import cut_at_stop_strings

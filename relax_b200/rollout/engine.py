@@ -52,6 +52,9 @@ class Request:
     finish_reason: Optional[str] = None
     weight_versions: list = field(default_factory=list)
     cached_tokens: int = 0
+    # with ``return_routed_experts``: per context position that was fed to the model, the expert ids every MoE layer
+    # chose - a list of ``[L_moe, k]`` int lists (positions 0 .. num_tokens - 2; the last token is never fed)
+    routed_experts: list = field(default_factory=list)
     t_arrive: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
@@ -102,7 +105,8 @@ class RolloutEngine:
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
                  use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
                  decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None,
-                 weights_shared_path: Optional[str] = None, ep: Optional[GroupInfo] = None):
+                 weights_shared_path: Optional[str] = None, ep: Optional[GroupInfo] = None,
+                 return_routed_experts: bool = False):
         self.cfg = cfg
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
@@ -121,6 +125,7 @@ class RolloutEngine:
                                       ep_size=self.ep.size if self.ep else 1, ep_rank=self.ep.rank if self.ep else 0,
                                       memory_saver=self.memory_saver, shared_path=weights_shared_path)
         self.weights.ep_group = self.ep
+        self.return_routed_experts = bool(return_routed_experts) and cfg.is_moe
         self.block_size = block_size
         self.bm = BlockManager(num_kv_blocks, block_size)
         self.max_running, self.max_prefill_tokens = max_running, max_prefill_tokens
@@ -375,9 +380,16 @@ class RolloutEngine:
         if leaders:
             t, pos_t, cu_t, slots_t, last_t = self._stage([(toks, torch.int64), (pos, torch.int64), (cu, torch.int32),
                                                            (slots, torch.int64), (last_rows, torch.int64)])
+            if self.return_routed_experts:
+                self.weights.routing_capture = []
             logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
                                                   max_seqlen=max(b - a for a, b in zip(cu, cu[1:])))
             self.stats["prefill_tokens"] += len(toks)
+            if self.return_routed_experts:
+                routed = torch.stack(self.weights.routing_capture, 1).tolist()      # [T][L_moe][k]
+                self.weights.routing_capture = None
+                for r, a, b in zip(leaders, cu, cu[1:]):
+                    r.routed_experts = routed[a:b]
         row_of = {id(r): i for i, r in enumerate(leaders)}
         # followers copy the leader's partially filled tail block and reuse its last-token logits
         rows = []
@@ -391,6 +403,8 @@ class RolloutEngine:
                         self.kv[:, :, r.blocks[j]] = self.kv[:, :, lead.blocks[j]]
                 self.stats["cached_tokens"] += len(r.prompt)
                 rows.append(row_of[id(lead)])
+                if self.return_routed_experts:
+                    r.routed_experts = [list(x) for x in lead.routed_experts[:len(r.prompt)]]
             else:
                 rows.append(row_of[id(r)])
         sel = logits[torch.tensor(rows, device=dev)] if rows != list(range(len(leaders))) else logits
@@ -421,7 +435,14 @@ class RolloutEngine:
             ([r.num_tokens for r in reqs], torch.int32),
             ([r.blocks[(r.num_tokens - 1) // bs] * bs + (r.num_tokens - 1) % bs for r in reqs], torch.int64),
             (bt_rows, torch.int32)])
+        if self.return_routed_experts:
+            self.weights.routing_capture = []
         logits = self.weights.forward_decode(tok, pos, bt, ctx, slots, self.kv, self.tp)
+        if self.return_routed_experts:
+            routed = torch.stack(self.weights.routing_capture, 1).tolist()
+            self.weights.routing_capture = None
+            for r, x in zip(reqs, routed):
+                r.routed_experts.append(x)
         self.stats["decode_tokens"] += B
         self._sample_and_append(reqs, logits)
 
@@ -475,8 +496,19 @@ class RolloutEngine:
         counter = d["counter"]
         d["counter"] = counter[:1]
 
+        if self.return_routed_experts:
+            nl, k = len(self.weights.moe_layers), self.cfg.moe_top_k
+            d["out_routed"] = torch.zeros(W, bucket, nl, k, dtype=torch.int32, device=dev)
+            st["host_routed"] = torch.zeros(W, bucket, nl, k, dtype=torch.int32, pin_memory=cuda)
+
         def run():
+            if self.return_routed_experts:
+                self.weights.routing_capture = []
             logits = self.weights.forward_decode(d["tok"], d["pos"], d["bt"], d["ctx"], d["slots"], self.kv, self.tp)
+            if self.return_routed_experts:      # ring slot = the step counter, read on the device (before it advances)
+                routed = torch.stack(self.weights.routing_capture, 1).to(torch.int32)
+                self.weights.routing_capture = None
+                d["out_routed"].index_copy_(0, d["counter"].long().clamp_max(W - 1), routed.unsqueeze(0))
             tok, lp = ops.sample(logits[:, :self.cfg.vocab_size], d["temp"], d["topk"], d["topp"], d["u"])
             ops.decode_advance(tok, lp, d, bs)
 
@@ -568,6 +600,8 @@ class RolloutEngine:
                 st["run"]()
         st["host_tok"][:W].copy_(d["out_tok"][:W], non_blocking=True)
         st["host_lp"][:W].copy_(d["out_lp"][:W], non_blocking=True)
+        if self.return_routed_experts:
+            st["host_routed"][:W].copy_(d["out_routed"][:W], non_blocking=True)
         if self.device.type == "cuda":
             torch.cuda.current_stream().synchronize()    # also completes the upload: the mirror may be rewritten
         tok_w, lp_w = st["host_tok"][:W, :B].tolist(), st["host_lp"][:W, :B].tolist()
@@ -575,10 +609,14 @@ class RolloutEngine:
         self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + W * bucket * 12
         self.stats["graph_replays"] = self.stats.get("graph_replays", 0) + W
         self.stats["steps"] += W - 1
+        routed_w = st["host_routed"][:W, :B].tolist() if self.return_routed_experts else None
         for i in range(W):
             live = [(j, r) for j, r in enumerate(reqs) if r.status == "running"]
             if not live:
                 break
+            if routed_w is not None:
+                for j, r in live:
+                    r.routed_experts.append(routed_w[i][j])
             row_t, row_l = tok_w[i], lp_w[i]
             if any(row_t[j] < 0 for j, _ in live):
                 raise RuntimeError("decode window: the device stopped a row the host still considers running")

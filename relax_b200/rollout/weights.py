@@ -86,6 +86,10 @@ class RolloutWeights:
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank
         self.ep_group: Optional[GroupInfo] = None     # the engine's expert-parallel group (set by the engine when ep > 1)
+        # routing capture (R3: the trainer replays the rollout's expert choices): when a list, every MoE layer appends
+        # its top-k expert ids ``[T, k]`` of the current forward, in layer order
+        self.routing_capture: Optional[list] = None
+        self.moe_layers = [i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)]
         self.device, self.dtype = torch.device(device), dtype
         self.shapes, self.offsets, self.numel = rollout_layout(cfg, tp_size, ep_size)
         # CPU only: back the buffer by a shared-memory file so that other processes can map and write it (the CPU
@@ -159,6 +163,8 @@ class RolloutWeights:
             from ..models.moe import route_tokens
 
             w, idx, _ = route_tokens(logits, cfg, p.get(pre + "router_bias"))
+            if self.routing_capture is not None:
+                self.routing_capture.append(idx)
             out = torch.zeros_like(x, dtype=torch.float32)
             if pre + "shared_gate_up" in p and self.ep_rank == 0:     # summed over the EP ranks afterwards: one rank adds it
                 sh = ops.linear(ops.swiglu(ops.linear(x, p[pre + "shared_gate_up"])), p[pre + "shared_down"]).float()

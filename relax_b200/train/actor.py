@@ -68,6 +68,9 @@ class TrainConfig:
     # MoE: the expert choices of the old-policy forward are replayed in the training forward, so both evaluate the
     # same experts (--use-routing-replay; relax/backends/megatron/actor.py fill_routing_replay :534-641)
     use_routing_replay: bool = False
+    # R3: replay the expert choices the ROLLOUT engine made (batch field ``rollout_routed_experts``) in the old-policy
+    # and training forwards (relax/backends/sglang/routing_replay_patch.py, --use-rollout-routing-replay)
+    use_rollout_routing_replay: bool = False
     # on-policy distillation: per-token divergence between the policy and a teacher on the sampled tokens, applied to
     # the advantages as a dense penalty (relax/utils/opd/opd_utils.py apply_opd_to_advantages :1275).  The teacher's
     # log-probs come with the batch (``teacher_log_probs``, external teacher) or from the ``teacher`` weight snapshot.
@@ -277,7 +280,7 @@ class TrainActor:
         return self.cp_comm
 
     def _forward_logp(self, pb, with_entropy: bool):
-        if self.cfg.use_routing_replay and self.mcfg.is_moe:
+        if (self.cfg.use_routing_replay or self.cfg.use_rollout_routing_replay) and self.mcfg.is_moe:
             from ..models.moe import RoutingReplay
 
             RoutingReplay.set_layout(getattr(self, "_cur_ids", None), pb.total_lengths)
@@ -362,7 +365,7 @@ class TrainActor:
         """Forward-only pass; returns per-sample lists ``log_probs`` (and ``entropy``)."""
         self.switch_model(tag)
         suspended = None
-        if tag not in ("actor", "old_actor") and self.cfg.use_routing_replay and self.mcfg.is_moe:
+        if tag not in ("actor", "old_actor") and (self.cfg.use_routing_replay or self.cfg.use_rollout_routing_replay) and self.mcfg.is_moe:
             from ..models.moe import RoutingReplay
 
             suspended, RoutingReplay.mode = RoutingReplay.mode, None     # reference / teacher route for themselves
@@ -525,12 +528,23 @@ class TrainActor:
         with self.timer.span("ref_log_probs"):
             if "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
                 batch["ref_log_probs"] = self.compute_log_prob(batch, "ref")["log_probs"]
+        r3 = (cfg.use_rollout_routing_replay and self.mcfg.is_moe and batch.get("rollout_routed_experts") is not None)
+        if r3:
+            from ..models.moe import RoutingReplay
+
+            RoutingReplay.begin_record()          # clears earlier records
+            moe_layers = [i for i in range(self.mcfg.num_layers) if self.mcfg.is_moe_layer(i)]
+            for sid, routed in enumerate(batch["rollout_routed_experts"]):
+                t = torch.as_tensor(routed, dtype=torch.int64, device=dev)        # [positions, L_moe, k]
+                for m, layer in enumerate(moe_layers):
+                    RoutingReplay.per_sample[(layer, sid)] = t[:, m]
+            RoutingReplay.mode = "replay"
         with self.timer.span("old_log_probs"):
             if cfg.use_rollout_logprobs and batch.get("rollout_log_probs") is not None:
                 batch["log_probs"] = [torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch["rollout_log_probs"]]
             elif not cfg.loss.true_on_policy:
                 tag = "old_actor" if (cfg.keep_old_actor and "old_actor" in self.snapshots) else "actor"
-                replay = cfg.use_routing_replay and self.mcfg.is_moe
+                replay = cfg.use_routing_replay and self.mcfg.is_moe and not r3
                 if replay:
                     from ..models.moe import RoutingReplay
 
@@ -589,7 +603,7 @@ class TrainActor:
                 self._ci_steps += 1
             for k, v in m.items():
                 agg[k] = agg.get(k, 0) + v / int(nsteps)
-        if cfg.use_routing_replay and self.mcfg.is_moe:
+        if (cfg.use_routing_replay or r3) and self.mcfg.is_moe:
             from ..models.moe import RoutingReplay
 
             RoutingReplay.end()

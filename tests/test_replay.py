@@ -80,3 +80,57 @@ def test_routing_replay_in_the_trainer_survives_different_microbatching():
     rep_rows = {s[2] for s in seen if s[0] == "replay"}
     assert rec_rows == {45} and rep_rows == {21, 24}            # one micro-batch of 4 samples vs two steps of 2
     assert abs(m["ppo_kl"]) < 1e-6 and m["pg_clipfrac"] == 0.0
+
+
+def test_rollout_routing_replay_r3_engine_choices_drive_the_trainer():
+    """R3: the engine returns, per fed position, the experts every MoE layer chose; with ``use_rollout_routing_replay``
+    the trainer's old-policy and training forwards replay exactly those choices (a spy on the router sees the recorded
+    ids come back), both through the host-driven and the windowed decode loop."""
+    import torch
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.models.moe import RoutingReplay
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+    from relax_b200.weight_sync.plan import TrainerLayout
+    from relax_b200.weight_sync.sync import WeightSync
+
+    mcfg = get_config("tiny-moe")
+    cfg = TrainConfig(advantage_estimator="grpo", global_batch_size=4, n_samples_per_prompt=2, max_tokens_per_gpu=1024, pad_multiple=1,
+                      use_rollout_routing_replay=True, loss=LossConfig(), optim=OptimizerConfig(lr=0.0))
+    actor = TrainActor(mcfg, cfg, role="actor", seed=0)
+    for windowed in (False, True):
+        eng = RolloutEngine(mcfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, return_routed_experts=True,
+                            windowed_decode=windowed, decode_window=4)
+        WeightSync(mcfg, TrainerLayout(), 1, [0], [0]).update_weights(dict(actor.named_local_params()), eng.weights, eng, 1)
+        g = torch.Generator().manual_seed(2)
+        prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (7, 7, 9, 9)]
+        res = eng.generate(prompts, SamplingParams(max_new_tokens=6, ignore_eos=True), group_keys=[0, 0, 1, 1])
+        n_moe = len(eng.weights.moe_layers)
+        for r in res:
+            assert len(r.routed_experts) == len(r.prompt) + len(r.output) - 1
+            assert len(r.routed_experts[0]) == n_moe and len(r.routed_experts[0][0]) == mcfg.moe_top_k
+        batch = {"tokens": [r.prompt + r.output for r in res], "response_lengths": [6] * 4, "loss_masks": [[1.0] * 6] * 4,
+                 "rewards": [1.0, 0.0, 0.0, 1.0], "rollout_routed_experts": [r.routed_experts for r in res]}
+        replayed = []
+        orig = RoutingReplay.route.__func__
+
+        def spy(cls, layer, idx):
+            out = orig(cls, layer, idx)
+            replayed.append((cls.mode, layer, out.clone()))
+            return out
+
+        RoutingReplay.route = classmethod(spy)
+        try:
+            m = actor.train(0, batch)
+        finally:
+            RoutingReplay.route = classmethod(orig)
+        assert RoutingReplay.mode is None and all(mode == "replay" for mode, _, _ in replayed if mode is not None)
+        # the first replayed call of the first MoE layer covers all four samples in order: its rows are the engine's ids
+        mode, layer, out = next(x for x in replayed if x[0] == "replay")
+        m_idx = eng.weights.moe_layers.index(layer)
+        want = torch.tensor([pos[m_idx] for pos in res[0].routed_experts])
+        assert torch.equal(out[:want.shape[0]], want)
+        # same weights, same routing: the engine's log-probs are the trainer's old-policy log-probs
+        assert abs(m["ppo_kl"]) < 1e-6
