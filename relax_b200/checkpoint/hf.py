@@ -283,3 +283,41 @@ def load_hf_into_model(path: str, cfg: ModelConfig, ps, model, strict: bool = Tr
     dtype = next(model.parameters()).dtype
     full = hf_to_megatron_state(cfg, load_hf_checkpoint(path, dequantize=True, dtype=dtype))
     return load_full_state(cfg, ps, model, full, strict)
+
+
+def config_from_hf(path: str) -> ModelConfig:
+    """``config.json`` of a Hugging Face checkpoint -> :class:`ModelConfig` (the inverse of :func:`hf_config_dict`;
+    the reference cross-checks its Megatron flags against this file, relax/backends/megatron/arguments.py)."""
+    import json
+
+    with open(os.path.join(path, "config.json")) as f:
+        d = json.load(f)
+    arch = (d.get("architectures") or [""])[0]
+    heads = d["num_attention_heads"]
+    kw = dict(name=os.path.basename(os.path.normpath(path)) or "hf", num_layers=d["num_hidden_layers"], hidden_size=d["hidden_size"],
+              num_attention_heads=heads, num_query_groups=d.get("num_key_value_heads", heads),
+              head_dim=d.get("head_dim") or d["hidden_size"] // heads, ffn_hidden_size=d.get("intermediate_size", 4 * d["hidden_size"]),
+              vocab_size=d["vocab_size"], rms_norm_eps=d.get("rms_norm_eps", 1e-6), rope_theta=float(d.get("rope_theta", 1e6)),
+              tie_word_embeddings=bool(d.get("tie_word_embeddings", False)), qk_layernorm="Qwen3" in arch,
+              qkv_bias="Qwen2" in arch)
+    n_exp = d.get("num_experts") or d.get("n_routed_experts") or 0
+    if n_exp:
+        kw.update(num_experts=n_exp, moe_top_k=d.get("num_experts_per_tok", 8), moe_ffn_hidden_size=d.get("moe_intermediate_size", kw["ffn_hidden_size"]),
+                  moe_router_norm_topk_prob=bool(d.get("norm_topk_prob", True)), moe_shared_expert_ffn=d.get("shared_expert_intermediate_size", 0) or 0,
+                  moe_first_dense_layers=d.get("first_k_dense_replace", 0) or 0)
+        if d.get("scoring_func") == "sigmoid":
+            kw.update(moe_router_score="sigmoid", moe_routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)))
+    return ModelConfig(**kw)
+
+
+def load_hf_into_rollout(path: str, cfg: ModelConfig, rollout_weights) -> None:
+    """Fill a rollout engine's parameter buffer straight from a Hugging Face checkpoint (a grader or any serving-only
+    model that has no trainer): HF names -> Megatron layout -> the block-copy plan the weight sync uses."""
+    from ..weight_sync.plan import TrainerLayout, build_plan
+    from ..weight_sync.sync import apply_block
+
+    full = hf_to_megatron_state(cfg, load_hf_checkpoint(path, dequantize=True, dtype=rollout_weights.dtype))
+    for b in build_plan(cfg, TrainerLayout(1, 1, 1), rollout_weights.tp_size, rollout_weights.ep_size):
+        mine = rollout_weights.ep_rank if ".experts." in b.src_name else rollout_weights.tp_rank
+        if b.dst_rank == mine:
+            apply_block(b, full[b.src_name].to(rollout_weights.device), rollout_weights.p[b.dst_name])

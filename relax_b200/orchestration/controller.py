@@ -241,7 +241,15 @@ class Controller:
                 eval_temperature=_get(a, "eval_temperature", None) or 0.0,
                 eval_max_response_len=_get(a, "eval_max_response_len", None),
                 eval_reward_key=_get(a, "eval_reward_key", None) or _get(a, "reward_key", None))
-            return ColocatedGRPO(cfg, device=self.device)
+            run = ColocatedGRPO(cfg, device=self.device)
+            if _get(a, "genrm_model_path", None):
+                # generative reward model on in-house engines that share this rank's GPU (relax/components/genrm.py)
+                from ..rewards.genrm import build_genrm
+
+                grm = build_genrm(a.genrm_model_path, self.device, codec=run.codec, seed=a.seed)
+                detok = run.codec.decode if run.codec is not None else (lambda ids: "")
+                run.reward_fn, run.genrm = grm.reward_fn(detok), grm
+            return run
         if self.mode == "sft":
             from ..train.actor import TrainActor
             from ..parallel.state import ParallelDims, init_parallel_state, single_process_state

@@ -77,3 +77,48 @@ class GenRM:
             return self.score([str(sample.prompt)], [str(sample.label)], [ans])[0]
 
         return fn
+
+
+def engine_judge(engine, codec, temperature: float = 0.0, max_prompt_tokens: int = 2048) -> JudgeEngine:
+    """A grader served by an in-house :class:`~relax_b200.rollout.engine.RolloutEngine` (the reference runs its
+    grader on dedicated SGLang engines, relax/distributed/ray/genrm.py): prompts are tokenised with ``codec``,
+    generated greedily (by default) and the completions detokenised for the verdict parser."""
+    from ..rollout.engine import SamplingParams
+
+    def generate_text(prompts: List[str], max_new_tokens: int) -> List[str]:
+        ids = [codec.encode(p)[-max_prompt_tokens:] for p in prompts]
+        sp = SamplingParams(temperature=temperature, max_new_tokens=max_new_tokens)
+        res = engine.generate(ids, sp)
+        return [codec.decode(r.output) for r in res]
+
+    return JudgeEngine(generate_text)
+
+
+def build_genrm(model_path: str, device, num_engines: int = 1, max_new_tokens: int = 64, codec=None, seed: int = 0) -> GenRM:
+    """``--genrm-model-path``: a Hugging Face checkpoint directory (its config picks the architecture) or
+    ``preset:<name>`` for a randomly initialised model of a built-in shape (tests).  One engine per ``num_engines``;
+    they share the device with the caller (the grader runs between rollout and training)."""
+    import torch
+
+    from ..checkpoint import hf as H
+    from ..data.tokenizer import build_codec
+    from ..models.config import get_config
+    from ..rollout.engine import RolloutEngine
+
+    if model_path.startswith("preset:"):
+        cfg, src = get_config(model_path.split(":", 1)[1]), None
+    else:
+        cfg, src = H.config_from_hf(model_path), model_path
+    codec = codec or build_codec(src, cfg.vocab_size)
+    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
+    engines = []
+    for i in range(max(1, num_engines)):
+        eng = RolloutEngine(cfg, device=device, dtype=dt, num_kv_blocks=512, block_size=16, seed=seed + i,
+                            eos_token_id=getattr(codec, "eos_token_id", None), use_cuda_graph=False, memory_saver=False)
+        if src is not None:
+            H.load_hf_into_rollout(src, cfg, eng.weights)
+        else:
+            g = torch.Generator(device="cpu").manual_seed(seed)
+            eng.weights.flat.copy_((torch.randn(eng.weights.numel, generator=g) * 0.02).to(dt))
+        engines.append(engine_judge(eng, codec))
+    return GenRM(engines, max_new_tokens=max_new_tokens)

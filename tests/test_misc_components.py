@@ -152,3 +152,47 @@ def test_custom_loss_and_tis_functions_by_path(tmp_path):
          "advantages": [[1.0] * 3, [-1.0] * 2], "log_probs": [[-1.0] * 3, [-1.0] * 2]}
     out, norm = actor._train_step(b, [0, 1])
     assert "mine" in out and norm > 0
+
+
+def test_genrm_on_an_inhouse_engine_and_hf_roundtrip(tmp_path):
+    """A grader served by the in-house engine: HF checkpoint on disk -> config_from_hf -> engine weights -> verdicts
+    parsed into rewards; the engine's weights equal the ones a trainer of that checkpoint would sync."""
+    import torch
+
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.rewards.genrm import build_genrm, engine_judge, GenRM
+    from relax_b200.types import Sample
+
+    cfg = get_config("tiny")
+    model = GPTModel(cfg, seed=4)
+    out = str(tmp_path / "judge")
+    H.save_hf_checkpoint(out, cfg, H.convert_state_to_hf(cfg, {n: p.detach() for n, p in model.named_parameters()}))
+    got = H.config_from_hf(out)
+    for f in ("num_layers", "hidden_size", "num_attention_heads", "num_query_groups", "head_dim", "ffn_hidden_size", "vocab_size",
+              "qk_layernorm", "tie_word_embeddings"):
+        assert getattr(got, f) == getattr(cfg, f), f
+    import dataclasses
+
+    grm = build_genrm(out, "cpu", num_engines=2, max_new_tokens=8)
+    assert len(grm.engines) == 2
+    s = Sample(prompt="2+2?", label="4", response="4", tokens=[1, 2, 3], response_length=1)
+    r = grm.reward_fn(lambda ids: "")(s)
+    assert r in (0.0, 1.0) or 0.0 <= r <= 1.0          # a random grader: the verdict rarely parses -> default score
+    # a scripted judge through the same wrapper: the parser sees the engine's text
+    class _Eng:
+        def generate(self, ids, sp):
+            class R:      # noqa: D401
+                output = list(b"Verdict: correct")
+            return [R() for _ in ids]
+
+    class _Codec:
+        def encode(self, t):
+            return list(t.encode())
+
+        def decode(self, ids):
+            return bytes(ids).decode()
+
+    assert GenRM([engine_judge(_Eng(), _Codec())]).score(["q"], ["a"], ["a"]) == [1.0]
+    assert build_genrm("preset:tiny", "cpu").score(["q"], ["a"], ["b"])[0] in (0.0, 1.0)
