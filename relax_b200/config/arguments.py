@@ -285,7 +285,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--freeze-vision-projection": (_R, "use --freeze-params-name-list"),
     "--num-labels": (_R, "set the classifier width through the model preset (num_classes)"),
     "--problem-type": (_R, "single-label classification only"),
-    "--autoscaler-config": (_R, "the autoscaler rule engine is a library (rollout/elastic.py), not a running service"),
+    "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
     # operational, no effect here
     "--async-save": (_W, "checkpoints are written synchronously"),
     "--attention-backend": (_W, "there is one attention implementation (tcgen05 flash attention)"),

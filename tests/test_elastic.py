@@ -119,3 +119,51 @@ def test_colocated_loop_recovers_from_engine_failures():
     calls.update(n=0, fail=99)
     with pytest.raises(RuntimeError, match="3 times in a row"):
         c.runner.step()
+
+
+def test_scale_out_and_in_over_real_engines_through_the_control_endpoints():
+    """Real engines behind the pool: POST /scale_out creates an engine, copies the seed's CURRENT weights engine to
+    engine and admits it (its log-probs equal the seed's), POST /scale_in drains and removes it, GET /engines reports."""
+    import json
+    import urllib.request
+
+    import torch
+
+    from relax_b200.models.config import get_config
+    from relax_b200.rollout.elastic_service import ElasticControlServer, engine_pool
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+
+    cfg = get_config("tiny")
+    seed = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=64, block_size=8)
+    seed.weights.flat.normal_(0, 0.02, generator=torch.Generator().manual_seed(0))
+    seed.update_weight_version(5)
+    pool = engine_pool(seed)
+    srv = ElasticControlServer(pool)
+    base = f"http://{srv.address[0]}:{srv.address[1]}"
+
+    def call(path, body=None):
+        req = urllib.request.Request(base + path, data=None if body is None else json.dumps(body).encode(),
+                                     method="GET" if body is None else "POST")
+        with urllib.request.urlopen(req, timeout=60) as r:
+            return json.loads(r.read())
+
+    try:
+        out = call("/scale_out", {"num_engines": 2})
+        assert len(out["succeeded"]) == 2 and not out["failed"]
+        st = call("/engines")
+        assert sum(v["state"] == "active" for v in st.values()) == 3 and all(v["weight_version"] == 5 for v in st.values())
+        new = pool.engines[out["succeeded"][0]].engine
+        assert torch.equal(new.weights.flat, seed.weights.flat) and new.weight_version == 5
+        sp = SamplingParams(temperature=0.0, max_new_tokens=5)
+        a, b = seed.generate([[3, 4, 5, 6]], sp)[0], new.generate([[3, 4, 5, 6]], sp)[0]
+        assert a.output == b.output and a.logprobs == b.logprobs
+        assert call("/health")["active"] == 3
+        removed = call("/scale_in", {"num_engines": 2})["removed"]
+        assert len(removed) == 2 and "seed" not in removed and len(pool.active()) == 1
+        import urllib.error
+
+        with pytest.raises(urllib.error.HTTPError) as bad:       # a bad request is answered with 400, the service lives on
+            call("/scale_out", {"num_engines": 1, "policy": "nonsense"})
+        assert bad.value.code == 400 and call("/health")["status"] == "ok"
+    finally:
+        srv.close()
