@@ -582,6 +582,10 @@ class TrainActor:
             tot = sum(float((d * m).sum()) for d, m in zip(sig, masks))
             opd_metric = tot / max(1.0, float(mask_all.sum()))
 
+        from ..data.rollout_log import log_rollout_data
+
+        rollout_stats = log_rollout_data(batch, self.ps.dp.group if self.ps.dp.size > 1 else None,
+                                         device=dev if (dist.is_initialized() and dist.get_backend() == "nccl") else "cpu")
         dp = self.ps.dp.size
         per_step = max(1, cfg.global_batch_size // dp)
         steps = max(1, math.ceil(n / per_step)) if n else 1
@@ -611,6 +615,7 @@ class TrainActor:
         if opd_metric is not None:
             out["opd_kl"] = opd_metric
         out.update({k: float(v) for k, v in adv_stats.items()})
+        out.update(rollout_stats)
         out["grad_norm"] = last_norm
         out["train_time"] = time.perf_counter() - t0
         return out

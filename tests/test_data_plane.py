@@ -92,3 +92,18 @@ def test_samplers():
     assert s(ready, meta, None) == [0, 1, 2, 3]          # both rows of samples 0 and 1, never split
     s.advance_window()
     assert s(ready, meta, None) == [4, 5, 6, 7]
+
+
+def test_log_rollout_data_masked_token_means_and_scalars():
+    import torch
+
+    from relax_b200.data.rollout_log import log_rollout_data
+
+    batch = {"tokens": [[1, 2, 3, 4], [5, 6, 7]], "response_lengths": [2, 2], "total_lengths": [4, 3],
+             "loss_masks": [[1.0, 0.0], [1.0, 1.0]], "rewards": [1.0, 0.0], "raw_reward": [2.0, 4.0],
+             "log_probs": [torch.tensor([-1.0, -9.0]), torch.tensor([-2.0, -4.0])], "advantages": [[0.5, 0.5], [-0.5, -0.5]]}
+    m = log_rollout_data(batch)
+    assert m["rollout/rewards"] == 0.5 and m["rollout/raw_reward"] == 3.0 and m["rollout/response_lengths"] == 2.0
+    assert m["rollout/prompt_lengths"] == 1.5
+    assert abs(m["rollout/log_probs"] - (-1.0 + -3.0) / 2) < 1e-6        # the masked-out -9 does not count
+    assert abs(m["rollout/advantages"]) < 1e-9 and "rollout/tokens" not in m
