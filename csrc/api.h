@@ -120,6 +120,8 @@ int rb_grouped_gemm_wgrad(const void* dY, const void* X, void* dW, const int* ex
 int rb_decode_gemm_splits(int tiles, int k_iters);
 int rb_decode_gemm(const void* x, const void* W, void* y, int Mt, int N, int K, int ldx, int ldw, int swiglu, int splits,
                    int* err, cudaStream_t st);
+int rb_policy_loss(const float* ppo_kl, const float* adv, float* loss, float* clipfrac, float* dkl, long long n, float eps_clip,
+                   float eps_clip_high, float eps_clip_c, cudaStream_t st);
 int rb_lm_head_splits(int M, int N);
 int rb_lm_head_logprob(const void* h, const void* W, const long long* targets, float* partials, int M, int N, int K,
                        int ldh, int ldw, int vocab_start, float inv_temp, int n_splits, int* err, cudaStream_t stream);

@@ -108,6 +108,16 @@ void decode_advance(torch::Tensor tok_new, torch::Tensor lp_new, torch::Tensor t
                           cur_stream()),
         "rb_decode_advance");
 }
+void policy_loss(torch::Tensor ppo_kl, torch::Tensor adv, torch::Tensor loss, torch::Tensor clipfrac, torch::Tensor dkl,
+                 double eps_clip, double eps_clip_high, double eps_clip_c) {
+  const c10::cuda::CUDAGuard guard(ppo_kl.device());
+  TORCH_CHECK(ppo_kl.scalar_type() == at::kFloat && adv.scalar_type() == at::kFloat, "fp32 inputs");
+  TORCH_CHECK(ppo_kl.is_contiguous() && adv.is_contiguous() && adv.numel() == ppo_kl.numel(), "contiguous inputs of one size");
+  check(rb_policy_loss(ppo_kl.data_ptr<float>(), adv.data_ptr<float>(), loss.data_ptr<float>(), clipfrac.data_ptr<float>(),
+                       dkl.data_ptr<float>(), ppo_kl.numel(), (float)eps_clip, (float)eps_clip_high, (float)eps_clip_c,
+                       cur_stream()),
+        "rb_policy_loss");
+}
 // Weight-streaming decode GEMM; returns false when the shape is outside its range (the caller uses the split-K path).
 bool decode_gemm(torch::Tensor x, torch::Tensor W, torch::Tensor y, bool swiglu, int64_t splits, torch::Tensor err) {
   const c10::cuda::CUDAGuard guard(x.device());
@@ -210,6 +220,7 @@ void register_more(pybind11::module_& m) {
   m.def("sample", &sample);
   m.def("sample_v2", &sample_v2);
   m.def("decode_advance", &decode_advance);
+  m.def("policy_loss", &policy_loss);
   m.def("decode_gemm", &decode_gemm);
   m.def("grouped_gemm_fwd", &grouped_gemm_fwd);
   m.def("grouped_gemm_dgrad", &grouped_gemm_dgrad);

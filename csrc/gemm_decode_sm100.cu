@@ -56,10 +56,19 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr));
   return v;
+}
+__device__ __forceinline__ void store_bf16x4(__nv_bfloat16* dst, const float4& v) {   // dst 8-byte aligned
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = u;
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -181,11 +190,17 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
     }
     const int nchunks = (p.Mt + CHUNK - 1) / CHUNK;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_grp * 32) << 16);
-    // slice of the tile this CTA reduces: feature rows (plain) or gate/up pairs (SwiGLU)
+    // slice of the tile this CTA reduces: feature rows (plain) or gate/up pairs (SwiGLU).  S is a power of two, so
+    // the slice is a power of two >= 8 and splits into float4 groups with shifts.
+    const int lgS = 31 - __clz(S);
     const int units = p.swiglu ? 64 : BM;
-    const int upc = (units + S - 1) / S;
-    const int u_lo = q * upc;
-    const int u_n = max(0, min(units, u_lo + upc) - u_lo);
+    const int u_n = units >> lgS;
+    const int u_lo = q * u_n;
+    const int lgG = 31 - __clz(u_n >> 2);
+    const int G = 1 << lgG;
+    uint32_t peer[8];   // the reduction buffers of every CTA of the cluster, in cluster shared addresses
+#pragma unroll
+    for (int z = 0; z < 8; ++z) peer[z] = map_to_cta(smem_u32(red), z < S ? z : 0);
     for (int c = 0; c < nchunks; ++c) {
       const int buf = c & 1, use = c >> 1;
       float* mine = red + buf * (CHUNK * BM);
@@ -210,27 +225,46 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
       if (et < S) mbar_arrive_remote(map_to_cta(smem_u32(&ready_bar[buf]), et));
       if (ok) ok = mbar_wait_cluster(&ready_bar[buf], static_cast<uint32_t>(use) & 1, abort_flag, p.err);
       if (ok) {
-        const uint32_t base = smem_u32(mine);
-        for (int idx = et; idx < u_n * CHUNK; idx += 128) {
-          const int uu = idx % u_n, j = idx / u_n;
+        const uint32_t boff = static_cast<uint32_t>(buf * (CHUNK * BM) * 4);
+        for (int idx = et; idx < CHUNK * G; idx += 128) {
+          const int g = idx & (G - 1), j = idx >> lgG;
           const int tok = c * CHUNK + j;
-          if (tok >= p.Mt) continue;
+          if (tok >= p.Mt) break;     // j grows with idx
+          const uint32_t off = boff + static_cast<uint32_t>((j * BM + u_lo + 4 * g) * 4);
+          float4 a[8];
+#pragma unroll
+          for (int z = 0; z < 8; ++z)
+            if (z < S) a[z] = ld_cluster_f32x4(peer[z] + off);
+          float4 acc = a[0];
+#pragma unroll
+          for (int z = 1; z < 8; ++z)
+            if (z < S) { acc.x += a[z].x; acc.y += a[z].y; acc.z += a[z].z; acc.w += a[z].w; }
           if (!p.swiglu) {
-            const int f = tile * BM + u_lo + uu;
-            if (f >= p.N) continue;
-            float acc = 0.f;
-            for (int z = 0; z < S; ++z) acc += ld_cluster_f32(map_to_cta(base + (j * BM + u_lo + uu) * 4, z));
-            reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.N + f] = __float2bfloat16(acc);
-          } else {
-            const int f = tile * 64 + u_lo + uu;
-            if (f >= F) continue;
-            float g = 0.f, u = 0.f;
-            for (int z = 0; z < S; ++z) {
-              g += ld_cluster_f32(map_to_cta(base + (j * BM + u_lo + uu) * 4, z));
-              u += ld_cluster_f32(map_to_cta(base + (j * BM + 64 + u_lo + uu) * 4, z));
+            const int f = tile * BM + u_lo + 4 * g;
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(tok) * p.N + f;
+            if (f + 3 < p.N) {
+              store_bf16x4(o, acc);
+            } else {
+              const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+              for (int e = 0; e < 4; ++e)
+                if (f + e < p.N) o[e] = __float2bfloat16(v[e]);
             }
-            const float a = g / (1.f + __expf(-g)) * u;
-            reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * F + f] = __float2bfloat16(a);
+          } else {
+            float4 b[8];
+#pragma unroll
+            for (int z = 0; z < 8; ++z)
+              if (z < S) b[z] = ld_cluster_f32x4(peer[z] + off + 64 * 4);
+            float4 up = b[0];
+#pragma unroll
+            for (int z = 1; z < 8; ++z)
+              if (z < S) { up.x += b[z].x; up.y += b[z].y; up.z += b[z].z; up.w += b[z].w; }
+            const int f = tile * 64 + u_lo + 4 * g;      // F is a multiple of 64: always inside
+            float4 r;
+            r.x = acc.x / (1.f + __expf(-acc.x)) * up.x;
+            r.y = acc.y / (1.f + __expf(-acc.y)) * up.y;
+            r.z = acc.z / (1.f + __expf(-acc.z)) * up.z;
+            r.w = acc.w / (1.f + __expf(-acc.w)) * up.w;
+            store_bf16x4(reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(tok) * F + f, r);
           }
         }
       }
@@ -283,20 +317,16 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const Params& p,
 }  // namespace dg
 }  // namespace rb
 
-// K splits (= cluster size) for a decode GEMM with `tiles` weight tiles and `k_iters` 64-deep steps: fill the
-// machine's 2 x SM CTA slots in whole waves, keep at least four k steps per CTA, at most 8 CTAs per cluster.
+// K splits (= cluster size: 1, 2, 4 or 8) for a decode GEMM with `tiles` weight tiles and `k_iters` 64-deep steps.
+// Measured on B200 at 128 and 256 tokens: one CTA per SM is enough to keep the weight stream going as long as
+// every CTA has a few k steps, a second wave costs more than it gains, and long reductions (k_iters / S >= 16
+// after doubling) are worth a second CTA per SM.
 extern "C" int rb_decode_gemm_splits(int tiles, int k_iters) {
   const int slots = 2 * rb::num_sms();
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; ++s) {
-    if (s > 1 && k_iters / s < 4) break;
-    const int ctas = tiles * s;
-    const int waves = (ctas + slots - 1) / slots;
-    const double eff = static_cast<double>(ctas) / (static_cast<double>(waves) * slots);
-    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
-  }
-  return best;
+  int s = 1;
+  while (s < 8 && tiles * s < 128 && k_iters / (2 * s) >= 4) s *= 2;
+  if (s < 8 && tiles * 2 * s <= slots && k_iters / (2 * s) >= 16) s *= 2;
+  return s;
 }
 
 // y = x W^T (swiglu = 0, y [Mt, N]) or y = silu(x Wg^T) * (x Wu^T) with W = [Wg; Wu] (swiglu = 1, y [Mt, N / 2]).
@@ -309,6 +339,7 @@ extern "C" int rb_decode_gemm(const void* x, const void* W, void* y, int Mt, int
   if (Mt > 256 || (ldx % 8) || (ldw % 8) || (K % 8)) return -20;
   if ((reinterpret_cast<uintptr_t>(x) % 16) || (reinterpret_cast<uintptr_t>(W) % 16)) return -20;
   if (swiglu && ((N / 2) % 64)) return -20;
+  if ((N % 4) || (reinterpret_cast<uintptr_t>(y) % 8)) return -20;   // 4 features per store
   const int nt = Mt <= 64 ? 64 : (Mt <= 128 ? 128 : 256);
   const int tiles = swiglu ? (N / 2) / 64 : (N + BM - 1) / BM;
   const int k_iters = (K + BK - 1) / BK;
@@ -316,6 +347,7 @@ extern "C" int rb_decode_gemm(const void* x, const void* W, void* y, int Mt, int
   p.Mt = Mt; p.N = N; p.K = K; p.swiglu = swiglu; p.out = y; p.err = err;
   p.S = splits > 0 ? splits : rb_decode_gemm_splits(tiles, k_iters);
   if (p.S > 8) p.S = 8;
+  while (p.S & (p.S - 1)) p.S &= p.S - 1;       // the reduction slices the tile in powers of two
   CUtensorMap tw, tx;
   int rc = encode_tma_2d_bf16(&tw, W, K, N, ldw, BK, swiglu ? 64 : BM);
   if (rc) return rc;

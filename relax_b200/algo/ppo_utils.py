@@ -127,7 +127,15 @@ def compute_opsm_mask(log_probs, old_log_probs, advantages, loss_mask, seg: Segm
 
 
 def compute_policy_loss(ppo_kl, advantages, eps_clip: float, eps_clip_high: float, eps_clip_c: float | None = None):
-    """PPO clipped surrogate with optional dual clip.  ``ppo_kl = old - new``."""
+    """PPO clipped surrogate with optional dual clip.  ``ppo_kl = old - new``.  On a GPU the whole chain (and its
+    gradient) is one kernel; advantages carry no gradient there (they never do in the trainers)."""
+    if eps_clip_c is not None and not eps_clip_c > 1.0:
+        raise ValueError(f"dual-clip lower bound must be > 1.0, got {eps_clip_c}")
+    if ppo_kl.is_cuda and not advantages.requires_grad and ppo_kl.dtype == torch.float32:
+        from ..ops import _use_cuda, _cuda
+
+        if _use_cuda(ppo_kl):
+            return _cuda().policy_loss(ppo_kl, advantages, eps_clip, eps_clip_high, eps_clip_c)
     ratio = torch.exp(-ppo_kl)
     l1 = -ratio * advantages
     l2 = -ratio.clamp(1.0 - eps_clip, 1.0 + eps_clip_high) * advantages

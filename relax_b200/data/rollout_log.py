@@ -26,17 +26,22 @@ def log_rollout_data(batch: dict, dp_group=None, device="cpu") -> dict:
             continue
         first = val[0]
         tot, cnt = 0.0, 0
-        if torch.is_tensor(first) or (isinstance(first, (list, tuple)) and first and isinstance(first[0], (int, float))):
-            # token level: masked mean inside each sample, then the mean over samples
+        if torch.is_tensor(first) and first.dim() == 0:
+            tot, cnt = float(torch.stack([x.float() for x in val]).sum()), len(val)
+        elif torch.is_tensor(first) or (isinstance(first, (list, tuple)) and first and isinstance(first[0], (int, float))):
+            # token level: masked mean inside each sample, then the mean over samples; the per-sample means stay
+            # on the tensors' device and come to the host in one read per field
+            means = []
             for i, v in enumerate(val):
                 t = torch.as_tensor(v, dtype=torch.float32).reshape(-1)
                 if masks is not None and resp is not None and t.numel() == int(resp[i]):
-                    m = torch.as_tensor(masks[i], dtype=torch.float32).reshape(-1)
-                    tot += float((t * m).sum() / m.sum().clamp_min(1))
-                else:
-                    tot += float(t.mean()) if t.numel() else 0.0
+                    m = torch.as_tensor(masks[i], dtype=torch.float32, device=t.device).reshape(-1)
+                    means.append((t * m).sum() / m.sum().clamp_min(1))
+                elif t.numel():
+                    means.append(t.mean())
                 cnt += 1
-        elif isinstance(first, (int, float, bool)) or (torch.is_tensor(first) and first.dim() == 0):
+            tot = float(torch.stack(means).sum()) if means else 0.0
+        elif isinstance(first, (int, float, bool)):
             tot, cnt = float(sum(float(x) for x in val)), len(val)
         else:
             continue

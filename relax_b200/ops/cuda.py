@@ -749,6 +749,32 @@ def fused_lm_head_logprob(hidden, weight, targets, tp_group=None, vocab_start=0,
     return _FusedLMHead.apply(hidden, weight, targets, tp_group, vocab_start, with_entropy, temperature)
 
 
+# --------------------------------------------------------------------------- fused policy loss
+
+
+class _PolicyLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ppo_kl, adv, eps_clip, eps_clip_high, eps_clip_c):
+        kl = ppo_kl.detach().float().contiguous()
+        loss, clip, g = (torch.empty_like(kl) for _ in range(3))
+        _load().policy_loss(kl, adv.detach().float().contiguous().expand_as(kl).contiguous(), loss, clip, g,
+                            float(eps_clip), float(eps_clip_high), float(eps_clip_c or 0.0))
+        ctx.save_for_backward(g)
+        ctx.mark_non_differentiable(clip)
+        return loss, clip
+
+    @staticmethod
+    def backward(ctx, dloss, _dclip):
+        (g,) = ctx.saved_tensors
+        return dloss * g, None, None, None, None
+
+
+def policy_loss(ppo_kl, advantages, eps_clip, eps_clip_high, eps_clip_c=None):
+    """``(loss, clipfrac)`` per token of the PPO clipped surrogate in one kernel; the same pass writes
+    d loss / d ppo_kl, so backward is one multiply.  Advantages are treated as constants."""
+    return _PolicyLoss.apply(ppo_kl, advantages, eps_clip, eps_clip_high, eps_clip_c)
+
+
 # --------------------------------------------------------------------------- grouped (MoE expert) GEMM
 
 

@@ -264,3 +264,53 @@ def test_kv_scatter():
     slots = torch.randperm(128, device="cuda", generator=g)[:T]
     C.kv_scatter(k, v, kc, vc, slots)
     assert torch.equal(kc[slots], k) and torch.equal(vc[slots], v)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("Mt,N,K,S", [(16, 128, 256, 1), (64, 256, 512, 2), (100, 384, 1024, 4), (128, 4096, 4096, 0),
+                                     (200, 256, 2048, 8), (256, 1024, 1024, 2), (130, 768, 2048, 0), (7, 136, 264, 1)])
+def test_decode_gemm_cluster_splitk(Mt, N, K, S, swiglu):
+    """Weight-streaming decode GEMM (weights as the MMA M operand, split-K reduced through distributed shared
+    memory), with and without the SwiGLU epilogue, against fp32."""
+    C = _C()
+    L = C._load()
+    if swiglu and (N // 2) % 64:
+        pytest.skip("the SwiGLU variant takes 64 gate/up pairs per tile")
+    g = torch.Generator(device="cuda").manual_seed(Mt + N + K + S)
+    x = torch.randn(Mt, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).bfloat16()
+    y = torch.full((Mt, N // 2 if swiglu else N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    assert L.decode_gemm(x, w, y, swiglu, S, C.err_flag(x.device)), "the shape is inside the kernel's range"
+    C.check_error_flag(x.device)
+    ref = x.float() @ w.float().t()
+    if swiglu:
+        F = N // 2
+        ref = torch.nn.functional.silu(ref[:, :F]) * ref[:, F:]
+    _close(y, ref, atol=0.002 * math.sqrt(K), rtol=2 ** -7)
+
+
+@pytest.mark.parametrize("dual", [None, 3.0])
+def test_fused_policy_loss_matches_eager(dual):
+    from relax_b200.algo import ppo_utils as P
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    n = 100_003
+    kl = (torch.randn(n, device="cuda", generator=g) * 0.3).requires_grad_(True)
+    adv = torch.randn(n, device="cuda", generator=g)
+    w = torch.rand(n, device="cuda", generator=g)
+    loss, clip = _C().policy_loss(kl, adv, 0.2, 0.28, dual)
+    (loss * w).sum().backward()
+    g_fused, kl.grad = kl.grad.clone(), None
+    # the eager statement of the same loss (CPU path of compute_policy_loss)
+    ratio = torch.exp(-kl)
+    l1, l2 = -ratio * adv, -ratio.clamp(0.8, 1.28) * adv
+    ref = torch.maximum(l1, l2)
+    if dual is not None:
+        ref = torch.where(adv < 0, torch.minimum(-dual * adv, ref), ref)
+    (ref * w).sum().backward()
+    _close(loss, ref, 1e-5, 1e-5)
+    assert torch.equal(clip, (l2 > l1).float())
+    _close(g_fused, kl.grad, 1e-5, 1e-5)
+    # and the public entry point takes the fused path on a GPU
+    out, _ = P.compute_policy_loss(kl.detach(), adv, 0.2, 0.28, dual)
+    _close(out, ref, 1e-5, 1e-5)
