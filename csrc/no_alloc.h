@@ -19,6 +19,11 @@
 //    to stderr); nothing is launched.
 //  * The first call on each device looks up the array's device address, with
 //    that device current.  Make that first call outside any stream capture.
+//    The looked-up address is cached in a per-device table that is filled
+//    without a lock: two host threads that race on the first use of a device
+//    both look the address up and both store the same value, so the race is
+//    benign (the address of a __device__ array never changes while the module
+//    is loaded).
 //  * All calls on a device share the one array and it keeps whatever the last
 //    call left in it.  The kernels overwrite every element they later read, so
 //    nothing has to be cleared between calls, but two calls whose kernels

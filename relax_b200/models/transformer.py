@@ -183,6 +183,35 @@ def _vocab_shard(gen, name, cfg, v_pad, start, v_local, dtype):
     return full[start:start + v_local].to(dtype).contiguous()
 
 
+class _EmbeddingLookup(torch.autograd.Function):
+    """``weight[idx]`` (rows with ``keep`` false give zeros) whose backward adds the incoming rows straight into the
+    optimizer's fp32 gradient buffer of the weight (``weight.main_grad``) instead of materialising a dense
+    [vocab, hidden] gradient and adding that: per micro-batch only the rows that were looked up are touched."""
+
+    @staticmethod
+    def forward(ctx, weight, idx, keep):
+        ctx.weight = weight
+        ctx.save_for_backward(idx, keep if keep is not None else idx.new_empty(0))
+        ctx.has_keep = keep is not None
+        out = weight.detach()[idx]
+        return out * keep[:, None].to(out.dtype) if keep is not None else out
+
+    @staticmethod
+    def backward(ctx, dy):
+        idx, keep = ctx.saved_tensors
+        w = ctx.weight
+        if ctx.has_keep:
+            dy = dy * keep[:, None].to(dy.dtype)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None and mg.dtype == torch.float32 and w.grad is not mg:
+            # sort-based accumulation: repeated tokens are summed in a fixed order (bit-identical reruns)
+            mg.index_put_((idx,), dy.float(), accumulate=True)
+            return None, None, None
+        g = torch.zeros_like(w)
+        g.index_put_((idx,), dy.to(g.dtype), accumulate=True)
+        return g, None, None
+
+
 class VocabParallelEmbedding(nn.Module):
     def __init__(self, cfg, ps, dtype, device, gen):
         super().__init__()
@@ -196,10 +225,14 @@ class VocabParallelEmbedding(nn.Module):
     def forward(self, tokens, sequence_parallel: bool):
         g = self.ps.tp
         if g.size == 1:
-            return self.weight[tokens]
+            return _EmbeddingLookup.apply(self.weight, tokens, None) if self.weight.requires_grad else self.weight[tokens]
         loc = tokens - self.start
         ok = (loc >= 0) & (loc < self.v_local)
-        e = self.weight[torch.where(ok, loc, torch.zeros_like(loc))] * ok[:, None].to(self.weight.dtype)
+        loc = torch.where(ok, loc, torch.zeros_like(loc))
+        if self.weight.requires_grad:
+            e = _EmbeddingLookup.apply(self.weight, loc, ok)
+        else:
+            e = self.weight[loc] * ok[:, None].to(self.weight.dtype)
         if sequence_parallel:
             return TP.reduce_scatter_seq(e, g)
         return TP.reduce_from_tp(e, g)

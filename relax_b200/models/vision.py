@@ -75,8 +75,21 @@ class VisionBlock(nn.Module):
         self.qkv = mk(3 * h, h)
         self.qkv_bias = nn.Parameter(torch.zeros(3 * h, dtype=dtype, device=device))
         self.proj = mk(h, h, std=0.02 / math.sqrt(2 * cfg.depth))
-        self.fc1 = mk(2 * f, h)        # [gate; up]
-        self.fc2 = mk(h, f, std=0.02 / math.sqrt(2 * cfg.depth))
+        # The MLP width is padded to a multiple of 64 with zero rows (fc1) / zero columns (fc2): 3420 (Qwen2.5-VL)
+        # becomes 3456, every row stride is a multiple of 16 bytes (what the TMA-fed GEMMs and the vectorised
+        # activation kernel need) and the function is unchanged - silu(0) * 0 = 0 and the padding receives zero
+        # gradients, so it stays zero through training.
+        fp = (f + 63) // 64 * 64
+        self.f, self.f_pad = f, fp
+        fc1, fc2 = mk(2 * f, h), mk(h, f, std=0.02 / math.sqrt(2 * cfg.depth))
+        if fp != f:
+            w1 = torch.zeros(2 * fp, h, dtype=dtype, device=device)
+            w1[:f], w1[fp:fp + f] = fc1.data[:f], fc1.data[f:]
+            w2 = torch.zeros(h, fp, dtype=dtype, device=device)
+            w2[:, :f] = fc2.data
+            fc1, fc2 = nn.Parameter(w1), nn.Parameter(w2)
+        self.fc1 = fc1                 # [gate; up], each f_pad rows
+        self.fc2 = fc2
 
     def forward(self, x, cos, sin, cu_seqlens, max_seqlen):
         cfg = self.cfg

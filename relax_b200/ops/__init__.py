@@ -30,16 +30,25 @@ def _cuda():
     return _c
 
 
+def _vec_ok(t) -> bool:
+    """Rows of ``t`` split into 16-byte vectors (what the elementwise kernels load)."""
+    return t.shape[-1] % (16 // t.element_size()) == 0
+
+
 def rmsnorm(x, w, eps=1e-6):
-    return _cuda().rmsnorm(x, w, eps) if _use_cuda(x) else ref.rmsnorm(x, w, eps)
+    return _cuda().rmsnorm(x, w, eps) if _use_cuda(x) and _vec_ok(x) else ref.rmsnorm(x, w, eps)
 
 
 def add_rmsnorm(x, residual, w, eps=1e-6):
-    return _cuda().add_rmsnorm(x, residual, w, eps) if _use_cuda(x) else ref.add_rmsnorm(x, residual, w, eps)
+    if _use_cuda(x) and _vec_ok(x):
+        return _cuda().add_rmsnorm(x, residual, w, eps)
+    return ref.add_rmsnorm(x, residual, w, eps)
 
 
 def swiglu(gate_up):
-    return _cuda().swiglu(gate_up) if _use_cuda(gate_up) else ref.swiglu(gate_up)
+    if _use_cuda(gate_up) and (gate_up.shape[-1] // 2) % (16 // gate_up.element_size()) == 0:
+        return _cuda().swiglu(gate_up)
+    return ref.swiglu(gate_up)
 
 
 def linear(x, w, bias=None):
@@ -50,19 +59,50 @@ def rope_cos_sin(positions, head_dim, theta, mrope_section=None):
     return ref.rope_cos_sin(positions, head_dim, theta, mrope_section)
 
 
+_WARNED: set = set()
+
+
+def _statement_on_gpu(what: str):
+    """A shape no sm_100a kernel of this package covers runs as its PyTorch statement on the GPU; said once."""
+    if what not in _WARNED:
+        _WARNED.add(what)
+        import warnings
+
+        warnings.warn(f"relax_b200: {what}: no sm_100a kernel for this shape, running the PyTorch statement", stacklevel=3)
+
+
 def apply_rope(x, cos, sin):
-    return _cuda().apply_rope(x, cos, sin) if _use_cuda(x) else ref.apply_rope(x, cos, sin)
+    if _use_cuda(x):
+        if (x.shape[-1] // 2) % (16 // x.element_size()) == 0:
+            return _cuda().apply_rope(x, cos, sin)
+        _statement_on_gpu(f"rotary width {x.shape[-1]}")
+    return ref.apply_rope(x, cos, sin)
 
 
 def attention_varlen(q, k, v, cu_seqlens, causal=True, scale=None, cu_seqlens_k=None, max_seqlen=None):
+    """Packed varlen attention.  On a GPU the tcgen05 kernels take bf16 with head_dim 128; narrower heads
+    (64 / 80 / 96 - ViT towers, small models) are zero-padded to 128, which leaves q k^T and the first ``D`` output
+    columns unchanged (the softmax scale stays 1 / sqrt(D))."""
     if _use_cuda(q):
-        return _cuda().attention_varlen(q, k, v, cu_seqlens, causal, scale, cu_seqlens_k, max_seqlen)
+        D = q.shape[-1]
+        if q.dtype == torch.bfloat16 and D == v.shape[-1] and D <= 128 and D % 8 == 0:
+            if D == 128:
+                return _cuda().attention_varlen(q, k, v, cu_seqlens, causal, scale, cu_seqlens_k, max_seqlen)
+            pad = (0, 128 - D)
+            F = torch.nn.functional
+            scale = scale if scale is not None else D ** -0.5
+            o = _cuda().attention_varlen(F.pad(q, pad), F.pad(k, pad), F.pad(v, pad), cu_seqlens, causal, scale,
+                                         cu_seqlens_k, max_seqlen)
+            return o[..., :D]
+        _statement_on_gpu(f"attention with {q.dtype}, head_dim {D} / {v.shape[-1]}")
     return ref.attention_varlen(q, k, v, cu_seqlens, causal, scale, cu_seqlens_k)
 
 
 def paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale=None):
     if _use_cuda(q):
-        return _cuda().paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
+        if q.dtype == torch.bfloat16 and q.shape[-1] == 128:
+            return _cuda().paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
+        _statement_on_gpu(f"paged decode attention with {q.dtype}, head_dim {q.shape[-1]}")
     return ref.paged_decode_attention(q, k_cache, v_cache, block_tables, context_lens, scale)
 
 

@@ -211,3 +211,55 @@ def test_fused_lm_head_vocab_shard_offsets():
     zt = part[..., 3].max(1).values
     assert torch.isfinite(zt).all()
     _close(zt - (m + torch.log(s)), full_lp, 1e-4, 1e-4)
+
+
+@pytest.mark.parametrize("D,causal", [(64, True), (80, False), (96, True)])
+def test_flash_attention_narrow_heads_are_padded_to_the_kernel_width(D, causal):
+    """head_dim 64 / 80 / 96 (ViT towers, small models) run through the head_dim-128 tensor-core kernels by zero
+    padding; forward and backward against the fp32 statement."""
+    from relax_b200 import ops
+    from relax_b200.ops import reference as R
+
+    C = _C()
+    lens, Hq, Hkv = [300, 77, 129], 4, 2
+    g = torch.Generator(device="cuda").manual_seed(D)
+    T = sum(lens)
+    q, k, v = (torch.randn(T, h, D, device="cuda", generator=g).bfloat16().requires_grad_() for h in (Hq, Hkv, Hkv))
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    launches = C._load().launch_count() if hasattr(C._load(), "launch_count") else None
+    o = ops.attention_varlen(q, k, v, cu, causal=causal)
+    assert o.shape == (T, Hq, D)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    of = R.attention_varlen(qf, kf, vf, cu, causal=causal)
+    of.backward(do.float())
+    _close(o, of, 2e-2, 2e-2, "o")
+    _close(q.grad, qf.grad, 4e-2, 4e-2, "dq")
+    _close(k.grad, kf.grad, 6e-2, 4e-2, "dk")
+    _close(v.grad, vf.grad, 6e-2, 4e-2, "dv")
+    if launches is not None:
+        assert C._load().launch_count() > launches, "the tensor-core kernels ran (no PyTorch statement)"
+    C.check_error_flag()
+
+
+def test_vision_encoder_runs_on_the_gpu_kernels():
+    """A Qwen2.5-VL style tower (head_dim 80, bias in qkv, 2-D rotary, windowless full attention per image) in bf16
+    on the GPU against the same module in fp32 on the CPU."""
+    from relax_b200.models.vision import VisionConfig, VisionEncoder
+
+    _C()
+    cfg = VisionConfig(depth=2, out_hidden_size=512)
+    assert cfg.head_dim == 80
+    cpu = VisionEncoder(cfg, dtype=torch.float32, device="cpu", seed=3)
+    gpu = VisionEncoder(cfg, dtype=torch.bfloat16, device="cuda", seed=3)
+    grid = torch.tensor([[1, 8, 12], [1, 4, 4]])
+    n = int((grid[:, 0] * grid[:, 1] * grid[:, 2]).sum())
+    px = torch.randn(n, cfg.patch_dim, generator=torch.Generator().manual_seed(1))
+    ref = cpu(px, grid)
+    out = gpu(px.cuda(), grid.cuda())
+    assert out.shape == ref.shape
+    rel = (out.float().cpu() - ref).norm() / ref.norm()
+    assert rel < 3e-2, f"relative error {rel:.3e}"
+    out.float().sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in gpu.parameters())
