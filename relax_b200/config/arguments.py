@@ -76,6 +76,7 @@ FLAGS: dict[str, list] = {
         ("--prompt-data", dict(type=str, default=None)), ("--input-key", dict(type=str, default="input")),
         ("--label-key", dict(type=str, default=None)), ("--metadata-key", dict(type=str, default="metadata")),
         ("--tool-key", dict(type=str, default=None)), ("--apply-chat-template", _b()),
+        ("--multimodal-keys", dict(type=json.loads, default=None)),      # {"image": "<row field with the image path(s)>"}
         ("--apply-chat-template-kwargs", dict(type=json.loads, default={})), ("--system-prompt", dict(type=str, default=None)),
         ("--rollout-batch-size", dict(type=int, default=None)), ("--n-samples-per-prompt", dict(type=int, default=1)),
         ("--over-sampling-batch-size", dict(type=int, default=None)),

@@ -109,6 +109,7 @@ class ColocateConfig:
     label_key: Optional[str] = "label"
     metadata_key: str = "metadata"
     tool_key: Optional[str] = None      # row field with tool definitions, rendered by the chat template
+    multimodal_keys: Optional[dict] = None   # {"image": row field with the image path(s)}; needs a vision-language model
     rollout_shuffle: bool = False
     use_streaming_dataset: bool = False     # read the prompt files lazily through a shuffle buffer
     streaming_buffer_size: int = 1024
@@ -194,6 +195,9 @@ class ColocatedGRPO:
                                     max_model_len=cfg.prompt_len + cfg.max_response_len,
                                     eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
                                     return_routed_experts=cfg.train.use_rollout_routing_replay)
+        if cfg.model.vision is not None:
+            # colocated: the engine embeds images with the trainer's tower itself (same parameters, nothing to sync)
+            self.engine.attach_vision(self.actor.model.vision)
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank
         tr_ranks = [r for r in self.ps.tp.ranks]
@@ -233,12 +237,35 @@ class ColocatedGRPO:
                                                               cfg.rollout_seed, cfg.input_key, cfg.label_key, cfg.metadata_key,
                                                               shuffle=cfg.rollout_shuffle)
             else:
-                ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key, cfg.tool_key)
+                image_key = (cfg.multimodal_keys or {}).get("image")
+                if image_key and cfg.model.vision is None:
+                    raise ValueError(f"--multimodal-keys names images but model {cfg.model.name} has no vision tower")
+                mmc = None
+                if image_key:
+                    from ..data.multimodal import MultimodalConfig
+
+                    v = cfg.model.vision
+                    mmc = MultimodalConfig(patch_size=v.patch_size, spatial_merge_size=v.spatial_merge_size,
+                                           temporal_patch_size=v.temporal_patch_size)
+                ds = JsonlPromptDataset(cfg.prompt_data, enc, cfg.input_key, cfg.label_key, cfg.metadata_key, cfg.tool_key,
+                                        image_key=image_key, image_token_id=cfg.model.image_token_id if image_key else None,
+                                        multimodal_config=mmc)
                 if len(ds) == 0:
                     raise ValueError(f"no usable prompt in {cfg.prompt_data} (limit {cfg.prompt_len} tokens)")
         else:
             self.codec = cfg.codec
-            ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
+            if cfg.model.vision is not None:      # synthetic image prompts: text, one 8 x 8-patch image, text
+                from ..rollout.data_source import SyntheticImagePromptDataset
+
+                v = cfg.model.vision
+                side = 4 * v.spatial_merge_size
+                n_img = side * side // v.spatial_merge_size ** 2
+                ds = SyntheticImagePromptDataset(cfg.num_prompts, max(1, (cfg.prompt_len - n_img) // 2), cfg.model.vocab_size,
+                                                 cfg.model.image_token_id, (side, side),
+                                                 v.in_channels * v.temporal_patch_size * v.patch_size ** 2,
+                                                 v.spatial_merge_size, seed=cfg.seed)
+            else:
+                ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
         if ds is not None:
             self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
         from ..rollout.custom_generate import load_function, load_generate_function
@@ -295,13 +322,13 @@ class ColocatedGRPO:
         return ms
 
     # ------------------------------------------------------------------ rollout
-    def _generate_with_recovery(self, prompts, sp, keys):
+    def _generate_with_recovery(self, prompts, sp, keys, images=None):
         if not self.cfg.use_health_check:
-            return self.engine.generate(prompts, sp, group_keys=keys)
+            return self.engine.generate(prompts, sp, group_keys=keys, images=images)
         failures = 0
         while True:
             try:
-                return self.engine.generate(prompts, sp, group_keys=keys)
+                return self.engine.generate(prompts, sp, group_keys=keys, images=images)
             except Exception as e:   # noqa: BLE001 - any engine failure takes the same recovery path
                 failures += 1
                 self.recoveries += 1
@@ -322,7 +349,8 @@ class ColocatedGRPO:
                 if s.reward is None:
                     s.reward = self.reward_fn(s)
             return mine
-        res = self._generate_with_recovery([s.tokens for s in flat], sp, [s.group_index for s in flat])
+        images = [s.multimodal_train_inputs for s in flat] if any(s.multimodal_train_inputs for s in flat) else None
+        res = self._generate_with_recovery([s.tokens for s in flat], sp, [s.group_index for s in flat], images)
         for s, r in zip(flat, res):
             s.tokens = list(r.prompt) + list(r.output)
             s.response_length = len(r.output)

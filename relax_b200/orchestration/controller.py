@@ -219,7 +219,7 @@ class Controller:
                 custom_rm_path=_get(a, "custom_rm_path", None),
                 prompt_data=_get(a, "prompt_data", None), input_key=_get(a, "input_key", None) or "prompt",
                 label_key=_get(a, "label_key", None), metadata_key=_get(a, "metadata_key", None) or "metadata",
-                tool_key=_get(a, "tool_key", None),
+                tool_key=_get(a, "tool_key", None), multimodal_keys=_get(a, "multimodal_keys", None),
                 rollout_shuffle=bool(_get(a, "rollout_shuffle", False)), codec=self._codec(a),
                 use_streaming_dataset=bool(_get(a, "use_streaming_dataset", False)),
                 streaming_buffer_size=_get(a, "streaming_buffer_size", None) or 1024,

@@ -32,11 +32,38 @@ class SyntheticPromptDataset:
         return {"prompt_tokens": self.data[i].tolist(), "label": None}
 
 
+class SyntheticImagePromptDataset:
+    """Random prompts with one random "image" each: ``text_len`` tokens, a run of image placeholders, ``text_len``
+    tokens.  Patches are Gaussian noise of the tower's patch size (benchmarks / tests of the vision-language loop)."""
+
+    def __init__(self, num_prompts: int, text_len: int, vocab_size: int, image_token_id: int, grid_hw=(8, 8),
+                 patch_dim: int = 1176, merge: int = 2, seed: int = 0):
+        g = torch.Generator().manual_seed(seed)
+        gh, gw = grid_hw
+        assert gh % merge == 0 and gw % merge == 0
+        n_img = gh * gw // (merge * merge)
+        self.rows = []
+        for _ in range(num_prompts):
+            text = torch.randint(0, vocab_size, (2 * text_len,), generator=g)
+            text[text == image_token_id] = (image_token_id + 1) % vocab_size
+            toks = text[:text_len].tolist() + [image_token_id] * n_img + text[text_len:].tolist()
+            self.rows.append({"prompt_tokens": toks, "label": None,
+                              "multimodal": {"pixel_patches": torch.randn(gh * gw, patch_dim, generator=g),
+                                             "grid_thw": torch.tensor([[1, gh, gw]])}})
+
+    def __len__(self):
+        return len(self.rows)
+
+    def __getitem__(self, i):
+        return self.rows[i]
+
+
 class JsonlPromptDataset:
     """``{"prompt": ..., "label": ...}`` per line; tokenised lazily by ``tokenize``."""
 
     def __init__(self, path: str, tokenize: Optional[Callable] = None, prompt_key="prompt", label_key="label",
-                 metadata_key: str = "metadata", tool_key: Optional[str] = None):
+                 metadata_key: str = "metadata", tool_key: Optional[str] = None, image_key: Optional[str] = None,
+                 image_token_id: Optional[int] = None, multimodal_config=None):
         """``path`` may list several files separated by commas.  Rows whose prompt ``tokenize`` rejects (returns
         None: longer than the prompt limit) are dropped at load time, so the epoch length is known up front."""
         self.rows = []
@@ -45,6 +72,11 @@ class JsonlPromptDataset:
                 with open(one, encoding="utf-8") as f:
                     self.rows += [json.loads(l) for l in f if l.strip()]
         self.tokenize, self.prompt_key, self.label_key, self.metadata_key = tokenize, prompt_key, label_key, metadata_key
+        # rows with images (``image_key``: a path / data URI or a list of them): the prompt carries ONE placeholder
+        # token per image, expanded to the image's token count when the row is read; the patches ride along
+        self.image_key, self.image_token_id, self.mm_cfg = image_key, image_token_id, multimodal_config
+        if image_key is not None and image_token_id is None:
+            raise ValueError("image_key needs image_token_id (the id of the placeholder the prompt contains)")
         if tokenize is not None:
             kept = []
             for r in self.rows:
@@ -65,8 +97,17 @@ class JsonlPromptDataset:
         r = self.rows[i]
         p = r[self.prompt_key]
         toks = r["_tokens"] if "_tokens" in r else list(p)
-        return {"prompt": p, "prompt_tokens": toks, "label": r.get(self.label_key) if self.label_key else None,
-                "metadata": r.get(self.metadata_key) or {}}
+        out = {"prompt": p, "prompt_tokens": toks, "label": r.get(self.label_key) if self.label_key else None,
+               "metadata": r.get(self.metadata_key) or {}}
+        imgs = r.get(self.image_key) if self.image_key else None
+        if imgs:
+            from ..data.multimodal import expand_placeholders, process_multimodal_info
+
+            imgs = [imgs] if isinstance(imgs, (str, bytes)) else list(imgs)
+            mm = process_multimodal_info([{"role": "user", "content": [{"type": "image", "image": x} for x in imgs]}], self.mm_cfg)
+            out["prompt_tokens"] = expand_placeholders(toks, self.image_token_id, mm["num_tokens"]["image"])
+            out["multimodal"] = {"pixel_patches": mm["pixel_values"], "grid_thw": mm["image_grid_thw"]}
+        return out
 
 
 class RolloutDataSource:
@@ -96,7 +137,7 @@ class RolloutDataSource:
             for _ in range(self.n):
                 s = Sample(group_index=self.group_index, index=self.sample_index, prompt=row.get("prompt", ""),
                            tokens=list(row["prompt_tokens"]), label=row.get("label"),
-                           metadata=dict(row.get("metadata") or {}))
+                           metadata=dict(row.get("metadata") or {}), multimodal_train_inputs=row.get("multimodal"))
                 self.sample_index += 1
                 grp.append(s)
             self.group_index += 1

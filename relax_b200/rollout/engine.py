@@ -55,6 +55,14 @@ class Request:
     # with ``return_routed_experts``: per context position that was fed to the model, the expert ids every MoE layer
     # chose - a list of ``[L_moe, k]`` int lists (positions 0 .. num_tokens - 2; the last token is never fed)
     routed_experts: list = field(default_factory=list)
+    # multimodal prompts: pre-cut patches of the prompt's images (``[N, patch_dim]`` + ``grid_thw [n_img, 3]``) or
+    # their embeddings (``[n_image_tokens, hidden]``), the M-RoPE position ids of the prompt ``[3][len(prompt)]`` and
+    # the offset between a generated token's index in the sequence and its rotary position
+    pixel_patches: Optional[torch.Tensor] = None
+    grid_thw: Optional[torch.Tensor] = None
+    image_embeds: Optional[torch.Tensor] = None
+    mrope_positions: Optional[list] = None
+    pos_delta: int = 0
     t_arrive: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
@@ -228,9 +236,36 @@ class RolloutEngine:
             st["rows"] = None
 
     # ------------------------------------------------------------------ requests
+    def attach_vision(self, encoder):
+        """Give the engine the vision tower that turns a request's image patches into embeddings at prefill
+        (SGLang loads the tower inside the engine: relax/backends/sglang/sglang_engine.py; here the colocated runner
+        hands over the trainer's module, a disaggregated engine builds its own and receives its weights by sync)."""
+        self.vision = encoder
+
     def add_request(self, prompt: Sequence[int], params: SamplingParams, group_key: Optional[int] = None,
-                    resume_output: Optional[Sequence[int]] = None, resume_logprobs: Optional[Sequence[float]] = None) -> int:
+                    resume_output: Optional[Sequence[int]] = None, resume_logprobs: Optional[Sequence[float]] = None,
+                    pixel_patches: Optional[torch.Tensor] = None, grid_thw=None,
+                    image_embeds: Optional[torch.Tensor] = None) -> int:
+        """Queue a prompt.  With images: ``prompt`` holds one run of ``cfg.image_token_id`` placeholders per image
+        (``t * h/merge * w/merge`` tokens), ``grid_thw`` the patch grid of every image, and either the patches
+        (an attached vision tower embeds them at prefill) or ready ``image_embeds``.  Requests that share a
+        ``group_key`` must carry the same prompt AND the same images: followers reuse the leader's prompt KV."""
         r = Request(self._next_rid, list(prompt), params, group_key, t_arrive=time.perf_counter())
+        if grid_thw is not None:
+            from ..models.vision import mrope_positions
+
+            if self.cfg.image_token_id < 0 or self.cfg.mrope_section is None:
+                raise ValueError(f"model {self.cfg.name} takes no images (no image token / M-RoPE sections)")
+            if pixel_patches is None and image_embeds is None:
+                raise ValueError("grid_thw given without pixel_patches or image_embeds")
+            if pixel_patches is not None and image_embeds is None and getattr(self, "vision", None) is None:
+                raise ValueError("pixel_patches need a vision tower: call attach_vision() or pass image_embeds")
+            grid = torch.as_tensor(grid_thw, dtype=torch.long).reshape(-1, 3)
+            merge = self.cfg.vision.spatial_merge_size if self.cfg.vision is not None else 2
+            mp = mrope_positions(r.prompt, grid.tolist(), self.cfg.image_token_id, merge)
+            r.mrope_positions = mp.tolist()
+            r.pos_delta = int(mp.max()) + 1 - len(r.prompt)
+            r.pixel_patches, r.grid_thw, r.image_embeds = pixel_patches, grid, image_embeds
         if resume_output:
             # partial rollout: earlier tokens become part of the context, generation continues
             r.output = list(resume_output)
@@ -369,21 +404,30 @@ class RolloutEngine:
     def _prefill(self, reqs: list[Request]):
         leaders = [r for r in reqs if r._lead is None]
         toks, pos, cu, slots, last_rows = [], [], [0], [], []
+        multimodal = any(r.mrope_positions is not None for r in leaders)
+        pos3 = [[], [], []]
         for r in leaders:
             ctx = r.prompt + r.output
             toks += ctx
-            pos += list(range(len(ctx)))
+            if multimodal:       # M-RoPE ids: three streams (equal for text), generated tokens continue after the prompt's maximum
+                mp = r.mrope_positions or [list(range(len(r.prompt)))] * 3
+                tail = [len(r.prompt) + r.pos_delta + i for i in range(len(r.output))]
+                for a in range(3):
+                    pos3[a] += list(mp[a]) + tail
+            else:
+                pos += list(range(len(ctx)))
             slots += self._slots(r, 0, len(ctx))
             cu.append(cu[-1] + len(ctx))
             last_rows.append(cu[-1] - 1)
         dev = self.device
         if leaders:
-            t, pos_t, cu_t, slots_t, last_t = self._stage([(toks, torch.int64), (pos, torch.int64), (cu, torch.int32),
-                                                           (slots, torch.int64), (last_rows, torch.int64)])
+            t, pos_t, cu_t, slots_t, last_t = self._stage([(toks, torch.int64), (pos3 if multimodal else pos, torch.int64),
+                                                           (cu, torch.int32), (slots, torch.int64), (last_rows, torch.int64)])
+            image = self._image_rows(leaders, cu, toks) if multimodal else None
             if self.return_routed_experts:
                 self.weights.routing_capture = []
             logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
-                                                  max_seqlen=max(b - a for a, b in zip(cu, cu[1:])))
+                                                  max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), image=image)
             self.stats["prefill_tokens"] += len(toks)
             if self.return_routed_experts:
                 routed = torch.stack(self.weights.routing_capture, 1).tolist()      # [T][L_moe][k]
@@ -413,6 +457,37 @@ class RolloutEngine:
         for r in reqs:
             r.t_first = now
 
+    def _image_rows(self, leaders, cu, toks):
+        """``(rows, embeds)``: the packed rows of this prefill that are image placeholders and what goes there.
+        All images of the batch pass through the vision tower in one call."""
+        img_id = self.cfg.image_token_id
+        rows, ready, patches, grids = [], [], [], []
+        for r, a in zip(leaders, cu):
+            if r.grid_thw is None:
+                continue
+            rows += [a + i for i, tk in enumerate(r.prompt) if tk == img_id]
+            if r.image_embeds is not None:
+                ready.append(("e", r.image_embeds))
+            else:
+                ready.append(("p", len(patches)))
+                patches.append(r.pixel_patches)
+                grids.append(r.grid_thw)
+        if not rows:
+            return None
+        embeds_of_patches = None
+        if patches:
+            tower = self.vision
+            wdev = tower.patch_embed.device
+            out = tower(torch.cat([p.to(wdev) for p in patches]), torch.cat(grids).to(wdev))
+            m2 = tower.cfg.spatial_merge_size ** 2
+            counts = [int((g[:, 0] * g[:, 1] * g[:, 2]).sum()) // m2 for g in grids]
+            embeds_of_patches = list(out.split(counts))
+        parts = [(e if kind == "e" else embeds_of_patches[e]).to(self.device) for kind, e in ready]
+        emb = torch.cat(parts)
+        if emb.shape[0] != len(rows):
+            raise ValueError(f"{len(rows)} image placeholder tokens in the batch but {emb.shape[0]} image embeddings")
+        return torch.tensor(rows, dtype=torch.int64, device=self.device), emb
+
     def _decode(self):
         if self.windowed_decode and self._decode_window():
             return
@@ -431,7 +506,7 @@ class RolloutEngine:
         bt_rows = [r.blocks + [0] * (maxb - len(r.blocks)) for r in reqs]
         tok, pos, ctx, slots, bt = self._stage([
             ([(r.output[-1] if r.output else r.prompt[-1]) for r in reqs], torch.int64),
-            ([r.num_tokens - 1 for r in reqs], torch.int64),
+            ([r.num_tokens - 1 + r.pos_delta for r in reqs], torch.int64),
             ([r.num_tokens for r in reqs], torch.int32),
             ([r.blocks[(r.num_tokens - 1) // bs] * bs + (r.num_tokens - 1) % bs for r in reqs], torch.int64),
             (bt_rows, torch.int32)])
@@ -466,7 +541,7 @@ class RolloutEngine:
         per_batch = [("tok", i64, (bucket,)), ("pos", i64, (bucket,)), ("slots", i64, (bucket,)), ("topk", i64, (bucket,)),
                      ("eos", i64, (bucket,)), ("stop", i64, (bucket, self.N_STOP)), ("ctx", i32, (bucket,)),
                      ("active", i32, (bucket,)), ("remain", i32, (bucket,)), ("bt", i32, (bucket, maxb)),
-                     ("temp", f32, (bucket,)), ("topp", f32, (bucket,))]
+                     ("temp", f32, (bucket,)), ("topp", f32, (bucket,)), ("delta", i64, (bucket,))]
         offs, n = {}, 0
         for name, dt, shp in per_window + per_batch:
             if name == "tok":
@@ -504,7 +579,10 @@ class RolloutEngine:
         def run():
             if self.return_routed_experts:
                 self.weights.routing_capture = []
-            logits = self.weights.forward_decode(d["tok"], d["pos"], d["bt"], d["ctx"], d["slots"], self.kv, self.tp)
+            # rotary position = cache position + the row's offset (non-zero after an image: M-RoPE advances by the
+            # largest grid side, not by the number of placeholder tokens)
+            rope_pos = d["pos"] + d["delta"] if self.cfg.mrope_section is not None else d["pos"]
+            logits = self.weights.forward_decode(d["tok"], rope_pos, d["bt"], d["ctx"], d["slots"], self.kv, self.tp)
             if self.return_routed_experts:      # ring slot = the step counter, read on the device (before it advances)
                 routed = torch.stack(self.weights.routing_capture, 1).to(torch.int32)
                 self.weights.routing_capture = None
@@ -531,6 +609,7 @@ class RolloutEngine:
         h, bs = st["h"], self.block_size
         h["tok"][lo:hi] = 0
         h["pos"][lo:hi] = 0
+        h["delta"][lo:hi] = 0
         h["ctx"][lo:hi] = 1
         h["bt"][lo:hi] = self._scratch_block
         h["slots"][lo:hi] = self._scratch_block * bs
@@ -573,6 +652,7 @@ class RolloutEngine:
             h["tok"][:B] = torch.tensor(last, dtype=torch.int64)
             h["pos"][:B] = torch.tensor(npos, dtype=torch.int64)
             h["ctx"][:B] = torch.tensor([p + 1 for p in npos], dtype=torch.int32)
+            h["delta"][:B] = torch.tensor([r.pos_delta for r in reqs], dtype=torch.int64)
             h["slots"][:B] = torch.tensor([r.blocks[p // bs] * bs + p % bs for r, p in zip(reqs, npos)], dtype=torch.int64)
             h["bt"][:B] = torch.tensor([r.blocks + [self._scratch_block] * (maxb - len(r.blocks)) for r in reqs], dtype=torch.int32)
             h["temp"][:B] = torch.tensor([r.params.temperature for r in reqs], dtype=torch.float32)
@@ -654,12 +734,15 @@ class RolloutEngine:
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams | Sequence[SamplingParams],
-                 group_keys: Optional[Sequence[int]] = None) -> list[Request]:
-        """Blocking generation of a batch; results in the order of ``prompts``."""
+                 group_keys: Optional[Sequence[int]] = None, images: Optional[Sequence[Optional[dict]]] = None) -> list[Request]:
+        """Blocking generation of a batch; results in the order of ``prompts``.  ``images[i]`` is None or a dict with
+        ``grid_thw`` and ``pixel_patches`` (or ``image_embeds``) of prompt ``i``."""
         ids = []
         for i, p in enumerate(prompts):
             sp = params if isinstance(params, SamplingParams) else params[i]
-            ids.append(self.add_request(p, sp, group_keys[i] if group_keys is not None else None))
+            im = images[i] if images is not None else None
+            ids.append(self.add_request(p, sp, group_keys[i] if group_keys is not None else None,
+                                        **({k: im.get(k) for k in ("pixel_patches", "grid_thw", "image_embeds")} if im else {})))
         res = {}
         while self.has_work:
             for r in self.step():

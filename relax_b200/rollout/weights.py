@@ -225,9 +225,11 @@ class RolloutWeights:
         x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
         return h, x
 
-    def _run(self, tokens, positions, attn, tp, cache):
+    def _run(self, tokens, positions, attn, tp, cache, image=None):
         cfg, p = self.cfg, self.p
         h = self._embed(tokens, tp)
+        if image is not None:      # (rows, embeddings): image placeholder rows take the vision tower's output
+            h = h.index_copy(0, image[0], image[1].to(h.dtype))
         cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
         x = ops.rmsnorm(h, p["layers.0.input_norm"], cfg.rms_norm_eps)
         for i in range(cfg.num_layers):
@@ -236,11 +238,12 @@ class RolloutWeights:
         return x
 
     # ------------------------------------------------------------------ entry points
-    def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
+    def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None,
+                        image=None):
         def attn(i, q, k, v):
             return ops.attention_varlen(q, k, v, cu_seqlens, causal=True, max_seqlen=max_seqlen)
 
-        h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True))
+        h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True), image=image)
         return self._logits(h[last_rows], tp)
 
     def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):

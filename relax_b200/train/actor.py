@@ -104,6 +104,16 @@ class TrainActor:
         self.ps = ps or single_process_state()
         self.device = torch.device(device)
         self.model = GPTModel(model_cfg, self.ps, device=device, seed=seed, recompute=cfg.recompute)
+        if model_cfg.vision is not None:
+            # vision-language model: the tower is a sub-module of the language model, so the optimizer, checkpoints
+            # and snapshots see its parameters like any other (relax/backends/megatron/model_provider.py builds the
+            # VL model the same way: one module tree)
+            from ..models.vision import VisionEncoder, vision_config_from_model
+
+            if self.ps.pp.size > 1 or self.ps.cp.size > 1:
+                raise NotImplementedError("vision-language training runs with pp = cp = 1")
+            self.model.vision = VisionEncoder(vision_config_from_model(model_cfg), dtype=self.model.dtype, device=device,
+                                              seed=seed + 17)
         self.ep_comm = None
         if (self.device.type == "cuda" and self.ps.ep.size > 1 and model_cfg.is_moe
                 and os.environ.get("RELAX_B200_EP_PEER", "1") == "1"):
@@ -221,6 +231,57 @@ class TrainActor:
         mult = self.ps.tp.size * (self.cfg.pad_multiple if self.device.type == "cuda" else 1)
         return pack_samples(tokens, response_lengths, pad_multiple=max(1, mult), device=self.device)
 
+    def _pack_batch(self, batch: dict, ids: Sequence[int]):
+        """Pack samples ``ids`` of ``batch``.  With ``multimodal_train_inputs`` (per sample None or a dict with
+        ``pixel_patches [N, patch_dim]`` and ``grid_thw [n_img, 3]``; relax/backends/megatron/data.py get_batch
+        carries the same field) the packed batch gets M-RoPE positions ``[3, T]`` and the concatenated patches."""
+        pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
+        mm = batch.get("multimodal_train_inputs")
+        if self.mcfg.vision is None or mm is None:
+            return pb
+        from ..models.vision import mrope_positions
+
+        merge = self.mcfg.vision.spatial_merge_size
+        pos, patches, grids, img_rows, row0 = [], [], [], [], 0
+        for i in ids:
+            toks = [int(t) for t in batch["tokens"][i]]
+            n_prompt = len(toks) - int(batch["response_lengths"][i])
+            m = mm[i]
+            if m is None:
+                pos.append(torch.arange(len(toks)).expand(3, -1))
+                row0 += len(toks)
+                continue
+            grid = torch.as_tensor(m["grid_thw"], dtype=torch.long).reshape(-1, 3)
+            # ids of the prompt from its image grids; the response continues linearly after the prompt's maximum
+            pp = mrope_positions(toks[:n_prompt], grid.tolist(), self.mcfg.image_token_id, merge)
+            tail = torch.arange(len(toks) - n_prompt) + (int(pp.max()) + 1 if n_prompt else 0)
+            pos.append(torch.cat([pp, tail.expand(3, -1)], 1))
+            patches.append(torch.as_tensor(m["pixel_patches"]))
+            grids.append(grid)
+            # placeholders of the PROMPT only: a sampled response token that happens to be the placeholder id is text
+            img_rows += [row0 + j for j in range(n_prompt) if toks[j] == self.mcfg.image_token_id]
+            row0 += len(toks)
+        T = int(pb.tokens.numel())
+        used = sum(p.shape[1] for p in pos)
+        if used < T:       # the padding sequence
+            pos.append(torch.arange(T - used).expand(3, -1))
+        pb.positions = torch.cat(pos, 1).to(self.device)
+        if patches:
+            pb.pixel_patches = torch.cat(patches).to(self.device)
+            pb.grid_thw = torch.cat(grids).to(self.device)
+            pb.image_rows = torch.tensor(img_rows, dtype=torch.int64, device=self.device)
+        return pb
+
+    def _embed_multimodal(self, pb):
+        """Token embeddings of a packed batch with the image placeholder rows replaced by the tower's output."""
+        if self.ps.tp.size > 1:
+            raise NotImplementedError("vision-language training runs with tp = 1 in the trainer")
+        emb = self.model.embedding.word_embeddings(pb.tokens, False)
+        img = self.model.vision(pb.pixel_patches, pb.grid_thw)
+        if img.shape[0] != pb.image_rows.numel():
+            raise ValueError(f"{pb.image_rows.numel()} image placeholders in the prompts but {img.shape[0]} image embeddings")
+        return emb.index_copy(0, pb.image_rows, img.to(emb.dtype))
+
     def _forward_logp_cp(self, pb, with_entropy: bool):
         """Context-parallel forward: every sample is sharded zig-zag over the CP ranks (two chunks per rank),
         attention runs as ring attention - or, with a :class:`~relax_b200.parallel.cp_peer.CPComm` attached as
@@ -288,7 +349,8 @@ class TrainActor:
             return self._forward_logp_pp(pb, with_entropy)
         if self.ps.cp.size > 1:
             return self._forward_logp_cp(pb, with_entropy)
-        h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen)
+        emb = self._embed_multimodal(pb) if getattr(pb, "pixel_patches", None) is not None else None
+        h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen, inputs_embeds=emb)
         hr = h.index_select(0, pb.logit_rows)
         return self.model.log_probs(hr, pb.targets, self.cfg.rollout_temperature, with_entropy)
 
@@ -377,7 +439,7 @@ class TrainActor:
             if not mb:
                 self._dummy_forward()
                 continue
-            pb = self._pack([toks[i] for i in mb], [rl[i] for i in mb])
+            pb = self._pack_batch(batch, mb)
             self._cur_ids = list(mb)
             lp, en = self._forward_logp(pb, with_entropy)
             for i, a, b in zip(mb, torch.split(lp, pb.response_lengths), torch.split(en, pb.response_lengths)):
@@ -654,7 +716,7 @@ class TrainActor:
                 continue
             ids = [idx[j] for j in mb]
             self._cur_ids = list(ids)
-            pb = self._pack([batch["tokens"][i] for i in ids], [batch["response_lengths"][i] for i in ids])
+            pb = self._pack_batch(batch, ids)
             lb = self._loss_batch(batch, ids, pb)
             use_mtp = (cfg.enable_mtp_training or cfg.mtp_only_training) and self.mcfg.mtp_num_layers > 0
             if self.role == "critic":
