@@ -266,9 +266,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--rollout-external": (_R, "external rollout engines are not supported"),
     "--rollout-external-engine-addrs": (_R, "external rollout engines are not supported"),
     "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
-    "--buffer-filter-path": (_R, "no rollout buffer filter hook"),
-    "--mask-offpolicy-in-partial-rollout": (_R, "partial rollouts keep all their tokens in the loss"),
-    "--partial-rollout-max-aborted-count": (_R, "aborted samples are resumed until they finish"),
     "--disable-rollout-global-dataset": (_R, "prompts always come from the global dataset"),
     "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
     "--use-agentic-rollout": (_R, "agentic rollouts are driven through --custom-generate-function-path (rollout/agentic.py)"),
@@ -278,12 +275,8 @@ FLAG_POLICY: dict[str, tuple] = {
     "--opd-teacher-urls": (_R, "remote teachers are not wired into the loop (teacher snapshot via --opd-teacher-load)"),
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
-    "--lora-dropout": (_R, "LoRA dropout is not implemented"),
-    "--genrm-num-gpus": (_R, "no generative reward-model engines (rewards/genrm.py parses verdicts of a remote one)"),
+    "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
     "--ref-ckpt-step": (_R, "the reference is loaded from --ref-load as a whole"),
-    "--freeze-language-model": (_R, "use --freeze-params-name-list"),
-    "--freeze-vision-model": (_R, "use --freeze-params-name-list"),
-    "--freeze-vision-projection": (_R, "use --freeze-params-name-list"),
     "--num-labels": (_R, "set the classifier width through the model preset (num_classes)"),
     "--problem-type": (_R, "single-label classification only"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
@@ -349,6 +342,19 @@ def apply_flag_policy(a: argparse.Namespace, parser: Optional[argparse.ArgumentP
             (warn or _warnings.warn)(msg)
         out.append(msg)
     return out
+
+
+def _freeze_list(a) -> Optional[list]:
+    """``--freeze-params-name-list`` plus the three multimodal switches (relax/utils/arguments.py:443-455) as name
+    patterns: the vision tower lives under ``vision.``, its projection into the language model is the merger."""
+    out = list(getattr(a, "freeze_params_name_list", None) or [])
+    if getattr(a, "freeze_language_model", False):
+        out.append(r"^(?!vision\.)")
+    if getattr(a, "freeze_vision_model", False):
+        out.append(r"^vision\.(?!merger_)")
+    if getattr(a, "freeze_vision_projection", False):
+        out.append(r"^vision\.merger_")
+    return out or None
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -543,6 +549,6 @@ def train_config_from_args(a):
         mtp_only_training=a.mtp_only_training,
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
-        freeze_params_name_list=getattr(a, "freeze_params_name_list", None),
+        freeze_params_name_list=_freeze_list(a),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
         ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

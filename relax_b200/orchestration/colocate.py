@@ -85,6 +85,13 @@ class ColocateConfig:
     custom_generate_function_path: Optional[str] = None
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
+    # partial rollout (relax/engine/rollout/sglang_rollout.py generate_rollout_async / abort): over-sampled groups
+    # still running when the batch is full are aborted, kept with their partial responses in the rollout buffer and
+    # continued by the next rollout step
+    partial_rollout: bool = False
+    mask_offpolicy_in_partial_rollout: bool = False        # resumed samples: tokens of earlier policies leave the loss
+    partial_rollout_max_aborted_count: Optional[int] = None  # a sample aborted more often is dropped with its group
+    buffer_filter_path: Optional[str] = None               # fn(buffer, n) -> groups taken from the rollout buffer
     stop_token_ids: tuple = ()
     stop_strings: tuple = ()        # --rollout-stop: the response ends with the first of these strings (needs a codec)
     critic_lr: Optional[float] = None
@@ -267,7 +274,15 @@ class ColocatedGRPO:
             else:
                 ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
         if ds is not None:
-            self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
+            if cfg.partial_rollout or cfg.buffer_filter_path:
+                from ..rollout.custom_generate import load_function as _lf
+                from ..rollout.data_source import RolloutDataSourceWithBuffer
+
+                bf = _lf(cfg.buffer_filter_path, 2, "rollout buffer filter") if cfg.buffer_filter_path else None
+                self.data_source = RolloutDataSourceWithBuffer(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle,
+                                                               seed=cfg.rollout_seed, buffer_filter=bf)
+            else:
+                self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=cfg.rollout_shuffle, seed=cfg.rollout_seed)
         from ..rollout.custom_generate import load_function, load_generate_function
 
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
@@ -352,25 +367,131 @@ class ColocatedGRPO:
         images = [s.multimodal_train_inputs for s in flat] if any(s.multimodal_train_inputs for s in flat) else None
         res = self._generate_with_recovery([s.tokens for s in flat], sp, [s.group_index for s in flat], images)
         for s, r in zip(flat, res):
-            s.tokens = list(r.prompt) + list(r.output)
-            s.response_length = len(r.output)
-            s.rollout_log_probs = list(r.logprobs)
-            s.weight_versions = sorted(set(r.weight_versions))
-            s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
-            if r.routed_experts:
-                s.rollout_routed_experts = r.routed_experts
-            if self.codec is not None:
-                if self.cfg.stop_strings:
-                    from ..data.tokenizer import cut_at_stop_strings
-
-                    n = cut_at_stop_strings(self.codec, list(r.output), self.cfg.stop_strings)
-                    if n is not None and n < len(r.output):      # generated past the stop string: drop the rest
-                        s.tokens = list(r.prompt) + list(r.output[:n])
-                        s.response_length, s.rollout_log_probs = n, list(r.logprobs[:n])
-                        s.status = SampleStatus.COMPLETED
-                s.response = self.codec.decode(s.tokens[len(s.tokens) - s.response_length:]) if s.response_length else ""
-            s.reward = self.reward_fn(s)
+            self._fill_sample(s, r)
         return mine
+
+    def _fill_sample(self, s, r, score: bool = True):
+        """Copy a finished (or aborted) engine request into its sample and score it."""
+        s.tokens = list(r.prompt) + list(r.output)
+        s.response_length = len(r.output)
+        s.rollout_log_probs = list(r.logprobs)
+        s.weight_versions = sorted(set(list(s.weight_versions) + list(r.weight_versions)))
+        if r.finish_reason == "abort":
+            s.status = SampleStatus.ABORTED
+        else:
+            s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
+        if r.routed_experts:
+            s.rollout_routed_experts = r.routed_experts
+        if self.codec is not None:
+            if self.cfg.stop_strings and r.finish_reason != "abort":
+                from ..data.tokenizer import cut_at_stop_strings
+
+                n = cut_at_stop_strings(self.codec, list(r.output), self.cfg.stop_strings)
+                if n is not None and n < len(r.output):      # generated past the stop string: drop the rest
+                    s.tokens = list(r.prompt) + list(r.output[:n])
+                    s.response_length, s.rollout_log_probs = n, list(r.logprobs[:n])
+                    s.status = SampleStatus.COMPLETED
+            s.response = self.codec.decode(s.tokens[len(s.tokens) - s.response_length:]) if s.response_length else ""
+        if score and r.finish_reason != "abort":
+            s.reward = self.reward_fn(s)
+
+    def _generate_streaming(self, per: int, over: int, sp) -> list:
+        """Over-sampled generation with early stop: ``over`` prompt groups are in flight, finished groups are scored
+        and filtered as they complete, and once ``per`` groups are kept everything still running is aborted.  With
+        ``partial_rollout`` the aborted groups go back to the rollout buffer with what they generated so far and the
+        next rollout step continues them (their earlier tokens leave the loss with
+        ``mask_offpolicy_in_partial_rollout``)."""
+        from ..rollout.filters import FilterOutput
+
+        cfg, eng = self.cfg, self.engine
+        kept, inflight, by_rid = [], {}, {}
+        stats = {"generated_groups": 0, "dropped_groups": 0, "rounds": 0, "aborted_samples": 0, "resumed_samples": 0}
+
+        def close_group(g):
+            out = self.group_filter(g) if self.group_filter is not None else FilterOutput(True)
+            if out.keep if isinstance(out, FilterOutput) else bool(out):
+                kept.append(g)
+            else:
+                stats["dropped_groups"] += 1
+                why = getattr(out, "reason", None)
+                if why:
+                    stats[f"drop/{why}"] = stats.get(f"drop/{why}", 0) + 1
+
+        def submit(n):
+            stats["rounds"] += 1
+            ds = self.data_source
+            if hasattr(ds, "get_buffered"):      # my buffered (aborted) groups first, then my slice of fresh ones
+                mine = ds.get_buffered(n)
+                fresh = n - len(mine)
+                if fresh:
+                    mine += ds.get_fresh(fresh * self.num_engines)[self.engine_id * fresh:(self.engine_id + 1) * fresh]
+            else:
+                mine = ds.get_samples(n * self.num_engines)[self.engine_id * n:(self.engine_id + 1) * n]
+            stats["generated_groups"] += len(mine)
+            for g in mine:
+                todo = 0
+                for smp in g:
+                    if smp.status in (SampleStatus.COMPLETED, SampleStatus.TRUNCATED) and smp.response_length:
+                        continue          # finished before its group was aborted: keeps its response
+                    n_prompt = len(smp.tokens) - smp.response_length
+                    resumed = smp.response_length > 0
+                    if resumed:
+                        stats["resumed_samples"] += 1
+                        smp.metadata["resumed_tokens"] = smp.response_length
+                    im = smp.multimodal_train_inputs
+                    rid = eng.add_request(smp.tokens[:n_prompt], sp, smp.group_index,
+                                          resume_output=smp.tokens[n_prompt:] if resumed else None,
+                                          resume_logprobs=smp.rollout_log_probs if resumed else None,
+                                          **({k: im.get(k) for k in ("pixel_patches", "grid_thw", "image_embeds")} if im else {}))
+                    by_rid[rid] = smp
+                    todo += 1
+                if todo:
+                    inflight[g[0].group_index] = [g, todo]
+                else:
+                    close_group(g)
+
+        submit(over)
+        while len(kept) < per:
+            if not eng.has_work:
+                if stats["rounds"] >= 64:
+                    raise RuntimeError(f"over-sampling: only {len(kept)}/{per} groups passed the filter after 64 rounds")
+                submit(over)
+                continue
+            for r in eng.step():
+                smp = by_rid.pop(r.rid)
+                self._fill_sample(smp, r)
+                n_old = smp.metadata.pop("resumed_tokens", 0)
+                if n_old and cfg.mask_offpolicy_in_partial_rollout:
+                    smp.loss_mask = [0] * n_old + [1] * (smp.response_length - n_old)
+                ent = inflight[smp.group_index]
+                ent[1] -= 1
+                if ent[1] == 0:
+                    del inflight[smp.group_index]
+                    close_group(ent[0])
+        surplus = kept[per:]
+        # the batch is full: stop what is still running
+        give_back = list(surplus)
+        for r in eng.abort_all():
+            smp = by_rid.pop(r.rid, None)
+            if smp is None:
+                continue
+            self._fill_sample(smp, r, score=False)
+            smp.metadata.pop("resumed_tokens", None)
+            smp.abort_count += 1
+            stats["aborted_samples"] += 1
+        limit = cfg.partial_rollout_max_aborted_count
+        for g, _ in inflight.values():
+            if cfg.partial_rollout and (limit is None or all(x.abort_count <= limit for x in g)):
+                give_back.append(g)
+            else:
+                stats["dropped_groups"] += 1
+        if give_back:
+            if hasattr(self.data_source, "buffer"):
+                self.data_source.add_samples(give_back)
+            else:
+                stats["dropped_groups"] += len(give_back)
+        self.sampling_stats = stats
+        return kept[:per]
 
     def generate(self, rollout_id: int) -> list[Sample]:
         """One rollout batch.  With a group filter (``dynamic_sampling_filter_path``, e.g.
@@ -381,7 +502,10 @@ class ColocatedGRPO:
         per = cfg.rollout_batch_size // self.num_engines
         sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                             max_new_tokens=cfg.max_response_len, stop_token_ids=tuple(cfg.stop_token_ids or ()))
-        if self.group_filter is None:
+        over_n = (cfg.over_sampling_batch_size or cfg.rollout_batch_size) // self.num_engines
+        if self.custom_generate is None and (cfg.partial_rollout or (self.group_filter is None and over_n > per)):
+            groups = self._generate_streaming(per, max(per, over_n), sp)
+        elif self.group_filter is None:
             groups = self._generate_groups(per, sp)
             self.sampling_stats = {}
         else:

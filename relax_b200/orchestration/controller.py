@@ -67,7 +67,8 @@ class Controller:
             if _get(args, "lora_target_modules", None):
                 tm = args.lora_target_modules
                 kw["target_modules"] = tuple(tm.split(",")) if isinstance(tm, str) else tuple(tm)
-            self.train_cfg.lora = LoRAConfig(rank=args.lora_rank, alpha=float(_get(args, "lora_alpha", None) or 2.0 * args.lora_rank), **kw)
+            self.train_cfg.lora = LoRAConfig(rank=args.lora_rank, alpha=float(_get(args, "lora_alpha", None) or 2.0 * args.lora_rank),
+                                             dropout=float(_get(args, "lora_dropout", None) or 0.0), **kw)
         self.mode = self._pick_mode()
         self._stop = False
         self.profiler = TrainProfiler(_get(args, "profile_dir", args.save and os.path.join(args.save, "profile")),
@@ -228,6 +229,10 @@ class Controller:
                 system_prompt=_get(a, "system_prompt", None),
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
+                partial_rollout=bool(_get(a, "partial_rollout", False)),
+                mask_offpolicy_in_partial_rollout=bool(_get(a, "mask_offpolicy_in_partial_rollout", False)),
+                partial_rollout_max_aborted_count=_get(a, "partial_rollout_max_aborted_count", None),
+                buffer_filter_path=_get(a, "buffer_filter_path", None),
                 stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
                 stop_strings=tuple(_get(a, "rollout_stop", None) or ()), critic_lr=_get(a, "critic_lr", None), use_health_check=bool(_get(a, "use_health_check", False)),
                 max_consecutive_failures=_get(a, "rollout_health_check_max_consecutive_failures", None) or 3, num_critic_only_steps=_get(a, "num_critic_only_steps", 0) or 0,

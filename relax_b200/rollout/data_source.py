@@ -183,6 +183,14 @@ class RolloutDataSourceWithBuffer(RolloutDataSource):
             out += super().get_samples(num_groups - len(out))
         return out
 
+    def get_buffered(self, num_groups: int) -> list:
+        """Up to ``num_groups`` groups from the buffer only (the buffer is local to an engine replica)."""
+        return self.buffer_filter(self.buffer, num_groups)
+
+    def get_fresh(self, num_groups: int) -> list:
+        """Fresh prompt groups from the dataset, bypassing the buffer (the global stream every replica slices)."""
+        return super().get_samples(num_groups)
+
     def add_samples(self, groups):
         for g in groups:
             if len(g) != self.n:

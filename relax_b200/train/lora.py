@@ -31,6 +31,7 @@ class LoRAConfig:
     alpha: float = 32.0
     target_modules: Tuple[str, ...] = DEFAULT_TARGETS
     seed: int = 1234
+    dropout: float = 0.0          # on the adapter's input, while gradients are enabled (peft's lora_dropout)
 
     @property
     def scale(self) -> float:
@@ -60,6 +61,7 @@ def apply_lora(model, cfg: LoRAConfig) -> List[str]:
         mod.lora_A = nn.Parameter(a.to(device=w.device, dtype=w.dtype))
         mod.lora_B = nn.Parameter(torch.zeros(out_f, cfg.rank, device=w.device, dtype=w.dtype))
         mod.lora_scale = cfg.scale
+        mod.lora_dropout = float(cfg.dropout)
         # the replicated factor sees a different token / feature shard on every TP rank: its gradient is a partial sum
         (mod.lora_A if leaf in _COLUMN_PARALLEL else mod.lora_B).tp_replicated = True
         names.append(name)
@@ -72,6 +74,9 @@ def lora_delta(mod, x, tp_group, column_parallel: bool):
     linear receives (a sequence shard for column-parallel layers, feature-sharded rows for row-parallel)."""
     if not hasattr(mod, "lora_A"):
         return None
+    p_drop = getattr(mod, "lora_dropout", 0.0)
+    if p_drop > 0.0 and torch.is_grad_enabled():
+        x = torch.nn.functional.dropout(x, p_drop, training=True)
     xa = torch.nn.functional.linear(x, mod.lora_A)              # [rows, r]
     if column_parallel:
         xa = TP.gather_seq(xa, tp_group)                         # rows of every rank

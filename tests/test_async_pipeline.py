@@ -199,3 +199,45 @@ def test_rollout_engine_monitor_and_fault_injection():
     assert maybe_inject_fault(True, True, 2, mon)
     mon.poll_once(); mon.poll_once()
     assert recreated == [1, 0]
+
+
+def test_partial_rollout_aborts_resumes_and_masks_offpolicy_tokens():
+    """Over-sampling with early stop: groups still running when the batch is full are aborted into the rollout
+    buffer with their partial responses, the next step continues them, and (with the mask flag) only the tokens of
+    the current policy stay in the loss."""
+    import torch
+
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+    from relax_b200.types import SampleStatus
+
+    torch.manual_seed(0)
+    cfg = ColocateConfig(
+        model=get_config("tiny"),
+        train=TrainConfig(advantage_estimator="grpo", n_samples_per_prompt=2, global_batch_size=8, max_tokens_per_gpu=2048,
+                          loss=LossConfig(eps_clip=0.2), optim=OptimizerConfig(lr=1e-5)),
+        rollout_batch_size=4, over_sampling_batch_size=8, partial_rollout=True, mask_offpolicy_in_partial_rollout=True,
+        prompt_len=8, max_response_len=160, temperature=1.0, rm_type="parity", eos_token_id=3, seed=0, rollout_seed=5,
+        stop_token_ids=list(range(0, 1024, 48)), kv_blocks=512)     # responses end at random lengths: some groups are mid-way when 4 are done
+    run = ColocatedGRPO(cfg)
+    first = run.generate(0)
+    assert len(first) == 8 and all(s.status in (SampleStatus.COMPLETED, SampleStatus.TRUNCATED) for s in first)
+    st = run.sampling_stats
+    assert st["aborted_samples"] > 0 and len(run.data_source.buffer) > 0
+    partial = {s.index: s.response_length for g in run.data_source.buffer for s in g if s.status == SampleStatus.ABORTED}
+    assert any(n > 0 for n in partial.values()), "at least one aborted sample had generated tokens"
+    assert run.engine.bm.num_free == run.engine.bm.num_blocks
+    second = run.generate(1)
+    assert run.sampling_stats["resumed_samples"] > 0
+    resumed = [s for s in second if s.index in partial and partial[s.index] > 0]
+    assert resumed, "buffered groups are served first"
+    for s in resumed:
+        n_old = partial[s.index]
+        assert s.response_length >= n_old and s.loss_mask[:n_old] == [0] * n_old and all(s.loss_mask[n_old:])
+        assert len(s.rollout_log_probs) == s.response_length
+    m = run.step()          # a full step on top (generation + training) still works with the buffer in place
+    assert m["grad_norm"] >= 0
+    run.close()
