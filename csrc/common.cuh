@@ -100,6 +100,12 @@ __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, 
   return false;
 }
 
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// wait: every grid this one depends on has completed and its writes are visible (no-op without the launch attribute)
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// the next kernel in the stream may start its pre-wait part once every CTA of this grid has passed this point
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------- TMA (no multicast anywhere)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

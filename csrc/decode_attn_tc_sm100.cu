@@ -54,6 +54,7 @@ struct DecodeTcParams {
 __global__ void __launch_bounds__(DT_THREADS, 2)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap tma_k, const __grid_constant__ CUtensorMap tma_v,
                       const DecodeTcParams p) {
+  griddep_wait();                    // q and the new K/V rows come from the kernels before this one
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DT_SMEM_BAR);
   // S, P and the "PV done" signal are double buffered (index = tile & 1) so that the softmax of tile j+1
@@ -339,7 +340,7 @@ extern "C" int rb_decode_attn_tc(const void* q, const void* kc, const void* vc, 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.err = err;
   dim3 grid(B, Hkv, splits);
-  decode_attn_tc_kernel<<<grid, DT_THREADS, DT_SMEM_TOTAL, st>>>(tk, tv, p);
+  launch_pdl(decode_attn_tc_kernel, dim3(grid), dim3(DT_THREADS), DT_SMEM_TOTAL, st, tk, tv, p);
   if (splits > 1) decode_attn_tc_combine_kernel<<<B * Hq, DT_D, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out, splits);
   rb_note_launch(splits > 1 ? 2 : 1);
   return (int)cudaGetLastError();

@@ -67,6 +67,7 @@ __global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict_
   __shared__ float red[RPB * (TPR / 32) + 1];
   const int t = threadIdx.x % TPR;
   const int rib = threadIdx.x / TPR;
+  griddep_wait();                    // launched with programmatic stream serialization: x / res come from the kernel before
   for (int row0 = blockIdx.x * RPB; row0 < rows; row0 += gridDim.x * RPB) {
     const int row = row0 + rib;
     const bool live = row < rows;
@@ -556,11 +557,11 @@ extern "C" int rb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
     const T *xx = (const T*)x, *rr = (const T*)res, *ww = (const T*)w;
     T *yy = (T*)y, *ro = (T*)r_out;
     if (res) {
-      if (small) rmsnorm_fwd_kernel<T, 32, true><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
-      else rmsnorm_fwd_kernel<T, 256, true><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+      if (small) launch_pdl(rmsnorm_fwd_kernel<T, 32, true>, dim3(grid), dim3(256), 0, st, xx, rr, ww, yy, ro, rows, cols, eps);
+      else launch_pdl(rmsnorm_fwd_kernel<T, 256, true>, dim3(grid), dim3(256), 0, st, xx, rr, ww, yy, ro, rows, cols, eps);
     } else {
-      if (small) rmsnorm_fwd_kernel<T, 32, false><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
-      else rmsnorm_fwd_kernel<T, 256, false><<<grid, 256, 0, st>>>(xx, rr, ww, yy, ro, rows, cols, eps);
+      if (small) launch_pdl(rmsnorm_fwd_kernel<T, 32, false>, dim3(grid), dim3(256), 0, st, xx, rr, ww, yy, ro, rows, cols, eps);
+      else launch_pdl(rmsnorm_fwd_kernel<T, 256, false>, dim3(grid), dim3(256), 0, st, xx, rr, ww, yy, ro, rows, cols, eps);
     }
   });
   rb_note_launch(1);

@@ -132,18 +132,15 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (!(warp == 0 && lane == 0)) griddep_wait();   // (the producer waits after it has started the weight stream)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tma_w);
       tma_prefetch_desc(&tma_x);
-      int s = 0;
-      uint32_t ph = 0;
-      for (int k = k_lo; k < k_hi; ++k) {
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) break;
+      auto load_w = [&](int s, int k) {
         uint8_t* sw = smem + s * C::kStageBytes;
-        uint8_t* sx = sw + C::kWBytes;
         mbar_expect_tx(&full_bar[s], C::kStageBytes);
         if (!p.swiglu) {
           tma_load_2d(sw, &tma_w, &full_bar[s], k * BK, tile * BM);
@@ -151,7 +148,22 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_const
           tma_load_2d(sw, &tma_w, &full_bar[s], k * BK, tile * 64);
           tma_load_2d(sw + 64 * 128, &tma_w, &full_bar[s], k * BK, F + tile * 64);
         }
-        tma_load_2d(sx, &tma_x, &full_bar[s], k * BK, 0);
+      };
+      auto load_x = [&](int s, int k) {
+        tma_load_2d(smem + s * C::kStageBytes + C::kWBytes, &tma_x, &full_bar[s], k * BK, 0);
+      };
+      // the weights do not depend on the kernel before this one: fill the ring with W tiles first, wait for the
+      // predecessor, then add the token tiles (the stage's barrier counts both)
+      const int pre = min(kStages, k_hi - k_lo);
+      for (int i = 0; i < pre; ++i) load_w(i, k_lo + i);
+      griddep_wait();
+      for (int i = 0; i < pre; ++i) load_x(i, k_lo + i);
+      int s = pre == kStages ? 0 : pre;
+      uint32_t ph = pre == kStages ? 1 : 0;
+      for (int k = k_lo + pre; k < k_hi; ++k) {
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, p.err)) break;
+        load_w(s, k);
+        load_x(s, k);
         if (++s == kStages) { s = 0; ph ^= 1; }
       }
     }
@@ -302,13 +314,15 @@ static int launch(const CUtensorMap& tw, const CUtensorMap& tx, const Params& p,
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = C::kTotal;
   cfg.stream = st;
-  cudaLaunchAttribute at[1];
+  cudaLaunchAttribute at[2];
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = p.S;
   at[0].val.clusterDim.y = 1;
   at[0].val.clusterDim.z = 1;
+  at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw, tx, p);
   rb_note_launch(1);
   return e != cudaSuccess ? static_cast<int>(e) : static_cast<int>(cudaGetLastError());

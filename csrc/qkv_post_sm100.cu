@@ -27,6 +27,7 @@ __global__ void qkv_post_kernel(const __nv_bfloat16* __restrict__ qkv, int ld, c
   const int heads = nq + 2 * nkv;
   const int lane = threadIdx.x & 31;
   const long long w = blockIdx.x * static_cast<long long>(blockDim.x >> 5) + (threadIdx.x >> 5);
+  griddep_wait();                    // qkv comes from the GEMM before this kernel
   if (w >= static_cast<long long>(T) * heads) return;
   const int t = static_cast<int>(w / heads), h = static_cast<int>(w % heads);
   const uint2 raw = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(t) * ld + h * 128 + lane * 4);
@@ -113,13 +114,13 @@ extern "C" int rb_qkv_post(const void* qkv, int ld, const void* qw, const void* 
   const int grid = static_cast<int>((warps + 7) / 8);
   auto* x = reinterpret_cast<const __nv_bfloat16*>(qkv);
   if (qw)
-    qkv_post_kernel<true><<<grid, 256, 0, st>>>(x, ld, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, cos_t, sin_t,
-                                                (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
-                                                (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, T, nq, nkv, eps);
+    launch_pdl(qkv_post_kernel<true>, dim3(grid), dim3(256), 0, st, x, ld, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw,
+               cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
+               (__nv_bfloat16*)v_cache, slots, T, nq, nkv, eps);
   else
-    qkv_post_kernel<false><<<grid, 256, 0, st>>>(x, ld, nullptr, nullptr, cos_t, sin_t, (__nv_bfloat16*)q_out,
-                                                 (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
-                                                 (__nv_bfloat16*)v_cache, slots, T, nq, nkv, eps);
+    launch_pdl(qkv_post_kernel<false>, dim3(grid), dim3(256), 0, st, x, ld, (const __nv_bfloat16*)nullptr,
+               (const __nv_bfloat16*)nullptr, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
+               (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slots, T, nq, nkv, eps);
   rb_note_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -202,13 +202,28 @@ _DECODE_GEMM = os.environ.get("RELAX_B200_DECODE_GEMM", "1") == "1"
 
 def _decode_gemm(x, w, swiglu: bool):
     """Weight-streaming decode GEMM (csrc/gemm_decode_sm100.cu) when the shape is in its range, else None."""
-    if not _DECODE_GEMM or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] > 256:
-        return None
+    if not _DECODE_GEMM or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.shape[0] > 128:
+        return None     # above 128 rows the 2-stage ring of the 256-column variant loses to the other paths (measured)
     if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16:
         return None
     N = w.shape[0]
     out = torch.empty(x.shape[0], N // 2 if swiglu else N, dtype=x.dtype, device=x.device)
     if _load().decode_gemm(x, w, out, swiglu, 0, err_flag(x.device)):
+        return out
+    return None
+
+
+def _wide_pair_gemm(x, w):
+    """129..256 token rows against a wide weight (N >= 6144: at least 24 pair tiles of 256 x 256): one row of CTA-pair
+    tiles of the training GEMM beats split-K here (measured on B200 at 160 and 256 rows: 33 vs 52 us at N = 12288,
+    31 vs 50 us at N = 6144; below that split-K wins).  Returns None when the shape is outside that range."""
+    M, K = x.shape
+    N = w.shape[0]
+    if not (_PAIR and 128 < M <= 256 and N >= 6144 and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and w.is_contiguous()):
+        return None
+    out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if _load().gemm_pair(x, w, out, M, N, K, x.stride(0), w.stride(0), N, False, False, False, 256, err_flag(x.device)):
         return out
     return None
 
@@ -223,6 +238,8 @@ def matmul_nt_skinny(x, w, bias=None, residual=None):
     C = _load()
     if bias is None and residual is None:
         y = _decode_gemm(x, w, False)
+        if y is None:
+            y = _wide_pair_gemm(x, w)
         if y is not None:
             return y
     splits, bn = C.gemm_splitk_plan(M, N, K)
@@ -245,6 +262,9 @@ def linear_swiglu_skinny(x, w):
     y = _decode_gemm(x, w, True)
     if y is not None:
         return y
+    y = _wide_pair_gemm(x, w)
+    if y is not None:
+        return swiglu(y)
     splits, bn = C.gemm_splitk_plan(M, N, K)
     if splits <= 1 or x.dtype != torch.bfloat16 or (N // 2) % 4:
         return swiglu(linear(x, w))
