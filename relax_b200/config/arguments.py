@@ -276,7 +276,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
-    "--ref-ckpt-step": (_R, "the reference is loaded from --ref-load as a whole"),
     "--num-labels": (_R, "set the classifier width through the model preset (num_classes)"),
     "--problem-type": (_R, "single-label classification only"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),

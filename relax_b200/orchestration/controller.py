@@ -302,6 +302,13 @@ class Controller:
             H.load_hf_into_model(ref, self.model_cfg, actor.ps, actor.model)
             actor.backup("ref", to_host=not actor.snapshots["ref"].is_cuda and actor.device.type == "cuda")
             actor.param_buf.copy_(keep)
+        elif ref and ref != src and os.path.isdir(ref) and dist_ckpt.is_dist_checkpoint(ref) and "ref" in actor.snapshots:
+            # --ref-load <training checkpoint dir> [--ref-ckpt-step N]: the reference is the policy of iteration N (default:
+            # the latest) of another run (relax/backends/megatron/checkpoint.py loads the reference the same way)
+            keep = actor.param_buf.clone()
+            dist_ckpt.load_checkpoint(ref, self.model_cfg, actor.ps, actor.model, None, iteration=_get(a, "ref_ckpt_step", None))
+            actor.backup("ref", to_host=not actor.snapshots["ref"].is_cuda and actor.device.type == "cuda")
+            actor.param_buf.copy_(keep)
 
     def _maybe_resume(self):
         a, actor = self.args, self._actor()

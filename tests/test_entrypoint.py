@@ -161,3 +161,27 @@ def test_openapi_chat_routes_exist_on_a_live_server():
     finally:
         srv.shutdown()
         srv.server_close()
+
+
+def test_reference_from_a_training_checkpoint_step(tmp_path):
+    """``--ref-load <checkpoint dir> --ref-ckpt-step N``: the frozen reference is the policy saved at iteration N of
+    another run, not the current initialisation."""
+    import torch
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    save = str(tmp_path / "ckpt")
+    assert main(COMMON + ["--num-rollout", "2", "--save", save, "--save-interval", "1", "--colocate", "--lr", "1e-2"]) == 0
+    a = parse_args(COMMON + ["--num-rollout", "1", "--colocate", "--ref-load", save, "--ref-ckpt-step", "0", "--kl-loss-coef", "0.01",
+                             "--use-kl-loss"])
+    c = Controller(a, device="cpu")
+    c._maybe_resume()
+    actor = c.runner.actor
+    saved = dist_ckpt.load_full_tensors(dist_ckpt.iter_dir(save, 0))
+    name, p = next((n, p) for n, p in actor.model.named_parameters() if n.endswith("linear_proj.weight"))
+    actor.switch_model("ref")
+    assert torch.allclose(p.detach(), saved[name].to(p.dtype))
+    actor.switch_model("actor")
+    assert not torch.allclose(p.detach(), saved[name].to(p.dtype)), "the policy itself keeps its own initialisation"
+    c.runner.close()
