@@ -63,6 +63,9 @@ def parse():
     ap.add_argument("--time-budget-s", type=float, default=float(os.environ.get("RELAX_B200_BENCH_BUDGET_S", "780")),
                     help="wall-clock budget of the whole process; warm-up / timed step counts shrink to fit (0: no budget)")
     ap.add_argument("--decode-window", type=int, default=None, help="decode steps per host round trip in the rollout engine")
+    ap.add_argument("--profile-kernels", type=int, default=0,
+                    help="debug: after the timed steps run ONE more step under torch.profiler and print rank 0's top N kernels "
+                         "by device time to stderr (the extra step is not part of any reported number)")
     return ap.parse_args()
 
 
@@ -218,6 +221,8 @@ def main():
     sampler = ClockSampler(local)
     sampler.start()
     C.reset_launch_count()
+    mem0 = torch.cuda.memory_stats(dev)
+    torch.cuda.reset_peak_memory_stats(dev)
     ev0 = torch.cuda.Event(enable_timing=True)
     step_events = []
     torch.cuda.synchronize()
@@ -225,6 +230,16 @@ def main():
     ev0.record()
     acc = {"resp": 0, "tot": 0, "sync_ms": [], "losses": [], "h2d": 0, "d2h": 0, "parts": {}, "lp_diff": None, "steps": 0,
            "wall": 0.0}
+
+    def allocator_summary():
+        """Caching-allocator traffic inside the timed region: device allocations (cudaMalloc calls) and retries
+        (cache flushes under memory pressure) stall the host, so they explain device idle time."""
+        m = torch.cuda.memory_stats(dev)
+        return {"device_allocs": int(m.get("num_device_alloc", 0) - mem0.get("num_device_alloc", 0)),
+                "device_frees": int(m.get("num_device_free", 0) - mem0.get("num_device_free", 0)),
+                "alloc_retries": int(m.get("num_alloc_retries", 0) - mem0.get("num_alloc_retries", 0)),
+                "peak_allocated_gb": round(m.get("allocated_bytes.all.peak", 0) / 2 ** 30, 1),
+                "peak_reserved_gb": round(m.get("reserved_bytes.all.peak", 0) / 2 ** 30, 1)}
 
     def build_line(dev_s, wall, resp_all, tot_all, launches, n_steps, partial=False):
         value = resp_all / max(dev_s, 1e-9)
@@ -250,6 +265,7 @@ def main():
             "e2e": {"value": round(resp_all / max(wall, 1e-9), 2), "unit": "tokens/s", "h2d_bytes_per_step": acc["h2d"] // max(1, n_steps),
                     "d2h_bytes_per_step": acc["d2h"] // max(1, n_steps)},
             "gpu_launches": launches,
+            "allocator": allocator_summary(),
             "clocks": sampler.summary(),
         }
         if partial:
@@ -324,6 +340,38 @@ def main():
         printed["done"] = True
         print(json.dumps(build_line(dev_s, wall, resp_all, tot_all, launches, n_steps)))
     sys.stdout.flush()
+    if args.profile_kernels > 0:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            t_p = time.perf_counter()
+            run.step()
+            torch.cuda.synchronize()
+            t_p = time.perf_counter() - t_p
+        if rank == 0:
+            rows = sorted(prof.key_averages(), key=lambda e: -e.device_time_total)
+            tot = sum(e.device_time_total for e in rows)
+            print(f"[profile] one extra step under the profiler: {t_p:.3f} s wall, {tot / 1e6:.3f} s of kernel time on rank 0", file=sys.stderr)
+            for e in rows[:args.profile_kernels]:
+                print(f"[profile] {e.device_time_total / 1e3:10.2f} ms {100 * e.device_time_total / max(tot, 1):5.1f}% x{e.count:6d}  {e.key[:110]}",
+                      file=sys.stderr)
+            # where the device sat idle: for every kernel, the time since the latest end of any earlier kernel
+            from torch.autograd import DeviceType
+
+            ks = sorted((e for e in prof.events() if e.device_type == DeviceType.CUDA and e.time_range is not None),
+                        key=lambda e: e.time_range.start)
+            idle, last_end = {}, None
+            for e in ks:
+                st, en = e.time_range.start, e.time_range.end
+                if last_end is not None and st > last_end:
+                    g = idle.setdefault(e.name, [0.0, 0])
+                    g[0] += st - last_end
+                    g[1] += 1
+                last_end = en if last_end is None else max(last_end, en)
+            tot_idle = sum(v[0] for v in idle.values())
+            print(f"[profile] device idle between kernels: {tot_idle / 1e6:.3f} s; by the kernel that ended the gap:", file=sys.stderr)
+            for name, (us, n) in sorted(idle.items(), key=lambda kv: -kv[1][0])[:12]:
+                print(f"[profile]   idle {us / 1e3:9.2f} ms before x{n:6d} (mean {us / max(n, 1):7.1f} us)  {name[:100]}", file=sys.stderr)
     run.close()
     if world > 1:
         from relax_b200.parallel.state import shutdown_distributed
