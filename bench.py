@@ -360,18 +360,19 @@ def main():
 
             ks = sorted((e for e in prof.events() if e.device_type == DeviceType.CUDA and e.time_range is not None),
                         key=lambda e: e.time_range.start)
-            idle, last_end = {}, None
+            idle, last_end, last_name = {}, None, ""
             for e in ks:
                 st, en = e.time_range.start, e.time_range.end
                 if last_end is not None and st > last_end:
-                    g = idle.setdefault(e.name, [0.0, 0])
+                    g = idle.setdefault(last_name[:48] + "  ->  " + e.name[:48], [0.0, 0])
                     g[0] += st - last_end
                     g[1] += 1
-                last_end = en if last_end is None else max(last_end, en)
+                if last_end is None or en >= last_end:
+                    last_end, last_name = en, e.name
             tot_idle = sum(v[0] for v in idle.values())
-            print(f"[profile] device idle between kernels: {tot_idle / 1e6:.3f} s; by the kernel that ended the gap:", file=sys.stderr)
-            for name, (us, n) in sorted(idle.items(), key=lambda kv: -kv[1][0])[:12]:
-                print(f"[profile]   idle {us / 1e3:9.2f} ms before x{n:6d} (mean {us / max(n, 1):7.1f} us)  {name[:100]}", file=sys.stderr)
+            print(f"[profile] device idle between kernels: {tot_idle / 1e6:.3f} s; by (last kernel before the gap -> first after):", file=sys.stderr)
+            for name, (us, n) in sorted(idle.items(), key=lambda kv: -kv[1][0])[:16]:
+                print(f"[profile]   idle {us / 1e3:9.2f} ms x{n:6d} (mean {us / max(n, 1):7.1f} us)  {name}", file=sys.stderr)
     run.close()
     if world > 1:
         from relax_b200.parallel.state import shutdown_distributed

@@ -585,6 +585,14 @@ class TrainActor:
         t0 = time.perf_counter()
         n = len(batch["tokens"])
         resp = [int(r) for r in batch["response_lengths"]]
+        # token-level list fields go to the device ONCE (one flat copy each, then views): the micro-batch loops below
+        # read them several times, and a host list -> tensor conversion per sample per pass leaves the device idle
+        for key in ("loss_masks", "rollout_log_probs"):
+            v = batch.get(key)
+            if v is not None and len(v) and not torch.is_tensor(v[0]):
+                lens = [len(x) for x in v]
+                flat = torch.tensor([y for x in v for y in x], dtype=torch.float32).to(dev, non_blocking=True)
+                batch[key] = list(torch.split(flat, lens))
         masks = [torch.as_tensor(m, dtype=torch.float32, device=dev) for m in batch["loss_masks"]]
 
         with self.timer.span("ref_log_probs"):
