@@ -310,6 +310,29 @@ def config_from_hf(path: str) -> ModelConfig:
     return ModelConfig(**kw)
 
 
+def validate_against_hf(cfg: ModelConfig, path: str) -> None:
+    """Stop when the model the flags / preset describe is not the model whose ``config.json`` sits under ``path``
+    (relax/backends/megatron/arguments.py _hf_validate_args :209-263 compares the same fields): a mismatch would
+    otherwise surface as a shape error in the middle of the load or, worse, as silently wrong rotary / norm constants."""
+    if not os.path.isfile(os.path.join(path, "config.json")):
+        return
+    hf = config_from_hf(path)
+    fields = ["hidden_size", "num_attention_heads", "num_query_groups", "num_layers", "head_dim", "vocab_size",
+              "tie_word_embeddings", "rope_theta", "rms_norm_eps"]
+    if cfg.is_moe or hf.is_moe:
+        fields += ["num_experts", "moe_top_k", "moe_ffn_hidden_size", "moe_shared_expert_ffn"]
+    if not cfg.is_moe or cfg.moe_first_dense_layers > 0:
+        fields.append("ffn_hidden_size")
+    errors = []
+    for f in fields:
+        a, b = getattr(cfg, f), getattr(hf, f)
+        same = abs(float(a) - float(b)) <= 1e-12 * max(1.0, abs(float(b))) if isinstance(a, float) or isinstance(b, float) else a == b
+        if not same:
+            errors.append(f"{f}: {a} here, {b} in {os.path.join(path, 'config.json')}")
+    if errors:
+        raise ValueError("the model configuration does not match the Hugging Face checkpoint: " + "; ".join(errors))
+
+
 def load_hf_into_rollout(path: str, cfg: ModelConfig, rollout_weights) -> None:
     """Fill a rollout engine's parameter buffer straight from a Hugging Face checkpoint (a grader or any serving-only
     model that has no trainer): HF names -> Megatron layout -> the block-copy plan the weight sync uses."""

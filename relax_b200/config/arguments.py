@@ -64,6 +64,7 @@ FLAGS: dict[str, list] = {
         ("--load", dict(type=str, default=None)), ("--save", dict(type=str, default=None)),
         ("--save-interval", dict(type=int, default=None)), ("--hf-checkpoint", dict(type=str, default=None)),
         ("--ref-load", dict(type=str, default=None)), ("--ref-ckpt-step", dict(type=int, default=None)),
+        ("--skip-hf-validate", _b()),       # do not compare the model shape with the config.json under --hf-checkpoint
         ("--ref-update-interval", dict(type=int, default=None)),
         ("--critic-load", dict(type=str, default=None)), ("--critic-save", dict(type=str, default=None)),
         ("--save-hf", dict(type=str, default=None)), ("--save-hf-dtype", dict(type=str, default="bf16", choices=["bf16", "fp8"])),

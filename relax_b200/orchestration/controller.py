@@ -281,6 +281,8 @@ class Controller:
         if actor is None:
             return
         src = _get(a, "hf_checkpoint", None)
+        if src and "://" not in src and os.path.isdir(src) and not _get(a, "skip_hf_validate", False):
+            H.validate_against_hf(self.model_cfg, src)
         if src and ("://" in src or H.is_hf_checkpoint(src)):
             H.load_hf_into_model(src, self.model_cfg, actor.ps, actor.model, strict=not _get(a, "only_load_weight", False))
             if actor.optimizer is not None:

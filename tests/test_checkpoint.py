@@ -168,3 +168,19 @@ def test_hf_checkpoint_loads_into_tp2_and_controller_flags(tmp_path):
     assert exported and H.is_hf_checkpoint(str(exported[0]))
     back = H.hf_to_megatron_state(cfg, H.load_hf_checkpoint(str(exported[0])))
     assert set(back) == {k for k, _ in src.named_parameters()}
+
+
+def test_model_flags_are_checked_against_the_hf_config(tmp_path):
+    """A model shape that differs from the ``config.json`` under ``--hf-checkpoint`` is refused with the list of
+    differing fields; the matching one passes."""
+    import pytest
+
+    for name in ("tiny", "tiny-moe"):
+        cfg = get_config(name)
+        m = GPTModel(cfg, seed=1)
+        d = str(tmp_path / name)
+        HF.save_hf_checkpoint(d, cfg, HF.convert_state_to_hf(cfg, {k: v.detach() for k, v in m.named_parameters()}))
+        HF.validate_against_hf(cfg, d)
+        with pytest.raises(ValueError, match="rope_theta.*|num_layers.*"):
+            HF.validate_against_hf(get_config(name, num_layers=cfg.num_layers + 1, rope_theta=5e5), d)
+    HF.validate_against_hf(get_config("tiny"), str(tmp_path / "no-such-dir"))        # nothing to compare with: no error
