@@ -228,10 +228,22 @@ def sft_loss(log_probs: torch.Tensor, b: LossBatch, cfg: LossConfig):
     return loss, {"loss": loss.detach()}
 
 
-def seq_cls_loss(logits: torch.Tensor, labels: torch.Tensor):
-    """Sum over samples of the class cross entropy (the caller divides by the global batch size, as for the
-    other per-sample losses) and the number of correct predictions
-    (relax/backends/megatron/loss.py :1301-1383)."""
+def seq_cls_loss(logits: torch.Tensor, labels: torch.Tensor, problem_type: str = "single_label_classification",
+                 threshold: float = 0.5):
+    """Sum over samples of the classification loss (the caller divides by the global batch size, as for the other
+    per-sample losses) and the number of correct predictions (relax/backends/megatron/loss.py :1301-1383).
+    ``single_label_classification``: ``labels [n]`` class ids, cross entropy, accuracy by arg-max.
+    ``multi_label_classification``: ``labels [n, C]`` multi-hot, mean binary cross entropy over the classes of each
+    sample, ``accuracy`` counts samples whose thresholded sigmoid matches every label, ``label_accuracy`` the mean
+    per-label agreement."""
+    if problem_type == "multi_label_classification":
+        y = labels.to(logits.device).float()
+        bce = torch.nn.functional.binary_cross_entropy_with_logits(logits.float(), y, reduction="none").mean(-1).sum()
+        pred = (torch.sigmoid(logits.float()) > threshold).float()
+        agree = (pred == y).float()
+        return bce, {"loss": bce.detach(), "accuracy": agree.min(-1).values.sum(), "label_accuracy": agree.mean(-1).sum()}
+    if problem_type not in ("single_label_classification", None):
+        raise ValueError(f"unknown problem type {problem_type!r}")
     ce = torch.nn.functional.cross_entropy(logits.float(), labels.long(), reduction="sum")
     acc = (logits.argmax(-1) == labels).float().sum()
     return ce, {"loss": ce.detach(), "accuracy": acc}

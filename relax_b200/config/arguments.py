@@ -277,8 +277,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
-    "--num-labels": (_R, "set the classifier width through the model preset (num_classes)"),
-    "--problem-type": (_R, "single-label classification only"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
     # operational, no effect here
     "--async-save": (_W, "checkpoints are written synchronously"),
@@ -292,7 +290,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--log-probs-chunk-size": (_W, "the fused LM head never materialises the logits"),
     "--agentic-concurrency": (_W, None), "--sglang-server-concurrency": (_W, None),
     "--sglang-mem-fraction-static": (_W, "the KV cache is sized from the batch shape"),
-    "--classification-threshold": (_W, None), "--critic-num-nodes": (_W, "the critic shares the actor's ranks"),
+    "--critic-num-nodes": (_W, "the critic shares the actor's ranks"),
     "--critic-num-gpus-per-node": (_W, "the critic shares the actor's ranks"),
     "--disable-rollout-trim-samples": (_W, None), "--disable-weights-backuper": (_W, None),
     "--enable-affinity": (_W, "no Ray node affinity"), "--genrm-num-gpus-per-engine": (_W, None),
@@ -512,6 +510,8 @@ def model_config_from_args(a):
         over["qkv_bias"] = bool(getattr(a, "add_qkv_bias", False))
         over["qk_layernorm"] = bool(getattr(a, "qk_layernorm", False))
         over["tie_word_embeddings"] = not getattr(a, "untie_embeddings_and_output_weights", False)
+    if getattr(a, "num_labels", None):
+        over["num_classes"] = int(a.num_labels)       # sequence-classification head on the last token
     if a.model_name:
         return get_config(a.model_name, **over)
     return ModelConfig(name="custom", **over)
@@ -549,6 +549,7 @@ def train_config_from_args(a):
         mtp_only_training=a.mtp_only_training,
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
-        freeze_params_name_list=_freeze_list(a),
+        freeze_params_name_list=_freeze_list(a), problem_type=getattr(a, "problem_type", None),
+        classification_threshold=float(getattr(a, "classification_threshold", 0.5) or 0.5),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
         ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

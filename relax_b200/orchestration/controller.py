@@ -186,7 +186,7 @@ class Controller:
     # ------------------------------------------------------------------ mode
     def _pick_mode(self) -> str:
         a = self.args
-        if getattr(a, "loss_type", "policy_loss") == "sft_loss":
+        if getattr(a, "loss_type", "policy_loss") in ("sft_loss", "seq_cls_loss"):
             return "sft"
         if getattr(a, "fully_async", False) or getattr(a, "hybrid", False):
             return "async"
@@ -263,7 +263,10 @@ class Controller:
             ps = (init_parallel_state(ParallelDims(tp=a.tensor_model_parallel_size, cp=a.context_parallel_size, pp=pp,
                                                    dp=self.world // (a.tensor_model_parallel_size * a.context_parallel_size * pp)))
                   if self.world > 1 else single_process_state())
-            return _SFTRunner(TrainActor(self.model_cfg, self.train_cfg, ps, device=self.device, seed=a.seed, role="sft"), a)
+            role = "seq_cls" if getattr(a, "loss_type", None) == "seq_cls_loss" else "sft"
+            if role == "seq_cls" and self.model_cfg.num_classes <= 0:
+                raise ValueError("--loss-type seq_cls_loss needs --num-labels (the width of the classification head)")
+            return _SFTRunner(TrainActor(self.model_cfg, self.train_cfg, ps, device=self.device, seed=a.seed, role=role), a)
         from .async_runner import build_async_runner
 
         return build_async_runner(self.args, self.model_cfg, self.train_cfg, self.device, self.start_rollout_id)
@@ -464,12 +467,52 @@ class _SFTRunner:
         ds = StreamingSFTDataset(files, tok, actor.ps.dp.rank, actor.ps.dp.size,
                                  max_len=_get(args, "rollout_max_context_len", 4096), epochs=None)
         per_rank = max(1, actor.cfg.global_batch_size // actor.ps.dp.size)
-        self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
+        if actor.role == "seq_cls":
+            self.batches = self._classification_batches(files, tok, per_rank, args)
+        else:
+            self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
         self.dataset = ds
+
+    def _classification_batches(self, files, tok, per_rank, args):
+        """``{"text" | "prompt": ..., "label": id | [ids] | multi-hot}`` rows -> batches with ``labels``
+        (relax/engine/sft/ classification datasets): the whole text is context, the class head reads its last token."""
+        import json
+
+        actor = self.actor
+        C = actor.mcfg.num_classes
+        multi = (actor.cfg.problem_type == "multi_label_classification")
+        key_in, key_lab = _get(args, "input_key", None) or "prompt", _get(args, "label_key", None) or "label"
+        max_len = _get(args, "rollout_max_context_len", 4096)
+        rows, n = [], 0
+        while True:
+            for path in files:
+                with open(path, encoding="utf-8") as f:
+                    for line in f:
+                        if not line.strip():
+                            continue
+                        mine = n % actor.ps.dp.size == actor.ps.dp.rank
+                        n += 1
+                        if not mine:
+                            continue
+                        r = json.loads(line)
+                        text = r.get(key_in) or r.get("prompt") or r.get("text") or ""
+                        toks = tok(text)[:max_len] or [0]
+                        lab = r[key_lab]
+                        if multi:
+                            ids = lab if isinstance(lab, (list, tuple)) else [lab]
+                            lab = [float(x) for x in ids] if len(ids) == C and set(ids) <= {0, 1} else \
+                                [1.0 if c in set(int(i) for i in ids) else 0.0 for c in range(C)]
+                        else:
+                            lab = int(lab)
+                        rows.append((toks, lab))
+                        if len(rows) == per_rank:
+                            yield {"tokens": [t for t, _ in rows], "response_lengths": [1] * len(rows),
+                                   "loss_masks": [[1]] * len(rows), "labels": [l for _, l in rows]}
+                            rows = []
 
     def step(self) -> dict:
         b = next(self.batches)
-        m = self.actor.train_sft(b)
+        m = self.actor.train_seq_cls(b) if self.actor.role == "seq_cls" else self.actor.train_sft(b)
         m["total_tokens_local"] = sum(len(t) for t in b["tokens"])
         return m
 

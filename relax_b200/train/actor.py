@@ -48,6 +48,8 @@ class TrainConfig:
     grpo_std_normalization: bool = True
     balance_data: bool = False
     recompute: bool = False
+    problem_type: Optional[str] = None        # sequence classification: single_label_classification (default) / multi_label_classification
+    classification_threshold: float = 0.5     # multi-label: sigmoid threshold of the accuracy metrics
     pad_multiple: int = 128
     # context parallelism: every zig-zag chunk is padded to a multiple of this many tokens (None: ``pad_multiple``
     # on a GPU, where the attention tiles want whole 128-row blocks, 1 on the CPU)
@@ -731,7 +733,8 @@ class TrainActor:
                 loss, m = L.value_loss(self._forward_values(pb), lb, cfg.loss)
             elif self.role == "seq_cls":
                 labels = torch.as_tensor([batch["labels"][i] for i in ids], device=self.device)
-                loss, m = L.seq_cls_loss(self._forward_class_logits(pb), labels)
+                loss, m = L.seq_cls_loss(self._forward_class_logits(pb), labels, cfg.problem_type or "single_label_classification",
+                                         cfg.classification_threshold)
             elif use_mtp:
                 lp, en, mtp = self._forward_logp_mtp(pb, cfg.compute_entropy and self.role != "sft", lb)
                 if cfg.mtp_only_training:

@@ -185,3 +185,23 @@ def test_reference_from_a_training_checkpoint_step(tmp_path):
     actor.switch_model("actor")
     assert not torch.allclose(p.detach(), saved[name].to(p.dtype)), "the policy itself keeps its own initialisation"
     c.runner.close()
+
+
+def test_sequence_classification_runs(tmp_path):
+    """``--loss-type seq_cls_loss --num-labels N`` fine-tunes the class head; single- and multi-label."""
+    data = tmp_path / "cls.jsonl"
+    with open(data, "w") as f:
+        for i in range(16):
+            f.write(json.dumps({"prompt": "aaaa" if i % 2 else "zzzz zzzz", "label": i % 2, "labels": [i % 2, 2] if i % 2 else [0]}) + "\n")
+    base = ["--model-name", "tiny", "--prompt-data", str(data), "--global-batch-size", "8", "--num-rollout", "8", "--lr", "1e-3",
+            "--max-tokens-per-gpu", "256", "--loss-type", "seq_cls_loss"]
+    save = str(tmp_path / "a")
+    assert main(base + ["--num-labels", "2", "--save", save]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    get = lambda l, k: l.get("train/" + k, l.get(k))
+    assert get(lines[-1], "accuracy") >= get(lines[0], "accuracy") and get(lines[-1], "loss") < get(lines[0], "loss")
+    assert lines[0]["total_tokens_local"] > 8
+    save = str(tmp_path / "b")
+    assert main(base + ["--num-labels", "3", "--problem-type", "multi_label_classification", "--label-key", "labels", "--save", save]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert get(lines[-1], "label_accuracy") is not None and get(lines[-1], "loss") < get(lines[0], "loss")
