@@ -58,6 +58,10 @@ def parse():
     ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
     ap.add_argument("--kv-gb", type=float, default=None)
     ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel size of trainer and engines (default 2 when N >= 2)")
+    ap.add_argument("--ep", type=int, default=1,
+                    help="expert parallelism of trainer and engines for MoE models (config 2 shape; sets tensor parallelism to 1)")
+    ap.add_argument("--loss", default="grpo", choices=["grpo", "gspo"],
+                    help="gspo: sequence-level ratio with clip 3e-4 / 4e-4 (the MoE config of the benchmark list)")
     ap.add_argument("--no-fused-tp", action="store_true",
                     help="A/B: use the NCCL statements instead of the fused GEMM+collective kernels (TP>1 only)")
     ap.add_argument("--time-budget-s", type=float, default=float(os.environ.get("RELAX_B200_BENCH_BUDGET_S", "780")),
@@ -158,21 +162,28 @@ def main():
     over = {} if args.layers is None else {"num_layers": args.layers}
     mcfg = get_config(args.model, **over)
     tp = args.tp if args.tp else (2 if world >= 2 else 1)
+    ep = max(1, args.ep)
+    if ep > 1:
+        if not mcfg.is_moe or world % ep:
+            raise SystemExit(f"--ep {ep} needs a MoE model and a world size it divides (world {world}, model {mcfg.name})")
+        tp = 1
+    gspo = args.loss == "gspo"
     G = args.group_size
     n_prompts = args.prompts_per_gpu * world
     kv_bytes_per_block = mcfg.num_layers * 2 * 16 * (mcfg.num_query_groups // tp) * mcfg.head_dim * 2
     ref_on_host = world == 1   # one GPU holds the whole model: park the frozen reference in pinned host memory
     kv_gb = args.kv_gb if args.kv_gb is not None else (52.0 if world == 1 else 40.0)
     kv_blocks = int(kv_gb * (1 << 30) / kv_bytes_per_block)
-    need_blocks = args.prompts_per_gpu * tp * G * ((args.prompt_len + args.response_len + 15) // 16 + 1)
+    need_blocks = args.prompts_per_gpu * tp * ep * G * ((args.prompt_len + args.response_len + 15) // 16 + 1)
     kv_blocks = min(kv_blocks, need_blocks)
     cfg = ColocateConfig(
         model=mcfg,
-        train=TrainConfig(advantage_estimator="grpo", n_samples_per_prompt=G, global_batch_size=n_prompts * G,
+        train=TrainConfig(advantage_estimator="gspo" if gspo else "grpo", n_samples_per_prompt=G, global_batch_size=n_prompts * G,
                           max_tokens_per_gpu=args.max_tokens_per_gpu, pad_multiple=128, ref_on_host=ref_on_host,
-                          loss=LossConfig(eps_clip=0.2, use_kl_loss=True, kl_loss_coef=0.001, kl_loss_type="k1"),
+                          loss=LossConfig(eps_clip=3e-4 if gspo else 0.2, eps_clip_high=4e-4 if gspo else 0.2, use_kl_loss=True,
+                                          kl_loss_coef=0.001, kl_loss_type="k1", advantage_estimator="gspo" if gspo else "grpo"),
                           optim=OptimizerConfig(lr=1e-6, clip_grad=1.0, grad_dtype="fp32")),
-        trainer_tp=tp, rollout_tp=tp, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
+        trainer_tp=tp, rollout_tp=tp, trainer_ep=ep, rollout_ep=ep, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
         max_response_len=args.response_len, temperature=1.0, rm_type="parity", eos_token_id=None,
         kv_blocks=kv_blocks, kv_block_size=16, max_running=512, seed=0, rollout_seed=42,
         offload_rollout=True, release_rollout_weights=True, pinned_prompts=True,
@@ -252,8 +263,11 @@ def main():
                 "model": mcfg.name + ("" if args.layers is None else f"-{args.layers}L-debug"),
                 "global_batch": n_prompts, "group_size": G, "seq_len": args.prompt_len + args.response_len,
                 "prompt_len": args.prompt_len, "max_response_len": args.response_len,
-                "parallelism": f"trainer tp{tp}xdp{world // tp} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated",
-                "loss": "grpo clip 0.2 + k1 kl 0.001 to frozen reference", "weight_sync_every_step": True,
+                "parallelism": (f"trainer tp{tp}xdp{world // tp} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated"
+                                if ep == 1 else
+                                f"trainer ep{ep} x dp{world} (distributed optimizer), rollout ep{ep}x{world // ep} engines, colocated"),
+                "loss": ("gspo sequence-level clip 3e-4/4e-4" if gspo else "grpo clip 0.2") + " + k1 kl 0.001 to frozen reference",
+                "weight_sync_every_step": True,
                 "cache": "working set per step (weights + activations + KV) far exceeds the 126 MB L2; no flush needed",
             },
             "steps_requested": steps_req, "warmup_requested": args.warmup, "time_budget_s": None if budget == float("inf") else budget,

@@ -154,6 +154,68 @@ class InProcessTeacher:
         return self.actor.compute_log_prob(batch, self.tag)["log_probs"]
 
 
+class HTTPTeacher:
+    """A teacher behind ``POST <url>/score`` (``{"tokens": [[...]], "response_lengths": [...]}`` ->
+    ``{"log_probs": [[...]]}``): what ``--opd-teacher-urls`` names (the reference scores against teacher engines
+    over HTTP, relax/engine/rollout/on_policy_distillation.py).  :func:`serve_teacher` is the matching server."""
+
+    def __init__(self, url: str, timeout_s: float = 600.0):
+        self.url, self.timeout_s = url.rstrip("/"), timeout_s
+
+    def score(self, batch: dict) -> List[torch.Tensor]:
+        import json
+        import urllib.request
+
+        body = json.dumps({"tokens": [[int(t) for t in x] for x in batch["tokens"]],
+                           "response_lengths": [int(r) for r in batch["response_lengths"]]}).encode()
+        req = urllib.request.Request(self.url + "/score", data=body, headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=self.timeout_s) as r:
+            out = json.loads(r.read().decode())
+        return [torch.tensor(x, dtype=torch.float32) for x in out["log_probs"]]
+
+
+def serve_teacher(scorer, host: str = "127.0.0.1", port: int = 0):
+    """Serve ``scorer.score(batch)`` (an :class:`InProcessTeacher`, anything with that call) over HTTP in a daemon
+    thread: ``POST /score`` and ``GET /health``.  Returns ``(server, thread)``; one request is scored at a time
+    (the scorer owns a GPU)."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    lock = threading.Lock()
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):       # quiet
+            pass
+
+        def _send(self, code, obj):
+            data = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+        def do_GET(self):
+            self._send(200, {"status": "ok"}) if self.path.rstrip("/") == "/health" else self._send(404, {"error": "not found"})
+
+        def do_POST(self):
+            if self.path.rstrip("/") != "/score":
+                return self._send(404, {"error": "not found"})
+            try:
+                req = json.loads(self.rfile.read(int(self.headers.get("Content-Length", "0"))).decode())
+                with lock:
+                    lp = scorer.score({"tokens": req["tokens"], "response_lengths": req["response_lengths"]})
+                self._send(200, {"log_probs": [[float(v) for v in x.tolist()] for x in lp]})
+            except Exception as e:   # noqa: BLE001 - the client marks this teacher unhealthy and retries elsewhere
+                self._send(500, {"error": repr(e)})
+
+    srv = ThreadingHTTPServer((host, port), H)
+    t = threading.Thread(target=srv.serve_forever, daemon=True, name="teacher-server")
+    t.start()
+    return srv, t
+
+
 class TeacherPool:
     """Several teacher scorers behind one ``score`` call: the batch is cut into per-teacher slices that run
     concurrently, a teacher that raises or exceeds the time limit is marked unhealthy and its slice is re-run on

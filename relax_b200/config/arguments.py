@@ -273,7 +273,6 @@ FLAG_POLICY: dict[str, tuple] = {
     # algorithm
     "--disable-compute-advantages-and-returns": (_R, "advantages are always computed by the trainer"),
     "--critic-train-only": (_R, "use --num-critic-only-steps for critic warm-up"),
-    "--opd-teacher-urls": (_R, "remote teachers are not wired into the loop (teacher snapshot via --opd-teacher-load)"),
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),

@@ -4,7 +4,9 @@
   tracking adapters chosen by the usual flags (relax/entrypoints/deploy_metrics_service.py);
 * ``coordinator`` - the weight-sync coordinator (register / heartbeat / topology / weight-metadata long poll,
   relax/checkpoint_service/coordinator/service.py);
-* ``viewer``      - the rollout result viewer (relax/entrypoints/visualize.py).
+* ``viewer``      - the rollout result viewer (relax/entrypoints/visualize.py);
+* ``teacher``     - an on-policy-distillation teacher: ``POST /score`` returns the teacher's log-probs of the response
+  tokens (``--model-name`` / ``--hf-checkpoint`` choose it; ``--opd-teacher-urls`` of the training job point here).
 
 Each serves until interrupted; the bound address is printed first so that launch scripts can read it.
 """
@@ -17,7 +19,11 @@ import time
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="relax_b200 control-plane services")
-    ap.add_argument("service", choices=["metrics", "coordinator", "viewer"])
+    ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher"])
+    ap.add_argument("--model-name", default="tiny", help="teacher: model preset")
+    ap.add_argument("--hf-checkpoint", default=None, help="teacher: Hugging Face directory with the teacher's weights")
+    ap.add_argument("--device", default=None, help="teacher: cuda / cpu (default: cuda when available)")
+    ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--host", default="127.0.0.1")
     ap.add_argument("--port", type=int, default=0)
     ap.add_argument("--dir", default=None, help="viewer: dump directory; metrics: output directory of metrics.jsonl")
@@ -34,6 +40,22 @@ def main(argv=None) -> int:
         from ..weight_sync.dcs import Coordinator, serve
 
         srv, _ = serve(Coordinator(), a.host, a.port)
+    elif a.service == "teacher":
+        import torch
+
+        from ..algo.opd import InProcessTeacher, serve_teacher
+        from ..models.config import get_config
+        from ..train.actor import TrainActor, TrainConfig
+
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        cfg = get_config(a.model_name)
+        actor = TrainActor(cfg, TrainConfig(), device=dev, seed=a.seed, with_optimizer=False)
+        if a.hf_checkpoint:
+            from ..checkpoint import hf as H
+
+            H.validate_against_hf(cfg, a.hf_checkpoint)
+            H.load_hf_into_model(a.hf_checkpoint, cfg, actor.ps, actor.model)
+        srv, _ = serve_teacher(InProcessTeacher(actor), a.host, a.port)
     else:
         from ..utils.visualize import serve_in_thread
 

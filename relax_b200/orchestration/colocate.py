@@ -88,6 +88,7 @@ class ColocateConfig:
     # partial rollout (relax/engine/rollout/sglang_rollout.py generate_rollout_async / abort): over-sampled groups
     # still running when the batch is full are aborted, kept with their partial responses in the rollout buffer and
     # continued by the next rollout step
+    opd_teacher_urls: Optional[list] = None      # remote teachers (POST <url>/score) scored before every training step
     partial_rollout: bool = False
     mask_offpolicy_in_partial_rollout: bool = False        # resumed samples: tokens of earlier policies leave the loss
     partial_rollout_max_aborted_count: Optional[int] = None  # a sample aborted more often is dropped with its group
@@ -178,6 +179,11 @@ class ColocatedGRPO:
                     if c is not None:
                         self.fused_comms.append(c)
 
+        self.teacher_pool = None
+        if cfg.opd_teacher_urls:
+            from ..algo.opd import HTTPTeacher, TeacherPool
+
+            self.teacher_pool = TeacherPool([HTTPTeacher(u) for u in cfg.opd_teacher_urls])
         need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
         cfg.train.n_samples_per_prompt = cfg.train.n_samples_per_prompt
         self.actor = TrainActor(cfg.model, cfg.train, self.ps, device=device, seed=cfg.seed, with_reference=need_ref)
@@ -616,6 +622,9 @@ class ColocatedGRPO:
             if cfg.save_debug_train_data:
                 os.makedirs(cfg.save_debug_train_data, exist_ok=True)
                 torch.save({k: v for k, v in data.items()}, os.path.join(cfg.save_debug_train_data, f"train_{rid}_rank{self._rank}.pt"))
+            if self.teacher_pool is not None and data.get("teacher_log_probs") is None:
+                with self.timer.span("teacher_log_probs"):
+                    data["teacher_log_probs"] = self.teacher_pool.score(data)
             m = self.actor.train(rid, data, update_policy=not (self.critic is not None and rid < cfg.num_critic_only_steps))
             self.actor.after_train()
             if self.critic is not None:       # `data` now carries the GAE returns computed with those values

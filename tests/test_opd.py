@@ -127,3 +127,42 @@ def test_opd_penalty_in_the_trainer_pulls_towards_the_teacher(tmp_path):
     assert actor._active_tag == "actor"
     m = c.runner.step()
     assert "opd_kl" in m and m["opd_kl"] != 0.0 and math.isfinite(m["grad_norm"])
+
+
+def test_remote_teacher_over_http_and_pool_failover():
+    """``--opd-teacher-urls``: a teacher served over HTTP scores the batch; a dead URL in the pool is marked
+    unhealthy and its slice is re-run on the live one; the colocated loop trains with the remote scores."""
+    import torch
+
+    from relax_b200.algo.opd import HTTPTeacher, InProcessTeacher, TeacherPool, serve_teacher
+    from relax_b200.models.config import get_config
+    from relax_b200.train.actor import TrainActor, TrainConfig
+
+    cfg = get_config("tiny")
+    teacher = TrainActor(cfg, TrainConfig(), seed=7, with_optimizer=False)
+    srv, _ = serve_teacher(InProcessTeacher(teacher))
+    url = f"http://127.0.0.1:{srv.server_address[1]}"
+    g = torch.Generator().manual_seed(0)
+    batch = {"tokens": [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 14, 11)],
+             "response_lengths": [4, 6, 5]}
+    ref = teacher.compute_log_prob(batch)["log_probs"]
+    got = HTTPTeacher(url).score(batch)
+    for a, b in zip(got, ref):
+        assert torch.allclose(a, b, atol=1e-6)
+    pool = TeacherPool([HTTPTeacher("http://127.0.0.1:9", timeout_s=2.0), HTTPTeacher(url)], timeout_s=5.0)
+    got = pool.score(batch)
+    assert pool.failures >= 1 and all(torch.allclose(a, b, atol=1e-6) for a, b in zip(got, ref))
+
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    run = ColocatedGRPO(ColocateConfig(
+        model=cfg, train=TrainConfig(n_samples_per_prompt=2, global_batch_size=8, max_tokens_per_gpu=1024, opd_kl_coef=0.5,
+                                     loss=LossConfig(), optim=OptimizerConfig(lr=1e-5)),
+        rollout_batch_size=4, prompt_len=8, max_response_len=8, rm_type="parity", opd_teacher_urls=[url]))
+    m = run.step()
+    assert "opd_reverse_kl" in m or any("opd" in k for k in m), sorted(m)
+    run.close()
+    srv.shutdown()
+    srv.server_close()
