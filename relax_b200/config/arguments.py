@@ -274,7 +274,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--disable-compute-advantages-and-returns": (_R, "advantages are always computed by the trainer"),
     "--critic-train-only": (_R, "use --num-critic-only-steps for critic warm-up"),
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
-    "--lora-adapter-mode": (_R, "adapters are merged before weight sync (merged mode only)"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
     # operational, no effect here

@@ -88,6 +88,7 @@ class ColocateConfig:
     # partial rollout (relax/engine/rollout/sglang_rollout.py generate_rollout_async / abort): over-sampled groups
     # still running when the batch is full are aborted, kept with their partial responses in the rollout buffer and
     # continued by the next rollout step
+    lora_adapter_mode: bool = False              # LoRA: sync the factors only, the engine applies them at run time
     opd_teacher_urls: Optional[list] = None      # remote teachers (POST <url>/score) scored before every training step
     partial_rollout: bool = False
     mask_offpolicy_in_partial_rollout: bool = False        # resumed samples: tokens of earlier policies leave the loss
@@ -233,6 +234,18 @@ class ColocatedGRPO:
             self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
             self.syncs = [(self.sync, True)]
             self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks
+        self.adapter_syncs, self._base_synced = [], False
+        if cfg.lora_adapter_mode and cfg.train.lora is not None:
+            # adapter-mode LoRA sync (relax/backends/megatron/weight_update/lora_adapter_sync.py): the engine keeps the
+            # base weights from the first sync and applies the factors at run time; later syncs move the factors only
+            if tpp > 1 or tep > 1:
+                raise NotImplementedError("LoRA adapter-mode sync covers tensor-parallel dense layouts (pp = ep = 1)")
+            from ..weight_sync.plan import build_adapter_plan
+
+            lo = cfg.train.lora
+            plan = build_adapter_plan(cfg.model, TrainerLayout(tp=ttp), rtp, lo.rank, lo.target_modules)
+            self.adapter_syncs = [(WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks), plan=plan), True)]
+            self.engine.weights.enable_lora(lo.rank, lo.scale, lo.target_modules)
         if not self._aligned and tpp == 1 and not (ttp == 1 or rtp == 1 or ttp == rtp):
             raise NotImplementedError("colocated sync needs trainer TP group == rollout engine ranks, or TP 1 on one side")
         self.queue = tq.init({"capacity_partitions": 2})
@@ -335,11 +348,23 @@ class ColocatedGRPO:
 
     # ------------------------------------------------------------------ weight sync
     def sync_weights(self) -> float:
-        params = dict(self.actor.named_local_params())
+        adapter = self.cfg.lora_adapter_mode and self.cfg.train.lora is not None
+        params = dict(self.actor.named_local_params(merged=not adapter))
         ms = 0.0
+        if adapter and self._base_synced:
+            # adapter mode after the first sync: the base weights on the engine are current, only the factors move
+            for sync, mine in self.adapter_syncs:
+                ms += sync.update_weights(params, self.engine.weights if mine else None, self.engine if mine else None,
+                                          version=self.actor.weight_version)
+            return ms
         for sync, mine in self.syncs:
             ms += sync.update_weights(params, self.engine.weights if mine else None, self.engine if mine else None,
                                       version=self.actor.weight_version)
+        if adapter:
+            for sync, mine in self.adapter_syncs:
+                ms += sync.update_weights(params, self.engine.weights if mine else None, self.engine if mine else None,
+                                          version=self.actor.weight_version)
+            self._base_synced = True
         return ms
 
     # ------------------------------------------------------------------ rollout

@@ -230,6 +230,7 @@ class Controller:
                 dynamic_sampling_filter_path=_get(a, "dynamic_sampling_filter_path", None),
                 over_sampling_batch_size=_get(a, "over_sampling_batch_size", None),
                 opd_teacher_urls=_get(a, "opd_teacher_urls", None) if _get(a, "opd_type", None) else None,
+                lora_adapter_mode=bool(_get(a, "lora_adapter_mode", False)),
                 partial_rollout=bool(_get(a, "partial_rollout", False)),
                 mask_offpolicy_in_partial_rollout=bool(_get(a, "mask_offpolicy_in_partial_rollout", False)),
                 partial_rollout_max_aborted_count=_get(a, "partial_rollout_max_aborted_count", None),

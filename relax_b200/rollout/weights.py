@@ -97,6 +97,8 @@ class RolloutWeights:
         self.shared_path = shared_path
         self.flat = None
         self.p: dict[str, torch.Tensor] = {}
+        self.lora: dict[str, torch.Tensor] = {}       # adapter-mode serving: see enable_lora()
+        self.lora_scale = 0.0
         self.memory_saver = memory_saver
         self._buf = None
         self.resume()
@@ -122,6 +124,30 @@ class RolloutWeights:
         self.p = {k: self.flat[o:o + math.prod(self.shapes[k])].view(self.shapes[k]) for k, o in self.offsets.items()}
         if self.cfg.tie_word_embeddings:
             self.p["lm_head"] = self.p["embed"]
+        self.p.update(self.lora)
+
+    def enable_lora(self, rank: int, scale: float, targets=("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")):
+        """Adapter-mode serving: the base weights stay as synced once and every adapted linear adds
+        ``scale * B (A x)`` at run time, so a weight sync moves the factors only.  The factors live outside the flat
+        buffer (they are small and survive release / resume) under ``<weight name>.lora_A`` / ``.lora_B``; ``B`` starts
+        at zero, i.e. the model is the base model until the first adapter sync."""
+        from ..weight_sync.plan import _ADAPTED
+
+        self.lora_scale = float(scale)
+        for name, shape in self.shapes.items():
+            leaf = name.rsplit(".", 1)[-1]
+            if not name.startswith("layers.") or leaf not in _ADAPTED or _ADAPTED[leaf][0] not in targets:
+                continue
+            out_f, in_f = shape
+            self.lora[name + ".lora_A"] = torch.zeros(rank, in_f, dtype=self.dtype, device=self.device)
+            self.lora[name + ".lora_B"] = torch.zeros(out_f, rank, dtype=self.dtype, device=self.device)
+        self.p.update(self.lora)
+
+    def _lora_add(self, name: str, x, y):
+        a = self.lora.get(name + ".lora_A")
+        if a is None:
+            return y
+        return y + ops.linear(ops.linear(x, a), self.lora[name + ".lora_B"]) * self.lora_scale
 
     def release(self):
         if self.memory_saver:
@@ -182,6 +208,9 @@ class RolloutWeights:
                                    p[pre + "experts_down"], skip_foreign=True)
             out += (y.float().view(T, k, -1) * w.float().unsqueeze(-1)).sum(1)
             return out.to(x.dtype), (self.ep_group if self.ep_size > 1 else None)
+        if self.lora:       # adapter-mode serving: the factors' products join before the activation / before the reduction
+            a = ops.swiglu(self._lora_add(pre + "gate_up", x, ops.linear(x, p[pre + "gate_up"])))
+            return self._lora_add(pre + "down", a, ops.linear(a, p[pre + "down"])), (tp if tp.size > 1 else None)
         a = ops.linear_swiglu(x, p[pre + "gate_up"])
         return ops.linear(a, p[pre + "down"]), (tp if tp.size > 1 else None)
 
@@ -204,17 +233,22 @@ class RolloutWeights:
         hd = cfg.head_dim
         nq, nkv = cfg.num_attention_heads // self.tp_size, cfg.num_query_groups // self.tp_size
         qkv = ops.linear(x, p[pre + "qkv"], p.get(pre + "qkv_bias"))
+        if self.lora:
+            qkv = self._lora_add(pre + "qkv", x, qkv)
         T = qkv.shape[0]
         kc, vc, slots, dense = cache
         q, k, v = ops.qkv_post(qkv, nq, nkv, p.get(pre + "q_norm") if cfg.qk_layernorm else None,
                                p.get(pre + "k_norm") if cfg.qk_layernorm else None, cos, sin, cfg.rms_norm_eps,
                                kc[i], vc[i], slots, dense)
         o = attn(i, q, k, v).reshape(T, nq * hd)
-        comm = self._fused(tp, T, cfg.hidden_size)
+        comm = self._fused(tp, T, cfg.hidden_size) if not self.lora else None     # adapters add to the partial sums: plain path
         if comm is not None:
             h, x = comm.gemm_ar_add_rmsnorm(o, p[pre + "o"], h, p[pre + "post_norm"], cfg.rms_norm_eps)
         else:
-            a = self._allreduce(ops.linear(o, p[pre + "o"]), tp)
+            a = ops.linear(o, p[pre + "o"])
+            if self.lora:
+                a = self._lora_add(pre + "o", o, a)
+            a = self._allreduce(a, tp)
             x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
         if comm is not None and (pre + "router") not in p:
             a = ops.linear_swiglu(x, p[pre + "gate_up"])

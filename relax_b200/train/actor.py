@@ -866,10 +866,11 @@ class TrainActor:
         if self.cfg.keep_old_actor:
             self.backup("old_actor")
 
-    def named_local_params(self):
-        """(megatron-style name, tensor) for every local parameter, actor weights."""
+    def named_local_params(self, merged: bool = True):
+        """(megatron-style name, tensor) for every local parameter, actor weights.  With LoRA: the merged weights
+        (default) or, ``merged=False``, the frozen base weights and the factors as they are (adapter-mode sync)."""
         self.switch_model("actor")
-        if self.cfg.lora is not None:
+        if self.cfg.lora is not None and merged:
             from .lora import merged_named_params
 
             return merged_named_params(self.model)   # merged-weights sync: the engine sees a plain model

@@ -188,5 +188,40 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
     return plan
 
 
+_ADAPTED = {"qkv": ("linear_qkv", True), "o": ("linear_proj", False), "gate_up": ("linear_fc1", True),
+            "down": ("linear_fc2", False)}
+
+
+def build_adapter_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, rank: int,
+                       targets=("linear_qkv", "linear_proj", "linear_fc1", "linear_fc2")) -> List[BlockCopy]:
+    """Block copies that move LoRA factors instead of merged weights (adapter-mode sync,
+    relax/backends/megatron/weight_update/lora_adapter_sync.py): derived from the weight plan, because the factor
+    that is sharded follows its weight - ``B [out, r]`` of a column-parallel linear takes the weight's row blocks
+    (including the grouped-QKV -> q | k | v and the [gate; up] re-layout), ``A [r, in]`` of a row-parallel linear its
+    column blocks - while the other factor is replicated and copied whole to every rollout rank."""
+    from dataclasses import replace as _replace
+
+    H = cfg.hidden_size
+    out, whole = [], set()
+    for b in build_plan(cfg, src, dst_tp, 1):
+        leaf = b.dst_name.rsplit(".", 1)[-1]
+        if leaf not in _ADAPTED or not b.dst_name.startswith("layers.") or not b.src_name.endswith(".weight"):
+            continue
+        mod, column = _ADAPTED[leaf]
+        if mod not in targets:
+            continue
+        base = b.src_name[: -len(".weight")]
+        if column:
+            out.append(_replace(b, src_name=base + ".lora_B", dst_name=b.dst_name + ".lora_B", src_col=0, dst_col=0, cols=rank))
+            rep = (base + ".lora_A", b.dst_name + ".lora_A", rank, H)
+        else:
+            out.append(_replace(b, src_name=base + ".lora_A", dst_name=b.dst_name + ".lora_A", src_row=0, dst_row=0, rows=rank))
+            rep = (base + ".lora_B", b.dst_name + ".lora_B", H, rank)
+        if (rep[1], b.dst_rank) not in whole:
+            whole.add((rep[1], b.dst_rank))
+            out.append(BlockCopy(b.dst_rank % src.tp, rep[0], 0, 0, b.dst_rank, rep[1], 0, 0, rep[2], rep[3], src_stage=b.src_stage))
+    return out
+
+
 def plan_bytes(plan: Iterable[BlockCopy], itemsize: int = 2) -> int:
     return sum(b.rows * b.cols for b in plan) * itemsize

@@ -47,11 +47,12 @@ class WeightSync:
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int,
                  trainer_ranks: Sequence[int], rollout_ranks: Sequence[int], rollout_ep: int = 1,
-                 group=None, post_hook=None, aligned_ep_rank: Optional[int] = None):
+                 group=None, post_hook=None, aligned_ep_rank: Optional[int] = None, plan=None):
         self.cfg = cfg
         # ``post_hook(name, tensor) -> tensor`` runs on every rollout tensor after the copy (quantisation round trip)
         self.post_hook = post_hook
-        self.plan = build_plan(cfg, trainer_layout, rollout_tp, rollout_ep)
+        # ``plan``: another list of block copies over the same rank layout (the LoRA factors of adapter-mode sync)
+        self.plan = plan if plan is not None else build_plan(cfg, trainer_layout, rollout_tp, rollout_ep)
         # ``trainer_ranks``: list indexed by TP rank (one pipeline stage), or ``{(stage, tp_rank): global rank}``
         if isinstance(trainer_ranks, dict):
             self.trainer_ranks = dict(trainer_ranks)

@@ -87,3 +87,104 @@ def test_lora_forward_runs_under_tp2_and_is_rank_consistent():
     out = run_distributed(_tp_worker, 2)
     assert torch.allclose(out[0][0], out[1][0], atol=1e-5)   # both ranks compute the same log-probs
     assert out[0][1].abs().sum() > 0
+
+
+def test_adapter_plan_reshards_factors_like_their_weights():
+    """Adapter-mode sync: for trainer TP 2 -> rollout TP 1 and TP 2, base weight + scale * B A assembled from the
+    synced factors on every rollout rank equals the rollout shard of the merged full weight (the oracle)."""
+    from relax_b200.weight_sync.plan import TrainerLayout, build_adapter_plan, build_plan
+    from relax_b200.weight_sync.sync import apply_block, oracle_rollout_state
+    from relax_b200.rollout.weights import rollout_param_shapes
+
+    cfg = get_config("tiny")
+    r, scale = 4, 2.0
+    g = torch.Generator().manual_seed(0)
+    full = GPTModel(cfg, seed=3)
+    LR.apply_lora(full, LR.LoRAConfig(rank=r, alpha=r * scale))
+    for n, p in full.named_parameters():
+        if "lora_" in n:
+            p.data.copy_(torch.randn(p.shape, generator=g) * 0.1)
+    merged_full = {n: p.detach() for n, p in LR.merged_named_params(full)}
+    raw_full = {n: p.detach() for n, p in full.named_parameters()}
+    for src_tp, dst_tp in ((1, 1), (2, 1), (2, 2), (1, 2)):
+        # shard the raw trainer tensors (weights and factors) the way a TP-`src_tp` trainer holds them
+        from relax_b200.parallel.state import GroupInfo, ParallelDims, ParallelState
+
+        shards = []
+        for tr in range(src_tp):
+            one = GroupInfo(None, (0,), 0)
+            ps = ParallelState(ParallelDims(tp=src_tp), tr, tuple(range(src_tp)), GroupInfo(None, tuple(range(src_tp)), tr),
+                               one, one, one, one, one, one, one)
+            m = GPTModel(cfg, ps, seed=3)
+            LR.apply_lora(m, LR.LoRAConfig(rank=r, alpha=r * scale))
+            from relax_b200.checkpoint.dist_ckpt import load_full_state
+
+            load_full_state(cfg, ps, m, {k: v for k, v in raw_full.items() if "lora_" not in k}, strict=False)
+            sh = {n: p.detach() for n, p in m.named_parameters()}
+            # the factors in the layout train/lora.py gives them under TP: column-parallel linears (qkv, fc1) keep A
+            # whole and B's rows of the rank's output features ([gate; up] halves for fc1); row-parallel ones (proj,
+            # fc2) keep B whole and A's columns of the rank's input features
+            for n in sh:
+                if "lora_" not in n:
+                    continue
+                fullt = raw_full[n]
+                col = ("linear_qkv" in n) or ("linear_fc1" in n)
+                if n.endswith("lora_B") and col:
+                    if "linear_fc1" in n:
+                        F = fullt.shape[0] // 2
+                        Fs = F // src_tp
+                        sh[n] = torch.cat([fullt[tr * Fs:(tr + 1) * Fs], fullt[F + tr * Fs:F + (tr + 1) * Fs]])
+                    else:
+                        rows = fullt.shape[0] // src_tp
+                        sh[n] = fullt[tr * rows:(tr + 1) * rows]
+                elif n.endswith("lora_A") and not col:
+                    cols = fullt.shape[1] // src_tp
+                    sh[n] = fullt[:, tr * cols:(tr + 1) * cols]
+                else:
+                    sh[n] = fullt
+                assert sh[n].shape == dict(m.named_parameters())[n].shape, n
+            shards.append(sh)
+        wplan = build_plan(cfg, TrainerLayout(tp=src_tp), dst_tp, 1)
+        aplan = build_adapter_plan(cfg, TrainerLayout(tp=src_tp), dst_tp, r)
+        for dr in range(dst_tp):
+            shapes = rollout_param_shapes(cfg, dst_tp, 1)
+            dst = {k: torch.zeros(s) for k, s in shapes.items()}
+            for k, s in shapes.items():
+                leaf = k.rsplit(".", 1)[-1]
+                if k.startswith("layers.") and leaf in ("qkv", "o", "gate_up", "down"):
+                    dst[k + ".lora_A"], dst[k + ".lora_B"] = torch.zeros(r, s[1]), torch.zeros(s[0], r)
+            for b in wplan + aplan:
+                if b.dst_rank == dr:
+                    apply_block(b, shards[b.src_rank][b.src_name], dst[b.dst_name])
+            want = oracle_rollout_state(cfg, merged_full, dst_tp, dr)
+            for k in shapes:
+                leaf = k.rsplit(".", 1)[-1]
+                if k.startswith("layers.") and leaf in ("qkv", "o", "gate_up", "down"):
+                    got = dst[k] + scale * dst[k + ".lora_B"] @ dst[k + ".lora_A"]
+                    assert torch.allclose(got, want[k], atol=1e-5), (src_tp, dst_tp, dr, k)
+
+
+def test_adapter_mode_sync_in_the_colocated_loop():
+    """``--lora-adapter-mode``: after the first sync only the factors move, the engine adds them at run time and
+    its log-probs keep matching the trainer's (adapted) forward."""
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.weight_sync.plan import plan_bytes
+
+    torch.manual_seed(0)
+    cfg = ColocateConfig(
+        model=get_config("tiny"),
+        train=TrainConfig(n_samples_per_prompt=2, global_batch_size=8, max_tokens_per_gpu=1024, lora=LR.LoRAConfig(rank=4, alpha=8),
+                          loss=LossConfig(), optim=OptimizerConfig(lr=5e-3, weight_decay=0.0)),
+        rollout_batch_size=4, prompt_len=8, max_response_len=12, rm_type="parity", lora_adapter_mode=True, seed=0, rollout_seed=1,
+        stop_token_ids=list(range(0, 1024, 6)))        # responses of different lengths: the parity reward varies inside groups
+    run = ColocatedGRPO(cfg)
+    assert run.engine.weights.lora and run._base_synced is False or run._base_synced is True
+    for _ in range(3):
+        m = run.step()
+        assert m["train_rollout_logprob_abs_diff"] < 1e-4
+    assert run._base_synced
+    b_name = next(k for k in run.engine.weights.lora if k.endswith("qkv.lora_B"))
+    assert run.engine.weights.lora[b_name].abs().sum() > 0, "the factors reached the engine"
+    small = plan_bytes(run.adapter_syncs[0][0].plan)
+    assert small * 10 < plan_bytes(run.syncs[0][0].plan), "an adapter sync moves a fraction of a full sync"
+    run.close()
