@@ -58,6 +58,10 @@ def parse():
     ap.add_argument("--max-tokens-per-gpu", type=int, default=5120)
     ap.add_argument("--kv-gb", type=float, default=None)
     ap.add_argument("--tp", type=int, default=0, help="debug only: tensor-parallel size of trainer and engines (default 2 when N >= 2)")
+    ap.add_argument("--cp", type=int, default=1,
+                    help="context parallelism of the trainer (long-context config shape): world = tp x cp x dp; engines keep tp")
+    ap.add_argument("--cp-attention", default=None, choices=["peer", "allgather"],
+                    help="how context-parallel ranks see each other's K/V: NVLink staging buffers (default) or one all-gather")
     ap.add_argument("--ep", type=int, default=1,
                     help="expert parallelism of trainer and engines for MoE models (config 2 shape; sets tensor parallelism to 1)")
     ap.add_argument("--loss", default="grpo", choices=["grpo", "gspo"],
@@ -168,6 +172,9 @@ def main():
             raise SystemExit(f"--ep {ep} needs a MoE model and a world size it divides (world {world}, model {mcfg.name})")
         tp = 1
     gspo = args.loss == "gspo"
+    cp = max(1, args.cp)
+    if world % (tp * cp):
+        raise SystemExit(f"--tp {tp} x --cp {cp} does not divide the world size {world}")
     G = args.group_size
     n_prompts = args.prompts_per_gpu * world
     kv_bytes_per_block = mcfg.num_layers * 2 * 16 * (mcfg.num_query_groups // tp) * mcfg.head_dim * 2
@@ -180,10 +187,11 @@ def main():
         model=mcfg,
         train=TrainConfig(advantage_estimator="gspo" if gspo else "grpo", n_samples_per_prompt=G, global_batch_size=n_prompts * G,
                           max_tokens_per_gpu=args.max_tokens_per_gpu, pad_multiple=128, ref_on_host=ref_on_host,
+                          cp_attention=args.cp_attention,
                           loss=LossConfig(eps_clip=3e-4 if gspo else 0.2, eps_clip_high=4e-4 if gspo else 0.2, use_kl_loss=True,
                                           kl_loss_coef=0.001, kl_loss_type="k1", advantage_estimator="gspo" if gspo else "grpo"),
                           optim=OptimizerConfig(lr=1e-6, clip_grad=1.0, grad_dtype="fp32")),
-        trainer_tp=tp, rollout_tp=tp, trainer_ep=ep, rollout_ep=ep, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
+        trainer_tp=tp, rollout_tp=tp, trainer_cp=cp, trainer_ep=ep, rollout_ep=ep, rollout_batch_size=n_prompts, prompt_len=args.prompt_len,
         max_response_len=args.response_len, temperature=1.0, rm_type="parity", eos_token_id=None,
         kv_blocks=kv_blocks, kv_block_size=16, max_running=512, seed=0, rollout_seed=42,
         offload_rollout=True, release_rollout_weights=True, pinned_prompts=True,
@@ -263,7 +271,9 @@ def main():
                 "model": mcfg.name + ("" if args.layers is None else f"-{args.layers}L-debug"),
                 "global_batch": n_prompts, "group_size": G, "seq_len": args.prompt_len + args.response_len,
                 "prompt_len": args.prompt_len, "max_response_len": args.response_len,
-                "parallelism": (f"trainer tp{tp}xdp{world // tp} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated"
+                "parallelism": (f"trainer tp{tp}xcp{cp}xdp{world // (tp * cp)} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated"
+                                if cp > 1 else
+                                f"trainer tp{tp}xdp{world // tp} (distributed optimizer), rollout tp{tp}x{world // tp} engines, colocated"
                                 if ep == 1 else
                                 f"trainer ep{ep} x dp{world} (distributed optimizer), rollout ep{ep}x{world // ep} engines, colocated"),
                 "loss": ("gspo sequence-level clip 3e-4/4e-4" if gspo else "grpo clip 0.2") + " + k1 kl 0.001 to frozen reference",
