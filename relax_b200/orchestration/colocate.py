@@ -233,7 +233,9 @@ class ColocatedGRPO:
         else:
             self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
             self.syncs = [(self.sync, True)]
-            self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks
+            # with context parallelism a trainer replica spans tp x cp ranks that must all see the SAME rows (each holds
+            # a slice of every sequence), while each of them feeds an engine of its own: rows always travel
+            self._aligned = ttp == rtp and tuple(tr_ranks) == eng_ranks and tcp == 1
         self.adapter_syncs, self._base_synced = [], False
         if cfg.lora_adapter_mode and cfg.train.lora is not None:
             # adapter-mode LoRA sync (relax/backends/megatron/weight_update/lora_adapter_sync.py): the engine keeps the
