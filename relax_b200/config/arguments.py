@@ -300,7 +300,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--sft-logits-chunk-size": (_W, None), "--sft-max-in-flight-steps": (_W, None), "--sft-prefetch-buffer-size": (_W, None),
     "--slime-router-health-check-failure-threshold": (_W, None), "--slime-router-max-connections": (_W, None),
     "--slime-router-middleware-paths": (_W, None), "--slime-router-sticky": (_W, None), "--slime-router-timeout": (_W, None),
-    "--use-slime-router": (_W, "the in-process router is used when several engines serve one rank"),
+    "--use-slime-router": (_W, "the in-process router is used when several engines serve one rank; the HTTP proxy is `serve router`"),
     "--train-env-vars": (_W, None), "--train-memory-margin-bytes": (_W, None), "--update-weight-buffer-size": (_W, None),
     "--scale-out-timeout": (_W, None), "--scale-in-drain-timeout": (_W, None), "--scale-in-shutdown-timeout": (_W, None),
     "--scale-weight-sync-precheck": (_W, None), "--scale-out-partial-success-policy": (_W, None),

@@ -5,6 +5,8 @@
 * ``coordinator`` - the weight-sync coordinator (register / heartbeat / topology / weight-metadata long poll,
   relax/checkpoint_service/coordinator/service.py);
 * ``viewer``      - the rollout result viewer (relax/entrypoints/visualize.py);
+* ``router``      - the request router as an HTTP proxy in front of engine servers (least loaded / sticky by key,
+  health probes, ``/add_worker`` ``/remove_worker`` ``/list_workers``; relax/engine/router/router.py);
 * ``teacher``     - an on-policy-distillation teacher: ``POST /score`` returns the teacher's log-probs of the response
   tokens (``--model-name`` / ``--hf-checkpoint`` choose it; ``--opd-teacher-urls`` of the training job point here).
 
@@ -19,7 +21,10 @@ import time
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="relax_b200 control-plane services")
-    ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher"])
+    ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher", "router"])
+    ap.add_argument("--workers", nargs="*", default=None, help="router: base URLs of the engine servers to start with")
+    ap.add_argument("--router-timeout", type=float, default=600.0)
+    ap.add_argument("--router-health-check-failure-threshold", type=int, default=3)
     ap.add_argument("--model-name", default="tiny", help="teacher: model preset")
     ap.add_argument("--hf-checkpoint", default=None, help="teacher: Hugging Face directory with the teacher's weights")
     ap.add_argument("--device", default=None, help="teacher: cuda / cpu (default: cuda when available)")
@@ -40,6 +45,13 @@ def main(argv=None) -> int:
         from ..weight_sync.dcs import Coordinator, serve
 
         srv, _ = serve(Coordinator(), a.host, a.port)
+    elif a.service == "router":
+        from ..rollout.router import Router, serve_router
+
+        r = Router(max_failures=a.router_health_check_failure_threshold)
+        for u in a.workers or []:
+            r.add_worker(u)
+        srv, _, _ = serve_router(r, a.host, a.port, timeout_s=a.router_timeout)
     elif a.service == "teacher":
         import torch
 

@@ -138,3 +138,106 @@ class Router:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout=5)
+
+
+# ----------------------------------------------------------------------------- HTTP front
+def serve_router(router: Optional[Router] = None, host: str = "127.0.0.1", port: int = 0, timeout_s: float = 600.0,
+                 health_path: str = "/health", health_interval_s: float = 10.0, retries: int = 2):
+    """The router as an HTTP proxy in front of engine servers (relax/engine/router/router.py: ``/add_worker``,
+    ``/remove_worker``, ``/list_workers``, and every other POST forwarded to a worker).  Workers are base URLs.
+    A forwarded request goes to the least-loaded healthy worker - or to the worker that already holds the request's
+    ``routing_key`` / ``session_id`` / ``user`` field - and is retried on another worker when the first fails;
+    ``GET <worker><health_path>`` probes run in the background and quarantine a worker after ``max_failures`` misses.
+    Returns ``(server, thread, router)``."""
+    import json
+    import urllib.error
+    import urllib.parse
+    import urllib.request
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    router = router or Router()
+
+    def probe(url) -> bool:
+        try:
+            with urllib.request.urlopen(str(url).rstrip("/") + health_path, timeout=5.0) as r:
+                return 200 <= r.status < 300
+        except Exception:  # noqa: BLE001
+            return False
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def _send(self, code, body: bytes, ctype="application/json"):
+            self.send_response(code)
+            self.send_header("Content-Type", ctype)
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def _json(self, code, obj):
+            self._send(code, json.dumps(obj).encode())
+
+        def _url_arg(self, body: bytes) -> Optional[str]:
+            q = urllib.parse.parse_qs(urllib.parse.urlparse(self.path).query)
+            if "url" in q:
+                return q["url"][0]
+            try:
+                return json.loads(body.decode() or "{}").get("url")
+            except ValueError:
+                return None
+
+        def do_GET(self):
+            path = urllib.parse.urlparse(self.path).path.rstrip("/")
+            if path == "/list_workers":
+                return self._json(200, {"urls": [str(w) for w in router.workers()], "workers": {str(k): v for k, v in router.workers().items()}})
+            if path == "/health":
+                return self._json(200, {"status": "ok", "workers": len(router.workers())})
+            self._json(404, {"error": "not found"})
+
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers.get("Content-Length", "0") or 0))
+            path = urllib.parse.urlparse(self.path).path.rstrip("/")
+            if path in ("/add_worker", "/remove_worker", "/drain_worker"):
+                url = self._url_arg(body)
+                if not url:
+                    return self._json(400, {"error": "url missing"})
+                {"/add_worker": router.add_worker, "/remove_worker": router.remove_worker, "/drain_worker": router.drain_worker}[path](url)
+                return self._json(200, {"status": "ok", "urls": [str(w) for w in router.workers()]})
+            key = None
+            try:
+                d = json.loads(body.decode() or "{}")
+                key = d.get("routing_key") or d.get("session_id") or d.get("user")
+            except ValueError:
+                pass
+            last = None
+            for _ in range(retries + 1):
+                try:
+                    wid = router.acquire(key)
+                except NoHealthyWorker as e:
+                    return self._json(503, {"error": str(e)})
+                failed = True
+                try:
+                    req = urllib.request.Request(str(router.handle(wid)).rstrip("/") + self.path, data=body,
+                                                 headers={"Content-Type": self.headers.get("Content-Type", "application/json")})
+                    with urllib.request.urlopen(req, timeout=timeout_s) as r:
+                        out, code, ctype = r.read(), r.status, r.headers.get("Content-Type", "application/json")
+                    failed = False
+                    return self._send(code, out, ctype)
+                except urllib.error.HTTPError as e:      # the worker answered: pass its verdict on, it is not down
+                    failed = e.code >= 500
+                    last = e
+                    if not failed:
+                        return self._send(e.code, e.read(), e.headers.get("Content-Type", "application/json"))
+                except Exception as e:  # noqa: BLE001 - connection refused / reset / timeout: try another worker
+                    last = e
+                finally:
+                    router.release(wid, failed=failed)
+            self._json(502, {"error": f"no worker could serve the request: {last!r}"})
+
+    srv = ThreadingHTTPServer((host, port), H)
+    t = threading.Thread(target=srv.serve_forever, daemon=True, name="router-http")
+    t.start()
+    if health_interval_s and health_interval_s > 0:
+        router.start_health_loop(probe, health_interval_s)
+    return srv, t, router

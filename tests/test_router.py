@@ -88,3 +88,60 @@ def test_radix_lru_eviction():
     assert c.stats()["tokens"] <= 30
     assert c.find_longest_prefix("bbbbbbbbbb").matched_prefix == ""
     assert c.find_longest_prefix("aaaaaaaaaa").matched_prefix == "aaaaaaaaaa"
+
+
+def test_http_router_proxies_sticks_and_fails_over():
+    """The router as an HTTP proxy: requests go to registered workers (least loaded, sticky by session), a dead
+    worker is skipped after a failed attempt, membership changes over HTTP."""
+    import json
+    import threading
+    import urllib.request
+    from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+
+    from relax_b200.rollout.router import Router, serve_router
+
+    def upstream(tag):
+        class H(BaseHTTPRequestHandler):
+            def log_message(self, *a):
+                pass
+
+            def do_GET(self):
+                self.send_response(200); self.end_headers(); self.wfile.write(b"{}")
+
+            def do_POST(self):
+                n = int(self.headers.get("Content-Length", "0"))
+                body = json.loads(self.rfile.read(n) or b"{}")
+                out = json.dumps({"worker": tag, "echo": body.get("text")}).encode()
+                self.send_response(200); self.send_header("Content-Length", str(len(out))); self.end_headers(); self.wfile.write(out)
+        s = ThreadingHTTPServer(("127.0.0.1", 0), H)
+        threading.Thread(target=s.serve_forever, daemon=True).start()
+        return s, f"http://127.0.0.1:{s.server_address[1]}"
+
+    a, ua = upstream("a")
+    b, ub = upstream("b")
+    srv, _, router = serve_router(Router(max_failures=1), health_interval_s=0)
+    base = f"http://127.0.0.1:{srv.server_address[1]}"
+
+    def post(path, obj):
+        req = urllib.request.Request(base + path, data=json.dumps(obj).encode(), headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=10) as r:
+            return json.loads(r.read())
+
+    post("/add_worker", {"url": ua})
+    post("/add_worker?url=" + ub, {})
+    with urllib.request.urlopen(base + "/list_workers") as r:
+        assert sorted(json.loads(r.read())["urls"]) == sorted([ua, ub])
+    first = post("/generate", {"text": "x", "session_id": "s1"})["worker"]
+    assert all(post("/generate", {"text": "y", "session_id": "s1"})["worker"] == first for _ in range(4))     # sticky
+    seen = {post("/generate", {"text": str(i)})["worker"] for i in range(6)}
+    assert seen == {"a", "b"}
+    # kill one upstream: its requests fail over to the other and it is quarantined
+    (a if first == "a" else b).shutdown()
+    (a if first == "a" else b).server_close()
+    other = "b" if first == "a" else "a"
+    assert all(post("/generate", {"text": "z", "session_id": "s1"})["worker"] == other for _ in range(3))
+    post("/remove_worker", {"url": ua if first == "a" else ub})
+    with urllib.request.urlopen(base + "/list_workers") as r:
+        assert len(json.loads(r.read())["urls"]) == 1
+    srv.shutdown(); srv.server_close(); router.stop()
+    (b if first == "a" else a).shutdown()
