@@ -75,6 +75,10 @@ class Controller:
                                       _get(args, "profile_step_start", -1), _get(args, "profile_step_end", -1), self.rank,
                                       with_stack=bool(_get(args, "profile_with_stack", False)),
                                       record_memory=bool(_get(args, "profile_with_memory", False) or _get(args, "record_memory_history", False)))
+        from ..utils.profiler import MemorySnapshotter
+
+        self.memory_snapshot = MemorySnapshotter(_get(args, "memory_snapshot_dir", None), _get(args, "memory_snapshot_num_steps", None),
+                                                 self.rank)
         self.start_rollout_id = dist_ckpt.resolve_start_rollout_id(args.load, args.start_rollout_id)
         self.runner = self._build_runner()
         self._maybe_resume()
@@ -432,6 +436,7 @@ class Controller:
             self.metrics.log_metrics_batch(rid, rec)
             self.metrics.report_step(rid)
             self.profiler.step()
+            self.memory_snapshot.step()
             history.append(rec)
             rid += 1
             if a.save and a.save_interval and rid % a.save_interval == 0:
@@ -439,6 +444,7 @@ class Controller:
         if self._stop and a.save and rid > self.start_rollout_id:
             self.save(rid - 1)   # interrupted: keep what was learned
         self.profiler.close()
+        self.memory_snapshot.close()
         tdir = _get(a, "timeline_dump_dir", None)
         timer = getattr(self.runner, "timer", None)
         if tdir and timer is not None and hasattr(timer, "dump_chrome_trace"):     # one Chrome trace of the phase spans per rank

@@ -67,3 +67,35 @@ class TrainProfiler:
     def close(self):
         if self._prof is not None:
             self._finish()
+
+
+class MemorySnapshotter:
+    """``--memory-snapshot-dir`` / ``--memory-snapshot-num-steps`` (relax/utils/memory_utils.py): record the CUDA
+    caching allocator's history from the first training step and dump one snapshot per rank (the pickle that
+    https://pytorch.org/memory_viz reads) after ``num_steps`` steps - independent of the kernel-trace window."""
+
+    def __init__(self, out_dir: Optional[str], num_steps: Optional[int] = None, rank: int = 0, max_entries: int = 200000):
+        self.out_dir, self.num_steps, self.rank, self.max_entries = out_dir, int(num_steps or 1), rank, max_entries
+        self.enabled = out_dir is not None and torch.cuda.is_available()
+        self._step, self.path, self._on = 0, None, False
+
+    def step(self):
+        if not self.enabled or self.path is not None:
+            return
+        if self._step == 0:
+            os.makedirs(self.out_dir, exist_ok=True)
+            torch.cuda.memory._record_memory_history(max_entries=self.max_entries)
+            self._on = True
+        self._step += 1
+        if self._step > self.num_steps:
+            self.dump()
+
+    def dump(self):
+        if self._on and self.path is None:
+            self.path = os.path.join(self.out_dir, f"memory_snapshot_rank{self.rank}.pickle")
+            torch.cuda.memory._dump_snapshot(self.path)
+            torch.cuda.memory._record_memory_history(enabled=None)
+            self._on = False
+
+    def close(self):
+        self.dump()
