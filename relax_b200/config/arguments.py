@@ -263,7 +263,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--use-rollout-entropy": (_R, "the rollout engine returns log-probs only"),
     "--rollout-external": (_R, "external rollout engines are not supported"),
     "--rollout-external-engine-addrs": (_R, "external rollout engines are not supported"),
     "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
@@ -548,6 +547,7 @@ def train_config_from_args(a):
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
         freeze_params_name_list=_freeze_list(a), problem_type=getattr(a, "problem_type", None),
+        use_rollout_entropy=bool(getattr(a, "use_rollout_entropy", False)),
         classification_threshold=float(getattr(a, "classification_threshold", 0.5) or 0.5),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
         ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

@@ -48,6 +48,7 @@ class TrainConfig:
     grpo_std_normalization: bool = True
     balance_data: bool = False
     recompute: bool = False
+    use_rollout_entropy: bool = False         # forward-only actor / reference passes also return per-token entropies
     problem_type: Optional[str] = None        # sequence classification: single_label_classification (default) / multi_label_classification
     classification_threshold: float = 0.5     # multi-label: sigmoid threshold of the accuracy metrics
     pad_multiple: int = 128
@@ -599,7 +600,10 @@ class TrainActor:
 
         with self.timer.span("ref_log_probs"):
             if "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
-                batch["ref_log_probs"] = self.compute_log_prob(batch, "ref")["log_probs"]
+                r_ = self.compute_log_prob(batch, "ref", with_entropy=cfg.use_rollout_entropy)
+                batch["ref_log_probs"] = r_["log_probs"]
+                if cfg.use_rollout_entropy:
+                    batch["ref_entropy"] = r_["entropy"]
         r3 = (cfg.use_rollout_routing_replay and self.mcfg.is_moe and batch.get("rollout_routed_experts") is not None)
         if r3:
             from ..models.moe import RoutingReplay
@@ -621,7 +625,10 @@ class TrainActor:
                     from ..models.moe import RoutingReplay
 
                     RoutingReplay.begin_record()
-                batch["log_probs"] = self.compute_log_prob(batch, tag)["log_probs"]
+                o_ = self.compute_log_prob(batch, tag, with_entropy=cfg.use_rollout_entropy)
+                batch["log_probs"] = o_["log_probs"]
+                if cfg.use_rollout_entropy:      # relax/backends/megatron/model.py forward_only(with_entropy=args.use_rollout_entropy)
+                    batch["entropy"] = o_["entropy"]
                 if replay:
                     RoutingReplay.end()
                     RoutingReplay.begin_replay()          # until the end of this rollout's optimizer steps

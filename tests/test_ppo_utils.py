@@ -205,3 +205,26 @@ def test_reinforce_pp_normalisation_uses_population_moments_and_reports_stats():
     raw = torch.tensor([1.0, 1.0, 1.0, -1.0, -1.0])
     assert torch.allclose(adv, (raw - raw.mean()) / raw.var(unbiased=False).sqrt(), atol=1e-6)
     assert "reinforce_pp_advantage_raw_std" in stats
+
+
+def test_use_rollout_entropy_adds_entropies_to_the_rollout_data():
+    """``--use-rollout-entropy``: the forward-only actor and reference passes also return per-token entropies; they
+    travel with the batch and show up in the rollout summary."""
+    import torch
+
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    actor = TrainActor(get_config("tiny"), TrainConfig(n_samples_per_prompt=2, global_batch_size=4, max_tokens_per_gpu=512,
+                                                       use_rollout_entropy=True, loss=LossConfig(use_kl_loss=True, kl_loss_coef=0.01),
+                                                       optim=OptimizerConfig(lr=1e-5)), with_reference=True)
+    g = torch.Generator().manual_seed(0)
+    toks = [torch.randint(0, 1024, (n,), generator=g).tolist() for n in (12, 9, 14, 10)]
+    batch = {"tokens": toks, "response_lengths": [5, 4, 6, 3], "rewards": [1.0, 0.0, 0.3, 0.9], "loss_masks": [[1] * r for r in (5, 4, 6, 3)],
+             "group_index": [0, 0, 1, 1]}
+    m = actor.train(0, batch)
+    assert [len(e) for e in batch["entropy"]] == [5, 4, 6, 3] and [len(e) for e in batch["ref_entropy"]] == [5, 4, 6, 3]
+    assert all(float(e.min()) >= 0 for e in batch["entropy"])
+    assert m["rollout/entropy"] > 0 and abs(m["rollout/entropy"] - m["rollout/ref_entropy"]) < 1e-5      # reference == initial policy
