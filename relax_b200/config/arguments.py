@@ -270,8 +270,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
     "--use-agentic-rollout": (_R, "agentic rollouts are driven through --custom-generate-function-path (rollout/agentic.py)"),
     # algorithm
-    "--disable-compute-advantages-and-returns": (_R, "advantages are always computed by the trainer"),
-    "--critic-train-only": (_R, "use --num-critic-only-steps for critic warm-up"),
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
@@ -548,6 +546,7 @@ def train_config_from_args(a):
         use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
         freeze_params_name_list=_freeze_list(a), problem_type=getattr(a, "problem_type", None),
         use_rollout_entropy=bool(getattr(a, "use_rollout_entropy", False)),
+        compute_advantages_and_returns=not getattr(a, "disable_compute_advantages_and_returns", False),
         classification_threshold=float(getattr(a, "classification_threshold", 0.5) or 0.5),
         only_train_params_name_list=getattr(a, "only_train_params_name_list", None), loss=loss, optim=optim,
         ci=_ci_config(a), cp_attention="allgather" if getattr(a, "allgather_cp", False) else None)

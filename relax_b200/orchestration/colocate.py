@@ -102,6 +102,7 @@ class ColocateConfig:
     use_health_check: bool = False
     max_consecutive_failures: int = 3
     num_critic_only_steps: int = 0      # PPO: the first rollouts train the critic alone
+    critic_train_only: bool = False     # PPO: never update the policy (critic pre-training runs)
     # more user hooks by path: fn(samples) -> (raw_rewards, shaped_rewards) replaces reward normalisation;
     # fn(args_like, samples) marks samples with remove_sample = True (their loss mask is zeroed);
     # fn(args_like, samples) may rewrite the samples of a rollout before they are converted
@@ -652,7 +653,7 @@ class ColocatedGRPO:
             if self.teacher_pool is not None and data.get("teacher_log_probs") is None:
                 with self.timer.span("teacher_log_probs"):
                     data["teacher_log_probs"] = self.teacher_pool.score(data)
-            m = self.actor.train(rid, data, update_policy=not (self.critic is not None and rid < cfg.num_critic_only_steps))
+            m = self.actor.train(rid, data, update_policy=not (self.critic is not None and (cfg.critic_train_only or rid < cfg.num_critic_only_steps)))
             self.actor.after_train()
             if self.critic is not None:       # `data` now carries the GAE returns computed with those values
                 cm = self.critic.train_critic(rid, data)

@@ -241,7 +241,7 @@ class Controller:
                 buffer_filter_path=_get(a, "buffer_filter_path", None),
                 stop_token_ids=tuple(_get(a, "rollout_stop_token_ids", None) or ()),
                 stop_strings=tuple(_get(a, "rollout_stop", None) or ()), critic_lr=_get(a, "critic_lr", None), use_health_check=bool(_get(a, "use_health_check", False)),
-                max_consecutive_failures=_get(a, "rollout_health_check_max_consecutive_failures", None) or 3, num_critic_only_steps=_get(a, "num_critic_only_steps", 0) or 0,
+                max_consecutive_failures=_get(a, "rollout_health_check_max_consecutive_failures", None) or 3, num_critic_only_steps=_get(a, "num_critic_only_steps", 0) or 0, critic_train_only=bool(_get(a, "critic_train_only", False)),
                 custom_reward_post_process_path=_get(a, "custom_reward_post_process_path", None),
                 rollout_sample_filter_path=_get(a, "rollout_sample_filter_path", None),
                 rollout_data_postprocess_path=_get(a, "rollout_data_postprocess_path", None),

@@ -48,6 +48,7 @@ class TrainConfig:
     grpo_std_normalization: bool = True
     balance_data: bool = False
     recompute: bool = False
+    compute_advantages_and_returns: bool = True   # False (--disable-compute-advantages-and-returns): a custom loss brings its own
     use_rollout_entropy: bool = False         # forward-only actor / reference passes also return per-token entropies
     problem_type: Optional[str] = None        # sequence classification: single_label_classification (default) / multi_label_classification
     classification_threshold: float = 0.5     # multi-label: sigmoid threshold of the accuracy metrics
@@ -638,14 +639,19 @@ class TrainActor:
         rewards = torch.as_tensor(batch["rewards"], dtype=torch.float32, device=dev)
         cat = lambda k: torch.cat([torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch[k]]) \
             if batch.get(k) is not None and len(batch[k]) else None
-        adv, ret = L.compute_advantages_and_returns(
-            cfg.advantage_estimator, rewards, seg_all, mask_all,
-            log_probs=cat("log_probs"), ref_log_probs=cat("ref_log_probs"), values=cat("values"),
-            kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type, gamma=cfg.gamma, lambd=cfg.lambd,
-            normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group, stats_out=(adv_stats := {}),
-        )
-        batch["advantages"] = seg_all.split(adv)
-        batch["returns"] = seg_all.split(ret)
+        adv_stats: dict = {}
+        if cfg.compute_advantages_and_returns:
+            adv, ret = L.compute_advantages_and_returns(
+                cfg.advantage_estimator, rewards, seg_all, mask_all,
+                log_probs=cat("log_probs"), ref_log_probs=cat("ref_log_probs"), values=cat("values"),
+                kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type, gamma=cfg.gamma, lambd=cfg.lambd,
+                normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group, stats_out=adv_stats,
+            )
+            batch["advantages"] = seg_all.split(adv)
+            batch["returns"] = seg_all.split(ret)
+        elif cfg.loss.custom_loss_function is None and self.role == "actor":
+            raise ValueError("--disable-compute-advantages-and-returns needs a custom loss function (the policy losses read "
+                             "the advantages)")
         opd_metric = None
         if cfg.opd_kl_coef != 0.0 and (batch.get("teacher_log_probs") is not None or "teacher" in self.snapshots):
             from ..algo import opd as OPD
