@@ -63,6 +63,13 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
     i, rest = m.groups()
     pre = f"model.layers.{i}."
     if rest == "self_attention.linear_qkv.weight":
+        if cfg.attention_output_gate:
+            # Qwen3.5 (HF Qwen3Next attention): q_proj holds, per head, the query rows followed by the gate rows
+            x = p.view(ng, 2 * qpg + 2, hd, H)
+            qg = torch.stack([x[:, :qpg], x[:, qpg:2 * qpg]], 2)          # [ng, qpg, 2, hd, H]
+            return [(pre + "self_attn.q_proj.weight", qg.reshape(-1, H)),
+                    (pre + "self_attn.k_proj.weight", x[:, 2 * qpg].reshape(-1, H)),
+                    (pre + "self_attn.v_proj.weight", x[:, 2 * qpg + 1].reshape(-1, H))]
         x = p.view(ng, qpg + 2, hd, H)
         return [(pre + "self_attn.q_proj.weight", x[:, :qpg].reshape(-1, H)),
                 (pre + "self_attn.k_proj.weight", x[:, qpg].reshape(-1, H)),
@@ -130,10 +137,14 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
             out[f"mtp.layers.{k}.hnorm.weight"] = hf[pre + "hnorm.weight"]
             out[f"mtp.layers.{k}.eh_proj.weight"] = hf[pre + "eh_proj.weight"]
             out[f"mtp.layers.{k}.final_layernorm.weight"] = hf[pre + "shared_head.norm.weight"]
-        q = hf[pre + "self_attn.q_proj.weight"].view(ng, qpg, hd, H)
         k = hf[pre + "self_attn.k_proj.weight"].view(ng, 1, hd, H)
         v = hf[pre + "self_attn.v_proj.weight"].view(ng, 1, hd, H)
-        out[b + "self_attention.linear_qkv.weight"] = torch.cat([q, k, v], 1).reshape(-1, H)
+        if cfg.attention_output_gate:
+            qg = hf[pre + "self_attn.q_proj.weight"].view(ng, qpg, 2, hd, H)
+            out[b + "self_attention.linear_qkv.weight"] = torch.cat([qg[:, :, 0], qg[:, :, 1], k, v], 1).reshape(-1, H)
+        else:
+            q = hf[pre + "self_attn.q_proj.weight"].view(ng, qpg, hd, H)
+            out[b + "self_attention.linear_qkv.weight"] = torch.cat([q, k, v], 1).reshape(-1, H)
         if cfg.qkv_bias:
             qb = hf[pre + "self_attn.q_proj.bias"].view(ng, qpg, hd)
             kb = hf[pre + "self_attn.k_proj.bias"].view(ng, 1, hd)

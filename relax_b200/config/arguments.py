@@ -76,6 +76,7 @@ FLAGS: dict[str, list] = {
     "rollout": [
         ("--prompt-data", dict(type=str, default=None)), ("--input-key", dict(type=str, default="input")),
         ("--label-key", dict(type=str, default=None)), ("--metadata-key", dict(type=str, default="metadata")),
+        ("--attention-output-gate", _b()), ("--use-gated-attention", _b()), ("--rotary-percent", dict(type=float, default=None)),
         ("--tool-key", dict(type=str, default=None)), ("--apply-chat-template", _b()),
         ("--multimodal-keys", dict(type=json.loads, default=None)),      # {"image": "<row field with the image path(s)>"}
         ("--apply-chat-template-kwargs", dict(type=json.loads, default={})), ("--system-prompt", dict(type=str, default=None)),
@@ -505,6 +506,10 @@ def model_config_from_args(a):
         over["qkv_bias"] = bool(getattr(a, "add_qkv_bias", False))
         over["qk_layernorm"] = bool(getattr(a, "qk_layernorm", False))
         over["tie_word_embeddings"] = not getattr(a, "untie_embeddings_and_output_weights", False)
+    if getattr(a, "attention_output_gate", False) or getattr(a, "use_gated_attention", False):
+        over["attention_output_gate"] = True
+    if getattr(a, "rotary_percent", None) is not None:
+        over["rotary_percent"] = float(a.rotary_percent)
     if getattr(a, "num_labels", None):
         over["num_classes"] = int(a.num_labels)       # sequence-classification head on the last token
     if a.model_name:

@@ -60,6 +60,10 @@ class ModelConfig:
     num_classes: int = 0                  # >0: sequence-classification head on the last token
     # multi-token prediction blocks after the trunk (0 = none)
     mtp_num_layers: int = 0
+    # Qwen3.5-style softmax attention: a sigmoid gate on the attention output (the query projection also produces one
+    # gate value per query feature) and rotary embedding on the first `rotary_percent` of every head only
+    attention_output_gate: bool = False
+    rotary_percent: float = 1.0
     # hybrid stacks: every `linear_attention_freq`-th layer is softmax attention, the others Gated DeltaNet (0 = all softmax)
     linear_attention_freq: int = 0
     gdn_k_heads: int = 2
@@ -93,9 +97,14 @@ class ModelConfig:
     def kv_size(self) -> int:
         return self.num_query_groups * self.head_dim
 
+    @property
+    def rotary_dim(self) -> int:
+        """Leading features of a head that are rotated (even; the whole head unless ``rotary_percent`` < 1)."""
+        return self.head_dim if self.rotary_percent >= 1.0 else max(2, int(self.head_dim * self.rotary_percent) // 2 * 2)
+
     def num_parameters(self) -> int:
         h, L = self.hidden_size, self.num_layers
-        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        attn = h * (self.q_size * (2 if self.attention_output_gate else 1) + 2 * self.kv_size) + self.q_size * h
         if self.qk_layernorm:
             attn += 2 * self.head_dim
         if self.is_moe:
@@ -127,6 +136,9 @@ _reg(ModelConfig(name="tiny-moe", num_layers=2, hidden_size=256, num_attention_h
                  moe_ffn_hidden_size=128, dtype="fp32"))
 _reg(ModelConfig(name="tiny-next", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, dtype="fp32"))
+_reg(ModelConfig(name="tiny-qwen35", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
+                 ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, attention_output_gate=True, rotary_percent=0.25,
+                 dtype="fp32"))
 _reg(ModelConfig(name="tiny-dsa", num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=4, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, dsa_topk=8, dtype="fp32"))
 _reg(ModelConfig(name="tiny-dsv3", num_layers=3, hidden_size=256, num_attention_heads=4, num_query_groups=2,

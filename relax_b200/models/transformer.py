@@ -67,8 +67,11 @@ class Attention(nn.Module):
         self.linear_qkv = nn.Module()
         self.linear_qkv.layer_norm_weight = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
         # draw the FULL weight so every TP layout of the same seed holds the same model
-        full = gen.draw(f"layers.{layer_idx}.qkv", (cfg.num_query_groups * (self.qpg + 2) * hd, cfg.hidden_size), 0.02)
-        rows = self.ng * (self.qpg + 2) * hd
+        # rows of one KV group: its query heads, (Qwen3.5 gated attention) one gate row per query feature, its key, its value
+        self.gate = bool(cfg.attention_output_gate)
+        self.grp = self.qpg * (2 if self.gate else 1) + 2
+        full = gen.draw(f"layers.{layer_idx}.qkv", (cfg.num_query_groups * self.grp * hd, cfg.hidden_size), 0.02)
+        rows = self.ng * self.grp * hd
         self.linear_qkv.weight = nn.Parameter(full[ps.tp.rank * rows:(ps.tp.rank + 1) * rows].to(device=device, dtype=dtype))
         if cfg.qkv_bias:
             self.linear_qkv.bias = nn.Parameter(torch.zeros(rows, dtype=dtype, device=device))
@@ -85,11 +88,20 @@ class Attention(nn.Module):
     def split_qkv(self, qkv):
         T = qkv.shape[0]
         hd = self.cfg.head_dim
-        x = qkv.view(T, self.ng, self.qpg + 2, hd)
+        x = qkv.view(T, self.ng, self.grp, hd)
         q = x[:, :, : self.qpg].reshape(T, self.ng * self.qpg, hd)
-        k = x[:, :, self.qpg]
-        v = x[:, :, self.qpg + 1]
+        k = x[:, :, self.grp - 2]
+        v = x[:, :, self.grp - 1]
+        if self.gate:
+            self._gate = x[:, :, self.qpg: 2 * self.qpg].reshape(T, self.ng * self.qpg, hd)
         return q, k, v
+
+    def _rope(self, x, cos, sin):
+        rot = self.cfg.rotary_dim
+        if rot >= self.cfg.head_dim:
+            return ops.apply_rope(x, cos, sin)
+        # partial rotary: only the first `rot` features of every head carry position
+        return torch.cat([ops.apply_rope(x[..., :rot].contiguous(), cos, sin), x[..., rot:]], -1)
 
     def forward(self, x_normed, cos, sin, cu_seqlens, attn_fn=None, max_seqlen=None):
         cfg = self.cfg
@@ -102,12 +114,15 @@ class Attention(nn.Module):
         if cfg.qk_layernorm:
             q = ops.rmsnorm(q, self.q_layernorm.weight, cfg.rms_norm_eps)
             k = ops.rmsnorm(k, self.k_layernorm.weight, cfg.rms_norm_eps)
-        q = ops.apply_rope(q, cos, sin)
-        k = ops.apply_rope(k, cos, sin)
+        q = self._rope(q, cos, sin)
+        k = self._rope(k, cos, sin)
         if attn_fn is not None:
             o = attn_fn(self.layer_idx, q, k, v)
         else:
             o = ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=True, max_seqlen=max_seqlen)
+        if self.gate:        # Qwen3.5: attention output gated per feature by a sigmoid of the gate projection
+            o = o * torch.sigmoid(self._gate.float()).to(o.dtype)
+            self._gate = None
         o = o.reshape(o.shape[0], -1)
         y = TP.linear_rs(o, self.linear_proj.weight, self.ps.tp)
         if hasattr(self.linear_proj, "lora_A"):
@@ -305,7 +320,7 @@ class GPTModel(nn.Module):
         return self.output_layer.weight
 
     def rope_tables(self, positions):
-        return ops.rope_cos_sin(positions, self.cfg.head_dim, self.cfg.rope_theta, self.cfg.mrope_section)
+        return ops.rope_cos_sin(positions, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section)
 
     # ------------------------------------------------------------------ forward
     def forward(self, tokens=None, positions=None, cu_seqlens=None, hidden_in=None, attn_fn=None,

