@@ -160,6 +160,22 @@ _reg(ModelConfig(name="qwen2.5-7b", num_layers=28, hidden_size=3584, num_attenti
 _reg(ModelConfig(name="qwen3-vl-8b", num_layers=36, hidden_size=4096, num_attention_heads=32, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=12288, vocab_size=151936, rope_theta=5e6,
                  vision=VisionConfig(out_hidden_size=4096), mrope_section=(24, 20, 20), image_token_id=151655))
+# Qwen3-VL family (scripts/models/qwen3-vl-*.sh of the reference): the language-model shapes of those recipes with the
+# Qwen-VL tower of this package; the 30B-A3B variant is the MoE shape
+_reg(ModelConfig(name="qwen3-vl-2b", num_layers=28, hidden_size=2048, num_attention_heads=16, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=6144, vocab_size=151936, rope_theta=1e6,
+                 vision=VisionConfig(out_hidden_size=2048), mrope_section=(24, 20, 20), image_token_id=151655))
+_reg(ModelConfig(name="qwen3-vl-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,
+                 head_dim=128, ffn_hidden_size=9728, vocab_size=151936, rope_theta=5e6, tie_word_embeddings=True,
+                 vision=VisionConfig(out_hidden_size=2560), mrope_section=(24, 20, 20), image_token_id=151655))
+_reg(ModelConfig(name="qwen3-vl-30b-a3b", num_layers=48, hidden_size=2048, num_attention_heads=32, num_query_groups=4,
+                 head_dim=128, ffn_hidden_size=6144, vocab_size=151936, rope_theta=5e6, num_experts=128, moe_top_k=8,
+                 moe_ffn_hidden_size=768, vision=VisionConfig(out_hidden_size=2048), mrope_section=(24, 20, 20),
+                 image_token_id=151655))
+_reg(ModelConfig(name="qwen3-omni-30b-a3b", num_layers=48, hidden_size=2048, num_attention_heads=32, num_query_groups=4,
+                 head_dim=128, ffn_hidden_size=768, vocab_size=152064, rope_theta=1e6, num_experts=128, moe_top_k=8,
+                 moe_ffn_hidden_size=768, vision=VisionConfig(out_hidden_size=2048), mrope_section=(24, 20, 20),
+                 image_token_id=151655))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,
