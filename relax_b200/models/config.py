@@ -136,6 +136,10 @@ _reg(ModelConfig(name="tiny-moe", num_layers=2, hidden_size=256, num_attention_h
                  moe_ffn_hidden_size=128, dtype="fp32"))
 _reg(ModelConfig(name="tiny-next", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, dtype="fp32"))
+_reg(ModelConfig(name="tiny-vl", num_layers=2, hidden_size=256, num_attention_heads=4, num_query_groups=2, head_dim=64,
+                 ffn_hidden_size=688, vocab_size=1024, dtype="fp32", mrope_section=(8, 12, 12), image_token_id=7,
+                 vision=VisionConfig(num_layers=1, hidden_size=64, num_heads=2, ffn_hidden_size=96, patch_size=4,
+                                     out_hidden_size=256)))
 _reg(ModelConfig(name="tiny-qwen35", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, attention_output_gate=True, rotary_percent=0.25,
                  dtype="fp32"))

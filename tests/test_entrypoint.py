@@ -205,3 +205,14 @@ def test_sequence_classification_runs(tmp_path):
     assert main(base + ["--num-labels", "3", "--problem-type", "multi_label_classification", "--label-key", "labels", "--save", save]) == 0
     lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
     assert get(lines[-1], "label_accuracy") is not None and get(lines[-1], "loss") < get(lines[0], "loss")
+
+
+def test_vision_language_run_through_the_entrypoint(tmp_path):
+    """A vision-language preset through the train entrypoint: synthetic image prompts, tower frozen by the switch."""
+    save = str(tmp_path / "vl")
+    assert main(["--model-name", "tiny-vl", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2",
+                 "--global-batch-size", "4", "--rollout-max-prompt-len", "24", "--rollout-max-response-len", "8", "--lr", "1e-4",
+                 "--max-tokens-per-gpu", "512", "--num-rollout", "2", "--freeze-vision-model", "--save", save]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert len(lines) == 2 and lines[-1]["train_rollout_logprob_abs_diff"] < 1e-3
+    assert lines[-1]["rollout/prompt_lengths"] == 24         # text + image placeholders
