@@ -158,3 +158,31 @@ def test_vision_language_loop_on_gpu():
     assert not torch.equal(tower0, run.actor.model.vision.patch_embed.detach())
     C.check_error_flag()
     run.close()
+
+
+def test_lora_adapter_mode_on_gpu():
+    """Adapter-mode LoRA on the GPU: rank-16 factor GEMMs inside prefill and the decode graph; the engine's log-probs
+    follow the trainer's adapted forward after factor-only syncs."""
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.ops import cuda as C
+    from relax_b200.orchestration.colocate import ColocateConfig, ColocatedGRPO
+    from relax_b200.train import lora as LR
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    torch.manual_seed(0)
+    cfg = ColocateConfig(
+        model=_cfg(),
+        train=TrainConfig(n_samples_per_prompt=4, global_batch_size=16, max_tokens_per_gpu=1024, pad_multiple=128,
+                          lora=LR.LoRAConfig(rank=16, alpha=32), loss=LossConfig(), optim=OptimizerConfig(lr=2e-3, weight_decay=0.0)),
+        rollout_batch_size=4, prompt_len=32, max_response_len=24, kv_blocks=128, lora_adapter_mode=True,
+        stop_token_ids=list(range(0, 4096, 9)))
+    run = ColocatedGRPO(cfg, device="cuda")
+    for _ in range(3):
+        m = run.step()
+        assert math.isfinite(m["loss"])
+        assert m["train_rollout_logprob_abs_diff"] < 0.05, m["train_rollout_logprob_abs_diff"]
+    b = next(v for k, v in run.engine.weights.lora.items() if k.endswith("qkv.lora_B"))
+    assert b.abs().sum() > 0 and run._base_synced
+    C.check_error_flag()
+    run.close()
