@@ -5,6 +5,9 @@
 * ``coordinator`` - the weight-sync coordinator (register / heartbeat / topology / weight-metadata long poll,
   relax/checkpoint_service/coordinator/service.py);
 * ``viewer``      - the rollout result viewer (relax/entrypoints/visualize.py);
+* ``engine``      - one rollout engine behind HTTP (``/generate``, ``/flush_cache``, ``/pause_generation``,
+  ``/continue_generation``, ``/abort_request``, ``/get_server_info``; relax/backends/sglang/sglang_engine.py talks to
+  its engines over the same surface); weights from ``--hf-checkpoint``;
 * ``router``      - the request router as an HTTP proxy in front of engine servers (least loaded / sticky by key,
   health probes, ``/add_worker`` ``/remove_worker`` ``/list_workers``; relax/engine/router/router.py);
 * ``teacher``     - an on-policy-distillation teacher: ``POST /score`` returns the teacher's log-probs of the response
@@ -21,7 +24,8 @@ import time
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="relax_b200 control-plane services")
-    ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher", "router"])
+    ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher", "router", "engine"])
+    ap.add_argument("--kv-blocks", type=int, default=4096, help="engine: KV-cache blocks of 16 tokens")
     ap.add_argument("--workers", nargs="*", default=None, help="router: base URLs of the engine servers to start with")
     ap.add_argument("--router-timeout", type=float, default=600.0)
     ap.add_argument("--router-health-check-failure-threshold", type=int, default=3)
@@ -52,6 +56,24 @@ def main(argv=None) -> int:
         for u in a.workers or []:
             r.add_worker(u)
         srv, _, _ = serve_router(r, a.host, a.port, timeout_s=a.router_timeout)
+    elif a.service == "engine":
+        import torch
+
+        from ..models.config import get_config
+        from ..rollout.engine import RolloutEngine
+        from ..rollout.http_server import EngineServer
+
+        dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
+        cfg = get_config(a.model_name)
+        eng = RolloutEngine(cfg, device=dev, dtype=torch.bfloat16 if dev.startswith("cuda") else torch.float32,
+                            num_kv_blocks=a.kv_blocks, block_size=16, seed=a.seed)
+        if a.hf_checkpoint:
+            from ..checkpoint import hf as H
+
+            H.validate_against_hf(cfg, a.hf_checkpoint)
+            H.load_hf_into_rollout(a.hf_checkpoint, cfg, eng.weights)
+        es = EngineServer(eng, a.host, a.port)
+        srv = es.httpd
     elif a.service == "teacher":
         import torch
 
