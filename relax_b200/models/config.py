@@ -180,6 +180,20 @@ _reg(ModelConfig(name="qwen3-omni-30b-a3b", num_layers=48, hidden_size=2048, num
                  head_dim=128, ffn_hidden_size=768, vocab_size=152064, rope_theta=1e6, num_experts=128, moe_top_k=8,
                  moe_ffn_hidden_size=768, vision=VisionConfig(out_hidden_size=2048), mrope_section=(24, 20, 20),
                  image_token_id=151655))
+# Qwen3.5 family (scripts/models/qwen35-*.sh): hybrid stack - three Gated-DeltaNet layers, then one gated softmax-attention
+# layer with 256-wide heads and rotary on their first quarter.  Trainer-side families (the rollout engine serves plain
+# softmax attention).
+_reg(ModelConfig(name="qwen3.5-9b", num_layers=32, hidden_size=4096, num_attention_heads=16, num_query_groups=4, head_dim=256,
+                 ffn_hidden_size=12288, vocab_size=248320, rope_theta=1e7, attention_output_gate=True, rotary_percent=0.25,
+                 linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128))
+_reg(ModelConfig(name="qwen3.5-35b-a3b", num_layers=40, hidden_size=2048, num_attention_heads=16, num_query_groups=2, head_dim=256,
+                 ffn_hidden_size=512, vocab_size=248320, rope_theta=1e7, attention_output_gate=True, rotary_percent=0.25,
+                 linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, num_experts=256, moe_top_k=8,
+                 moe_ffn_hidden_size=512, moe_shared_expert_ffn=512, moe_shared_expert_gate=True))
+# dots.ocr (scripts/models/dotsocr2.sh): a Qwen2.5-1.5B-shaped language model behind a vision tower
+_reg(ModelConfig(name="dotsocr2", num_layers=28, hidden_size=1536, num_attention_heads=12, num_query_groups=2, head_dim=128,
+                 ffn_hidden_size=8960, vocab_size=151936, qk_layernorm=False, qkv_bias=True, rope_theta=1e6,
+                 vision=VisionConfig(out_hidden_size=1536), mrope_section=(16, 24, 24), image_token_id=151655))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,
