@@ -110,11 +110,20 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
     raise ValueError(f"unknown layer parameter {rest!r}")
 
 
+_NORM_SUFFIXES = ("norm.weight", "layernorm.weight", "layer_norm_weight")
+
+
+def _is_norm(name: str) -> bool:
+    return name.endswith(_NORM_SUFFIXES)
+
+
 def convert_state_to_hf(cfg: ModelConfig, state: dict) -> dict:
     out = {}
     for k, v in state.items():
         for hk, hv in megatron_to_hf(cfg, k, v):
-            out[hk] = hv.contiguous()
+            # zero-centred norms (Qwen3.5, ``--apply-layernorm-1p``): the checkpoint stores gamma - 1, the model here
+            # keeps gamma itself, so the offset lives in the conversion only
+            out[hk] = (hv - 1.0).contiguous() if (cfg.layernorm_zero_centered and _is_norm(hk)) else hv.contiguous()
     if cfg.tie_word_embeddings:
         out.pop("lm_head.weight", None)
     return out
@@ -122,6 +131,8 @@ def convert_state_to_hf(cfg: ModelConfig, state: dict) -> dict:
 
 def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
     """Full HF state dict -> full Megatron-layout state dict (inverse of :func:`convert_state_to_hf`)."""
+    if cfg.layernorm_zero_centered:
+        hf = {k: (v + 1.0 if _is_norm(k) else v) for k, v in hf.items()}
     H, hd = cfg.hidden_size, cfg.head_dim
     ng, qpg = cfg.num_query_groups, cfg.num_attention_heads // cfg.num_query_groups
     out = {"embedding.word_embeddings.weight": hf["model.embed_tokens.weight"],

@@ -76,7 +76,7 @@ FLAGS: dict[str, list] = {
     "rollout": [
         ("--prompt-data", dict(type=str, default=None)), ("--input-key", dict(type=str, default="input")),
         ("--label-key", dict(type=str, default=None)), ("--metadata-key", dict(type=str, default="metadata")),
-        ("--attention-output-gate", _b()), ("--use-gated-attention", _b()), ("--rotary-percent", dict(type=float, default=None)),
+        ("--attention-output-gate", _b()), ("--use-gated-attention", _b()), ("--apply-layernorm-1p", _b()), ("--rotary-percent", dict(type=float, default=None)),
         ("--tool-key", dict(type=str, default=None)), ("--apply-chat-template", _b()),
         ("--multimodal-keys", dict(type=json.loads, default=None)),      # {"image": "<row field with the image path(s)>"}
         ("--apply-chat-template-kwargs", dict(type=json.loads, default={})), ("--system-prompt", dict(type=str, default=None)),
@@ -508,6 +508,8 @@ def model_config_from_args(a):
         over["tie_word_embeddings"] = not getattr(a, "untie_embeddings_and_output_weights", False)
     if getattr(a, "attention_output_gate", False) or getattr(a, "use_gated_attention", False):
         over["attention_output_gate"] = True
+    if getattr(a, "apply_layernorm_1p", False):
+        over["layernorm_zero_centered"] = True
     if getattr(a, "rotary_percent", None) is not None:
         over["rotary_percent"] = float(a.rotary_percent)
     if getattr(a, "num_labels", None):

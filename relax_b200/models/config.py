@@ -64,6 +64,9 @@ class ModelConfig:
     # gate value per query feature) and rotary embedding on the first `rotary_percent` of every head only
     attention_output_gate: bool = False
     rotary_percent: float = 1.0
+    # norm weights are stored zero-centred (gamma - 1) in this family's checkpoints (``--apply-layernorm-1p``); the model
+    # keeps gamma, the Hugging Face conversion adds / removes the offset
+    layernorm_zero_centered: bool = False
     # hybrid stacks: every `linear_attention_freq`-th layer is softmax attention, the others Gated DeltaNet (0 = all softmax)
     linear_attention_freq: int = 0
     gdn_k_heads: int = 2
@@ -185,10 +188,10 @@ _reg(ModelConfig(name="qwen3-omni-30b-a3b", num_layers=48, hidden_size=2048, num
 # softmax attention).
 _reg(ModelConfig(name="qwen3.5-9b", num_layers=32, hidden_size=4096, num_attention_heads=16, num_query_groups=4, head_dim=256,
                  ffn_hidden_size=12288, vocab_size=248320, rope_theta=1e7, attention_output_gate=True, rotary_percent=0.25,
-                 linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128))
+                 layernorm_zero_centered=True, linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128))
 _reg(ModelConfig(name="qwen3.5-35b-a3b", num_layers=40, hidden_size=2048, num_attention_heads=16, num_query_groups=2, head_dim=256,
                  ffn_hidden_size=512, vocab_size=248320, rope_theta=1e7, attention_output_gate=True, rotary_percent=0.25,
-                 linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, num_experts=256, moe_top_k=8,
+                 layernorm_zero_centered=True, linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, num_experts=256, moe_top_k=8,
                  moe_ffn_hidden_size=512, moe_shared_expert_ffn=512, moe_shared_expert_gate=True))
 # dots.ocr (scripts/models/dotsocr2.sh): a Qwen2.5-1.5B-shaped language model behind a vision tower
 _reg(ModelConfig(name="dotsocr2", num_layers=28, hidden_size=1536, num_attention_heads=12, num_query_groups=2, head_dim=128,
