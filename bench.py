@@ -71,6 +71,7 @@ def parse():
     ap.add_argument("--time-budget-s", type=float, default=float(os.environ.get("RELAX_B200_BENCH_BUDGET_S", "780")),
                     help="wall-clock budget of the whole process; warm-up / timed step counts shrink to fit (0: no budget)")
     ap.add_argument("--decode-window", type=int, default=None, help="decode steps per host round trip in the rollout engine")
+    ap.add_argument("--profile-host", action="store_true", help="debug: with --profile-kernels, also list the host-side operators by self CPU time")
     ap.add_argument("--profile-kernels", type=int, default=0,
                     help="debug: after the timed steps run ONE more step under torch.profiler and print rank 0's top N kernels "
                          "by device time to stderr (the extra step is not part of any reported number)")
@@ -367,7 +368,8 @@ def main():
     if args.profile_kernels > 0:
         from torch.profiler import ProfilerActivity, profile
 
-        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        acts = [ProfilerActivity.CUDA] + ([ProfilerActivity.CPU] if args.profile_host else [])
+        with profile(activities=acts) as prof:
             t_p = time.perf_counter()
             run.step()
             torch.cuda.synchronize()
@@ -379,6 +381,13 @@ def main():
             for e in rows[:args.profile_kernels]:
                 print(f"[profile] {e.device_time_total / 1e3:10.2f} ms {100 * e.device_time_total / max(tot, 1):5.1f}% x{e.count:6d}  {e.key[:110]}",
                       file=sys.stderr)
+            if args.profile_host:
+                host = sorted(prof.key_averages(), key=lambda e: -e.self_cpu_time_total)
+                tot_h = sum(e.self_cpu_time_total for e in host)
+                print(f"[profile] host: {tot_h / 1e6:.3f} s of self CPU time in profiled operators", file=sys.stderr)
+                for e in host[:args.profile_kernels]:
+                    print(f"[profile]   host {e.self_cpu_time_total / 1e3:9.2f} ms x{e.count:6d} (mean {e.self_cpu_time_total / max(e.count, 1):7.1f} us)  {e.key[:90]}",
+                          file=sys.stderr)
             # where the device sat idle: for every kernel, the time since the latest end of any earlier kernel
             from torch.autograd import DeviceType
 

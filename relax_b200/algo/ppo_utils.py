@@ -20,6 +20,18 @@ from typing import Sequence
 
 import torch
 
+def to_device_async(t: torch.Tensor, device) -> torch.Tensor:
+    """Host tensor -> ``device`` without blocking the host: through pinned memory with a non-blocking copy (the
+    caching host allocator keeps the pinned block alive until the copy has run).  A plain ``.to(device)`` from
+    pageable memory waits for everything queued on the stream, which stops the host from running ahead of the GPU."""
+    if device is None:
+        return t
+    device = torch.device(device)
+    if device.type != "cuda" or t.is_cuda:
+        return t.to(device)
+    return t.pin_memory().to(device, non_blocking=True)
+
+
 # --------------------------------------------------------------------------- segments
 
 
@@ -28,11 +40,16 @@ class Segments:
     """Describes how a packed 1-D tensor splits into per-sample pieces."""
 
     lengths: torch.Tensor  # [B] int64 (on the data device)
+    # the same lengths on the host when the caller had them there: ``split`` / ``ids`` then need no device read (a
+    # ``tolist()`` or a ``repeat_interleave`` without a known output size blocks the host until the stream drains)
+    host: "list | None" = None
 
     @staticmethod
     def from_lengths(lengths: Sequence[int] | torch.Tensor, device=None) -> "Segments":
-        t = torch.as_tensor(lengths, dtype=torch.int64, device=device)
-        return Segments(t)
+        if torch.is_tensor(lengths):
+            return Segments(lengths.to(device=device, dtype=torch.int64))
+        host = [int(x) for x in lengths]
+        return Segments(to_device_async(torch.tensor(host, dtype=torch.int64), device), host)
 
     @property
     def num(self) -> int:
@@ -45,9 +62,8 @@ class Segments:
 
     @property
     def ids(self) -> torch.Tensor:
-        return torch.repeat_interleave(
-            torch.arange(self.num, device=self.lengths.device), self.lengths
-        )
+        total = sum(self.host) if self.host is not None else None
+        return torch.repeat_interleave(torch.arange(self.num, device=self.lengths.device), self.lengths, output_size=total)
 
     def seg_sum(self, x: torch.Tensor) -> torch.Tensor:
         out = torch.zeros(self.num, dtype=x.dtype, device=x.device)
@@ -57,7 +73,7 @@ class Segments:
         return per_seg[self.ids.to(per_seg.device)]
 
     def split(self, x: torch.Tensor) -> list[torch.Tensor]:
-        return list(torch.split(x, self.lengths.tolist()))
+        return list(torch.split(x, self.host if self.host is not None else self.lengths.tolist()))
 
 
 def pack(xs: Sequence[torch.Tensor]) -> tuple[torch.Tensor, Segments]:

@@ -56,11 +56,20 @@ def pack_samples(token_lists: Sequence, response_lengths: Sequence[int], pad_mul
         tr.append(torch.arange(s + L - R, s + L))
     logit_rows = torch.cat(lr) if lr else torch.zeros(0, dtype=torch.int64)
     target_rows = torch.cat(tr) if tr else torch.zeros(0, dtype=torch.int64)
+    # one pinned, non-blocking copy for the four index vectors (a blocking copy per tensor would make the host wait for
+    # the previous micro-batch's kernels five times per micro-batch)
+    from ..algo.ppo_utils import to_device_async
+
+    n_t, n_r = int(tokens.numel()), int(logit_rows.numel())
+    flat = to_device_async(torch.cat([tokens, positions, logit_rows, target_rows, torch.tensor(cu, dtype=torch.int64)]), device)
+    tokens, positions = flat[:n_t], flat[n_t:2 * n_t]
+    logit_rows, target_rows = flat[2 * n_t:2 * n_t + n_r], flat[2 * n_t + n_r:2 * n_t + 2 * n_r]
+    cu_dev = flat[2 * n_t + 2 * n_r:].to(torch.int32)
     return PackedBatch(
-        tokens=tokens.to(device), positions=positions.to(device),
-        cu_seqlens=torch.tensor(cu, dtype=torch.int32, device=device),
+        tokens=tokens, positions=positions,
+        cu_seqlens=cu_dev,
         total_lengths=lens, response_lengths=[int(r) for r in response_lengths],
-        logit_rows=logit_rows.to(device), target_rows=target_rows.to(device),
+        logit_rows=logit_rows, target_rows=target_rows,
         max_seqlen=max(lens + ([pad] if pad else [])) if lens else 0, num_real_tokens=total,
     )
 

@@ -712,7 +712,9 @@ class TrainActor:
         seg = Segments.from_lengths(pb.response_lengths, device=dev)
         denoms = None
         if batch.get("sample_index_mask_sums") is not None:
-            denoms = torch.as_tensor([batch["sample_index_mask_sums"][i] for i in idx], dtype=torch.float32, device=dev)
+            from ..algo.ppo_utils import to_device_async
+
+            denoms = to_device_async(torch.tensor([float(batch["sample_index_mask_sums"][i]) for i in idx], dtype=torch.float32), dev)
         return L.LossBatch(seg=seg, loss_mask=f("loss_masks"), advantages=f("advantages"),
                            old_log_probs=f("log_probs"), ref_log_probs=f("ref_log_probs"),
                            rollout_log_probs=f("rollout_log_probs"), returns=f("returns"), values=f("values"),
