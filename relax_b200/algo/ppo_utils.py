@@ -20,16 +20,51 @@ from typing import Sequence
 
 import torch
 
+class _PinnedRing:
+    """A few pinned staging buffers reused round-robin.  ``tensor.pin_memory()`` per call would ask the driver for a new
+    pinned block for every new size (a slow call that also stalls the device); here a slot grows in powers of two and is
+    reused once the copy that last read it has run (an event per slot; with 8 slots the wait is never taken in practice)."""
+
+    SLOTS = 8
+
+    def __init__(self):
+        self.bufs = [None] * self.SLOTS
+        self.events = [None] * self.SLOTS
+        self.i = 0
+
+    def stage(self, t: torch.Tensor, device: torch.device) -> torch.Tensor:
+        nbytes = t.numel() * t.element_size()
+        k = self.i
+        self.i = (self.i + 1) % self.SLOTS
+        if self.events[k] is not None:
+            self.events[k].synchronize()
+        if self.bufs[k] is None or self.bufs[k].numel() < nbytes:
+            self.bufs[k] = torch.empty(max(4096, 1 << max(0, (nbytes - 1).bit_length())), dtype=torch.uint8, pin_memory=True)
+        src = self.bufs[k][:nbytes].view(t.dtype).view(t.shape)
+        src.copy_(t)
+        out = src.to(device, non_blocking=True)
+        ev = self.events[k] or torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(device))
+        self.events[k] = ev
+        return out
+
+
+_RING = None
+
+
 def to_device_async(t: torch.Tensor, device) -> torch.Tensor:
-    """Host tensor -> ``device`` without blocking the host: through pinned memory with a non-blocking copy (the
-    caching host allocator keeps the pinned block alive until the copy has run).  A plain ``.to(device)`` from
-    pageable memory waits for everything queued on the stream, which stops the host from running ahead of the GPU."""
+    """Host tensor -> ``device`` without blocking the host: through a pinned staging buffer with a non-blocking copy.
+    A plain ``.to(device)`` from pageable memory waits for everything queued on the stream, which stops the host from
+    running ahead of the GPU."""
+    global _RING
     if device is None:
         return t
     device = torch.device(device)
-    if device.type != "cuda" or t.is_cuda:
+    if device.type != "cuda" or t.is_cuda or t.numel() == 0:
         return t.to(device)
-    return t.pin_memory().to(device, non_blocking=True)
+    if _RING is None:
+        _RING = _PinnedRing()
+    return _RING.stage(t.contiguous(), device)
 
 
 # --------------------------------------------------------------------------- segments
