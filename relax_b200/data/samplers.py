@@ -89,3 +89,63 @@ class IdentityWindowSampler(StreamingTokenBudgetSampler):
             out.extend(r for r, _ in groups[si])
             tot += gl
         return out
+
+
+class StreamingTQIterator:
+    """Micro-batches pulled from the transfer queue on demand, while the rollout is still producing
+    (relax/utils/data/stream_dataloader.py StreamingTQIterator :1071-1250).
+
+    ``next()`` blocks until a token-budget-sized micro-batch of rows with all ``data_fields`` is available and returns
+    ``(batch, meta)`` with ``__loss_scale__`` added to the batch; it stops when the partition is sealed and this task has
+    consumed every row.  Rows of this data-parallel rank only: row ``i`` of the partition belongs to rank ``i % dp_size``
+    (every rank sees the same partition, the rule keeps the ranks disjoint without talking to each other).  ``window_quota``
+    bounds how many rows one iterator hands out (one optimizer window of a longer rollout)."""
+
+    def __init__(self, queue, data_fields, partition_id: str, token_budget: int, loss_scale: float = 1.0, dp_rank: int = 0,
+                 dp_size: int = 1, task_name: str = "actor_train", window_quota: int = 0, poll_s: float = 0.05,
+                 timeout_s: float = 3600.0):
+        self.q, self.fields, self.part, self.task = queue, list(data_fields), partition_id, f"{task_name}/dp{dp_rank}"
+        self.loss_scale, self.dp_rank, self.dp_size = loss_scale, dp_rank, dp_size
+        self.window_quota, self.poll_s, self.timeout_s = window_quota, poll_s, timeout_s
+        self.handed_out = 0
+        self._budget = StreamingTokenBudgetSampler(token_budget)
+
+    def _sampler(self, ready, meta, n):
+        mine = [(r, m) for r, m in zip(ready, meta) if int(r) % self.dp_size == self.dp_rank]
+        if not mine:
+            return []
+        left = self.window_quota - self.handed_out if self.window_quota else 0
+        return self._budget([r for r, _ in mine], [m for _, m in mine], left if self.window_quota else 0)
+
+    def _mine_left(self) -> bool:
+        """Rows of this rank that the task has not consumed yet (known only once the partition is sealed)."""
+        with self.q._cv:
+            part = self.q._p.get(self.part)
+            if part is None:
+                return True
+            done = part.consumed.get(self.task, set())
+            return any(int(r) % self.dp_size == self.dp_rank and r not in done for r in part.rows)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        import time
+
+        if self.window_quota and self.handed_out >= self.window_quota:
+            raise StopIteration
+        t0 = time.monotonic()
+        while True:
+            meta = self.q.get_meta(self.fields, 1, self.part, self.task, sampler=self._sampler, timeout=self.poll_s, allow_partial=True)
+            if meta is not None and len(meta):
+                self.handed_out += len(meta)
+                batch = self.q.get_data(meta)
+                batch["__loss_scale__"] = self.loss_scale
+                return batch, meta
+            with self.q._cv:
+                part = self.q._p.get(self.part)
+                sealed = part is not None and part.sealed
+            if sealed and not self._mine_left():
+                raise StopIteration
+            if time.monotonic() - t0 > self.timeout_s:
+                raise TimeoutError(f"no micro-batch from partition {self.part} within {self.timeout_s:.0f} s")

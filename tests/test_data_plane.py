@@ -107,3 +107,44 @@ def test_log_rollout_data_masked_token_means_and_scalars():
     assert m["rollout/prompt_lengths"] == 1.5
     assert abs(m["rollout/log_probs"] - (-1.0 + -3.0) / 2) < 1e-6        # the masked-out -9 does not count
     assert abs(m["rollout/advantages"]) < 1e-9 and "rollout/tokens" not in m
+
+
+def test_streaming_iterator_consumes_while_the_producer_is_still_writing():
+    """StreamingTQIterator: token-budget micro-batches arrive while rows are still being produced, data-parallel ranks
+    get disjoint rows, the loss scale rides along, and iteration ends when the sealed partition is consumed."""
+    import threading
+    import time
+
+    from relax_b200.data import transfer_queue as tq
+    from relax_b200.data.samplers import StreamingTQIterator
+
+    q = tq.TransferQueue()
+    part = tq.partition_name(0)
+    lens = [5, 9, 4, 7, 6, 3, 8, 2]
+
+    def produce():
+        for i, L in enumerate(lens):
+            time.sleep(0.02)
+            q.put({"tokens": [list(range(L))], "response_lengths": [L // 2]}, part, custom_meta=[{"total_lengths": L, "sample_index": i}],
+                  is_last=(i == len(lens) - 1))
+
+    th = threading.Thread(target=produce)
+    th.start()
+    seen = {0: [], 1: []}
+    first_batch_time = {}
+
+    def consume(r):
+        it = StreamingTQIterator(q, ["tokens", "response_lengths"], part, token_budget=12, loss_scale=0.5, dp_rank=r, dp_size=2)
+        for batch, meta in it:
+            first_batch_time.setdefault(r, time.monotonic())
+            assert batch["__loss_scale__"] == 0.5
+            assert sum(len(t) for t in batch["tokens"]) <= 12 or len(batch["tokens"]) == 1
+            seen[r] += [len(t) for t in batch["tokens"]]
+
+    cs = [threading.Thread(target=consume, args=(r,)) for r in (0, 1)]
+    [c.start() for c in cs]
+    th.join()
+    t_done = time.monotonic()
+    [c.join(timeout=20) for c in cs]
+    assert sorted(seen[0]) == sorted(lens[0::2]) and sorted(seen[1]) == sorted(lens[1::2])
+    assert min(first_batch_time.values()) < t_done, "consumption started before the producer finished"
