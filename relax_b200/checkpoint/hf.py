@@ -303,8 +303,35 @@ def load_hf_into_model(path: str, cfg: ModelConfig, ps, model, strict: bool = Tr
     from .dist_ckpt import load_full_state
 
     dtype = next(model.parameters()).dtype
-    full = hf_to_megatron_state(cfg, load_hf_checkpoint(path, dequantize=True, dtype=dtype))
+    hf = load_hf_checkpoint(path, dequantize=True, dtype=dtype)
+    if any(k.startswith("model.language_model.") for k in hf):
+        # vision-language checkpoints keep the decoder under model.language_model.* (and the tower under model.visual.*)
+        hf = {("model." + k[len("model.language_model."):] if k.startswith("model.language_model.") else k): v for k, v in hf.items()}
+    tower = getattr(model, "vision", None)
+    missing = []
+    if tower is not None:
+        from ..models.vision import load_vision_from_hf
+
+        missing += load_vision_from_hf(tower, hf, strict=strict)
+    lm = {k: v for k, v in hf.items() if not k.startswith(("visual.", "model.visual."))}
+    full = hf_to_megatron_state(cfg, lm)
+    if tower is not None:       # the tower's tensors were filled above: leave them out of the layout-aware load
+        named = [(n, p) for n, p in model.named_parameters() if not n.startswith("vision.")]
+        return missing + load_full_state(cfg, ps, _NamedView(named), full, strict)
     return load_full_state(cfg, ps, model, full, strict)
+
+
+class _NamedView:
+    """Just enough of a module for ``load_full_state``: a fixed list of named parameters."""
+
+    def __init__(self, named):
+        self._named = list(named)
+
+    def named_parameters(self):
+        return iter(self._named)
+
+    def parameters(self):
+        return (p for _, p in self._named)
 
 
 def config_from_hf(path: str) -> ModelConfig:

@@ -90,6 +90,9 @@ class VisionBlock(nn.Module):
             fc1, fc2 = nn.Parameter(w1), nn.Parameter(w2)
         self.fc1 = fc1                 # [gate; up], each f_pad rows
         self.fc2 = fc2
+        # Qwen2.5-VL's tower has a bias on every linear (zero here until a checkpoint is loaded)
+        zb = lambda n: nn.Parameter(torch.zeros(n, dtype=dtype, device=device))
+        self.proj_bias, self.fc1_bias, self.fc2_bias = zb(h), zb(2 * fp), zb(h)
 
     def forward(self, x, cos, sin, cu_seqlens, max_seqlen):
         cfg = self.cfg
@@ -99,9 +102,9 @@ class VisionBlock(nn.Module):
         q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
         q, k = ops.apply_rope(q.contiguous(), cos, sin), ops.apply_rope(k.contiguous(), cos, sin)
         o = ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=False, max_seqlen=max_seqlen)
-        x = x + ops.linear(o.reshape(o.shape[0], -1), self.proj)
+        x = x + ops.linear(o.reshape(o.shape[0], -1), self.proj, self.proj_bias)
         y = ops.rmsnorm(x, self.norm2, cfg.rms_norm_eps)
-        return x + ops.linear(ops.swiglu(ops.linear(y, self.fc1)), self.fc2)
+        return x + ops.linear(ops.swiglu(ops.linear(y, self.fc1, self.fc1_bias)), self.fc2, self.fc2_bias)
 
 
 class VisionEncoder(nn.Module):
@@ -116,6 +119,8 @@ class VisionEncoder(nn.Module):
         self.merger_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
         self.merger_fc1 = nn.Parameter((torch.randn(h * m2, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
         self.merger_fc2 = nn.Parameter((torch.randn(cfg.out_hidden_size, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
+        self.merger_fc1_bias = nn.Parameter(torch.zeros(h * m2, dtype=dtype, device=device))
+        self.merger_fc2_bias = nn.Parameter(torch.zeros(cfg.out_hidden_size, dtype=dtype, device=device))
 
     def forward(self, pixel_patches: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
         """``pixel_patches [N, patch_dim]`` (all images concatenated, merge-window-major), ``grid_thw [n_img, 3]`` in
@@ -131,7 +136,8 @@ class VisionEncoder(nn.Module):
             x = blk(x, cos, sin, cu, mx)
         x = ops.rmsnorm(x, self.merger_norm, cfg.rms_norm_eps)
         x = x.view(-1, cfg.hidden_size * cfg.spatial_merge_size ** 2)
-        return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1)), self.merger_fc2)
+        return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1, self.merger_fc1_bias)), self.merger_fc2,
+                          self.merger_fc2_bias)
 
 
 def mrope_positions(input_ids: Sequence[int], image_grid_thw: Sequence[Sequence[int]], image_token_id: int,
@@ -214,3 +220,63 @@ class VLModel(nn.Module):
         elif has:
             emb = merge_image_embeddings(emb, self.vision(pixel_patches, grid_thw), tokens, self.image_token_id)
         return self.lm(tokens, positions, cu_seqlens, inputs_embeds=emb, max_seqlen=max_seqlen)
+
+
+# ----------------------------------------------------------------------------- Hugging Face names of the tower
+def vision_state_to_hf(enc: "VisionEncoder", prefix: str = "visual.") -> dict:
+    """This tower's parameters under the names of a Qwen2.5-VL checkpoint (``visual.patch_embed.proj.weight`` as the
+    3-D convolution kernel, ``visual.blocks.N.attn.qkv / proj``, ``mlp.gate_proj / up_proj / down_proj`` with the width
+    padding removed, ``visual.merger.ln_q / mlp.0 / mlp.2``)."""
+    c = enc.cfg
+    out = {prefix + "patch_embed.proj.weight": enc.patch_embed.detach().view(c.hidden_size, c.in_channels, c.temporal_patch_size,
+                                                                             c.patch_size, c.patch_size)}
+    for i, b in enumerate(enc.blocks):
+        p, f, fp = f"{prefix}blocks.{i}.", b.f, b.f_pad
+        out[p + "norm1.weight"], out[p + "norm2.weight"] = b.norm1.detach(), b.norm2.detach()
+        out[p + "attn.qkv.weight"], out[p + "attn.qkv.bias"] = b.qkv.detach(), b.qkv_bias.detach()
+        out[p + "attn.proj.weight"], out[p + "attn.proj.bias"] = b.proj.detach(), b.proj_bias.detach()
+        out[p + "mlp.gate_proj.weight"], out[p + "mlp.up_proj.weight"] = b.fc1.detach()[:f], b.fc1.detach()[fp:fp + f]
+        out[p + "mlp.gate_proj.bias"], out[p + "mlp.up_proj.bias"] = b.fc1_bias.detach()[:f], b.fc1_bias.detach()[fp:fp + f]
+        out[p + "mlp.down_proj.weight"], out[p + "mlp.down_proj.bias"] = b.fc2.detach()[:, :f], b.fc2_bias.detach()
+    out[prefix + "merger.ln_q.weight"] = enc.merger_norm.detach()
+    out[prefix + "merger.mlp.0.weight"], out[prefix + "merger.mlp.0.bias"] = enc.merger_fc1.detach(), enc.merger_fc1_bias.detach()
+    out[prefix + "merger.mlp.2.weight"], out[prefix + "merger.mlp.2.bias"] = enc.merger_fc2.detach(), enc.merger_fc2_bias.detach()
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+@torch.no_grad()
+def load_vision_from_hf(enc: "VisionEncoder", hf: dict, strict: bool = True) -> list:
+    """Fill the tower from a Hugging Face state dict; the prefix may be ``visual.`` or ``model.visual.`` (newer
+    checkpoints).  Returns the tower tensors for which the checkpoint had nothing (empty when ``strict``)."""
+    prefix = next((p for p in ("model.visual.", "visual.") if any(k.startswith(p) for k in hf)), None)
+    if prefix is None:
+        if strict:
+            raise KeyError("the checkpoint holds no vision tower (no visual.* tensors)")
+        return ["visual.*"]
+    want = vision_state_to_hf(enc, prefix)
+    missing = [k for k in want if k not in hf]
+    if missing and strict:
+        raise KeyError(f"vision tower tensors missing from the checkpoint: {missing[:4]} ...")
+    g = lambda k: hf[prefix + k].to(enc.patch_embed.dtype)
+    has = lambda k: (prefix + k) in hf
+    if has("patch_embed.proj.weight"):
+        enc.patch_embed.copy_(g("patch_embed.proj.weight").reshape(enc.patch_embed.shape))
+    for i, b in enumerate(enc.blocks):
+        p, f, fp = f"blocks.{i}.", b.f, b.f_pad
+        for ours, theirs in ((b.norm1, "norm1.weight"), (b.norm2, "norm2.weight"), (b.qkv, "attn.qkv.weight"), (b.qkv_bias, "attn.qkv.bias"),
+                             (b.proj, "attn.proj.weight"), (b.proj_bias, "attn.proj.bias"), (b.fc2_bias, "mlp.down_proj.bias")):
+            if has(p + theirs):
+                ours.copy_(g(p + theirs))
+        if has(p + "mlp.gate_proj.weight"):
+            b.fc1.zero_()
+            b.fc1[:f], b.fc1[fp:fp + f] = g(p + "mlp.gate_proj.weight"), g(p + "mlp.up_proj.weight")
+            b.fc2.zero_()
+            b.fc2[:, :f] = g(p + "mlp.down_proj.weight")
+        if has(p + "mlp.gate_proj.bias"):
+            b.fc1_bias.zero_()
+            b.fc1_bias[:f], b.fc1_bias[fp:fp + f] = g(p + "mlp.gate_proj.bias"), g(p + "mlp.up_proj.bias")
+    for ours, theirs in ((enc.merger_norm, "merger.ln_q.weight"), (enc.merger_fc1, "merger.mlp.0.weight"), (enc.merger_fc1_bias, "merger.mlp.0.bias"),
+                         (enc.merger_fc2, "merger.mlp.2.weight"), (enc.merger_fc2_bias, "merger.mlp.2.bias")):
+        if has(theirs):
+            ours.copy_(g(theirs))
+    return missing

@@ -183,3 +183,40 @@ def test_colocated_grpo_with_images_end_to_end():
         assert m["train_rollout_logprob_abs_diff"] < 1e-3
     assert not torch.equal(tower0, run.actor.model.vision.patch_embed.detach())
     run.close()
+
+
+def test_vision_language_checkpoint_names_round_trip(tmp_path):
+    """A vision-language model saved under Qwen2.5-VL's Hugging Face names (decoder under ``model.language_model.*``, tower
+    under ``model.visual.*`` with the convolution-shaped patch embedding and un-padded MLP width) loads back exactly."""
+    import torch
+
+    from relax_b200.checkpoint import hf as HF
+    from relax_b200.models.vision import load_vision_from_hf, vision_state_to_hf
+    from relax_b200.train.actor import TrainActor, TrainConfig
+
+    cfg = _tiny_vl()
+    a = TrainActor(cfg, TrainConfig(), seed=1, with_optimizer=False)
+    g = torch.Generator().manual_seed(0)
+    for n, p in a.model.named_parameters():      # biases start at zero: give everything a value
+        p.data.copy_(torch.randn(p.shape, generator=g) * 0.05)
+    for b in a.model.vision.blocks:              # the width padding is structurally zero
+        b.fc1.data[b.f:b.f_pad] = 0; b.fc1.data[b.f_pad + b.f:] = 0; b.fc2.data[:, b.f:] = 0
+        b.fc1_bias.data[b.f:b.f_pad] = 0; b.fc1_bias.data[b.f_pad + b.f:] = 0
+    tower = vision_state_to_hf(a.model.vision, "model.visual.")
+    v = cfg.vision
+    assert tower["model.visual.patch_embed.proj.weight"].shape == (v.hidden_size, v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)
+    assert tower["model.visual.blocks.0.mlp.gate_proj.weight"].shape[0] == v.ffn_hidden_size
+    lm = HF.convert_state_to_hf(cfg, {n: p.detach() for n, p in a.model.named_parameters() if not n.startswith("vision.")})
+    state = {("model.language_model." + k[len("model."):] if k.startswith("model.") else k): t for k, t in lm.items()}
+    state.update(tower)
+    d = str(tmp_path / "vl")
+    HF.save_hf_checkpoint(d, cfg, state)
+    b = TrainActor(cfg, TrainConfig(), seed=2, with_optimizer=False)
+    assert HF.load_hf_into_model(d, cfg, b.ps, b.model) == []
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert torch.equal(p, q), n
+    # a text-only checkpoint leaves the tower alone unless strict
+    import pytest
+
+    with pytest.raises(KeyError):
+        load_vision_from_hf(b.model.vision, lm, strict=True)
