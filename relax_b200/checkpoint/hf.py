@@ -117,10 +117,47 @@ def _is_norm(name: str) -> bool:
     return name.endswith(_NORM_SUFFIXES)
 
 
+def _vision_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list:
+    """One tensor of the vision tower (``vision.*`` in the trainer's state) under its Qwen2.5-VL checkpoint name(s)."""
+    v = cfg.vision
+    f = v.ffn_hidden_size
+    fp = (f + 63) // 64 * 64
+    n = name[len("vision."):]
+    pre = "model.visual."
+    top = {"patch_embed": ("patch_embed.proj.weight", lambda x: x.reshape(v.hidden_size, v.in_channels, v.temporal_patch_size, v.patch_size, v.patch_size)),
+           "merger_norm": ("merger.ln_q.weight", None), "merger_fc1": ("merger.mlp.0.weight", None), "merger_fc1_bias": ("merger.mlp.0.bias", None),
+           "merger_fc2": ("merger.mlp.2.weight", None), "merger_fc2_bias": ("merger.mlp.2.bias", None)}
+    if n in top:
+        hk, fn = top[n]
+        return [(pre + hk, fn(t) if fn else t)]
+    m = re.match(r"blocks\.(\d+)\.(\w+)$", n)
+    if not m:
+        raise ValueError(f"unknown vision tower parameter {name!r}")
+    b, leaf = pre + f"blocks.{m.group(1)}.", m.group(2)
+    simple = {"norm1": "norm1.weight", "norm2": "norm2.weight", "qkv": "attn.qkv.weight", "qkv_bias": "attn.qkv.bias",
+              "proj": "attn.proj.weight", "proj_bias": "attn.proj.bias", "fc2_bias": "mlp.down_proj.bias"}
+    if leaf in simple:
+        return [(b + simple[leaf], t)]
+    if leaf == "fc1":
+        return [(b + "mlp.gate_proj.weight", t[:f]), (b + "mlp.up_proj.weight", t[fp:fp + f])]
+    if leaf == "fc1_bias":
+        return [(b + "mlp.gate_proj.bias", t[:f]), (b + "mlp.up_proj.bias", t[fp:fp + f])]
+    if leaf == "fc2":
+        return [(b + "mlp.down_proj.weight", t[:, :f])]
+    raise ValueError(f"unknown vision tower parameter {name!r}")
+
+
 def convert_state_to_hf(cfg: ModelConfig, state: dict) -> dict:
     out = {}
+    vl = cfg.vision is not None and any(strip_prefix(k).startswith("vision.") for k in state)
     for k, v in state.items():
+        if strip_prefix(k).startswith("vision."):
+            for hk, hv in _vision_to_hf(cfg, strip_prefix(k), v):
+                out[hk] = hv.contiguous()
+            continue
         for hk, hv in megatron_to_hf(cfg, k, v):
+            if vl and hk.startswith("model."):       # vision-language layout: the decoder lives under model.language_model.*
+                hk = "model.language_model." + hk[len("model."):]
             # zero-centred norms (Qwen3.5, ``--apply-layernorm-1p``): the checkpoint stores gamma - 1, the model here
             # keeps gamma itself, so the offset lives in the conversion only
             out[hk] = (hv - 1.0).contiguous() if (cfg.layernorm_zero_centered and _is_norm(hk)) else hv.contiguous()
