@@ -154,6 +154,9 @@ class DisaggregatedRL:
         if self.is_trainer:
             need_ref = cfg.train.loss.use_kl_loss or cfg.train.kl_coef != 0
             self.actor = TrainActor(cfg.model, cfg.train, self.ps, device=device, seed=cfg.seed, with_reference=need_ref)
+            if cfg.model.vision is not None and any(p.requires_grad for p in self.actor.model.vision.parameters()):
+                raise ValueError("disaggregated mode pushes the language model's weights only: freeze the vision tower "
+                                 "(--freeze-vision-model / freeze_params_name_list=['^vision\\.'])")
         if self.is_rollout:
             cuda = self.device.type == "cuda"
             shm = None if cuda else f"/dev/shm/relax_b200_{self.tag}_{self.rank}.bin"
@@ -167,7 +170,22 @@ class DisaggregatedRL:
             self._shm = shm
             if cfg.weight_push == "peer":
                 self.region = SharedWeightRegion(self.engine.weights, self.tag, self.rank)
-            ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
+            if cfg.model.vision is not None:
+                # vision-language: the rollout rank builds the tower itself with the trainer's initialisation (same seed
+                # rule as TrainActor) and keeps it; the trainer side must therefore hold the tower fixed (checked there)
+                from ..models.vision import VisionEncoder, vision_config_from_model
+                from ..rollout.data_source import SyntheticImagePromptDataset
+
+                self.vision = VisionEncoder(vision_config_from_model(cfg.model), dtype=dtype, device=device, seed=cfg.seed + 17)
+                self.engine.attach_vision(self.vision)
+                v = cfg.model.vision
+                side = 4 * v.spatial_merge_size
+                n_img = side * side // v.spatial_merge_size ** 2
+                ds = SyntheticImagePromptDataset(cfg.num_prompts, max(1, (cfg.prompt_len - n_img) // 2), cfg.model.vocab_size,
+                                                 cfg.model.image_token_id, (side, side),
+                                                 v.in_channels * v.temporal_patch_size * v.patch_size ** 2, v.spatial_merge_size, seed=cfg.seed)
+            else:
+                ds = SyntheticPromptDataset(cfg.num_prompts, cfg.prompt_len, cfg.model.vocab_size, seed=cfg.seed)
             self.data_source = RolloutDataSource(ds, cfg.train.n_samples_per_prompt, shuffle=False, seed=cfg.rollout_seed)
             self.reward_fn = get_reward_spec(cfg.rm_type).fn
         dist.barrier()        # every exported buffer is being served before anyone maps it
@@ -267,7 +285,11 @@ class DisaggregatedRL:
         mine = groups[self.engine_id * per:(self.engine_id + 1) * per]
         flat = [s for g in mine for s in g]
         sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k, max_new_tokens=cfg.max_response_len)
-        ids = [self.engine.add_request(s.tokens, sp, s.group_index) for s in flat]
+        ids = []
+        for s_ in flat:
+            im = s_.multimodal_train_inputs
+            ids.append(self.engine.add_request(s_.tokens, sp, s_.group_index,
+                                               **({k: im.get(k) for k in ("pixel_patches", "grid_thw")} if im else {})))
         res = {}
         while self.engine.has_work:
             for r in self.engine.step():

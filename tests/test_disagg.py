@@ -88,3 +88,40 @@ def test_disjoint_pools_trainer_tp2_broadcast_arm():
     out = run_distributed(_worker, 4, "broadcast", 2, 2, 2, os.getpid() % 10000 + 4, timeout=600)
     ro = [o for o in out if o["role"] == "rollout"]
     assert len(ro) == 2 and all(o["version"] == 3 for o in ro)
+
+
+def _vl_worker(rank, world, port_tag):
+    from relax_b200.algo.loss import LossConfig
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.disagg import DisaggConfig, DisaggregatedRL
+    from relax_b200.train.actor import TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    cfg = DisaggConfig(
+        model=get_config("tiny-vl"),
+        train=TrainConfig(n_samples_per_prompt=2, global_batch_size=8, pad_multiple=1, max_tokens_per_gpu=1024,
+                          freeze_params_name_list=[r"^vision\."], loss=LossConfig(use_kl_loss=True, kl_loss_coef=0.001),
+                          optim=OptimizerConfig(lr=1e-2)),
+        trainer_ranks=(0,), rollout_ranks=(1,), trainer_tp=1, rollout_tp=1, rollout_batch_size=4, prompt_len=24, max_response_len=6,
+        kv_blocks=128, kv_block_size=4, num_rollout=2, max_staleness=1, weight_push="peer", tag=f"v{port_tag}", handshake_timeout_s=120.0)
+    run = DisaggregatedRL(cfg, device="cpu")
+    out = run.run()
+    import torch.distributed as dist
+
+    res = {"role": "actor" if run.is_trainer else "rollout"}
+    if run.is_trainer:
+        res["metrics"] = [(rid, {k: float(v) for k, v in m.items()}) for rid, m in out]
+    dist.barrier()
+    run.close()
+    return res
+
+
+def test_vision_language_on_disjoint_pools():
+    """Config-3 shape on the CPU: image prompts generated by an engine process with its own (frozen) tower, batches with
+    the patches through the queue service, trained by another process; log-probs of the two sides agree."""
+    out = run_distributed(_vl_worker, 2, os.getpid() % 10000 + 7, timeout=600)
+    tr = [o for o in out if o["role"] == "actor"][0]
+    assert len(tr["metrics"]) == 2
+    assert all(m["response_tokens"] > 0 for _, m in tr["metrics"])
+    # the first rollout was generated with the weights the trainer still holds (later ones may be one version behind)
+    assert tr["metrics"][0][1]["train_rollout_logprob_abs_diff"] < 1e-3
