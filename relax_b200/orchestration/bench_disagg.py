@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     ap.add_argument("--num-rollout", type=int, default=4)
     ap.add_argument("--max-staleness", type=int, default=1)
     ap.add_argument("--arms", default="peer,broadcast")
+    ap.add_argument("--image-side", type=int, default=0,
+                    help="vision-language models: patches per side of the synthetic image in every prompt (32 = 448 x 448 pixels = 256 tokens)")
     a = ap.parse_args(argv)
 
     from ..algo.loss import LossConfig
@@ -58,8 +60,10 @@ def main(argv=None) -> int:
     blocks = seqs * ((a.prompt_len + a.response_len) // 16 + 2) + 16
     for i, arm in enumerate(a.arms.split(",")):
         cfg = DisaggConfig(
-            model=mcfg, train=TrainConfig(n_samples_per_prompt=a.group_size, global_batch_size=a.prompts * a.group_size,
+            model=mcfg, image_grid_side=a.image_side,
+            train=TrainConfig(n_samples_per_prompt=a.group_size, global_batch_size=a.prompts * a.group_size,
                                           max_tokens_per_gpu=8192, pad_multiple=128 if cuda else 1,
+                                          freeze_params_name_list=[r"^vision\."] if mcfg.vision is not None else None,
                                           loss=LossConfig(eps_clip=0.2, use_kl_loss=True, kl_loss_coef=0.001),
                                           optim=OptimizerConfig(lr=1e-6)),
             trainer_ranks=tr, rollout_ranks=ro, trainer_tp=a.trainer_tp, rollout_tp=a.rollout_tp,

@@ -73,6 +73,7 @@ class DisaggConfig:
     num_rollout: int = 4
     max_staleness: int = 1
     update_weights_interval: int = 1
+    image_grid_side: int = 0              # vision-language models: patches per side of the synthetic images (0: 4 x merge size)
     weight_push: str = "peer"            # "peer": NVLink stores into the engines' buffers; "broadcast": NCCL baseline
     seed: int = 0
     rollout_seed: int = 42
@@ -179,7 +180,7 @@ class DisaggregatedRL:
                 self.vision = VisionEncoder(vision_config_from_model(cfg.model), dtype=dtype, device=device, seed=cfg.seed + 17)
                 self.engine.attach_vision(self.vision)
                 v = cfg.model.vision
-                side = 4 * v.spatial_merge_size
+                side = cfg.image_grid_side or 4 * v.spatial_merge_size
                 n_img = side * side // v.spatial_merge_size ** 2
                 ds = SyntheticImagePromptDataset(cfg.num_prompts, max(1, (cfg.prompt_len - n_img) // 2), cfg.model.vocab_size,
                                                  cfg.model.image_token_id, (side, side),
