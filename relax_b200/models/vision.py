@@ -102,9 +102,11 @@ class VisionBlock(nn.Module):
         q, k, v = qkv[:, 0], qkv[:, 1], qkv[:, 2]
         q, k = ops.apply_rope(q.contiguous(), cos, sin), ops.apply_rope(k.contiguous(), cos, sin)
         o = ops.attention_varlen(q, k, v.contiguous(), cu_seqlens, causal=False, max_seqlen=max_seqlen)
-        x = x + ops.linear(o.reshape(o.shape[0], -1), self.proj, self.proj_bias)
+        # the biases are added as separate elementwise steps: these linears then take exactly the bias-free GEMM paths
+        # (the tower is a small share of a step; the q/k/v bias above rides in the GEMM epilogue)
+        x = x + (ops.linear(o.reshape(o.shape[0], -1), self.proj) + self.proj_bias)
         y = ops.rmsnorm(x, self.norm2, cfg.rms_norm_eps)
-        return x + ops.linear(ops.swiglu(ops.linear(y, self.fc1, self.fc1_bias)), self.fc2, self.fc2_bias)
+        return x + (ops.linear(ops.swiglu(ops.linear(y, self.fc1) + self.fc1_bias), self.fc2) + self.fc2_bias)
 
 
 class VisionEncoder(nn.Module):
@@ -136,8 +138,8 @@ class VisionEncoder(nn.Module):
             x = blk(x, cos, sin, cu, mx)
         x = ops.rmsnorm(x, self.merger_norm, cfg.rms_norm_eps)
         x = x.view(-1, cfg.hidden_size * cfg.spatial_merge_size ** 2)
-        return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1, self.merger_fc1_bias)), self.merger_fc2,
-                          self.merger_fc2_bias)
+        return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1) + self.merger_fc1_bias), self.merger_fc2) \
+            + self.merger_fc2_bias
 
 
 def mrope_positions(input_ids: Sequence[int], image_grid_thw: Sequence[Sequence[int]], image_token_id: int,

@@ -34,28 +34,31 @@ class SyntheticPromptDataset:
 
 class SyntheticImagePromptDataset:
     """Random prompts with one random "image" each: ``text_len`` tokens, a run of image placeholders, ``text_len``
-    tokens.  Patches are Gaussian noise of the tower's patch size (benchmarks / tests of the vision-language loop)."""
+    tokens.  Patches are Gaussian noise of the tower's patch size (benchmarks / tests of the vision-language loop).
+    Rows are made on access from a per-row seed, so a large ``num_prompts`` costs nothing up front (one 448 x 448 image
+    is 4.8 MB of patches)."""
 
     def __init__(self, num_prompts: int, text_len: int, vocab_size: int, image_token_id: int, grid_hw=(8, 8),
                  patch_dim: int = 1176, merge: int = 2, seed: int = 0):
-        g = torch.Generator().manual_seed(seed)
         gh, gw = grid_hw
         assert gh % merge == 0 and gw % merge == 0
-        n_img = gh * gw // (merge * merge)
-        self.rows = []
-        for _ in range(num_prompts):
-            text = torch.randint(0, vocab_size, (2 * text_len,), generator=g)
-            text[text == image_token_id] = (image_token_id + 1) % vocab_size
-            toks = text[:text_len].tolist() + [image_token_id] * n_img + text[text_len:].tolist()
-            self.rows.append({"prompt_tokens": toks, "label": None,
-                              "multimodal": {"pixel_patches": torch.randn(gh * gw, patch_dim, generator=g),
-                                             "grid_thw": torch.tensor([[1, gh, gw]])}})
+        self.n, self.text_len, self.vocab, self.img_id = num_prompts, text_len, vocab_size, image_token_id
+        self.gh, self.gw, self.patch_dim, self.merge, self.seed = gh, gw, patch_dim, merge, seed
 
     def __len__(self):
-        return len(self.rows)
+        return self.n
 
     def __getitem__(self, i):
-        return self.rows[i]
+        if not 0 <= i < self.n:
+            raise IndexError(i)
+        g = torch.Generator().manual_seed(self.seed * 1000003 + i)
+        n_img = self.gh * self.gw // (self.merge * self.merge)
+        text = torch.randint(0, self.vocab, (2 * self.text_len,), generator=g)
+        text[text == self.img_id] = (self.img_id + 1) % self.vocab
+        toks = text[:self.text_len].tolist() + [self.img_id] * n_img + text[self.text_len:].tolist()
+        return {"prompt_tokens": toks, "label": None,
+                "multimodal": {"pixel_patches": torch.randn(self.gh * self.gw, self.patch_dim, generator=g),
+                               "grid_thw": torch.tensor([[1, self.gh, self.gw]])}}
 
 
 class JsonlPromptDataset:
