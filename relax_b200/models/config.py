@@ -20,6 +20,12 @@ class VisionConfig:
     in_channels: int = 3
     temporal_patch_size: int = 2
     out_hidden_size: int = 3584
+    # dots.ocr's tower (relax/models/dots_ocr/vision.py): RMSNorm after the patch projection and after the last block, a
+    # LayerNorm (with bias) in front of the merger, its own norm epsilon
+    patch_norm: bool = False
+    post_trunk_norm: bool = False
+    merger_layernorm: bool = False
+    rms_norm_eps: "float | None" = None
 
 
 @dataclass
@@ -193,10 +199,13 @@ _reg(ModelConfig(name="qwen3.5-35b-a3b", num_layers=40, hidden_size=2048, num_at
                  ffn_hidden_size=512, vocab_size=248320, rope_theta=1e7, attention_output_gate=True, rotary_percent=0.25,
                  layernorm_zero_centered=True, linear_attention_freq=4, gdn_k_heads=16, gdn_v_heads=32, gdn_head_dim=128, num_experts=256, moe_top_k=8,
                  moe_ffn_hidden_size=512, moe_shared_expert_ffn=512, moe_shared_expert_gate=True))
-# dots.ocr (scripts/models/dotsocr2.sh): a Qwen2.5-1.5B-shaped language model behind a vision tower
+# dots.ocr (scripts/models/dotsocr2.sh): a Qwen2.5-1.5B-shaped language model behind the dots tower (42 blocks of 1536, head_dim 128)
 _reg(ModelConfig(name="dotsocr2", num_layers=28, hidden_size=1536, num_attention_heads=12, num_query_groups=2, head_dim=128,
                  ffn_hidden_size=8960, vocab_size=151936, qk_layernorm=False, qkv_bias=True, rope_theta=1e6,
-                 vision=VisionConfig(out_hidden_size=1536), mrope_section=(16, 24, 24), image_token_id=151655))
+                 vision=VisionConfig(num_layers=42, hidden_size=1536, num_heads=12, ffn_hidden_size=4224, temporal_patch_size=1,
+                                     out_hidden_size=1536, patch_norm=True, post_trunk_norm=True, merger_layernorm=True,
+                                     rms_norm_eps=1e-5),
+                 mrope_section=(16, 24, 24), image_token_id=151655))
 _reg(ModelConfig(name="qwen3-0.6b", num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8,
                  head_dim=128, ffn_hidden_size=3072, vocab_size=151936, tie_word_embeddings=True))
 _reg(ModelConfig(name="qwen3-4b", num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8,

@@ -36,6 +36,9 @@ class VisionConfig:
     out_hidden_size: int = 3584
     rms_norm_eps: float = 1e-6
     rope_theta: float = 10000.0
+    patch_norm: bool = False          # RMSNorm on the patch embeddings (dots.ocr)
+    post_trunk_norm: bool = False     # RMSNorm after the last block (dots.ocr)
+    merger_layernorm: bool = False    # LayerNorm with bias in front of the merger instead of RMSNorm (dots.ocr)
 
     @property
     def head_dim(self) -> int:
@@ -119,6 +122,12 @@ class VisionEncoder(nn.Module):
         self.blocks = nn.ModuleList([VisionBlock(cfg, dtype, device, gen) for _ in range(cfg.depth)])
         m2 = cfg.spatial_merge_size ** 2
         self.merger_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        if cfg.patch_norm:
+            self.patch_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        if cfg.post_trunk_norm:
+            self.post_trunk_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
+        if cfg.merger_layernorm:
+            self.merger_norm_bias = nn.Parameter(torch.zeros(h, dtype=dtype, device=device))
         self.merger_fc1 = nn.Parameter((torch.randn(h * m2, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
         self.merger_fc2 = nn.Parameter((torch.randn(cfg.out_hidden_size, h * m2, generator=gen) * 0.02).to(device=device, dtype=dtype))
         self.merger_fc1_bias = nn.Parameter(torch.zeros(h * m2, dtype=dtype, device=device))
@@ -129,6 +138,8 @@ class VisionEncoder(nn.Module):
         patches.  Returns ``[N / merge^2, out_hidden]`` language-model embeddings."""
         cfg = self.cfg
         x = ops.linear(pixel_patches.to(self.patch_embed.dtype), self.patch_embed)
+        if cfg.patch_norm:
+            x = ops.rmsnorm(x, self.patch_norm, cfg.rms_norm_eps)
         cos, sin = vision_rope_tables(grid_thw, cfg.head_dim, cfg.rope_theta, cfg.spatial_merge_size)
         lens = (grid_thw[:, 0] * grid_thw[:, 1] * grid_thw[:, 2]).to(torch.int32)
         cu = torch.zeros(len(lens) + 1, dtype=torch.int32, device=x.device)
@@ -136,7 +147,13 @@ class VisionEncoder(nn.Module):
         mx = int(lens.max())
         for blk in self.blocks:
             x = blk(x, cos, sin, cu, mx)
-        x = ops.rmsnorm(x, self.merger_norm, cfg.rms_norm_eps)
+        if cfg.post_trunk_norm:
+            x = ops.rmsnorm(x, self.post_trunk_norm, cfg.rms_norm_eps)
+        if cfg.merger_layernorm:
+            x = torch.nn.functional.layer_norm(x.float(), (cfg.hidden_size,), self.merger_norm.float(), self.merger_norm_bias.float(),
+                                               1e-6).to(x.dtype)
+        else:
+            x = ops.rmsnorm(x, self.merger_norm, cfg.rms_norm_eps)
         x = x.view(-1, cfg.hidden_size * cfg.spatial_merge_size ** 2)
         return ops.linear(torch.nn.functional.gelu(ops.linear(x, self.merger_fc1) + self.merger_fc1_bias), self.merger_fc2) \
             + self.merger_fc2_bias
@@ -191,7 +208,8 @@ def vision_config_from_model(mc) -> VisionConfig:
     return VisionConfig(patch_size=v.patch_size, temporal_patch_size=v.temporal_patch_size, in_channels=v.in_channels,
                         hidden_size=v.hidden_size, num_heads=v.num_heads, intermediate_size=v.ffn_hidden_size,
                         depth=v.num_layers, spatial_merge_size=v.spatial_merge_size, out_hidden_size=v.out_hidden_size,
-                        rms_norm_eps=mc.rms_norm_eps)
+                        rms_norm_eps=v.rms_norm_eps if v.rms_norm_eps is not None else mc.rms_norm_eps,
+                        patch_norm=v.patch_norm, post_trunk_norm=v.post_trunk_norm, merger_layernorm=v.merger_layernorm)
 
 
 class VLModel(nn.Module):

@@ -220,3 +220,48 @@ def test_vision_language_checkpoint_names_round_trip(tmp_path):
 
     with pytest.raises(KeyError):
         load_vision_from_hf(b.model.vision, lm, strict=True)
+
+
+def test_dots_ocr_tower_variant_matches_a_plain_statement():
+    """The dots.ocr tower: RMSNorm on the patch embeddings and after the trunk, LayerNorm in front of the merger, one
+    temporal slice per patch - against a direct PyTorch statement of the same network."""
+    import math
+
+    import torch
+    import torch.nn.functional as F
+
+    from relax_b200 import ops
+    from relax_b200.models.config import get_config
+    from relax_b200.models.vision import VisionConfig, VisionEncoder, vision_config_from_model, vision_rope_tables
+
+    full = vision_config_from_model(get_config("dotsocr2"))
+    assert full.depth == 42 and full.head_dim == 128 and full.patch_norm and full.post_trunk_norm and full.merger_layernorm
+    cfg = VisionConfig(patch_size=4, temporal_patch_size=1, hidden_size=64, num_heads=2, intermediate_size=96, depth=2,
+                       out_hidden_size=48, rms_norm_eps=1e-5, patch_norm=True, post_trunk_norm=True, merger_layernorm=True)
+    enc = VisionEncoder(cfg, seed=4)
+    g = torch.Generator().manual_seed(1)
+    for p in enc.parameters():
+        p.data.add_(torch.randn(p.shape, generator=g) * 0.05)
+    grid = torch.tensor([[1, 4, 6]])
+    px = torch.randn(24, cfg.patch_dim, generator=g)
+    got = enc(px, grid)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.rms_norm_eps) * w
+
+    x = rms(px @ enc.patch_embed.t(), enc.patch_norm)
+    cos, sin = vision_rope_tables(grid, cfg.head_dim, cfg.rope_theta, cfg.spatial_merge_size)
+    for b in enc.blocks:
+        y = rms(x, b.norm1)
+        qkv = (y @ b.qkv.t() + b.qkv_bias).view(-1, 3, cfg.num_heads, cfg.head_dim)
+        q, k, v = ops.apply_rope(qkv[:, 0], cos, sin), ops.apply_rope(qkv[:, 1], cos, sin), qkv[:, 2]
+        att = torch.softmax(torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(cfg.head_dim), -1)
+        o = torch.einsum("hqk,khd->qhd", att, v).reshape(x.shape[0], -1)
+        x = x + o @ b.proj.t() + b.proj_bias
+        y = rms(x, b.norm2)
+        gu = y @ b.fc1.t() + b.fc1_bias
+        x = x + (F.silu(gu[:, :b.f_pad]) * gu[:, b.f_pad:]) @ b.fc2.t() + b.fc2_bias
+    x = rms(x, enc.post_trunk_norm)
+    x = F.layer_norm(x, (cfg.hidden_size,), enc.merger_norm, enc.merger_norm_bias, 1e-6).view(-1, cfg.hidden_size * 4)
+    want = F.gelu(x @ enc.merger_fc1.t() + enc.merger_fc1_bias) @ enc.merger_fc2.t() + enc.merger_fc2_bias
+    assert torch.allclose(got, want, atol=2e-5), (got - want).abs().max()
