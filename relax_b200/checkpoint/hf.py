@@ -86,6 +86,8 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
         "mlp.linear_fc1.layer_norm_weight": "post_attention_layernorm.weight",
         "pre_mlp_layernorm.weight": "post_attention_layernorm.weight",
         "mlp.linear_fc2.weight": "mlp.down_proj.weight",
+        "post_self_attn_layernorm.weight": "post_self_attn_layernorm.weight",      # GLM-4 sandwich norms
+        "post_mlp_layernorm.weight": "post_mlp_layernorm.weight",
         "mlp.router.weight": "mlp.gate.weight",
         "mlp.router.expert_bias": "mlp.gate.e_score_correction_bias",
         "mlp.shared_experts.linear_fc2.weight": _shared(cfg) + ".down_proj.weight",
@@ -200,6 +202,9 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
             out[b + "self_attention.linear_qkv.bias"] = torch.cat([qb, kb, vb], 1).reshape(-1)
         out[b + "self_attention.linear_proj.weight"] = hf[pre + "self_attn.o_proj.weight"]
         out[b + "self_attention.linear_qkv.layer_norm_weight"] = hf[pre + "input_layernorm.weight"]
+        if cfg.sandwich_norm:
+            out[b + "post_self_attn_layernorm.weight"] = hf[pre + "post_self_attn_layernorm.weight"]
+            out[b + "post_mlp_layernorm.weight"] = hf[pre + "post_mlp_layernorm.weight"]
         if cfg.qk_layernorm:
             out[b + "self_attention.q_layernorm.weight"] = hf[pre + "self_attn.q_norm.weight"]
             out[b + "self_attention.k_layernorm.weight"] = hf[pre + "self_attn.k_norm.weight"]

@@ -70,6 +70,8 @@ class ModelConfig:
     # gate value per query feature) and rotary embedding on the first `rotary_percent` of every head only
     attention_output_gate: bool = False
     rotary_percent: float = 1.0
+    # GLM-4 dense: "sandwich" norms - the attention and MLP outputs are normalised once more before they join the residual
+    sandwich_norm: bool = False
     # norm weights are stored zero-centred (gamma - 1) in this family's checkpoints (``--apply-layernorm-1p``); the model
     # keeps gamma, the Hugging Face conversion adds / removes the offset
     layernorm_zero_centered: bool = False
@@ -149,6 +151,13 @@ _reg(ModelConfig(name="tiny-vl", num_layers=2, hidden_size=256, num_attention_he
                  ffn_hidden_size=688, vocab_size=1024, dtype="fp32", mrope_section=(8, 12, 12), image_token_id=7,
                  vision=VisionConfig(num_layers=1, hidden_size=64, num_heads=2, ffn_hidden_size=96, patch_size=4,
                                      out_hidden_size=256)))
+_reg(ModelConfig(name="tiny-glm4", num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
+                 ffn_hidden_size=256, vocab_size=512, qk_layernorm=False, qkv_bias=True, sandwich_norm=True, rotary_percent=0.5,
+                 dtype="fp32"))
+# GLM-4-9B-0414 / GLM-Z1 shape (trainer-side family like the other non-plain attention stacks)
+_reg(ModelConfig(name="glm4-9b", num_layers=40, hidden_size=4096, num_attention_heads=32, num_query_groups=2, head_dim=128,
+                 ffn_hidden_size=13696, vocab_size=151552, qk_layernorm=False, qkv_bias=True, sandwich_norm=True, rotary_percent=0.5,
+                 rope_theta=1e4, rms_norm_eps=1e-5))
 _reg(ModelConfig(name="tiny-qwen35", num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, head_dim=32,
                  ffn_hidden_size=256, vocab_size=512, linear_attention_freq=4, attention_output_gate=True, rotary_percent=0.25,
                  dtype="fp32"))

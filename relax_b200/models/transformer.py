@@ -178,6 +178,12 @@ class TransformerLayer(nn.Module):
         else:
             self.mlp = MLP(cfg, ps, dtype, device, gen, layer_idx)
             self.is_moe_layer = False
+        if cfg.sandwich_norm:
+            one = lambda: nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
+            self.post_self_attn_layernorm = nn.Module()
+            self.post_self_attn_layernorm.weight = one()
+            self.post_mlp_layernorm = nn.Module()
+            self.post_mlp_layernorm.weight = one()
 
     def mlp_norm_weight(self):
         return self.pre_mlp_layernorm.weight if self.is_moe_layer else self.mlp.linear_fc1.layer_norm_weight
@@ -186,8 +192,12 @@ class TransformerLayer(nn.Module):
         eps = self.cfg.rms_norm_eps
         x = ops.rmsnorm(h, self.self_attention.linear_qkv.layer_norm_weight, eps)
         a = self.self_attention(x, cos, sin, cu_seqlens, attn_fn, max_seqlen)
+        if self.cfg.sandwich_norm:      # GLM-4: h += norm(attention(norm(h))); h += norm(mlp(norm(h)))
+            a = ops.rmsnorm(a, self.post_self_attn_layernorm.weight, eps)
         x, h = ops.add_rmsnorm(a, h, self.mlp_norm_weight(), eps)
         m = self.mlp(x)
+        if self.cfg.sandwich_norm:
+            m = ops.rmsnorm(m, self.post_mlp_layernorm.weight, eps)
         return h + m
 
 

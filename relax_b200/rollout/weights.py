@@ -80,9 +80,9 @@ def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1):
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
                  memory_saver: bool = False, shared_path: Optional[str] = None):
-        if cfg.attention_output_gate or cfg.rotary_percent < 1.0:
-            raise NotImplementedError("the rollout engine serves plain softmax attention; gated attention / partial rotary "
-                                      "(Qwen3.5) models are trainer-side for now")
+        if cfg.attention_output_gate or cfg.rotary_percent < 1.0 or cfg.sandwich_norm:
+            raise NotImplementedError("the rollout engine serves plain pre-norm softmax attention; gated attention / partial "
+                                      "rotary (Qwen3.5) and sandwich-norm (GLM-4) models are trainer-side for now")
         if cfg.dsa_topk > 0 or cfg.linear_attention_freq > 0 or cfg.multi_latent_attention:
             raise NotImplementedError("the rollout engine serves softmax-attention stacks only; GDN / MLA / DSA layers are "
                                       "trainer-side (SFT, log-prob evaluation) for now")

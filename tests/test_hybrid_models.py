@@ -137,3 +137,45 @@ def test_qwen35_style_gated_attention_and_partial_rotary():
     assert parts[qname].shape == (nq * 2 * hd, H)
     per_head = parts[qname].view(nq, 2, hd, H)
     assert torch.equal(per_head[:, 0].reshape(ng, qpg, hd, H), w[:, :qpg]) and torch.equal(per_head[:, 1].reshape(ng, qpg, hd, H), w[:, qpg:2 * qpg])
+
+
+def test_glm4_style_sandwich_norms_and_half_rotary():
+    """GLM-4 dense layer: the attention and MLP outputs pass through a second RMSNorm before the residual add, rotary
+    on the first half of every head, q/k/v bias; trains, and its tensors round-trip through the HF names."""
+    import torch
+
+    from relax_b200 import ops
+    from relax_b200.checkpoint import hf as HF
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+
+    cfg = get_config("tiny-glm4")
+    assert cfg.rotary_dim == 16 and get_config("glm4-9b").sandwich_norm
+    m = GPTModel(cfg, seed=5)
+    g = torch.Generator().manual_seed(0)
+    for n, p in m.named_parameters():
+        if "layernorm" in n or "norm" in n:
+            p.data.add_(torch.randn(p.shape, generator=g) * 0.1)
+    layer = m.decoder.layers[0]
+    T = 9
+    h = torch.randn(T, cfg.hidden_size, generator=g)
+    pos = torch.arange(T)
+    cos, sin = ops.rope_cos_sin(pos, cfg.rotary_dim, cfg.rope_theta, None)
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    out = layer(h, cos, sin, cu)
+    eps = cfg.rms_norm_eps
+    a = layer.self_attention(ops.rmsnorm(h, layer.self_attention.linear_qkv.layer_norm_weight, eps), cos, sin, cu)
+    h1 = h + ops.rmsnorm(a, layer.post_self_attn_layernorm.weight, eps)
+    mo = layer.mlp(ops.rmsnorm(h1, layer.mlp.linear_fc1.layer_norm_weight, eps))
+    want = h1 + ops.rmsnorm(mo, layer.post_mlp_layernorm.weight, eps)
+    assert torch.allclose(out, want, atol=1e-5)
+    toks = torch.randint(0, cfg.vocab_size, (T,), generator=g)
+    hid = m(toks, pos, cu)
+    lp, _ = m.log_probs(hid[:-1], toks[1:], 1.0, False)
+    (-lp.mean()).backward()
+    assert layer.post_mlp_layernorm.weight.grad.abs().sum() > 0
+    state = {k: v.detach() for k, v in m.named_parameters()}
+    hf = HF.convert_state_to_hf(cfg, state)
+    assert "model.layers.1.post_self_attn_layernorm.weight" in hf
+    back = HF.hf_to_megatron_state(cfg, hf)
+    assert all(torch.equal(back[k], v) for k, v in state.items())
