@@ -28,11 +28,18 @@ class _PinnedRing:
     SLOTS = 8
 
     def __init__(self):
+        import threading
+
         self.bufs = [None] * self.SLOTS
         self.events = [None] * self.SLOTS
         self.i = 0
+        self.lock = threading.Lock()       # role threads of one process (actor, forward roles) stage concurrently
 
     def stage(self, t: torch.Tensor, device: torch.device) -> torch.Tensor:
+        with self.lock:
+            return self._stage(t, device)
+
+    def _stage(self, t: torch.Tensor, device: torch.device) -> torch.Tensor:
         nbytes = t.numel() * t.element_size()
         k = self.i
         self.i = (self.i + 1) % self.SLOTS
