@@ -136,9 +136,12 @@ def engine_generate_fn(engine, sampling) -> GenerateFn:
 
 def run_episodes(envs: Sequence[AgentEnv], generate: GenerateFn, tok: Tokenizer, max_turns: int = 8,
                  max_new_tokens: int = 256, max_context: int = 4096, max_concurrent: Optional[int] = None,
-                 forest: Optional[SessionForest] = None) -> List[Session]:
+                 forest: Optional[SessionForest] = None, admission=None) -> List[Session]:
     """Advance all episodes turn by turn; each engine call batches the sessions that still run (at most
-    ``max_concurrent`` at a time: admission control against KV-cache exhaustion)."""
+    ``max_concurrent`` at a time).  With ``admission`` (a :class:`relax_b200.rollout.admission.AdmissionController`) an
+    episode joins only once it holds a token lease for everything it may occupy in the KV cache - its prompt plus
+    ``max_turns`` replies, capped by ``max_context`` - and gives the lease back when it ends; episodes are admitted in
+    order, so a large one is not starved by small ones behind it."""
     forest = forest or SessionForest()
     sess: List[Session] = []
     for env in envs:
@@ -148,8 +151,29 @@ def run_episodes(envs: Sequence[AgentEnv], generate: GenerateFn, tok: Tokenizer,
         s.prompt_len = len(s.tokens)
         sess.append(s)
     live = list(range(len(envs)))
+    leases: dict = {}
+    pending = list(live) if admission is not None else []
+
+    def admit():
+        from .admission import reservation_tokens
+
+        while pending:
+            i = pending[0]
+            need = min(max_context, reservation_tokens(sess[i].prompt_len, max_turns * max_new_tokens))
+            # nothing admitted is running: wait for real (other users of the engines may free capacity; an aged waiter passes)
+            lease = admission.acquire(need, timeout_s=None if not leases else 0.0)
+            if lease is None:
+                return
+            leases[i] = lease
+            pending.pop(0)
+
     while live:
-        wave = live[:max_concurrent] if max_concurrent else live
+        if admission is not None:
+            admit()
+            admitted = [i for i in live if i in leases]
+        else:
+            admitted = live
+        wave = admitted[:max_concurrent] if max_concurrent else admitted
         prompts, budget = [], []
         for i in wave:
             s = sess[i]
@@ -185,6 +209,9 @@ def run_episodes(envs: Sequence[AgentEnv], generate: GenerateFn, tok: Tokenizer,
                         s.truncated = s.done = True
                     else:
                         s.append(ot, 0)
+        if admission is not None:
+            for i in [i for i in live if sess[i].done and i in leases]:
+                admission.release(leases.pop(i))
         live = [i for i in live if not sess[i].done]
     return sess
 
@@ -224,8 +251,15 @@ def env_generate(engine, samples, sampling_params):
         turns = int((s.metadata or {}).get("max_turns", turns))
         envs.append(make_env(spec.pop("name"), **spec))
     max_ctx = getattr(engine, "max_model_len", None) or 4096
+    admission = None
+    if getattr(engine, "bm", None) is not None:          # an in-process engine: lease against its KV capacity
+        admission = getattr(engine, "_admission", None)
+        if admission is None:
+            from .admission import AdmissionController
+
+            admission = engine._admission = AdmissionController.for_engine(engine)
     sessions = run_episodes(envs, engine_generate_fn(engine, sampling_params), tok, max_turns=turns,
-                            max_new_tokens=new_tokens, max_context=max_ctx)
+                            max_new_tokens=new_tokens, max_context=max_ctx, admission=admission)
     for s, sess in zip(samples, sessions):
         done = sess.to_sample(s.group_index, s.index)
         s.tokens, s.response_length, s.loss_mask = done.tokens, done.response_length, done.loss_mask

@@ -190,3 +190,68 @@ def test_env_generate_plugs_into_the_colocated_loop(tmp_path):
     assert len(s.loss_mask) == s.response_length == len(s.rollout_log_probs) and 0 < sum(s.loss_mask) < s.response_length
     m = c.runner.step()
     assert m["raw_reward_mean"] == 1.25
+
+
+def test_admission_controller_leases_fifo_ageing_and_pressure():
+    import threading
+    import time
+
+    from relax_b200.rollout.admission import AdmissionController, reservation_tokens
+
+    assert reservation_tokens(100, 50) == 150
+    ac = AdmissionController(capacity_tokens=100, max_wait_s=0.4)
+    a = ac.acquire(60)
+    assert a is not None and not a.bypass
+    assert ac.acquire(60, timeout_s=0.0) is None                 # does not fit next to the first lease
+    order = []
+
+    def waiter(tag, n):
+        l = ac.acquire(n)
+        order.append((tag, l.bypass))
+        time.sleep(0.02)
+        ac.release(l)
+
+    t1 = threading.Thread(target=waiter, args=("big", 70))
+    t1.start()
+    time.sleep(0.05)
+    t2 = threading.Thread(target=waiter, args=("small", 10))      # would fit now, but arrived second: stays behind "big"
+    t2.start()
+    time.sleep(0.05)
+    assert order == []
+    ac.release(a)
+    t1.join(); t2.join()
+    assert [t for t, _ in order] == ["big", "small"] and not any(b for _, b in order)
+    # ageing: capacity never frees, the waiter is admitted after max_wait_s and the lease says so
+    hold = ac.acquire(100)
+    t0 = time.monotonic()
+    late = ac.acquire(50)
+    assert late.bypass and 0.3 < time.monotonic() - t0 < 2.0
+    ac.release(hold); ac.release(late)
+    # pressure guard: the engines report a full cache, nothing more is admitted next to a running lease
+    usage = [0.99]
+    ac2 = AdmissionController(1000, pressure_guard=0.9, max_wait_s=5.0, usage_fn=lambda: usage[0])
+    first = ac2.acquire(10)
+    assert ac2.acquire(10, timeout_s=0.05) is None
+    usage[0] = 0.5
+    second = ac2.acquire(10, timeout_s=1.0)
+    assert second is not None
+    m = ac2.metrics()
+    assert m["granted"] == 2 and m["reserved"] == 20 and m["cancelled"] == 1
+    ac2.release(first); ac2.release(second)
+
+
+def test_episodes_run_under_admission_control():
+    """Episodes join as leases become available and all finish; the reserved peak respects the capacity."""
+    from relax_b200.rollout.admission import AdmissionController
+
+    calls = []
+
+    def gen(prompts, max_new, keys):
+        calls.append(len(prompts))
+        return _fake_generate(prompts, max_new, keys)
+
+    ac = AdmissionController(capacity_tokens=2 * 300, max_wait_s=5.0)
+    out = A.run_episodes([_CountEnv() for _ in range(6)], gen, TOK, max_turns=4, max_new_tokens=50, max_context=300, admission=ac)
+    assert len(out) == 6 and all(s.done and s.turns == 2 for s in out)
+    m = ac.metrics()
+    assert max(calls) <= 2 and m["peak_reserved"] <= 600 and m["reserved"] == 0 and m["granted"] == 6
