@@ -260,7 +260,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--expert-tensor-parallel-size": (_R, "experts are not tensor-parallel here (expert TP = 1)"),
     "--qkv-format": (_R, "only the packed thd layout is implemented"),
     "--padded-vocab-size": (_R, "the vocabulary is padded to a multiple of the tensor-parallel size only"),
-    "--num-iters-per-train-update": (_R, "one optimizer pass per rollout batch"),
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
@@ -443,6 +442,12 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             if per_rollout % a.global_batch_size:
                 raise ValueError(f"samples per rollout ({per_rollout}) must be a multiple of --global-batch-size ({a.global_batch_size})")
             a.num_steps_per_rollout = per_rollout // a.global_batch_size
+    if (a.num_iters_per_train_update or 1) > 1:
+        # relax/utils/arguments.py:246-250: "fully async pipeline num of iters every global batch"
+        if not (getattr(a, "fully_async", False) or getattr(a, "hybrid", False)):
+            raise ValueError("--num-iters-per-train-update > 1 streams parts of a rollout batch to the trainer: it needs --fully-async")
+        if a.rollout_batch_size is not None and a.rollout_batch_size % a.num_iters_per_train_update:
+            raise ValueError("--rollout-batch-size must divide by --num-iters-per-train-update (whole prompt groups per part)")
     if a.use_dynamic_batch_size and a.max_tokens_per_gpu is None:
         raise ValueError("--use-dynamic-batch-size needs --max-tokens-per-gpu")
     if a.log_probs_max_tokens_per_gpu is None:

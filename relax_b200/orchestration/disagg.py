@@ -73,6 +73,8 @@ class DisaggConfig:
     num_rollout: int = 4
     max_staleness: int = 1
     update_weights_interval: int = 1
+    num_iters_per_train_update: int = 1   # > 1: the engines publish finished prompt groups in that many parts per rollout
+                                          # and the trainer runs its forward-only passes on each part as it arrives
     image_grid_side: int = 0              # vision-language models: patches per side of the synthetic images (0: 4 x merge size)
     weight_push: str = "peer"            # "peer": NVLink stores into the engines' buffers; "broadcast": NCCL baseline
     seed: int = 0
@@ -292,19 +294,58 @@ class DisaggregatedRL:
             ids.append(self.engine.add_request(s_.tokens, sp, s_.group_index,
                                                **({k: im.get(k) for k in ("pixel_patches", "grid_thw")} if im else {})))
         res = {}
-        while self.engine.has_work:
-            for r in self.engine.step():
-                res[r.rid] = r
-            self._maybe_sync_weights()        # between decode windows
-        for s, i in zip(flat, ids):
-            r = res[i]
+        by_rid = dict(zip(ids, flat))
+        parts = max(1, cfg.num_iters_per_train_update)
+        chunk = max(1, len(mine) // parts) if parts > 1 else 0      # prompt groups per published part (0: publish at the end)
+        left = {id(g): len(g) for g in mine}
+        group_of = {id(s_): g for g in mine for s_ in g}
+        ready, published = [], 0
+
+        def fill(s, r):
             s.tokens = list(r.prompt) + list(r.output)
             s.response_length = len(r.output)
             s.rollout_log_probs = list(r.logprobs)
             s.weight_versions = sorted(set(r.weight_versions))
             s.status = SampleStatus.TRUNCATED if r.finish_reason == "length" else SampleStatus.COMPLETED
             s.reward = self.reward_fn(s)
+
+        while self.engine.has_work:
+            for r in self.engine.step():
+                res[r.rid] = r
+                if chunk:
+                    s_ = by_rid[r.rid]
+                    fill(s_, r)
+                    g = group_of[id(s_)]
+                    left[id(g)] -= 1
+                    if left[id(g)] == 0:
+                        ready.append(g)
+            while chunk and len(ready) >= chunk and published < parts - 1:       # the last part goes out with the seal
+                self._publish(rid, [s_ for g in ready[:chunk] for s_ in g], last=False)
+                ready, published = ready[chunk:], published + 1
+            self._maybe_sync_weights()        # between decode windows
+        if chunk:
+            return [s_ for g in ready for s_ in g]
+        for s, i in zip(flat, ids):
+            fill(s, res[i])
         return flat
+
+    def _publish(self, rid: int, samples: list, last: bool):
+        """Leader of an engine: advantages per prompt group, rows into the rollout's partition; the engine that
+        publishes the last part of all seals it."""
+        if not self.is_leader:
+            return
+        cfg = self.cfg
+        part = tq.partition_name(rid)
+        if samples:
+            batch = convert_samples_to_train_data(
+                samples, advantage_estimator=cfg.train.advantage_estimator,
+                n_samples_per_prompt=cfg.train.n_samples_per_prompt,
+                rewards_normalization=cfg.train.rewards_normalization,
+                grpo_std_normalization=cfg.train.grpo_std_normalization)
+            self.store.set(f"fields/{rid}", json.dumps(sorted(batch.keys())))
+            self.tq.put(batch, part, custom_meta=custom_meta_rows(batch))
+        if last and self.store.add(f"puts/{rid}", 1) == len(self.engines):
+            self.tq.seal(part)
 
     def _rollout_loop(self):
         cfg = self.cfg
@@ -320,17 +361,7 @@ class DisaggregatedRL:
                 time.sleep(cfg.poll_interval)
             self.stats["rollout_started"].append((rid, self.applied_version))
             samples = self._generate(rid)
-            if self.is_leader:
-                batch = convert_samples_to_train_data(
-                    samples, advantage_estimator=cfg.train.advantage_estimator,
-                    n_samples_per_prompt=cfg.train.n_samples_per_prompt,
-                    rewards_normalization=cfg.train.rewards_normalization,
-                    grpo_std_normalization=cfg.train.grpo_std_normalization)
-                part = tq.partition_name(rid)
-                self.tq.put(batch, part, custom_meta=custom_meta_rows(batch))
-                self.store.set(f"fields/{rid}", json.dumps(sorted(batch.keys())))
-                if self.store.add(f"puts/{rid}", 1) == len(self.engines):
-                    self.tq.seal(part)
+            self._publish(rid, samples, last=True)
         # keep answering weight pushes until the trainer has finished
         deadline = time.monotonic() + cfg.handshake_timeout_s
         while True:
@@ -368,15 +399,65 @@ class DisaggregatedRL:
             dist.broadcast_object_list(box, src=cfg.trainer_ranks[0], group=self.ps.world.group)
         return box[0]
 
+    def _fetch_part(self, rid: int, rows: int):
+        """Up to ``rows`` rows of rollout ``rid`` that the trainer has not taken yet - exactly ``rows`` while the engines
+        still publish, the remainder once the partition is sealed.  Every trainer rank receives them, with a flag that
+        says whether the partition is now used up."""
+        cfg = self.cfg
+        box = [None]
+        if self.is_fetcher:
+            part = tq.partition_name(rid)
+            deadline = time.monotonic() + cfg.handshake_timeout_s
+            meta = None
+            while meta is None:
+                if part in self.tq.get_partition_list():
+                    fields = json.loads(self.store.get(f"fields/{rid}"))
+                    meta = self.tq.get_meta(fields, rows, part, "actor", timeout=0.05, allow_partial=True)
+                if meta is None:
+                    if time.monotonic() > deadline:
+                        raise TimeoutError(f"no rows of rollout batch {rid} within {cfg.handshake_timeout_s:.0f} s")
+                    time.sleep(cfg.poll_interval)
+            data = self.tq.get_data(meta)
+            box[0] = ({k: (v.tolist() if torch.is_tensor(v) else v) for k, v in data.items()},
+                      bool(self.tq.check_consumption_status("actor", part)))
+        if len(cfg.trainer_ranks) > 1:
+            dist.broadcast_object_list(box, src=cfg.trainer_ranks[0], group=self.ps.world.group)
+        return box[0]
+
+    def _fetch_streamed(self, rid: int):
+        """The rollout batch in about ``num_iters_per_train_update`` parts; the forward-only passes (reference and
+        old-policy log-probs) run on each part while the engines still generate the rest.  Returns (all rows, this
+        replica's forwarded share, seconds spent waiting)."""
+        from ..train.actor import concat_batches
+
+        cfg = self.cfg
+        unit = cfg.train.n_samples_per_prompt * self.ps.dp.size          # whole prompt groups, equal shares per replica
+        rows = cfg.rollout_batch_size * cfg.train.n_samples_per_prompt // cfg.num_iters_per_train_update
+        rows = max(unit, rows - rows % unit)
+        whole, mine, idle, done = [], [], 0.0, False
+        while not done:
+            t0 = time.perf_counter()
+            data, done = self._fetch_part(rid, rows)
+            idle += time.perf_counter() - t0
+            whole.append(data)
+            mine.append(self.actor.forward_log_probs(self.actor.split_for_dp(dict(data))))
+            self.stats["parts_forwarded"] = self.stats.get("parts_forwarded", 0) + 1
+        return concat_batches(whole), concat_batches(mine), idle
+
     def _trainer_loop(self):
         cfg = self.cfg
         t_start = time.perf_counter()
         for rid in range(cfg.num_rollout):
             t0 = time.perf_counter()
-            data = self._fetch(rid)
-            self.stats["idle_s"] += time.perf_counter() - t0
-            t1 = time.perf_counter()
-            batch = self.actor.split_for_dp(data)
+            if cfg.num_iters_per_train_update > 1:
+                data, batch, idle = self._fetch_streamed(rid)
+                self.stats["idle_s"] += idle
+                t1 = t0 + idle            # the forward passes count as busy time
+            else:
+                data = self._fetch(rid)
+                self.stats["idle_s"] += time.perf_counter() - t0
+                t1 = time.perf_counter()
+                batch = self.actor.split_for_dp(data)
             m = self.actor.train(rid, batch)
             self.actor.after_train()
             if self.is_fetcher:

@@ -100,6 +100,20 @@ def _shift_mask(mask: torch.Tensor, response_lengths: Sequence[int], k: int) -> 
     return out
 
 
+def concat_batches(parts: Sequence[dict]) -> dict:
+    """Join row-wise batches (field -> one entry per row); scalar fields must agree and are kept once."""
+    out: dict = {}
+    for k in parts[0]:
+        v0 = parts[0][k]
+        if isinstance(v0, list):
+            out[k] = [x for p in parts for x in p[k]]
+        elif torch.is_tensor(v0) and v0.dim() > 0:
+            out[k] = torch.cat([p[k] for p in parts])
+        else:
+            out[k] = v0
+    return out
+
+
 class TrainActor:
     def __init__(self, model_cfg: ModelConfig, cfg: TrainConfig, ps: Optional[ParallelState] = None,
                  device="cpu", seed: int = 0, role: str = "actor", with_optimizer: bool = True,
@@ -581,6 +595,33 @@ class TrainActor:
         return {k: ([v[i] for i in idx] if isinstance(v, list) and len(v) == n else v) for k, v in batch.items()}
 
     # ------------------------------------------------------------------ training
+    def forward_log_probs(self, batch: dict) -> dict:
+        """The forward-only part of :meth:`train` - reference and old-policy log-probs - on a PART of a rollout batch,
+        so that it can run while the rest of the batch is still being generated
+        (relax/backends/megatron/actor.py:1103-1125 pulls ``global_batch_size / num_iters_per_train_update`` rows at a
+        time for these passes).  The rows come back marked; :meth:`train` then skips the passes.  Parts are joined
+        with :func:`concat_batches`.  Routing replay records the routing of the old-policy pass for the optimizer
+        passes that follow it directly, which a split pass cannot provide: refused."""
+        cfg = self.cfg
+        if self.mcfg.is_moe and (cfg.use_routing_replay or cfg.use_rollout_routing_replay):
+            raise ValueError("routing replay needs the old-policy pass directly before the optimizer passes: "
+                             "use --num-iters-per-train-update 1")
+        if "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
+            r_ = self.compute_log_prob(batch, "ref", with_entropy=cfg.use_rollout_entropy)
+            batch["ref_log_probs"] = r_["log_probs"]
+            if cfg.use_rollout_entropy:
+                batch["ref_entropy"] = r_["entropy"]
+        if cfg.use_rollout_logprobs and batch.get("rollout_log_probs") is not None:
+            batch["log_probs"] = [torch.as_tensor(x, dtype=torch.float32, device=self.device) for x in batch["rollout_log_probs"]]
+        elif not cfg.loss.true_on_policy:
+            tag = "old_actor" if (cfg.keep_old_actor and "old_actor" in self.snapshots) else "actor"
+            o_ = self.compute_log_prob(batch, tag, with_entropy=cfg.use_rollout_entropy)
+            batch["log_probs"] = o_["log_probs"]
+            if cfg.use_rollout_entropy:
+                batch["entropy"] = o_["entropy"]
+        batch["__forwarded__"] = True
+        return batch
+
     def train(self, rollout_id: int, batch: dict, update_policy: bool = True) -> dict:
         """One rollout's worth of optimizer steps on this replica's samples
         (``batch`` already split for data parallelism).  Returns reduced metrics.  With ``update_policy=False`` only
@@ -599,8 +640,9 @@ class TrainActor:
                 batch[key] = list(torch.split(flat, lens))
         masks = [torch.as_tensor(m, dtype=torch.float32, device=dev) for m in batch["loss_masks"]]
 
+        forwarded = bool(batch.get("__forwarded__"))      # forward_log_probs() already ran on these rows
         with self.timer.span("ref_log_probs"):
-            if "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
+            if not forwarded and "ref" in self.snapshots and (cfg.loss.use_kl_loss or cfg.kl_coef != 0):
                 r_ = self.compute_log_prob(batch, "ref", with_entropy=cfg.use_rollout_entropy)
                 batch["ref_log_probs"] = r_["log_probs"]
                 if cfg.use_rollout_entropy:
@@ -617,7 +659,9 @@ class TrainActor:
                     RoutingReplay.per_sample[(layer, sid)] = t[:, m]
             RoutingReplay.mode = "replay"
         with self.timer.span("old_log_probs"):
-            if cfg.use_rollout_logprobs and batch.get("rollout_log_probs") is not None:
+            if forwarded:
+                pass
+            elif cfg.use_rollout_logprobs and batch.get("rollout_log_probs") is not None:
                 batch["log_probs"] = [torch.as_tensor(x, dtype=torch.float32, device=dev) for x in batch["rollout_log_probs"]]
             elif not cfg.loss.true_on_policy:
                 tag = "old_actor" if (cfg.keep_old_actor and "old_actor" in self.snapshots) else "actor"
