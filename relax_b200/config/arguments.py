@@ -99,7 +99,18 @@ FLAGS: dict[str, list] = {
         ("--use-rollout-routing-replay", _b()), ("--use-routing-replay", _b()), ("--use-rollout-logprobs", _b()),
         ("--use-rollout-entropy", _b()), ("--disable-rollout-global-dataset", _b()), ("--disable-rollout-trim-samples", _b()),
         ("--use-streaming-dataset", _b()), ("--streaming-buffer-size", dict(type=int, default=10000)),
-        ("--use-agentic-rollout", _b()), ("--agentic-concurrency", dict(type=int, default=32)),
+        ("--use-agentic-rollout", _b()), ("--agentic-concurrency", dict(type=int, default=None)),
+        # agents as external commands (relax/utils/arguments.py:1421-1552)
+        ("--agent-command", dict(type=str, default=None)), ("--agent-cwd", dict(type=str, default=None)),
+        ("--agent-timeout", dict(type=float, default=1800.0)), ("--agent-env", dict(type=str, nargs="+", default=[])),
+        ("--agentic-program-admission", _b()), ("--agentic-admission-headroom", dict(type=float, default=0.90)),
+        ("--agentic-admission-expected-decode-cap", dict(type=int, default=None)),
+        ("--agentic-admission-pressure-threshold", dict(type=float, default=0.92)),
+        ("--agentic-admission-max-wait-s", dict(type=float, default=30.0)),
+        ("--agentic-admission-scope", dict(type=str, default="train", choices=["train", "all"])),
+        ("--agentic-eval-concurrency", dict(type=int, default=None)), ("--agentic-prelaunch", _b()),
+        ("--agentic-session-lifecycle", _b()), ("--agentic-tool-call-parser", dict(type=str, default=None)),
+        ("--agentic-reasoning-parser", dict(type=str, default=None)), ("--agentic-custom-advantage-path", dict(type=str, default=None)),
     ],
     "fault_tolerance": [
         ("--use-fault-tolerance", _b()), ("--use-health-check", _b()), ("--max-global-restart", dict(type=int, default=3)),
@@ -268,7 +279,9 @@ FLAG_POLICY: dict[str, tuple] = {
     "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
     "--disable-rollout-global-dataset": (_R, "prompts always come from the global dataset"),
     "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
-    "--use-agentic-rollout": (_R, "agentic rollouts are driven through --custom-generate-function-path (rollout/agentic.py)"),
+    "--agentic-tool-call-parser": (_R, "the chat endpoint returns the model's text; tool calls are parsed by the agent"),
+    "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
+    "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
     "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
@@ -283,7 +296,10 @@ FLAG_POLICY: dict[str, tuple] = {
     "--recompute-method": (_W, "--recompute-granularity full recomputes every layer"),
     "--recompute-num-layers": (_W, "--recompute-granularity full recomputes every layer"),
     "--log-probs-chunk-size": (_W, "the fused LM head never materialises the logits"),
-    "--agentic-concurrency": (_W, None), "--sglang-server-concurrency": (_W, None),
+    "--sglang-server-concurrency": (_W, None), "--agentic-prelaunch": (_W, "agents start when their sample is scheduled"),
+    "--agentic-session-lifecycle": (_W, "a session's cache entries are released by the engine's own eviction"),
+    "--agentic-eval-concurrency": (_W, None), "--agentic-admission-expected-decode-cap": (_W, None),
+    "--agentic-admission-scope": (_W, None),
     "--sglang-mem-fraction-static": (_W, "the KV cache is sized from the batch shape"),
     "--critic-num-nodes": (_W, "the critic shares the actor's ranks"),
     "--critic-num-gpus-per-node": (_W, "the critic shares the actor's ranks"),
@@ -442,6 +458,15 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             if per_rollout % a.global_batch_size:
                 raise ValueError(f"samples per rollout ({per_rollout}) must be a multiple of --global-batch-size ({a.global_batch_size})")
             a.num_steps_per_rollout = per_rollout // a.global_batch_size
+    if a.use_agentic_rollout:
+        # relax/utils/arguments.py:3015-3017 points the rollout function at the agentic entry; same here
+        if not a.agent_command or not a.agent_cwd:
+            raise ValueError("--use-agentic-rollout needs --agent-command and --agent-cwd")
+        if a.custom_generate_function_path:
+            raise ValueError("--use-agentic-rollout installs its own generate function; drop --custom-generate-function-path")
+        a.custom_generate_function_path = "relax_b200.rollout.agent_pipeline:command_generate"
+        if a.agentic_concurrency is None:
+            a.agentic_concurrency = getattr(a, "over_sampling_batch_size", None) or a.rollout_batch_size or 32
     if (a.num_iters_per_train_update or 1) > 1:
         # relax/utils/arguments.py:246-250: "fully async pipeline num of iters every global batch"
         if not (getattr(a, "fully_async", False) or getattr(a, "hybrid", False)):

@@ -679,6 +679,9 @@ class ColocatedGRPO:
         if cfg.use_health_check:
             m["rollout/recoveries"] = float(self.recoveries)
         m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
+        extra = getattr(self.custom_generate, "stats", None)        # a generate function may report its own gauges
+        if callable(extra):
+            m.update({k: float(v) for k, v in (extra() or {}).items()})
         self.rollout_id += 1
         return m
 

@@ -80,6 +80,12 @@ class Controller:
         self.memory_snapshot = MemorySnapshotter(_get(args, "memory_snapshot_dir", None), _get(args, "memory_snapshot_num_steps", None),
                                                  self.rank)
         self.start_rollout_id = dist_ckpt.resolve_start_rollout_id(args.load, args.start_rollout_id)
+        if _get(args, "use_agentic_rollout", False):
+            # the launcher daemon is forked here, while this process is still small
+            from ..data.tokenizer import build_codec
+            from ..rollout import agent_pipeline
+
+            agent_pipeline.configure(args, build_codec(_get(args, "hf_checkpoint", None), self.model_cfg.vocab_size))
         self.runner = self._build_runner()
         self._maybe_resume()
         self._setup_health()

@@ -27,8 +27,11 @@ from .engine import SamplingParams
 
 
 class EngineServer:
-    def __init__(self, engine, host: str = "127.0.0.1", port: int = 0, idle_sleep_s: float = 0.002):
+    def __init__(self, engine, host: str = "127.0.0.1", port: int = 0, idle_sleep_s: float = 0.002, http: bool = True):
+        """``http=False``: only the engine loop and the thread-safe :meth:`generate` / :meth:`command` calls (an
+        in-process batching backend, e.g. under the chat endpoint that agent processes talk to)."""
         self.engine, self.idle_sleep_s = engine, idle_sleep_s
+        self.httpd, self.url = None, None
         self._lock = threading.Lock()           # guards the hand-over lists; the engine itself is touched by ONE thread
         self._incoming: list = []               # (prompt, SamplingParams, group_key, ticket)
         self._commands: list = []               # (name, ticket)
@@ -38,6 +41,8 @@ class EngineServer:
         self._loop = threading.Thread(target=self._run, daemon=True, name="engine-loop")
         self._loop.start()
         server = self
+        if not http:
+            return
 
         class H(BaseHTTPRequestHandler):
             def log_message(self, *a):
@@ -122,6 +127,11 @@ class EngineServer:
 
     def _run(self):
         eng = self.engine
+        dev = getattr(eng, "device", None)
+        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+            import torch
+
+            torch.cuda.set_device(dev)        # the current device is per thread
         while not self._stop.is_set():
             with self._lock:
                 incoming, self._incoming = self._incoming, []
@@ -160,9 +170,27 @@ class EngineServer:
 
     def close(self):
         self._stop.set()
-        self.httpd.shutdown()
-        self.httpd.server_close()
+        if self.httpd is not None:
+            self.httpd.shutdown()
+            self.httpd.server_close()
         self._loop.join(timeout=5)
+
+    def generate_fn(self, sampling):
+        """The engine loop as a ``generate(prompts, max_new_tokens, group_keys)`` callable (the signature the agentic
+        code uses); calls from several threads join one running batch."""
+        sp = {"temperature": sampling.temperature, "top_p": sampling.top_p, "top_k": sampling.top_k,
+              "stop_token_ids": list(sampling.stop_token_ids), "ignore_eos": sampling.ignore_eos}
+
+        def gen(prompts, max_new, keys):
+            outs = []
+            # one request list per routing key keeps the prefix-sharing groups of the engine intact
+            body = {"input_ids": [list(p) for p in prompts], "sampling_params": dict(sp, max_new_tokens=int(max_new)),
+                    "routing_key": keys[0] if keys and len(set(keys)) == 1 else None}
+            for d in self.generate(body):
+                outs.append((d["output_ids"], d["logprobs"], d["finish_reason"], d["weight_versions"]))
+            return outs
+
+        return gen
 
 
 class _Result:
