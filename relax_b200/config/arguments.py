@@ -274,8 +274,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--rollout-external": (_R, "external rollout engines are not supported"),
-    "--rollout-external-engine-addrs": (_R, "external rollout engines are not supported"),
     "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
     "--disable-rollout-global-dataset": (_R, "prompts always come from the global dataset"),
     "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
@@ -458,6 +456,13 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             if per_rollout % a.global_batch_size:
                 raise ValueError(f"samples per rollout ({per_rollout}) must be a multiple of --global-batch-size ({a.global_batch_size})")
             a.num_steps_per_rollout = per_rollout // a.global_batch_size
+    if a.rollout_external:
+        if not a.rollout_external_engine_addrs:
+            raise ValueError("--rollout-external needs --rollout-external-engine-addrs host:port [host:port ...]")
+        if getattr(a, "fully_async", False) and not getattr(a, "hybrid", False):
+            raise ValueError("--rollout-external drives pre-launched engines from the colocated loop (--colocate)")
+    elif a.rollout_external_engine_addrs:
+        raise ValueError("--rollout-external-engine-addrs has no effect without --rollout-external")
     if a.use_agentic_rollout:
         # relax/utils/arguments.py:3015-3017 points the rollout function at the agentic entry; same here
         if not a.agent_command or not a.agent_cwd:

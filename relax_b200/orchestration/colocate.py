@@ -19,7 +19,7 @@ from __future__ import annotations
 import os
 import time
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -83,6 +83,9 @@ class ColocateConfig:
     # user code by path ("pkg.mod:fn" or "/file.py:fn"): generate(engine, samples, sampling_params) -> samples fills
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
+    # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
+    # of the list (--rollout-external / --rollout-external-engine-addrs)
+    rollout_external_addrs: Optional[Sequence[str]] = None
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     # partial rollout (relax/engine/rollout/sglang_rollout.py generate_rollout_async / abort): over-sampled groups
@@ -202,14 +205,29 @@ class ColocatedGRPO:
             self.actor.optimizer.release_grads()   # before the engine allocates its weights and KV cache
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
-        self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
-                                    num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
-                                    max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
-                                    max_prefill_tokens=cfg.max_prefill_tokens, use_cuda_graph=cfg.use_cuda_graph,
-                                    memory_saver=cfg.engine_memory_saver,
-                                    max_model_len=cfg.prompt_len + cfg.max_response_len,
-                                    eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
-                                    return_routed_experts=cfg.train.use_rollout_routing_replay)
+        self.external = bool(cfg.rollout_external_addrs)
+        if self.external:
+            from ..rollout.external import ExternalEngine
+
+            addrs = list(cfg.rollout_external_addrs)
+            if cfg.rollout_tp != 1 or cfg.rollout_ep != 1:
+                raise ValueError("external engines are addressed one per engine replica: --rollout-num-gpus-per-engine 1")
+            if len(addrs) % self.num_engines:
+                raise ValueError(f"{len(addrs)} external engine addresses do not divide over {self.num_engines} engine replicas")
+            if cfg.partial_rollout or cfg.train.use_rollout_routing_replay or cfg.lora_adapter_mode:
+                raise ValueError("partial rollout, rollout routing replay and adapter-mode LoRA sync need an in-process engine")
+            k = len(addrs) // self.num_engines
+            self.engine = ExternalEngine(cfg.model, addrs[self.engine_id * k:(self.engine_id + 1) * k], device, self.actor.model.dtype,
+                                         max_model_len=cfg.prompt_len + cfg.max_response_len)
+        else:
+            self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
+                                        num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
+                                        max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
+                                        max_prefill_tokens=cfg.max_prefill_tokens, use_cuda_graph=cfg.use_cuda_graph,
+                                        memory_saver=cfg.engine_memory_saver,
+                                        max_model_len=cfg.prompt_len + cfg.max_response_len,
+                                        eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
+                                        return_routed_experts=cfg.train.use_rollout_routing_replay)
         if cfg.model.vision is not None:
             # colocated: the engine embeds images with the trainer's tower itself (same parameters, nothing to sync)
             self.engine.attach_vision(self.actor.model.vision)
@@ -537,7 +555,7 @@ class ColocatedGRPO:
         sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                             max_new_tokens=cfg.max_response_len, stop_token_ids=tuple(cfg.stop_token_ids or ()))
         over_n = (cfg.over_sampling_batch_size or cfg.rollout_batch_size) // self.num_engines
-        if self.custom_generate is None and (cfg.partial_rollout or (self.group_filter is None and over_n > per)):
+        if self.custom_generate is None and not self.external and (cfg.partial_rollout or (self.group_filter is None and over_n > per)):
             groups = self._generate_streaming(per, max(per, over_n), sp)
         elif self.group_filter is None:
             groups = self._generate_groups(per, sp)

@@ -71,7 +71,24 @@ class EngineServer:
                 n = int(self.headers.get("Content-Length", "0") or 0)
                 path = self.path.split("?")[0].rstrip("/")
                 try:
+                    if path == "/update_weights":
+                        # body: torch.save of {name: tensor} in the engine's own layout; ?version=N
+                        import io
+                        from urllib.parse import parse_qs, urlparse
+
+                        import torch
+
+                        q = parse_qs(urlparse(self.path).query)
+                        state = torch.load(io.BytesIO(self.rfile.read(n)), map_location="cpu", weights_only=True)
+                        return self._reply(200, server.command("update_weights", payload=(state, int(q.get("version", ["0"])[0])),
+                                                               timeout_s=600.0))
                     body = json.loads(self.rfile.read(n) or b"{}")
+                    if path == "/update_weights_from_disk":
+                        import torch
+
+                        state = torch.load(body["path"], map_location="cpu", weights_only=True)
+                        return self._reply(200, server.command("update_weights", payload=(state, int(body.get("weight_version", 0))),
+                                                               timeout_s=600.0))
                     if path == "/generate":
                         return self._reply(200, server.generate(body))
                     if path in ("/flush_cache", "/pause_generation", "/continue_generation", "/abort_request"):
@@ -107,8 +124,8 @@ class EngineServer:
             out.append(t["result"])
         return out if many else out[0]
 
-    def command(self, name: str, timeout_s: float = 60.0):
-        t = {"event": threading.Event(), "result": None}
+    def command(self, name: str, timeout_s: float = 60.0, payload=None):
+        t = {"event": threading.Event(), "result": None, "payload": payload}
         with self._lock:
             self._commands.append((name, t))
         if not t["event"].wait(timeout_s):
@@ -148,6 +165,29 @@ class EngineServer:
                 elif name == "continue_generation":
                     eng.continue_generation()
                     t["result"] = {"status": "ok"}
+                elif name == "update_weights":
+                    # between scheduler iterations: running requests continue with the new weights and record both
+                    # versions, exactly as with an in-process sync
+                    state, version = t["payload"]
+                    try:
+                        missing = [k for k in eng.weights.p if k not in state]
+                        extra = [k for k in state if k not in eng.weights.p]
+                        if missing or extra:
+                            raise KeyError(f"weight names differ: missing {missing[:3]}, unexpected {extra[:3]}")
+                        import torch
+
+                        with torch.no_grad():
+                            for k, v in state.items():
+                                dst = eng.weights.p[k]
+                                if tuple(dst.shape) != tuple(v.shape):
+                                    raise ValueError(f"{k}: shape {tuple(v.shape)} does not fit {tuple(dst.shape)}")
+                                dst.copy_(v.to(dst.dtype))
+                        if not eng.running:
+                            eng.flush_cache()
+                        eng.update_weight_version(version)
+                        t["result"] = {"status": "ok", "weight_version": version, "tensors": len(state)}
+                    except Exception as e:  # noqa: BLE001 - reported to the caller, the server keeps its old weights
+                        t["result"] = {"status": "error", "error": f"{type(e).__name__}: {e}"}
                 elif name == "abort_request":
                     done = eng.abort_all()
                     for r in done:
@@ -226,6 +266,29 @@ class HTTPEngine:
 
     def flush_cache(self):
         return self._post("/flush_cache", {})
+
+    def info(self) -> dict:
+        import urllib.request
+
+        with urllib.request.urlopen(self.url + "/get_server_info", timeout=30.0) as r:
+            return json.loads(r.read().decode())
+
+    def update_weights(self, state: dict, version: int) -> dict:
+        """Ship ``{name: tensor}`` (the engine's layout) in the request body."""
+        import io
+        import urllib.request
+
+        import torch
+
+        buf = io.BytesIO()
+        torch.save({k: v.detach().to("cpu") for k, v in state.items()}, buf)
+        req = urllib.request.Request(f"{self.url}/update_weights?version={int(version)}", data=buf.getvalue(),
+                                     headers={"Content-Type": "application/octet-stream"})
+        with urllib.request.urlopen(req, timeout=self.timeout_s) as r:
+            out = json.loads(r.read().decode())
+        if out.get("status") != "ok":
+            raise RuntimeError(f"{self.url} refused the weights: {out.get('error', out)}")
+        return out
 
     def health(self) -> bool:
         import urllib.request

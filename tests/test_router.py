@@ -203,3 +203,54 @@ def test_engine_http_server_behind_the_router_matches_in_process_generation():
     for s in servers:
         s.close()
     srv.shutdown(); srv.server_close(); router.stop()
+
+
+def test_external_engines_driven_by_the_colocated_loop():
+    """``--rollout-external``: two pre-launched engine servers; the training job checks what they serve, generates
+    through them and ships its weights after every step.  The servers end up with the trainer's weights, bit for
+    bit, and are still running when the job is gone."""
+    import torch
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.engine import RolloutEngine
+    from relax_b200.rollout.http_server import EngineServer, HTTPEngine
+    from relax_b200.weight_sync.sync import oracle_rollout_state
+
+    cfg = get_config("tiny")
+    servers = [EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, seed=7 + i))
+               for i in range(2)]
+    try:
+        addrs = [s.url.replace("http://", "") for s in servers]
+        with pytest.raises(ValueError, match="engine-addrs"):
+            parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--rollout-external"])
+        a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                        "--global-batch-size", "8", "--num-rollout", "2", "--rollout-max-response-len", "6", "--rollout-max-prompt-len", "16",
+                        "--lr", "1e-2", "--rm-type", "token_sum_parity", "--rollout-external", "--rollout-external-engine-addrs", *addrs])
+        c = Controller(a, device="cpu")
+        assert all(s.engine.weight_version == c.runner.actor.weight_version for s in servers)      # initial sync reached them
+        before = {k: v.clone() for k, v in servers[0].engine.weights.p.items()}
+        for _ in range(2):
+            m = c.runner.step()
+        assert m["response_tokens_local"] > 0 and all(s.served > 0 for s in servers)              # both servers generated
+        want = oracle_rollout_state(cfg, dict(c.runner.actor.named_local_params()), 1, 0)
+        for s in servers:
+            assert s.engine.weight_version == c.runner.actor.weight_version == 2
+            for k, w in want.items():
+                assert torch.equal(s.engine.weights.p[k], w.to(s.engine.weights.p[k].dtype)), k
+        assert any(not torch.equal(before[k], servers[0].engine.weights.p[k]) for k in before)
+        c.runner.close()
+        assert HTTPEngine(servers[0].url).health()                                                  # not ours to stop
+        # a server that serves another model is refused at start-up
+        other = EngineServer(RolloutEngine(get_config("tiny-moe"), device="cpu", dtype=torch.float32, num_kv_blocks=32, block_size=8))
+        try:
+            a2 = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--rollout-external",
+                             "--rollout-external-engine-addrs", other.url.replace("http://", "")])
+            with pytest.raises(ValueError, match="serves model"):
+                Controller(a2, device="cpu")
+        finally:
+            other.close()
+    finally:
+        for s in servers:
+            s.close()
