@@ -165,6 +165,14 @@ FLAGS: dict[str, list] = {
         ("--opd-type", dict(type=str, default=None, choices=[None, "sglang", "megatron", "opsd"])),
         ("--opd-kl-coef", dict(type=float, default=1.0)), ("--opd-teacher-load", dict(type=str, default=None)),
         ("--opd-teacher-urls", dict(type=str, nargs="*", default=None)), ("--opd-topk", dict(type=int, default=0)),
+        # relax/utils/opd/opd_utils.py add_opd_arguments :466-680
+        ("--use-opd", _b()), ("--opd-teacher-url", dict(type=str, default=None)),
+        ("--opd-token-selection", dict(type=str, default="student_sampled", choices=["student_sampled", "student_topk", "teacher_topk", "union"])),
+        ("--opd-log-prob-top-k", dict(type=int, default=0)),
+        ("--opd-kl-type", dict(type=str, default="reverse_kl", choices=["reverse_kl", "forward_kl", "jsd", "low_var_kl"])),
+        ("--opd-jsd-alpha", dict(type=float, default=0.5)), ("--opd-norm-mode", dict(type=str, default="tail", choices=["tail", "norm", "trunc"])),
+        ("--opd-log-prob-min-clamp", dict(type=float, default=None)), ("--opd-per-token-clip", dict(type=float, default=None)),
+        ("--opd-loss-coef", dict(type=float, default=0.0)), ("--opd-only-reward", _b()),
     ],
     "lora": [
         ("--lora-rank", dict(type=int, default=0)), ("--lora-alpha", dict(type=float, default=16.0)),
@@ -281,7 +289,8 @@ FLAG_POLICY: dict[str, tuple] = {
     "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
     "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
-    "--opd-topk": (_R, "top-k distillation is not wired into the loop"),
+    "--opd-loss-coef": (_R, "the distillation signal enters through the advantages (--opd-kl-coef); the separate loss term is not wired"),
+    "--opd-only-reward": (_R, "the task reward is always kept next to the distillation signal"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
     "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
     # operational, no effect here
@@ -456,6 +465,25 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             if per_rollout % a.global_batch_size:
                 raise ValueError(f"samples per rollout ({per_rollout}) must be a multiple of --global-batch-size ({a.global_batch_size})")
             a.num_steps_per_rollout = per_rollout // a.global_batch_size
+    # --- on-policy distillation
+    if a.use_opd and not a.opd_type:
+        a.opd_type = "sglang" if (a.opd_teacher_urls or a.opd_teacher_url) else "megatron"
+    if a.opd_teacher_url and not a.opd_teacher_urls:
+        a.opd_teacher_urls = [a.opd_teacher_url]
+    if a.opd_topk and not a.opd_log_prob_top_k:          # short form: the teacher's top-K ids
+        a.opd_log_prob_top_k = a.opd_topk
+        if a.opd_token_selection == "student_sampled":
+            a.opd_token_selection = "teacher_topk"
+    if a.opd_token_selection != "student_sampled":
+        if a.opd_log_prob_top_k <= 0:
+            raise ValueError(f"--opd-token-selection {a.opd_token_selection} needs --opd-log-prob-top-k > 0")
+        if a.opd_teacher_urls:
+            raise ValueError("top-K token selections need an in-process teacher (--opd-teacher-load): remote teachers return "
+                             "the sampled token's log-prob only")
+        if a.opd_kl_type == "low_var_kl" and a.opd_token_selection == "union":
+            pass
+    elif a.opd_kl_type in ("forward_kl", "jsd"):
+        raise ValueError(f"--opd-kl-type {a.opd_kl_type} needs both distributions: choose a top-K --opd-token-selection")
     if a.rollout_external:
         if not a.rollout_external_engine_addrs:
             raise ValueError("--rollout-external needs --rollout-external-engine-addrs host:port [host:port ...]")
@@ -584,7 +612,11 @@ def train_config_from_args(a):
         use_rollout_logprobs=a.use_rollout_logprobs, keep_old_actor=a.keep_old_actor,
         enable_mtp_training=a.enable_mtp_training, mtp_loss_scaling_factor=a.mtp_loss_scaling_factor,
         mtp_only_training=a.mtp_only_training,
-        opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0, use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
+        opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0,
+        opd_kl_type=a.opd_kl_type, opd_jsd_alpha=a.opd_jsd_alpha, opd_norm_mode=a.opd_norm_mode,
+        opd_log_prob_min_clamp=a.opd_log_prob_min_clamp, opd_per_token_clip=a.opd_per_token_clip,
+        opd_token_selection={"student_sampled": "sampled_token"}.get(a.opd_token_selection, a.opd_token_selection),
+        opd_log_prob_top_k=int(a.opd_log_prob_top_k or 0), use_routing_replay=bool(getattr(a, "use_routing_replay", False)),
         use_rollout_routing_replay=bool(getattr(a, "use_rollout_routing_replay", False) or getattr(a, "engine_return_routed_experts", False)),
         freeze_params_name_list=_freeze_list(a), problem_type=getattr(a, "problem_type", None),
         use_rollout_entropy=bool(getattr(a, "use_rollout_entropy", False)),

@@ -80,6 +80,11 @@ class TrainConfig:
     # log-probs come with the batch (``teacher_log_probs``, external teacher) or from the ``teacher`` weight snapshot.
     opd_kl_coef: float = 0.0
     opd_kl_type: str = "reverse_kl"
+    opd_token_selection: str = "sampled_token"     # or student_topk / teacher_topk / union (with opd_log_prob_top_k)
+    opd_log_prob_top_k: int = 0
+    opd_jsd_alpha: float = 0.5
+    opd_norm_mode: str = "tail"
+    opd_log_prob_min_clamp: Optional[float] = None
     opd_per_token_clip: Optional[float] = None
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
@@ -472,6 +477,60 @@ class TrainActor:
             res["entropy"] = out_en
         return res
 
+    @torch.no_grad()
+    def compute_topk_log_probs(self, batch: dict, tag: str = "actor", k: int = 0, ids: Optional[Sequence] = None,
+                               row_chunk: int = 2048) -> dict:
+        """Forward-only pass that reads the distribution on a SET of token ids per response position instead of the
+        sampled token only (top-K distillation; relax/utils/opd/opd_utils.py compute_log_probs_on_topk_token_ids
+        :1023).  Without ``ids``: this model's own top-``k`` ids per position and their log-probs, ``[R_i, k]`` each.
+        With ``ids`` (per sample ``[R_i, K]``, global vocabulary ids, negative = padding): the log-probs of exactly
+        those ids (padding gives ``-inf``).  The logits of ``row_chunk`` positions at a time exist in fp32; nothing of
+        vocabulary size is kept.  One model-parallel rank per replica (tp = pp = cp = 1)."""
+        if self.ps.tp.size > 1 or self.ps.pp.size > 1 or self.ps.cp.size > 1:
+            raise NotImplementedError("top-K distillation reads full-vocabulary rows: trainer tp = pp = cp = 1")
+        if ids is None and k <= 0:
+            raise ValueError("either k > 0 or ids")
+        self.switch_model(tag)
+        toks = batch["tokens"]
+        out_ids, out_lp = [None] * len(toks), [None] * len(toks)
+        w = self.model.lm_head_weight()[: self.mcfg.vocab_size].float()
+        inv_t = 1.0 / float(self.cfg.rollout_temperature or 1.0)
+        for mb in self._microbatches([len(t) for t in toks]):
+            if not mb:
+                self._dummy_forward()
+                continue
+            pb = self._pack_batch(batch, mb)
+            emb = self._embed_multimodal(pb) if getattr(pb, "pixel_patches", None) is not None else None
+            h = self.model(pb.tokens, pb.positions, pb.cu_seqlens, max_seqlen=pb.max_seqlen, inputs_embeds=emb)
+            hr = h.index_select(0, pb.logit_rows).float()
+            want = None
+            if ids is not None:
+                rows = [torch.as_tensor(ids[i], dtype=torch.long, device=self.device) for i in mb]
+                kmax = max(t.shape[-1] for t in rows)          # union sets differ in width: pad with -1
+                want = torch.cat([torch.nn.functional.pad(t, (0, kmax - t.shape[-1]), value=-1) for t in rows])
+                if want.shape[0] != hr.shape[0]:
+                    raise ValueError("ids must hold one row per response position")
+            got_ids, got_lp = [], []
+            for a in range(0, hr.shape[0], row_chunk):
+                logits = (hr[a:a + row_chunk] @ w.t()) * inv_t
+                lse = torch.logsumexp(logits, -1, keepdim=True)
+                if want is None:
+                    val, idx = logits.topk(k, -1)
+                    got_ids.append(idx)
+                    got_lp.append(val - lse)
+                else:
+                    q = want[a:a + row_chunk]
+                    lp = logits.gather(-1, q.clamp_min(0)) - lse
+                    got_lp.append(lp.masked_fill(q < 0, float("-inf")))
+            lp_all = torch.cat(got_lp) if got_lp else hr.new_zeros(0, k)
+            for j, (i, piece) in enumerate(zip(mb, torch.split(lp_all, pb.response_lengths))):
+                out_lp[i] = piece if ids is None else piece[:, : torch.as_tensor(ids[i]).shape[-1]]
+            if want is None:
+                for i, piece in zip(mb, torch.split(torch.cat(got_ids), pb.response_lengths)):
+                    out_ids[i] = piece
+        self.switch_model("actor")
+        return {"ids": out_ids if ids is None else list(ids), "log_probs": out_lp}
+
     # ------------------------------------------------------------------ pipeline parallelism
     def _stage_forward(self, pb, x):
         """This pipeline stage's layers on one packed micro-batch: the first stage embeds the tokens, later stages
@@ -700,13 +759,44 @@ class TrainActor:
         if cfg.opd_kl_coef != 0.0 and (batch.get("teacher_log_probs") is not None or "teacher" in self.snapshots):
             from ..algo import opd as OPD
 
-            with self.timer.span("teacher_log_probs"):
-                if batch.get("teacher_log_probs") is None:
-                    batch["teacher_log_probs"] = self.compute_log_prob(batch, "teacher")["log_probs"]
-            student = batch.get("log_probs") or self.compute_log_prob(batch, "actor")["log_probs"]
-            sig = [OPD.per_token_signal("sampled_token", student_lp=torch.as_tensor(a, dtype=torch.float32, device=dev),
-                                        teacher_lp=torch.as_tensor(b, dtype=torch.float32, device=dev), kl_type=cfg.opd_kl_type)
-                   for a, b in zip(student, batch["teacher_log_probs"])]
+            sel = cfg.opd_token_selection
+            kw = dict(kl_type=cfg.opd_kl_type, alpha=cfg.opd_jsd_alpha, norm_mode=cfg.opd_norm_mode,
+                      log_prob_min_clamp=cfg.opd_log_prob_min_clamp)
+            if sel == "sampled_token":
+                with self.timer.span("teacher_log_probs"):
+                    if batch.get("teacher_log_probs") is None:
+                        batch["teacher_log_probs"] = self.compute_log_prob(batch, "teacher")["log_probs"]
+                student = batch.get("log_probs") or self.compute_log_prob(batch, "actor")["log_probs"]
+                sig = [OPD.per_token_signal("sampled_token", student_lp=torch.as_tensor(a, dtype=torch.float32, device=dev),
+                                            teacher_lp=torch.as_tensor(b, dtype=torch.float32, device=dev), **kw)
+                       for a, b in zip(student, batch["teacher_log_probs"])]
+            else:
+                # both distributions on a set of K ids per position (relax/utils/opd/opd_utils.py:1275-1420): the set is
+                # the student's top-K, the teacher's, or their union (rows of different width, padded and masked)
+                if "teacher" not in self.snapshots:
+                    raise ValueError(f"--opd-token-selection {sel} needs the teacher's distribution: an in-process teacher "
+                                     "(--opd-teacher-load); remote teachers return the sampled token's log-prob only")
+                k = cfg.opd_log_prob_top_k
+                if k <= 0:
+                    raise ValueError(f"--opd-token-selection {sel} needs --opd-log-prob-top-k > 0")
+                with self.timer.span("teacher_log_probs"):
+                    own_s = self.compute_topk_log_probs(batch, "actor", k=k) if sel in ("student_topk", "union") else None
+                    own_t = self.compute_topk_log_probs(batch, "teacher", k=k) if sel in ("teacher_topk", "union") else None
+                    lengths = None
+                    if sel == "student_topk":
+                        ids = own_s["ids"]
+                    elif sel == "teacher_topk":
+                        ids = own_t["ids"]
+                    else:
+                        pairs = [OPD.union_ids(a, b) for a, b in zip(own_s["ids"], own_t["ids"])]
+                        lengths = [n for _, n in pairs]
+                        col = lambda u, n: torch.arange(u.shape[-1], device=u.device)[None, :] < n[:, None]
+                        ids = [u.masked_fill(~col(u, n), -1) for u, n in pairs]
+                    s_lp = own_s["log_probs"] if sel == "student_topk" else self.compute_topk_log_probs(batch, "actor", ids=ids)["log_probs"]
+                    t_lp = own_t["log_probs"] if sel == "teacher_topk" else self.compute_topk_log_probs(batch, "teacher", ids=ids)["log_probs"]
+                sig = [OPD.per_token_signal(sel, student_topk_lp=a, teacher_topk_lp=b, k_lengths=(lengths[i] if lengths else None), **kw)
+                       for i, (a, b) in enumerate(zip(s_lp, t_lp))]
+                batch["opd_topk_token_ids"] = ids
             batch["advantages"] = OPD.apply_to_advantages(list(batch["advantages"]), sig, cfg.opd_kl_coef, cfg.opd_per_token_clip)
             tot = sum(float((d * m).sum()) for d, m in zip(sig, masks))
             opd_metric = tot / max(1.0, float(mask_all.sum()))

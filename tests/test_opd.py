@@ -166,3 +166,58 @@ def test_remote_teacher_over_http_and_pool_failover():
     run.close()
     srv.shutdown()
     srv.server_close()
+
+
+def test_topk_log_probs_match_a_plain_softmax_and_drive_the_topk_selections(tmp_path):
+    """``compute_topk_log_probs`` against log_softmax of the full logits (fp32), and a training step per top-K token
+    selection: teacher = student gives a zero signal, a different teacher a positive one (a KL on the chosen ids)."""
+    import torch.nn.functional as F
+
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.train.actor import TrainActor, TrainConfig
+
+    cfg = get_config("tiny")
+    actor = TrainActor(cfg, TrainConfig(), seed=3, with_optimizer=False)
+    g = torch.Generator().manual_seed(0)
+    toks = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (13, 9, 17)]
+    batch = {"tokens": toks, "response_lengths": [5, 4, 9], "total_lengths": [13, 9, 17]}
+    own = actor.compute_topk_log_probs(batch, k=6)
+    # reference: full logits of the response positions with plain PyTorch
+    w = actor.model.lm_head_weight()[:cfg.vocab_size].float()
+    sampled = actor.compute_log_prob(batch)["log_probs"]
+    for i, (t, r) in enumerate(zip(toks, batch["response_lengths"])):
+        x = torch.tensor(t)
+        with torch.no_grad():
+            h = actor.model(x, torch.arange(len(t)), torch.tensor([0, len(t)], dtype=torch.int32), max_seqlen=len(t))
+        full = F.log_softmax(h[len(t) - r - 1:len(t) - 1].float() @ w.t(), -1)
+        val, idx = full.topk(6, -1)
+        assert torch.equal(own["ids"][i], idx) and torch.allclose(own["log_probs"][i], val, atol=1e-5)
+        # gather mode, with padding, and consistency with the sampled-token pass
+        ids = torch.cat([x[len(t) - r:, None], torch.full((r, 1), -1)], -1)
+        got = actor.compute_topk_log_probs(batch, ids=[ids if j == i else torch.zeros(batch["response_lengths"][j], 2, dtype=torch.long)
+                                                       for j in range(3)])["log_probs"][i]
+        assert torch.allclose(got[:, 0], sampled[i].float(), atol=1e-5) and torch.isinf(got[:, 1]).all()
+
+    teacher = GPTModel(cfg, seed=77)
+    d = str(tmp_path / "teacher")
+    H.save_hf_checkpoint(d, cfg, H.convert_state_to_hf(cfg, {k: v.detach() for k, v in teacher.named_parameters()}))
+    base = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+            "--num-rollout", "1", "--rollout-max-response-len", "6", "--use-opd", "--opd-teacher-load", d, "--opd-kl-coef", "0.5", "--lr", "1e-4"]
+    with pytest.raises(ValueError, match="top-k"):
+        parse_args(base + ["--opd-token-selection", "union"])
+    with pytest.raises(ValueError, match="both distributions"):
+        parse_args(base + ["--opd-kl-type", "jsd"])
+    for sel, kl in (("student_topk", "reverse_kl"), ("teacher_topk", "forward_kl"), ("union", "jsd")):
+        a = parse_args(base + ["--opd-token-selection", sel, "--opd-log-prob-top-k", "8", "--opd-kl-type", kl])
+        assert a.opd_type == "megatron"
+        c = Controller(a, device="cpu")
+        assert c.runner.actor.cfg.opd_token_selection == sel
+        m = c.runner.step()
+        assert m["opd_kl"] > 0 and math.isfinite(m["grad_norm"]), (sel, m["opd_kl"])
+        c.runner.close()
+    a = parse_args(base[:-6] + ["--opd-type", "megatron", "--opd-kl-coef", "0.5", "--opd-topk", "4"])       # short form, no teacher: nothing to distil
+    assert a.opd_token_selection == "teacher_topk" and a.opd_log_prob_top_k == 4
