@@ -88,7 +88,7 @@ FLAGS: dict[str, list] = {
         ("--rollout-top-k", dict(type=int, default=-1)), ("--rollout-stop", dict(type=str, nargs="*", default=None)),
         ("--rollout-stop-token-ids", dict(type=int, nargs="*", default=None)), ("--rollout-skip-special-tokens", _b()),
         ("--rollout-shuffle", _b()), ("--rollout-seed", dict(type=int, default=42)),
-        ("--rollout-function-path", dict(type=str, default="relax_b200.rollout.generate.generate_rollout")),
+        ("--rollout-function-path", dict(type=str, default=None)),
         ("--custom-generate-function-path", dict(type=str, default=None)),
         ("--rollout-data-postprocess-path", dict(type=str, default=None)), ("--rollout-sample-filter-path", dict(type=str, default=None)),
         ("--dynamic-sampling-filter-path", dict(type=str, default=None)), ("--buffer-filter-path", dict(type=str, default=None)),
@@ -282,7 +282,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--rollout-function-path": (_R, "use --custom-generate-function-path to replace generation"),
     "--disable-rollout-global-dataset": (_R, "prompts always come from the global dataset"),
     "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
     "--agentic-tool-call-parser": (_R, "the chat endpoint returns the model's text; tool calls are parsed by the agent"),

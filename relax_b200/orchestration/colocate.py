@@ -83,6 +83,7 @@ class ColocateConfig:
     # user code by path ("pkg.mod:fn" or "/file.py:fn"): generate(engine, samples, sampling_params) -> samples fills
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
+    rollout_function_path: Optional[str] = None     # user code that produces the whole rollout batch (see _run_rollout_function)
     # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
     # of the list (--rollout-external / --rollout-external-engine-addrs)
     rollout_external_addrs: Optional[Sequence[str]] = None
@@ -328,6 +329,7 @@ class ColocatedGRPO:
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
             else get_reward_spec(cfg.rm_type).fn
         self.custom_generate = load_generate_function(cfg.custom_generate_function_path, None)
+        self.rollout_function = load_function(cfg.rollout_function_path, 3, "rollout function") if cfg.rollout_function_path else None
         self.group_filter = load_function(cfg.dynamic_sampling_filter_path, 1, "group filter") \
             if cfg.dynamic_sampling_filter_path else None
         self.sampling_stats: dict = {}
@@ -545,6 +547,34 @@ class ColocatedGRPO:
         self.sampling_stats = stats
         return kept[:per]
 
+    def _run_rollout_function(self, rollout_id: int, per: int, sp) -> list[Sample]:
+        """``--rollout-function-path``: user code produces the whole rollout batch of this engine replica
+        (relax/utils/arguments.py:725-737: ``generate_rollout(args, rollout_id, data_source, evaluation=False)``).  The
+        first argument here is a context object instead of the flag namespace, because the engine is a library object
+        and not an HTTP address: ``ctx.engine``, ``ctx.sampling_params``, ``ctx.reward_fn``, ``ctx.codec``, ``ctx.cfg``,
+        ``ctx.groups_wanted``, ``ctx.engine_id`` / ``ctx.num_engines``.  It returns prompt groups (lists of samples), a
+        flat list of samples, or an object with a ``samples`` attribute holding either; every sample needs ``tokens``,
+        ``response_length``, ``reward`` and ``status`` (a missing reward is filled by the reward function)."""
+        from types import SimpleNamespace
+
+        ctx = SimpleNamespace(engine=self.engine, sampling_params=sp, reward_fn=self.reward_fn, codec=self.codec, cfg=self.cfg,
+                              groups_wanted=per, engine_id=self.engine_id, num_engines=self.num_engines)
+        out = self.rollout_function(ctx, rollout_id, self.data_source, False)
+        out = getattr(out, "samples", out)
+        flat = [s for g in out for s in (g if isinstance(g, (list, tuple)) else [g])]
+        n = self.cfg.train.n_samples_per_prompt
+        if not flat or len(flat) % n:
+            raise ValueError(f"the rollout function returned {len(flat)} samples; whole prompt groups of {n} are needed")
+        for s in flat:
+            if not s.tokens or not s.response_length:
+                raise ValueError("the rollout function must set tokens and response_length on every sample")
+            if s.reward is None:
+                s.reward = self.reward_fn(s)
+            if s.status == SampleStatus.PENDING:
+                s.status = SampleStatus.COMPLETED
+        self.sampling_stats = {}
+        return flat
+
     def generate(self, rollout_id: int) -> list[Sample]:
         """One rollout batch.  With a group filter (``dynamic_sampling_filter_path``, e.g.
         ``relax_b200.rollout.filters:check_reward_nonzero_std``) the replica keeps generating
@@ -555,6 +585,8 @@ class ColocatedGRPO:
         sp = SamplingParams(temperature=cfg.temperature, top_p=cfg.top_p, top_k=cfg.top_k,
                             max_new_tokens=cfg.max_response_len, stop_token_ids=tuple(cfg.stop_token_ids or ()))
         over_n = (cfg.over_sampling_batch_size or cfg.rollout_batch_size) // self.num_engines
+        if self.rollout_function is not None:
+            return self._run_rollout_function(rollout_id, per, sp)
         if self.custom_generate is None and not self.external and (cfg.partial_rollout or (self.group_filter is None and over_n > per)):
             groups = self._generate_streaming(per, max(per, over_n), sp)
         elif self.group_filter is None:

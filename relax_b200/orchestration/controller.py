@@ -227,6 +227,7 @@ class Controller:
                 offload_rollout=a.offload_rollout, offload_train=a.offload_train,
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),
+                rollout_function_path=_get(a, "rollout_function_path", None),
                 rollout_external_addrs=(_get(a, "rollout_external_engine_addrs", None) if _get(a, "rollout_external", False) else None),
                 custom_rm_path=_get(a, "custom_rm_path", None),
                 prompt_data=_get(a, "prompt_data", None), input_key=_get(a, "input_key", None) or "prompt",

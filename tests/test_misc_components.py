@@ -196,3 +196,33 @@ def test_genrm_on_an_inhouse_engine_and_hf_roundtrip(tmp_path):
 
     assert GenRM([engine_judge(_Eng(), _Codec())]).score(["q"], ["a"], ["a"]) == [1.0]
     assert build_genrm("preset:tiny", "cpu").score(["q"], ["a"], ["b"])[0] in (0.0, 1.0)
+
+
+def test_rollout_function_by_path_produces_the_batch(tmp_path):
+    """``--rollout-function-path``: user code draws the prompts, drives the engine and returns scored prompt groups."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "my_rollout.py"
+    f.write_text(
+        "CALLS = []\n"
+        "def generate_rollout(ctx, rollout_id, data_source, evaluation=False):\n"
+        "    CALLS.append((rollout_id, ctx.groups_wanted, evaluation))\n"
+        "    groups = data_source.get_samples(ctx.groups_wanted)\n"
+        "    flat = [s for g in groups for s in g]\n"
+        "    res = ctx.engine.generate([s.tokens for s in flat], ctx.sampling_params, group_keys=[s.group_index for s in flat])\n"
+        "    for s, r in zip(flat, res):\n"
+        "        s.tokens = list(r.prompt) + list(r.output)\n"
+        "        s.response_length, s.rollout_log_probs = len(r.output), list(r.logprobs)\n"
+        "        s.reward = float(len(r.output) % 2) if s.index % 2 else None      # the loop scores the rest\n"
+        "    return type('Out', (), {'samples': groups})()\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "5", "--rm-type", "token_sum_parity",
+                    "--rollout-function-path", f"{f}:generate_rollout"])
+    c = Controller(a, device="cpu")
+    m = c.runner.step()
+    import sys
+
+    mod = [v for k, v in sys.modules.items() if k.startswith("relax_b200_user_") and hasattr(v, "CALLS")][-1]
+    assert mod.CALLS == [(0, 2, False)] and m["response_tokens_local"] > 0 and "loss" in m
+    c.runner.close()
