@@ -121,6 +121,10 @@ FLAGS: dict[str, list] = {
         ("--scale-in-shutdown-timeout", dict(type=float, default=60.0)), ("--scale-weight-sync-precheck", _b()),
         ("--scale-out-partial-success-policy", dict(type=str, default="keep", choices=["keep", "rollback"])),
         ("--autoscaler-config", dict(type=str, default=None)),
+        # external engines only: the control endpoints of the elastic pool (/scale_out, /scale_in, /engines) and further
+        # pre-launched servers the autoscaler may bring in
+        ("--elastic-control-port", dict(type=int, default=None)), ("--rollout-standby-engine-addrs", dict(type=str, nargs="*", default=None)),
+        ("--autoscaler-interval", dict(type=float, default=15.0)),
     ],
     "eval": [
         ("--eval-interval", dict(type=int, default=None)), ("--eval-prompt-data", dict(type=str, nargs="*", default=None)),
@@ -291,7 +295,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--opd-loss-coef": (_R, "the distillation signal enters through the advantages (--opd-kl-coef); the separate loss term is not wired"),
     "--opd-only-reward": (_R, "the task reward is always kept next to the distillation signal"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
-    "--autoscaler-config": (_W, "read by the elastic control service (rollout/elastic_service.py), which the training loop does not start"),
     # operational, no effect here
     "--async-save": (_W, "checkpoints are written synchronously"),
     "--attention-backend": (_W, "there is one attention implementation (tcgen05 flash attention)"),
@@ -321,8 +324,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--slime-router-middleware-paths": (_W, None), "--slime-router-sticky": (_W, None), "--slime-router-timeout": (_W, None),
     "--use-slime-router": (_W, "the in-process router is used when several engines serve one rank; the HTTP proxy is `serve router`"),
     "--train-env-vars": (_W, None), "--train-memory-margin-bytes": (_W, None), "--update-weight-buffer-size": (_W, None),
-    "--scale-out-timeout": (_W, None), "--scale-in-drain-timeout": (_W, None), "--scale-in-shutdown-timeout": (_W, None),
-    "--scale-weight-sync-precheck": (_W, None), "--scale-out-partial-success-policy": (_W, None),
+    "--scale-in-shutdown-timeout": (_W, "external engines are drained and forgotten, not shut down"),
 }
 _WARNED: set = set()
 
@@ -490,6 +492,9 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             raise ValueError("--rollout-external drives pre-launched engines from the colocated loop (--colocate)")
     elif a.rollout_external_engine_addrs:
         raise ValueError("--rollout-external-engine-addrs has no effect without --rollout-external")
+    if (a.autoscaler_config or a.elastic_control_port is not None or a.rollout_standby_engine_addrs) and not a.rollout_external:
+        raise ValueError("--autoscaler-config / --elastic-control-port / --rollout-standby-engine-addrs scale a pool of "
+                         "pre-launched engine servers: add --rollout-external --rollout-external-engine-addrs ...")
     if a.use_agentic_rollout:
         # relax/utils/arguments.py:3015-3017 points the rollout function at the agentic entry; same here
         if not a.agent_command or not a.agent_cwd:

@@ -87,6 +87,16 @@ class ColocateConfig:
     # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
     # of the list (--rollout-external / --rollout-external-engine-addrs)
     rollout_external_addrs: Optional[Sequence[str]] = None
+    # elastic pool over external engines: control endpoints on this port (+ engine replica index), autoscaling rules,
+    # further servers that may be brought in, and the scale-out / scale-in knobs
+    elastic_control_port: Optional[int] = None
+    autoscaler_config: Optional[str] = None
+    autoscaler_interval_s: float = 15.0
+    rollout_standby_addrs: Optional[Sequence[str]] = None
+    scale_out_timeout_s: float = 1800.0
+    scale_in_drain_timeout_s: float = 300.0
+    scale_weight_sync_precheck: bool = False
+    scale_out_policy: str = "keep_partial"
     dynamic_sampling_filter_path: Optional[str] = None     # fn(group) -> bool | FilterOutput
     over_sampling_batch_size: Optional[int] = None         # groups generated per round while filtering (global)
     # partial rollout (relax/engine/rollout/sglang_rollout.py generate_rollout_async / abort): over-sampled groups
@@ -220,6 +230,18 @@ class ColocatedGRPO:
             k = len(addrs) // self.num_engines
             self.engine = ExternalEngine(cfg.model, addrs[self.engine_id * k:(self.engine_id + 1) * k], device, self.actor.model.dtype,
                                          max_model_len=cfg.prompt_len + cfg.max_response_len)
+            self.elastic = None
+            if cfg.elastic_control_port is not None or cfg.autoscaler_config:
+                from ..rollout.elastic_service import ElasticControlServer
+                from ..rollout.external import external_pool
+
+                pool = external_pool(self.engine, cfg.rollout_standby_addrs or (), precheck=cfg.scale_weight_sync_precheck)
+                self.elastic = ElasticControlServer(
+                    pool, port=(cfg.elastic_control_port + self.engine_id) if cfg.elastic_control_port else 0,
+                    autoscaler_config=cfg.autoscaler_config, metrics_fn=self.engine.server_metrics,
+                    scale_out_timeout_s=cfg.scale_out_timeout_s, policy=cfg.scale_out_policy,
+                    autoscale_interval_s=cfg.autoscaler_interval_s if cfg.autoscaler_config else 0.0)
+                self.elastic.default_drain_s = cfg.scale_in_drain_timeout_s
         else:
             self.engine = RolloutEngine(cfg.model, self.rollout_tp_group, device=device, dtype=self.actor.model.dtype,
                                         num_kv_blocks=cfg.kv_blocks, block_size=cfg.kv_block_size,
@@ -351,6 +373,8 @@ class ColocatedGRPO:
 
         if self.device.type == "cuda":
             torch.cuda.synchronize()
+        if getattr(self, "elastic", None) is not None:
+            self.elastic.close()
         self.engine.close()        # graphs that captured NCCL operations must die before their communicator can
         for g in (self.rollout_tp_group, self.ps.tp):
             fused_comm.detach(g)
@@ -729,6 +753,8 @@ class ColocatedGRPO:
         if cfg.use_health_check:
             m["rollout/recoveries"] = float(self.recoveries)
         m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
+        if getattr(self, "elastic", None) is not None:
+            m["rollout/engines_active"] = float(len(self.elastic.pool.active()))
         extra = getattr(self.custom_generate, "stats", None)        # a generate function may report its own gauges
         if callable(extra):
             m.update({k: float(v) for k, v in (extra() or {}).items()})

@@ -228,6 +228,13 @@ class Controller:
                 save_debug_rollout_data=_get(a, "save_debug_rollout_data", None),
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),
                 rollout_function_path=_get(a, "rollout_function_path", None),
+                elastic_control_port=_get(a, "elastic_control_port", None), autoscaler_config=_get(a, "autoscaler_config", None),
+                autoscaler_interval_s=float(_get(a, "autoscaler_interval", 15.0)),
+                rollout_standby_addrs=_get(a, "rollout_standby_engine_addrs", None),
+                scale_out_timeout_s=float(_get(a, "scale_out_timeout", 1800.0)),
+                scale_in_drain_timeout_s=float(_get(a, "scale_in_drain_timeout", 300.0)),
+                scale_weight_sync_precheck=bool(_get(a, "scale_weight_sync_precheck", False)),
+                scale_out_policy={"keep": "keep_partial", "rollback": "rollback_all"}[_get(a, "scale_out_partial_success_policy", "keep")],
                 rollout_external_addrs=(_get(a, "rollout_external_engine_addrs", None) if _get(a, "rollout_external", False) else None),
                 custom_rm_path=_get(a, "custom_rm_path", None),
                 prompt_data=_get(a, "prompt_data", None), input_key=_get(a, "input_key", None) or "prompt",

@@ -56,6 +56,7 @@ class EnginePool:
         self.precheck, self.shutdown, self.abort = precheck, shutdown, abort
         self.clock, self.sleep = clock, sleep
         self.engines: Dict[Hashable, EngineRecord] = {}
+        self.next_id: Optional[Callable[[], Hashable]] = None      # names the engines of a count-based scale-out
         self._next = 0
         self._lock = threading.Lock()
 
@@ -77,20 +78,42 @@ class EnginePool:
                 r.weight_version = version
 
     # ------------------------------------------------------------------ scale out
-    def scale_out(self, n: int, timeout_s: float = 600.0, partial_success_policy: str = "keep_partial") -> ScaleResult:
+    def scale_out(self, n: int, timeout_s: float = 600.0, partial_success_policy: str = "keep_partial",
+                  ids: Optional[Sequence[Hashable]] = None, cancelled: Optional[Callable[[], bool]] = None) -> ScaleResult:
+        """``ids``: explicit engine ids (addresses of engines that already run) instead of ``n`` new ones; ids that
+        are active or on their way in are skipped, so that a repeated request changes nothing.  ``cancelled()`` is
+        polled between engines; engines not yet started when it turns true are not started."""
         if partial_success_policy not in ("keep_partial", "rollback_all"):
             raise ValueError("partial_success_policy is keep_partial or rollback_all")
+        if ids is not None:
+            live = (EngineState.ACTIVE, EngineState.PENDING, EngineState.SYNCING)
+            ids = [i for i in dict.fromkeys(ids) if not (i in self.engines and self.engines[i].state in live)]
+            n = len(ids)
         res = ScaleResult(requested=n)
+        if n == 0:
+            return res
         seed_id = self._seed()
         if seed_id is None:
             raise RuntimeError("scale-out needs at least one active engine to copy the weights from")
         seed = self.engines[seed_id]
         deadline = self.clock() + timeout_s
         new_ids = []
-        for _ in range(n):
+        for j in range(n):
+            if cancelled is not None and cancelled():
+                break
             with self._lock:
-                eid = f"scaled-{self._next}"
-                self._next += 1
+                if ids is not None:
+                    eid = ids[j]
+                elif self.next_id is not None:
+                    try:
+                        eid = self.next_id()           # e.g. the next address of a standby list
+                    except Exception as e:  # noqa: BLE001 - nothing left to scale out to
+                        res.failed[f"scaled-{self._next}"] = f"{type(e).__name__}: {e}"
+                        self._next += 1
+                        break
+                else:
+                    eid = f"scaled-{self._next}"
+                    self._next += 1
             rec = EngineRecord(None, EngineState.PENDING, -1, self.clock())
             self.engines[eid] = rec
             new_ids.append(eid)

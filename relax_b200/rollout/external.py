@@ -21,6 +21,14 @@ from typing import Optional, Sequence
 from .http_server import HTTPEngine
 
 
+def _guard(fn, arg):
+    try:
+        fn(arg)
+        return None
+    except Exception as e:  # noqa: BLE001 - reported per server by the caller
+        return e
+
+
 class ExternalEngine:
     def __init__(self, cfg, addrs: Sequence[str], device, dtype, max_model_len: Optional[int] = None, timeout_s: float = 3600.0,
                  check_fields: Sequence[str] = ("model",)):
@@ -31,21 +39,57 @@ class ExternalEngine:
         if cfg.vision is not None:
             raise NotImplementedError("image prompts do not travel over the HTTP surface: external engines serve text models")
         self.cfg, self.device, self.dtype, self.max_model_len = cfg, device, dtype, max_model_len
-        self.clients = [HTTPEngine(a if "://" in a else f"http://{a}", timeout_s) for a in addrs]
+        from .router import Router
+
+        self.timeout_s, self.check_fields = timeout_s, tuple(check_fields)
+        self.router = Router()                                           # membership, load, draining, health of the servers
+        clients = [self.connect(a) for a in addrs]
         self.weights = RolloutWeights(cfg, 1, 0, device, dtype)          # staging, in the servers' layout (TP 1)
         self.weight_version = 0
         self.running: list = []
         self.paused = False
         self.bm = None                                                   # no local KV cache
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0}
-        self._pool = ThreadPoolExecutor(max_workers=max(1, len(self.clients)), thread_name_prefix="ext-engine")
+        self._pool = ThreadPoolExecutor(max_workers=16, thread_name_prefix="ext-engine")
         self._lock = threading.Lock()
+        for c in clients:
+            self.router.add_worker(c.url, c)
+
+    # ------------------------------------------------------------------ membership
+    def connect(self, addr: str) -> HTTPEngine:
+        """A client for ``addr`` after checking that the server answers and serves what this job trains."""
+        c = HTTPEngine(addr if "://" in addr else f"http://{addr}", self.timeout_s)
+        info = c.info()
+        for f in self.check_fields:
+            want = {"model": self.cfg.name}.get(f)
+            if want is not None and info.get(f) != want:
+                raise ValueError(f"{c.url} serves {f}={info.get(f)!r}, this job trains {want!r}")
+        return c
+
+    @property
+    def clients(self) -> list:
+        """The servers that currently take requests and weight updates (draining ones included until removed)."""
+        return [self.router.handle(k) for k in self.router.workers()]
+
+    def ship_current_weights(self, client: HTTPEngine) -> int:
+        """Bring one server to the staging buffer's version (a server that joins while training runs)."""
+        v = self.weight_version
+        client.update_weights({k: t.detach().to("cpu") for k, t in self.weights.p.items()}, v)
+        return v
+
+    def server_metrics(self) -> dict:
+        """Gauges for autoscaling rules, from the servers' own status pages."""
+        infos = []
         for c in self.clients:
-            info = c.info()
-            for f in check_fields:
-                want = {"model": cfg.name}.get(f)
-                if want is not None and info.get(f) != want:
-                    raise ValueError(f"{c.url} serves {f}={info.get(f)!r}, this job trains {want!r}")
+            try:
+                infos.append(c.info())
+            except Exception:  # noqa: BLE001 - a dead server is the health loop's business
+                pass
+        n = max(1, len(infos))
+        used = sum(1.0 - i.get("kv_blocks_free", 0) / max(1, i.get("kv_blocks", 1)) for i in infos)
+        return {"queue_depth_per_engine": sum(i.get("waiting", 0) for i in infos) / n,
+                "running_per_engine": sum(i.get("running", 0) for i in infos) / n,
+                "kv_cache_utilization": used / n, "num_engines": float(len(infos))}
 
     # ------------------------------------------------------------------ what WeightSync calls
     def _all(self, fn):
@@ -74,29 +118,37 @@ class ExternalEngine:
         runs; results come back in the order of ``prompts``."""
         if images is not None and any(images):
             raise NotImplementedError("image prompts do not travel over the HTTP surface")
-        n, k = len(prompts), len(self.clients)
+        n = len(prompts)
         keys = list(group_keys) if group_keys is not None else list(range(n))
-        order = sorted(range(n), key=lambda i: (str(keys[i]), i))
-        groups: list = []
-        for i in order:
-            if groups and keys[groups[-1][-1]] == keys[i]:
-                groups[-1].append(i)
-            else:
-                groups.append([i])
-        shares = [[] for _ in range(k)]
-        for g_i, g in enumerate(groups):
-            shares[g_i * k // max(1, len(groups))] += g
+        groups: dict = {}
+        for i in range(n):
+            groups.setdefault(keys[i], []).append(i)
+        # the router picks a server per prompt group: least loaded among the healthy ones that are not draining
+        shares: dict = {}
+        taken = []
+        for key, idx in groups.items():
+            wid = self.router.acquire(key)
+            taken.append(wid)
+            shares.setdefault(wid, []).extend(idx)
         out = [None] * n
 
-        def run(j):
-            idx = shares[j]
-            if not idx:
-                return
+        def run(item):
+            wid, idx = item
             sp = params if not isinstance(params, (list, tuple)) else params[idx[0]]
-            for i, r in zip(idx, self.clients[j].generate([prompts[i] for i in idx], sp)):
+            for i, r in zip(idx, self.router.handle(wid).generate([prompts[i] for i in idx], sp)):
                 out[i] = r
 
-        list(self._pool.map(run, range(k)))
+        failed = set()
+        try:
+            for (wid, _), res in zip(shares.items(), self._pool.map(lambda it: _guard(run, it), shares.items())):
+                if res is not None:
+                    failed.add(wid)
+                    err = res
+        finally:
+            for wid in taken:
+                self.router.release(wid, failed=wid in failed)
+        if failed:
+            raise RuntimeError(f"external engine(s) {sorted(failed)} failed: {err}")
         with self._lock:
             self.stats["decode_tokens"] += sum(len(r.output) for r in out)
             self.stats["prefill_tokens"] += sum(len(p) for p in prompts)
@@ -122,3 +174,46 @@ class ExternalEngine:
 
     def close(self):
         self._pool.shutdown(wait=False)                    # the servers keep running: they are not ours
+
+
+def external_pool(engine: ExternalEngine, standby: Sequence[str] = (), precheck: bool = True):
+    """An :class:`~relax_b200.rollout.elastic.EnginePool` over the servers of ``engine``: scale-out connects further
+    servers (named by URL, or the next of ``standby``), checks them, ships the CURRENT weights and only then lets
+    the router send them requests; scale-in drains a server and forgets it (it keeps running: it is not ours).
+    relax/distributed/ray/rollout.py create_scale_out_request / execute_scale_out (external mode)."""
+    from .elastic import EnginePool
+    from .engine import SamplingParams
+
+    spare = [a if "://" in a else f"http://{a}" for a in standby]
+
+    def factory(eid):
+        return engine.connect(eid)
+
+    def next_standby():
+        with engine._lock:
+            if not spare:
+                raise RuntimeError("no standby engine address left to scale out to")
+            return spare.pop(0)
+
+    def check(seed, new) -> bool:
+        if not precheck:
+            return True
+        try:
+            return new.health() and len(new.generate([[1, 2]], SamplingParams(temperature=0.0, max_new_tokens=1))[0].output) == 1
+        except Exception:  # noqa: BLE001
+            return False
+
+    def release_addr(client):
+        with engine._lock:
+            if client is not None and client.url not in spare:
+                spare.append(client.url)             # may be scaled out to again later
+
+    pool = EnginePool(engine.router, factory, lambda seed, new: engine.ship_current_weights(new), precheck=check,
+                      shutdown=release_addr, abort=lambda c: c._post("/abort_request", {}) and [])
+    for url in list(engine.router.workers()):
+        from .elastic import EngineRecord, EngineState
+
+        pool.engines[url] = EngineRecord(engine.router.handle(url), EngineState.ACTIVE, engine.weight_version, pool.clock())
+    pool.next_id = next_standby
+    pool.external = engine
+    return pool

@@ -167,3 +167,78 @@ def test_scale_out_and_in_over_real_engines_through_the_control_endpoints():
         assert bad.value.code == 400 and call("/health")["status"] == "ok"
     finally:
         srv.close()
+
+
+def test_elastic_pool_of_external_engine_servers_in_a_training_job(tmp_path):
+    """A training job on one pre-launched engine server grows to three while it runs: a scale-out request by URL (the
+    new server gets the CURRENT weights before it sees a request; repeating the request is a no-op), a second server
+    brought in by an autoscaling rule from the standby list, then a scale-in that drains one and leaves it running."""
+    import json
+    import time
+    import urllib.request
+
+    import torch
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.engine import RolloutEngine
+    from relax_b200.rollout.http_server import EngineServer, HTTPEngine
+
+    cfg = get_config("tiny")
+    servers = [EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, seed=i)) for i in range(3)]
+    addr = [s.url.replace("http://", "") for s in servers]
+    rules = tmp_path / "rules.json"
+    rules.write_text(json.dumps({"min_engines": 1, "max_engines": 3, "scale_out_cooldown_s": 0.0, "scale_in_cooldown_s": 1e9,
+                                 "rules": [{"metric": "num_engines", "threshold": 2.5, "direction": "below", "for_s": 1e9},
+                                           {"metric": "always_high", "threshold": 0.5, "direction": "above", "for_s": 0.0}]}))
+
+    def call(url, path, body=None):
+        req = urllib.request.Request(url + path, data=None if body is None else json.dumps(body).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as r:
+            return json.loads(r.read())
+
+    try:
+        a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                        "--global-batch-size", "8", "--num-rollout", "3", "--rollout-max-response-len", "5", "--rollout-max-prompt-len", "16",
+                        "--lr", "1e-2", "--rm-type", "token_sum_parity", "--rollout-external", "--rollout-external-engine-addrs", addr[0],
+                        "--elastic-control-port", "0", "--autoscaler-config", str(rules), "--autoscaler-interval", "1000",
+                        "--rollout-standby-engine-addrs", addr[2], "--scale-weight-sync-precheck", "--scale-out-timeout", "60"])
+        c = Controller(a, device="cpu")
+        run = c.runner
+        ctl = f"http://127.0.0.1:{run.elastic.address[1]}"
+        run.step()
+        v1 = run.actor.weight_version
+        assert servers[0].engine.weight_version == v1 and servers[1].engine.weight_version == 0
+        # scale out by URL: accepted, runs in the background, the server ends up ACTIVE with the current weights
+        out = call(ctl, "/scale_out", {"engine_urls": [addr[1]], "timeout_secs": 60})
+        assert out["status"] == "PENDING"
+        deadline = time.monotonic() + 60
+        while call(ctl, "/scale_out")["requests"][-1]["status"] in ("PENDING", "SYNCING") and time.monotonic() < deadline:
+            time.sleep(0.05)
+        last = call(ctl, "/scale_out?status=ACTIVE")["requests"]
+        assert len(last) == 1 and last[0]["succeeded"] == [servers[1].url]
+        assert servers[1].engine.weight_version == v1
+        assert all(torch.equal(servers[1].engine.weights.p[k], servers[0].engine.weights.p[k]) for k in servers[0].engine.weights.p)
+        assert call(ctl, "/scale_out", {"engine_urls": [addr[1]]})["status"] == "NOOP"
+        served = servers[1].served
+        m = run.step()                                             # both servers generate and take the next weights
+        assert m["rollout/engines_active"] == 2.0 and servers[1].served > served
+        assert servers[1].engine.weight_version == servers[0].engine.weight_version == run.actor.weight_version == v1 + 1
+        # the autoscaler brings in the standby server
+        run.elastic.autoscaler.metrics_fn = lambda: dict(run.engine.server_metrics(), always_high=1.0)
+        assert call(ctl, "/autoscale_step", {})["action"] == "scale_out"
+        assert len(run.elastic.pool.active()) == 3 and servers[2].engine.weight_version == v1 + 1
+        # scale in by URL: drained, forgotten, still running
+        assert call(ctl, "/scale_in", {"engine_urls": [addr[1]], "timeout": 5})["removed"] == [servers[1].url]
+        served = servers[1].served
+        m = run.step()
+        assert m["rollout/engines_active"] == 2.0 and servers[1].served == served and HTTPEngine(servers[1].url).health()
+        assert servers[1].engine.weight_version == v1 + 1 and servers[2].engine.weight_version == v1 + 2
+        eng = call(ctl, "/engines")
+        assert eng[servers[1].url]["state"] == "removed" and eng[servers[2].url]["state"] == "active"
+        run.close()
+    finally:
+        for s in servers:
+            s.close()
