@@ -264,6 +264,11 @@ ENGINE_FLAGS = {
     "--sglang-tp-size": ("engine_tp", int, None), "--sglang-ep-size": ("engine_ep", int, 1),
     "--sglang-dp-size": ("engine_dp", int, 1), "--sglang-pp-size": ("engine_pp", int, 1),
     "--sglang-enable-return-routed-experts": ("engine_return_routed_experts", "flag", False),
+    # speculative decoding drafted by the model's MTP block (rollout/speculative.py): one proposal per verify pass
+    "--sglang-speculative-algorithm": ("engine_speculative_algorithm", str, None),
+    "--sglang-speculative-num-steps": ("engine_speculative_num_steps", int, 1),
+    "--sglang-speculative-eagle-topk": ("engine_speculative_eagle_topk", int, 1),
+    "--sglang-speculative-num-draft-tokens": ("engine_speculative_num_draft_tokens", int, 2),
 }
 
 
@@ -305,6 +310,8 @@ FLAG_POLICY: dict[str, tuple] = {
     "--recompute-method": (_W, "--recompute-granularity full recomputes every layer"),
     "--recompute-num-layers": (_W, "--recompute-granularity full recomputes every layer"),
     "--log-probs-chunk-size": (_W, "the fused LM head never materialises the logits"),
+    "--sglang-speculative-num-steps": (_W, "one proposal per verify pass (the output distribution does not depend on it)"),
+    "--sglang-speculative-num-draft-tokens": (_W, "one proposal per verify pass: two rows per request"),
     "--sglang-server-concurrency": (_W, None), "--agentic-prelaunch": (_W, "agents start when their sample is scheduled"),
     "--agentic-session-lifecycle": (_W, "a session's cache entries are released by the engine's own eviction"),
     "--agentic-eval-concurrency": (_W, None), "--agentic-admission-expected-decode-cap": (_W, None),
@@ -485,6 +492,15 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             pass
     elif a.opd_kl_type in ("forward_kl", "jsd"):
         raise ValueError(f"--opd-kl-type {a.opd_kl_type} needs both distributions: choose a top-K --opd-token-selection")
+    if a.engine_speculative_algorithm:
+        if a.engine_speculative_algorithm.upper() not in ("EAGLE", "NEXTN", "MTP"):
+            raise ValueError("--sglang-speculative-algorithm: the draft model is the policy's own MTP block (EAGLE / NEXTN)")
+        if not (a.mtp_num_layers or 0) and not a.hf_checkpoint:
+            raise ValueError("speculative decoding drafts with the multi-token-prediction block: set --mtp-num-layers")
+        if a.engine_speculative_eagle_topk != 1:
+            raise ValueError("--sglang-speculative-eagle-topk: one chain of proposals (top-k 1) is implemented")
+        if getattr(a, "fully_async", False) and not getattr(a, "hybrid", False):
+            raise ValueError("speculative decoding is wired into the colocated loop (the MTP block's weights travel with its sync plan)")
     if a.rollout_external:
         if not a.rollout_external_engine_addrs:
             raise ValueError("--rollout-external needs --rollout-external-engine-addrs host:port [host:port ...]")

@@ -83,6 +83,7 @@ class ColocateConfig:
     # user code by path ("pkg.mod:fn" or "/file.py:fn"): generate(engine, samples, sampling_params) -> samples fills
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
+    speculative: bool = False            # the engine drafts with the model's MTP block (rollout/speculative.py)
     rollout_function_path: Optional[str] = None     # user code that produces the whole rollout batch (see _run_rollout_function)
     # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
     # of the list (--rollout-external / --rollout-external-engine-addrs)
@@ -250,10 +251,21 @@ class ColocatedGRPO:
                                         memory_saver=cfg.engine_memory_saver,
                                         max_model_len=cfg.prompt_len + cfg.max_response_len,
                                         eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
-                                        return_routed_experts=cfg.train.use_rollout_routing_replay)
+                                        return_routed_experts=cfg.train.use_rollout_routing_replay, speculative=cfg.speculative)
         if cfg.model.vision is not None:
             # colocated: the engine embeds images with the trainer's tower itself (same parameters, nothing to sync)
             self.engine.attach_vision(self.actor.model.vision)
+        if cfg.speculative and self.external:
+            raise ValueError("speculative decoding runs in the in-process engine")
+
+        def _plan(layout, r_tp, r_ep):
+            """None (the default plan) unless the engine also needs the MTP block's weights."""
+            if not cfg.speculative:
+                return None
+            from ..weight_sync.plan import build_plan
+
+            return build_plan(cfg.model, layout, r_tp, r_ep, mtp=True)
+
         # the trainer replica that feeds my engine is the one I belong to (colocated)
         my_dp = self.ps.dp.rank
         tr_ranks = [r for r in self.ps.tp.ranks]
@@ -264,16 +276,18 @@ class ColocatedGRPO:
             self.syncs = []
             for st in range(tpp):
                 er = [grid[(st, j)] for j in range(ttp)]
-                self.syncs.append((WeightSync(cfg.model, TrainerLayout(tp=ttp, pp=tpp), rtp, grid, er), tuple(er) == eng_ranks))
+                self.syncs.append((WeightSync(cfg.model, TrainerLayout(tp=ttp, pp=tpp), rtp, grid, er,
+                                              plan=_plan(TrainerLayout(tp=ttp, pp=tpp), rtp, 1)), tuple(er) == eng_ranks))
             self.sync = next(sy for sy, mine in self.syncs if mine)
             self._aligned = False
         elif tep > 1:
             self.sync = WeightSync(cfg.model, TrainerLayout(tp=1, ep=tep), 1, [self.rank], list(eng_ranks), rollout_ep=rep_,
+                                   plan=_plan(TrainerLayout(tp=1, ep=tep), 1, rep_),
                                    aligned_ep_rank=self.ps.ep.rank)
             self.syncs = [(self.sync, True)]
             self._aligned = False        # the ranks of one engine generate the same samples: rows are re-split over DP
         else:
-            self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks))
+            self.sync = WeightSync(cfg.model, TrainerLayout(tp=ttp), rtp, tr_ranks, list(eng_ranks), plan=_plan(TrainerLayout(tp=ttp), rtp, 1))
             self.syncs = [(self.sync, True)]
             # with context parallelism a trainer replica spans tp x cp ranks that must all see the SAME rows (each holds
             # a slice of every sequence), while each of them feeds an engine of its own: rows always travel
@@ -755,6 +769,10 @@ class ColocatedGRPO:
         m.update({f"rollout/dynamic_sampling/{k}": float(v) for k, v in self.sampling_stats.items()})
         if getattr(self, "elastic", None) is not None:
             m["rollout/engines_active"] = float(len(self.elastic.pool.active()))
+        if cfg.speculative:
+            d, a_, v_ = (st.pop(k, 0) for k in ("spec_draft_tokens", "spec_accepted_tokens", "spec_verify_steps"))
+            m.update({"rollout/spec_accept_rate": a_ / max(1, d), "rollout/spec_draft_tokens": float(d),
+                      "rollout/spec_verify_steps": float(v_)})
         extra = getattr(self.custom_generate, "stats", None)        # a generate function may report its own gauges
         if callable(extra):
             m.update({k: float(v) for k, v in (extra() or {}).items()})

@@ -25,6 +25,7 @@ import torch.distributed as dist
 from .. import ops
 from ..models.config import ModelConfig
 from ..parallel.state import GroupInfo
+from .speculative import SpeculativeMixin
 from .weights import RolloutWeights
 
 
@@ -66,6 +67,10 @@ class Request:
     t_arrive: float = 0.0
     t_first: float = 0.0
     t_done: float = 0.0
+    # speculative decoding: proposals checked / accepted and verify passes of this request
+    spec_draft: int = 0
+    spec_accept: int = 0
+    spec_verify: int = 0
 
     @property
     def num_tokens(self) -> int:
@@ -107,15 +112,22 @@ class BlockManager:
         return (ntokens + self.block_size - 1) // self.block_size
 
 
-class RolloutEngine:
+class RolloutEngine(SpeculativeMixin):
     def __init__(self, cfg: ModelConfig, tp: Optional[GroupInfo] = None, device="cpu", dtype=None,
                  num_kv_blocks: int = 256, block_size: int = 16, max_running: int = 256,
                  max_prefill_tokens: int = 16384, seed: int = 42, eos_token_id: Optional[int] = None,
                  use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
                  decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None,
                  weights_shared_path: Optional[str] = None, ep: Optional[GroupInfo] = None,
-                 return_routed_experts: bool = False):
+                 return_routed_experts: bool = False, speculative: bool = False):
         self.cfg = cfg
+        # speculative decoding drafted by the model's multi-token-prediction block (rollout/speculative.py)
+        self.speculative = bool(speculative)
+        if self.speculative:
+            if cfg.mtp_num_layers < 1:
+                raise ValueError("speculative decoding drafts with the model's multi-token-prediction block; this model has none")
+            if cfg.vision is not None or (return_routed_experts and cfg.is_moe):
+                raise NotImplementedError("speculative decoding serves text prompts and does not record routed experts")
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
         self.dtype = dtype or {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
@@ -131,7 +143,7 @@ class RolloutEngine:
             raise NotImplementedError("an engine is tensor-parallel or expert-parallel, not both")
         self.weights = RolloutWeights(cfg, self.tp.size, self.tp.rank, self.device, self.dtype,
                                       ep_size=self.ep.size if self.ep else 1, ep_rank=self.ep.rank if self.ep else 0,
-                                      memory_saver=self.memory_saver, shared_path=weights_shared_path)
+                                      memory_saver=self.memory_saver, shared_path=weights_shared_path, mtp=self.speculative)
         self.weights.ep_group = self.ep
         self.return_routed_experts = bool(return_routed_experts) and cfg.is_moe
         self.block_size = block_size
@@ -155,6 +167,8 @@ class RolloutEngine:
             decode_window = int(os.environ.get("RELAX_B200_DECODE_WINDOW", "16"))
         self.decode_window = max(1, int(decode_window))
         self.windowed_decode = self.use_cuda_graph if windowed_decode is None else bool(windowed_decode)
+        if self.speculative:
+            self.windowed_decode = False     # the rows per request change from step to step: host-driven iterations
         if os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") == "1" and self.device.type == "cuda":
             self.windowed_decode = False     # the library-path arm keeps the host-driven loop
         self._graphs = {}
@@ -167,7 +181,8 @@ class RolloutEngine:
     def _alloc_kv(self):
         c = self.cfg
         hkv = c.num_query_groups // self.tp.size
-        shape = (c.num_layers, 2, self.bm.num_blocks, self.block_size, hkv, c.head_dim)
+        # with speculative decoding the draft block keeps its own cache as one more layer under the same block tables
+        shape = (c.num_layers + (1 if self.speculative else 0), 2, self.bm.num_blocks, self.block_size, hkv, c.head_dim)
         if self.memory_saver:
             from ..utils.memory_saver import PausableBuffer
 
@@ -426,8 +441,13 @@ class RolloutEngine:
             image = self._image_rows(leaders, cu, toks) if multimodal else None
             if self.return_routed_experts:
                 self.weights.routing_capture = []
-            logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
-                                                  max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), image=image)
+            h_all = None
+            if self.speculative:
+                logits, h_all = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
+                                                             max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), return_hidden=True)
+            else:
+                logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
+                                                      max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), image=image)
             self.stats["prefill_tokens"] += len(toks)
             if self.return_routed_experts:
                 routed = torch.stack(self.weights.routing_capture, 1).tolist()      # [T][L_moe][k]
@@ -453,6 +473,8 @@ class RolloutEngine:
                 rows.append(row_of[id(r)])
         sel = logits[torch.tensor(rows, device=dev)] if rows != list(range(len(leaders))) else logits
         self._sample_and_append(reqs, sel)
+        if self.speculative and leaders:
+            self._draft_after_prefill(reqs, leaders, h_all, cu, slots_t, pos_t, cu_t, row_of)
         now = time.perf_counter()
         for r in reqs:
             r.t_first = now
@@ -489,6 +511,8 @@ class RolloutEngine:
         return torch.tensor(rows, dtype=torch.int64, device=self.device), emb
 
     def _decode(self):
+        if self.speculative:
+            return self._decode_speculative()
         if self.windowed_decode and self._decode_window():
             return
         reqs = self.running

@@ -28,12 +28,16 @@ from ..models.config import ModelConfig
 from ..parallel.state import GroupInfo
 
 
-def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
+def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = False) -> dict:
+    """``mtp``: the buffer also holds the first multi-token-prediction block (draft model of speculative decoding) -
+    its transformer layer as layer ``num_layers`` and ``mtp.enorm / mtp.hnorm / mtp.eh_proj / mtp.final_norm`` - AFTER
+    everything else, so that the offsets of the policy's own tensors do not depend on the switch."""
     hd, H = cfg.head_dim, cfg.hidden_size
     nq, nkv = cfg.num_attention_heads // tp, cfg.num_query_groups // tp
     v_pad = (cfg.vocab_size + tp - 1) // tp * tp
     shapes = {"embed": (v_pad // tp, H)}
-    for i in range(cfg.num_layers):
+
+    def layer(i):
         p = f"layers.{i}."
         shapes[p + "input_norm"] = (H,)
         shapes[p + "qkv"] = ((nq + 2 * nkv) * hd, H)
@@ -60,16 +64,23 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1) -> dict:
             F = cfg.ffn_hidden_size // tp
             shapes[p + "gate_up"] = (2 * F, H)
             shapes[p + "down"] = (H, F)
+
+    for i in range(cfg.num_layers):
+        layer(i)
     shapes["final_norm"] = (H,)
     if not cfg.tie_word_embeddings:
         shapes["lm_head"] = (v_pad // tp, H)
+    if mtp:
+        layer(cfg.num_layers)
+        shapes["mtp.enorm"], shapes["mtp.hnorm"], shapes["mtp.final_norm"] = (H,), (H,), (H,)
+        shapes["mtp.eh_proj"] = (H, 2 * H)
     return shapes
 
 
-def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1):
+def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = False):
     """``(shapes, element offsets, total elements)`` of one rank's flat parameter buffer.  A pure function of the
     configuration, so a trainer rank can address tensors inside a rollout rank's buffer without asking it."""
-    shapes = rollout_param_shapes(cfg, tp, ep)
+    shapes = rollout_param_shapes(cfg, tp, ep, mtp)
     offsets, n = {}, 0
     for k, s in shapes.items():
         offsets[k] = n
@@ -79,7 +90,7 @@ def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1):
 
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
-                 memory_saver: bool = False, shared_path: Optional[str] = None):
+                 memory_saver: bool = False, shared_path: Optional[str] = None, mtp: bool = False):
         if cfg.attention_output_gate or cfg.rotary_percent < 1.0 or cfg.sandwich_norm:
             raise NotImplementedError("the rollout engine serves plain pre-norm softmax attention; gated attention / partial "
                                       "rotary (Qwen3.5) and sandwich-norm (GLM-4) models are trainer-side for now")
@@ -94,7 +105,10 @@ class RolloutWeights:
         self.routing_capture: Optional[list] = None
         self.moe_layers = [i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)]
         self.device, self.dtype = torch.device(device), dtype
-        self.shapes, self.offsets, self.numel = rollout_layout(cfg, tp_size, ep_size)
+        self.mtp = bool(mtp)          # the buffer also holds the first MTP block (draft model of speculative decoding)
+        if self.mtp and cfg.mtp_num_layers < 1:
+            raise ValueError("speculative decoding drafts with the model's multi-token-prediction block; this model has none")
+        self.shapes, self.offsets, self.numel = rollout_layout(cfg, tp_size, ep_size, self.mtp)
         # CPU only: back the buffer by a shared-memory file so that other processes can map and write it (the CPU
         # stand-in for a peer mapping of device memory; see weight_sync/peer_push.py)
         self.shared_path = shared_path
@@ -262,7 +276,9 @@ class RolloutWeights:
         x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
         return h, x
 
-    def _run(self, tokens, positions, attn, tp, cache, image=None):
+    def _run(self, tokens, positions, attn, tp, cache, image=None, prenorm: bool = False):
+        """The trunk.  Returns the final-norm output of every row; with ``prenorm`` also the residual stream before the
+        final norm (the input of the multi-token-prediction block)."""
         cfg, p = self.cfg, self.p
         h = self._embed(tokens, tp)
         if image is not None:      # (rows, embeddings): image placeholder rows take the vision tower's output
@@ -272,16 +288,65 @@ class RolloutWeights:
         for i in range(cfg.num_layers):
             nxt = p[f"layers.{i + 1}.input_norm"] if i + 1 < cfg.num_layers else p["final_norm"]
             h, x = self._layer(i, h, x, cos, sin, attn, tp, nxt, cache)
-        return x
+        return (x, h) if prenorm else x
 
     # ------------------------------------------------------------------ entry points
     def forward_prefill(self, tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None,
-                        image=None):
+                        image=None, return_hidden: bool = False):
         def attn(i, q, k, v):
             return ops.attention_varlen(q, k, v, cu_seqlens, causal=True, max_seqlen=max_seqlen)
 
+        if return_hidden:      # speculative decoding: the draft block reads the trunk's pre-norm hidden of every row
+            x, h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True), image=image, prenorm=True)
+            return self._logits(x[last_rows], tp), h
         h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True), image=image)
         return self._logits(h[last_rows], tp)
+
+    # ------------------------------------------------------------------ speculative decoding (draft = the MTP block)
+    def forward_rows(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
+        """A decode-shaped pass in which a request may own SEVERAL rows (its newest token and draft tokens after it):
+        row ``j`` writes its K/V to ``slots[j]`` and attends to the first ``context_lens[j]`` positions of its block
+        table, which include the rows of the same request before it - every layer writes all rows' K/V before its
+        attention runs.  Returns ``(logits, pre-norm hidden)`` per row."""
+        def attn(i, q, k, v):
+            return ops.paged_decode_attention(q, kv[i, 0], kv[i, 1], block_tables, context_lens)
+
+        x, h = self._run(tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, False), prenorm=True)
+        return self._logits(x, tp), h
+
+    def _mtp_block(self, h_prev, next_tokens, positions, attn, tp, cache):
+        """The multi-token-prediction block on rows: ``h_prev`` is the trunk's pre-norm hidden at a position,
+        ``next_tokens`` the token that FOLLOWS that position; the output predicts the token after that one
+        (relax_b200/models/mtp.py MTPBlock.forward: concat of the two normed inputs, projection, one decoder layer,
+        final norm, the shared LM head)."""
+        cfg, p = self.cfg, self.p
+        L = cfg.num_layers
+        eps = cfg.rms_norm_eps
+        emb = self._embed(next_tokens, tp)
+        x = torch.cat([ops.rmsnorm(emb, p["mtp.enorm"], eps), ops.rmsnorm(h_prev.to(emb.dtype), p["mtp.hnorm"], eps)], -1)
+        h = ops.linear(x, p["mtp.eh_proj"])
+        cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        xin = ops.rmsnorm(h, p[f"layers.{L}.input_norm"], eps)
+        _, xn = self._layer(L, h, xin, cos, sin, attn, tp, p["mtp.final_norm"], cache)
+        return xn
+
+    def forward_mtp_rows(self, h_prev, next_tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo, out_rows=None):
+        """Draft logits from decode-shaped rows (layer ``num_layers`` of ``kv`` is the block's own cache)."""
+        L = self.cfg.num_layers
+
+        def attn(i, q, k, v):
+            return ops.paged_decode_attention(q, kv[L, 0], kv[L, 1], block_tables, context_lens)
+
+        xn = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, False))
+        return self._logits(xn if out_rows is None else xn[out_rows], tp)
+
+    def forward_mtp_prefill(self, h_prev, next_tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
+        """The block over whole prompts (fills its cache for every prompt position); draft logits of the last rows."""
+        def attn(i, q, k, v):
+            return ops.attention_varlen(q, k, v, cu_seqlens, causal=True, max_seqlen=max_seqlen)
+
+        xn = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True))
+        return self._logits(xn[last_rows], tp)
 
     def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
         def attn(i, q, k, v):

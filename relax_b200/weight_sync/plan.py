@@ -65,7 +65,7 @@ def _row_sharded(canon_rows: int, src_parts: int, dst_parts: int):
                 yield sp, it[0] - sp * s, dp, it[0] - dp * d, it[1] - it[0]
 
 
-def trainer_param_name(layer_local: int, kind: str) -> str:
+def _trainer_param_name(layer_local: int, kind: str) -> str:
     base = f"decoder.layers.{layer_local}."
     return {
         "qkv": base + "self_attention.linear_qkv.weight",
@@ -88,11 +88,21 @@ def trainer_param_name(layer_local: int, kind: str) -> str:
     }[kind]
 
 
-def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 1) -> list[BlockCopy]:
+trainer_param_name = _trainer_param_name
+
+
+MTP_TRAINER_PREFIX = "mtp.layers.0."
+
+
+def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 1, mtp: bool = False) -> list[BlockCopy]:
     """All block copies for one rollout engine, sourced from ONE trainer
     data-parallel replica.  ``src_rank`` is the trainer TP rank for dense
     tensors and the EP rank for expert tensors (``src_batch`` = local expert);
-    the pipeline stage that owns a layer is implied by the layer index."""
+    the pipeline stage that owns a layer is implied by the layer index.
+
+    ``mtp``: also the first multi-token-prediction block (the engine's draft model for speculative decoding): its
+    transformer layer becomes rollout layer ``num_layers``, its norms and projection ``mtp.*``; it lives on the last
+    pipeline stage."""
     H, hd = cfg.hidden_size, cfg.head_dim
     ng, qpg = cfg.num_query_groups, cfg.num_attention_heads // cfg.num_query_groups
     plan: list[BlockCopy] = []
@@ -120,9 +130,22 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
 
     ng_s, ng_d = ng // src.tp, ng // dst_tp
     grp_rows = (qpg + 2) * hd
-    for layer in range(cfg.num_layers):
-        ll = layer % per_stage
+    layers = [(layer, layer % per_stage, None) for layer in range(cfg.num_layers)]
+    if mtp:
+        if cfg.mtp_num_layers < 1:
+            raise ValueError("the model has no multi-token-prediction block to draft with")
+        layers.append((cfg.num_layers, 0, MTP_TRAINER_PREFIX + "transformer_layer."))
+        rep(MTP_TRAINER_PREFIX + "enorm.weight", "mtp.enorm", H)
+        rep(MTP_TRAINER_PREFIX + "hnorm.weight", "mtp.hnorm", H)
+        rep(MTP_TRAINER_PREFIX + "final_layernorm.weight", "mtp.final_norm", H)
+        for r in range(dst_tp):
+            add(BlockCopy(r % src.tp, MTP_TRAINER_PREFIX + "eh_proj.weight", 0, 0, r, "mtp.eh_proj", 0, 0, H, 2 * H))
+    for layer, ll, base in layers:
         p = f"layers.{layer}."
+        if base is not None:
+            trainer_param_name = lambda l_, kind, _b=base: _trainer_param_name(l_, kind).replace("decoder.layers.0.", _b)  # noqa: E731
+        else:
+            trainer_param_name = _trainer_param_name
         rep(trainer_param_name(ll, "input_norm"), p + "input_norm", H)
         if cfg.qk_layernorm:
             rep(trainer_param_name(ll, "q_norm"), p + "q_norm", hd)
@@ -180,7 +203,7 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
 
         def stage_of(b: BlockCopy) -> int:
             if b.dst_name.startswith("layers."):
-                return int(b.dst_name.split(".")[1]) // per_stage
+                return min(int(b.dst_name.split(".")[1]) // per_stage, src.pp - 1)      # the MTP layer sits on the last stage
             if b.dst_name == "embed":
                 return 0
             return src.pp - 1          # final norm, output layer
