@@ -148,3 +148,32 @@ def test_speculative_rollouts_in_the_colocated_loop():
                        p["mtp.layers.0.transformer_layer.mlp.linear_fc2.weight"].detach().to(run.engine.weights.p[f"layers.{L}.down"].dtype))
     run.step()
     run.close()
+
+
+def test_a_trained_block_halves_the_number_of_passes():
+    """Policy and MTP block trained (SFT with the MTP loss) on a predictable sequence: the block's proposals are
+    accepted and 24 tokens take 12 verify passes instead of 23 decode passes."""
+    from relax_b200.train.actor import TrainActor, TrainConfig
+    from relax_b200.train.optimizer import OptimizerConfig
+
+    torch.manual_seed(0)
+    cfg = get_config("tiny", mtp_num_layers=1)
+    actor = TrainActor(cfg, TrainConfig(global_batch_size=16, enable_mtp_training=True, mtp_loss_scaling_factor=1.0, pad_multiple=1,
+                                        max_tokens_per_gpu=4096, optim=OptimizerConfig(lr=3e-3)), role="sft")
+
+    def seq(start, n):
+        return [3 + (start + 5 * i) % 40 for i in range(n)]
+
+    batch = {"tokens": [seq(s, 40) for s in range(16)], "response_lengths": [39] * 16, "total_lengths": [40] * 16,
+             "loss_masks": [[1] * 39 for _ in range(16)]}
+    for _ in range(30):
+        m = actor.train_sft(batch)
+    assert m["loss"] < 0.01 and m["mtp_loss"] < 0.01
+    spec = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=256, block_size=8, speculative=True)
+    WeightSync(cfg, TrainerLayout(tp=1), 1, [0], [0], plan=build_plan(cfg, TrainerLayout(tp=1), 1, mtp=True)) \
+        .update_weights(dict(actor.named_local_params()), spec.weights, spec, version=1)
+    out = spec.generate([seq(s, 8) for s in (1, 7, 20)], SamplingParams(temperature=0.0, max_new_tokens=24))
+    for s, r in zip((1, 7, 20), out):
+        assert r.output == seq(s, 32)[8:]
+        assert r.spec_accept == r.spec_draft == 11 and r.spec_verify == 12
+    assert spec.stats["steps"] == 13 and spec.stats["spec_accepted_tokens"] == 33
