@@ -84,6 +84,7 @@ class ColocateConfig:
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
     speculative: bool = False            # the engine drafts with the model's MTP block (rollout/speculative.py)
+    rollout_global_dataset: bool = True             # False: no prompt dataset; the rollout function brings its own data
     rollout_function_path: Optional[str] = None     # user code that produces the whole rollout batch (see _run_rollout_function)
     # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
     # of the list (--rollout-external / --rollout-external-engine-addrs)
@@ -307,7 +308,15 @@ class ColocatedGRPO:
         if not self._aligned and tpp == 1 and not (ttp == 1 or rtp == 1 or ttp == rtp):
             raise NotImplementedError("colocated sync needs trainer TP group == rollout engine ranks, or TP 1 on one side")
         self.queue = tq.init({"capacity_partitions": 2})
-        if cfg.prompt_data:
+        ds = None
+        if not cfg.rollout_global_dataset:
+            from ..rollout.data_source import ShellDataSource
+
+            if not cfg.rollout_function_path:
+                raise ValueError("--disable-rollout-global-dataset leaves the prompts to user code: set --rollout-function-path")
+            self.codec = cfg.codec
+            self.data_source = ShellDataSource(cfg.train.n_samples_per_prompt)
+        elif cfg.prompt_data:
             from ..data.tokenizer import ByteCodec, PromptEncoder
             from ..rollout.data_source import JsonlPromptDataset
 

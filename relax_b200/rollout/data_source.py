@@ -172,6 +172,31 @@ class RolloutDataSource:
         return True
 
 
+class _NoPrompts:
+    """Stand-in dataset of a data source without a global dataset: every row is an empty prompt."""
+
+    def __len__(self):
+        return 1 << 62
+
+    def __getitem__(self, i):
+        return {"prompt": "", "prompt_tokens": [], "label": None, "metadata": {}}
+
+
+class ShellDataSource(RolloutDataSource):
+    """``--disable-rollout-global-dataset``: no prompt dataset is loaded; the source hands out numbered, empty samples
+    and the rollout function brings its own data (relax/engine/rollout/data_source.py:169-231 - ``dataset`` stays
+    None, groups of ``Sample()`` shells; nothing is saved or loaded for it)."""
+
+    def __init__(self, n_samples_per_prompt: int):
+        super().__init__(_NoPrompts(), n_samples_per_prompt, shuffle=False)
+
+    def _make_order(self):
+        return range(len(self.dataset))
+
+    def save(self, directory: str, rollout_id: int):
+        pass
+
+
 class RolloutDataSourceWithBuffer(RolloutDataSource):
     """Aborted groups go to a buffer and are served before fresh prompts."""
 

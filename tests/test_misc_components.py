@@ -226,3 +226,33 @@ def test_rollout_function_by_path_produces_the_batch(tmp_path):
     mod = [v for k, v in sys.modules.items() if k.startswith("relax_b200_user_") and hasattr(v, "CALLS")][-1]
     assert mod.CALLS == [(0, 2, False)] and m["response_tokens_local"] > 0 and "loss" in m
     c.runner.close()
+
+
+def test_rollout_function_brings_its_own_prompts_without_a_global_dataset(tmp_path):
+    """``--disable-rollout-global-dataset``: the data source hands out numbered empty samples, user code fills them."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "own_data.py"
+    f.write_text(
+        "def generate_rollout(ctx, rollout_id, data_source, evaluation=False):\n"
+        "    groups = data_source.get_samples(ctx.groups_wanted)\n"
+        "    assert all(s.tokens == [] and s.prompt == '' for g in groups for s in g)\n"
+        "    flat = [s for g in groups for s in g]\n"
+        "    for s in flat:\n"
+        "        s.prompt = 'task %d' % s.group_index\n"
+        "        s.tokens = [5 + s.group_index % 7, 9, 11]\n"
+        "    res = ctx.engine.generate([s.tokens for s in flat], ctx.sampling_params, group_keys=[s.group_index for s in flat])\n"
+        "    for s, r in zip(flat, res):\n"
+        "        s.tokens, s.response_length = list(r.prompt) + list(r.output), len(r.output)\n"
+        "        s.rollout_log_probs, s.reward = list(r.logprobs), float(s.index % 2)\n"
+        "    return groups\n")
+    base = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+            "--num-rollout", "1", "--rollout-max-response-len", "4", "--disable-rollout-global-dataset"]
+    with pytest.raises(ValueError, match="rollout-function-path"):
+        Controller(parse_args(base), device="cpu")
+    c = Controller(parse_args(base + ["--rollout-function-path", f"{f}:generate_rollout", "--save", str(tmp_path / "ck"), "--save-interval", "1"]),
+                   device="cpu")
+    m = c.runner.step()
+    assert m["raw_reward_mean"] == 0.5 and c.runner.data_source.group_index == 2
+    c.runner.close()
