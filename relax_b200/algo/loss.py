@@ -29,6 +29,12 @@ class LossConfig:
     kl_loss_coef: float = 0.0
     kl_loss_type: str = "k1"
     use_unbiased_kl: bool = False
+    # on-policy distillation as a loss term (the teacher's log-probs of the sampled tokens travel in LossBatch.extras)
+    opd_loss_coef: float = 0.0
+    opd_kl_type: str = "reverse_kl"
+    opd_per_token_clip: Optional[float] = None
+    opd_is_clip: Optional[float] = None
+    opd_log_prob_min_clamp: Optional[float] = None
     use_tis: bool = False
     tis_clip: float = 2.0
     tis_clip_low: float = 0.0
@@ -191,6 +197,25 @@ def policy_loss(log_probs: torch.Tensor, entropy: torch.Tensor, b: LossBatch, cf
         kl_loss = red(kl)
         loss = loss + cfg.kl_loss_coef * kl_loss
         metrics["kl_loss"] = kl_loss.detach()
+
+    if cfg.opd_loss_coef != 0.0 and b.extras.get("teacher_log_probs") is not None:
+        # on-policy distillation as a differentiable loss term (relax/utils/opd/opd_utils.py compute_policy_opd_loss
+        # :1366-1455): per-token divergence of the sampled token, clipped from above, optionally weighted by the
+        # truncated importance ratio of the current to the old policy
+        from . import opd as _opd
+
+        d = _opd.token_kl(log_probs, b.extras["teacher_log_probs"].detach(), kl_type=cfg.opd_kl_type,
+                          log_prob_min_clamp=cfg.opd_log_prob_min_clamp)
+        if cfg.opd_per_token_clip is not None:
+            metrics["opd_per_token_clip_frac"] = red((d > cfg.opd_per_token_clip).float()).detach()
+            d = d.clamp(max=float(cfg.opd_per_token_clip))
+        if cfg.opd_is_clip is not None:
+            ratio = torch.exp(log_probs.detach() - old.detach())
+            metrics["opd_is_clip_frac"] = red((ratio > cfg.opd_is_clip).float()).detach()
+            d = d * ratio.clamp(max=float(cfg.opd_is_clip))
+        opd_l = red(d)
+        loss = loss + cfg.opd_loss_coef * opd_l
+        metrics["opd_loss"] = opd_l.detach()
 
     if log_probs.numel() == 0:
         loss = loss + 0.0 * log_probs.sum()

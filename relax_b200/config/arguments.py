@@ -176,7 +176,7 @@ FLAGS: dict[str, list] = {
         ("--opd-kl-type", dict(type=str, default="reverse_kl", choices=["reverse_kl", "forward_kl", "jsd", "low_var_kl"])),
         ("--opd-jsd-alpha", dict(type=float, default=0.5)), ("--opd-norm-mode", dict(type=str, default="tail", choices=["tail", "norm", "trunc"])),
         ("--opd-log-prob-min-clamp", dict(type=float, default=None)), ("--opd-per-token-clip", dict(type=float, default=None)),
-        ("--opd-loss-coef", dict(type=float, default=0.0)), ("--opd-only-reward", _b()),
+        ("--opd-loss-coef", dict(type=float, default=0.0)), ("--opd-only-reward", _b()), ("--opd-is-clip", dict(type=float, default=None)),
     ],
     "lora": [
         ("--lora-rank", dict(type=int, default=0)), ("--lora-alpha", dict(type=float, default=16.0)),
@@ -296,8 +296,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
     "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
-    "--opd-loss-coef": (_R, "the distillation signal enters through the advantages (--opd-kl-coef); the separate loss term is not wired"),
-    "--opd-only-reward": (_R, "the task reward is always kept next to the distillation signal"),
     "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
     # operational, no effect here
     "--async-save": (_W, "checkpoints are written synchronously"),
@@ -481,6 +479,18 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
         a.opd_log_prob_top_k = a.opd_topk
         if a.opd_token_selection == "student_sampled":
             a.opd_token_selection = "teacher_topk"
+    if not a.opd_type:
+        a.opd_loss_coef = 0.0
+    if a.opd_type and (a.opd_loss_coef or 0.0) != 0.0:
+        # relax/utils/opd/opd_utils.py:719-731: the signal enters through the advantages OR as a loss term
+        if a.opd_kl_coef not in (0.0, 1.0):          # 1.0 is the flag's default: loss mode overrides it
+            raise ValueError("exactly one of --opd-kl-coef / --opd-loss-coef is non-zero (advantage mode or loss mode)")
+        a.opd_kl_coef = 0.0
+        if a.opd_token_selection != "student_sampled":
+            raise ValueError("--opd-loss-coef (loss mode) is wired for the sampled token; top-K selections use --opd-kl-coef")
+    for name in ("opd_per_token_clip", "opd_is_clip"):
+        if getattr(a, name) is not None and getattr(a, name) <= 0:
+            raise ValueError(f"--{name.replace('_', '-')} must be > 0")
     if a.opd_token_selection != "student_sampled":
         if a.opd_log_prob_top_k <= 0:
             raise ValueError(f"--opd-token-selection {a.opd_token_selection} needs --opd-log-prob-top-k > 0")
@@ -632,6 +642,7 @@ def train_config_from_args(a):
         enable_mtp_training=a.enable_mtp_training, mtp_loss_scaling_factor=a.mtp_loss_scaling_factor,
         mtp_only_training=a.mtp_only_training,
         opd_kl_coef=float(a.opd_kl_coef) if getattr(a, "opd_type", None) else 0.0,
+        opd_only_reward=bool(a.opd_only_reward) and bool(getattr(a, "opd_type", None)),
         opd_kl_type=a.opd_kl_type, opd_jsd_alpha=a.opd_jsd_alpha, opd_norm_mode=a.opd_norm_mode,
         opd_log_prob_min_clamp=a.opd_log_prob_min_clamp, opd_per_token_clip=a.opd_per_token_clip,
         opd_token_selection={"student_sampled": "sampled_token"}.get(a.opd_token_selection, a.opd_token_selection),

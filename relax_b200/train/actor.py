@@ -85,6 +85,7 @@ class TrainConfig:
     opd_jsd_alpha: float = 0.5
     opd_norm_mode: str = "tail"
     opd_log_prob_min_clamp: Optional[float] = None
+    opd_only_reward: bool = False                  # drop the task reward's advantages, keep the distillation signal
     opd_per_token_clip: Optional[float] = None
     enable_mtp_training: bool = False   # add the multi-token-prediction loss of the model's MTP blocks
     mtp_loss_scaling_factor: float = 0.1
@@ -756,6 +757,13 @@ class TrainActor:
             raise ValueError("--disable-compute-advantages-and-returns needs a custom loss function (the policy losses read "
                              "the advantages)")
         opd_metric = None
+        if cfg.opd_only_reward and (cfg.opd_kl_coef != 0.0 or cfg.loss.opd_loss_coef != 0.0) and batch.get("advantages") is not None:
+            # pure distillation (relax/backends/megatron/loss.py:638-644): the task reward's contribution is removed
+            batch["advantages"] = [torch.zeros_like(a) for a in batch["advantages"]]
+            batch["returns"] = [torch.zeros_like(r_) for r_ in batch["returns"]]
+        if cfg.loss.opd_loss_coef != 0.0 and batch.get("teacher_log_probs") is None and "teacher" in self.snapshots:
+            with self.timer.span("teacher_log_probs"):      # loss mode: the term itself is built in the policy loss
+                batch["teacher_log_probs"] = self.compute_log_prob(batch, "teacher")["log_probs"]
         if cfg.opd_kl_coef != 0.0 and (batch.get("teacher_log_probs") is not None or "teacher" in self.snapshots):
             from ..algo import opd as OPD
 
@@ -849,10 +857,13 @@ class TrainActor:
             from ..algo.ppo_utils import to_device_async
 
             denoms = to_device_async(torch.tensor([float(batch["sample_index_mask_sums"][i]) for i in idx], dtype=torch.float32), dev)
+        extras = {}
+        if self.cfg.loss.opd_loss_coef != 0.0 and batch.get("teacher_log_probs") is not None:
+            extras["teacher_log_probs"] = f("teacher_log_probs")
         return L.LossBatch(seg=seg, loss_mask=f("loss_masks"), advantages=f("advantages"),
                            old_log_probs=f("log_probs"), ref_log_probs=f("ref_log_probs"),
                            rollout_log_probs=f("rollout_log_probs"), returns=f("returns"), values=f("values"),
-                           sample_denoms=denoms)
+                           sample_denoms=denoms, extras=extras)
 
     def _train_step(self, batch, idx):
         cfg, ps = self.cfg, self.ps

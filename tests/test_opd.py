@@ -221,3 +221,48 @@ def test_topk_log_probs_match_a_plain_softmax_and_drive_the_topk_selections(tmp_
         c.runner.close()
     a = parse_args(base[:-6] + ["--opd-type", "megatron", "--opd-kl-coef", "0.5", "--opd-topk", "4"])       # short form, no teacher: nothing to distil
     assert a.opd_token_selection == "teacher_topk" and a.opd_log_prob_top_k == 4
+
+
+def test_loss_mode_and_pure_distillation(tmp_path):
+    """``--opd-loss-coef`` (the divergence as a differentiable loss term, with the per-token and importance clips) and
+    ``--opd-only-reward`` (the task reward's advantages removed): the loss term equals its definition, and a pure
+    distillation step moves the policy towards the teacher."""
+    from relax_b200.algo import loss as L
+    from relax_b200.algo.ppo_utils import Segments
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.orchestration.controller import Controller
+
+    # the term in isolation
+    lp = torch.tensor([-1.0, -2.0, -0.5, -3.0], requires_grad=True)
+    tlp = torch.tensor([-1.5, -1.0, -0.5, -0.5])
+    b = L.LossBatch(seg=Segments.from_lengths([2, 2]), loss_mask=torch.ones(4), advantages=torch.zeros(4),
+                    old_log_probs=lp.detach() - 1.0, extras={"teacher_log_probs": tlp})
+    cfg = L.LossConfig(opd_loss_coef=2.0, opd_kl_type="reverse_kl", opd_per_token_clip=0.75, opd_is_clip=2.0)
+    loss, m = L.policy_loss(lp, torch.zeros(4), b, cfg)
+    d = (lp.detach() - tlp).clamp(max=0.75) * 2.0           # ratio e^1 clipped to 2
+    assert torch.allclose(m["opd_loss"], d.view(2, 2).mean(1).sum()) and float(m["opd_is_clip_frac"]) == 2.0
+    loss.backward()
+    # clipped tokens (0.5 -> only token 0 is below the clip... tokens with d > clip pass no gradient)
+    raw = lp.detach() - tlp
+    assert all((lp.grad[i] == 0) == bool(raw[i] > 0.75) for i in range(4))
+
+    cfgm = get_config("tiny")
+    teacher = GPTModel(cfgm, seed=77)
+    d_ = str(tmp_path / "teacher")
+    H.save_hf_checkpoint(d_, cfgm, H.convert_state_to_hf(cfgm, {k: v.detach() for k, v in teacher.named_parameters()}))
+    base = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+            "--num-rollout", "3", "--rollout-max-response-len", "6", "--use-opd", "--opd-teacher-load", d_, "--lr", "5e-3"]
+    with pytest.raises(ValueError, match="exactly one"):
+        parse_args(base + ["--opd-loss-coef", "1.0", "--opd-kl-coef", "0.3"])
+    a = parse_args(base + ["--opd-loss-coef", "1.0", "--opd-only-reward", "--opd-per-token-clip", "20"])
+    assert a.opd_kl_coef == 0.0
+    c = Controller(a, device="cpu")
+    assert c.runner.actor.cfg.opd_only_reward and c.runner.actor.cfg.loss.opd_loss_coef == 1.0
+    hist = [c.runner.step() for _ in range(3)]
+    assert all("opd_loss" in m and math.isfinite(m["grad_norm"]) for m in hist)
+    assert all(abs(m["rollout/advantages"]) < 1e-6 for m in hist)         # the task reward does not reach the policy
+    assert all(m["pg_loss"] == 0.0 and m["loss"] == pytest.approx(m["opd_loss"], abs=1e-6) for m in hist)   # only the term trains
+    c.runner.close()
