@@ -164,6 +164,7 @@ FLAGS: dict[str, list] = {
         ("--reward-max-concurrency", dict(type=int, default=64)), ("--defer-reward-to-post-process", _b()),
         ("--genrm-model-path", dict(type=str, default=None)), ("--genrm-num-gpus", dict(type=int, default=0)),
         ("--genrm-num-gpus-per-engine", dict(type=int, default=1)),
+        ("--genrm-engine-addrs", dict(type=str, nargs="*", default=None)),     # grader engine servers on their own GPUs
     ],
     "opd": [
         ("--opd-type", dict(type=str, default=None, choices=[None, "sglang", "megatron", "opsd"])),
@@ -296,7 +297,8 @@ FLAG_POLICY: dict[str, tuple] = {
     "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
     "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
-    "--genrm-num-gpus": (_R, "generative reward-model engines share the rollout ranks (--genrm-model-path); they get no GPUs of their own"),
+    "--genrm-num-gpus": (_R, "grader engines either share the rollout ranks (--genrm-model-path) or run as engine servers on their own "
+                             "GPUs, started with `serve engine` and named by --genrm-engine-addrs; this job does not launch them"),
     # operational, no effect here
     "--async-save": (_W, "checkpoints are written synchronously"),
     "--attention-backend": (_W, "there is one attention implementation (tcgen05 flash attention)"),
@@ -355,6 +357,8 @@ def apply_flag_policy(a: argparse.Namespace, parser: Optional[argparse.ArgumentP
             continue
         if flag == "--sglang-dp-size" and val in (None, 1):
             continue
+        if flag == "--genrm-num-gpus" and getattr(a, "genrm_engine_addrs", None):
+            continue            # the GPUs are the ones behind the named servers
         msg = f"{flag}={val!r} is accepted for recipe compatibility but not implemented here" + (f": {why}" if why else "")
         if kind == _R:
             raise ValueError(msg)

@@ -270,7 +270,16 @@ class Controller:
                 eval_max_response_len=_get(a, "eval_max_response_len", None),
                 eval_reward_key=_get(a, "eval_reward_key", None) or _get(a, "reward_key", None))
             run = ColocatedGRPO(cfg, device=self.device)
-            if _get(a, "genrm_model_path", None):
+            if _get(a, "genrm_engine_addrs", None):
+                # graders on their own engine servers (their own GPUs): nothing of theirs lives in this process
+                from ..data.tokenizer import build_codec
+                from ..rewards.genrm import build_remote_genrm
+
+                gcodec = run.codec or build_codec(_get(a, "genrm_model_path", None) or _get(a, "hf_checkpoint", None), self.model_cfg.vocab_size)
+                grm = build_remote_genrm(a.genrm_engine_addrs, gcodec)
+                detok = run.codec.decode if run.codec is not None else (lambda ids: "")
+                run.reward_fn, run.genrm = grm.reward_fn(detok), grm
+            elif _get(a, "genrm_model_path", None):
                 # generative reward model on in-house engines that share this rank's GPU (relax/components/genrm.py)
                 from ..rewards.genrm import build_genrm
 

@@ -122,3 +122,16 @@ def build_genrm(model_path: str, device, num_engines: int = 1, max_new_tokens: i
             eng.weights.flat.copy_((torch.randn(eng.weights.numel, generator=g) * 0.02).to(dt))
         engines.append(engine_judge(eng, codec))
     return GenRM(engines, max_new_tokens=max_new_tokens)
+
+
+def build_remote_genrm(addrs: Sequence[str], codec, max_new_tokens: int = 64, timeout_s: float = 600.0) -> GenRM:
+    """``--genrm-engine-addrs``: graders on engine servers of their own (``serve engine --hf-checkpoint <grader>`` on the
+    GPUs set aside for them; the reference places its grader engines on ``--genrm-num-gpus`` dedicated GPUs,
+    relax/distributed/ray/genrm.py).  Requests rotate over the servers; one that fails is skipped until it answers
+    a probe again (:meth:`GenRM.recover`)."""
+    from ..rollout.http_server import HTTPEngine
+
+    if not addrs:
+        raise ValueError("no grader address given")
+    engines = [engine_judge(HTTPEngine(a if "://" in a else f"http://{a}", timeout_s), codec) for a in addrs]
+    return GenRM(engines, max_new_tokens=max_new_tokens)

@@ -256,3 +256,35 @@ def test_rollout_function_brings_its_own_prompts_without_a_global_dataset(tmp_pa
     m = c.runner.step()
     assert m["raw_reward_mean"] == 0.5 and c.runner.data_source.group_index == 2
     c.runner.close()
+
+
+def test_graders_on_their_own_engine_servers():
+    """``--genrm-engine-addrs``: the generative reward model runs on engine servers of its own; a dead server is
+    skipped and the rewards still arrive; the training job holds no grader weights."""
+    import torch
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.config import get_config
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.engine import RolloutEngine
+    from relax_b200.rollout.http_server import EngineServer
+
+    cfg = get_config("tiny")
+    alive = EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=256, block_size=16, seed=3))
+    dead = EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=32, block_size=16, seed=4))
+    dead_addr = dead.url.replace("http://", "")
+    dead.close()
+    try:
+        with pytest.raises(ValueError, match="genrm-num-gpus"):
+            parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--genrm-num-gpus", "2"])
+        a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2",
+                        "--global-batch-size", "4", "--num-rollout", "1", "--rollout-max-response-len", "4", "--rollout-max-prompt-len", "16",
+                        "--genrm-num-gpus", "2", "--genrm-engine-addrs", dead_addr, alive.url.replace("http://", "")])
+        c = Controller(a, device="cpu")
+        assert len(c.runner.genrm.engines) == 2
+        m = c.runner.step()
+        assert alive.served >= 4 and "loss" in m            # every sample was graded by the server that is up
+        assert sum(e.healthy for e in c.runner.genrm.engines) == 1
+        c.runner.close()
+    finally:
+        alive.close()
