@@ -292,7 +292,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--defer-reward-to-post-process": (_R, "rewards are computed when a sample finishes"),
     "--agentic-tool-call-parser": (_R, "the chat endpoint returns the model's text; tool calls are parsed by the agent"),
     "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
     "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),

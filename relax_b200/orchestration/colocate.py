@@ -123,6 +123,7 @@ class ColocateConfig:
     # fn(args_like, samples) marks samples with remove_sample = True (their loss mask is zeroed);
     # fn(args_like, samples) may rewrite the samples of a rollout before they are converted
     custom_reward_post_process_path: Optional[str] = None
+    defer_reward_to_post_process: bool = False      # samples are not scored when they finish; the post-process scores the batch
     rollout_sample_filter_path: Optional[str] = None
     rollout_data_postprocess_path: Optional[str] = None
     log_passrate: bool = False                      # rollout/pass@k over the training groups (reward > 0.5 = correct)
@@ -373,6 +374,12 @@ class ColocatedGRPO:
 
         self.reward_fn = load_function(cfg.custom_rm_path, 1, "reward function") if cfg.custom_rm_path \
             else get_reward_spec(cfg.rm_type).fn
+        if cfg.defer_reward_to_post_process:
+            # relax/utils/arguments.py:2381-2390: with --rm-type dummy and a post-process function that owns the grader
+            # (wakes it, scores the whole batch, puts it back to sleep) nothing is scored sample by sample
+            if not cfg.custom_reward_post_process_path:
+                raise ValueError("--defer-reward-to-post-process needs --custom-reward-post-process-path (the function that scores the batch)")
+            self.reward_fn = lambda s: 0.0
         self.custom_generate = load_generate_function(cfg.custom_generate_function_path, None)
         self.rollout_function = load_function(cfg.rollout_function_path, 3, "rollout function") if cfg.rollout_function_path else None
         self.group_filter = load_function(cfg.dynamic_sampling_filter_path, 1, "group filter") \

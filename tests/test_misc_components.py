@@ -288,3 +288,29 @@ def test_graders_on_their_own_engine_servers():
         c.runner.close()
     finally:
         alive.close()
+
+
+def test_rewards_deferred_to_the_post_process(tmp_path):
+    """``--defer-reward-to-post-process``: no per-sample scoring; the batch-level function sets raw and shaped rewards."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "post.py"
+    f.write_text(
+        "import torch\n"
+        "SEEN = []\n"
+        "def post(samples):\n"
+        "    SEEN.append([s.reward for s in samples])\n"
+        "    raw = torch.tensor([float(len(s.tokens) % 3) for s in samples])\n"
+        "    return raw, raw - raw.mean()\n")
+    base = ["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+            "--num-rollout", "1", "--rollout-max-response-len", "4", "--defer-reward-to-post-process"]
+    with pytest.raises(ValueError, match="custom-reward-post-process-path"):
+        Controller(parse_args(base), device="cpu")
+    c = Controller(parse_args(base + ["--custom-reward-post-process-path", f"{f}:post"]), device="cpu")
+    m = c.runner.step()
+    import sys
+
+    mod = [v for k, v in sys.modules.items() if k.startswith("relax_b200_user_") and hasattr(v, "SEEN")][-1]
+    assert mod.SEEN == [[0.0] * 4] and "loss" in m
+    c.runner.close()
