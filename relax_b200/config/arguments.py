@@ -292,8 +292,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--agentic-tool-call-parser": (_R, "the chat endpoint returns the model's text; tool calls are parsed by the agent"),
-    "--agentic-reasoning-parser": (_R, "the chat endpoint returns the model's text; reasoning is not split off"),
     "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
     "--genrm-num-gpus": (_R, "grader engines either share the rollout ranks (--genrm-model-path) or run as engine servers on their own "
@@ -530,6 +528,12 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
         if a.custom_generate_function_path:
             raise ValueError("--use-agentic-rollout installs its own generate function; drop --custom-generate-function-path")
         a.custom_generate_function_path = "relax_b200.rollout.agent_pipeline:command_generate"
+        from ..rollout.openai_api import parse_tool_calls, split_reasoning
+
+        if a.agentic_tool_call_parser:
+            parse_tool_calls("", a.agentic_tool_call_parser)         # unknown names stop here, not in the first rollout
+        if a.agentic_reasoning_parser:
+            split_reasoning("", a.agentic_reasoning_parser)
         if a.agentic_concurrency is None:
             a.agentic_concurrency = getattr(a, "over_sampling_batch_size", None) or a.rollout_batch_size or 32
     if (a.num_iters_per_train_update or 1) > 1:

@@ -38,11 +38,13 @@ from .agentic import Tokenizer
 class AgentPipeline:
     def __init__(self, spec: AgentSpec, tok: Tokenizer, concurrency: int = 32, admission: bool = True,
                  admission_headroom: float = 0.9, admission_pressure: float = 0.92, admission_max_wait_s: float = 30.0,
-                 max_context: Optional[int] = None, socket_path: Optional[str] = None, rollout_mode: str = "train"):
+                 max_context: Optional[int] = None, socket_path: Optional[str] = None, rollout_mode: str = "train",
+                 tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None):
         self.spec, self.tok, self.concurrency = spec, tok, max(1, int(concurrency))
         self.use_admission, self.headroom = admission, admission_headroom
         self.pressure, self.max_wait_s = admission_pressure, admission_max_wait_s
         self.max_context, self.socket_path, self.rollout_mode = max_context, socket_path, rollout_mode
+        self.tool_call_parser, self.reasoning_parser = tool_call_parser, reasoning_parser
         self.stats: Dict[str, float] = {}
         self._seq = itertools.count(1)
 
@@ -65,7 +67,8 @@ class AgentPipeline:
 
         backend = EngineServer(engine, http=False)
         chat = ChatService(backend.generate_fn(sampling), self.tok, max_context=self.max_context or getattr(engine, "max_model_len", None) or 8192,
-                           concurrent=True, admission=adm, on_gate=on_gate)
+                           concurrent=True, admission=adm, on_gate=on_gate, tool_call_parser=self.tool_call_parser,
+                           reasoning_parser=self.reasoning_parser)
         httpd, url = serve(chat)
         launcher = AgentLauncher(self.spec, url, self.socket_path)
         t0 = time.perf_counter()
@@ -185,7 +188,8 @@ def configure(args, codec=None) -> AgentPipeline:
             AgentSpec.from_args(args), tok, concurrency=g("agentic_concurrency", 32),
             admission=bool(g("agentic_program_admission", False)), admission_headroom=g("agentic_admission_headroom", 0.9),
             admission_pressure=g("agentic_admission_pressure_threshold", 0.92), admission_max_wait_s=g("agentic_admission_max_wait_s", 30.0),
-            socket_path=ensure_launcher_daemon())
+            socket_path=ensure_launcher_daemon(), tool_call_parser=g("agentic_tool_call_parser", None),
+            reasoning_parser=g("agentic_reasoning_parser", None))
     return _PIPELINE
 
 

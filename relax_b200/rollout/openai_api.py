@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import contextlib
 import json
+import re
 import threading
 import time
 import uuid
@@ -18,9 +19,78 @@ from typing import Dict, Optional
 from .agentic import GenerateFn, Session, SessionForest, Tokenizer
 
 
+# --------------------------------------------------------------------------- parsers of the model's text
+_TOOL_TAG = re.compile(r"<tool_call>\s*(\{.*?\})\s*</tool_call>", re.S)
+
+
+def parse_tool_calls(text: str, parser: str):
+    """``(content, tool_calls)``: calls the model wrote in the format of ``parser`` are cut out of the text.
+    ``hermes`` / ``qwen`` / ``qwen25``: ``<tool_call>{"name": ..., "arguments": {...}}</tool_call>`` blocks;
+    ``json``: the whole reply is one ``{"name": ..., "arguments"|"parameters": ...}`` object (Llama-3 style).
+    A block that is not valid JSON stays in the content (the agent sees what the model wrote)."""
+    calls = []
+    if parser in ("hermes", "qwen", "qwen25", "qwen3"):
+        def take(m):
+            try:
+                obj = json.loads(m.group(1))
+                if not isinstance(obj, dict) or "name" not in obj:
+                    return m.group(0)
+            except ValueError:
+                return m.group(0)
+            calls.append(obj)
+            return ""
+
+        text = _TOOL_TAG.sub(take, text)
+    elif parser in ("json", "llama3"):
+        try:
+            obj = json.loads(text.strip())
+            if isinstance(obj, dict) and "name" in obj:
+                calls.append(obj)
+                text = ""
+        except ValueError:
+            pass
+    else:
+        raise ValueError(f"unknown tool-call parser {parser!r} (hermes, qwen, qwen25, qwen3, json, llama3)")
+    out = []
+    for c in calls:
+        args = c.get("arguments", c.get("parameters", {}))
+        out.append({"id": "call_" + uuid.uuid4().hex[:24], "type": "function",
+                    "function": {"name": str(c["name"]), "arguments": args if isinstance(args, str) else json.dumps(args)}})
+    return text.strip() if out else text, out
+
+
+def split_reasoning(text: str, parser: str):
+    """``(reasoning, rest)`` for models that think inside ``<think> ... </think>`` (``qwen3``, ``deepseek-r1``); an
+    unterminated block (the reply was cut off while thinking) is all reasoning."""
+    if parser not in ("qwen3", "deepseek-r1", "deepseek_r1", "think"):
+        raise ValueError(f"unknown reasoning parser {parser!r} (qwen3, deepseek-r1)")
+    t = text.lstrip()
+    if t.startswith("<think>"):
+        t = t[len("<think>"):]
+    elif "</think>" not in t:
+        return None, text
+    if "</think>" in t:
+        a, b = t.split("</think>", 1)
+        return a.strip(), b.lstrip("\n")
+    return t.strip(), ""
+
+
+def _calls_sig(tool_calls) -> str:
+    """What identifies the tool calls of a message when a client sends it back."""
+    if not tool_calls:
+        return ""
+    out = []
+    for c in tool_calls:
+        f = c.get("function", c)
+        a = f.get("arguments", "")
+        out.append((f.get("name"), a if isinstance(a, str) else json.dumps(a)))
+    return json.dumps(out)
+
+
 class ChatService:
     def __init__(self, generate: GenerateFn, tok: Tokenizer, model_name: str = "relax-b200-policy", max_context: int = 8192,
-                 permits=None, abort_check=None, concurrent: bool = False, admission=None, on_gate=None):
+                 permits=None, abort_check=None, concurrent: bool = False, admission=None, on_gate=None,
+                 tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None):
         """``concurrent``: ``generate`` may be called from several threads at once (a batching backend joins the calls
         into one running batch), so only the session bookkeeping is serialised - needed when many agent processes talk
         to the endpoint.  ``admission`` (:class:`~relax_b200.rollout.admission.AdmissionController`): every completion
@@ -29,6 +99,9 @@ class ChatService:
         stops waiting for its lease (the owner pauses the agent's time budget meanwhile)."""
         self.generate, self.tok, self.model_name, self.max_context = generate, tok, model_name, max_context
         self.concurrent, self.admission, self.on_gate = concurrent, admission, on_gate
+        # --agentic-tool-call-parser / --agentic-reasoning-parser: how replies are split into content, tool calls and
+        # reasoning for the client (the recorded tokens are always the model's full text)
+        self.tool_call_parser, self.reasoning_parser = tool_call_parser, reasoning_parser
         self._busy: Dict[int, threading.Lock] = {}
         self._history: Dict[int, list] = {}       # session id -> [(role, content)] as exchanged with the client
         mark = "\x00"
@@ -41,24 +114,33 @@ class ChatService:
         self.by_key: Dict[str, Session] = {}
         self._lock = threading.Lock()   # the engine is single-consumer
 
-    def _session(self, key: Optional[str], messages: list) -> Session:
+    def _session(self, key: Optional[str], messages: list, tools=None) -> Session:
         """The session a request belongs to.  A request continues a known conversation when its message list starts
         with the messages already seen (compared as text, replies as they were returned): then the tokens kept for
         that part - the generated ones included, whose text need not re-tokenise to the same ids - stay, and only the
         new messages are rendered and appended."""
-        turns = [(m["role"], m.get("content") or "") for m in messages]
+        turns = [(m["role"], m.get("content") or "", _calls_sig(m.get("tool_calls"))) for m in messages]
+
+        def render(t):
+            role, content, calls = t
+            if calls:         # an assistant turn with tool calls that did not come from this session's own tokens
+                content += "".join(f'\n<tool_call>{json.dumps({"name": n, "arguments": a})}</tool_call>' for n, a in json.loads(calls))
+            return self.tok.render_turn(role, content)
+
         s = self.by_key.get(key) if key else None
         if s is not None:
             h = self._history.get(s.sid, [])
             if len(turns) > len(h) and turns[:len(h)] == h:
                 text = self._turn_end if (h and h[-1][0] == "assistant") else ""
-                text += "".join(self.tok.render_turn(r, c) for r, c in turns[len(h):]) + self.tok.generation_prompt
+                text += "".join(render(t) for t in turns[len(h):]) + self.tok.generation_prompt
                 s.append(self.tok.encode(text), 0)
                 self._history[s.sid] = turns
                 return s
         prompt = []
-        for r, c in turns:
-            prompt += self.tok.encode(self.tok.render_turn(r, c))
+        if tools:
+            prompt += self.tok.encode(self.tok.render_turn("tools", json.dumps(tools, sort_keys=True)))
+        for t in turns:
+            prompt += self.tok.encode(render(t))
         prompt += self.tok.encode(self.tok.generation_prompt)
         s = self.forest.new()
         s.append(prompt, 0)
@@ -76,17 +158,19 @@ class ChatService:
         max_new = int(body.get("max_tokens") or body.get("max_completion_tokens") or 256)
         gate = self.permits.permit(self.abort_check) if self.permits is not None else contextlib.nullcontext()
         key = session_key or body.get("user")
+        tools = body.get("tools") or None
         if not self.concurrent:
             with gate, self._lock:
-                s, outs = self._complete(key, msgs, n, max_new)
+                s, outs, first = self._complete(key, msgs, n, max_new, tools)
         else:
             with gate:
-                s, outs = self._complete(key, msgs, n, max_new)
+                s, outs, first = self._complete(key, msgs, n, max_new, tools)
         toks = outs[0][0]
         choices = []
         for i, (t, lp, r, _) in enumerate(outs):
-            c = {"index": i, "message": {"role": "assistant", "content": self.tok.decode(t)},
-                 "finish_reason": "length" if r == "length" else "stop"}
+            msg = first if i == 0 else self._message(self.tok.decode(t), bool(tools))
+            c = {"index": i, "message": msg,
+                 "finish_reason": "length" if r == "length" else ("tool_calls" if msg.get("tool_calls") else "stop")}
             if body.get("logprobs"):
                 c["logprobs"] = {"content": [{"token": self.tok.decode([a]), "logprob": b} for a, b in zip(t, lp)]}
             choices.append(c)
@@ -96,15 +180,28 @@ class ChatService:
                 "usage": {"prompt_tokens": ptoks, "completion_tokens": sum(len(o[0]) for o in outs),
                           "total_tokens": ptoks + sum(len(o[0]) for o in outs)}}
 
-    def _complete(self, key, msgs, n: int, max_new: int):
+    def _message(self, text: str, has_tools: bool) -> dict:
+        """The assistant message a client receives for the model's ``text``."""
+        msg = {"role": "assistant", "content": text}
+        if self.reasoning_parser:
+            thought, rest = split_reasoning(text, self.reasoning_parser)
+            if thought is not None:
+                msg["reasoning_content"], msg["content"] = thought, rest
+        if self.tool_call_parser and has_tools:
+            content, calls = parse_tool_calls(msg["content"], self.tool_call_parser)
+            if calls:
+                msg["content"], msg["tool_calls"] = (content or None), calls
+        return msg
+
+    def _complete(self, key, msgs, n: int, max_new: int, tools=None):
         """Session lookup, lease, generation, bookkeeping.  In concurrent mode the service lock covers only the
         bookkeeping; two requests of the SAME session still run one after the other."""
         if self.concurrent:
             with self._lock:
-                s = self._session(key, msgs)
+                s = self._session(key, msgs, tools)
                 busy = self._busy.setdefault(s.sid, threading.Lock())
         else:
-            s, busy = self._session(key, msgs), contextlib.nullcontext()
+            s, busy = self._session(key, msgs, tools), contextlib.nullcontext()
         with busy:
             room = self.max_context - len(s.tokens)
             if room <= 0:
@@ -131,10 +228,12 @@ class ChatService:
                 s.append(toks, 1, lps)
                 s.weight_versions += versions
                 s.turns += 1
-                self._history.setdefault(s.sid, []).append(("assistant", self.tok.decode(toks)))
+                first = self._message(self.tok.decode(toks), bool(tools))
+                # the client sends back what it received: that, not the raw text, identifies the turn
+                self._history.setdefault(s.sid, []).append(("assistant", first.get("content") or "", _calls_sig(first.get("tool_calls"))))
                 if reason == "length" and budget == room:
                     s.truncated = True
-        return s, outs
+        return s, outs, first
 
     def finish_session(self, key: str, reward: float = 0.0):
         """Close a conversation and return it as a training sample."""

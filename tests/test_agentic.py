@@ -255,3 +255,46 @@ def test_episodes_run_under_admission_control():
     assert len(out) == 6 and all(s.done and s.turns == 2 for s in out)
     m = ac.metrics()
     assert max(calls) <= 2 and m["peak_reserved"] <= 600 and m["reserved"] == 0 and m["granted"] == 6
+
+
+def test_tool_call_and_reasoning_parsers_and_a_tool_using_session():
+    from relax_b200.rollout.openai_api import parse_tool_calls, split_reasoning
+
+    text = 'Let me look.\n<tool_call>\n{"name": "search", "arguments": {"q": "b200"}}\n</tool_call><tool_call>{"name": "open", "arguments": "{\\"id\\": 3}"}</tool_call>'
+    content, calls = parse_tool_calls(text, "hermes")
+    assert content == "Let me look." and [c["function"]["name"] for c in calls] == ["search", "open"]
+    assert json.loads(calls[0]["function"]["arguments"]) == {"q": "b200"} and calls[1]["function"]["arguments"] == '{"id": 3}'
+    assert parse_tool_calls("<tool_call>{broken</tool_call>", "qwen")[1] == []
+    assert parse_tool_calls('{"name": "f", "parameters": {"x": 1}}', "llama3")[1][0]["function"]["arguments"] == '{"x": 1}'
+    assert split_reasoning("<think>step 1\nstep 2</think>\n\nThe answer is 4.", "qwen3") == ("step 1\nstep 2", "The answer is 4.")
+    assert split_reasoning("<think>cut off while thin", "deepseek-r1") == ("cut off while thin", "")
+    assert split_reasoning("no thoughts here", "qwen3") == (None, "no thoughts here")
+    with pytest.raises(ValueError):
+        parse_tool_calls("x", "nope")
+
+    # a scripted policy: thinks, calls a tool, then answers; the session keeps one token stream through both requests
+    script = iter(['<think>need data</think><tool_call>{"name": "lookup", "arguments": {"k": 1}}</tool_call>', "It is 42."])
+
+    def gen(prompts, max_new, keys):
+        t = next(script)
+        return [(TOK.encode(t), [-0.5] * len(TOK.encode(t)), "stop", [7]) for _ in prompts]
+
+    svc = ChatService(gen, TOK, tool_call_parser="hermes", reasoning_parser="qwen3")
+    tools = [{"type": "function", "function": {"name": "lookup", "parameters": {"type": "object"}}}]
+    msgs = [{"role": "user", "content": "what is k?"}]
+    r1 = svc.chat({"messages": msgs, "tools": tools}, session_key="s")
+    m1 = r1["choices"][0]["message"]
+    assert r1["choices"][0]["finish_reason"] == "tool_calls" and m1["content"] is None and m1["reasoning_content"] == "need data"
+    assert m1["tool_calls"][0]["function"] == {"name": "lookup", "arguments": '{"k": 1}'}
+    # the client echoes the assistant message (without the reasoning) and adds the tool's result
+    msgs += [{"role": "assistant", "content": None, "tool_calls": m1["tool_calls"]},
+             {"role": "tool", "tool_call_id": m1["tool_calls"][0]["id"], "content": "k = 42"}]
+    r2 = svc.chat({"messages": msgs, "tools": tools}, session_key="s")
+    assert r2["choices"][0]["message"]["content"] == "It is 42." and r2["choices"][0]["finish_reason"] == "stop"
+    smp = svc.finish_session("s", reward=1.0)
+    full = TOK.decode(smp.tokens)
+    assert len(svc.forest.sessions) == 1 and smp.weight_versions == [7]          # ONE session: the echo was recognised
+    assert "<think>need data</think><tool_call>" in full and "k = 42" in full and full.rstrip().endswith("It is 42.")
+    assert '"lookup"' in full.split("what is k?")[0]                              # the tool list is part of the prompt
+    gen_text = TOK.decode([t for t, m_ in zip(smp.tokens[-smp.response_length:], smp.loss_mask) if m_])
+    assert gen_text == '<think>need data</think><tool_call>{"name": "lookup", "arguments": {"k": 1}}</tool_call>It is 42.'
