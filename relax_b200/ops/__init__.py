@@ -191,7 +191,12 @@ def qkv_post(qkv, nq, nkv, q_norm_w, k_norm_w, cos, sin, eps, k_cache=None, v_ca
     v = qkv[:, (nq + nkv) * hd:].reshape(T, nkv, hd)
     if q_norm_w is not None:
         q, k = rmsnorm(q, q_norm_w, eps), rmsnorm(k, k_norm_w, eps)
-    q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+    rot = 2 * cos.shape[-1]
+    if rot < hd:      # partial rotary (GLM-4, Qwen3.5): only the first ``rot`` dims of every head turn
+        q = torch.cat([apply_rope(q[..., :rot].contiguous(), cos, sin), q[..., rot:]], -1)
+        k = torch.cat([apply_rope(k[..., :rot].contiguous(), cos, sin), k[..., rot:]], -1)
+    else:
+        q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
     if slots is not None:
         kv_cache_write(k, v, k_cache, v_cache, slots)
     return (q, k, v.contiguous()) if dense_kv else (q, None, None)

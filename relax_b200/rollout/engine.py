@@ -126,8 +126,9 @@ class RolloutEngine(SpeculativeMixin):
         if self.speculative:
             if cfg.mtp_num_layers < 1:
                 raise ValueError("speculative decoding drafts with the model's multi-token-prediction block; this model has none")
-            if cfg.vision is not None or (return_routed_experts and cfg.is_moe):
-                raise NotImplementedError("speculative decoding serves text prompts and does not record routed experts")
+            if cfg.vision is not None or (return_routed_experts and cfg.is_moe) or cfg.linear_attention_freq > 0:
+                raise NotImplementedError("speculative decoding serves text prompts of softmax-attention models and does not "
+                                          "record routed experts")
         self.tp = tp or GroupInfo(None, (0,), 0)
         self.device = torch.device(device)
         self.dtype = dtype or {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
@@ -169,6 +170,12 @@ class RolloutEngine(SpeculativeMixin):
         self.windowed_decode = self.use_cuda_graph if windowed_decode is None else bool(windowed_decode)
         if self.speculative:
             self.windowed_decode = False     # the rows per request change from step to step: host-driven iterations
+        # hybrid stacks: Gated-DeltaNet layers keep a convolution window and a recurrent matrix per request
+        # (Request._gdn: layer -> [window, matrix]) next to the paged K/V of the softmax layers; host-driven decode
+        self.hybrid = cfg.linear_attention_freq > 0
+        if self.hybrid:
+            self.windowed_decode = False
+            self.use_cuda_graph = False
         if os.environ.get("RELAX_B200_FORCE_REFERENCE", "0") == "1" and self.device.type == "cuda":
             self.windowed_decode = False     # the library-path arm keeps the host-driven loop
         self._graphs = {}
@@ -442,6 +449,8 @@ class RolloutEngine(SpeculativeMixin):
             if self.return_routed_experts:
                 self.weights.routing_capture = []
             h_all = None
+            if self.hybrid:
+                self.weights.seq_ctx = {"mode": "prefill", "cu": list(cu), "cu_t": cu_t, "out": {}}
             if self.speculative:
                 logits, h_all = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
                                                              max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), return_hidden=True)
@@ -449,6 +458,11 @@ class RolloutEngine(SpeculativeMixin):
                 logits = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
                                                       max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), image=image)
             self.stats["prefill_tokens"] += len(toks)
+            if self.hybrid:
+                out = self.weights.seq_ctx["out"]
+                for j, r in enumerate(leaders):
+                    r._gdn = {i: out[i][j] for i in out}
+                self.weights.seq_ctx = None
             if self.return_routed_experts:
                 routed = torch.stack(self.weights.routing_capture, 1).tolist()      # [T][L_moe][k]
                 self.weights.routing_capture = None
@@ -466,6 +480,8 @@ class RolloutEngine(SpeculativeMixin):
                     if j < len(r.blocks):
                         self.kv[:, :, r.blocks[j]] = self.kv[:, :, lead.blocks[j]]
                 self.stats["cached_tokens"] += len(r.prompt)
+                if self.hybrid:          # the same prompt leaves the same recurrent state
+                    r._gdn = {i: [c.clone(), S.clone()] for i, (c, S) in lead._gdn.items()}
                 rows.append(row_of[id(lead)])
                 if self.return_routed_experts:
                     r.routed_experts = [list(x) for x in lead.routed_experts[:len(r.prompt)]]
@@ -536,7 +552,16 @@ class RolloutEngine(SpeculativeMixin):
             (bt_rows, torch.int32)])
         if self.return_routed_experts:
             self.weights.routing_capture = []
+        if self.hybrid:
+            layers = list(reqs[0]._gdn)
+            self.weights.seq_ctx = {"mode": "decode", "state": {i: [torch.stack([r._gdn[i][0] for r in reqs]),
+                                                                   torch.stack([r._gdn[i][1] for r in reqs])] for i in layers}}
         logits = self.weights.forward_decode(tok, pos, bt, ctx, slots, self.kv, self.tp)
+        if self.hybrid:
+            st = self.weights.seq_ctx["state"]
+            for j, r in enumerate(reqs):
+                r._gdn = {i: [st[i][0][j], st[i][1][j]] for i in st}
+            self.weights.seq_ctx = None
         if self.return_routed_experts:
             routed = torch.stack(self.weights.routing_capture, 1).tolist()
             self.weights.routing_capture = None

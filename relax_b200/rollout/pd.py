@@ -51,6 +51,8 @@ class PrefilledRequest:
 
 def detach(engine: RolloutEngine, reqs: Sequence[Request]) -> List[PrefilledRequest]:
     """Take ``reqs`` (running on ``engine``, prefilled) out of it together with their KV rows; frees their blocks."""
+    if getattr(engine, "hybrid", False):
+        raise NotImplementedError("the hand-over moves paged K/V; the recurrent state of Gated-DeltaNet layers does not travel yet")
     out = []
     bs = engine.block_size
     for r in reqs:

@@ -28,6 +28,9 @@ from ..models.config import ModelConfig
 from ..parallel.state import GroupInfo
 
 
+GDN_CONV_KERNEL = 4      # taps of the Gated-DeltaNet depth-wise convolution (relax_b200/models/gdn.py)
+
+
 def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = False) -> dict:
     """``mtp``: the buffer also holds the first multi-token-prediction block (draft model of speculative decoding) -
     its transformer layer as layer ``num_layers`` and ``mtp.enorm / mtp.hnorm / mtp.eh_proj / mtp.final_norm`` - AFTER
@@ -38,16 +41,35 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = Fal
     shapes = {"embed": (v_pad // tp, H)}
 
     def layer(i):
+        from ..models.hybrid import mixer_kind
+
         p = f"layers.{i}."
         shapes[p + "input_norm"] = (H,)
+        if mixer_kind(cfg, i) == "gdn":
+            hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+            kd, vd = hk * d, hv * d
+            shapes[p + "gdn_qkvz"] = (2 * kd + 2 * vd, H)
+            shapes[p + "gdn_ba"] = (2 * hv, H)
+            shapes[p + "gdn_conv"] = (2 * kd + vd, GDN_CONV_KERNEL)
+            shapes[p + "gdn_dt_bias"], shapes[p + "gdn_A_log"], shapes[p + "gdn_norm"] = (hv,), (hv,), (d,)
+            shapes[p + "gdn_out"] = (H, vd)
+            return mlp(i, p)
         shapes[p + "qkv"] = ((nq + 2 * nkv) * hd, H)
+        if cfg.attention_output_gate:
+            shapes[p + "attn_gate"] = (nq * hd, H)       # one gate row per query feature (sigmoid on the attention output)
         if cfg.qkv_bias:
             shapes[p + "qkv_bias"] = ((nq + 2 * nkv) * hd,)
         if cfg.qk_layernorm:
             shapes[p + "q_norm"] = (hd,)
             shapes[p + "k_norm"] = (hd,)
         shapes[p + "o"] = (H, nq * hd)
+        mlp(i, p)
+
+    def mlp(i, p):
         shapes[p + "post_norm"] = (H,)
+        if cfg.sandwich_norm:          # GLM-4: the block outputs are normed before they join the residual stream
+            shapes[p + "post_attn_norm"] = (H,)
+            shapes[p + "post_mlp_norm"] = (H,)
         if cfg.is_moe_layer(i):
             el = cfg.num_experts // ep
             shapes[p + "router"] = (cfg.num_experts, H)
@@ -91,12 +113,14 @@ def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = False):
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
                  memory_saver: bool = False, shared_path: Optional[str] = None, mtp: bool = False):
-        if cfg.attention_output_gate or cfg.rotary_percent < 1.0 or cfg.sandwich_norm:
-            raise NotImplementedError("the rollout engine serves plain pre-norm softmax attention; gated attention / partial "
-                                      "rotary (Qwen3.5) and sandwich-norm (GLM-4) models are trainer-side for now")
-        if cfg.dsa_topk > 0 or cfg.linear_attention_freq > 0 or cfg.multi_latent_attention:
-            raise NotImplementedError("the rollout engine serves softmax-attention stacks only; GDN / MLA / DSA layers are "
-                                      "trainer-side (SFT, log-prob evaluation) for now")
+        if cfg.dsa_topk > 0 or cfg.multi_latent_attention:
+            raise NotImplementedError("the rollout engine serves softmax-attention and Gated-DeltaNet layers; MLA / DSA layers "
+                                      "are trainer-side (SFT, log-prob evaluation) for now")
+        if (cfg.linear_attention_freq > 0 or cfg.attention_output_gate) and (tp_size > 1 or ep_size > 1 or mtp):
+            raise NotImplementedError("hybrid stacks (Gated DeltaNet layers, gated attention) run on one rank per engine, "
+                                      "without speculative decoding")
+        if cfg.attention_output_gate and cfg.qkv_bias:
+            raise NotImplementedError("gated attention with a QKV bias")
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
         self.ep_size, self.ep_rank = ep_size, ep_rank
         self.ep_group: Optional[GroupInfo] = None     # the engine's expert-parallel group (set by the engine when ep > 1)
@@ -105,6 +129,7 @@ class RolloutWeights:
         self.routing_capture: Optional[list] = None
         self.moe_layers = [i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)]
         self.device, self.dtype = torch.device(device), dtype
+        self.seq_ctx: Optional[dict] = None      # what the rows of the running forward are (read by the GDN layers)
         self.mtp = bool(mtp)          # the buffer also holds the first MTP block (draft model of speculative decoding)
         if self.mtp and cfg.mtp_num_layers < 1:
             raise ValueError("speculative decoding drafts with the model's multi-token-prediction block; this model has none")
@@ -241,12 +266,73 @@ class RolloutWeights:
             return None
         return comm
 
+    # ------------------------------------------------------------------ Gated DeltaNet layers (hybrid stacks)
+    def _gdn(self, i, x):
+        """The GDN token mixer on rows (relax_b200/models/gdn.py GatedDeltaNet.forward), with the per-sequence state
+        that incremental decoding needs: the last ``K - 1`` pre-convolution rows and the recurrent matrix
+        ``S [hv, dk, dv]`` (fp32).  ``self.seq_ctx`` says what the rows are: whole sequences (``mode = "prefill"``,
+        ``cu`` boundaries; the final states are left in ``ctx["out"][i]``, one pair per sequence) or one new token per
+        sequence (``mode = "decode"``, ``ctx["state"][i] = [conv [B, K-1, C], S [B, hv, dk, dv]]``, updated in place)."""
+        import torch.nn.functional as F
+
+        from ..models.gdn import causal_conv1d_varlen, gated_delta_rule_chunked
+
+        cfg, p, ctx = self.cfg, self.p, self.seq_ctx
+        pre = f"layers.{i}."
+        hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        kd, vd, K = hk * d, hv * d, GDN_CONV_KERNEL
+        T = x.shape[0]
+        qkvz = ops.linear(x, p[pre + "gdn_qkvz"])
+        ba = ops.linear(x, p[pre + "gdn_ba"]).float()
+        raw, z = qkvz[:, : 2 * kd + vd], qkvz[:, 2 * kd + vd:]
+        w = p[pre + "gdn_conv"]
+        if ctx["mode"] == "prefill":
+            qkv = causal_conv1d_varlen(raw, w, ctx["cu_t"])
+        else:
+            conv, _ = ctx["state"][i]
+            win = torch.cat([conv.to(raw.dtype), raw[:, None]], 1)                   # [B, K, C]
+            qkv = F.silu((win.float() * w.float().t()[None]).sum(1)).to(raw.dtype)
+            ctx["state"][i][0] = win[:, 1:]
+        q = F.normalize(qkv[:, :kd].reshape(T, hk, d).float(), dim=-1)
+        k = F.normalize(qkv[:, kd:2 * kd].reshape(T, hk, d).float(), dim=-1)
+        v = qkv[:, 2 * kd:].reshape(T, hv, d)
+        if hv // hk > 1:
+            q, k = q.repeat_interleave(hv // hk, 1), k.repeat_interleave(hv // hk, 1)
+        beta = torch.sigmoid(ba[:, :hv])
+        g = -p[pre + "gdn_A_log"].float().exp() * F.softplus(ba[:, hv:] + p[pre + "gdn_dt_bias"].float())
+        if ctx["mode"] == "prefill":
+            outs, fin = [], []
+            for a, b in zip(ctx["cu"], ctx["cu"][1:]):
+                o_, S = gated_delta_rule_chunked(q[a:b], k[a:b], v[a:b], g[a:b], beta[a:b])
+                tail = raw[max(a, b - (K - 1)):b]
+                if tail.shape[0] < K - 1:
+                    tail = torch.cat([tail.new_zeros(K - 1 - tail.shape[0], tail.shape[1]), tail])
+                outs.append(o_)
+                fin.append([tail.clone(), S])
+            ctx["out"][i] = fin
+            o = torch.cat(outs) if outs else q.new_zeros(0, hv, d)
+        else:
+            S = ctx["state"][i][1]
+            S = S * g.exp()[:, :, None, None]
+            u = (v.float() - torch.einsum("bhkv,bhk->bhv", S, k)) * beta[..., None]
+            S = S + torch.einsum("bhk,bhv->bhkv", k, u)
+            o = torch.einsum("bhkv,bhk->bhv", S, q * d ** -0.5)
+            ctx["state"][i][1] = S
+        o = ops.rmsnorm(o.to(x.dtype), p[pre + "gdn_norm"], cfg.rms_norm_eps) * F.silu(z.reshape(T, hv, d))
+        return ops.linear(o.reshape(T, vd), p[pre + "gdn_out"])
+
     def _layer(self, i, h, x, cos, sin, attn, tp, next_norm, cache):
         """One decoder layer.  ``h`` is the residual stream, ``x`` its normed copy (input of the attention
         block); returns the new ``(h, x)`` where ``x`` is already normed with ``next_norm`` (the next layer's
         input norm or the final norm), so every residual add is fused with the norm that follows it."""
         cfg, p = self.cfg, self.p
         pre = f"layers.{i}."
+        if (pre + "gdn_qkvz") in p:
+            a = self._gdn(i, x)
+            x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
+            m, _ = self._mlp(i, x, tp)
+            x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
+            return h, x
         hd = cfg.head_dim
         nq, nkv = cfg.num_attention_heads // self.tp_size, cfg.num_query_groups // self.tp_size
         qkv = ops.linear(x, p[pre + "qkv"], p.get(pre + "qkv_bias"))
@@ -258,6 +344,21 @@ class RolloutWeights:
                                p.get(pre + "k_norm") if cfg.qk_layernorm else None, cos, sin, cfg.rms_norm_eps,
                                kc[i], vc[i], slots, dense)
         o = attn(i, q, k, v).reshape(T, nq * hd)
+        if cfg.attention_output_gate:      # Qwen3.5: the attention output is gated per feature by a sigmoid of a projection of x
+            o = o * torch.sigmoid(ops.linear(x, p[pre + "attn_gate"]).float()).to(o.dtype)
+        if cfg.sandwich_norm:
+            # h += norm(attention(norm(h))); h += norm(mlp(norm(h))): the extra norms sit between the reduction and the add
+            a = ops.linear(o, p[pre + "o"])
+            if self.lora:
+                a = self._lora_add(pre + "o", o, a)
+            a = ops.rmsnorm(self._allreduce(a, tp), p[pre + "post_attn_norm"], cfg.rms_norm_eps)
+            x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
+            m, reduce_over = self._mlp(i, x, tp)
+            if reduce_over is not None:
+                m = self._allreduce(m, reduce_over)
+            m = ops.rmsnorm(m, p[pre + "post_mlp_norm"], cfg.rms_norm_eps)
+            x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)
+            return h, x
         comm = self._fused(tp, T, cfg.hidden_size) if not self.lora else None     # adapters add to the partial sums: plain path
         if comm is not None:
             h, x = comm.gemm_ar_add_rmsnorm(o, p[pre + "o"], h, p[pre + "post_norm"], cfg.rms_norm_eps)
@@ -283,7 +384,7 @@ class RolloutWeights:
         h = self._embed(tokens, tp)
         if image is not None:      # (rows, embeddings): image placeholder rows take the vision tower's output
             h = h.index_copy(0, image[0], image[1].to(h.dtype))
-        cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        cos, sin = ops.rope_cos_sin(positions, cfg.rotary_dim, cfg.rope_theta, cfg.mrope_section)
         x = ops.rmsnorm(h, p["layers.0.input_norm"], cfg.rms_norm_eps)
         for i in range(cfg.num_layers):
             nxt = p[f"layers.{i + 1}.input_norm"] if i + 1 < cfg.num_layers else p["final_norm"]
@@ -325,7 +426,7 @@ class RolloutWeights:
         emb = self._embed(next_tokens, tp)
         x = torch.cat([ops.rmsnorm(emb, p["mtp.enorm"], eps), ops.rmsnorm(h_prev.to(emb.dtype), p["mtp.hnorm"], eps)], -1)
         h = ops.linear(x, p["mtp.eh_proj"])
-        cos, sin = ops.rope_cos_sin(positions, cfg.head_dim, cfg.rope_theta, cfg.mrope_section)
+        cos, sin = ops.rope_cos_sin(positions, cfg.rotary_dim, cfg.rope_theta, cfg.mrope_section)
         xin = ops.rmsnorm(h, p[f"layers.{L}.input_norm"], eps)
         _, xn = self._layer(L, h, xin, cos, sin, attn, tp, p["mtp.final_norm"], cache)
         return xn

@@ -85,6 +85,8 @@ def _trainer_param_name(layer_local: int, kind: str) -> str:
         "shared_fc1": base + "mlp.shared_experts.linear_fc1.weight",
         "shared_fc2": base + "mlp.shared_experts.linear_fc2.weight",
         "shared_gate": base + "mlp.shared_experts.gate_weight",
+        "post_attn_norm": base + "post_self_attn_layernorm.weight",
+        "post_mlp_norm": base + "post_mlp_layernorm.weight",
     }[kind]
 
 
@@ -147,26 +149,49 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
         else:
             trainer_param_name = _trainer_param_name
         rep(trainer_param_name(ll, "input_norm"), p + "input_norm", H)
-        if cfg.qk_layernorm:
+        from ..models.hybrid import mixer_kind
+
+        gdn_layer = mixer_kind(cfg, layer) == "gdn"
+        if gdn_layer:
+            # Gated DeltaNet mixer: whole tensors (hybrid stacks run with tp = 1 on both sides)
+            if src.tp > 1 or dst_tp > 1:
+                raise NotImplementedError("Gated-DeltaNet layers are synchronised between tp = 1 layouts")
+            hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+            kd, vd = hk * d, hv * d
+            gbase = trainer_param_name(ll, "o").replace("linear_proj.weight", "gdn.")
+            for sname, dname, r_, c_ in (("in_proj_qkvz.weight", "gdn_qkvz", 2 * kd + 2 * vd, H), ("in_proj_ba.weight", "gdn_ba", 2 * hv, H),
+                                        ("conv1d.weight", "gdn_conv", 2 * kd + vd, 4), ("out_proj.weight", "gdn_out", H, vd)):
+                add(BlockCopy(0, gbase + sname, 0, 0, 0, p + dname, 0, 0, r_, c_))
+            rep(gbase + "dt_bias", p + "gdn_dt_bias", hv)
+            rep(gbase + "A_log", p + "gdn_A_log", hv)
+            rep(gbase + "norm.weight", p + "gdn_norm", d)
+        if cfg.sandwich_norm:
+            rep(trainer_param_name(ll, "post_attn_norm"), p + "post_attn_norm", H)
+            rep(trainer_param_name(ll, "post_mlp_norm"), p + "post_mlp_norm", H)
+        if cfg.qk_layernorm and not gdn_layer:
             rep(trainer_param_name(ll, "q_norm"), p + "q_norm", hd)
             rep(trainer_param_name(ll, "k_norm"), p + "k_norm", hd)
-        # QKV: per global group g, three row blocks
+        # QKV: per global group g, three row blocks (with gated attention the group also holds one gate row per query
+        # feature, between its query heads and its key: they go to a tensor of their own)
         nq_d, nkv_d = cfg.num_attention_heads // dst_tp, ng_d
-        for g in range(ng):
+        gate_rows = qpg * hd if cfg.attention_output_gate else 0
+        for g in range(ng if not gdn_layer else 0):
             st, sg = g // ng_s, g % ng_s
             dt, dg = g // ng_d, g % ng_d
-            sbase = sg * grp_rows
+            sbase = sg * (grp_rows + gate_rows)
             blocks = (
                 (sbase, dg * qpg * hd, qpg * hd),                      # q heads of the group
-                (sbase + qpg * hd, nq_d * hd + dg * hd, hd),           # k
-                (sbase + (qpg + 1) * hd, (nq_d + nkv_d) * hd + dg * hd, hd),  # v
+                (sbase + gate_rows + qpg * hd, nq_d * hd + dg * hd, hd),           # k
+                (sbase + gate_rows + (qpg + 1) * hd, (nq_d + nkv_d) * hd + dg * hd, hd),  # v
             )
             for srow, drow, n in blocks:
                 add(BlockCopy(st, trainer_param_name(ll, "qkv"), srow, 0, dt, p + "qkv", drow, 0, n, H))
                 if cfg.qkv_bias:
                     add(BlockCopy(st, trainer_param_name(ll, "qkv_bias"), 0, srow, dt, p + "qkv_bias", 0, drow, 1, n))
+            if gate_rows:
+                add(BlockCopy(st, trainer_param_name(ll, "qkv"), sbase + qpg * hd, 0, dt, p + "attn_gate", dg * qpg * hd, 0, gate_rows, H))
         # o_proj: column sharded
-        for sp, so, dp, do, n in _row_sharded(cfg.q_size, src.tp, dst_tp):
+        for sp, so, dp, do, n in (_row_sharded(cfg.q_size, src.tp, dst_tp) if not gdn_layer else ()):
             add(BlockCopy(sp, trainer_param_name(ll, "o"), 0, so, dp, p + "o", 0, do, H, n))
         is_moe = cfg.is_moe_layer(layer)
         if is_moe:

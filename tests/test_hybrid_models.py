@@ -56,11 +56,15 @@ def test_sft_learns(preset):
         assert "indexer_loss" in m and m["indexer_loss"] >= 0
 
 
-def test_rollout_engine_refuses_hybrid_stacks():
+def test_rollout_engine_refuses_what_it_does_not_serve():
     from relax_b200.rollout.weights import RolloutWeights
 
-    with pytest.raises(NotImplementedError):
-        RolloutWeights(get_config("tiny-next"), 1, 0, "cpu", torch.float32)
+    for name in ("tiny-dsa", "tiny-mla"):
+        with pytest.raises(NotImplementedError):
+            RolloutWeights(get_config(name), 1, 0, "cpu", torch.float32)
+    with pytest.raises(NotImplementedError):          # hybrid stacks: one rank per engine
+        RolloutWeights(get_config("tiny-next"), 2, 0, "cpu", torch.float32)
+    RolloutWeights(get_config("tiny-next"), 1, 0, "cpu", torch.float32)
 
 
 def test_mla_preset_trains_and_big_presets_resolve():
@@ -179,3 +183,80 @@ def test_glm4_style_sandwich_norms_and_half_rotary():
     assert "model.layers.1.post_self_attn_layernorm.weight" in hf
     back = HF.hf_to_megatron_state(cfg, hf)
     assert all(torch.equal(back[k], v) for k, v in state.items())
+
+
+def test_glm4_dense_runs_in_the_rollout_engine_and_the_rl_loop():
+    """Sandwich norms and half rotary in the ENGINE: the engine's log-probs of its own samples equal the trainer's, so
+    GLM-4 dense models can be trained with RL (not only evaluated trainer-side)."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    a = parse_args(["--model-name", "tiny-glm4", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                    "--global-batch-size", "8", "--num-rollout", "2", "--rollout-max-response-len", "8", "--lr", "1e-3",
+                    "--rm-type", "token_sum_parity"])
+    c = Controller(a, device="cpu")
+    cfg = c.runner.cfg.model
+    assert cfg.sandwich_norm and cfg.rotary_dim < cfg.head_dim
+    assert "layers.0.post_attn_norm" in c.runner.engine.weights.p and "layers.1.post_mlp_norm" in c.runner.engine.weights.p
+    for _ in range(2):
+        m = c.runner.step()
+        assert m["train_rollout_logprob_abs_diff"] < 1e-4, m["train_rollout_logprob_abs_diff"]
+    c.runner.close()
+
+
+def test_hybrid_stack_in_the_rollout_engine_matches_the_trainer():
+    """Gated-DeltaNet layers and gated attention in the ENGINE: incremental decoding with the per-request convolution
+    window and recurrent matrix gives the tokens and log-probs of a full recomputation by the trainer's model, for
+    leaders, followers of a shared prompt, and a request resumed from a partial output."""
+    from relax_b200.models.config import get_config
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+    from relax_b200.weight_sync.plan import TrainerLayout
+    from relax_b200.weight_sync.sync import WeightSync
+
+    cfg = get_config("tiny-qwen35")
+    model = GPTModel(cfg, seed=5)
+    eng = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8)
+    assert eng.hybrid and not eng.windowed_decode
+    WeightSync(cfg, TrainerLayout(tp=1), 1, [0], [0]).update_weights({k: v.detach() for k, v in model.named_parameters()}, eng.weights, eng, version=1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (2, 7, 19)]
+    prompts.append(list(prompts[2]))
+    out = eng.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=9), group_keys=[0, 1, 2, 2])
+
+    def trainer_greedy(seq, n):
+        lps = []
+        seq = list(seq)
+        for _ in range(n):
+            t = torch.tensor(seq)
+            with torch.no_grad():
+                h = model(t, torch.arange(len(seq)), torch.tensor([0, len(seq)], dtype=torch.int32), max_seqlen=len(seq))
+                lp = torch.log_softmax(h[-1].float() @ model.lm_head_weight()[:cfg.vocab_size].float().t(), -1)
+            seq.append(int(lp.argmax()))
+            lps.append(float(lp.max()))
+        return seq, lps
+
+    for p_, r in zip(prompts, out):
+        seq, lps = trainer_greedy(p_, 9)
+        assert r.output == seq[len(p_):]          # (the log-probs are compared under sampling by the loop test below)
+    # partial rollout: a request resumed with half of its output continues to the same end
+    rid = eng.add_request(prompts[1], SamplingParams(temperature=0.0, max_new_tokens=9), resume_output=out[1].output[:4],
+                          resume_logprobs=out[1].logprobs[:4])
+    done = []
+    while eng.has_work:
+        done += eng.step()
+    assert done[0].rid == rid and done[0].output == out[1].output
+
+
+def test_qwen35_style_hybrid_model_in_the_rl_loop():
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    a = parse_args(["--model-name", "tiny-qwen35", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                    "--global-batch-size", "8", "--num-rollout", "2", "--rollout-max-response-len", "6", "--lr", "1e-3",
+                    "--rm-type", "token_sum_parity"])
+    c = Controller(a, device="cpu")
+    for _ in range(2):
+        m = c.runner.step()
+        assert m["train_rollout_logprob_abs_diff"] < 1e-4, m["train_rollout_logprob_abs_diff"]
+    c.runner.close()
