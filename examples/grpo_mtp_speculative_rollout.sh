@@ -8,6 +8,6 @@ python -m relax_b200.entrypoints.train \
   --rollout-batch-size 4 --n-samples-per-prompt 4 --global-batch-size 16 \
   --rollout-max-response-len 16 --num-rollout 3 --lr 1e-4 --rm-type token_sum_parity \
   --mtp-num-layers 1 --enable-mtp-training --mtp-loss-scaling-factor 0.3 \
-  --sglang-speculative-algorithm EAGLE --sglang-speculative-num-steps 1 \
-  --sglang-speculative-eagle-topk 1 --sglang-speculative-num-draft-tokens 2 \
+  --sglang-speculative-algorithm EAGLE --sglang-speculative-num-steps 2 \
+  --sglang-speculative-eagle-topk 1 --sglang-speculative-num-draft-tokens 3 \
   "$@"

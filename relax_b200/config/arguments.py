@@ -265,7 +265,7 @@ ENGINE_FLAGS = {
     "--sglang-tp-size": ("engine_tp", int, None), "--sglang-ep-size": ("engine_ep", int, 1),
     "--sglang-dp-size": ("engine_dp", int, 1), "--sglang-pp-size": ("engine_pp", int, 1),
     "--sglang-enable-return-routed-experts": ("engine_return_routed_experts", "flag", False),
-    # speculative decoding drafted by the model's MTP block (rollout/speculative.py): one proposal per verify pass
+    # speculative decoding drafted by the model's MTP block (rollout/speculative.py): num-steps chained proposals per pass
     "--sglang-speculative-algorithm": ("engine_speculative_algorithm", str, None),
     "--sglang-speculative-num-steps": ("engine_speculative_num_steps", int, 1),
     "--sglang-speculative-eagle-topk": ("engine_speculative_eagle_topk", int, 1),
@@ -306,8 +306,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--recompute-method": (_W, "--recompute-granularity full recomputes every layer"),
     "--recompute-num-layers": (_W, "--recompute-granularity full recomputes every layer"),
     "--log-probs-chunk-size": (_W, "the fused LM head never materialises the logits"),
-    "--sglang-speculative-num-steps": (_W, "one proposal per verify pass (the output distribution does not depend on it)"),
-    "--sglang-speculative-num-draft-tokens": (_W, "one proposal per verify pass: two rows per request"),
+    "--sglang-speculative-num-draft-tokens": (_W, "a verify pass carries --sglang-speculative-num-steps + 1 rows per request (one chain of proposals)"),
     "--sglang-server-concurrency": (_W, None), "--agentic-prelaunch": (_W, "agents start when their sample is scheduled"),
     "--agentic-session-lifecycle": (_W, "a session's cache entries are released by the engine's own eviction"),
     "--agentic-eval-concurrency": (_W, None), "--agentic-admission-expected-decode-cap": (_W, None),
@@ -354,6 +353,8 @@ def apply_flag_policy(a: argparse.Namespace, parser: Optional[argparse.ArgumentP
             continue
         if flag == "--sglang-dp-size" and val in (None, 1):
             continue
+        if flag == "--sglang-speculative-num-draft-tokens" and val == (getattr(a, "engine_speculative_num_steps", 1) or 1) + 1:
+            continue            # exactly what one chain of that many proposals needs
         if flag == "--genrm-num-gpus" and getattr(a, "genrm_engine_addrs", None):
             continue            # the GPUs are the ones behind the named servers
         msg = f"{flag}={val!r} is accepted for recipe compatibility but not implemented here" + (f": {why}" if why else "")

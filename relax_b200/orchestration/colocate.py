@@ -84,6 +84,7 @@ class ColocateConfig:
     # tokens / response_length / rollout_log_probs / status itself (multi-turn, tool use); reward(sample) -> float | dict
     custom_generate_function_path: Optional[str] = None
     speculative: bool = False            # the engine drafts with the model's MTP block (rollout/speculative.py)
+    speculative_steps: int = 1           # proposals per verify pass
     rollout_global_dataset: bool = True             # False: no prompt dataset; the rollout function brings its own data
     rollout_function_path: Optional[str] = None     # user code that produces the whole rollout batch (see _run_rollout_function)
     # engines started by somebody else (``serve engine``): "host:port" each; engine replica r of this job uses its share
@@ -253,7 +254,8 @@ class ColocatedGRPO:
                                         memory_saver=cfg.engine_memory_saver,
                                         max_model_len=cfg.prompt_len + cfg.max_response_len,
                                         eos_token_id=cfg.eos_token_id, ep=self.rollout_ep_group,
-                                        return_routed_experts=cfg.train.use_rollout_routing_replay, speculative=cfg.speculative)
+                                        return_routed_experts=cfg.train.use_rollout_routing_replay, speculative=cfg.speculative,
+                                        speculative_steps=cfg.speculative_steps)
         if cfg.model.vision is not None:
             # colocated: the engine embeds images with the trainer's tower itself (same parameters, nothing to sync)
             self.engine.attach_vision(self.actor.model.vision)

@@ -229,6 +229,7 @@ class Controller:
                 custom_generate_function_path=_get(a, "custom_generate_function_path", None),
                 rollout_function_path=_get(a, "rollout_function_path", None),
                 speculative=bool(_get(a, "engine_speculative_algorithm", None)),
+                speculative_steps=int(_get(a, "engine_speculative_num_steps", 1) or 1),
                 defer_reward_to_post_process=bool(_get(a, "defer_reward_to_post_process", False)),
                 rollout_global_dataset=not bool(_get(a, "disable_rollout_global_dataset", False)),
                 elastic_control_port=_get(a, "elastic_control_port", None), autoscaler_config=_get(a, "autoscaler_config", None),

@@ -119,10 +119,11 @@ class RolloutEngine(SpeculativeMixin):
                  use_cuda_graph: bool = True, max_model_len: int = 4096, memory_saver: Optional[bool] = None,
                  decode_window: Optional[int] = None, windowed_decode: Optional[bool] = None,
                  weights_shared_path: Optional[str] = None, ep: Optional[GroupInfo] = None,
-                 return_routed_experts: bool = False, speculative: bool = False):
+                 return_routed_experts: bool = False, speculative: bool = False, speculative_steps: int = 1):
         self.cfg = cfg
         # speculative decoding drafted by the model's multi-token-prediction block (rollout/speculative.py)
         self.speculative = bool(speculative)
+        self.speculative_steps = max(1, int(speculative_steps))      # proposals per verify pass (the block is chained)
         if self.speculative:
             if cfg.mtp_num_layers < 1:
                 raise ValueError("speculative decoding drafts with the model's multi-token-prediction block; this model has none")

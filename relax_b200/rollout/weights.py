@@ -428,26 +428,31 @@ class RolloutWeights:
         h = ops.linear(x, p["mtp.eh_proj"])
         cos, sin = ops.rope_cos_sin(positions, cfg.rotary_dim, cfg.rope_theta, cfg.mrope_section)
         xin = ops.rmsnorm(h, p[f"layers.{L}.input_norm"], eps)
-        _, xn = self._layer(L, h, xin, cos, sin, attn, tp, p["mtp.final_norm"], cache)
-        return xn
+        h_out, xn = self._layer(L, h, xin, cos, sin, attn, tp, p["mtp.final_norm"], cache)
+        return xn, h_out         # h_out: the block's own un-normalised output (stands in for the trunk's hidden when proposals are chained)
 
-    def forward_mtp_rows(self, h_prev, next_tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo, out_rows=None):
-        """Draft logits from decode-shaped rows (layer ``num_layers`` of ``kv`` is the block's own cache)."""
+    def forward_mtp_rows(self, h_prev, next_tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo, out_rows=None,
+                         return_hidden: bool = False):
+        """Draft logits from decode-shaped rows (layer ``num_layers`` of ``kv`` is the block's own cache); with
+        ``return_hidden`` also the block's output hidden of the same rows."""
         L = self.cfg.num_layers
 
         def attn(i, q, k, v):
             return ops.paged_decode_attention(q, kv[L, 0], kv[L, 1], block_tables, context_lens)
 
-        xn = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, False))
-        return self._logits(xn if out_rows is None else xn[out_rows], tp)
+        xn, ho = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, False))
+        if out_rows is not None:
+            xn, ho = xn[out_rows], ho[out_rows]
+        return (self._logits(xn, tp), ho) if return_hidden else self._logits(xn, tp)
 
     def forward_mtp_prefill(self, h_prev, next_tokens, positions, cu_seqlens, slots, kv, last_rows, tp: GroupInfo, max_seqlen=None):
-        """The block over whole prompts (fills its cache for every prompt position); draft logits of the last rows."""
+        """The block over whole prompts (fills its cache for every prompt position); draft logits and the block's
+        output hidden of the last rows."""
         def attn(i, q, k, v):
             return ops.attention_varlen(q, k, v, cu_seqlens, causal=True, max_seqlen=max_seqlen)
 
-        xn = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True))
-        return self._logits(xn[last_rows], tp)
+        xn, ho = self._mtp_block(h_prev, next_tokens, positions, attn, tp, (kv[:, 0], kv[:, 1], slots, True))
+        return self._logits(xn[last_rows], tp), ho[last_rows]
 
     def forward_decode(self, tokens, positions, block_tables, context_lens, slots, kv, tp: GroupInfo):
         def attn(i, q, k, v):

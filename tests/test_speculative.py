@@ -60,7 +60,7 @@ def test_greedy_output_is_unchanged_with_rejected_and_with_accepted_proposals():
     def oracle_drafts():
         for r in spec.running:
             out = truth[tuple(r.prompt)]
-            r._draft = out[len(r.output)] if len(r.output) < len(out) else None
+            r._draft = out[len(r.output):len(r.output) + spec.speculative_steps] or None
         real()
 
     spec._decode_speculative = oracle_drafts
@@ -71,6 +71,40 @@ def test_greedy_output_is_unchanged_with_rejected_and_with_accepted_proposals():
         assert torch.allclose(torch.tensor(a.logprobs), torch.tensor(b.logprobs), atol=1e-5)
         assert b.spec_accept == b.spec_draft >= 5 and b.spec_verify <= 7     # 11 tokens after the prefill's in about 6 passes
     assert spec.stats["spec_accepted_tokens"] - before == sum(r.spec_accept for r in again)
+
+
+def test_chained_proposals_three_per_pass():
+    """``speculative_steps = 3``: four rows per verify pass; with proposals that plain decoding confirms, four tokens
+    per pass; with the untrained block's own (chained) proposals the output is still plain decoding's."""
+    cfg, model, plain, spec = _engines()
+    spec.speculative_steps = 3
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (6, 13, 21)]
+    prompts.append(list(prompts[0]))
+    keys = [0, 1, 2, 0]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=14)
+    want = plain.generate(prompts, sp, group_keys=keys)
+    got = spec.generate(prompts, sp, group_keys=keys)
+    assert [r.output for r in got] == [r.output for r in want]
+    assert all(r.spec_draft > r.spec_verify for r in got)                # more than one proposal per pass was checked
+    truth = {tuple(r.prompt): r.output for r in want}
+    real = spec._decode_speculative
+
+    def oracle_drafts():
+        for r in spec.running:
+            out = truth[tuple(r.prompt)]
+            r._draft = out[len(r.output):len(r.output) + 3] or None
+        real()
+
+    spec._decode_speculative = oracle_drafts
+    again = spec.generate(prompts, sp, group_keys=keys)
+    for a, b in zip(want, again):
+        assert a.output == b.output and torch.allclose(torch.tensor(a.logprobs), torch.tensor(b.logprobs), atol=1e-5)
+        assert b.spec_accept == b.spec_draft and b.spec_verify == 4      # 13 tokens after the prefill's: 4 + 4 + 4 + 1
+    # sampling stays well-formed
+    del spec._decode_speculative
+    c = spec.generate(prompts, SamplingParams(temperature=1.0, max_new_tokens=11), group_keys=keys)
+    assert all(len(r.output) == len(r.logprobs) == 11 for r in c)
 
 
 def test_the_engine_drafts_what_the_trainers_block_predicts():
@@ -99,7 +133,7 @@ def test_the_engine_drafts_what_the_trainers_block_predicts():
     for _ in range(5):
         spec.step()
         r = spec.running[0]
-        assert r._draft == trainer_draft(r.prompt + r.output), len(r.output)
+        assert r._draft == [trainer_draft(r.prompt + r.output)], len(r.output)
 
 
 def test_stop_token_and_length_limits_under_speculation():
@@ -128,15 +162,15 @@ def test_speculative_rollouts_in_the_colocated_loop():
 
     with pytest.raises(ValueError, match="mtp-num-layers"):
         parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--sglang-speculative-algorithm", "EAGLE"])
-    with pytest.warns(UserWarning, match="one proposal per verify pass"):
+    with pytest.warns(UserWarning, match="rows per request"):
         a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
                         "--global-batch-size", "8", "--num-rollout", "2", "--rollout-max-response-len", "8", "--lr", "1e-2",
                         "--rm-type", "token_sum_parity", "--mtp-num-layers", "1", "--enable-mtp-training",
                         "--sglang-speculative-algorithm", "EAGLE", "--sglang-speculative-num-steps", "2",
-                        "--sglang-speculative-eagle-topk", "1", "--sglang-speculative-num-draft-tokens", "3"])
+                        "--sglang-speculative-eagle-topk", "1", "--sglang-speculative-num-draft-tokens", "4"])
     c = Controller(a, device="cpu")
     run = c.runner
-    assert run.engine.speculative and run.engine.kv.shape[0] == run.cfg.model.num_layers + 1
+    assert run.engine.speculative and run.engine.speculative_steps == 2 and run.engine.kv.shape[0] == run.cfg.model.num_layers + 1
     m = run.step()
     assert m["rollout/spec_draft_tokens"] > 0 and 0.0 <= m["rollout/spec_accept_rate"] <= 1.0 and "mtp_loss" in m
     # rollout log-probs are the policy's: the trainer reproduces them on the sampled tokens
@@ -177,3 +211,7 @@ def test_a_trained_block_halves_the_number_of_passes():
         assert r.output == seq(s, 32)[8:]
         assert r.spec_accept == r.spec_draft == 11 and r.spec_verify == 12
     assert spec.stats["steps"] == 13 and spec.stats["spec_accepted_tokens"] == 33
+    # three chained proposals per pass (the block runs on its own output for the second and third): 6 passes
+    spec.speculative_steps = 3
+    out = spec.generate([seq(s, 8) for s in (1, 7, 20)], SamplingParams(temperature=0.0, max_new_tokens=24))
+    assert all(r.output == seq(s, 32)[8:] and r.spec_verify == 6 and r.spec_accept == 17 for s, r in zip((1, 7, 20), out))
