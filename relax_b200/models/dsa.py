@@ -40,7 +40,10 @@ def indexer_logits(q_idx, k_idx, head_w, starts, ends):
 def topk_indices(logits, topk: int):
     """Indices of the ``topk`` largest finite logits per row, ``-1`` where a row has fewer candidates."""
     k = min(topk, logits.shape[1])
-    val, idx = logits.topk(k, dim=-1)
+    # equal scores (the same token at two positions has the same indexer key): the earlier position wins, so that every
+    # implementation of the selection - packed training rows, the rollout engine's per-request cache - picks the same set
+    val, idx = logits.sort(dim=-1, descending=True, stable=True)
+    val, idx = val[:, :k], idx[:, :k]
     idx = torch.where(torch.isfinite(val), idx, torch.full_like(idx, -1))
     if k < topk:
         idx = F.pad(idx, (0, topk - k), value=-1)

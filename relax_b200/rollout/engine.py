@@ -173,7 +173,10 @@ class RolloutEngine(SpeculativeMixin):
             self.windowed_decode = False     # the rows per request change from step to step: host-driven iterations
         # hybrid stacks: Gated-DeltaNet layers keep a convolution window and a recurrent matrix per request
         # (Request._gdn: layer -> [window, matrix]) next to the paged K/V of the softmax layers; host-driven decode
-        self.hybrid = cfg.linear_attention_freq > 0
+        self.hybrid = cfg.linear_attention_freq > 0 or cfg.dsa_topk > 0 or cfg.multi_latent_attention
+        # latent-attention layers (MLA / DSA) keep per request the latent rows (and indexer keys) of every fed token
+        # (Request._mla: layer -> [rows, keys]), pre-sized for the request's maximum length
+        self.latent = cfg.dsa_topk > 0 or cfg.multi_latent_attention
         if self.hybrid:
             self.windowed_decode = False
             self.use_cuda_graph = False
@@ -451,7 +454,8 @@ class RolloutEngine(SpeculativeMixin):
                 self.weights.routing_capture = []
             h_all = None
             if self.hybrid:
-                self.weights.seq_ctx = {"mode": "prefill", "cu": list(cu), "cu_t": cu_t, "out": {}}
+                self.weights.seq_ctx = {"mode": "prefill", "cu": list(cu), "cu_t": cu_t, "out": {}, "positions": pos_t,
+                                        "cap": [len(r.prompt) + r.params.max_new_tokens for r in leaders]}
             if self.speculative:
                 logits, h_all = self.weights.forward_prefill(t, pos_t, cu_t, slots_t, self.kv, last_t, self.tp,
                                                              max_seqlen=max(b - a for a, b in zip(cu, cu[1:])), return_hidden=True)
@@ -462,7 +466,8 @@ class RolloutEngine(SpeculativeMixin):
             if self.hybrid:
                 out = self.weights.seq_ctx["out"]
                 for j, r in enumerate(leaders):
-                    r._gdn = {i: out[i][j] for i in out}
+                    st = {i: out[i][j] for i in out}
+                    r._gdn, r._mla = ({}, st) if self.latent else (st, {})
                 self.weights.seq_ctx = None
             if self.return_routed_experts:
                 routed = torch.stack(self.weights.routing_capture, 1).tolist()      # [T][L_moe][k]
@@ -481,8 +486,9 @@ class RolloutEngine(SpeculativeMixin):
                     if j < len(r.blocks):
                         self.kv[:, :, r.blocks[j]] = self.kv[:, :, lead.blocks[j]]
                 self.stats["cached_tokens"] += len(r.prompt)
-                if self.hybrid:          # the same prompt leaves the same recurrent state
+                if self.hybrid:          # the same prompt leaves the same recurrent state / the same latent rows
                     r._gdn = {i: [c.clone(), S.clone()] for i, (c, S) in lead._gdn.items()}
+                    r._mla = {i: [a.clone(), None if b is None else b.clone()] for i, (a, b) in lead._mla.items()}
                 rows.append(row_of[id(lead)])
                 if self.return_routed_experts:
                     r.routed_experts = [list(x) for x in lead.routed_experts[:len(r.prompt)]]
@@ -555,8 +561,11 @@ class RolloutEngine(SpeculativeMixin):
             self.weights.routing_capture = []
         if self.hybrid:
             layers = list(reqs[0]._gdn)
-            self.weights.seq_ctx = {"mode": "decode", "state": {i: [torch.stack([r._gdn[i][0] for r in reqs]),
-                                                                   torch.stack([r._gdn[i][1] for r in reqs])] for i in layers}}
+            self.weights.seq_ctx = {"mode": "decode", "positions": pos,
+                                    "state": {i: [torch.stack([r._gdn[i][0] for r in reqs]),
+                                                  torch.stack([r._gdn[i][1] for r in reqs])] for i in layers},
+                                    "cache": {i: [r._mla[i] for r in reqs] for i in reqs[0]._mla},
+                                    "lens": [r.num_tokens - 1 for r in reqs]}
         logits = self.weights.forward_decode(tok, pos, bt, ctx, slots, self.kv, self.tp)
         if self.hybrid:
             st = self.weights.seq_ctx["state"]

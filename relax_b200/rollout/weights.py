@@ -54,6 +54,18 @@ def rollout_param_shapes(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = Fal
             shapes[p + "gdn_dt_bias"], shapes[p + "gdn_A_log"], shapes[p + "gdn_norm"] = (hv,), (hv,), (d,)
             shapes[p + "gdn_out"] = (H, vd)
             return mlp(i, p)
+        if mixer_kind(cfg, i) == "dsa":          # multi-head latent attention, sparse when dsa_topk > 0
+            nh, nope, rope, kvl, vh = cfg.num_attention_heads, cfg.dsa_nope, cfg.dsa_rope, cfg.dsa_kv_lora, cfg.dsa_v_head
+            shapes[p + "mla_q_down"], shapes[p + "mla_q_norm"] = (cfg.dsa_q_lora, H), (cfg.dsa_q_lora,)
+            shapes[p + "mla_q_up"] = (nh * (nope + rope), cfg.dsa_q_lora)
+            shapes[p + "mla_kv_down"], shapes[p + "mla_kv_norm"] = (kvl + rope, H), (kvl,)
+            shapes[p + "mla_kv_up"] = (nh * (nope + vh), kvl)
+            shapes[p + "mla_o"] = (H, nh * vh)
+            if cfg.dsa_topk > 0:
+                shapes[p + "idx_wq"] = (cfg.dsa_index_heads * cfg.dsa_index_dim, H)
+                shapes[p + "idx_wk"] = (cfg.dsa_index_dim, H)
+                shapes[p + "idx_w"] = (cfg.dsa_index_heads, H)
+            return mlp(i, p)
         shapes[p + "qkv"] = ((nq + 2 * nkv) * hd, H)
         if cfg.attention_output_gate:
             shapes[p + "attn_gate"] = (nq * hd, H)       # one gate row per query feature (sigmoid on the attention output)
@@ -113,12 +125,10 @@ def rollout_layout(cfg: ModelConfig, tp: int, ep: int = 1, mtp: bool = False):
 class RolloutWeights:
     def __init__(self, cfg: ModelConfig, tp_size: int, tp_rank: int, device, dtype, ep_size: int = 1, ep_rank: int = 0,
                  memory_saver: bool = False, shared_path: Optional[str] = None, mtp: bool = False):
-        if cfg.dsa_topk > 0 or cfg.multi_latent_attention:
-            raise NotImplementedError("the rollout engine serves softmax-attention and Gated-DeltaNet layers; MLA / DSA layers "
-                                      "are trainer-side (SFT, log-prob evaluation) for now")
-        if (cfg.linear_attention_freq > 0 or cfg.attention_output_gate) and (tp_size > 1 or ep_size > 1 or mtp):
-            raise NotImplementedError("hybrid stacks (Gated DeltaNet layers, gated attention) run on one rank per engine, "
-                                      "without speculative decoding")
+        if (cfg.linear_attention_freq > 0 or cfg.attention_output_gate or cfg.dsa_topk > 0 or cfg.multi_latent_attention) \
+                and (tp_size > 1 or ep_size > 1 or mtp):
+            raise NotImplementedError("stacks with Gated-DeltaNet, gated-attention or latent-attention (MLA / DSA) layers run on "
+                                      "one rank per engine, without speculative decoding")
         if cfg.attention_output_gate and cfg.qkv_bias:
             raise NotImplementedError("gated attention with a QKV bias")
         self.cfg, self.tp_size, self.tp_rank = cfg, tp_size, tp_rank
@@ -321,14 +331,89 @@ class RolloutWeights:
         o = ops.rmsnorm(o.to(x.dtype), p[pre + "gdn_norm"], cfg.rms_norm_eps) * F.silu(z.reshape(T, hv, d))
         return ops.linear(o.reshape(T, vd), p[pre + "gdn_out"])
 
+    # ------------------------------------------------------------------ latent attention layers (MLA, sparse = DSA)
+    def _mla(self, i, x):
+        """Multi-head latent attention on rows (relax_b200/models/dsa.py DSAAttention, absorbed form) with the cache that
+        incremental decoding needs: per sequence the latent rows ``[kv_lora | rope]`` of every fed token and, for the
+        sparse form, its indexer keys.  ``seq_ctx``: ``mode = "prefill"`` (whole sequences; the caches of every sequence
+        are left in ``ctx["out"][i]`` with room for ``ctx["cap"][j]`` rows) or ``"decode"`` (one new token per sequence:
+        ``ctx["cache"][i][j] = [latent rows, indexer keys]`` holding ``ctx["lens"][j]`` rows; the new row is appended)."""
+        import torch.nn.functional as F
+
+        from ..models import dsa as D
+
+        cfg, p, ctx = self.cfg, self.p, self.seq_ctx
+        pre = f"layers.{i}."
+        H, nope, rope, kvl, vh = cfg.num_attention_heads, cfg.dsa_nope, cfg.dsa_rope, cfg.dsa_kv_lora, cfg.dsa_v_head
+        Hi, Di, topk = cfg.dsa_index_heads, cfg.dsa_index_dim, cfg.dsa_topk
+        T, eps = x.shape[0], cfg.rms_norm_eps
+        cos, sin = ops.rope_cos_sin(ctx["positions"], rope, cfg.rope_theta, None)
+        ql = ops.rmsnorm(ops.linear(x, p[pre + "mla_q_down"]), p[pre + "mla_q_norm"], eps)
+        q = ops.linear(ql, p[pre + "mla_q_up"]).view(T, H, nope + rope)
+        q_rope = ops.apply_rope(q[..., nope:].contiguous(), cos, sin)
+        kvd = ops.linear(x, p[pre + "mla_kv_down"])
+        c = ops.rmsnorm(kvd[:, :kvl].contiguous(), p[pre + "mla_kv_norm"], eps)
+        k_rope = ops.apply_rope(kvd[:, None, kvl:].contiguous(), cos, sin)[:, 0]
+        w = p[pre + "mla_kv_up"].view(H, nope + vh, kvl)
+        w_uk, w_uv = w[:, :nope], w[:, nope:]
+        qf = torch.cat([torch.einsum("thn,hnc->thc", q[..., :nope].float(), w_uk.float()).to(x.dtype), q_rope], -1)
+        kv_new = torch.cat([c, k_rope], -1)
+        scale = (nope + rope) ** -0.5
+        if topk > 0:
+            qi = ops.linear(x, p[pre + "idx_wq"]).view(T, Hi, Di)
+            ki = ops.linear(x, p[pre + "idx_wk"])
+            hw = ops.linear(x, p[pre + "idx_w"]) * Hi ** -0.5
+        if ctx["mode"] == "prefill":
+            starts, ends = D.causal_ranges(ctx["cu_t"], T)
+            if topk > 0:
+                idx = D.topk_indices(D.indexer_logits(qi, ki, hw, starts, ends), topk)
+                lat, _ = D.sparse_mla_attention(qf, kv_new, idx, kvl, scale)
+            else:
+                lat, _ = D.dense_mla_attention(qf, kv_new, starts, ends, kvl, scale)
+            fin = []
+            for j, (a, b) in enumerate(zip(ctx["cu"], ctx["cu"][1:])):
+                buf = kv_new.new_zeros(ctx["cap"][j], kv_new.shape[1])
+                buf[: b - a] = kv_new[a:b]
+                kb = None
+                if topk > 0:
+                    kb = ki.new_zeros(ctx["cap"][j], Di)
+                    kb[: b - a] = ki[a:b]
+                fin.append([buf, kb])
+            ctx["out"][i] = fin
+        else:
+            cache, lens = ctx["cache"][i], ctx["lens"]
+            for j in range(T):
+                cache[j][0][lens[j]] = kv_new[j]
+                if topk > 0:
+                    cache[j][1][lens[j]] = ki[j]
+            Lmax = max(lens) + 1
+            n = torch.tensor([l_ + 1 for l_ in lens], device=x.device)
+            cut = lambda t: F.pad(t[:Lmax], (0, 0, 0, max(0, Lmax - t.shape[0])))          # short requests own short buffers
+            KV = torch.stack([cut(cb[0]) for cb in cache]).float()                          # [B, Lmax, C]
+            beyond = torch.arange(Lmax, device=x.device)[None, :] >= n[:, None]             # [B, Lmax]
+            sc = torch.einsum("bhc,blc->bhl", qf.float(), KV) * scale
+            sc = sc.masked_fill(beyond[:, None, :], float("-inf"))
+            if topk > 0:
+                KI = torch.stack([cut(cb[1]) for cb in cache]).float()
+                il = (F.relu(torch.einsum("bhd,bld->bhl", qi.float(), KI)) * hw.float()[..., None]).sum(1)
+                il = il.masked_fill(beyond, float("-inf"))
+                k_ = min(topk, Lmax)
+                val, sel = il.sort(dim=-1, descending=True, stable=True)         # ties: the earlier position, as in training
+                val, sel = val[:, :k_], sel[:, :k_]
+                keep = torch.zeros_like(beyond).scatter_(1, sel, torch.isfinite(val))
+                sc = sc.masked_fill(~keep[:, None, :], float("-inf"))
+            lat = torch.einsum("bhl,blc->bhc", torch.softmax(sc, -1), KV[..., :kvl]).to(x.dtype)
+        o = torch.einsum("thc,hvc->thv", lat.float(), w_uv.float()).to(x.dtype).reshape(T, H * vh)
+        return ops.linear(o, p[pre + "mla_o"])
+
     def _layer(self, i, h, x, cos, sin, attn, tp, next_norm, cache):
         """One decoder layer.  ``h`` is the residual stream, ``x`` its normed copy (input of the attention
         block); returns the new ``(h, x)`` where ``x`` is already normed with ``next_norm`` (the next layer's
         input norm or the final norm), so every residual add is fused with the norm that follows it."""
         cfg, p = self.cfg, self.p
         pre = f"layers.{i}."
-        if (pre + "gdn_qkvz") in p:
-            a = self._gdn(i, x)
+        if (pre + "gdn_qkvz") in p or (pre + "mla_q_down") in p:
+            a = self._gdn(i, x) if (pre + "gdn_qkvz") in p else self._mla(i, x)
             x, h = ops.add_rmsnorm(a, h, p[pre + "post_norm"], cfg.rms_norm_eps)
             m, _ = self._mlp(i, x, tp)
             x, h = ops.add_rmsnorm(m, h, next_norm, cfg.rms_norm_eps)

@@ -165,6 +165,23 @@ def build_plan(cfg: ModelConfig, src: TrainerLayout, dst_tp: int, dst_ep: int = 
             rep(gbase + "dt_bias", p + "gdn_dt_bias", hv)
             rep(gbase + "A_log", p + "gdn_A_log", hv)
             rep(gbase + "norm.weight", p + "gdn_norm", d)
+        mla_layer = mixer_kind(cfg, layer) == "dsa"
+        if mla_layer:
+            if src.tp > 1 or dst_tp > 1:
+                raise NotImplementedError("latent-attention layers are synchronised between tp = 1 layouts")
+            nh, nope, rope, kvl, vh = cfg.num_attention_heads, cfg.dsa_nope, cfg.dsa_rope, cfg.dsa_kv_lora, cfg.dsa_v_head
+            dbase = trainer_param_name(ll, "o").replace("linear_proj.weight", "dsa.")
+            mats = [("linear_q_down_proj.weight", "mla_q_down", cfg.dsa_q_lora, H), ("linear_q_up_proj.weight", "mla_q_up", nh * (nope + rope), cfg.dsa_q_lora),
+                    ("linear_kv_down_proj.weight", "mla_kv_down", kvl + rope, H), ("linear_kv_up_proj.weight", "mla_kv_up", nh * (nope + vh), kvl),
+                    ("linear_proj.weight", "mla_o", H, nh * vh)]
+            if cfg.dsa_topk > 0:
+                mats += [("indexer.linear_wq.weight", "idx_wq", cfg.dsa_index_heads * cfg.dsa_index_dim, H),
+                         ("indexer.linear_wk.weight", "idx_wk", cfg.dsa_index_dim, H), ("indexer.linear_weights.weight", "idx_w", cfg.dsa_index_heads, H)]
+            for sname, dname, r_, c_ in mats:
+                add(BlockCopy(0, dbase + sname, 0, 0, 0, p + dname, 0, 0, r_, c_))
+            rep(dbase + "linear_q_up_proj.layer_norm_weight", p + "mla_q_norm", cfg.dsa_q_lora)
+            rep(dbase + "linear_kv_up_proj.layer_norm_weight", p + "mla_kv_norm", kvl)
+            gdn_layer = True            # from here on: no softmax-attention tensors for this layer
         if cfg.sandwich_norm:
             rep(trainer_param_name(ll, "post_attn_norm"), p + "post_attn_norm", H)
             rep(trainer_param_name(ll, "post_mlp_norm"), p + "post_mlp_norm", H)

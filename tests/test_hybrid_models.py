@@ -59,12 +59,10 @@ def test_sft_learns(preset):
 def test_rollout_engine_refuses_what_it_does_not_serve():
     from relax_b200.rollout.weights import RolloutWeights
 
-    for name in ("tiny-dsa", "tiny-mla"):
-        with pytest.raises(NotImplementedError):
-            RolloutWeights(get_config(name), 1, 0, "cpu", torch.float32)
-    with pytest.raises(NotImplementedError):          # hybrid stacks: one rank per engine
-        RolloutWeights(get_config("tiny-next"), 2, 0, "cpu", torch.float32)
-    RolloutWeights(get_config("tiny-next"), 1, 0, "cpu", torch.float32)
+    for name in ("tiny-dsa", "tiny-mla", "tiny-next"):
+        with pytest.raises(NotImplementedError):          # stateful layers: one rank per engine
+            RolloutWeights(get_config(name), 2, 0, "cpu", torch.float32)
+        RolloutWeights(get_config(name), 1, 0, "cpu", torch.float32)
 
 
 def test_mla_preset_trains_and_big_presets_resolve():
@@ -259,4 +257,40 @@ def test_qwen35_style_hybrid_model_in_the_rl_loop():
     for _ in range(2):
         m = c.runner.step()
         assert m["train_rollout_logprob_abs_diff"] < 1e-4, m["train_rollout_logprob_abs_diff"]
+    c.runner.close()
+
+
+@pytest.mark.parametrize("name", ["tiny-mla", "tiny-dsa"])
+def test_latent_attention_in_the_rollout_engine_matches_the_trainer(name):
+    """MLA (dense) and DSA (indexer + top-k) in the ENGINE: decoding from the per-request latent cache gives the tokens
+    of a full recomputation by the trainer's model, and the RL loop's trainer / engine log-probs agree."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+    from relax_b200.weight_sync.plan import TrainerLayout
+    from relax_b200.weight_sync.sync import WeightSync
+
+    cfg = get_config(name)
+    model = GPTModel(cfg, seed=5)
+    eng = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8)
+    WeightSync(cfg, TrainerLayout(tp=1), 1, [0], [0]).update_weights({k: v.detach() for k, v in model.named_parameters()}, eng.weights, eng, version=1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (3, 12, 21)]
+    prompts.append(list(prompts[1]))
+    out = eng.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=12), group_keys=[0, 1, 2, 1])
+    for p_, r in zip(prompts, out):
+        seq = list(p_)
+        for _ in range(12):
+            t = torch.tensor(seq)
+            with torch.no_grad():
+                h = model(t, torch.arange(len(seq)), torch.tensor([0, len(seq)], dtype=torch.int32), max_seqlen=len(seq))
+            seq.append(int((h[-1].float() @ model.lm_head_weight()[:cfg.vocab_size].float().t()).argmax()))
+        assert r.output == seq[len(p_):], name
+    a = parse_args(["--model-name", name, "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2",
+                    "--global-batch-size", "8", "--num-rollout", "1", "--rollout-max-response-len", "6", "--lr", "1e-3",
+                    "--rm-type", "token_sum_parity"])
+    c = Controller(a, device="cpu")
+    m = c.runner.step()
+    assert m["train_rollout_logprob_abs_diff"] < 1e-4, m["train_rollout_logprob_abs_diff"]
     c.runner.close()
