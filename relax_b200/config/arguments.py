@@ -210,6 +210,7 @@ FLAGS: dict[str, list] = {
         ("--mtp-loss-scaling-factor", dict(type=float, default=0.1)), ("--mtp-only-training", _b()),
     ],
     "sft": [
+        ("--sft-predict-interval", dict(type=int, default=None)),
         ("--sft-chunked-logits", _b()), ("--sft-logits-chunk-size", dict(type=int, default=4096)),
         ("--sft-max-in-flight-steps", dict(type=int, default=2)), ("--sft-prefetch-buffer-size", dict(type=int, default=64)),
         ("--loss-mask-type", dict(type=str, default="qwen")), ("--num-labels", dict(type=int, default=None)),

@@ -508,6 +508,7 @@ class _SFTRunner:
         else:
             self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
         self.dataset = ds
+        self._init_predict(args, files, tok)
 
     def _classification_batches(self, files, tok, per_rank, args):
         """``{"text" | "prompt": ..., "label": id | [ids] | multi-hot}`` rows -> batches with ``labels``
@@ -550,7 +551,89 @@ class _SFTRunner:
         b = next(self.batches)
         m = self.actor.train_seq_cls(b) if self.actor.role == "seq_cls" else self.actor.train_sft(b)
         m["total_tokens_local"] = sum(len(t) for t in b["tokens"])
+        self.steps = getattr(self, "steps", 0) + 1
+        if self.predict is not None and self.steps % self.predict["interval"] == 0:
+            m.update(self.run_predict(self.steps))
         return m
+
+    # ------------------------------------------------------------------ periodic predict pass
+    def _init_predict(self, args, files, tok):
+        """``--sft-predict-interval N`` (relax/engine/sft/predict/loop.py, predict/runner.py): every N steps the current
+        weights generate completions for the evaluation conversations - each cut before its last assistant turn,
+        which becomes the reference - and the results go to ``<save>/predict/predictions_step_<step>.jsonl``.  The
+        evaluation set is ``--eval-prompt-data`` (name path pairs) or a fixed-seed ``--eval-size`` subset of the
+        training files.  The engine is built on first use and gives its KV cache back after every pass."""
+        import json
+        import random
+
+        self.predict = None
+        n = _get(args, "sft_predict_interval", None)
+        if not n:
+            return
+        if not _get(args, "save", None):
+            raise ValueError("--sft-predict-interval writes to <save>/predict/: set --save")
+        if self.actor.ps.tp.size > 1 or self.actor.ps.pp.size > 1:
+            raise NotImplementedError("the predict pass runs an engine next to a tp = pp = 1 trainer")
+        rows = []
+        pairs = _get(args, "eval_prompt_data", None) or []
+        paths = [pairs[i + 1] for i in range(0, len(pairs) - 1, 2)]
+        for path in (paths or files):
+            with open(path, encoding="utf-8") as f:
+                rows += [json.loads(line) for line in f if line.strip()]
+        if not paths:
+            k = _get(args, "eval_size", None)
+            if not k:
+                raise ValueError("--sft-predict-interval needs --eval-prompt-data or --eval-size")
+            rows = random.Random(int(_get(args, "seed", 0)) + 1234).sample(rows, min(int(k), len(rows)))
+        conv = []
+        for r in rows:
+            msgs = r.get("messages") or [{"role": "user", "content": r.get("prompt", "")}, {"role": "assistant", "content": r.get("response", "")}]
+            last = max((i for i, m_ in enumerate(msgs) if m_["role"] == "assistant"), default=-1)
+            ref = msgs[last]["content"] if last >= 0 else ""
+            conv.append((msgs[:last] if last >= 0 else msgs, ref if isinstance(ref, str) else json.dumps(ref, ensure_ascii=False)))
+        self.predict = {"interval": int(n), "conv": conv, "tok": tok, "dir": os.path.join(args.save, "predict"),
+                        "max_new": int(_get(args, "eval_max_response_len", None) or _get(args, "rollout_max_response_len", 64)),
+                        "max_ctx": int(_get(args, "rollout_max_context_len", 4096)), "engine": None, "sync": None,
+                        "hf": _get(args, "hf_checkpoint", None)}
+
+    def run_predict(self, step: int) -> dict:
+        import json
+        import time as _time
+
+        from ..data.sft import render_chat
+        from ..data.tokenizer import build_codec
+        from ..rollout.engine import RolloutEngine, SamplingParams
+        from ..weight_sync.plan import TrainerLayout
+        from ..weight_sync.sync import WeightSync
+
+        P, actor = self.predict, self.actor
+        t0 = _time.perf_counter()
+        mine = P["conv"][actor.ps.dp.rank::actor.ps.dp.size]
+        prompts = []
+        for msgs, _ in mine:
+            toks, _m = render_chat(msgs, P["tok"])
+            prompts.append((toks + P["tok"]("<|assistant|>\n"))[-(P["max_ctx"] - P["max_new"]):])
+        if P["engine"] is None:
+            need = sum((len(p) + P["max_new"]) // 16 + 2 for p in prompts) + 8
+            P["engine"] = RolloutEngine(actor.mcfg, device=actor.device, dtype=actor.model.dtype, num_kv_blocks=max(64, need), block_size=16,
+                                        max_model_len=P["max_ctx"], use_cuda_graph=False, memory_saver=False)
+            me = dist.get_rank() if dist.is_initialized() else 0
+            P["sync"] = WeightSync(actor.mcfg, TrainerLayout(tp=1), 1, [me], [me])
+            P["decode"] = build_codec(P["hf"], actor.mcfg.vocab_size).decode
+        eng = P["engine"]
+        eng.resume_memory_occupation(("kv_cache",))
+        P["sync"].update_weights(dict(actor.named_local_params()), eng.weights, eng, version=step)
+        out = eng.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=P["max_new"]))
+        eng.release_memory_occupation(("kv_cache", "cuda_graph"))
+        os.makedirs(P["dir"], exist_ok=True)
+        suffix = f"_rank{actor.ps.dp.rank}" if actor.ps.dp.size > 1 else ""
+        path = os.path.join(P["dir"], f"predictions_step_{step}{suffix}.jsonl")
+        with open(path, "w", encoding="utf-8") as f:
+            for (msgs, ref), r in zip(mine, out):
+                f.write(json.dumps({"step": step, "prompt": msgs, "reference": ref, "prediction": P["decode"](r.output),
+                                    "finish_reason": r.finish_reason}, ensure_ascii=False) + "\n")
+        return {"predict/samples": float(len(out)), "predict/time": _time.perf_counter() - t0,
+                "predict/response_len": sum(len(r.output) for r in out) / max(1, len(out))}
 
 
 def _eval_sets_from_args(a, vocab: int):

@@ -216,3 +216,23 @@ def test_vision_language_run_through_the_entrypoint(tmp_path):
     lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
     assert len(lines) == 2 and lines[-1]["train_rollout_logprob_abs_diff"] < 1e-3
     assert lines[-1]["rollout/prompt_lengths"] == 24         # text + image placeholders
+
+
+def test_sft_with_a_periodic_predict_pass(tmp_path):
+    """``--sft-predict-interval``: every second step the current weights answer the evaluation conversations (cut before
+    their last assistant turn) and the completions land in <save>/predict/."""
+    data = tmp_path / "sft.jsonl"
+    with open(data, "w") as f:
+        for i in range(16):
+            f.write(json.dumps({"messages": [{"role": "user", "content": f"say {i}"}, {"role": "assistant", "content": f"number {i}"}]}) + "\n")
+    save = str(tmp_path / "sft_ckpt")
+    assert main(["--model-name", "tiny", "--loss-type", "sft_loss", "--prompt-data", str(data), "--num-rollout", "4",
+                 "--global-batch-size", "4", "--lr", "1e-3", "--max-tokens-per-gpu", "512", "--save", save,
+                 "--sft-predict-interval", "2", "--eval-size", "3", "--rollout-max-response-len", "6"]) == 0
+    files = sorted(os.listdir(os.path.join(save, "predict")))
+    assert files == ["predictions_step_2.jsonl", "predictions_step_4.jsonl"]
+    rows = [json.loads(l) for l in open(os.path.join(save, "predict", files[0]))]
+    assert len(rows) == 3 and all(r["prompt"][0]["role"] == "user" and r["reference"].startswith("number ") for r in rows)
+    assert all(isinstance(r["prediction"], str) and r["finish_reason"] in ("length", "stop") for r in rows)
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    assert [("predict/samples" in l) for l in lines] == [False, True, False, True]
