@@ -508,6 +508,7 @@ class _SFTRunner:
         else:
             self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
         self.dataset = ds
+        self._init_eval(args, files, tok)
         self._init_predict(args, files, tok)
 
     def _classification_batches(self, files, tok, per_rank, args):
@@ -552,9 +553,92 @@ class _SFTRunner:
         m = self.actor.train_seq_cls(b) if self.actor.role == "seq_cls" else self.actor.train_sft(b)
         m["total_tokens_local"] = sum(len(t) for t in b["tokens"])
         self.steps = getattr(self, "steps", 0) + 1
+        if self.eval is not None and self.steps % self.eval["interval"] == 0:
+            m.update(self.run_eval())
         if self.predict is not None and self.steps % self.predict["interval"] == 0:
             m.update(self.run_predict(self.steps))
         return m
+
+    # ------------------------------------------------------------------ periodic evaluation
+    def _eval_rows(self, args, files):
+        """The evaluation rows: ``--eval-prompt-data`` (name path pairs) or a fixed-seed ``--eval-size`` subset of the
+        training files (relax/engine/sft/runtime.py resolve_sft_eval_split / resolve_sft_split_indices)."""
+        import json
+        import random
+
+        rows = []
+        pairs = _get(args, "eval_prompt_data", None) or []
+        paths = [pairs[i + 1] for i in range(0, len(pairs) - 1, 2)]
+        for path in (paths or files):
+            with open(path, encoding="utf-8") as f:
+                rows += [json.loads(line) for line in f if line.strip()]
+        if not paths:
+            k = _get(args, "eval_size", None)
+            if not k:
+                return None
+            rows = random.Random(int(_get(args, "seed", 0)) + 1234).sample(rows, min(int(k), len(rows)))
+        return rows
+
+    def _init_eval(self, args, files, tok):
+        """``--eval-interval N`` under SFT: every N steps the held-out rows are scored without training on them -
+        token-level NLL / perplexity over the assistant turns (relax/engine/sft/eval/ppl.py), or accuracy and macro-F1
+        of the class head (relax/engine/sft/eval/classification.py)."""
+        from ..data.sft import render_chat, to_train_sample
+
+        self.eval = None
+        n = _get(args, "eval_interval", None)
+        rows = self._eval_rows(args, files) if n else None
+        if not n or not rows:
+            return
+        actor = self.actor
+        rows = rows[actor.ps.dp.rank::actor.ps.dp.size]
+        max_len = _get(args, "rollout_max_context_len", 4096)
+        if actor.role == "seq_cls":
+            key_in, key_lab = _get(args, "input_key", None) or "prompt", _get(args, "label_key", None) or "label"
+            toks = [(tok(r.get(key_in) or r.get("prompt") or r.get("text") or "")[:max_len] or [0]) for r in rows]
+            batch = {"tokens": toks, "response_lengths": [1] * len(rows), "loss_masks": [[1]] * len(rows), "labels": [r[key_lab] for r in rows]}
+        else:
+            samples = []
+            for r in rows:
+                msgs = r.get("messages") or [{"role": "user", "content": r.get("prompt", "")}, {"role": "assistant", "content": r.get("response", "")}]
+                smp = to_train_sample(*render_chat(msgs, tok), max_len=max_len)
+                if smp is not None:
+                    samples.append(smp)
+            batch = {"tokens": [s_["tokens"] for s_ in samples], "response_lengths": [s_["response_length"] for s_ in samples],
+                     "loss_masks": [s_["loss_mask"] for s_ in samples]}
+        self.eval = {"interval": int(n), "batch": batch}
+
+    def run_eval(self) -> dict:
+        actor, batch = self.actor, self.eval["batch"]
+        if actor.role != "seq_cls":
+            return actor.evaluate_ppl(batch)
+        C = actor.mcfg.num_classes
+        logits = torch.stack([x.float() for x in actor.predict_classes(batch)]) if batch["tokens"] else torch.zeros(0, C)
+        stats = torch.zeros(3, C, dtype=torch.float64, device=actor.device)           # tp, predicted, actual per class
+        if actor.cfg.problem_type == "multi_label_classification":
+            pred = torch.sigmoid(logits) > (actor.cfg.classification_threshold or 0.5)
+            lab = torch.zeros_like(pred)
+            for i, l_ in enumerate(batch["labels"]):
+                ids = l_ if isinstance(l_, (list, tuple)) else [l_]
+                hot = [bool(x) for x in ids] if len(ids) == C and set(ids) <= {0, 1} else [c in set(int(x) for x in ids) for c in range(C)]
+                lab[i] = torch.tensor(hot, device=lab.device)
+            correct = (pred == lab).all(-1).double().sum()
+        else:
+            cls = logits.argmax(-1)
+            want = torch.tensor([int(l_) for l_ in batch["labels"]], device=cls.device)
+            pred = torch.nn.functional.one_hot(cls, C).bool()
+            lab = torch.nn.functional.one_hot(want, C).bool()
+            correct = (cls == want).double().sum()
+        stats[0], stats[1], stats[2] = (pred & lab).sum(0), pred.sum(0), lab.sum(0)
+        tot = torch.stack([correct, torch.tensor(float(len(batch["tokens"])), dtype=torch.float64, device=actor.device)])
+        if actor.ps.dp.size > 1:
+            dist.all_reduce(stats, group=actor.ps.dp.group)
+            dist.all_reduce(tot, group=actor.ps.dp.group)
+        prec, rec = stats[0] / stats[1].clamp_min(1), stats[0] / stats[2].clamp_min(1)
+        f1 = torch.where(prec + rec > 0, 2 * prec * rec / (prec + rec).clamp_min(1e-12), torch.zeros_like(prec))
+        seen = stats[2] > 0
+        return {"eval/accuracy": float(tot[0] / tot[1].clamp_min(1)), "eval/macro_f1": float(f1[seen].mean()) if bool(seen.any()) else 0.0,
+                "eval/samples": float(tot[1])}
 
     # ------------------------------------------------------------------ periodic predict pass
     def _init_predict(self, args, files, tok):
@@ -574,17 +658,9 @@ class _SFTRunner:
             raise ValueError("--sft-predict-interval writes to <save>/predict/: set --save")
         if self.actor.ps.tp.size > 1 or self.actor.ps.pp.size > 1:
             raise NotImplementedError("the predict pass runs an engine next to a tp = pp = 1 trainer")
-        rows = []
-        pairs = _get(args, "eval_prompt_data", None) or []
-        paths = [pairs[i + 1] for i in range(0, len(pairs) - 1, 2)]
-        for path in (paths or files):
-            with open(path, encoding="utf-8") as f:
-                rows += [json.loads(line) for line in f if line.strip()]
-        if not paths:
-            k = _get(args, "eval_size", None)
-            if not k:
-                raise ValueError("--sft-predict-interval needs --eval-prompt-data or --eval-size")
-            rows = random.Random(int(_get(args, "seed", 0)) + 1234).sample(rows, min(int(k), len(rows)))
+        rows = self._eval_rows(args, files)
+        if not rows:
+            raise ValueError("--sft-predict-interval needs --eval-prompt-data or --eval-size")
         conv = []
         for r in rows:
             msgs = r.get("messages") or [{"role": "user", "content": r.get("prompt", "")}, {"role": "assistant", "content": r.get("response", "")}]

@@ -236,3 +236,29 @@ def test_sft_with_a_periodic_predict_pass(tmp_path):
     assert all(isinstance(r["prediction"], str) and r["finish_reason"] in ("length", "stop") for r in rows)
     lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
     assert [("predict/samples" in l) for l in lines] == [False, True, False, True]
+
+
+def test_sft_periodic_evaluation_ppl_and_classification(tmp_path):
+    """``--eval-interval`` under SFT: held-out perplexity for the language-model loss, accuracy / macro-F1 for the class head."""
+    data = tmp_path / "sft.jsonl"
+    with open(data, "w") as f:
+        for i in range(16):
+            f.write(json.dumps({"prompt": f"say {i % 4}", "response": f"number {i % 4}"}) + "\n")
+    save = str(tmp_path / "sft_ckpt")
+    assert main(["--model-name", "tiny", "--loss-type", "sft_loss", "--prompt-data", str(data), "--num-rollout", "6",
+                 "--global-batch-size", "8", "--lr", "3e-3", "--max-tokens-per-gpu", "512", "--save", save,
+                 "--eval-interval", "3", "--eval-size", "4"]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save, "metrics.jsonl"))]
+    ev = [l for l in lines if "eval/ppl" in l]
+    assert [l["step"] for l in ev] == [2, 5] and ev[1]["eval/nll"] < ev[0]["eval/nll"] and ev[0]["eval/tokens"] > 0
+    cls = tmp_path / "cls.jsonl"
+    with open(cls, "w") as f:
+        for i in range(24):
+            f.write(json.dumps({"text": "good " * (1 + i % 3) if i % 2 else "bad " * (1 + i % 3), "label": i % 2}) + "\n")
+    save2 = str(tmp_path / "cls_ckpt")
+    assert main(["--model-name", "tiny", "--loss-type", "seq_cls_loss", "--num-labels", "2", "--prompt-data", str(cls), "--input-key", "text",
+                 "--num-rollout", "8", "--global-batch-size", "8", "--lr", "3e-3", "--max-tokens-per-gpu", "512", "--save", save2,
+                 "--eval-interval", "4", "--eval-size", "8"]) == 0
+    lines = [json.loads(l) for l in open(os.path.join(save2, "metrics.jsonl"))]
+    ev = [l for l in lines if "eval/accuracy" in l]
+    assert len(ev) == 2 and ev[-1]["eval/samples"] == 8 and ev[-1]["eval/accuracy"] >= 0.75 and 0 <= ev[-1]["eval/macro_f1"] <= 1
