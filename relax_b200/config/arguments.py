@@ -322,7 +322,7 @@ FLAG_POLICY: dict[str, tuple] = {
     "--profile-target": (_W, "the trainer is the profiled role"), "--reward-max-concurrency": (_W, None),
     "--reward-num-workers": (_W, None), "--rollout-engine-init-timeout": (_W, None), "--rollout-http-timeout": (_W, None),
     "--rollout-skip-special-tokens": (_W, None), "--selective-offload": (_W, None), "--sft-chunked-logits": (_W, "always on"),
-    "--sft-logits-chunk-size": (_W, None), "--sft-max-in-flight-steps": (_W, None), "--sft-prefetch-buffer-size": (_W, None),
+    "--sft-logits-chunk-size": (_W, None), "--sft-max-in-flight-steps": (_W, None),
     "--slime-router-health-check-failure-threshold": (_W, None), "--slime-router-max-connections": (_W, None),
     "--slime-router-middleware-paths": (_W, None), "--slime-router-sticky": (_W, None), "--slime-router-timeout": (_W, None),
     "--use-slime-router": (_W, "the in-process router is used when several engines serve one rank; the HTTP proxy is `serve router`"),

@@ -120,3 +120,63 @@ def as_batch(samples: Sequence[dict]) -> dict:
     return {"tokens": [s["tokens"] for s in samples],
             "response_lengths": [s["response_length"] for s in samples],
             "loss_masks": [s["loss_mask"] for s in samples]}
+
+
+def batches_with_cursor(ds: StreamingSFTDataset, samples_per_batch: int) -> Iterator[tuple]:
+    """``(batch, dataset state after its last sample)`` pairs: a run that stores the state of the last batch it TRAINED
+    on resumes with the next unseen sample, however far a prefetcher had read ahead."""
+    cur: List[dict] = []
+    for s in ds:
+        cur.append(s)
+        if len(cur) >= samples_per_batch:
+            yield as_batch(cur), ds.state_dict()
+            cur = []
+    if cur:
+        yield as_batch(cur), ds.state_dict()
+
+
+class Prefetcher:
+    """A background thread that keeps up to ``depth`` items of an iterator ready (the tokenisation of the next SFT
+    batches overlaps the training step; relax/engine/sft/dataset/streaming.py prefetch buffer,
+    ``--sft-prefetch-buffer-size``).  Exceptions of the producer surface at the consumer."""
+
+    _END = object()
+
+    def __init__(self, it: Iterable, depth: int = 4):
+        import queue
+        import threading
+
+        self._q: "queue.Queue" = queue.Queue(maxsize=max(1, int(depth)))
+        self._stop = threading.Event()
+
+        def run():
+            try:
+                for x in it:
+                    while not self._stop.is_set():
+                        try:
+                            self._q.put(x, timeout=0.1)
+                            break
+                        except queue.Full:
+                            continue
+                    if self._stop.is_set():
+                        return
+                self._q.put(self._END)
+            except BaseException as e:  # noqa: BLE001 - handed to the consumer
+                self._q.put(e)
+
+        self._t = threading.Thread(target=run, daemon=True, name="sft-prefetch")
+        self._t.start()
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        x = self._q.get()
+        if x is self._END:
+            raise StopIteration
+        if isinstance(x, BaseException):
+            raise x
+        return x
+
+    def close(self):
+        self._stop.set()

@@ -492,7 +492,7 @@ class _SFTRunner:
     """One ``step()`` = one global batch of the streaming SFT dataset."""
 
     def __init__(self, actor, args):
-        from ..data.sft import StreamingSFTDataset, pack_batches
+        from ..data.sft import Prefetcher, StreamingSFTDataset, batches_with_cursor
 
         self.actor = actor
         files = [p for p in str(args.prompt_data).split(",") if p]
@@ -506,10 +506,37 @@ class _SFTRunner:
         if actor.role == "seq_cls":
             self.batches = self._classification_batches(files, tok, per_rank, args)
         else:
-            self.batches = pack_batches(ds, max_tokens=1 << 30, max_samples=per_rank)
+            # batches are tokenised ahead of the step by a background thread (--sft-prefetch-buffer-size, counted in samples)
+            depth = max(1, int(_get(args, "sft_prefetch_buffer_size", 64)) // per_rank)
+            self._pairs = Prefetcher(batches_with_cursor(ds, per_rank), depth)
+            self.batches = self._consume(self._pairs)
         self.dataset = ds
+        self._cursor = ds.state_dict()
+        self.data_source = self            # what the controller saves / restores next to a checkpoint
         self._init_eval(args, files, tok)
         self._init_predict(args, files, tok)
+
+    def _consume(self, pairs):
+        for batch, state in pairs:
+            self._cursor = state
+            yield batch
+
+    def state_dict(self) -> dict:
+        """Where the data stream stands after the last batch that was trained on."""
+        return dict(self._cursor, steps=getattr(self, "steps", 0))
+
+    def load_state_dict(self, st: dict):
+        from ..data.sft import Prefetcher, batches_with_cursor
+
+        if getattr(self, "_pairs", None) is None:
+            return                       # classification batches restart from the top of their files
+        self._pairs.close()
+        self.dataset.load_state_dict(st)
+        self._cursor = self.dataset.state_dict()
+        self.steps = int(st.get("steps", 0))
+        per_rank = max(1, self.actor.cfg.global_batch_size // self.actor.ps.dp.size)
+        self._pairs = Prefetcher(batches_with_cursor(self.dataset, per_rank), self._pairs._q.maxsize)
+        self.batches = self._consume(self._pairs)
 
     def _classification_batches(self, files, tok, per_rank, args):
         """``{"text" | "prompt": ..., "label": id | [ids] | multi-hot}`` rows -> batches with ``labels``

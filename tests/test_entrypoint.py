@@ -262,3 +262,29 @@ def test_sft_periodic_evaluation_ppl_and_classification(tmp_path):
     lines = [json.loads(l) for l in open(os.path.join(save2, "metrics.jsonl"))]
     ev = [l for l in lines if "eval/accuracy" in l]
     assert len(ev) == 2 and ev[-1]["eval/samples"] == 8 and ev[-1]["eval/accuracy"] >= 0.75 and 0 <= ev[-1]["eval/macro_f1"] <= 1
+
+
+def test_sft_resume_continues_the_data_stream(tmp_path):
+    """The SFT data cursor travels with the checkpoint: a resumed run trains on the samples that follow the last trained
+    batch (not on what the prefetcher had already read, and not from the top of the file)."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    data = tmp_path / "sft.jsonl"
+    with open(data, "w") as f:
+        for i in range(40):
+            f.write(json.dumps({"prompt": f"q{i}", "response": f"a{i}"}) + "\n")
+    save = str(tmp_path / "ck")
+    base = ["--model-name", "tiny", "--loss-type", "sft_loss", "--prompt-data", str(data), "--global-batch-size", "4", "--lr", "1e-3",
+            "--max-tokens-per-gpu", "512", "--save", save, "--save-interval", "1", "--sft-prefetch-buffer-size", "16"]
+    assert main(base + ["--num-rollout", "3"]) == 0
+    it = dist_ckpt.read_latest_iteration(save)
+    st = json.load(open(os.path.join(dist_ckpt.iter_dir(save, it), "rollout_data_source.json")))
+    assert st["line"] == 12 and st["file_index"] == 0                 # three batches of four samples were trained on
+    c = Controller(parse_args(base + ["--num-rollout", "5", "--load", save]), device="cpu")
+    assert c.runner.state_dict()["line"] == 12
+    nxt = next(c.runner.batches)
+    from relax_b200.data.tokenizer import ByteCodec
+
+    text = ByteCodec(c.model_cfg.vocab_size).decode(nxt["tokens"][0])
+    assert "q12" in text and "a12" in text
