@@ -163,6 +163,15 @@ class TrainActor:
                 raise ValueError("the freeze lists leave no trainable parameter")
         self.optimizer = DistributedOptimizer(self.model, self.ps, cfg.optim) if with_optimizer else None
         self.timer = Timer()
+        # trajectory replay capture (utils/replay.py): off unless RELAX_REPLAY_CAPTURE_DIR is set
+        from ..utils.replay import ReplayRecorder, run_identity
+
+        self.replay = ReplayRecorder.from_env(
+            dist.get_rank() if dist.is_initialized() else 0,
+            run_identity(model_cfg.name, cfg.loss, {"dp": [ps.dp.rank, ps.dp.size], "tp": [ps.tp.rank, ps.tp.size],
+                                                     "cp": [ps.cp.rank, ps.cp.size], "pp": [ps.pp.rank, ps.pp.size]}, model_cfg.dtype)
+        ) if os.environ.get("RELAX_REPLAY_CAPTURE_DIR") else ReplayRecorder(None)
+        self._cur_rollout, self._cur_step = -1, 0
         self.weight_version = 0
         self.snapshots: dict[str, torch.Tensor] = {}
         self._active_tag = "actor"
@@ -753,6 +762,12 @@ class TrainActor:
             )
             batch["advantages"] = seg_all.split(adv)
             batch["returns"] = seg_all.split(ret)
+            if self.replay.wants("advantages", rollout_id) and not (self.ps.dp.size > 1 and cfg.normalize_advantages):
+                self.replay.capture("advantages", rollout_id, dict(
+                    estimator=cfg.advantage_estimator, rewards=rewards, seg=seg_all, loss_mask=mask_all, log_probs=cat("log_probs"),
+                    ref_log_probs=cat("ref_log_probs"), values=cat("values"), kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type,
+                    gamma=cfg.gamma, lambd=cfg.lambd, normalize_advantages=cfg.normalize_advantages),
+                    {"advantages": adv, "returns": ret})
         elif cfg.loss.custom_loss_function is None and self.role == "actor":
             raise ValueError("--disable-compute-advantages-and-returns needs a custom loss function (the policy losses read "
                              "the advantages)")
@@ -824,6 +839,7 @@ class TrainActor:
         for s in range(int(nsteps) if update_policy else 0):
             idx = list(range(s * per_step, min(n, (s + 1) * per_step)))
             with self.timer.span("train_step"):
+                self._cur_rollout, self._cur_step = rollout_id, s
                 m, last_norm = self._train_step(batch, idx)
             if cfg.ci is not None and (cfg.ci.enabled or cfg.ci.save_grad_norm or cfg.ci.load_grad_norm):
                 from . import ci_utils as CI
@@ -912,6 +928,10 @@ class TrainActor:
             else:
                 lp, en = self._forward_logp(pb, cfg.compute_entropy)
                 loss, m = L.policy_loss(lp, en, lb, cfg.loss)
+                if self.replay.wants("loss", self._cur_rollout, self._cur_step) and ps.cp.size == 1:
+                    # what the loss consumed and produced (post-forward statistics, no logits, no weights)
+                    self.replay.capture("loss", self._cur_rollout, dict(log_probs=lp.detach(), entropy=en.detach(), batch=lb, cfg=cfg.loss),
+                                        {"loss": loss.detach(), "metrics": m}, step_id=self._cur_step)
             if self.mcfg.dsa_topk > 0:
                 from ..models.hybrid import collect_indexer_loss
 

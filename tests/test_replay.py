@@ -28,8 +28,8 @@ def test_capture_and_replay_roundtrip(tmp_path):
     # a changed implementation is flagged with the path of the first difference
     bad = dict(fns)
     bad["loss"] = lambda **kw: {"loss": fns["loss"](**kw)["loss"] * 1.01, "metrics": fns["loss"](**kw)["metrics"]}
-    rep = replay_bundle(str(tmp_path), bad)
-    assert rep[0]["ok"] is False and rep[0]["diffs"][0][0] == "out.loss" and rep[1]["ok"]
+    rep = {r["stage"]: r for r in replay_bundle(str(tmp_path), bad)}       # reports come in run order: advantages, then loss
+    assert rep["loss"]["ok"] is False and rep["loss"]["diffs"][0][0] == "out.loss" and rep["advantages"]["ok"]
     assert torch.is_tensor(out["loss"])
 
 
@@ -134,3 +134,54 @@ def test_rollout_routing_replay_r3_engine_choices_drive_the_trainer():
         assert torch.equal(out[:want.shape[0]], want)
         # same weights, same routing: the engine's log-probs are the trainer's old-policy log-probs
         assert abs(m["ppo_kl"]) < 1e-6
+
+
+def test_capture_in_a_training_run_and_the_offline_tools(tmp_path, monkeypatch):
+    """RELAX_REPLAY_CAPTURE_DIR on a colocated GRPO run: the advantage and loss stages of the chosen rollouts are
+    written by the background writer; the bundle validates, replays clean on this host, names the first divergence
+    when an implementation changes, and notices a record that was tampered with."""
+    import json
+    import os
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.utils import replay as R
+
+    root = tmp_path / "bundles"
+    monkeypatch.setenv("RELAX_REPLAY_CAPTURE_DIR", str(root))
+    monkeypatch.setenv("RELAX_REPLAY_CAPTURE_ROLLOUTS", "1,2")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "4", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "3", "--rollout-max-response-len", "6", "--lr", "1e-3", "--rm-type", "token_sum_parity",
+                    "--use-kl-loss", "--kl-loss-coef", "0.01", "--max-tokens-per-gpu", "4096"])       # one micro-batch per optimizer step
+    c = Controller(a, device="cpu")
+    for _ in range(3):
+        c.runner.step()
+    c.runner.actor.replay.close()
+    c.runner.close()
+    bundle = str(root / "rank-0")
+    m = R.load_manifest(bundle)
+    assert m["identity"]["model"] == "tiny" and m["identity"]["layout"]["dp"] == [0, 1] and len(m["identity"]["config_sha"]) == 16
+    recs = R.select_records(m["records"])
+    assert {r["rollout_id"] for r in recs} == {1, 2}                              # rollout 0 was not asked for
+    # two optimizer steps of four samples, one micro-batch per sample: one record per micro-batch
+    assert [r["stage"] for r in recs if r["rollout_id"] == 1] == ["advantages"] + ["loss"] * 8
+    assert [r["step_id"] for r in recs if r["rollout_id"] == 1] == [None] + [0] * 4 + [1] * 4 and all(r["sha256"] for r in recs)
+    assert R.validate_bundle(bundle) == [] and R.validate_bundle(str(root)) == []
+    assert R.main(["validate", bundle]) == 0 and R.main(["replay", bundle, "--stage", "loss"]) == 0 and R.main(["inspect", str(root)]) == 0
+    reps = R.replay_bundle(str(root))
+    assert len(reps) == 18 and all(r["ok"] for r in reps) and R.first_divergence(reps) is None
+    only = R.replay_bundle(bundle, stages=["loss"], steps=[(2, 1)])
+    assert [(r["rollout_id"], r["step_id"]) for r in only] == [(2, 1)] * 4
+    # a changed advantage estimator is found at the first record it touches
+    fns = R.default_stage_functions()
+    good = fns["advantages"]
+    fns["advantages"] = lambda **kw: {k: v * 1.001 for k, v in good(**kw).items()}
+    first = R.first_divergence(R.replay_bundle(bundle, fns))
+    assert first["stage"] == "advantages" and first["rollout_id"] == 1 and first["field"].startswith("out.")
+    # integrity: a modified record and a missing COMPLETE marker are reported
+    victim = os.path.join(bundle, recs[1]["file"])
+    with open(victim, "ab") as f:
+        f.write(b"x")
+    os.remove(os.path.join(bundle, "COMPLETE"))
+    problems = R.validate_bundle(bundle)
+    assert any("checksum" in p for p in problems) and any("COMPLETE" in p for p in problems) and R.main(["validate", bundle]) == 1
