@@ -293,7 +293,6 @@ FLAG_POLICY: dict[str, tuple] = {
     "--train-backend": (_R, "there is one trainer (this package); Megatron-LM is not used"),
     # rollout behaviour
     "--sglang-dp-size": (_R, "rollout engines are replicated per engine group, not data-parallel inside one engine"),
-    "--agentic-custom-advantage-path": (_R, "explicit exports are scored by their reward; no custom group advantage hook"),
     # algorithm
     "--genrm-num-gpus": (_R, "grader engines either share the rollout ranks (--genrm-model-path) or run as engine servers on their own "
                              "GPUs, started with `serve engine` and named by --genrm-engine-addrs; this job does not launch them"),

@@ -56,6 +56,11 @@ def convert_samples_to_train_data(samples: Sequence[Sample], *, advantage_estima
         batch["rollout_routed_experts"] = [s.rollout_routed_experts for s in samples]
     if any(s.multimodal_train_inputs for s in samples):
         batch["multimodal_train_inputs"] = [s.multimodal_train_inputs for s in samples]
+    if any(s.custom_advantage is not None for s in samples):
+        # advantages set by user code (agentic exports): they replace the estimator's, one scalar per sample
+        if not all(s.custom_advantage is not None or s.remove_sample for s in samples):
+            raise ValueError("custom advantages must be set on every sample of the batch (or on none)")
+        batch["custom_advantages"] = [float(s.custom_advantage or 0.0) for s in samples]
     if any(s.teacher_log_probs is not None for s in samples):
         batch["teacher_log_probs"] = [s.teacher_log_probs for s in samples]
     if any(s.metadata for s in samples):

@@ -35,16 +35,28 @@ from .agent_runner import AgentExecutionError, AgentLauncher, AgentSpec, Managed
 from .agentic import Tokenizer
 
 
+def rollout_mode_is_train(mode: str) -> bool:
+    return mode == "train"
+
+
 class AgentPipeline:
     def __init__(self, spec: AgentSpec, tok: Tokenizer, concurrency: int = 32, admission: bool = True,
                  admission_headroom: float = 0.9, admission_pressure: float = 0.92, admission_max_wait_s: float = 30.0,
                  max_context: Optional[int] = None, socket_path: Optional[str] = None, rollout_mode: str = "train",
-                 tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None):
+                 tool_call_parser: Optional[str] = None, reasoning_parser: Optional[str] = None,
+                 custom_advantage_path: Optional[str] = None):
         self.spec, self.tok, self.concurrency = spec, tok, max(1, int(concurrency))
         self.use_admission, self.headroom = admission, admission_headroom
         self.pressure, self.max_wait_s = admission_pressure, admission_max_wait_s
         self.max_context, self.socket_path, self.rollout_mode = max_context, socket_path, rollout_mode
         self.tool_call_parser, self.reasoning_parser = tool_call_parser, reasoning_parser
+        # --agentic-custom-advantage-path: ``fn(samples of one prompt group) -> one number per sample``; the numbers become
+        # the samples' advantages instead of the estimator's (relax/agentic/pipeline/reward.py custom_advantage_func)
+        self.custom_advantage = None
+        if custom_advantage_path:
+            from .custom_generate import load_function
+
+            self.custom_advantage = load_function(custom_advantage_path, 1, "custom advantage function")
         self.stats: Dict[str, float] = {}
         self._seq = itertools.count(1)
 
@@ -112,6 +124,20 @@ class AgentPipeline:
         for s in samples:
             if s.group_index in failed_groups:
                 self._drop(s)
+        if self.custom_advantage is not None and rollout_mode_is_train(self.rollout_mode):
+            groups: Dict[object, list] = {}
+            for s in samples:
+                if s.group_index not in failed_groups:
+                    groups.setdefault(s.group_index, []).append(s)
+            for g in groups.values():
+                vals = list(self.custom_advantage(g))
+                if len(vals) != len(g) or any(isinstance(v_, bool) or not isinstance(v_, (int, float)) for v_ in vals):
+                    raise TypeError("the custom advantage function returns one number per sample of the group")
+                for s, v_ in zip(g, vals):
+                    s.custom_advantage = float(v_)
+            for s in samples:
+                if s.group_index in failed_groups:
+                    s.custom_advantage = 0.0
         self.stats = {"agentic/sessions": float(len(samples)), "agentic/failed_groups": float(len(failed_groups)),
                       "agentic/wall_s": time.perf_counter() - t0,
                       "agentic/turns_mean": sum((s.metadata or {}).get("turns", 0) for s in samples) / max(1, len(samples))}
@@ -189,7 +215,7 @@ def configure(args, codec=None) -> AgentPipeline:
             admission=bool(g("agentic_program_admission", False)), admission_headroom=g("agentic_admission_headroom", 0.9),
             admission_pressure=g("agentic_admission_pressure_threshold", 0.92), admission_max_wait_s=g("agentic_admission_max_wait_s", 30.0),
             socket_path=ensure_launcher_daemon(), tool_call_parser=g("agentic_tool_call_parser", None),
-            reasoning_parser=g("agentic_reasoning_parser", None))
+            reasoning_parser=g("agentic_reasoning_parser", None), custom_advantage_path=g("agentic_custom_advantage_path", None))
     return _PIPELINE
 
 

@@ -759,6 +759,8 @@ class TrainActor:
                 log_probs=cat("log_probs"), ref_log_probs=cat("ref_log_probs"), values=cat("values"),
                 kl_coef=cfg.kl_coef, kl_loss_type=cfg.loss.kl_loss_type, gamma=cfg.gamma, lambd=cfg.lambd,
                 normalize_advantages=cfg.normalize_advantages, dp_group=self.ps.dp.group, stats_out=adv_stats,
+                custom_advantage=(torch.as_tensor(batch["custom_advantages"], dtype=torch.float32, device=dev)
+                                  if batch.get("custom_advantages") is not None else None),
             )
             batch["advantages"] = seg_all.split(adv)
             batch["returns"] = seg_all.split(ret)

@@ -181,3 +181,28 @@ def test_use_agentic_rollout_through_the_controller(tmp_path):
         assert "loss" in m and m["agentic/admission_peak_reserved"] > 0
     finally:
         R.stop_launcher_daemon(agent_pipeline._PIPELINE.socket_path)
+
+
+def test_custom_group_advantage_for_agent_rollouts(tmp_path):
+    """``--agentic-custom-advantage-path``: user code turns a prompt group's samples into advantages; the trainer uses
+    them as they are (the estimator's group normalisation is bypassed)."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout import agent_pipeline
+
+    (tmp_path / "agent.py").write_text(AGENT)
+    (tmp_path / "adv.py").write_text("def rank_in_group(samples):\n    return [float(i) - 0.5 for i, _ in enumerate(samples)]\n")
+    f = tmp_path / "prompts.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"task {i}", "label": None}) for i in range(2)) + "\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "5", "--rollout-max-prompt-len", "256", "--prompt-data", str(f),
+                    "--input-key", "prompt", "--use-agentic-rollout", "--agent-command", f"{sys.executable} agent.py",
+                    "--agent-cwd", str(tmp_path), "--agentic-custom-advantage-path", f"{tmp_path / 'adv.py'}:rank_in_group"])
+    c = Controller(a, device="cpu")
+    try:
+        samples = c.runner.generate(0)
+        assert [s.custom_advantage for s in samples] == [-0.5, 0.5, -0.5, 0.5]
+        m = c.runner.step()
+        assert abs(m["rollout/advantages"]) < 1e-6 and "loss" in m          # mean of -0.5 / +0.5 over equally long responses
+    finally:
+        R.stop_launcher_daemon(agent_pipeline._PIPELINE.socket_path)
