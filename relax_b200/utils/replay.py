@@ -118,8 +118,12 @@ class ReplayRecorder:
                 raise ValueError
         except ValueError:
             raise ValueError("RELAX_REPLAY_CAPTURE_ROLLOUTS is 'id,id,...' and RELAX_REPLAY_CAPTURE_STEPS 'rollout:step,...'") from None
-        return cls(os.path.join(root, f"rank-{rank}"), max_records=int(os.environ.get("RELAX_REPLAY_CAPTURE_MAX", "64")), rank=rank,
-                   identity=identity, rollouts=rollouts, steps=steps, background=True)
+        rec = cls(os.path.join(root, f"rank-{rank}"), max_records=int(os.environ.get("RELAX_REPLAY_CAPTURE_MAX", "64")), rank=rank,
+                  identity=identity, rollouts=rollouts, steps=steps, background=True)
+        import atexit
+
+        atexit.register(rec.close)            # a run that ends normally leaves a complete bundle behind
+        return rec
 
     @property
     def enabled(self) -> bool:
@@ -168,7 +172,10 @@ class ReplayRecorder:
                 pass
 
     def close(self):
-        """Flush the writer and mark the bundle complete."""
+        """Flush the writer and mark the bundle complete (safe to call twice)."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
         if self._q is not None:
             self._q.put(None)
             self._thread.join(timeout=60)
