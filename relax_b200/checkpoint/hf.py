@@ -431,7 +431,8 @@ def load_hf_into_rollout(path: str, cfg: ModelConfig, rollout_weights) -> None:
     from ..weight_sync.sync import apply_block
 
     full = hf_to_megatron_state(cfg, load_hf_checkpoint(path, dequantize=True, dtype=rollout_weights.dtype))
-    for b in build_plan(cfg, TrainerLayout(1, 1, 1), rollout_weights.tp_size, rollout_weights.ep_size):
+    for b in build_plan(cfg, TrainerLayout(1, 1, 1), rollout_weights.tp_size, rollout_weights.ep_size,
+                        mtp=bool(getattr(rollout_weights, "mtp", False))):         # the draft block too, when the engine speculates
         mine = rollout_weights.ep_rank if ".experts." in b.src_name else rollout_weights.tp_rank
         if b.dst_rank == mine:
             apply_block(b, full[b.src_name].to(rollout_weights.device), rollout_weights.p[b.dst_name])

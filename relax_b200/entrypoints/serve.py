@@ -26,6 +26,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="relax_b200 control-plane services")
     ap.add_argument("service", choices=["metrics", "coordinator", "viewer", "teacher", "router", "engine"])
     ap.add_argument("--kv-blocks", type=int, default=4096, help="engine: KV-cache blocks of 16 tokens")
+    ap.add_argument("--speculative-steps", type=int, default=0,
+                    help="engine: proposals per pass drafted by the model's multi-token-prediction block (0 = off)")
     ap.add_argument("--workers", nargs="*", default=None, help="router: base URLs of the engine servers to start with")
     ap.add_argument("--router-timeout", type=float, default=600.0)
     ap.add_argument("--router-health-check-failure-threshold", type=int, default=3)
@@ -66,7 +68,8 @@ def main(argv=None) -> int:
         dev = a.device or ("cuda" if torch.cuda.is_available() else "cpu")
         cfg = get_config(a.model_name)
         eng = RolloutEngine(cfg, device=dev, dtype=torch.bfloat16 if dev.startswith("cuda") else torch.float32,
-                            num_kv_blocks=a.kv_blocks, block_size=16, seed=a.seed)
+                            num_kv_blocks=a.kv_blocks, block_size=16, seed=a.seed, speculative=a.speculative_steps > 0,
+                            speculative_steps=max(1, a.speculative_steps))
         if a.hf_checkpoint:
             from ..checkpoint import hf as H
 

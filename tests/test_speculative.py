@@ -215,3 +215,21 @@ def test_a_trained_block_halves_the_number_of_passes():
     spec.speculative_steps = 3
     out = spec.generate([seq(s, 8) for s in (1, 7, 20)], SamplingParams(temperature=0.0, max_new_tokens=24))
     assert all(r.output == seq(s, 32)[8:] and r.spec_verify == 6 and r.spec_accept == 17 for s, r in zip((1, 7, 20), out))
+
+
+def test_hf_checkpoint_with_mtp_block_loads_into_a_speculating_engine(tmp_path):
+    """A Hugging Face checkpoint of an MTP model fills a speculating engine directly (serving without a trainer): the
+    draft block's tensors arrive with the rest and the engine's output equals a plain engine's."""
+    from relax_b200.checkpoint import hf as H
+
+    cfg, model, plain, spec = _engines(seed=21)
+    d = str(tmp_path / "hf")
+    H.save_hf_checkpoint(d, cfg, H.convert_state_to_hf(cfg, {k: v.detach() for k, v in model.named_parameters()}))
+    fresh = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, speculative=True, speculative_steps=2)
+    fresh.weights.flat.zero_()
+    H.load_hf_into_rollout(d, cfg, fresh.weights)
+    for k, v in spec.weights.p.items():
+        assert torch.equal(fresh.weights.p[k], v), k
+    prompt = [5, 9, 17, 33, 2, 8]
+    sp = SamplingParams(temperature=0.0, max_new_tokens=9)
+    assert fresh.generate([prompt], sp)[0].output == plain.generate([prompt], sp)[0].output
