@@ -258,17 +258,24 @@ def serve(service: ChatService, host: str = "127.0.0.1", port: int = 0):
             self.wfile.write(data)
 
         def do_GET(self):
-            if self.path == "/health":
-                return self._reply(200, {"status": "ok"})
-            if self.path == "/v1/models":
-                return self._reply(200, {"object": "list", "data": [{"id": service.model_name, "object": "model"}]})
+            path = self.path.split("?")[0].rstrip("/") or "/"
+            if path in ("/health", "/healthz"):
+                return self._reply(200, {"status": "ok", "ok": True})
+            if path in ("/v1/models", "/models"):
+                return self._reply(200, {"object": "list", "data": [{"id": service.model_name, "object": "model", "created": 0,
+                                                                    "owned_by": "relax_b200"}]})
+            if path == "/debug_state":      # relax/agentic/session/service.py:2251: what the service holds right now
+                ss = list(service.forest.sessions.values())
+                return self._reply(200, {"session_count": len(ss), "open_sessions": len(service.by_key),
+                                         "turns": sum(s_.turns for s_ in ss), "tokens": sum(len(s_.tokens) for s_ in ss),
+                                         "admission": service.admission.metrics() if service.admission is not None else None})
             self._reply(404, {"error": {"message": "unknown route", "type": "invalid_request_error"}})
 
         def do_POST(self):
             n = int(self.headers.get("Content-Length", "0"))
             try:
                 body = json.loads(self.rfile.read(n) or b"{}")
-                if self.path == "/v1/chat/completions":
+                if self.path.split("?")[0].rstrip("/") in ("/v1/chat/completions", "/chat/completions", ""):
                     if body.get("stream"):
                         raise ValueError("streaming responses are not supported")
                     return self._reply(200, service.chat(body, self.headers.get("X-Session-Id")))

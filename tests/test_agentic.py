@@ -93,6 +93,14 @@ def test_openai_endpoint_roundtrip_and_session_sample():
         assert sum(smp.loss_mask) == 8 and smp.reward == 1.0 and "pong" in TOK.decode(smp.tokens)
         models = json.loads(urllib.request.urlopen(url + "/v1/models", timeout=10).read())
         assert models["data"][0]["id"] == svc.model_name
+        # the short forms of the routes, and the state page
+        assert json.loads(urllib.request.urlopen(url + "/models", timeout=10).read())["data"][0]["id"] == svc.model_name
+        assert json.loads(urllib.request.urlopen(url + "/healthz", timeout=10).read())["ok"] is True
+        req = urllib.request.Request(url + "/chat/completions", data=json.dumps({"messages": [{"role": "user", "content": "x"}]}).encode(),
+                                     headers={"Content-Type": "application/json", "X-Session-Id": "s2"})
+        assert json.loads(urllib.request.urlopen(req, timeout=10).read())["choices"][0]["message"]["content"] == "ping"
+        st = json.loads(urllib.request.urlopen(url + "/debug_state", timeout=10).read())
+        assert st["session_count"] == 2 and st["open_sessions"] == 1 and st["turns"] == 3
     finally:
         srv.shutdown()
 
