@@ -78,6 +78,13 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
         x = p.view(ng, qpg + 2, hd)
         return [(pre + "self_attn.q_proj.bias", x[:, :qpg].reshape(-1)), (pre + "self_attn.k_proj.bias", x[:, qpg].reshape(-1)),
                 (pre + "self_attn.v_proj.bias", x[:, qpg + 1].reshape(-1))]
+    if rest.startswith("self_attention.gdn."):
+        return _gdn_to_hf(cfg, pre, rest[len("self_attention.gdn."):], p)
+    if rest.startswith("self_attention.dsa."):
+        sub = rest[len("self_attention.dsa."):]
+        if sub not in _MLA_NAMES:
+            raise ValueError(f"unknown latent-attention parameter {rest!r}")
+        return [(pre + "self_attn." + _MLA_NAMES[sub], p)]
     simple = {
         "self_attention.linear_proj.weight": "self_attn.o_proj.weight",
         "self_attention.linear_qkv.layer_norm_weight": "input_layernorm.weight",
@@ -112,11 +119,72 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
     raise ValueError(f"unknown layer parameter {rest!r}")
 
 
+# multi-head latent attention under its DeepSeek-V3 names (relax/backends/megatron/weight_conversion/deepseekv3.py); the
+# lightning indexer of the sparse variant keeps its own small projections next to them
+_MLA_NAMES = {
+    "linear_q_down_proj.weight": "q_a_proj.weight", "linear_q_up_proj.layer_norm_weight": "q_a_layernorm.weight",
+    "linear_q_up_proj.weight": "q_b_proj.weight", "linear_kv_down_proj.weight": "kv_a_proj_with_mqa.weight",
+    "linear_kv_up_proj.layer_norm_weight": "kv_a_layernorm.weight", "linear_kv_up_proj.weight": "kv_b_proj.weight",
+    "linear_proj.weight": "o_proj.weight", "indexer.linear_wq.weight": "indexer.wq_b.weight",
+    "indexer.linear_wk.weight": "indexer.wk.weight", "indexer.linear_weights.weight": "indexer.weights_proj.weight",
+}
+
+
+def _gdn_perm(cfg: ModelConfig, what: str) -> torch.Tensor:
+    """Row order that turns this package's flat Gated-DeltaNet projections into the Hugging Face ones.  Here the rows
+    of ``in_proj_qkvz`` are ``[q of all key heads | k | v of all value heads | z]`` and those of ``in_proj_ba``
+    ``[b | a]``; Hugging Face (Qwen3-Next ``fix_query_key_value_ordering``) groups them per KEY head:
+    ``[q_h | k_h | v of the head's value heads | z of the same]`` and ``[b of the head's value heads | a ...]``."""
+    hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+    r, kd, vd = hv // hk, hk * d, hv * d
+    rows = []
+    for h in range(hk):
+        if what == "qkvz":
+            rows += list(range(h * d, (h + 1) * d))                                  # q_h
+            rows += list(range(kd + h * d, kd + (h + 1) * d))                        # k_h
+            rows += list(range(2 * kd + h * r * d, 2 * kd + (h + 1) * r * d))        # v of value heads h*r .. h*r + r - 1
+            rows += list(range(2 * kd + vd + h * r * d, 2 * kd + vd + (h + 1) * r * d))   # z of the same heads
+        else:
+            rows += list(range(h * r, (h + 1) * r)) + list(range(hv + h * r, hv + (h + 1) * r))
+    return torch.tensor(rows)
+
+
+def _gdn_to_hf(cfg: ModelConfig, pre: str, sub: str, p: torch.Tensor) -> list:
+    """Gated-DeltaNet tensors under their Qwen3-Next names (relax/backends/megatron/weight_conversion/qwen3_next.py
+    :176-184 passes ``linear_attn.*`` through)."""
+    la = pre + "linear_attn."
+    if sub == "in_proj_qkvz.weight":
+        return [(la + sub, p.index_select(0, _gdn_perm(cfg, "qkvz").to(p.device)))]
+    if sub == "in_proj_ba.weight":
+        return [(la + sub, p.index_select(0, _gdn_perm(cfg, "ba").to(p.device)))]
+    if sub == "conv1d.weight":
+        return [(la + sub, p.unsqueeze(1))]              # [channels, 1, taps]: channels are [q | k | v] on both sides
+    if sub in ("dt_bias", "A_log", "norm.weight", "out_proj.weight"):
+        return [(la + sub, p)]
+    raise ValueError(f"unknown Gated-DeltaNet parameter {sub!r}")
+
+
+def _gdn_from_hf(cfg: ModelConfig, hf: dict, pre: str, b: str, out: dict) -> None:
+    la, g = pre + "linear_attn.", b + "self_attention.gdn."
+    for what in ("qkvz", "ba"):
+        perm = _gdn_perm(cfg, what)
+        inv = torch.empty_like(perm)
+        inv[perm] = torch.arange(perm.numel())
+        w = hf[la + f"in_proj_{what}.weight"]
+        out[g + f"in_proj_{what}.weight"] = w.index_select(0, inv.to(w.device))
+    c = hf[la + "conv1d.weight"]
+    out[g + "conv1d.weight"] = c[:, 0] if c.dim() == 3 else c
+    for sub in ("dt_bias", "A_log", "norm.weight", "out_proj.weight"):
+        out[g + sub] = hf[la + sub]
+
+
 _NORM_SUFFIXES = ("norm.weight", "layernorm.weight", "layer_norm_weight")
 
 
 def _is_norm(name: str) -> bool:
-    return name.endswith(_NORM_SUFFIXES)
+    """Norm weights that a zero-centred checkpoint stores as ``gamma - 1``.  The gated norm inside a Gated-DeltaNet
+    mixer is an ordinary RMSNorm in those checkpoints too (Qwen3-Next ``Qwen3NextRMSNormGated``)."""
+    return name.endswith(_NORM_SUFFIXES) and "linear_attn.norm." not in name
 
 
 def _vision_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list:
@@ -187,6 +255,19 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
             out[f"mtp.layers.{k}.hnorm.weight"] = hf[pre + "hnorm.weight"]
             out[f"mtp.layers.{k}.eh_proj.weight"] = hf[pre + "eh_proj.weight"]
             out[f"mtp.layers.{k}.final_layernorm.weight"] = hf[pre + "shared_head.norm.weight"]
+        from ..models.hybrid import mixer_kind
+
+        kind = mixer_kind(cfg, i) if i < cfg.num_layers else "attention"
+        if kind == "gdn":
+            _gdn_from_hf(cfg, hf, pre, b, out)
+        elif kind == "dsa":
+            for ours, theirs in _MLA_NAMES.items():
+                if (pre + "self_attn." + theirs) in hf:
+                    out[b + "self_attention.dsa." + ours] = hf[pre + "self_attn." + theirs]
+        if kind != "attention":
+            out[b + "self_attention.linear_qkv.layer_norm_weight"] = hf[pre + "input_layernorm.weight"]
+            _mlp_from_hf(cfg, hf, i, pre, b, out)
+            continue
         k = hf[pre + "self_attn.k_proj.weight"].view(ng, 1, hd, H)
         v = hf[pre + "self_attn.v_proj.weight"].view(ng, 1, hd, H)
         if cfg.attention_output_gate:
@@ -208,6 +289,13 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
         if cfg.qk_layernorm:
             out[b + "self_attention.q_layernorm.weight"] = hf[pre + "self_attn.q_norm.weight"]
             out[b + "self_attention.k_layernorm.weight"] = hf[pre + "self_attn.k_norm.weight"]
+        _mlp_from_hf(cfg, hf, i, pre, b, out)
+    return out
+
+
+def _mlp_from_hf(cfg: ModelConfig, hf: dict, i: int, pre: str, b: str, out: dict) -> None:
+    """The feed-forward half of layer ``i`` (dense or mixture of experts) and the norm in front of it."""
+    if True:
         if cfg.is_moe_layer(i):
             out[b + "pre_mlp_layernorm.weight"] = hf[pre + "post_attention_layernorm.weight"]
             out[b + "mlp.router.weight"] = hf[pre + "mlp.gate.weight"]
@@ -228,7 +316,6 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
             out[b + "mlp.linear_fc1.layer_norm_weight"] = hf[pre + "post_attention_layernorm.weight"]
             out[b + "mlp.linear_fc1.weight"] = torch.cat([hf[pre + "mlp.gate_proj.weight"], hf[pre + "mlp.up_proj.weight"]], 0)
             out[b + "mlp.linear_fc2.weight"] = hf[pre + "mlp.down_proj.weight"]
-    return out
 
 
 def hf_config_dict(cfg: ModelConfig) -> dict:

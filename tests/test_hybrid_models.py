@@ -294,3 +294,59 @@ def test_latent_attention_in_the_rollout_engine_matches_the_trainer(name):
     m = c.runner.step()
     assert m["train_rollout_logprob_abs_diff"] < 1e-4, m["train_rollout_logprob_abs_diff"]
     c.runner.close()
+
+
+def test_hf_names_and_layouts_of_hybrid_and_latent_families(tmp_path):
+    """Checkpoint conversion for the Gated-DeltaNet and latent-attention families: Qwen3-Next ``linear_attn.*`` names
+    with the projections grouped per key head (checked against the split Hugging Face applies to the projection's
+    output), DeepSeek-V3 names for MLA / DSA, exact round trips, and a checkpoint on disk that loads into a trainer and
+    straight into a rollout engine."""
+    from relax_b200.checkpoint import hf as H
+    from relax_b200.models.transformer import GPTModel
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+
+    cfg = get_config("tiny-qwen35")
+    model = GPTModel(cfg, seed=3)
+    st = {k: v.detach() for k, v in model.named_parameters()}
+    hf = H.convert_state_to_hf(cfg, st)
+    back = H.hf_to_megatron_state(cfg, hf)
+    assert all(torch.equal(back[k], v) for k, v in st.items()) and len(back) == len(st)
+    hk, hv, d = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+    r, kd, vd = hv // hk, hk * d, hv * d
+    x = torch.randn(5, cfg.hidden_size)
+    ours = x @ st["decoder.layers.0.self_attention.gdn.in_proj_qkvz.weight"].t()
+    theirs = (x @ hf["model.layers.0.linear_attn.in_proj_qkvz.weight"].t()).view(5, hk, 2 * d + 2 * r * d)
+    q, k, v, z = torch.split(theirs, [d, d, r * d, r * d], dim=-1)             # what the Hugging Face module does
+    assert torch.equal(q.reshape(5, kd), ours[:, :kd]) and torch.equal(k.reshape(5, kd), ours[:, kd:2 * kd])
+    assert torch.equal(v.reshape(5, vd), ours[:, 2 * kd:2 * kd + vd]) and torch.equal(z.reshape(5, vd), ours[:, 2 * kd + vd:])
+    ba = (x @ hf["model.layers.0.linear_attn.in_proj_ba.weight"].t()).view(5, hk, 2 * r)
+    ours_ba = x @ st["decoder.layers.0.self_attention.gdn.in_proj_ba.weight"].t()
+    assert torch.equal(ba[..., :r].reshape(5, hv), ours_ba[:, :hv]) and torch.equal(ba[..., r:].reshape(5, hv), ours_ba[:, hv:])
+    assert hf["model.layers.0.linear_attn.conv1d.weight"].shape == (2 * kd + vd, 1, 4)
+    for name in ("tiny-dsa", "tiny-mla", "tiny-next"):
+        c2 = get_config(name)
+        s2 = {k: v.detach() for k, v in GPTModel(c2, seed=4).named_parameters()}
+        h2 = H.convert_state_to_hf(c2, s2)
+        b2 = H.hf_to_megatron_state(c2, h2)
+        assert all(torch.equal(b2[k], v) for k, v in s2.items()) and len(b2) == len(s2), name
+    h2 = H.convert_state_to_hf(get_config("tiny-dsa"), {k: v.detach() for k, v in GPTModel(get_config("tiny-dsa"), seed=4).named_parameters()})
+    assert {"model.layers.0.self_attn.kv_a_proj_with_mqa.weight", "model.layers.0.self_attn.q_b_proj.weight",
+            "model.layers.1.self_attn.indexer.wk.weight"} <= set(h2)
+    # on disk -> trainer model and rollout engine
+    d_ = str(tmp_path / "hybrid")
+    H.save_hf_checkpoint(d_, cfg, hf)
+    fresh = GPTModel(cfg, seed=99)
+    from relax_b200.parallel.state import single_process_state
+
+    H.load_hf_into_model(d_, cfg, single_process_state(), fresh)
+    assert all(torch.equal(p_.detach(), st[n]) for n, p_ in fresh.named_parameters())
+    eng = RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=64, block_size=8)
+    H.load_hf_into_rollout(d_, cfg, eng.weights)
+    out = eng.generate([[5, 6, 7, 8]], SamplingParams(temperature=0.0, max_new_tokens=4))[0].output
+    seq = [5, 6, 7, 8]
+    for _ in range(4):
+        t = torch.tensor(seq)
+        with torch.no_grad():
+            h = model(t, torch.arange(len(seq)), torch.tensor([0, len(seq)], dtype=torch.int32), max_seqlen=len(seq))
+        seq.append(int((h[-1].float() @ model.lm_head_weight()[:cfg.vocab_size].float().t()).argmax()))
+    assert out == seq[4:]
