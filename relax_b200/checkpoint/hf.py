@@ -334,6 +334,30 @@ def hf_config_dict(cfg: ModelConfig) -> dict:
             d.update(first_k_dense_replace=cfg.moe_first_dense_layers)
         if cfg.moe_router_score == "sigmoid":
             d.update(scoring_func="sigmoid", routed_scaling_factor=cfg.moe_routed_scaling_factor, n_routed_experts=cfg.num_experts)
+        if cfg.moe_router_bias:         # aux-loss-free balancing: a selection bias per expert (DeepSeek-V3 "noaux_tc")
+            d["topk_method"] = "noaux_tc"
+    d["attention_bias"] = bool(cfg.qkv_bias)
+    if not cfg.is_moe and not cfg.qk_layernorm and not cfg.qkv_bias:
+        d["architectures"] = ["LlamaForCausalLM"]
+    if cfg.rotary_percent < 1.0:
+        d["partial_rotary_factor"] = cfg.rotary_percent
+    if cfg.linear_attention_freq > 0:
+        # Qwen3-Next / Qwen3.5: every ``full_attention_interval``-th layer is (gated) softmax attention, the others
+        # Gated DeltaNet with these head counts; norms are stored zero-centred
+        d.update(architectures=["Qwen3NextForCausalLM"], model_type="qwen3_next", full_attention_interval=cfg.linear_attention_freq,
+                 linear_num_key_heads=cfg.gdn_k_heads, linear_num_value_heads=cfg.gdn_v_heads, linear_key_head_dim=cfg.gdn_head_dim,
+                 linear_value_head_dim=cfg.gdn_head_dim, linear_conv_kernel_dim=4, attn_output_gate=bool(cfg.attention_output_gate),
+                 zero_centered_norms=bool(cfg.layernorm_zero_centered))
+    elif cfg.dsa_topk > 0 or cfg.multi_latent_attention:
+        # DeepSeek-V3 / GLM-MoE-DSA: latent attention ranks and head splits; ``index_topk`` > 0 adds the lightning indexer
+        d.update(architectures=["GlmMoeDsaForCausalLM" if cfg.dsa_topk > 0 else "DeepseekV3ForCausalLM"],
+                 model_type="glm_moe_dsa" if cfg.dsa_topk > 0 else "deepseek_v3", q_lora_rank=cfg.dsa_q_lora, kv_lora_rank=cfg.dsa_kv_lora,
+                 qk_nope_head_dim=cfg.dsa_nope, qk_rope_head_dim=cfg.dsa_rope, v_head_dim=cfg.dsa_v_head, index_topk=cfg.dsa_topk,
+                 index_n_heads=cfg.dsa_index_heads, index_head_dim=cfg.dsa_index_dim)
+    elif cfg.sandwich_norm:
+        d.update(architectures=["Glm4ForCausalLM"], model_type="glm4")
+    if cfg.layernorm_zero_centered:
+        d["zero_centered_norms"] = True
     return d
 
 
@@ -485,6 +509,26 @@ def config_from_hf(path: str) -> ModelConfig:
                   moe_first_dense_layers=d.get("first_k_dense_replace", 0) or 0)
         if d.get("scoring_func") == "sigmoid":
             kw.update(moe_router_score="sigmoid", moe_routed_scaling_factor=float(d.get("routed_scaling_factor", 1.0)))
+        if d.get("topk_method") == "noaux_tc":
+            kw["moe_router_bias"] = True
+    if "attention_bias" in d:
+        kw["qkv_bias"] = bool(d["attention_bias"])
+    if d.get("partial_rotary_factor") is not None:
+        kw["rotary_percent"] = float(d["partial_rotary_factor"])
+    if d.get("full_attention_interval"):            # Qwen3-Next / Qwen3.5 hybrids
+        kw.update(linear_attention_freq=int(d["full_attention_interval"]), gdn_k_heads=d.get("linear_num_key_heads", 2),
+                  gdn_v_heads=d.get("linear_num_value_heads", 4), gdn_head_dim=d.get("linear_key_head_dim", 32),
+                  attention_output_gate=bool(d.get("attn_output_gate", True)), qk_layernorm=True,
+                  layernorm_zero_centered=bool(d.get("zero_centered_norms", True)))
+    elif d.get("kv_lora_rank"):                     # DeepSeek-V3 / GLM-MoE-DSA latent attention
+        kw.update(dsa_q_lora=d.get("q_lora_rank") or 64, dsa_kv_lora=d["kv_lora_rank"], dsa_nope=d.get("qk_nope_head_dim", 16),
+                  dsa_rope=d.get("qk_rope_head_dim", 8), dsa_v_head=d.get("v_head_dim", 16), dsa_topk=int(d.get("index_topk", 0) or 0),
+                  dsa_index_heads=d.get("index_n_heads", 4), dsa_index_dim=d.get("index_head_dim", 16), qkv_bias=False)
+        kw["multi_latent_attention"] = kw["dsa_topk"] == 0
+    elif "Glm4" in arch:
+        kw.update(sandwich_norm=True, qk_layernorm=False)
+    if "zero_centered_norms" in d:
+        kw["layernorm_zero_centered"] = bool(d["zero_centered_norms"])
     return ModelConfig(**kw)
 
 
