@@ -48,6 +48,22 @@ def megatron_to_hf(cfg: ModelConfig, name: str, p: torch.Tensor) -> list:
     if name == "value_head.weight":
         return [("score.weight", p)]
     mt = re.match(r"mtp\.layers\.(\d+)\.(.+)", name)
+    if mt and cfg.linear_attention_freq > 0:
+        # Qwen3-Next / Qwen3.5 convention (relax/backends/megatron/weight_conversion/qwen3_next.py _convert_mtp_layer
+        # :6-41): the block lives under ``mtp.*``; its projection takes [hidden | embedding], the other way round
+        k_, sub = int(mt.group(1)), mt.group(2)
+        own = {"enorm.weight": "mtp.pre_fc_norm_embedding.weight", "hnorm.weight": "mtp.pre_fc_norm_hidden.weight",
+               "final_layernorm.weight": "mtp.norm.weight"}
+        if sub in own:
+            return [(own[sub], p)]
+        if sub == "eh_proj.weight":
+            e, h_ = p.chunk(2, dim=1)
+            return [("mtp.fc.weight", torch.cat([h_, e], 1))]
+        if sub.startswith("transformer_layer."):
+            li = cfg.num_layers + k_              # the index the block's layer was built with
+            return [(n.replace(f"model.layers.{li}.", f"mtp.layers.{k_}."), t)
+                    for n, t in megatron_to_hf(cfg, f"decoder.layers.{li}." + sub[len("transformer_layer."):], p)]
+        raise ValueError(f"unknown MTP parameter {name!r}")
     if mt:      # DeepSeek-V3 convention: MTP depth k lives at layer index num_layers + k
         li, sub = cfg.num_layers + int(mt.group(1)), mt.group(2)
         own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
@@ -248,7 +264,15 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
         out["output_layer.weight"] = hf.get("lm_head.weight", hf["model.embed_tokens.weight"])
     for i in range(cfg.num_layers + cfg.mtp_num_layers):
         pre, b = f"model.layers.{i}.", f"decoder.layers.{i}."
-        if i >= cfg.num_layers:
+        if i >= cfg.num_layers and cfg.linear_attention_freq > 0:        # Qwen3-Next style ``mtp.*`` names
+            k = i - cfg.num_layers
+            pre, b = f"mtp.layers.{k}.", f"mtp.layers.{k}.transformer_layer."
+            out[f"mtp.layers.{k}.enorm.weight"] = hf["mtp.pre_fc_norm_embedding.weight"]
+            out[f"mtp.layers.{k}.hnorm.weight"] = hf["mtp.pre_fc_norm_hidden.weight"]
+            out[f"mtp.layers.{k}.final_layernorm.weight"] = hf["mtp.norm.weight"]
+            h_, e = hf["mtp.fc.weight"].chunk(2, dim=1)
+            out[f"mtp.layers.{k}.eh_proj.weight"] = torch.cat([e, h_], 1)
+        elif i >= cfg.num_layers:
             k = i - cfg.num_layers
             b = f"mtp.layers.{k}.transformer_layer."
             out[f"mtp.layers.{k}.enorm.weight"] = hf[pre + "enorm.weight"]
@@ -257,7 +281,7 @@ def hf_to_megatron_state(cfg: ModelConfig, hf: dict) -> dict:
             out[f"mtp.layers.{k}.final_layernorm.weight"] = hf[pre + "shared_head.norm.weight"]
         from ..models.hybrid import mixer_kind
 
-        kind = mixer_kind(cfg, i) if i < cfg.num_layers else "attention"
+        kind = mixer_kind(cfg, i)          # the draft block's layer is built by the same rule, from its index
         if kind == "gdn":
             _gdn_from_hf(cfg, hf, pre, b, out)
         elif kind == "dsa":
