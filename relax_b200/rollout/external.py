@@ -42,6 +42,7 @@ class ExternalEngine:
         from .router import Router
 
         self.timeout_s, self.check_fields = timeout_s, tuple(check_fields)
+        self.max_retries = 3                     # rounds of re-routing the prompt groups of servers that failed
         self.router = Router()                                           # membership, load, draining, health of the servers
         clients = [self.connect(a) for a in addrs]
         self.weights = RolloutWeights(cfg, 1, 0, device, dtype)          # staging, in the servers' layout (TP 1)
@@ -91,9 +92,35 @@ class ExternalEngine:
                 "running_per_engine": sum(i.get("running", 0) for i in infos) / n,
                 "kv_cache_utilization": used / n, "num_engines": float(len(infos))}
 
+    def readmit_recovered(self) -> list:
+        """Servers that were taken out of rotation and answer again get the CURRENT weights and only then requests."""
+        back = []
+        for wid, w in self.router.workers().items():
+            if w["healthy"]:
+                continue
+            c = self.router.handle(wid)
+            try:
+                if c.health():
+                    self.ship_current_weights(c)
+                    self.router.readmit(wid)
+                    back.append(wid)
+            except Exception:  # noqa: BLE001 - still down
+                pass
+        return back
+
     # ------------------------------------------------------------------ what WeightSync calls
     def _all(self, fn):
-        return list(self._pool.map(fn, self.clients))
+        """``fn`` on every server in rotation; one that fails is taken out (it is brought up to date when it returns)."""
+        live = [(wid, self.router.handle(wid)) for wid, w in self.router.workers().items() if w["healthy"]]
+        if not live:
+            raise RuntimeError("no external engine is reachable")
+        res = list(self._pool.map(lambda it: _guard(lambda c: fn(c), it[1]), live))
+        bad = [wid for (wid, _), r in zip(live, res) if r is not None]
+        for wid in bad:
+            self.router.quarantine(wid)
+        if len(bad) == len(live):
+            raise RuntimeError(f"every external engine failed: {[r for r in res if r is not None][0]}")
+        return res
 
     def pause_generation(self):
         self.paused = True
@@ -114,22 +141,17 @@ class ExternalEngine:
 
     # ------------------------------------------------------------------ what the rollout loop calls
     def generate(self, prompts, params, group_keys=None, images=None):
-        """Prompt groups are kept together (prefix sharing on the server) and spread over the servers in contiguous
-        runs; results come back in the order of ``prompts``."""
+        """Prompt groups are kept together (prefix sharing on the server) and spread over the servers by load; the groups
+        of a server that fails are generated again on the others.  Results come back in the order of ``prompts``."""
         if images is not None and any(images):
             raise NotImplementedError("image prompts do not travel over the HTTP surface")
+        if any(not w["healthy"] for w in self.router.workers().values()):
+            self.readmit_recovered()
         n = len(prompts)
         keys = list(group_keys) if group_keys is not None else list(range(n))
         groups: dict = {}
         for i in range(n):
             groups.setdefault(keys[i], []).append(i)
-        # the router picks a server per prompt group: least loaded among the healthy ones that are not draining
-        shares: dict = {}
-        taken = []
-        for key, idx in groups.items():
-            wid = self.router.acquire(key)
-            taken.append(wid)
-            shares.setdefault(wid, []).extend(idx)
         out = [None] * n
 
         def run(item):
@@ -138,17 +160,34 @@ class ExternalEngine:
             for i, r in zip(idx, self.router.handle(wid).generate([prompts[i] for i in idx], sp)):
                 out[i] = r
 
-        failed = set()
-        try:
-            for (wid, _), res in zip(shares.items(), self._pool.map(lambda it: _guard(run, it), shares.items())):
-                if res is not None:
-                    failed.add(wid)
-                    err = res
-        finally:
-            for wid in taken:
-                self.router.release(wid, failed=wid in failed)
-        if failed:
-            raise RuntimeError(f"external engine(s) {sorted(failed)} failed: {err}")
+        todo, err, attempt = dict(groups), None, 0
+        while todo:
+            # the router picks a server per prompt group: least loaded among the healthy ones that are not draining
+            shares: dict = {}
+            taken = []
+            for key, idx in todo.items():
+                wid = self.router.acquire(key)          # raises NoHealthyWorker when nothing is left to try
+                taken.append(wid)
+                shares.setdefault(wid, []).extend(idx)
+            failed = set()
+            try:
+                for (wid, _), res in zip(shares.items(), self._pool.map(lambda it: _guard(run, it), list(shares.items()))):
+                    if res is not None:
+                        failed.add(wid)
+                        err = res
+            finally:
+                for wid in taken:
+                    self.router.release(wid, failed=wid in failed)
+            # prompt groups of a server that failed go to the others; a server that keeps failing is quarantined by the
+            # router (and comes back when it answers health probes again)
+            todo = {key: idx for key, idx in todo.items() if any(out[i] is None for i in idx)}
+            if todo:
+                attempt += 1
+                self.stats["failovers"] = self.stats.get("failovers", 0) + len(todo)
+                for wid in failed:
+                    self.router.quarantine(wid)
+                if attempt > self.max_retries:
+                    raise RuntimeError(f"external engine(s) {sorted(failed)} failed: {err}")
         with self._lock:
             self.stats["decode_tokens"] += sum(len(r.output) for r in out)
             self.stats["prefill_tokens"] += sum(len(p) for p in prompts)

@@ -99,6 +99,22 @@ class Router:
             if failed:
                 self._note_failure(wid, w)
 
+    def quarantine(self, wid: Hashable):
+        """Take ``wid`` out of rotation now (a request to it failed outright); health probes readmit it."""
+        with self._lock:
+            w = self._workers.get(wid)
+            if w is not None and w.healthy:
+                w.healthy = False
+                w.consecutive_failures = max(w.consecutive_failures, self.max_failures)
+                self._sticky = {k: v for k, v in self._sticky.items() if v[0] != wid}
+
+    def readmit(self, wid: Hashable):
+        """Put ``wid`` back into rotation (its owner has checked it and brought it up to date)."""
+        with self._lock:
+            w = self._workers.get(wid)
+            if w is not None:
+                w.healthy, w.consecutive_failures = True, 0
+
     def handle(self, wid: Hashable):
         return self._workers[wid].handle
 

@@ -254,3 +254,54 @@ def test_external_engines_driven_by_the_colocated_loop():
     finally:
         for s in servers:
             s.close()
+
+
+def test_external_engine_fails_over_when_a_server_dies():
+    """A server that stops answering in the middle of a job: its prompt groups are generated by the other one, the dead
+    server is out of rotation, and weight updates report the failure instead of hanging."""
+    import torch
+
+    from relax_b200.models.config import get_config
+    from relax_b200.rollout.engine import RolloutEngine, SamplingParams
+    from relax_b200.rollout.external import ExternalEngine
+    from relax_b200.rollout.http_server import EngineServer
+    from relax_b200.rollout.router import NoHealthyWorker
+
+    cfg = get_config("tiny")
+    servers = [EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, seed=i)) for i in range(2)]
+    try:
+        ext = ExternalEngine(cfg, [s.url for s in servers], "cpu", torch.float32, timeout_s=20.0)
+        prompts = [[5 + i, 6, 7, 8] for i in range(6)]
+        sp = SamplingParams(temperature=0.0, max_new_tokens=4)
+        first = ext.generate(prompts, sp, group_keys=list(range(6)))
+        assert all(len(r.output) == 4 for r in first) and all(s.served > 0 for s in servers)
+        servers[1].close()
+        again = ext.generate(prompts, sp, group_keys=list(range(10, 16)))
+        assert all(len(r.output) == 4 for r in again) and ext.stats["failovers"] >= 1
+        w = ext.router.workers()
+        assert w[servers[1].url]["healthy"] is False and w[servers[0].url]["healthy"] is True
+        third = ext.generate(prompts, sp, group_keys=list(range(20, 26)))          # no request reaches the dead server any more
+        assert all(len(r.output) == 4 for r in third)
+        # weight updates go to the servers in rotation only; a replacement on the same address is brought up to date
+        # before it gets requests again
+        with torch.no_grad():
+            for t in ext.weights.p.values():
+                t.fill_(0.01)
+        ext.update_weight_version(5)
+        assert servers[0].engine.weight_version == 5
+        port = int(servers[1].url.rsplit(":", 1)[1])
+        servers[1] = EngineServer(RolloutEngine(cfg, device="cpu", dtype=torch.float32, num_kv_blocks=128, block_size=8, seed=9), port=port)
+        fourth = ext.generate(prompts, sp, group_keys=list(range(30, 36)))
+        assert all(len(r.output) == 4 for r in fourth) and ext.router.workers()[servers[1].url]["healthy"]
+        assert servers[1].engine.weight_version == 5 and float(servers[1].engine.weights.p["final_norm"][0]) == pytest.approx(0.01)
+        servers[1].close()
+        servers[0].close()
+        with pytest.raises((NoHealthyWorker, RuntimeError)):
+            ext.generate(prompts[:1], sp)
+        ext.close()
+    finally:
+        for s in servers:
+            try:
+                s.close()
+            except Exception:  # noqa: BLE001 - already closed above
+                pass
