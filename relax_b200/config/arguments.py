@@ -510,8 +510,6 @@ def validate_args(a: argparse.Namespace) -> argparse.Namespace:
             raise ValueError("speculative decoding drafts with the multi-token-prediction block: set --mtp-num-layers")
         if a.engine_speculative_eagle_topk != 1:
             raise ValueError("--sglang-speculative-eagle-topk: one chain of proposals (top-k 1) is implemented")
-        if getattr(a, "fully_async", False) and not getattr(a, "hybrid", False):
-            raise ValueError("speculative decoding is wired into the colocated loop (the MTP block's weights travel with its sync plan)")
     if a.rollout_external:
         if not a.rollout_external_engine_addrs:
             raise ValueError("--rollout-external needs --rollout-external-engine-addrs host:port [host:port ...]")

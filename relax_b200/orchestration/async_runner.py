@@ -71,7 +71,8 @@ def build_disagg_runner(args, model_cfg, train_cfg, device, start_rollout_id: in
         max_running=_get(args, "engine_max_running", 256), use_cuda_graph=not _get(args, "engine_disable_cuda_graph", False),
         num_rollout=args.num_rollout - start_rollout_id, max_staleness=args.max_staleness,
         update_weights_interval=args.update_weights_interval, seed=args.seed, rollout_seed=args.rollout_seed,
-        weight_push=_get(args, "weight_push", "peer"), num_iters_per_train_update=_get(args, "num_iters_per_train_update", 1) or 1)
+        weight_push=_get(args, "weight_push", "peer"), speculative=bool(_get(args, "engine_speculative_algorithm", None)),
+        speculative_steps=int(_get(args, "engine_speculative_num_steps", 1) or 1), num_iters_per_train_update=_get(args, "num_iters_per_train_update", 1) or 1)
     return DisaggRunner(DisaggregatedRL(cfg, device=device))
 
 

@@ -73,6 +73,8 @@ class DisaggConfig:
     num_rollout: int = 4
     max_staleness: int = 1
     update_weights_interval: int = 1
+    speculative: bool = False             # the engines draft with the model's MTP block (its weights are pushed with the rest)
+    speculative_steps: int = 1
     num_iters_per_train_update: int = 1   # > 1: the engines publish finished prompt groups in that many parts per rollout
                                           # and the trainer runs its forward-only passes on each part as it arrives
     image_grid_side: int = 0              # vision-language models: patches per side of the synthetic images (0: 4 x merge size)
@@ -169,7 +171,7 @@ class DisaggregatedRL:
                                         max_running=cfg.max_running, seed=cfg.rollout_seed + self.engine_id,
                                         use_cuda_graph=cfg.use_cuda_graph, memory_saver=True if cuda else False,
                                         max_model_len=cfg.prompt_len + cfg.max_response_len, eos_token_id=cfg.eos_token_id,
-                                        weights_shared_path=shm)
+                                        weights_shared_path=shm, speculative=cfg.speculative, speculative_steps=cfg.speculative_steps)
             self._shm = shm
             if cfg.weight_push == "peer":
                 self.region = SharedWeightRegion(self.engine.weights, self.tag, self.rank)
@@ -197,11 +199,11 @@ class DisaggregatedRL:
             mine = [e for i, e in enumerate(self.engines) if i % dp == my_dp]
             if cfg.weight_push == "peer":
                 self.pusher = PeerWeightPusher(cfg.model, TrainerLayout(tp=cfg.trainer_tp), rtp, self.ps.tp.rank, mine,
-                                               self.tag, device, dtype)
+                                               self.tag, device, dtype, mtp=cfg.speculative)
         if cfg.weight_push == "broadcast" and (self.is_rollout or (self.is_trainer and self.ps.dp.rank == 0)):
             # one group per source rank of replica 0: a trainer rank takes part in its own group only
             self.bcast = [BroadcastPusher(cfg.model, TrainerLayout(tp=cfg.trainer_tp), rtp, tr[:cfg.trainer_tp], self.engines,
-                                          g, device, dtype, src_index=i)
+                                          g, device, dtype, src_index=i, mtp=cfg.speculative)
                           for i, g in enumerate(self.bcast_groups) if self.is_rollout or self.rank == tr[i]]
         self.metrics: list = []
         self.stats = {"idle_s": 0.0, "busy_s": 0.0, "sync_ms": [], "push_kernel_ms": [], "rollout_started": []}

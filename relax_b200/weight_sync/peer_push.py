@@ -92,9 +92,9 @@ class PeerRegion:
     """Importer side (a trainer rank): another rank's flat weight buffer mapped here, with per-parameter views."""
 
     def __init__(self, cfg: ModelConfig, rollout_tp: int, tag: str, owner_rank: int, device, dtype, rollout_ep: int = 1,
-                 timeout: float = 120.0):
+                 timeout: float = 120.0, mtp: bool = False):
         self.device, self.dtype = torch.device(device), dtype
-        shapes, offsets, numel = rollout_layout(cfg, rollout_tp, rollout_ep)
+        shapes, offsets, numel = rollout_layout(cfg, rollout_tp, rollout_ep, mtp)
         payload, fds = fetch_fds(socket_path(tag, owner_rank), timeout=timeout)
         if int(payload["numel"]) != numel:
             raise RuntimeError(f"rollout rank {owner_rank} holds {payload['numel']} elements, the layout says {numel}")
@@ -132,9 +132,10 @@ class PeerWeightPusher:
     feeds.  ``engines`` is a list of global-rank lists (one per engine, ordered by the engine's TP rank)."""
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int, my_src_rank: int,
-                 engines: Sequence[Sequence[int]], tag: str, device, dtype):
+                 engines: Sequence[Sequence[int]], tag: str, device, dtype, mtp: bool = False):
+        # ``mtp``: the engines also hold the first multi-token-prediction block (they speculate with it)
         self.cfg, self.device = cfg, torch.device(device)
-        plan = build_plan(cfg, trainer_layout, rollout_tp, 1)
+        plan = build_plan(cfg, trainer_layout, rollout_tp, 1, mtp=mtp)
         self.regions: dict = {}
         self.work: list = []      # (region, blocks)
         for eng in engines:
@@ -143,7 +144,7 @@ class PeerWeightPusher:
                 if not blocks:
                     continue
                 if grank not in self.regions:
-                    self.regions[grank] = PeerRegion(cfg, rollout_tp, tag, grank, device, dtype)
+                    self.regions[grank] = PeerRegion(cfg, rollout_tp, tag, grank, device, dtype, mtp=mtp)
                 self.work.append((self.regions[grank], blocks))
         self.bytes_per_push = sum(b.rows * b.cols for _, bl in self.work for b in bl) * torch.empty(0, dtype=dtype).element_size()
         self._table, self._key = None, None
@@ -195,11 +196,11 @@ class BroadcastPusher:
     ``rollout_weights`` None on sources)."""
 
     def __init__(self, cfg: ModelConfig, trainer_layout: TrainerLayout, rollout_tp: int, src_global_ranks: Sequence[int],
-                 engines: Sequence[Sequence[int]], group, device, dtype, src_index: Optional[int] = None):
+                 engines: Sequence[Sequence[int]], group, device, dtype, src_index: Optional[int] = None, mtp: bool = False):
         # ``src_index``: this object moves the blocks of ONE source rank (its group holds that rank and the
         # destinations); None: all sources through one group that contains them all
         self.src_index = src_index
-        self.plan = build_plan(cfg, trainer_layout, rollout_tp, 1)
+        self.plan = build_plan(cfg, trainer_layout, rollout_tp, 1, mtp=mtp)
         self.src, self.engines, self.group = list(src_global_ranks), [list(e) for e in engines], group
         self.device, self.dtype = torch.device(device), dtype
         self.me = dist.get_rank() if dist.is_initialized() else 0

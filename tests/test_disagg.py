@@ -10,7 +10,7 @@ import torch
 from tests._mp import run_distributed
 
 
-def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_iters=1):
+def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_iters=1, speculative=False):
     from relax_b200.algo.loss import LossConfig
     from relax_b200.models.config import get_config
     from relax_b200.orchestration.disagg import DisaggConfig, DisaggregatedRL
@@ -21,13 +21,14 @@ def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_it
 
     ranks = assign_ranks({"actor": (1, n_train), "rollout": (1, world - n_train)}, world, colocate=False)
     assert ranks["actor"] == tuple(range(n_train)) and ranks["rollout"] == tuple(range(n_train, world))
-    mcfg = get_config("tiny")
+    mcfg = get_config("tiny", mtp_num_layers=1) if speculative else get_config("tiny")
     cfg = DisaggConfig(
         model=mcfg, train=TrainConfig(n_samples_per_prompt=2, global_batch_size=8, pad_multiple=1, max_tokens_per_gpu=512,
                                       loss=LossConfig(use_kl_loss=True, kl_loss_coef=0.001), optim=OptimizerConfig(lr=1e-2)),
         trainer_ranks=ranks["actor"], rollout_ranks=ranks["rollout"], trainer_tp=trainer_tp, rollout_tp=rollout_tp,
         rollout_batch_size=4, prompt_len=8, max_response_len=6, kv_blocks=64, kv_block_size=4, num_rollout=3, max_staleness=1,
-        weight_push=push, tag=f"t{port_tag}", handshake_timeout_s=120.0, num_iters_per_train_update=num_iters)
+        weight_push=push, tag=f"t{port_tag}", handshake_timeout_s=120.0, num_iters_per_train_update=num_iters,
+        speculative=speculative, speculative_steps=2)
     run = DisaggregatedRL(cfg, device="cpu")
     out = run.run()
     res = {"role": "actor" if run.is_trainer else "rollout"}
@@ -36,6 +37,7 @@ def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_it
     if run.is_trainer:
         res["metrics"] = [(rid, {k: float(v) for k, v in m.items()}) for rid, m in out]
         res["stats"] = {k: v for k, v in run.stats.items() if isinstance(v, (int, float))}
+        res["mtp"] = {k: v.detach().numpy().copy() for k, v in run.actor.named_local_params() if k.startswith("mtp.layers.0.eh_proj")}
         res["version"] = run.actor.weight_version
         res["params"] = {k: v.detach().numpy().copy() for k, v in run.actor.named_local_params()} if trainer_tp == 1 else None
     else:
@@ -43,6 +45,7 @@ def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_it
         res["version"] = run.engine.weight_version
         res["weights"] = {k: v.numpy().copy() for k, v in run.engine.weights.p.items()}
         res["tp_rank"] = run.engine.tp.rank
+        res["spec"] = {k: run.engine.stats.get(k, 0) for k in ("spec_draft_tokens", "spec_verify_steps")}
     dist.barrier()
     run.close()
     return res
@@ -140,3 +143,14 @@ def test_streamed_parts_forward_early_and_train_like_the_whole_batch():
     for (_, ma), (_, mb) in zip(a["metrics"][:1], b["metrics"][:1]):          # later rollouts depend on the overlap timing
         assert ma["response_tokens"] == mb["response_tokens"]
         assert abs(ma["loss"] - mb["loss"]) < 1e-4 and abs(ma["grad_norm"] - mb["grad_norm"]) < 1e-3 * max(1.0, ma["grad_norm"])
+
+
+@pytest.mark.parametrize("push", ["peer", "broadcast"])
+def test_speculating_engines_on_disjoint_pools(push):
+    """Fully-async with engines that draft with the MTP block: the block's weights are pushed with the policy's (peer
+    stores and the broadcast arm) and the engines speculate with them."""
+    out = run_distributed(_worker, 2, push, 1, 1, 1, os.getpid() % 10000 + (11 if push == "peer" else 12), 1, True, timeout=600)
+    tr = [o for o in out if o["role"] == "actor"][0]
+    ro = [o for o in out if o["role"] == "rollout"][0]
+    assert tr["version"] == 3 and ro["version"] == 3 and ro["spec"]["spec_draft_tokens"] > 0 and ro["spec"]["spec_verify_steps"] > 0
+    assert torch.equal(torch.from_numpy(ro["weights"]["mtp.eh_proj"]), torch.from_numpy(tr["mtp"]["mtp.layers.0.eh_proj.weight"]))
