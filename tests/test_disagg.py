@@ -10,7 +10,7 @@ import torch
 from tests._mp import run_distributed
 
 
-def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_iters=1, speculative=False):
+def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_iters=1, speculative=False, model="tiny"):
     from relax_b200.algo.loss import LossConfig
     from relax_b200.models.config import get_config
     from relax_b200.orchestration.disagg import DisaggConfig, DisaggregatedRL
@@ -21,7 +21,7 @@ def _worker(rank, world, push, trainer_tp, rollout_tp, n_train, port_tag, num_it
 
     ranks = assign_ranks({"actor": (1, n_train), "rollout": (1, world - n_train)}, world, colocate=False)
     assert ranks["actor"] == tuple(range(n_train)) and ranks["rollout"] == tuple(range(n_train, world))
-    mcfg = get_config("tiny", mtp_num_layers=1) if speculative else get_config("tiny")
+    mcfg = get_config(model, mtp_num_layers=1) if speculative else get_config(model)
     cfg = DisaggConfig(
         model=mcfg, train=TrainConfig(n_samples_per_prompt=2, global_batch_size=8, pad_multiple=1, max_tokens_per_gpu=512,
                                       loss=LossConfig(use_kl_loss=True, kl_loss_coef=0.001), optim=OptimizerConfig(lr=1e-2)),
@@ -154,3 +154,20 @@ def test_speculating_engines_on_disjoint_pools(push):
     ro = [o for o in out if o["role"] == "rollout"][0]
     assert tr["version"] == 3 and ro["version"] == 3 and ro["spec"]["spec_draft_tokens"] > 0 and ro["spec"]["spec_verify_steps"] > 0
     assert torch.equal(torch.from_numpy(ro["weights"]["mtp.eh_proj"]), torch.from_numpy(tr["mtp"]["mtp.layers.0.eh_proj.weight"]))
+
+
+@pytest.mark.parametrize("model", ["tiny-qwen35", "tiny-dsa"])
+def test_hybrid_and_latent_families_on_disjoint_pools(model):
+    """Fully-async with a Gated-DeltaNet hybrid and with sparse latent attention: the engines serve the family and end
+    with the trainer's weights (the extra tensors travel through the same peer stores)."""
+    from relax_b200.models.config import get_config
+    from relax_b200.weight_sync.sync import oracle_rollout_state
+
+    out = run_distributed(_worker, 2, "peer", 1, 1, 1, os.getpid() % 10000 + (21 if model == "tiny-dsa" else 22), 1, False, model, timeout=600)
+    tr = [o for o in out if o["role"] == "actor"][0]
+    ro = [o for o in out if o["role"] == "rollout"][0]
+    assert tr["version"] == 3 and ro["version"] == 3 and all("loss" in m for _, m in tr["metrics"])
+    want = oracle_rollout_state(get_config(model), {k: torch.from_numpy(v) for k, v in tr["params"].items()}, 1, 0)
+    assert set(want) == set(ro["weights"])
+    for k, w in want.items():
+        assert torch.equal(torch.from_numpy(ro["weights"][k]), w), k
