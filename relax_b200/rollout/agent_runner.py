@@ -193,6 +193,10 @@ def _kill_group(proc: subprocess.Popen, grace_s: float = GRACE_S) -> int:
     return proc.poll() if proc.poll() is not None else -9
 
 
+_LIVE: set = set()            # agent processes of this daemon that have not exited yet
+_LIVE_LOCK = threading.Lock()
+
+
 def _serve_connection(conn: socket.socket, grace_s: float) -> None:
     """One connection owns one agent process: launch, then wait for its exit or for a terminate request."""
     proc = None
@@ -213,6 +217,8 @@ def _serve_connection(conn: socket.socket, grace_s: float) -> None:
         except Exception as e:  # noqa: BLE001 - reported to the owner of the connection
             _send(conn, {"error": f"{type(e).__name__}: {e}"})
             return
+        with _LIVE_LOCK:
+            _LIVE.add(proc)
         _send(conn, {"op": "started", "pid": proc.pid})
         stop = threading.Event()
 
@@ -242,6 +248,8 @@ def _serve_connection(conn: socket.socket, grace_s: float) -> None:
     finally:
         if proc is not None and proc.poll() is None:
             _kill_group(proc, grace_s)
+        with _LIVE_LOCK:
+            _LIVE.discard(proc)
         try:
             conn.shutdown(socket.SHUT_RDWR)
         except OSError:
@@ -274,6 +282,11 @@ def daemon_main(socket_path: str, grace_s: float = GRACE_S, parent_pid: Optional
             os.unlink(socket_path)
         except FileNotFoundError:
             pass
+        # the daemon leaves (its owner is gone or asked it to): no agent outlives it
+        with _LIVE_LOCK:
+            live = list(_LIVE)
+        for proc in live:
+            _kill_group(proc, min(grace_s, 1.0))
 
 
 _DAEMONS: dict = {}

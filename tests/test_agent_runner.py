@@ -206,3 +206,28 @@ def test_custom_group_advantage_for_agent_rollouts(tmp_path):
         assert abs(m["rollout/advantages"]) < 1e-6 and "loss" in m          # mean of -0.5 / +0.5 over equally long responses
     finally:
         R.stop_launcher_daemon(agent_pipeline._PIPELINE.socket_path)
+
+
+def test_no_agent_outlives_the_daemon(tmp_path):
+    """When the daemon leaves (its owner stopped it or died), the agents it started are ended with it."""
+    sock = str(tmp_path / "d.sock")
+    R.ensure_launcher_daemon(sock)
+    mark = tmp_path / "pid"
+    a = R.ManagedAgent(sock, R.AgentSpec(f"echo $$ > {mark}; sleep 60", str(tmp_path), {}, 120.0), "s", "g", {}, "http://127.0.0.1:1").start()
+    deadline = time.monotonic() + 5
+    while not mark.exists() and time.monotonic() < deadline:
+        time.sleep(0.02)
+    pid = int(mark.read_text())
+    os.kill(pid, 0)                                   # alive
+    R.stop_launcher_daemon(sock)
+    deadline = time.monotonic() + 6
+    while time.monotonic() < deadline:
+        try:
+            os.kill(pid, 0)
+        except ProcessLookupError:
+            break
+        time.sleep(0.05)
+    else:
+        pytest.fail("the agent survived its daemon")
+    with pytest.raises(R.AgentExecutionError):
+        a.wait(poll_s=5)
