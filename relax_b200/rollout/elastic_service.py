@@ -200,6 +200,19 @@ class ElasticControlServer:
                     self._reply(200, {"requests": reqs, "total_count": len(reqs), "status_filter": st})
                 elif self.path == "/health":
                     self._reply(200, {"status": "ok", "active": len(srv.pool.active())})
+                elif self.path == "/metrics":          # pool gauges in Prometheus text format
+                    st = [r.state.value for r in srv.pool.engines.values()]
+                    rows = [("relax_rollout_engines_active", st.count("active")), ("relax_rollout_engines_draining", st.count("draining")),
+                            ("relax_rollout_engines_failed", st.count("failed")),
+                            ("relax_rollout_scale_requests_pending", len([r for r in srv.requests.requests.values() if r["status"] in ("PENDING", "SYNCING")]))]
+                    if srv.autoscaler is not None:
+                        rows.append(("relax_rollout_autoscaler_decisions_total", len(srv.autoscaler.decisions)))
+                    body = "".join(f"# TYPE {n} gauge\n{n} {v}\n" for n, v in rows).encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/plain; version=0.0.4")
+                    self.send_header("Content-Length", str(len(body)))
+                    self.end_headers()
+                    self.wfile.write(body)
                 else:
                     self._reply(404, {"error": "unknown path"})
 

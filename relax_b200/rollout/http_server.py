@@ -60,6 +60,23 @@ class EngineServer:
                 path = self.path.split("?")[0].rstrip("/")
                 if path in ("/health", "/health_generate"):
                     return self._reply(200, {"status": "ok"})
+                if path == "/metrics":
+                    # Prometheus text format: what an external autoscaler (Prometheus + KEDA in the reference's set-up,
+                    # relax/utils/autoscaler/) scrapes from every engine
+                    e = server.engine
+                    used = 1.0 - e.bm.num_free / max(1, e.bm.num_blocks)
+                    rows = [("relax_engine_running_requests", "gauge", len(e.running)), ("relax_engine_waiting_requests", "gauge", len(e.waiting)),
+                            ("relax_engine_kv_cache_usage", "gauge", round(used, 6)), ("relax_engine_weight_version", "gauge", e.weight_version),
+                            ("relax_engine_requests_served_total", "counter", server.served),
+                            ("relax_engine_decode_tokens_total", "counter", e.stats.get("decode_tokens", 0)),
+                            ("relax_engine_prefill_tokens_total", "counter", e.stats.get("prefill_tokens", 0))]
+                    text = "".join(f"# TYPE {n} {t}\n{n} {v}\n" for n, t, v in rows).encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/plain; version=0.0.4")
+                    self.send_header("Content-Length", str(len(text)))
+                    self.end_headers()
+                    self.wfile.write(text)
+                    return None
                 if path in ("/get_server_info", "/get_model_info"):
                     e = server.engine
                     return self._reply(200, {"model": e.cfg.name, "weight_version": e.weight_version, "running": len(e.running),

@@ -238,6 +238,12 @@ def test_elastic_pool_of_external_engine_servers_in_a_training_job(tmp_path):
         assert servers[1].engine.weight_version == v1 + 1 and servers[2].engine.weight_version == v1 + 2
         eng = call(ctl, "/engines")
         assert eng[servers[1].url]["state"] == "removed" and eng[servers[2].url]["state"] == "active"
+        # what a Prometheus scraper sees: pool gauges on the control port, engine gauges on every server
+        text = urllib.request.urlopen(ctl + "/metrics", timeout=10).read().decode()
+        assert "relax_rollout_engines_active 2" in text and "relax_rollout_autoscaler_decisions_total 1" in text
+        text = urllib.request.urlopen(servers[0].url + "/metrics", timeout=10).read().decode()
+        assert "# TYPE relax_engine_kv_cache_usage gauge" in text and f"relax_engine_weight_version {v1 + 2}" in text
+        assert "relax_engine_requests_served_total" in text
         run.close()
     finally:
         for s in servers:
