@@ -397,6 +397,38 @@ class ColocatedGRPO:
         self.rollout_id = 0
         self.sync_weights()
 
+    # user code by path: (attribute, configuration field, positional arguments it must take)
+    RELOADABLE = (("custom_generate", "custom_generate_function_path", 3), ("rollout_function", "rollout_function_path", 3),
+                  ("reward_fn", "custom_rm_path", 1), ("group_filter", "dynamic_sampling_filter_path", 1),
+                  ("reward_post_process", "custom_reward_post_process_path", 1), ("sample_filter", "rollout_sample_filter_path", 2),
+                  ("data_postprocess", "rollout_data_postprocess_path", 2))
+
+    def reload_functions(self, names: Optional[Sequence[str]] = None) -> list:
+        """Load the configured user functions again from their files, between two steps of a running job (an edited
+        reward function or filter takes effect without a restart; relax/utils/reload_utils.py RELOADABLE_FUNCTIONS).
+        Returns the attributes that were reloaded; a function that fails to load keeps its old version."""
+        from ..rollout.custom_generate import reload_object
+
+        done = []
+        for attr, field_, npos in self.RELOADABLE:
+            path = getattr(self.cfg, field_, None)
+            if not path or (names is not None and attr not in names) or path.startswith("relax_b200."):
+                continue
+            if attr == "reward_fn" and self.cfg.defer_reward_to_post_process:
+                continue
+            try:
+                fn = reload_object(path)
+                if not callable(fn):
+                    raise TypeError(f"{path} is not callable")
+            except Exception as e:  # noqa: BLE001 - a broken edit must not take the run down
+                import warnings
+
+                warnings.warn(f"reload of {attr} from {path} failed, keeping the loaded version: {type(e).__name__}: {e}")
+                continue
+            setattr(self, attr, fn)
+            done.append(attr)
+        return done
+
     def close(self):
         """Collective over all ranks, before the process groups are destroyed: unmap the peers' symmetric buffers
         (tensor-parallel workspaces, the distributed optimizer's parameter / gradient buffers), meet, free this

@@ -420,6 +420,14 @@ class Controller:
             except ValueError:   # not the main thread (tests)
                 pass
 
+        def reload_handler(signum, frame):       # kill -HUP <pid>: user functions are loaded again before the next step
+            self._reload_requested = True
+
+        try:
+            signal.signal(signal.SIGHUP, reload_handler)
+        except (ValueError, AttributeError):
+            pass
+
     def training_loop(self) -> list:
         a = self.args
         self._install_signal_handlers()
@@ -442,6 +450,9 @@ class Controller:
         ref_every = _get(a, "ref_update_interval", None)
         while rid < a.num_rollout and not self._stop:
             t0 = time.perf_counter()
+            if getattr(self, "_reload_requested", False) and hasattr(self.runner, "reload_functions"):
+                self._reload_requested = False
+                print(f"[reload] user functions reloaded: {self.runner.reload_functions()}", flush=True)
             m = self._guarded_step()
             if m is None:                     # recovered from a failure: go on from where the restart left the job
                 rid = getattr(self.runner, "rollout_id", rid)

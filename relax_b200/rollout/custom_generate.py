@@ -51,6 +51,24 @@ def load_object(path: str) -> Any:
     return obj
 
 
+def reload_object(path: str) -> Any:
+    """Load ``path`` again from its source: the cached object is dropped and the module is re-executed (a user file is
+    re-read from disk, an importable module goes through ``importlib.reload``).  For hot-reloading user code in a
+    running job (relax/utils/reload_utils.py)."""
+    _CACHE.pop(path, None)
+    mod_part, sep, _ = path.rpartition(":")
+    if not sep:
+        mod_part, _, _ = path.rpartition(".")
+    if mod_part.endswith(".py") or os.sep in mod_part:
+        name = "relax_b200_user_" + hashlib.sha1(os.path.abspath(mod_part).encode()).hexdigest()[:12]
+        sys.modules.pop(name, None)
+        for k in [k for k in _CACHE if k.startswith(mod_part + ":")]:
+            _CACHE.pop(k, None)               # other attributes of the same file were bound to the old module
+    elif mod_part in sys.modules:
+        importlib.reload(sys.modules[mod_part])
+    return load_object(path)
+
+
 def load_function(path: str, min_positional: int = 0, name: str = "function") -> Callable:
     """``load_object`` plus a check that the callable accepts at least ``min_positional`` positional arguments."""
     fn = load_object(path)

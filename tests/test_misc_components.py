@@ -314,3 +314,28 @@ def test_rewards_deferred_to_the_post_process(tmp_path):
     mod = [v for k, v in sys.modules.items() if k.startswith("relax_b200_user_") and hasattr(v, "SEEN")][-1]
     assert mod.SEEN == [[0.0] * 4] and "loss" in m
     c.runner.close()
+
+
+def test_user_functions_are_reloaded_in_a_running_job(tmp_path):
+    """An edited reward function takes effect between two steps (``reload_functions``, also on SIGHUP); an edit that does
+    not import keeps the loaded version."""
+    import warnings
+
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+
+    f = tmp_path / "my_rm.py"
+    f.write_text("def score(sample):\n    return 1.0\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "3", "--rollout-max-response-len", "4", "--custom-rm-path", f"{f}:score", "--disable-rewards-normalization"])
+    c = Controller(a, device="cpu")
+    assert c.runner.step()["raw_reward_mean"] == 1.0
+    f.write_text("def score(sample):\n    return 3.0\n")
+    assert c.runner.reload_functions() == ["reward_fn"]
+    assert c.runner.step()["raw_reward_mean"] == 3.0
+    f.write_text("def score(sample:\n")            # a syntax error
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        assert c.runner.reload_functions() == [] and any("keeping the loaded version" in str(x.message) for x in w)
+    assert c.runner.step()["raw_reward_mean"] == 3.0
+    c.runner.close()
