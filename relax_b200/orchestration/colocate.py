@@ -730,7 +730,7 @@ class ColocatedGRPO:
                             max_new_tokens=cfg.eval_max_response_len or cfg.max_response_len)
         with self.timer.span("eval"):
             m = _eval(self.engine, cfg.eval_datasets, self.reward_fn, sp, decode=self.codec.decode if self.codec is not None else None,
-                      reward_key=cfg.eval_reward_key)
+                      reward_key=cfg.eval_reward_key, generate_fn=self.custom_generate)
         if cfg.offload_rollout:
             self.engine.release_memory_occupation(("kv_cache", "cuda_graph"))
         return m

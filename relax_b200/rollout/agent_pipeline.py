@@ -61,11 +61,12 @@ class AgentPipeline:
         self._seq = itertools.count(1)
 
     # ------------------------------------------------------------------ one rollout batch
-    def run(self, engine, samples: list, sampling) -> list:
+    def run(self, engine, samples: list, sampling, rollout_mode: Optional[str] = None) -> list:
         from .admission import AdmissionController
         from .http_server import EngineServer
         from .openai_api import ChatService, serve
 
+        mode = rollout_mode or self.rollout_mode            # "eval": agents see RELAX_ROLLOUT_MODE=eval, no custom advantages
         agents: Dict[str, ManagedAgent] = {}
         adm = None
         if self.use_admission and getattr(engine, "bm", None) is not None:
@@ -92,7 +93,7 @@ class AgentPipeline:
                 payload = {"prompt": s.prompt, "label": s.label, "metadata": s.metadata or {}, "group_index": s.group_index,
                            "index": s.index, "max_new_tokens": sampling.max_new_tokens}
                 try:
-                    a = ManagedAgent(launcher.socket_path, launcher.spec, sid, str(s.group_index), payload, url, self.rollout_mode)
+                    a = ManagedAgent(launcher.socket_path, launcher.spec, sid, str(s.group_index), payload, url, mode)
                     agents[sid] = a
                     a.start()
                     out = a.wait()
@@ -124,7 +125,7 @@ class AgentPipeline:
         for s in samples:
             if s.group_index in failed_groups:
                 self._drop(s)
-        if self.custom_advantage is not None and rollout_mode_is_train(self.rollout_mode):
+        if self.custom_advantage is not None and rollout_mode_is_train(mode):
             groups: Dict[object, list] = {}
             for s in samples:
                 if s.group_index not in failed_groups:
@@ -226,5 +227,12 @@ def command_generate(engine, samples, sampling_params):
     return _PIPELINE.run(engine, samples, sampling_params)
 
 
+def _command_generate_eval(engine, samples, sampling_params):
+    if _PIPELINE is None:
+        raise RuntimeError("agent_pipeline.configure(args) has not run")
+    return _PIPELINE.run(engine, samples, sampling_params, rollout_mode="eval")
+
+
+command_generate.eval_variant = _command_generate_eval
 command_generate.manages_inference_permit = True
 command_generate.stats = lambda: dict(_PIPELINE.stats) if _PIPELINE is not None else {}

@@ -103,9 +103,12 @@ def load_eval_datasets(pairs: Sequence[str], tokenize: Callable[[Any], list], in
 
 def evaluate(engine, datasets: Sequence[EvalDataset], reward_fn: Callable[[Sample], Any], sampling_defaults,
              decode: Optional[Callable[[list], str]] = None, reward_fns: Optional[Dict[str, Callable]] = None,
-             reward_key: Optional[str] = None) -> Dict[str, float]:
+             reward_key: Optional[str] = None, generate_fn: Optional[Callable] = None) -> Dict[str, float]:
     """Run every set through ``engine.generate`` (one call per set, all samples batched) and score it.
-    ``sampling_defaults`` is a :class:`~relax_b200.rollout.engine.SamplingParams`; per-set fields override it."""
+    ``sampling_defaults`` is a :class:`~relax_b200.rollout.engine.SamplingParams`; per-set fields override it.
+    ``generate_fn(engine, samples, sampling_params) -> samples``: the run's custom generate function produces the
+    evaluation samples as well (multi-turn environments, agent programs; the reference's ``--eval-function-path``
+    defaults to its rollout function); samples it has scored keep their reward."""
     import dataclasses as _dc
 
     metrics: Dict[str, float] = {}
@@ -116,9 +119,22 @@ def evaluate(engine, datasets: Sequence[EvalDataset], reward_fn: Callable[[Sampl
         n = ds.n_samples_per_prompt
         flat_prompts = [p for p in ds.prompts for _ in range(n)]
         keys = [i for i in range(len(ds.prompts)) for _ in range(n)]
-        res = engine.generate(flat_prompts, sp, group_keys=keys)
         score = (reward_fns or {}).get(ds.rm_type, reward_fn) if ds.rm_type else reward_fn
         groups: List[List[Sample]] = [[] for _ in ds.prompts]
+        if generate_fn is not None:
+            shells = [Sample(group_index=gi, index=j, prompt=(decode(list(p)) if decode is not None else list(p)), tokens=list(p),
+                             label=ds.labels[gi] if ds.labels else None, metadata=dict(ds.metadata[gi]) if ds.metadata else {})
+                      for j, (gi, p) in enumerate(zip(keys, flat_prompts))]
+            fn = getattr(generate_fn, "eval_variant", generate_fn)
+            for s in fn(engine, shells, sp):
+                if s.remove_sample:
+                    continue
+                if s.reward is None:
+                    s.reward = score(s)
+                groups[s.group_index].append(s)
+            metrics.update(summarize(ds.name, [g for g in groups if g], reward_key=reward_key))
+            continue
+        res = engine.generate(flat_prompts, sp, group_keys=keys)
         for gi, r in zip(keys, res):
             s = Sample(group_index=gi, index=len(groups[gi]), prompt=list(r.prompt), tokens=list(r.prompt) + list(r.output),
                        response_length=len(r.output), label=ds.labels[gi] if ds.labels else None,

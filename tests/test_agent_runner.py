@@ -231,3 +231,36 @@ def test_no_agent_outlives_the_daemon(tmp_path):
         pytest.fail("the agent survived its daemon")
     with pytest.raises(R.AgentExecutionError):
         a.wait(poll_s=5)
+
+
+def test_evaluation_runs_through_the_agent_pipeline(tmp_path):
+    """Held-out prompts are evaluated the way the policy is trained: agent processes (in eval mode) produce the samples."""
+    from relax_b200.config.arguments import parse_args
+    from relax_b200.orchestration.controller import Controller
+    from relax_b200.rollout import agent_pipeline
+
+    (tmp_path / "agent.py").write_text(AGENT.replace('"tool_calls": 2}', '"tool_calls": 2, "mode": os.environ["RELAX_ROLLOUT_MODE"]}'))
+    f = tmp_path / "prompts.jsonl"
+    f.write_text("\n".join(json.dumps({"prompt": f"task {i}", "label": None}) for i in range(2)) + "\n")
+    ev = tmp_path / "eval.jsonl"
+    ev.write_text("\n".join(json.dumps({"prompt": f"held out {i}", "label": None}) for i in range(3)) + "\n")
+    a = parse_args(["--model-name", "tiny", "--colocate", "--rollout-batch-size", "2", "--n-samples-per-prompt", "2", "--global-batch-size", "4",
+                    "--num-rollout", "1", "--rollout-max-response-len", "5", "--rollout-max-prompt-len", "256", "--prompt-data", str(f),
+                    "--input-key", "prompt", "--use-agentic-rollout", "--agent-command", f"{sys.executable} agent.py",
+                    "--agent-cwd", str(tmp_path), "--eval-prompt-data", "heldout", str(ev), "--eval-interval", "1"])
+    c = Controller(a, device="cpu")
+    try:
+        seen = []
+        real = agent_pipeline._PIPELINE._export
+
+        def spy(s, sess, out):
+            seen.append(out.metadata.get("mode"))
+            return real(s, sess, out)
+
+        agent_pipeline._PIPELINE._export = spy
+        m = c.runner.step()
+        assert "eval" in seen and "train" in seen
+        ek = [k for k in m if k.startswith("eval/heldout")]
+        assert ek and any("reward" in k or "score" in k or "mean" in k for k in ek), sorted(m)
+    finally:
+        R.stop_launcher_daemon(agent_pipeline._PIPELINE.socket_path)
